@@ -1,0 +1,303 @@
+/*
+ * libsofie_b200 -- C ABI of the B200 (sm_100a) runtime that SOFIE-emitted Session code calls.
+ *
+ * The reference emits, per Session, an object `sofieBLAS<tagAcc> blas{queue}`
+ * (core/src/RModel_ALPAKA.cxx:1138-1141), registers one configuration per contraction at
+ * Session construction (`blas.addOperationConfig(m,n,k,lda,ldb,ldc,ta,tb,Epilogue)`,
+ * core/src/RModel_ALPAKA.cxx:1334-1341) and then enqueues `blas.gemm / gemmrelu / matmul /
+ * gemmStridedBatched` (core/inc/SOFIE/operators/ROperator_Gemm.hxx:931-1098,
+ * core/inc/SOFIE/operators/ROperator_Conv.hxx:1039-1094) plus one alpaka kernel per
+ * memory-bound operator.  This header is the seam that replaces those calls:
+ *
+ *   sofie_b200_ctx      <->  the Session's queue + blas object   (one per Session / GPU / stream)
+ *   sofie_b200_*_plan   <->  one addOperationConfig entry        (created at Session init)
+ *   sofie_b200_*_enqueue<->  one blas.* call or alpaka enqueue   (records work on the stream only)
+ *
+ * Conventions
+ *  - plain pointers and sizes only; all tensors are row-major as ONNX defines them (no
+ *    column-major operand swap as in ROperator_Gemm.hxx:997-1016);
+ *  - every function returns 0 on success and a negative sofie_b200_status otherwise; nothing
+ *    throws across this boundary.  The emitted wrapper turns non-zero into std::runtime_error,
+ *    which is the reference's own error convention (core/src/RModel_ALPAKA.cxx:749-752);
+ *  - the ctx borrows the CUDA stream and every tensor pointer; it owns only plans, TMA
+ *    descriptors, a small status word and (for the *_host helpers) staging buffers;
+ *  - enqueue functions never synchronise.  Device-side problems (a bounded wait inside a
+ *    kernel that ran out) are written to a status word that sofie_b200_ctx_sync() reads;
+ *  - a ctx is thread-compatible, not thread-safe: one ctx per (thread, GPU), as a reference
+ *    Session is (core/src/RModel_ALPAKA.cxx:1283-1285).
+ */
+#ifndef SOFIE_B200_H
+#define SOFIE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SOFIE_B200_ABI_VERSION 1
+
+typedef enum sofie_b200_status {
+  SOFIE_B200_OK = 0,
+  SOFIE_B200_ERR_INVALID = -1,     /* bad argument / unsupported combination            */
+  SOFIE_B200_ERR_CUDA = -2,        /* a CUDA runtime or driver call failed               */
+  SOFIE_B200_ERR_DEVICE_WAIT = -3, /* a bounded wait inside a kernel gave up             */
+  SOFIE_B200_ERR_NO_DEVICE = -4,   /* no sm_100 device / driver entry point unavailable  */
+  SOFIE_B200_ERR_TOO_LARGE = -5    /* size beyond a documented static limit              */
+} sofie_b200_status;
+
+/* Element types.  The reference's ETensorType (core/inc/SOFIE/utils/SOFIE_common.hxx:29-32)
+ * names FLOAT, INT8, UINT8, INT32, BFLOAT16; F8E4M3 is the ONNX FLOAT8E4M3FN type (17). */
+typedef enum sofie_b200_dtype {
+  SOFIE_B200_F32 = 0,
+  SOFIE_B200_BF16 = 1,
+  SOFIE_B200_I8 = 2,
+  SOFIE_B200_F8E4M3 = 3,
+  SOFIE_B200_I32 = 4,
+  SOFIE_B200_U8 = 5
+} sofie_b200_dtype;
+
+/* Activations the reference can attach to a contraction or emits as its own operator:
+ * Relu (ROperator_Relu.hxx:47-114), LeakyRelu (ROperator_LeakyRelu.hxx), Gelu erf / tanh
+ * forms (ROperator_Gelu.hxx:62-98), Sigmoid (fused after Gemm in LinearWithSigmoid). */
+typedef enum sofie_b200_act {
+  SOFIE_B200_ACT_NONE = 0,
+  SOFIE_B200_ACT_RELU = 1,
+  SOFIE_B200_ACT_GELU_ERF = 2,
+  SOFIE_B200_ACT_GELU_TANH = 3,
+  SOFIE_B200_ACT_LEAKY_RELU = 4,
+  SOFIE_B200_ACT_SIGMOID = 5
+} sofie_b200_act;
+
+/* How the additive operand C of Gemm is broadcast (ROperator_Gemm.hxx:270-301,578-617). */
+typedef enum sofie_b200_bias_mode {
+  SOFIE_B200_BIAS_NONE = 0,
+  SOFIE_B200_BIAS_COL_F32 = 1,   /* C has shape [N]: one value per output column / channel   */
+  SOFIE_B200_BIAS_ROW_F32 = 2,   /* C has shape [M,1]                                         */
+  SOFIE_B200_BIAS_SCALAR_F32 = 3,/* C is a scalar                                             */
+  SOFIE_B200_BIAS_COL_I32 = 4,   /* int32 bias added to the int32 accumulator (QLinearConv)   */
+  SOFIE_B200_BIAS_FULL_F32 = 5,  /* C has shape [M,N] with row pitch ldc, multiplied by beta  */
+  SOFIE_B200_BIAS_ROW_I32 = 6    /* int32 bias per output row, added to the int32 accumulator */
+} sofie_b200_bias_mode;
+
+/*
+ * Fused epilogue of a contraction.  For accumulator value acc at (row i, column j) the
+ * kernels evaluate, with every step a separately rounded fp32 operation (no FMA contraction):
+ *
+ *   a = acc (+ bias_i32[j] / bias_i32[i] as an integer add when bias_mode == COL_I32 / ROW_I32)
+ *   v = (float)a
+ *   v = v * row_scale[i]          if row_scale
+ *   v = v * col_scale[j]          if col_scale
+ *   v = v * alpha                 if alpha != 1
+ *   v = v + bias                  (COL/ROW/SCALAR) or v + beta * C[i,j]   (FULL)
+ *   v = v + residual[i,j]         if residual
+ *   v = act(v)
+ *   out dtype F32: v;  BF16: round-to-nearest-even;  I32: a (integer accumulators only);
+ *   I8/U8: q = rintf(out_scale == 1 ? v : v / out_scale) + out_zero_point, saturated
+ *          (ONNX QuantizeLinear / QLinearMatMul rounding: half to even, then saturate).
+ *
+ * BatchNorm folded into a contraction is expressed as col_scale = gamma/sqrt(var+eps) and
+ * a COL_F32 bias = beta_bn - mean*col_scale (+ conv bias * col_scale); the reference computes
+ * the same scale at code-generation time (ROperator_BatchNormalization.hxx:100-109).
+ */
+typedef struct sofie_b200_epilogue {
+  const float *row_scale;   /* [M] or NULL                                   */
+  const float *col_scale;   /* [N] or NULL                                   */
+  float alpha;              /* Gemm alpha; 1 = skip                          */
+  float beta;               /* multiplies C when bias_mode == FULL_F32       */
+  int32_t bias_mode;        /* sofie_b200_bias_mode                          */
+  const void *bias;         /* see bias_mode                                 */
+  int64_t ldc;              /* row pitch (elements) of C for FULL_F32        */
+  const void *residual;     /* [M,N] added before the activation, or NULL    */
+  int32_t residual_dtype;   /* F32 or BF16                                   */
+  int64_t ldr;              /* row pitch (elements) of residual              */
+  int32_t act;              /* sofie_b200_act                                */
+  float act_alpha;          /* LeakyRelu slope                               */
+  float out_scale;          /* quantised outputs: divide by this; 1 = skip   */
+  int32_t out_zero_point;   /* quantised outputs                             */
+} sofie_b200_epilogue;
+
+/*
+ * One contraction  Y[b] = epilogue( op(A[b]) * op(B[b]) ),  b = 0..batch-1.
+ * Replaces one blas.addOperationConfig registration (RModel_ALPAKA.cxx:1334-1341) and the
+ * shape half of blas.gemmStridedBatched (ROperator_Gemm.hxx:991-1065).
+ *   op(A) is [M,K]: A is stored [M,K] with row pitch lda, or [K,M] when trans_a.
+ *   op(B) is [K,N]: B is stored [K,N] with row pitch ldb, or [N,K] when trans_b
+ *   (ONNX Gemm transB; SOFIE's parser also turns a Transpose feeding a MatMul into this flag,
+ *   parsers/src/RModelParser_ONNX.cxx:1186-1197).
+ * A and B share one element type: F32 (computed as error-compensated 3xTF32 or fp32 FMA, see
+ * `precise`), BF16, F8E4M3 (fp32 accumulate) or I8 (int32 accumulate).  A batch stride of 0
+ * broadcasts that operand over the batch (a shared weight, ROperator_Gemm.hxx:854-859).
+ */
+typedef struct sofie_b200_gemm_desc {
+  int64_t M, N, K;
+  int64_t batch;                 /* >= 1 */
+  int32_t trans_a, trans_b;
+  int32_t ab_dtype;              /* sofie_b200_dtype of A and B   */
+  int32_t y_dtype;               /* sofie_b200_dtype of Y         */
+  int64_t lda, ldb, ldy;         /* row pitches in elements       */
+  int64_t stride_a, stride_b, stride_y; /* batch strides in elements */
+  int64_t stride_c, stride_r;    /* batch strides of FULL_F32 C and of residual */
+  int32_t precise;               /* F32 inputs: 1 = fp32-accurate path (default), 0 = single-pass TF32 */
+  int32_t reserved;
+} sofie_b200_gemm_desc;
+
+/*
+ * Convolution over a whole NCHW batch as one implicit GEMM; replaces the reference's per-image
+ * loop of Im2ColKernel + blas.matmul (ROperator_Conv.hxx:985-1103) and its per-call weight
+ * re-layout (ROperator_Conv.hxx:985-997).  Shape rules follow ROperator_Conv.hxx:123-262.
+ * X is [N,C,H,W]; W is [K, C/groups, R, S]; Y is [N,K,Ho,Wo].
+ */
+typedef struct sofie_b200_conv_desc {
+  int64_t N, C, H, W;
+  int64_t K, R, S;
+  int32_t pad_top, pad_left, pad_bottom, pad_right;
+  int32_t stride_h, stride_w;
+  int32_t dil_h, dil_w;
+  int32_t groups;
+  int32_t x_dtype;               /* F32 or I8 (QLinearConv)   */
+  int32_t y_dtype;               /* F32, BF16 or I8           */
+  int32_t x_zero_point;          /* I8 input zero point: padding is filled with it */
+  int32_t precise;               /* as in sofie_b200_gemm_desc */
+} sofie_b200_conv_desc;
+
+typedef struct sofie_b200_ctx sofie_b200_ctx;
+typedef struct sofie_b200_gemm_plan sofie_b200_gemm_plan;
+typedef struct sofie_b200_conv_plan sofie_b200_conv_plan;
+
+/* ---- library / context -------------------------------------------------------------- */
+
+/* ABI version of the loaded library (compare with SOFIE_B200_ABI_VERSION). */
+int sofie_b200_abi_version(void);
+
+/* Message for a status code; never NULL. */
+const char *sofie_b200_status_string(int status);
+
+/* Text of the last error raised on this thread by any entry point ("" if none).  The emitted
+ * Session wrapper puts it into the std::runtime_error it throws. */
+const char *sofie_b200_last_error(void);
+
+/* Creates the per-Session context on `device`, enqueuing on `stream` (a cudaStream_t passed as
+ * void*, NULL = the legacy default stream).  Mirrors the Session constructors that take a queue
+ * or, with Options::kExternalStream, a cudaStream_t (RModel_ALPAKA.cxx:1450-1477): the stream
+ * is borrowed, never destroyed. */
+int sofie_b200_ctx_create(sofie_b200_ctx **out, int device, void *stream);
+
+/* Destroys plans' shared state; call after the stream is idle (RModel_ALPAKA.cxx:1479-1485). */
+int sofie_b200_ctx_destroy(sofie_b200_ctx *ctx);
+
+/* Waits for the stream (the alpaka::wait(queue) at the end of Session::infer,
+ * RModel_ALPAKA.cxx:857-909) and returns SOFIE_B200_ERR_DEVICE_WAIT if a kernel reported a
+ * bounded wait that ran out since the last call. */
+int sofie_b200_ctx_sync(sofie_b200_ctx *ctx);
+
+/* Number of kernels this ctx has launched so far (for launch accounting in benchmarks). */
+int64_t sofie_b200_ctx_launch_count(const sofie_b200_ctx *ctx);
+
+/* ---- contractions -------------------------------------------------------------------- */
+
+/* Registers one contraction (blas.addOperationConfig, RModel_ALPAKA.cxx:1334-1341). */
+int sofie_b200_gemm_plan_create(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc *desc,
+                                sofie_b200_gemm_plan **out);
+int sofie_b200_gemm_plan_destroy(sofie_b200_gemm_plan *plan);
+
+/* Name of the kernel family the plan selected: "umma" (tcgen05 + TMEM + TMA) or "simt". */
+const char *sofie_b200_gemm_plan_kernel(const sofie_b200_gemm_plan *plan);
+
+/* Enqueues the contraction with its fused epilogue on the ctx's stream: the replacement of
+ * blas.gemm / gemmrelu / matmul / gemmStridedBatched (ROperator_Gemm.hxx:931-1098) and of
+ * GemmBiasAddKernel (ROperator_Gemm.hxx:743-764).  `ep` may be NULL (plain product). */
+int sofie_b200_gemm_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, void *Y,
+                            const sofie_b200_epilogue *ep);
+
+/* Same contraction with HOST operands: copies A and B to ctx-owned device staging buffers,
+ * runs the plan, copies Y back and waits.  This is the shape of Session::infer on host data
+ * (the CPU Session's infer(const float*), core/src/RModel.cxx:1303-1419).  Epilogue vectors
+ * (scales, bias) are device pointers as in sofie_b200_gemm_enqueue. */
+int sofie_b200_gemm_run_host(sofie_b200_gemm_plan *plan, const void *hostA, const void *hostB,
+                             void *hostY, const sofie_b200_epilogue *ep);
+
+/* ---- convolution ---------------------------------------------------------------------- */
+
+/* Registers a convolution and re-lays the weights once (the reference redoes its weight
+ * re-layout on every inference, ROperator_Conv.hxx:985-997).  `W` is the device pointer of the
+ * [K, C/groups, R, S] weights in x_dtype (F32 or I8). */
+int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc *desc, const void *W,
+                                sofie_b200_conv_plan **out);
+int sofie_b200_conv_plan_destroy(sofie_b200_conv_plan *plan);
+/* Output extent per ROperator_Conv.hxx:123-262. */
+int sofie_b200_conv_out_shape(const sofie_b200_conv_desc *desc, int64_t *Ho, int64_t *Wo);
+/* Bytes of caller-provided scratch the plan needs per enqueue (0 if none). */
+int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan);
+/* Enqueues Y = epilogue(conv(X, W)); columns of the epilogue are output channels. */
+int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, void *workspace,
+                            const sofie_b200_epilogue *ep);
+
+/* ---- memory-bound operators the fusion pass leaves ----------------------------------- */
+
+/* LayerNormalization over the last `cols` elements of each of `rows` rows
+ * (ROperator_LayerNormalization.hxx:249-321): mean, biased variance, invStd = 1/sqrt(var+eps),
+ * y = scale*invStd*(x-mean)+bias.  scale/bias are F32 [cols] or NULL; mean_out/invstd_out are
+ * optional F32 [rows].  x and y are F32 or BF16. */
+int sofie_b200_layernorm_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t x_dtype,
+                                 int32_t y_dtype, int64_t rows, int64_t cols, const float *scale,
+                                 const float *bias, float eps, float *mean_out, float *invstd_out);
+
+/* Softmax / LogSoftmax along the last axis (ROperator_Softmax.hxx:82-119). */
+int sofie_b200_softmax_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t x_dtype,
+                               int32_t y_dtype, int64_t rows, int64_t cols, int32_t log_softmax);
+
+/* Unary elementwise y = act(x) (ROperator_Relu.hxx:47-114, ROperator_Gelu.hxx:42-123,
+ * ROperator_LeakyRelu.hxx).  F32 or BF16. */
+int sofie_b200_unary_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t dtype, int64_t n,
+                             int32_t act, float act_alpha);
+
+/* Binary elementwise with trailing-dimension broadcast of b (ROperator_BasicBinary.hxx:380,
+ * 520-636): y[i] = a[i] op b[i % nb], op: 0 Add, 1 Sub, 2 Mul, 3 Div; optional activation. */
+int sofie_b200_binary_enqueue(sofie_b200_ctx *ctx, const void *a, const void *b, void *y, int32_t dtype,
+                              int64_t n, int64_t nb, int32_t op, int32_t act);
+
+/* Inference BatchNormalization on NCHW-like data (ROperator_BatchNormalization.hxx:100-153):
+ * y = (x - mean[c]) * fused_scale[c] + bias[c], c = (i / inner) % channels; optional Relu. */
+int sofie_b200_batchnorm_enqueue(sofie_b200_ctx *ctx, const float *x, float *y, int64_t outer,
+                                 int64_t channels, int64_t inner, const float *fused_scale,
+                                 const float *bias, const float *mean, int32_t act);
+
+/* GlobalAveragePool: y[n,c] = sum(x[n,c,:]) / inner (ROperator_Pool.hxx:225-237,531-536).
+ * x is F32, BF16 or I8; y is F32. */
+int sofie_b200_global_avgpool_enqueue(sofie_b200_ctx *ctx, const void *x, float *y, int32_t x_dtype,
+                                      int64_t nc, int64_t inner);
+
+/* QuantizeLinear / DequantizeLinear (ONNX): q = sat(rint(x/scale)+zp);  x = (q-zp)*scale.
+ * Per-tensor when channels == 1, else per-channel with c = (i / inner) % channels. */
+int sofie_b200_quantize_enqueue(sofie_b200_ctx *ctx, const float *x, void *q, int32_t q_dtype, int64_t n,
+                                const float *scale, const int32_t *zero_point, int64_t channels,
+                                int64_t inner);
+int sofie_b200_dequantize_enqueue(sofie_b200_ctx *ctx, const void *q, float *x, int32_t q_dtype, int64_t n,
+                                  const float *scale, const int32_t *zero_point, int64_t channels,
+                                  int64_t inner);
+
+/* Type conversion between F32, BF16 and F8E4M3 (saturating round-to-nearest-even), with an
+ * optional per-row scale: y[r,c] = cvt(x[r,c] / row_scale[r]) (row_scale may be NULL). */
+int sofie_b200_convert_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t x_dtype, int32_t y_dtype,
+                               int64_t rows, int64_t cols, const float *row_scale);
+
+/* ---- device arena (Options::kCustomMemory) -------------------------------------------- */
+
+/* Lifetime of one pooled tensor: alive on operator steps [begin, end), `size` bytes
+ * (TensorLifeInfo, core/inc/SOFIE/utils/shared/MemoryPlanner.inc:33-45). */
+typedef struct sofie_b200_tensor_life {
+  int64_t begin, end, size;
+} sofie_b200_tensor_life;
+
+/* Plans one arena for `n` tensors: best fit with coalescing of freed neighbours and 256-byte
+ * alignment, the policy of OrganizeMemory (MemoryPlanner.inc:47-132, alignment
+ * RModel_ALPAKA.cxx:25).  Writes n offsets and the arena size in bytes. */
+int sofie_b200_plan_arena(const sofie_b200_tensor_life *lives, int64_t n, int64_t *offsets,
+                          int64_t *total_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SOFIE_B200_H */

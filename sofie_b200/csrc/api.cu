@@ -1,0 +1,249 @@
+// C ABI: context, error reporting and the contraction plan / enqueue entry points.
+#include <stdarg.h>
+#include <string.h>
+
+#include "gemm.cuh"
+
+namespace sb200 {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int fail(int status, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+int ensure_stage(sofie_b200_ctx *ctx, int idx, size_t bytes) {
+  if (ctx->stage_bytes[idx] >= bytes) return 0;
+  if (ctx->stage[idx]) SB_CUDA(cudaFree(ctx->stage[idx]));
+  ctx->stage[idx] = nullptr;
+  ctx->stage_bytes[idx] = 0;
+  SB_CUDA(cudaMalloc(&ctx->stage[idx], bytes));
+  ctx->stage_bytes[idx] = bytes;
+  return 0;
+}
+
+static const char *kDeviceWait[] = {"ok", "TMA producer: no free shared-memory stage", "MMA issuer: stage never filled",
+                                    "MMA issuer: accumulator never drained", "epilogue: accumulator never completed"};
+
+}  // namespace sb200
+
+using namespace sb200;
+
+extern "C" {
+
+int sofie_b200_abi_version(void) { return SOFIE_B200_ABI_VERSION; }
+
+const char *sofie_b200_status_string(int status) {
+  switch (status) {
+    case SOFIE_B200_OK: return "ok";
+    case SOFIE_B200_ERR_INVALID: return "invalid argument or unsupported combination";
+    case SOFIE_B200_ERR_CUDA: return "CUDA call failed";
+    case SOFIE_B200_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel gave up";
+    case SOFIE_B200_ERR_NO_DEVICE: return "no usable sm_100 device";
+    case SOFIE_B200_ERR_TOO_LARGE: return "size beyond a static limit";
+  }
+  return "unknown status";
+}
+
+const char *sofie_b200_last_error(void) { return g_err; }
+
+int sofie_b200_ctx_create(sofie_b200_ctx **out, int device, void *stream) {
+  if (!out) return fail(SOFIE_B200_ERR_INVALID, "ctx_create: out is NULL");
+  *out = nullptr;
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) {
+    cudaGetLastError();
+    return fail(SOFIE_B200_ERR_NO_DEVICE, "ctx_create: no CUDA device visible");
+  }
+  if (device < 0 || device >= ndev) return fail(SOFIE_B200_ERR_INVALID, "ctx_create: device %d of %d", device, ndev);
+  cudaDeviceProp prop;
+  SB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(SOFIE_B200_ERR_NO_DEVICE, "ctx_create: device %d is sm_%d%d; this library is built for sm_100a only",
+                device, prop.major, prop.minor);
+  SB_CUDA(cudaSetDevice(device));
+  sofie_b200_ctx *ctx = new sofie_b200_ctx();
+  ctx->device = device;
+  ctx->stream = (cudaStream_t)stream;
+  ctx->sm_count = prop.multiProcessorCount;
+  if (cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMallocHost(&ctx->h_status, sizeof(int)) != cudaSuccess) {
+    delete ctx;
+    return fail(SOFIE_B200_ERR_CUDA, "ctx_create: allocating the status word failed: %s", cudaGetErrorString(cudaGetLastError()));
+  }
+  SB_CUDA(cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+  SB_CUDA(cudaStreamSynchronize(ctx->stream));
+  *out = ctx;
+  return 0;
+}
+
+int sofie_b200_ctx_destroy(sofie_b200_ctx *ctx) {
+  if (!ctx) return 0;
+  cudaSetDevice(ctx->device);
+  for (int i = 0; i < 3; ++i)
+    if (ctx->stage[i]) cudaFree(ctx->stage[i]);
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->h_status) cudaFreeHost(ctx->h_status);
+  delete ctx;
+  return 0;
+}
+
+int sofie_b200_ctx_sync(sofie_b200_ctx *ctx) {
+  if (!ctx) return fail(SOFIE_B200_ERR_INVALID, "ctx_sync: ctx is NULL");
+  SB_CUDA(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  SB_CUDA(cudaStreamSynchronize(ctx->stream));
+  int s = *ctx->h_status;
+  if (s != 0) {
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+    return fail(SOFIE_B200_ERR_DEVICE_WAIT, "device status %d: %s", s, (s > 0 && s < 5) ? kDeviceWait[s] : "unknown");
+  }
+  return 0;
+}
+
+int64_t sofie_b200_ctx_launch_count(const sofie_b200_ctx *ctx) { return ctx ? ctx->launches : 0; }
+
+// ---------------------------------------------------------------------------------------
+
+int sofie_b200_gemm_plan_create(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc *desc, sofie_b200_gemm_plan **out) {
+  if (!ctx || !desc || !out) return fail(SOFIE_B200_ERR_INVALID, "gemm_plan_create: NULL argument");
+  *out = nullptr;
+  sofie_b200_gemm_desc d = *desc;
+  if (d.M < 0 || d.N < 0 || d.K < 0) return fail(SOFIE_B200_ERR_INVALID, "gemm_plan_create: negative extent");
+  if (d.batch < 1) d.batch = 1;
+  if (d.lda == 0) d.lda = d.trans_a ? d.M : d.K;
+  if (d.ldb == 0) d.ldb = d.trans_b ? d.K : d.N;
+  if (d.ldy == 0) d.ldy = d.N;
+  if (d.lda < (d.trans_a ? d.M : d.K) || d.ldb < (d.trans_b ? d.K : d.N) || d.ldy < d.N)
+    return fail(SOFIE_B200_ERR_INVALID, "gemm_plan_create: a row pitch is smaller than the row (lda %lld ldb %lld ldy %lld)",
+                (long long)d.lda, (long long)d.ldb, (long long)d.ldy);
+  switch (d.ab_dtype) {
+    case SOFIE_B200_F32: case SOFIE_B200_BF16: case SOFIE_B200_I8: case SOFIE_B200_F8E4M3: break;
+    default: return fail(SOFIE_B200_ERR_INVALID, "gemm_plan_create: operand type %d not supported", d.ab_dtype);
+  }
+  const bool int_acc = d.ab_dtype == SOFIE_B200_I8;
+  switch (d.y_dtype) {
+    case SOFIE_B200_F32: case SOFIE_B200_BF16: case SOFIE_B200_I8: case SOFIE_B200_U8: break;
+    case SOFIE_B200_I32:
+      if (!int_acc) return fail(SOFIE_B200_ERR_INVALID, "gemm_plan_create: I32 output needs I8 operands");
+      break;
+    default: return fail(SOFIE_B200_ERR_INVALID, "gemm_plan_create: output type %d not supported", d.y_dtype);
+  }
+  SB_CUDA(cudaSetDevice(ctx->device));
+  sofie_b200_gemm_plan *plan = new sofie_b200_gemm_plan();
+  plan->ctx = ctx;
+  plan->desc = d;
+  plan->use_umma = 0;
+  // fp32 operands: the single-pass TF32 tensor path only on request; otherwise fp32 FMA.
+  const bool want_umma = !(d.ab_dtype == SOFIE_B200_F32 && d.precise != 0);
+  if (want_umma && d.M > 0 && d.N > 0 && d.K > 0) {
+    int rc = umma_plan_init(plan);
+    if (rc < 0) { delete plan; return rc; }
+    plan->use_umma = (rc == 0);
+  }
+  ctx->live_plans++;
+  *out = plan;
+  return 0;
+}
+
+int sofie_b200_gemm_plan_destroy(sofie_b200_gemm_plan *plan) {
+  if (!plan) return 0;
+  plan->ctx->live_plans--;
+  delete plan;
+  return 0;
+}
+
+const char *sofie_b200_gemm_plan_kernel(const sofie_b200_gemm_plan *plan) {
+  if (!plan) return "";
+  return plan->use_umma ? "umma" : "simt";
+}
+
+static int make_epi(const sofie_b200_gemm_plan *plan, void *Y, const sofie_b200_epilogue *ep, EpiParams *o) {
+  const sofie_b200_gemm_desc &d = plan->desc;
+  memset(o, 0, sizeof(*o));
+  o->Y = Y;
+  o->ldy = d.ldy;
+  o->stride_y = d.stride_y;
+  o->stride_c = d.stride_c;
+  o->stride_r = d.stride_r;
+  o->alpha = 1.f; o->beta = 1.f; o->out_scale = 1.f;
+  o->y_dtype = d.y_dtype;
+  o->acc_is_int = d.ab_dtype == SOFIE_B200_I8;
+  if (ep) {
+    o->row_scale = ep->row_scale;
+    o->col_scale = ep->col_scale;
+    o->alpha = ep->alpha;
+    o->beta = ep->beta;
+    o->bias_mode = ep->bias_mode;
+    o->bias = ep->bias;
+    o->ldc = ep->ldc ? ep->ldc : d.N;
+    o->residual = ep->residual;
+    o->residual_dtype = ep->residual_dtype;
+    o->ldr = ep->ldr ? ep->ldr : d.N;
+    o->act = ep->act;
+    o->act_alpha = ep->act_alpha;
+    o->out_scale = ep->out_scale == 0.f ? 1.f : ep->out_scale;
+    o->out_zp = ep->out_zero_point;
+    o->params_aligned = ((uintptr_t)ep->col_scale % 16 == 0) && ((uintptr_t)ep->bias % 16 == 0);
+    if (ep->bias_mode != SOFIE_B200_BIAS_NONE && !ep->bias)
+      return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue: bias_mode %d with a NULL bias", ep->bias_mode);
+    if ((ep->bias_mode == SOFIE_B200_BIAS_COL_I32 || ep->bias_mode == SOFIE_B200_BIAS_ROW_I32) && !o->acc_is_int)
+      return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue: an int32 bias needs int8 operands");
+    if (ep->bias_mode < 0 || ep->bias_mode > SOFIE_B200_BIAS_ROW_I32)
+      return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue: bias_mode %d unknown", ep->bias_mode);
+    if (ep->act < 0 || ep->act > SOFIE_B200_ACT_SIGMOID)
+      return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue: activation %d unknown", ep->act);
+  }
+  return 0;
+}
+
+int sofie_b200_gemm_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, void *Y,
+                            const sofie_b200_epilogue *ep) {
+  if (!plan) return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue: plan is NULL");
+  const sofie_b200_gemm_desc &d = plan->desc;
+  if (d.M == 0 || d.N == 0) return 0;  // empty output: nothing to enqueue
+  if (!A || !B || !Y) return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue: NULL tensor pointer");
+  EpiParams e;
+  int rc = make_epi(plan, Y, ep, &e);
+  if (rc) return rc;
+  SB_CUDA(cudaSetDevice(plan->ctx->device));
+  if (plan->use_umma && d.K > 0) return umma_enqueue(plan, A, B, e);
+  return simt_enqueue(plan, A, B, e);
+}
+
+int sofie_b200_gemm_run_host(sofie_b200_gemm_plan *plan, const void *hostA, const void *hostB, void *hostY,
+                             const sofie_b200_epilogue *ep) {
+  if (!plan || !hostA || !hostB || !hostY) return fail(SOFIE_B200_ERR_INVALID, "gemm_run_host: NULL argument");
+  const sofie_b200_gemm_desc &d = plan->desc;
+  sofie_b200_ctx *ctx = plan->ctx;
+  const size_t es = dtype_size(d.ab_dtype), ys = dtype_size(d.y_dtype);
+  auto extent = [](int64_t rows, int64_t ld, int64_t batch, int64_t stride) -> size_t {
+    if (batch > 1 && stride != 0) return (size_t)((batch - 1) * stride + rows * ld);
+    return (size_t)(rows * ld);
+  };
+  const size_t a_bytes = extent(d.trans_a ? d.K : d.M, d.lda, d.batch, d.stride_a) * es;
+  const size_t b_bytes = extent(d.trans_b ? d.N : d.K, d.ldb, d.batch, d.stride_b) * es;
+  const size_t y_bytes = extent(d.M, d.ldy, d.batch, d.stride_y) * ys;
+  SB_CUDA(cudaSetDevice(ctx->device));
+  int rc;
+  if ((rc = ensure_stage(ctx, 0, a_bytes)) || (rc = ensure_stage(ctx, 1, b_bytes)) || (rc = ensure_stage(ctx, 2, y_bytes)))
+    return rc;
+  SB_CUDA(cudaMemcpyAsync(ctx->stage[0], hostA, a_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  SB_CUDA(cudaMemcpyAsync(ctx->stage[1], hostB, b_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  rc = sofie_b200_gemm_enqueue(plan, ctx->stage[0], ctx->stage[1], ctx->stage[2], ep);
+  if (rc) return rc;
+  SB_CUDA(cudaMemcpyAsync(hostY, ctx->stage[2], y_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  return sofie_b200_ctx_sync(ctx);
+}
+
+}  // extern "C"

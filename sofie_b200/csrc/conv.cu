@@ -1,0 +1,207 @@
+// Convolution over a whole NCHW batch.
+//
+// Y[n, k, :, :] (a [Cout, Ho*Wo] matrix per image, which is exactly the NCHW output) is computed
+// as  W[Cout, C*R*S] x xcol[n][Ho*Wo, C*R*S]^T : the weights are the K-major A operand as they
+// are stored (only padded once, at plan creation, to a 16-byte row pitch), the unfolded input is
+// the K-major B operand, the batch index is the image, and output channels are accumulator ROWS.
+// One unfold kernel and one batched contraction per group replace the reference's host loop of
+// per-image Im2ColKernel + blas.matmul launches (ROperator_Conv.hxx:1002-1103).  The K order
+// (c, r, s) is the reference's (ROperator_Conv.hxx:456-476), so weights need no permutation.
+#include "gemm.cuh"
+
+struct sofie_b200_conv_plan {
+  sofie_b200_ctx *ctx = nullptr;
+  sofie_b200_conv_desc d{};
+  int64_t Ho = 0, Wo = 0;
+  int64_t cg = 0, kg = 0;      // input channels / output channels per group
+  int64_t kdim = 0, kpad = 0;  // C/g*R*S and its padded pitch
+  void *w_padded = nullptr;    // [K, kpad] device copy of the weights
+  sofie_b200_gemm_plan *gemm = nullptr;
+};
+
+namespace sb200 {
+
+static int conv_out_shape(const sofie_b200_conv_desc &d, int64_t *Ho, int64_t *Wo) {
+  if (d.stride_h < 1 || d.stride_w < 1 || d.dil_h < 1 || d.dil_w < 1) return fail(SOFIE_B200_ERR_INVALID, "conv: strides and dilations must be >= 1");
+  const int64_t eff_r = (d.R - 1) * d.dil_h + 1, eff_s = (d.S - 1) * d.dil_w + 1;  // dilated kernel extent
+  const int64_t h = d.H + d.pad_top + d.pad_bottom - eff_r, w = d.W + d.pad_left + d.pad_right - eff_s;
+  if (h < 0 || w < 0) return fail(SOFIE_B200_ERR_INVALID, "conv: kernel larger than the padded input");
+  *Ho = h / d.stride_h + 1;
+  *Wo = w / d.stride_w + 1;
+  return 0;
+}
+
+// xcol[g][n][pix][kpad]; one thread writes 16 bytes (VEC elements along k).
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256) unfold_kernel(const T *__restrict__ x, T *__restrict__ xcol, sofie_b200_conv_desc d,
+                                                     long long Ho, long long Wo, long long cg, long long kdim, long long kpad,
+                                                     T pad_value) {
+  const long long chunks = kpad / VEC;
+  const long long pix = Ho * Wo;
+  const long long total = (long long)d.groups * d.N * pix * chunks;
+  const long long rs = d.R * d.S;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long ch = i % chunks;
+    long long t = i / chunks;
+    const long long p = t % pix; t /= pix;
+    const long long n = t % d.N;
+    const long long g = t / d.N;
+    const long long oh = p / Wo, ow = p % Wo;
+    const long long ih0 = oh * d.stride_h - d.pad_top, iw0 = ow * d.stride_w - d.pad_left;
+    const T *xg = x + (n * d.C + g * cg) * d.H * d.W;
+    __align__(16) T v[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const long long k = ch * VEC + e;
+      T val = (T)0;
+      if (k < kdim) {
+        const long long c = k / rs, q = k % rs;
+        const long long r = q / d.S, s = q % d.S;
+        const long long ih = ih0 + r * d.dil_h, iw = iw0 + s * d.dil_w;
+        val = (ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) ? xg[(c * d.H + ih) * d.W + iw] : pad_value;
+      }
+      v[e] = val;
+    }
+    *reinterpret_cast<uint4 *>(xcol + i * VEC) = *reinterpret_cast<const uint4 *>(v);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) pad_weights_kernel(const T *__restrict__ w, T *__restrict__ wp, long long rows, long long kdim,
+                                                          long long kpad) {
+  const long long total = rows * kpad;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / kpad, k = i % kpad;
+    wp[i] = k < kdim ? w[r * kdim + k] : (T)0;
+  }
+}
+
+}  // namespace sb200
+
+using namespace sb200;
+
+extern "C" {
+
+int sofie_b200_conv_out_shape(const sofie_b200_conv_desc *desc, int64_t *Ho, int64_t *Wo) {
+  if (!desc || !Ho || !Wo) return fail(SOFIE_B200_ERR_INVALID, "conv_out_shape: NULL argument");
+  return conv_out_shape(*desc, Ho, Wo);
+}
+
+int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc *desc, const void *W,
+                                sofie_b200_conv_plan **out) {
+  if (!ctx || !desc || !W || !out) return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: NULL argument");
+  *out = nullptr;
+  sofie_b200_conv_desc d = *desc;
+  if (d.groups < 1) d.groups = 1;
+  if (d.N < 0 || d.C < 1 || d.H < 1 || d.W < 1 || d.K < 1 || d.R < 1 || d.S < 1)
+    return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: bad extent");
+  if (d.C % d.groups || d.K % d.groups)
+    return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: channels %lld / filters %lld not divisible by groups %d", (long long)d.C, (long long)d.K, d.groups);
+  if (d.x_dtype != SOFIE_B200_F32 && d.x_dtype != SOFIE_B200_I8)
+    return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: input type %d not supported (F32, I8)", d.x_dtype);
+  int64_t Ho, Wo;
+  int rc = conv_out_shape(d, &Ho, &Wo);
+  if (rc) return rc;
+  SB_CUDA(cudaSetDevice(ctx->device));
+  const int es = dtype_size(d.x_dtype);
+  sofie_b200_conv_plan *p = new sofie_b200_conv_plan();
+  p->ctx = ctx; p->d = d; p->Ho = Ho; p->Wo = Wo;
+  p->cg = d.C / d.groups; p->kg = d.K / d.groups;
+  p->kdim = p->cg * d.R * d.S;
+  const int64_t vec = 16 / es;
+  p->kpad = (p->kdim + vec - 1) / vec * vec;
+  if (cudaMalloc(&p->w_padded, (size_t)(d.K * p->kpad * es)) != cudaSuccess) {
+    delete p;
+    return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: allocating padded weights failed: %s", cudaGetErrorString(cudaGetLastError()));
+  }
+  const long long total = d.K * p->kpad;
+  const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 16);
+  if (d.x_dtype == SOFIE_B200_F32)
+    pad_weights_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float *)W, (float *)p->w_padded, d.K, p->kdim, p->kpad);
+  else
+    pad_weights_kernel<int8_t><<<grid, 256, 0, ctx->stream>>>((const int8_t *)W, (int8_t *)p->w_padded, d.K, p->kdim, p->kpad);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { cudaFree(p->w_padded); delete p; return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: %s", cudaGetErrorString(e)); }
+  ctx->launches++;
+
+  sofie_b200_gemm_desc g{};
+  g.M = p->kg; g.N = Ho * Wo; g.K = p->kpad; g.batch = d.N > 0 ? d.N : 1;
+  g.trans_a = 0; g.trans_b = 1;
+  g.ab_dtype = d.x_dtype; g.y_dtype = d.y_dtype;
+  g.lda = p->kpad; g.ldb = p->kpad; g.ldy = Ho * Wo;
+  g.stride_a = 0; g.stride_b = Ho * Wo * p->kpad; g.stride_y = d.K * Ho * Wo;
+  g.stride_r = d.K * Ho * Wo;
+  g.precise = d.precise;
+  rc = sofie_b200_gemm_plan_create(ctx, &g, &p->gemm);
+  if (rc) { cudaFree(p->w_padded); delete p; return rc; }
+  *out = p;
+  return 0;
+}
+
+int sofie_b200_conv_plan_destroy(sofie_b200_conv_plan *plan) {
+  if (!plan) return 0;
+  cudaSetDevice(plan->ctx->device);
+  if (plan->gemm) sofie_b200_gemm_plan_destroy(plan->gemm);
+  if (plan->w_padded) cudaFree(plan->w_padded);
+  delete plan;
+  return 0;
+}
+
+int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan) {
+  if (!plan) return 0;
+  return (int64_t)plan->d.groups * plan->d.N * plan->Ho * plan->Wo * plan->kpad * dtype_size(plan->d.x_dtype);
+}
+
+int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, void *workspace,
+                            const sofie_b200_epilogue *ep) {
+  if (!plan) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: plan is NULL");
+  const sofie_b200_conv_desc &d = plan->d;
+  if (d.N == 0) return 0;
+  if (!X || !Y || !workspace) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: NULL tensor or workspace");
+  if ((uintptr_t)workspace % 16) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: workspace must be 16-byte aligned");
+  sofie_b200_ctx *ctx = plan->ctx;
+  SB_CUDA(cudaSetDevice(ctx->device));
+  const int es = dtype_size(d.x_dtype);
+  const long long pix = plan->Ho * plan->Wo;
+  const long long total = (long long)d.groups * d.N * pix * (plan->kpad / (16 / es));
+  const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 32);
+  if (d.x_dtype == SOFIE_B200_F32)
+    unfold_kernel<float, 4><<<grid, 256, 0, ctx->stream>>>((const float *)X, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, 0.f);
+  else
+    unfold_kernel<int8_t, 16><<<grid, 256, 0, ctx->stream>>>((const int8_t *)X, (int8_t *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, (int8_t)d.x_zero_point);
+  SB_CUDA(cudaGetLastError());
+  ctx->launches++;
+
+  // Output channels are accumulator rows here: per-channel vectors of the caller's epilogue
+  // (documented per column = per channel) become per-row vectors.
+  sofie_b200_epilogue e{};
+  e.alpha = 1.f; e.beta = 1.f; e.out_scale = 1.f;
+  if (ep) {
+    if (ep->row_scale) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: row_scale has no meaning for a convolution");
+    e = *ep;
+    e.row_scale = ep->col_scale;
+    e.col_scale = nullptr;
+    switch (ep->bias_mode) {
+      case SOFIE_B200_BIAS_NONE: case SOFIE_B200_BIAS_SCALAR_F32: break;
+      case SOFIE_B200_BIAS_COL_F32: e.bias_mode = SOFIE_B200_BIAS_ROW_F32; break;
+      case SOFIE_B200_BIAS_COL_I32: e.bias_mode = SOFIE_B200_BIAS_ROW_I32; break;
+      default: return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: bias_mode %d not supported for a convolution", ep->bias_mode);
+    }
+    e.ldr = pix;
+  }
+  const int ys = dtype_size(d.y_dtype);
+  for (int g = 0; g < d.groups; ++g) {
+    sofie_b200_epilogue eg = e;
+    if (eg.row_scale) eg.row_scale += g * plan->kg;
+    if (eg.bias && eg.bias_mode != SOFIE_B200_BIAS_SCALAR_F32) eg.bias = (const char *)eg.bias + (size_t)g * plan->kg * 4;
+    if (eg.residual) eg.residual = (const char *)eg.residual + (size_t)g * plan->kg * pix * dtype_size(eg.residual_dtype);
+    const char *a = (const char *)plan->w_padded + (size_t)g * plan->kg * plan->kpad * es;
+    const char *b = (const char *)workspace + (size_t)g * d.N * pix * plan->kpad * es;
+    char *y = (char *)Y + (size_t)g * plan->kg * pix * ys;
+    int rc = sofie_b200_gemm_enqueue(plan->gemm, a, b, y, &eg);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,69 @@
+// Plan object behind sofie_b200_gemm_plan and the two kernel families it can select.
+#pragma once
+#include <cuda.h>
+#include "epilogue.cuh"
+
+namespace sb200 {
+
+constexpr int UMMA_BM = 128;          // rows of one accumulator tile (TMEM lanes)
+constexpr int UMMA_STAGE_K_BYTES = 128;  // K extent of one shared-memory stage, in bytes (one 128B swizzle row)
+constexpr int UMMA_THREADS = 192;     // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+
+// Everything the tcgen05 kernel needs besides the two tensor maps.
+struct UmmaParams {
+  int M, N, K, batch;
+  int tiles_m, tiles_n;
+  long long num_tiles;
+  int num_kb;          // K blocks of kb_elems elements
+  int kb_elems;        // K elements per stage (128 bytes / element size)
+  int bn;              // N extent of the tile and of each MMA (32, 64, 128 or 256)
+  int stages;
+  uint32_t tmem_cols;  // allocated TMEM columns: power of two >= 2*bn
+  uint32_t a_stage_bytes, b_stage_bytes;
+  uint32_t idesc;      // tcgen05 instruction descriptor
+  uint32_t a_desc_hi, b_desc_hi;   // upper words of the shared-memory matrix descriptors
+  uint32_t a_desc_lo, b_desc_lo;   // constant part of the lower words (leading byte offset field)
+  uint32_t a_kadv, b_kadv;         // start-address advance per MMA K step, in 16-byte units
+  int a_mn, b_mn;                  // operand is MN-major (its M or N index is contiguous) in global memory
+  int a_boxes, b_boxes;            // TMA boxes per stage
+  uint32_t a_box_bytes, b_box_bytes;
+  int a_box_mn, b_box_mn;          // MN elements covered by one box of an MN-major operand
+  int a_bcast, b_bcast;            // operand shared by the whole batch
+  int vec_ok;                      // 16-byte vector stores of 32-column chunks are aligned
+  EpiParams ep;
+  int *status;
+};
+
+struct SimtParams {
+  const void *A, *B;
+  int M, N, K, batch;
+  long long lda, ldb, stride_a, stride_b;
+  int trans_a, trans_b;
+  EpiParams ep;
+};
+
+}  // namespace sb200
+
+struct sofie_b200_gemm_plan {
+  sofie_b200_ctx *ctx = nullptr;
+  sofie_b200_gemm_desc desc{};
+  int use_umma = 0;
+  int kind = 0;                    // ptx::KIND_*
+  sb200::UmmaParams up{};
+  size_t smem_bytes = 0;
+  int grid = 0;
+  // tensor maps are rebuilt only when an operand pointer changes
+  const void *cached_a = nullptr, *cached_b = nullptr;
+  CUtensorMap tm_a{}, tm_b{};
+  // 3xTF32 split scratch (precise F32 on the tensor path)
+  void *split_a = nullptr, *split_b = nullptr;
+  const void *split_src_b = nullptr;
+};
+
+namespace sb200 {
+// gemm_umma.cu
+int umma_plan_init(sofie_b200_gemm_plan *plan);          // 0 if the tcgen05 path applies, 1 if not, <0 error
+int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep);
+// gemm_simt.cu
+int simt_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep);
+}  // namespace sb200

@@ -1,0 +1,614 @@
+// Contraction kernel for sm_100a: tcgen05.mma with the accumulator in tensor memory, operands
+// staged in 128B-swizzled shared memory by TMA, one persistent CTA per SM.
+//
+// Roles inside a CTA of 192 threads
+//   warp 0, lane 0 : TMA producer.  Fills a ring of `stages` shared-memory stages; each stage
+//                    holds a 128 x (128 bytes of K) slice of op(A) and a bn x (128 bytes of K)
+//                    slice of op(B).
+//   warp 1, lane 0 : MMA issuer.  Four tcgen05.mma (K = 32 bytes each) per stage into one of two
+//                    TMEM accumulators (128 lanes x bn columns each); tcgen05.commit releases
+//                    the stage to the producer and, after the last K block, hands the accumulator
+//                    to the epilogue.
+//   warps 2-5      : epilogue.  tcgen05.ld 32 columns at a time (thread = row), apply the fused
+//                    epilogue (epilogue.cuh) and store with 16-byte vector stores.  The second
+//                    accumulator lets the epilogue of tile t overlap the main loop of tile t+1.
+//
+// Data layout: a K-major operand (row-major [rows, K]) is one TMA box of rows x 128 bytes per
+// stage; an MN-major operand (row-major [K, cols]) is cols*es/128 boxes of (128 bytes x K-rows).
+// Both land in the canonical 128B-swizzle layouts that the shared-memory matrix descriptors
+// name, so no operand is transposed or re-laid in global memory.
+//
+// Every wait is bounded (ptx::mbar_wait).  A wait that runs out raises an abort flag in shared
+// memory, writes a DeviceStatus code to the ctx status word, and all roles fall through to the
+// common exit where tensor memory is freed.
+#include <cudaTypedefs.h>
+#include <mutex>
+
+#include "gemm.cuh"
+#include "ptx.cuh"
+
+namespace sb200 {
+using namespace ptx;
+
+__device__ __forceinline__ void raise_abort(volatile int *abort_flag, int *status, int code) {
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+}
+
+__device__ __forceinline__ void st_v4(void *p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  *reinterpret_cast<uint4 *>(p) = make_uint4(a, b, c, d);
+}
+
+// Applies the fused epilogue to one 32-column chunk of one accumulator row and stores it.
+//
+// The work is staged as passes over a register array, with every data-independent decision
+// (which scales exist, which activation, which output type) taken once per chunk OUTSIDE the
+// unrolled per-element loops: a warp cannot overlap instructions across a branch, so uniform
+// branches inside the element loop would serialise the whole epilogue.  Absent scales multiply
+// by 1.0f and an absent bias adds 0.0f; both are exact, so the value equals the documented
+// step-by-step formula (sofie_b200_epilogue) bit for bit.
+__device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t (&raw)[32], long long b, long long row,
+                                            int col0, int ncols, bool vec) {
+  const bool full = ncols == 32;
+  const long long off = b * ep.stride_y + row * ep.ldy + col0;
+
+  if (ep.y_dtype == SOFIE_B200_I32) {  // raw integer accumulator (+ int32 bias)
+    int a[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) a[c] = (int)raw[c];
+    if (ep.bias_mode == SOFIE_B200_BIAS_COL_I32) {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) a[c] += (full || c < ncols) ? ((const int *)ep.bias)[col0 + c] : 0;
+    } else if (ep.bias_mode == SOFIE_B200_BIAS_ROW_I32) {
+      const int br = ((const int *)ep.bias)[row];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) a[c] += br;
+    }
+    int *y = (int *)ep.Y + off;
+    if (vec && full) {
+#pragma unroll
+      for (int c = 0; c < 32; c += 4) st_v4(y + c, a[c], a[c + 1], a[c + 2], a[c + 3]);
+    } else {
+#pragma unroll
+      for (int c = 0; c < 32; ++c)
+        if (c < ncols) y[c] = a[c];
+    }
+    return;
+  }
+
+  float v[32];
+  // 1. accumulator -> fp32
+  if (ep.acc_is_int) {
+    if (ep.bias_mode == SOFIE_B200_BIAS_COL_I32) {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = (float)((int)raw[c] + ((full || c < ncols) ? ((const int *)ep.bias)[col0 + c] : 0));
+    } else {
+      const int br = ep.bias_mode == SOFIE_B200_BIAS_ROW_I32 ? ((const int *)ep.bias)[row] : 0;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = (float)((int)raw[c] + br);
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(raw[c]);
+  }
+  // 2. scales, in the documented order: row, column, alpha
+  if (ep.row_scale) {
+    const float rs = ep.row_scale[row];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) v[c] = __fmul_rn(v[c], rs);
+  }
+  if (ep.col_scale) {
+    if (full && ep.params_aligned) {
+#pragma unroll
+      for (int c = 0; c < 32; c += 4) {
+        const float4 s4 = *reinterpret_cast<const float4 *>(ep.col_scale + col0 + c);  // col0 % 32 == 0
+        v[c] = __fmul_rn(v[c], s4.x); v[c + 1] = __fmul_rn(v[c + 1], s4.y);
+        v[c + 2] = __fmul_rn(v[c + 2], s4.z); v[c + 3] = __fmul_rn(v[c + 3], s4.w);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = __fmul_rn(v[c], c < ncols ? ep.col_scale[col0 + c] : 1.f);
+    }
+  }
+  if (ep.alpha != 1.f) {
+#pragma unroll
+    for (int c = 0; c < 32; ++c) v[c] = __fmul_rn(v[c], ep.alpha);
+  }
+  // 3. additive terms
+  switch (ep.bias_mode) {
+    case SOFIE_B200_BIAS_COL_F32:
+      if (full && ep.params_aligned) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          const float4 b4 = *reinterpret_cast<const float4 *>((const float *)ep.bias + col0 + c);
+          v[c] = __fadd_rn(v[c], b4.x); v[c + 1] = __fadd_rn(v[c + 1], b4.y);
+          v[c + 2] = __fadd_rn(v[c + 2], b4.z); v[c + 3] = __fadd_rn(v[c + 3], b4.w);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          if (c < ncols) v[c] = __fadd_rn(v[c], ((const float *)ep.bias)[col0 + c]);
+      }
+      break;
+    case SOFIE_B200_BIAS_ROW_F32: {
+      const float br = ((const float *)ep.bias)[row];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = __fadd_rn(v[c], br);
+      break;
+    }
+    case SOFIE_B200_BIAS_SCALAR_F32: {
+      const float bs = ((const float *)ep.bias)[0];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = __fadd_rn(v[c], bs);
+      break;
+    }
+    case SOFIE_B200_BIAS_FULL_F32: {
+      const float *cr = (const float *)ep.bias + b * ep.stride_c + row * ep.ldc + col0;
+#pragma unroll
+      for (int c = 0; c < 32; ++c)
+        if (full || c < ncols) v[c] = __fadd_rn(v[c], __fmul_rn(ep.beta, cr[c]));
+      break;
+    }
+    default: break;
+  }
+  if (ep.residual) {
+    const long long roff = b * ep.stride_r + row * ep.ldr + col0;
+    if (ep.residual_dtype == SOFIE_B200_BF16) {
+      const __nv_bfloat16 *r = (const __nv_bfloat16 *)ep.residual + roff;
+#pragma unroll
+      for (int c = 0; c < 32; ++c)
+        if (full || c < ncols) v[c] = __fadd_rn(v[c], __bfloat162float(r[c]));
+    } else {
+      const float *r = (const float *)ep.residual + roff;
+#pragma unroll
+      for (int c = 0; c < 32; ++c)
+        if (full || c < ncols) v[c] = __fadd_rn(v[c], r[c]);
+    }
+  }
+  // 4. activation
+  switch (ep.act) {
+    case SOFIE_B200_ACT_NONE: break;
+    case SOFIE_B200_ACT_RELU:
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_RELU, 0.f);
+      break;
+    case SOFIE_B200_ACT_GELU_ERF:
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_GELU_ERF, 0.f);
+      break;
+    default:
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], ep.act, ep.act_alpha);
+      break;
+  }
+  // 5. convert and store
+  if (ep.y_dtype == SOFIE_B200_F32) {
+    float *y = (float *)ep.Y + off;
+    if (vec && full) {
+#pragma unroll
+      for (int c = 0; c < 32; c += 4)
+        st_v4(y + c, __float_as_uint(v[c]), __float_as_uint(v[c + 1]), __float_as_uint(v[c + 2]), __float_as_uint(v[c + 3]));
+    } else {
+#pragma unroll
+      for (int c = 0; c < 32; ++c)
+        if (c < ncols) y[c] = v[c];
+    }
+  } else if (ep.y_dtype == SOFIE_B200_BF16) {
+    __nv_bfloat16 *y = (__nv_bfloat16 *)ep.Y + off;
+    if (vec && full) {
+#pragma unroll
+      for (int c = 0; c < 32; c += 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(v[c + 2 * u], v[c + 2 * u + 1]);
+          w[u] = *reinterpret_cast<uint32_t *>(&h2);
+        }
+        st_v4(y + c, w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 32; ++c)
+        if (c < ncols) y[c] = __float2bfloat16_rn(v[c]);
+    }
+  } else {  // I8 / U8: ONNX rounding (half to even), zero point, saturate
+    const float lo = ep.y_dtype == SOFIE_B200_I8 ? -128.f : 0.f;
+    const float hi = ep.y_dtype == SOFIE_B200_I8 ? 127.f : 255.f;
+    const float zp = (float)ep.out_zp;
+    if (ep.out_scale != 1.f) {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = __fdiv_rn(v[c], ep.out_scale);
+    }
+    uint32_t q[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) q[c] = (uint32_t)(int)fminf(fmaxf(rintf(v[c]) + zp, lo), hi) & 0xffu;
+    uint8_t *y = (uint8_t *)ep.Y + off;
+    if (vec && full) {
+#pragma unroll
+      for (int c = 0; c < 32; c += 16) {
+        uint32_t w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          w[u] = q[c + 4 * u] | (q[c + 4 * u + 1] << 8) | (q[c + 4 * u + 2] << 16) | (q[c + 4 * u + 3] << 24);
+        st_v4(y + c, w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 32; ++c)
+        if (c < ncols) y[c] = (uint8_t)q[c];
+    }
+  }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(UMMA_THREADS, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ UmmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;  // swizzle atoms are 1024-byte aligned
+  uint8_t *smem = smem_raw + pad;
+
+  const int stages = p.stages;
+  const uint32_t smem_a = smem_u32(smem);
+  const uint32_t smem_b = smem_a + stages * p.a_stage_bytes;
+  uint8_t *tail = smem + stages * (p.a_stage_bytes + p.b_stage_bytes);
+  const uint32_t bar_full = smem_u32(tail);             // [stages]
+  const uint32_t bar_empty = bar_full + 8 * stages;     // [stages]
+  const uint32_t bar_tfull = bar_empty + 8 * stages;    // [2]
+  const uint32_t bar_tempty = bar_tfull + 16;           // [2]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail + 16 * stages + 32);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_tfull + 8 * i, 1);
+      mbar_init(bar_tempty + 8 * i, 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        const int b = (int)(t / tiles_per_batch);
+        const int r = (int)(t % tiles_per_batch);
+        const int m0 = (r % p.tiles_m) * UMMA_BM;
+        const int n0 = (r / p.tiles_m) * p.bn;
+        const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+            raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_EMPTY);
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_arrive_expect_tx(full, p.a_stage_bytes + p.b_stage_bytes);
+          const int k0 = kb * p.kb_elems;
+          const uint32_t sa = smem_a + stage * p.a_stage_bytes;
+          const uint32_t sb = smem_b + stage * p.b_stage_bytes;
+          if (!p.a_mn) {
+            tma_load_3d(sa, &tm_a, full, k0, m0, ba);
+          } else {
+            for (int x = 0; x < p.a_boxes; ++x)
+              tma_load_3d(sa + x * p.a_box_bytes, &tm_a, full, m0 + x * p.a_box_mn, k0, ba);
+          }
+          if (!p.b_mn) {
+            tma_load_3d(sb, &tm_b, full, k0, n0, bb);
+          } else {
+            for (int x = 0; x < p.b_boxes; ++x)
+              tma_load_3d(sb + x * p.b_box_bytes, &tm_b, full, n0 + x * p.b_box_mn, k0, bb);
+          }
+          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // give copies that may still be in flight time to land before the CTA exits
+        const uint64_t t0 = globaltimer();
+        while (globaltimer() - t0 < 200000ull) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) {
+          raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_EMPTY);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * p.bn;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+            raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_a + stage * p.a_stage_bytes;
+          const uint32_t sb = smem_b + stage * p.b_stage_bytes;
+          const uint32_t a_lo = p.a_desc_lo | ((sa >> 4) & 0x3fffu);
+          const uint32_t b_lo = p.b_desc_lo | ((sb >> 4) & 0x3fffu);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t ad = ((uint64_t)p.a_desc_hi << 32) | (uint64_t)(a_lo + k * p.a_kadv);
+            const uint64_t bd = ((uint64_t)p.b_desc_hi << 32) | (uint64_t)(b_lo + k * p.b_kadv);
+            umma<KIND>(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(bar_empty + 8 * stage);  // stage may be refilled once these MMAs have read it
+          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(bar_tfull + 8 * acc);      // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue -----------------------------------------
+    const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
+    uint32_t acc = 0, acc_phase = 0;
+    for (long long t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+      const int b = (int)(t / tiles_per_batch);
+      const int r = (int)(t % tiles_per_batch);
+      const int m0 = (r % p.tiles_m) * UMMA_BM;
+      const int n0 = (r / p.tiles_m) * p.bn;
+      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+        raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_FULL);
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * p.bn;
+      for (int c = 0; c < p.bn; c += 32) {
+        if (n0 + c >= p.N) break;  // warp-uniform
+        uint32_t raw[32];
+        tmem_ld_x32(taddr + c, raw);
+        tmem_ld_wait();
+        if (row < p.M) {
+          const int ncols = min(32, p.N - (n0 + c));
+          store_chunk(p.ep, raw, b, row, n0 + c, ncols, p.vec_ok != 0);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+}
+
+// ------------------------------------ host side ------------------------------------------
+
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(sym);
+  });
+  return fn;
+}
+
+static int encode_map(CUtensorMap *tm, int dtype, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
+                      uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1) {
+  auto enc = get_encode();
+  if (!enc) return fail(SOFIE_B200_ERR_NO_DEVICE, "cuTensorMapEncodeTiled entry point not available");
+  CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  if (dtype == SOFIE_B200_BF16) dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (dtype == SOFIE_B200_F32) dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(SOFIE_B200_ERR_CUDA,
+                "cuTensorMapEncodeTiled failed (%d): dims %llu,%llu,%llu strides %llu,%llu box %u,%u", (int)r,
+                (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2,
+                (unsigned long long)stride1_bytes, (unsigned long long)stride2_bytes, b0, b1);
+  return 0;
+}
+
+static int pick_bn(long long N, long long tiles_m, long long batch, int sms, int min_bn) {
+  // Per-tile time model: MMA time grows with bn, shared-memory operand traffic with 128 + bn.
+  const int cand[4] = {256, 128, 64, 32};
+  int best = 256;
+  double best_cost = 1e300;
+  for (int bn : cand) {
+    if (bn < min_bn) continue;
+    long long tiles = tiles_m * ((N + bn - 1) / bn) * batch;
+    long long waves = (tiles + sms - 1) / sms;
+    double per_tile = bn > 0.67 * (128 + bn) ? (double)bn : 0.67 * (128 + bn);
+    double cost = waves * (per_tile + 8.0);
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
+int umma_plan_init(sofie_b200_gemm_plan *plan) {
+  const sofie_b200_gemm_desc &d = plan->desc;
+  UmmaParams &u = plan->up;
+  int kind, es;
+  switch (d.ab_dtype) {
+    case SOFIE_B200_I8: kind = KIND_I8; es = 1; break;
+    case SOFIE_B200_F8E4M3: kind = KIND_F8; es = 1; break;
+    case SOFIE_B200_BF16: kind = KIND_F16; es = 2; break;
+    case SOFIE_B200_F32: kind = KIND_TF32; es = 4; break;
+    default: return 1;
+  }
+  // TMA needs 16-byte multiples for every global stride.
+  if ((d.lda * es) % 16 || (d.ldb * es) % 16) return 1;
+  if (d.batch > 1 && (((d.stride_a * es) % 16) || ((d.stride_b * es) % 16))) return 1;
+  if (d.M <= 0 || d.N <= 0 || d.K <= 0) return 1;
+  // TF32 operands are taken K-major only (an MN-major fp32 operand goes to the CUDA-core kernel)
+  if (d.ab_dtype == SOFIE_B200_F32 && (d.trans_a || !d.trans_b)) return 1;
+  if (d.M > 0x7fffffffLL || d.N > 0x7fffffffLL || d.K > 0x7fffffffLL) return 1;
+
+  plan->kind = kind;
+  u.M = (int)d.M; u.N = (int)d.N; u.K = (int)d.K; u.batch = (int)d.batch;
+  u.tiles_m = (int)((d.M + UMMA_BM - 1) / UMMA_BM);
+  // an MN-major B tile is made of 128-byte-wide TMA boxes, so bn*es must reach 128
+  u.bn = pick_bn(d.N, u.tiles_m, d.batch, plan->ctx->sm_count, d.trans_b ? 32 : 128 / es);
+  u.tiles_n = (int)((d.N + u.bn - 1) / u.bn);
+  u.num_tiles = (long long)u.tiles_m * u.tiles_n * d.batch;
+  u.kb_elems = UMMA_STAGE_K_BYTES / es;
+  u.num_kb = (int)((d.K + u.kb_elems - 1) / u.kb_elems);
+  u.a_stage_bytes = UMMA_BM * UMMA_STAGE_K_BYTES;
+  u.b_stage_bytes = u.bn * UMMA_STAGE_K_BYTES;
+  u.tmem_cols = 32;
+  while (u.tmem_cols < 2u * u.bn) u.tmem_cols <<= 1;
+
+  const size_t budget = 227 * 1024 - 1024 /*alignment*/ - 512 /*barriers*/;
+  int stages = (int)(budget / (u.a_stage_bytes + u.b_stage_bytes));
+  if (stages > 8) stages = 8;
+  if (stages < 2) return 1;
+  u.stages = stages;
+  plan->smem_bytes = (size_t)stages * (u.a_stage_bytes + u.b_stage_bytes) + 1024 + 512;
+
+  u.a_mn = d.trans_a ? 1 : 0;   // stored [K,M]: M contiguous
+  u.b_mn = d.trans_b ? 0 : 1;   // stored [K,N]: N contiguous
+  u.a_bcast = (d.batch > 1 && d.stride_a == 0);
+  u.b_bcast = (d.batch > 1 && d.stride_b == 0);
+
+  // Shared-memory matrix descriptors (128B swizzle): stride byte offset = 1024 (one 8-row
+  // swizzle atom), descriptor version 1, layout type 2 (SWIZZLE_128B).
+  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  u.a_desc_hi = hi;
+  u.b_desc_hi = hi;
+  const uint32_t panel_bytes = (uint32_t)u.kb_elems * 128u;  // one MN-major box: 128 bytes x K rows
+  const uint32_t k_rows_per_mma = 32u / es;
+  if (!u.a_mn) { u.a_desc_lo = 1u << 16; u.a_kadv = 32u >> 4; u.a_boxes = 1; u.a_box_bytes = u.a_stage_bytes; u.a_box_mn = 0; }
+  else { u.a_desc_lo = ((panel_bytes >> 4) & 0x3fffu) << 16; u.a_kadv = (k_rows_per_mma * 128u) >> 4;
+         u.a_boxes = (UMMA_BM * es) / 128; u.a_box_bytes = panel_bytes; u.a_box_mn = 128 / es; }
+  if (!u.b_mn) { u.b_desc_lo = 1u << 16; u.b_kadv = 32u >> 4; u.b_boxes = 1; u.b_box_bytes = u.b_stage_bytes; u.b_box_mn = 0; }
+  else { u.b_desc_lo = ((panel_bytes >> 4) & 0x3fffu) << 16; u.b_kadv = (k_rows_per_mma * 128u) >> 4;
+         u.b_boxes = (u.bn * es) / 128; u.b_box_bytes = panel_bytes; u.b_box_mn = 128 / es;
+         if (u.b_boxes < 1) return 1; }
+
+  // Instruction descriptor: D format [4,6), A format [7,10), B format [10,13), A major bit 15,
+  // B major bit 16, N>>3 at [17,23), M>>4 at [24,29).
+  uint32_t cfmt, abfmt;
+  switch (kind) {
+    case KIND_I8: cfmt = 2; abfmt = 1; break;    // S32 accumulate, signed 8-bit operands
+    case KIND_F8: cfmt = 1; abfmt = 0; break;    // F32 accumulate, E4M3
+    case KIND_F16: cfmt = 1; abfmt = 1; break;   // F32 accumulate, BF16
+    default: cfmt = 1; abfmt = 2; break;         // F32 accumulate, TF32
+  }
+  u.idesc = (cfmt << 4) | (abfmt << 7) | (abfmt << 10) | ((uint32_t)u.a_mn << 15) | ((uint32_t)u.b_mn << 16) |
+            ((uint32_t)(u.bn >> 3) << 17) | ((uint32_t)(UMMA_BM >> 4) << 24);
+
+  const int ys = dtype_size(d.y_dtype);
+  u.vec_ok = ((d.ldy * ys) % 16 == 0) && ((d.stride_y * ys) % 16 == 0);
+  u.status = plan->ctx->d_status;
+
+  long long grid = u.num_tiles < plan->ctx->sm_count ? u.num_tiles : plan->ctx->sm_count;
+  plan->grid = (int)grid;
+
+  cudaError_t e = cudaSuccess;
+  switch (kind) {
+    case KIND_I8: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan->smem_bytes); break;
+    case KIND_F8: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan->smem_bytes); break;
+    case KIND_F16: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan->smem_bytes); break;
+    default: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan->smem_bytes); break;
+  }
+  if (e != cudaSuccess) return fail(SOFIE_B200_ERR_CUDA, "cudaFuncSetAttribute(smem=%zu): %s", plan->smem_bytes, cudaGetErrorString(e));
+  return 0;
+}
+
+static int build_maps(sofie_b200_gemm_plan *plan, const void *A, const void *B) {
+  const sofie_b200_gemm_desc &d = plan->desc;
+  const UmmaParams &u = plan->up;
+  const int es = dtype_size(d.ab_dtype);
+  if (A != plan->cached_a) {
+    if ((uintptr_t)A % 16) return fail(SOFIE_B200_ERR_INVALID, "A must be 16-byte aligned for the tcgen05 path");
+    const uint64_t nb = u.a_bcast ? 1 : (uint64_t)d.batch;
+    int rc;
+    if (!u.a_mn) {
+      uint64_t s2 = d.batch > 1 && !u.a_bcast ? (uint64_t)d.stride_a * es : (uint64_t)d.M * d.lda * es;
+      rc = encode_map(&plan->tm_a, d.ab_dtype, A, (uint64_t)d.K, (uint64_t)d.M, nb, (uint64_t)d.lda * es, s2,
+                      (uint32_t)u.kb_elems, UMMA_BM);
+    } else {
+      uint64_t s2 = d.batch > 1 && !u.a_bcast ? (uint64_t)d.stride_a * es : (uint64_t)d.K * d.lda * es;
+      rc = encode_map(&plan->tm_a, d.ab_dtype, A, (uint64_t)d.M, (uint64_t)d.K, nb, (uint64_t)d.lda * es, s2,
+                      (uint32_t)u.a_box_mn, (uint32_t)u.kb_elems);
+    }
+    if (rc) return rc;
+    plan->cached_a = A;
+  }
+  if (B != plan->cached_b) {
+    if ((uintptr_t)B % 16) return fail(SOFIE_B200_ERR_INVALID, "B must be 16-byte aligned for the tcgen05 path");
+    const uint64_t nb = u.b_bcast ? 1 : (uint64_t)d.batch;
+    int rc;
+    if (!u.b_mn) {
+      uint64_t s2 = d.batch > 1 && !u.b_bcast ? (uint64_t)d.stride_b * es : (uint64_t)d.N * d.ldb * es;
+      rc = encode_map(&plan->tm_b, d.ab_dtype, B, (uint64_t)d.K, (uint64_t)d.N, nb, (uint64_t)d.ldb * es, s2,
+                      (uint32_t)u.kb_elems, (uint32_t)u.bn);
+    } else {
+      uint64_t s2 = d.batch > 1 && !u.b_bcast ? (uint64_t)d.stride_b * es : (uint64_t)d.K * d.ldb * es;
+      rc = encode_map(&plan->tm_b, d.ab_dtype, B, (uint64_t)d.N, (uint64_t)d.K, nb, (uint64_t)d.ldb * es, s2,
+                      (uint32_t)u.b_box_mn, (uint32_t)u.kb_elems);
+    }
+    if (rc) return rc;
+    plan->cached_b = B;
+  }
+  return 0;
+}
+
+int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep) {
+  int rc = build_maps(plan, A, B);
+  if (rc) return rc;
+  UmmaParams u = plan->up;
+  u.ep = ep;
+  if (((uintptr_t)ep.Y % 16) != 0) u.vec_ok = 0;
+  cudaStream_t st = plan->ctx->stream;
+  dim3 grid(plan->grid), block(UMMA_THREADS);
+  switch (plan->kind) {
+    case KIND_I8: umma_gemm_kernel<KIND_I8><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, u); break;
+    case KIND_F8: umma_gemm_kernel<KIND_F8><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, u); break;
+    case KIND_F16: umma_gemm_kernel<KIND_F16><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, u); break;
+    default: umma_gemm_kernel<KIND_TF32><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, u); break;
+  }
+  SB_CUDA(cudaGetLastError());
+  plan->ctx->launches++;
+  return 0;
+}
+
+}  // namespace sb200

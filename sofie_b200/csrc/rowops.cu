@@ -1,0 +1,318 @@
+// LayerNormalization and Softmax: the row-wise memory-bound operators the fusion pass leaves.
+//
+// Each row is read from HBM exactly once with 128-bit loads into registers, reduced with warp
+// shuffles, and written once with 128-bit stores.  A row is owned by a group of G lanes
+// (G = 4..32, the smallest power of two whose 16-byte chunks cover the row), so short rows
+// (Softmax over 128 attention scores) keep every lane busy and long rows (LayerNorm over
+// d_model) use a whole warp.  Rows too long for the register cache, or not 16-byte aligned,
+// take a CTA-per-row kernel that re-reads through L2.
+//
+// Arithmetic follows the reference's CPU code: LayerNorm is two-pass (mean, then biased
+// variance of x-mean), invStd = 1/sqrt(var+eps), y = scale*invStd*(x-mean)+bias
+// (ROperator_LayerNormalization.hxx:257-312); Softmax is max, exp(x-max), sum, multiply by the
+// reciprocal of the sum (ROperator_Softmax.hxx:97-118).
+#include "common.cuh"
+
+namespace sb200 {
+
+template <typename T> struct Vec16;  // one 16-byte chunk of T as floats
+template <> struct Vec16<float> {
+  static constexpr int E = 4;
+  static __device__ __forceinline__ void load(const float *p, float *v) {
+    float4 t = *reinterpret_cast<const float4 *>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  }
+  static __device__ __forceinline__ void store(float *p, const float *v) {
+    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int E = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16 *p, float *v) {
+    uint4 t = *reinterpret_cast<const uint4 *>(p);
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16 *p, const float *v) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t *>(&h);
+    }
+    *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+// Stores E floats (E = elements of one input chunk) as TOut; may take one or two 16-byte stores.
+template <typename TOut, int E>
+__device__ __forceinline__ void store_chunk_as(TOut *p, const float *v) {
+  if constexpr (std::is_same<TOut, float>::value) {
+#pragma unroll
+    for (int i = 0; i < E; i += 4) Vec16<float>::store(p + i, v + i);
+  } else {
+    if constexpr (E == 8) {
+      Vec16<__nv_bfloat16>::store(p, v);
+    } else {  // 4 bf16 = 8 bytes
+      __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+      *reinterpret_cast<uint2 *>(p) = make_uint2(*reinterpret_cast<uint32_t *>(&a), *reinterpret_cast<uint32_t *>(&b));
+    }
+  }
+}
+
+__device__ __forceinline__ float group_sum(float v, int G) {
+  for (int o = G >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float group_max(float v, int G) {
+  for (int o = G >> 1; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// MODE 0: LayerNorm, 1: Softmax, 2: LogSoftmax.  CH = 16-byte chunks cached per lane.
+template <typename TIn, typename TOut, int CH, int MODE>
+__global__ void __launch_bounds__(256) row_group_kernel(const TIn *__restrict__ x, TOut *__restrict__ y, long long rows,
+                                                        int cols, int G, const float *__restrict__ scale,
+                                                        const float *__restrict__ bias, float eps,
+                                                        float *__restrict__ mean_out, float *__restrict__ invstd_out) {
+  constexpr int E = Vec16<TIn>::E;
+  const int lane = threadIdx.x & 31;
+  const int gl = lane & (G - 1);                   // lane within the group
+  const int groups_per_cta = blockDim.x / G;
+  const long long gid0 = (long long)blockIdx.x * groups_per_cta + threadIdx.x / G;
+  const long long gstride = (long long)gridDim.x * groups_per_cta;
+  const float inv_n = 1.f / (float)cols;
+  const long long iters = (rows + gstride - 1) / gstride;  // same trip count for every thread
+  for (long long it = 0; it < iters; ++it) {
+    // all lanes of a warp must reach the shuffles: rows beyond the end compute on filler values
+    const long long row = gid0 + it * gstride;
+    const bool live = row < rows;
+    const TIn *xr = x + row * (long long)cols;
+    float v[CH][E];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int col = (c * G + gl) * E;
+      if (live && col < cols) Vec16<TIn>::load(xr + col, v[c]);
+      else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) v[c][e] = MODE == 0 ? 0.f : -INFINITY;
+      }
+    }
+    if constexpr (MODE == 0) {
+      float s = 0.f;
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+#pragma unroll
+        for (int e = 0; e < E; ++e) s += v[c][e];
+      const float mean = group_sum(s, G) * inv_n;
+      float q = 0.f;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const int col = (c * G + gl) * E;
+        if (col < cols) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) { float d = v[c][e] - mean; q += d * d; }
+        }
+      }
+      const float var = group_sum(q, G) * inv_n;
+      const float inv = 1.f / sqrtf(var + eps);
+      if (live) {
+        TOut *yr = y + row * (long long)cols;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          const int col = (c * G + gl) * E;
+          if (col < cols) {
+            float o[E];
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+              float t = (v[c][e] - mean) * inv;
+              if (scale) t *= scale[col + e];
+              if (bias) t += bias[col + e];
+              o[e] = t;
+            }
+            store_chunk_as<TOut, E>(yr + col, o);
+          }
+        }
+        if (gl == 0) {
+          if (mean_out) mean_out[row] = mean;
+          if (invstd_out) invstd_out[row] = inv;
+        }
+      }
+    } else {
+      float m = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+#pragma unroll
+        for (int e = 0; e < E; ++e) m = fmaxf(m, v[c][e]);
+      m = group_max(m, G);
+      float s = 0.f;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const int col = (c * G + gl) * E;
+        if (col < cols) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) {
+            if constexpr (MODE == 1) { v[c][e] = expf(v[c][e] - m); s += v[c][e]; }
+            else { v[c][e] = v[c][e] - m; s += expf(v[c][e]); }
+          }
+        }
+      }
+      s = group_sum(s, G);
+      const float r = MODE == 1 ? 1.f / s : logf(s);
+      if (live) {
+        TOut *yr = y + row * (long long)cols;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          const int col = (c * G + gl) * E;
+          if (col < cols) {
+            float o[E];
+#pragma unroll
+            for (int e = 0; e < E; ++e) o[e] = MODE == 1 ? v[c][e] * r : v[c][e] - r;
+            store_chunk_as<TOut, E>(yr + col, o);
+          }
+        }
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float ld_as_float(const float *p) { return *p; }
+__device__ __forceinline__ float ld_as_float(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void st_from_float(float *p, float v) { *p = v; }
+__device__ __forceinline__ void st_from_float(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <int OP>  // 0 sum, 1 max
+__device__ __forceinline__ float block_reduce(float v, float *sh) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  v = OP == 0 ? group_sum(v, 32) : group_max(v, 32);
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  float r = OP == 0 ? 0.f : -INFINITY;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) r = OP == 0 ? r + sh[i] : fmaxf(r, sh[i]);
+  return r;
+}
+
+// One CTA per row, scalar accesses, the row re-read through L2: any length, any alignment.
+template <typename TIn, typename TOut, int MODE>
+__global__ void __launch_bounds__(256) row_block_kernel(const TIn *__restrict__ x, TOut *__restrict__ y, long long rows,
+                                                        long long cols, const float *__restrict__ scale,
+                                                        const float *__restrict__ bias, float eps,
+                                                        float *__restrict__ mean_out, float *__restrict__ invstd_out) {
+  __shared__ float sh[8];
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const TIn *xr = x + row * cols;
+    TOut *yr = y + row * cols;
+    if constexpr (MODE == 0) {
+      float s = 0.f;
+      for (long long c = threadIdx.x; c < cols; c += blockDim.x) s += ld_as_float(xr + c);
+      const float mean = block_reduce<0>(s, sh) / (float)cols;
+      float q = 0.f;
+      for (long long c = threadIdx.x; c < cols; c += blockDim.x) { float d = ld_as_float(xr + c) - mean; q += d * d; }
+      const float var = block_reduce<0>(q, sh) / (float)cols;
+      const float inv = 1.f / sqrtf(var + eps);
+      for (long long c = threadIdx.x; c < cols; c += blockDim.x) {
+        float t = (ld_as_float(xr + c) - mean) * inv;
+        if (scale) t *= scale[c];
+        if (bias) t += bias[c];
+        st_from_float(yr + c, t);
+      }
+      if (threadIdx.x == 0) {
+        if (mean_out) mean_out[row] = mean;
+        if (invstd_out) invstd_out[row] = inv;
+      }
+    } else {
+      float m = -INFINITY;
+      for (long long c = threadIdx.x; c < cols; c += blockDim.x) m = fmaxf(m, ld_as_float(xr + c));
+      m = block_reduce<1>(m, sh);
+      float s = 0.f;
+      for (long long c = threadIdx.x; c < cols; c += blockDim.x) s += expf(ld_as_float(xr + c) - m);
+      s = block_reduce<0>(s, sh);
+      const float r = MODE == 1 ? 1.f / s : logf(s);
+      for (long long c = threadIdx.x; c < cols; c += blockDim.x) {
+        float d = ld_as_float(xr + c) - m;
+        st_from_float(yr + c, MODE == 1 ? expf(d) * r : d - r);
+      }
+    }
+  }
+}
+
+template <typename TIn, typename TOut, int MODE>
+static int launch_rows(sofie_b200_ctx *ctx, const void *x, void *y, long long rows, long long cols, const float *scale,
+                       const float *bias, float eps, float *mean_out, float *invstd_out) {
+  constexpr int E = Vec16<TIn>::E;
+  cudaStream_t st = ctx->stream;
+  const bool aligned = (cols % E == 0) && ((uintptr_t)x % 16 == 0) &&
+                       ((uintptr_t)y % (sizeof(TOut) * E > 16 ? 16 : sizeof(TOut) * E) == 0);
+  const long long chunks = (cols + E - 1) / E;
+  if (aligned && chunks <= 32 * 16) {
+    int G = 4;
+    while (G < 32 && G < chunks) G <<= 1;
+    const int ch = (int)((chunks + G - 1) / G);
+    const int groups_per_cta = 256 / G;
+    long long ctas = (rows + groups_per_cta - 1) / groups_per_cta;
+    const long long cap = (long long)ctas > (long long)ctx->sm_count * 32 ? (long long)ctx->sm_count * 32 : ctas;
+    const unsigned grid = (unsigned)(cap < 1 ? 1 : cap);
+    const TIn *xi = (const TIn *)x;
+    TOut *yo = (TOut *)y;
+#define SB_ROW_LAUNCH(CHV) \
+  row_group_kernel<TIn, TOut, CHV, MODE><<<grid, 256, 0, st>>>(xi, yo, rows, (int)cols, G, scale, bias, eps, mean_out, invstd_out)
+    if (ch <= 1) SB_ROW_LAUNCH(1);
+    else if (ch <= 2) SB_ROW_LAUNCH(2);
+    else if (ch <= 4) SB_ROW_LAUNCH(4);
+    else if (ch <= 8) SB_ROW_LAUNCH(8);
+    else SB_ROW_LAUNCH(16);
+#undef SB_ROW_LAUNCH
+  } else {
+    long long g = rows < (long long)ctx->sm_count * 16 ? rows : (long long)ctx->sm_count * 16;
+    row_block_kernel<TIn, TOut, MODE><<<(unsigned)g, 256, 0, st>>>((const TIn *)x, (TOut *)y, rows, cols, scale, bias,
+                                                                    eps, mean_out, invstd_out);
+  }
+  SB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return 0;
+}
+
+template <int MODE>
+static int dispatch_rows(sofie_b200_ctx *ctx, const void *x, void *y, int xd, int yd, long long rows, long long cols,
+                         const float *scale, const float *bias, float eps, float *mo, float *io) {
+  if (xd == SOFIE_B200_F32 && yd == SOFIE_B200_F32) return launch_rows<float, float, MODE>(ctx, x, y, rows, cols, scale, bias, eps, mo, io);
+  if (xd == SOFIE_B200_BF16 && yd == SOFIE_B200_BF16) return launch_rows<__nv_bfloat16, __nv_bfloat16, MODE>(ctx, x, y, rows, cols, scale, bias, eps, mo, io);
+  if (xd == SOFIE_B200_F32 && yd == SOFIE_B200_BF16) return launch_rows<float, __nv_bfloat16, MODE>(ctx, x, y, rows, cols, scale, bias, eps, mo, io);
+  if (xd == SOFIE_B200_BF16 && yd == SOFIE_B200_F32) return launch_rows<__nv_bfloat16, float, MODE>(ctx, x, y, rows, cols, scale, bias, eps, mo, io);
+  return fail(SOFIE_B200_ERR_INVALID, "row operator: types %d -> %d not supported (F32 and BF16 only)", xd, yd);
+}
+
+}  // namespace sb200
+
+using namespace sb200;
+
+extern "C" {
+
+int sofie_b200_layernorm_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t x_dtype, int32_t y_dtype,
+                                 int64_t rows, int64_t cols, const float *scale, const float *bias, float eps,
+                                 float *mean_out, float *invstd_out) {
+  if (!ctx) return fail(SOFIE_B200_ERR_INVALID, "layernorm_enqueue: ctx is NULL");
+  if (rows < 0 || cols < 0) return fail(SOFIE_B200_ERR_INVALID, "layernorm_enqueue: negative extent");
+  if (rows == 0 || cols == 0) return 0;
+  if (!x || !y) return fail(SOFIE_B200_ERR_INVALID, "layernorm_enqueue: NULL tensor");
+  SB_CUDA(cudaSetDevice(ctx->device));
+  return dispatch_rows<0>(ctx, x, y, x_dtype, y_dtype, rows, cols, scale, bias, eps, mean_out, invstd_out);
+}
+
+int sofie_b200_softmax_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t x_dtype, int32_t y_dtype,
+                               int64_t rows, int64_t cols, int32_t log_softmax) {
+  if (!ctx) return fail(SOFIE_B200_ERR_INVALID, "softmax_enqueue: ctx is NULL");
+  if (rows < 0 || cols < 0) return fail(SOFIE_B200_ERR_INVALID, "softmax_enqueue: negative extent");
+  if (rows == 0 || cols == 0) return 0;
+  if (!x || !y) return fail(SOFIE_B200_ERR_INVALID, "softmax_enqueue: NULL tensor");
+  SB_CUDA(cudaSetDevice(ctx->device));
+  if (log_softmax) return dispatch_rows<2>(ctx, x, y, x_dtype, y_dtype, rows, cols, nullptr, nullptr, 0.f, nullptr, nullptr);
+  return dispatch_rows<1>(ctx, x, y, x_dtype, y_dtype, rows, cols, nullptr, nullptr, 0.f, nullptr, nullptr);
+}
+
+}  // extern "C"

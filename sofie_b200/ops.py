@@ -1,0 +1,196 @@
+"""Host-side handles over the C ABI: a Context (the Session's queue + blas object) and plans.
+
+torch is used for device memory and streams only; every computation is a call into
+libsofie_b200.so.  Tensors must live on the context's CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import lib as L
+
+_DT = {
+    torch.float32: L.F32,
+    torch.bfloat16: L.BF16,
+    torch.int8: L.I8,
+    torch.float8_e4m3fn: L.F8E4M3,
+    torch.int32: L.I32,
+    torch.uint8: L.U8,
+}
+
+
+def dtype_code(t: torch.dtype) -> int:
+    try:
+        return _DT[t]
+    except KeyError:
+        raise TypeError(f"dtype {t} is not part of the sofie_b200 ABI") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("sofie_b200 operators take CUDA tensors; host data goes through run_host()")
+    return t.data_ptr()
+
+
+class Context:
+    """One per Session / GPU / stream (sofie_b200_ctx)."""
+
+    def __init__(self, device: int = 0, stream: Optional[torch.cuda.Stream] = None):
+        self._lib = L.load()
+        self.device = device
+        self.stream = stream
+        h = C.c_void_p()
+        sp = C.c_void_p(stream.cuda_stream) if stream is not None else C.c_void_p(
+            torch.cuda.current_stream(device).cuda_stream)
+        L.check(self._lib.sofie_b200_ctx_create(C.byref(h), device, sp), "ctx_create")
+        self._h = h
+
+    def sync(self) -> None:
+        L.check(self._lib.sofie_b200_ctx_sync(self._h), "ctx_sync")
+
+    @property
+    def launches(self) -> int:
+        return int(self._lib.sofie_b200_ctx_launch_count(self._h))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.sofie_b200_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- memory-bound operators -----------------------------------------------------
+    def layernorm(self, x, y, scale=None, bias=None, eps=1e-5, mean_out=None, invstd_out=None):
+        cols = x.shape[-1]
+        rows = x.numel() // cols
+        L.check(self._lib.sofie_b200_layernorm_enqueue(
+            self._h, _ptr(x), _ptr(y), dtype_code(x.dtype), dtype_code(y.dtype), rows, cols, _ptr(scale),
+            _ptr(bias), eps, _ptr(mean_out), _ptr(invstd_out)), "layernorm_enqueue")
+
+    def softmax(self, x, y, log_softmax=False):
+        cols = x.shape[-1]
+        rows = x.numel() // cols if cols else 0
+        L.check(self._lib.sofie_b200_softmax_enqueue(
+            self._h, _ptr(x), _ptr(y), dtype_code(x.dtype), dtype_code(y.dtype), rows, cols, int(log_softmax)),
+            "softmax_enqueue")
+
+    def unary(self, x, y, act, act_alpha=0.0):
+        L.check(self._lib.sofie_b200_unary_enqueue(self._h, _ptr(x), _ptr(y), dtype_code(x.dtype), x.numel(), act,
+                                                   act_alpha), "unary_enqueue")
+
+    def binary(self, a, b, y, op=0, act=L.ACT_NONE):
+        L.check(self._lib.sofie_b200_binary_enqueue(self._h, _ptr(a), _ptr(b), _ptr(y), dtype_code(a.dtype),
+                                                    a.numel(), b.numel(), op, act), "binary_enqueue")
+
+    def batchnorm(self, x, y, fused_scale, bias, mean, act=L.ACT_NONE):
+        outer, ch = x.shape[0], x.shape[1]
+        inner = x.numel() // (outer * ch) if outer * ch else 0
+        L.check(self._lib.sofie_b200_batchnorm_enqueue(self._h, _ptr(x), _ptr(y), outer, ch, inner,
+                                                       _ptr(fused_scale), _ptr(bias), _ptr(mean), act),
+                "batchnorm_enqueue")
+
+    def global_avgpool(self, x, y):
+        nc = x.shape[0] * x.shape[1]
+        inner = x.numel() // nc if nc else 0
+        L.check(self._lib.sofie_b200_global_avgpool_enqueue(self._h, _ptr(x), _ptr(y), dtype_code(x.dtype), nc,
+                                                            inner), "global_avgpool_enqueue")
+
+    def quantize(self, x, q, scale, zero_point, channels=1, inner=1):
+        L.check(self._lib.sofie_b200_quantize_enqueue(self._h, _ptr(x), _ptr(q), dtype_code(q.dtype), x.numel(),
+                                                      _ptr(scale), _ptr(zero_point), channels, inner),
+                "quantize_enqueue")
+
+    def dequantize(self, q, x, scale, zero_point, channels=1, inner=1):
+        L.check(self._lib.sofie_b200_dequantize_enqueue(self._h, _ptr(q), _ptr(x), dtype_code(q.dtype), q.numel(),
+                                                        _ptr(scale), _ptr(zero_point), channels, inner),
+                "dequantize_enqueue")
+
+    def convert(self, x, y, row_scale=None):
+        cols = x.shape[-1]
+        rows = x.numel() // cols if cols else 0
+        L.check(self._lib.sofie_b200_convert_enqueue(self._h, _ptr(x), _ptr(y), dtype_code(x.dtype),
+                                                     dtype_code(y.dtype), rows, cols, _ptr(row_scale)),
+                "convert_enqueue")
+
+
+def make_epilogue(row_scale=None, col_scale=None, alpha=1.0, beta=1.0, bias=None, bias_mode=None, ldc=0,
+                  residual=None, ldr=0, act=L.ACT_NONE, act_alpha=0.0, out_scale=1.0,
+                  out_zero_point=0) -> tuple[L.Epilogue, list]:
+    """Builds a sofie_b200_epilogue from torch tensors; returns it with the tensors to keep alive."""
+    e = L.Epilogue()
+    e.row_scale = _ptr(row_scale)
+    e.col_scale = _ptr(col_scale)
+    e.alpha = alpha
+    e.beta = beta
+    if bias is not None and bias_mode is None:
+        bias_mode = L.BIAS_COL_I32 if bias.dtype == torch.int32 else L.BIAS_COL_F32
+    e.bias_mode = bias_mode or L.BIAS_NONE
+    e.bias = _ptr(bias)
+    e.ldc = ldc
+    e.residual = _ptr(residual)
+    e.residual_dtype = dtype_code(residual.dtype) if residual is not None else L.F32
+    e.ldr = ldr
+    e.act = act
+    e.act_alpha = act_alpha
+    e.out_scale = out_scale
+    e.out_zero_point = out_zero_point
+    return e, [row_scale, col_scale, bias, residual]
+
+
+class GemmPlan:
+    """One registered contraction (sofie_b200_gemm_plan)."""
+
+    def __init__(self, ctx: Context, M, N, K, ab_dtype, y_dtype, trans_a=False, trans_b=False, batch=1, lda=0,
+                 ldb=0, ldy=0, stride_a=0, stride_b=0, stride_y=0, stride_c=0, stride_r=0, precise=True):
+        self.ctx = ctx
+        self._lib = ctx._lib
+        d = L.GemmDesc()
+        d.M, d.N, d.K, d.batch = M, N, K, batch
+        d.trans_a, d.trans_b = int(trans_a), int(trans_b)
+        d.ab_dtype = dtype_code(ab_dtype)
+        d.y_dtype = dtype_code(y_dtype)
+        d.lda, d.ldb, d.ldy = lda, ldb, ldy
+        d.stride_a, d.stride_b, d.stride_y = stride_a, stride_b, stride_y
+        d.stride_c, d.stride_r = stride_c, stride_r
+        d.precise = int(precise)
+        self.desc = d
+        h = C.c_void_p()
+        L.check(self._lib.sofie_b200_gemm_plan_create(ctx._h, C.byref(d), C.byref(h)), "gemm_plan_create")
+        self._h = h
+
+    @property
+    def kernel(self) -> str:
+        return self._lib.sofie_b200_gemm_plan_kernel(self._h).decode()
+
+    def enqueue(self, A, B, Y, epilogue: Optional[L.Epilogue] = None) -> None:
+        ep = C.byref(epilogue) if epilogue is not None else None
+        L.check(self._lib.sofie_b200_gemm_enqueue(self._h, _ptr(A), _ptr(B), _ptr(Y), ep), "gemm_enqueue")
+
+    def run_host(self, hostA, hostB, hostY, epilogue: Optional[L.Epilogue] = None) -> None:
+        """Host operands (pinned or pageable CPU tensors): H2D, contraction, D2H, wait."""
+        for t in (hostA, hostB, hostY):
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError("run_host takes contiguous CPU tensors")
+        ep = C.byref(epilogue) if epilogue is not None else None
+        L.check(self._lib.sofie_b200_gemm_run_host(self._h, hostA.data_ptr(), hostB.data_ptr(), hostY.data_ptr(), ep),
+                "gemm_run_host")
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.sofie_b200_gemm_plan_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
