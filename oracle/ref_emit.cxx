@@ -9,8 +9,8 @@
 // text weight file <Name>.dat into the current directory (core/src/RModel.cxx:1744-1828,2242).
 // It also builds the benchmark MLP (fp32, 64 -> 256 -> 256 -> 10, Relu after the first two Gemms)
 // through the reference's C++ model API, the way the reference's own generators do
-// (tests/models/LowRankModelGenerator.cxx:36-51), and finally writes ref_models_gen.inc: one
-// wrapper per model so that ref_models.cxx can expose them through one C function.
+// (tests/models/LowRankModelGenerator.cxx:36-51), and finally writes ref_<Name>.cxx per model:
+// a C entry point `ref_run` around the emitted Session, built into its own shared library.
 #include "SOFIE/RModel.hxx"
 #include "SOFIE/RModelParser_ONNX.hxx"
 #include "SOFIE/operators/ROperator_Gemm.hxx"
@@ -68,6 +68,7 @@ int main(int argc, char **argv)
    const std::string dir = argv[1];
    std::ifstream list(argv[2]);
    std::vector<std::string> names;
+   std::vector<size_t> ninputs;
    for (std::string n; std::getline(list, n);) {
       if (n.empty() || n[0] == '#') continue;
       names.push_back(n);
@@ -77,18 +78,32 @@ int main(int argc, char **argv)
       RModel model = parser.Parse(dir + "/" + n + ".onnx");
       model.Generate();
       model.OutputGenerated(n + ".hxx");
+      ninputs.push_back(model.GetInputTensorNames().size());
    }
    emit_mlp("MLP_C1", 1024);
    names.push_back("MLP_C1");
+   ninputs.push_back(1);
 
-   std::ofstream inc("ref_models_gen.inc");
-   for (const auto &n : names) inc << "#include \"" << n << ".hxx\"\n";
-   for (const auto &n : names)
-      inc << "static std::vector<float> run_" << n << "(const float *x, const std::string &dir) {\n"
-          << "   SOFIE_" << n << "::Session s(dir + \"/" << n << ".dat\");\n"
-          << "   return s.infer(const_cast<float *>(x));\n}\n";
-   inc << "static const RefModel kModels[] = {\n";
-   for (const auto &n : names) inc << "   {\"" << n << "\", run_" << n << "},\n";
-   inc << "};\n";
+   // One translation unit per model: the emitted headers paste their helper functions on demand,
+   // so two of them cannot share a translation unit (nor, safely, a shared library).
+   for (size_t m = 0; m < names.size(); ++m) {
+      const auto &n = names[m];
+      std::ofstream tu("ref_" + n + ".cxx");
+      tu << "#include \"" << n << ".hxx\"\n#include <cstring>\n#include <string>\n"
+         << "static std::string g_err;\n"
+         << "extern \"C\" const char *ref_last_error(void) { return g_err.c_str(); }\n"
+         << "extern \"C\" int ref_ninputs(void) { return " << ninputs[m] << "; }\n"
+         << "extern \"C\" long ref_run(const float *const *x, const char *dir, float *out, long cap) {\n"
+         << "   try {\n"
+         << "      SOFIE_" << n << "::Session s(std::string(dir) + \"/" << n << ".dat\");\n"
+         << "      std::vector<float> y = s.infer(";
+      for (size_t i = 0; i < ninputs[m]; ++i) tu << (i ? ", " : "") << "x[" << i << "]";
+      tu << ");\n"
+         << "      const long n = long(y.size());\n"
+         << "      std::memcpy(out, y.data(), sizeof(float) * size_t(n < cap ? n : cap));\n"
+         << "      return n;\n"
+         << "   } catch (const std::exception &e) { g_err = e.what(); return -3; }\n"
+         << "}\n";
+   }
    return 0;
 }

@@ -129,8 +129,8 @@ __global__ void __launch_bounds__(256) row_group_kernel(const TIn *__restrict__ 
             float o[E];
 #pragma unroll
             for (int e = 0; e < E; ++e) {
-              float t = (v[c][e] - mean) * inv;
-              if (scale) t *= scale[col + e];
+              const float dlt = v[c][e] - mean;  // scale * invStd * (x - mean) + bias, left to right
+              float t = scale ? (scale[col + e] * inv) * dlt : inv * dlt;
               if (bias) t += bias[col + e];
               o[e] = t;
             }
@@ -216,8 +216,8 @@ __global__ void __launch_bounds__(256) row_block_kernel(const TIn *__restrict__ 
       const float var = block_reduce<0>(q, sh) / (float)cols;
       const float inv = 1.f / sqrtf(var + eps);
       for (long long c = threadIdx.x; c < cols; c += blockDim.x) {
-        float t = (ld_as_float(xr + c) - mean) * inv;
-        if (scale) t *= scale[c];
+        const float dlt = ld_as_float(xr + c) - mean;
+        float t = scale ? (scale[c] * inv) * dlt : inv * dlt;
         if (bias) t += bias[c];
         st_from_float(yr + c, t);
       }
