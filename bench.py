@@ -1,0 +1,380 @@
+#!/usr/bin/env python
+"""Benchmark of the SOFIE inference hot path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Prints ONE JSON line (rank 0).  A step is one pass of the hot path over one batch of synthetic
+input.  The default workload is the int8 QLinearMatMul M=N=K=4096 (per-tensor symmetric scales
+0.02 / 0.01, output scale 0.5, zero points 0): A [M,K] and B [K,N] int8 uniform in [-127,127],
+int32 accumulation, ONNX requantisation to int8 fused in the kernel's epilogue.
+
+  value      whole-job TOPS with operands resident in HBM (CUDA events, max over ranks)
+  e2e        the same metric through the C ABI's host-operand call (sofie_b200_gemm_run_host):
+             pinned host A and B copied in, Y copied out, inside the timed region
+  roofline   the contraction kernel against the dense tensor peak measured on this pool
+  cpu_baseline  the CPU restatement (oracle/) timed on the host cores on a bounded row sample
+
+With --impl reference the CPU implementation is the thing timed (rank 0 only).  Multi-GPU runs
+are launched with torchrun; every rank runs its own replica of the workload on its own GPU and
+nothing crosses NVLink on the data path (weak scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+L2_BYTES = 126 * 1024 * 1024
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (None until a capture exists for that workload).
+NCU_TRAFFIC_BYTES = {
+    "qlinear_matmul_4096": 33.64e6 + 0.03e6,  # profiles/umma_gemm_i8_qlinear_matmul_4096.md
+    "fp8_gemm_8192": None,
+}
+
+
+def measured_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs (NVML, read-only)."""
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thr = None
+
+    def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            uuid_index = self.index
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if vis:
+                ent = vis.split(",")[self.index]
+                uuid_index = int(ent) if ent.isdigit() else self.index
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(uuid_index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+            return
+        self._thr = threading.Thread(target=self._run, daemon=True)
+        self._thr.start()
+
+    def _run(self):
+        nv = self._nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._thr:
+            self._thr.join(timeout=1.0)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------------------------
+class QLinearMatMul:
+    """int8 x int8 -> int32 -> requantised int8 (ONNX QLinearMatMul), square."""
+
+    def __init__(self, n: int, name: str):
+        self.name, self.n = name, n
+        self.ops = 2.0 * n * n * n
+        self.unit = "TOPS"
+        self.metric = f"int8 QLinearMatMul {n}^3 throughput"
+        self.dtype = "int8"
+        self.a_scale, self.b_scale, self.y_scale = np.float32(0.02), np.float32(0.01), np.float32(0.5)
+        self.mult = float(np.float32(self.a_scale * self.b_scale) / self.y_scale)  # fp32 on the host, once
+        self.bytes_alg = 3.0 * n * n
+
+    def host_operands(self, seed: int):
+        rng = np.random.default_rng(seed)
+        a = rng.integers(-127, 128, size=(self.n, self.n), dtype=np.int8)
+        b = rng.integers(-127, 128, size=(self.n, self.n), dtype=np.int8)
+        return a, b
+
+    def epilogue(self):
+        from sofie_b200.ops import make_epilogue
+        return make_epilogue(alpha=self.mult)
+
+    def plan(self, ctx):
+        import torch
+        from sofie_b200.ops import GemmPlan
+        return GemmPlan(ctx, self.n, self.n, self.n, torch.int8, torch.int8, trans_b=False)
+
+    def torch_dtypes(self):
+        import torch
+        return torch.int8, torch.int8
+
+    # CPU restatement on `rows` rows of A (all of B): ops = 2*rows*n*n
+    def cpu_rows(self, lib, a, b, rows: int) -> float:
+        from sofie_b200 import lib as L
+        d = L.GemmDesc()
+        d.M, d.N, d.K, d.batch = rows, self.n, self.n, 1
+        d.ab_dtype, d.y_dtype = L.I8, L.I8
+        e = L.Epilogue()
+        e.alpha, e.beta, e.out_scale = self.mult, 1.0, 1.0
+        y = np.zeros((rows, self.n), dtype=np.int8)
+        t0 = time.perf_counter()
+        lib.so_gemm(C.byref(d), a.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p), y.ctypes.data_as(C.c_void_p), C.byref(e))
+        return time.perf_counter() - t0
+
+
+class Fp8Gemm(QLinearMatMul):
+    """FP8 e4m3 x e4m3 -> fp32, per-row / per-column scales, bias, Gelu, bf16 output."""
+
+    def __init__(self, n: int, name: str):
+        super().__init__(n, name)
+        self.metric = f"FP8 e4m3 GEMM {n}^3 + scales + bias + Gelu -> bf16 throughput"
+        self.unit = "TFLOP/s"
+        self.dtype = "fp8_e4m3"
+        self.bytes_alg = 2.0 * n * n + 2.0 * n * n
+
+    def host_operands(self, seed: int):
+        import torch
+        g = torch.Generator().manual_seed(seed)
+        a = torch.randn(self.n, self.n, generator=g)
+        b = torch.randn(self.n, self.n, generator=g)
+        self.sa = (a.abs().amax(dim=1) / 448.0).contiguous()
+        self.sb = (b.abs().amax(dim=0) / 448.0).contiguous()
+        self.bias = (torch.randn(self.n, generator=g) * 0.1).contiguous()
+        a8 = (a / self.sa[:, None]).to(torch.float8_e4m3fn)
+        b8 = (b / self.sb[None, :]).to(torch.float8_e4m3fn)
+        return a8.view(torch.uint8).numpy(), b8.view(torch.uint8).numpy()
+
+    def epilogue(self):
+        from sofie_b200 import lib as L
+        from sofie_b200.ops import make_epilogue
+        dev = "cuda"
+        self._keep = (self.sa.to(dev), self.sb.to(dev), self.bias.to(dev))
+        return make_epilogue(row_scale=self._keep[0], col_scale=self._keep[1], bias=self._keep[2], act=L.ACT_GELU_ERF)
+
+    def plan(self, ctx):
+        import torch
+        from sofie_b200.ops import GemmPlan
+        return GemmPlan(ctx, self.n, self.n, self.n, torch.float8_e4m3fn, torch.bfloat16, trans_b=False)
+
+    def torch_dtypes(self):
+        import torch
+        return torch.float8_e4m3fn, torch.bfloat16
+
+    def cpu_rows(self, lib, a, b, rows: int) -> float:
+        from sofie_b200 import lib as L
+        d = L.GemmDesc()
+        d.M, d.N, d.K, d.batch = rows, self.n, self.n, 1
+        d.ab_dtype, d.y_dtype = L.F8E4M3, L.BF16
+        e = L.Epilogue()
+        sa, sb, bias = self.sa.numpy(), self.sb.numpy(), self.bias.numpy()
+        e.row_scale, e.col_scale = sa.ctypes.data_as(C.c_void_p), sb.ctypes.data_as(C.c_void_p)
+        e.alpha, e.beta, e.out_scale = 1.0, 1.0, 1.0
+        e.bias_mode, e.bias, e.act = L.BIAS_COL_F32, bias.ctypes.data_as(C.c_void_p), L.ACT_GELU_ERF
+        y = np.zeros((rows, self.n), dtype=np.uint16)
+        t0 = time.perf_counter()
+        lib.so_gemm(C.byref(d), a.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p), y.ctypes.data_as(C.c_void_p), C.byref(e))
+        return time.perf_counter() - t0
+
+
+WORKLOADS = {
+    "qlinear_matmul_4096": lambda: QLinearMatMul(4096, "qlinear_matmul_4096"),
+    "fp8_gemm_8192": lambda: Fp8Gemm(8192, "fp8_gemm_8192"),
+}
+
+
+def load_oracle():
+    """The CPU checker library; only the CPU-baseline legs use it."""
+    so = ROOT / "oracle" / "libsofie_oracle.so"
+    if not so.exists():
+        import subprocess
+        subprocess.run(["make", "-C", str(ROOT / "oracle"), "oracle"], check=True, capture_output=True)
+    lib = C.CDLL(str(so))
+    lib.so_threads.restype = C.c_int
+    return lib
+
+
+def cpu_sample(w, budget_s: float):
+    """Times the CPU restatement on a row sample sized to about `budget_s` seconds."""
+    lib = load_oracle()
+    a, b = w.host_operands(seed=1)
+    t = w.cpu_rows(lib, a, b, 8)  # calibration
+    rows = int(max(8, min(w.n, 8 * budget_s / max(t, 1e-6))))
+    t = w.cpu_rows(lib, a, b, rows)
+    ops = 2.0 * rows * w.n * w.n
+    return ops / t / 1e12, lib.so_threads(), f"{rows} of {w.n} rows of A against all of B ({ops / 1e9:.1f} GOP, {t:.1f} s)", rows
+
+
+# ---------------------------------------------------------------------------------------------
+def run_reference(args, w) -> None:
+    """The reference has no int8 / FP8 operator (ROperator_Gemm is fp32 only), so its arm is the
+    CPU restatement of the operator, on every host thread OpenMP gives it; rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    lib = load_oracle()
+    a, b = w.host_operands(seed=1)
+    total = max(1, args.steps + args.warmup)
+    t_cal = w.cpu_rows(lib, a, b, 8)
+    rows = int(max(1, min(w.n, 8 * (90.0 / total) / max(t_cal, 1e-6))))
+    for _ in range(args.warmup):
+        w.cpu_rows(lib, a, b, rows)
+    t = 0.0
+    for _ in range(args.steps):
+        t += w.cpu_rows(lib, a, b, rows)
+    ops = 2.0 * rows * w.n * w.n * args.steps
+    val = ops / t / 1e12
+    sample = f"each step = {rows} of {w.n} rows of A against all of B"
+    line = {"impl": "reference", "metric": w.metric, "value": val, "unit": w.unit, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * t / max(1, args.steps), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+            "config": {"workload": w.name, "note": "CPU restatement of the operator on host threads; the reference itself has no int8/FP8 path"},
+            "cpu_baseline": {"value": val, "unit": w.unit, "cores": lib.so_threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, w) -> None:
+    import torch
+    from sofie_b200 import replicas
+    from sofie_b200.ops import Context
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    rep = replicas.init_from_env("nccl")
+    torch.cuda.set_device(rep.local_rank)
+    dev = f"cuda:{rep.local_rank}"
+    ctx = Context(rep.local_rank)
+    in_dt, out_dt = w.torch_dtypes()
+
+    # operand sets rotated between steps so that each step's inputs come from HBM, not L2
+    set_bytes = w.bytes_alg
+    nsets = int(max(3, np.ceil(1.6 * L2_BYTES / set_bytes)))
+    ha, hb = w.host_operands(seed=1 + rep.rank)
+    sets = []
+    for s in range(nsets):
+        a = torch.from_numpy(np.roll(ha, s, axis=0).copy()).to(dev).view(in_dt)
+        b = torch.from_numpy(np.roll(hb, s, axis=1).copy()).to(dev).view(in_dt)
+        y = torch.empty((w.n, w.n), dtype=out_dt, device=dev)
+        sets.append((a, b, y))
+    plan = w.plan(ctx)
+    ep, keep = w.epilogue()
+
+    def step(i):
+        a, b, y = sets[i % nsets]
+        plan.enqueue(a, b, y, ep)
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    ctx.sync()
+    sampler = ClockSampler(rep.local_rank)
+    replicas.barrier(rep)
+    torch.cuda.synchronize()
+    launches0 = ctx.launches
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ctx.sync()
+    launches = ctx.launches - launches0
+    ms_local = e0.elapsed_time(e1)
+    replicas.barrier(rep)
+    ms = replicas.max_over_ranks(rep, ms_local)
+    value = rep.world * w.ops * args.steps / (ms * 1e-3) / 1e12
+
+    # end to end through the host-operand entry point of the C ABI
+    pa = torch.from_numpy(ha).pin_memory()
+    pb = torch.from_numpy(hb).pin_memory()
+    py = torch.empty((w.n, w.n), dtype=out_dt).pin_memory()
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(2):
+        plan.run_host(pa, pb, py, ep)
+    replicas.barrier(rep)
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        plan.run_host(pa, pb, py, ep)
+    t_e2e = replicas.max_over_ranks(rep, time.perf_counter() - t0)
+    e2e_val = rep.world * w.ops * e2e_steps / t_e2e / 1e12
+    h2d = pa.numel() * pa.element_size() + pb.numel() * pb.element_size()
+    d2h = py.numel() * py.element_size()
+
+    line = None
+    if rep.is_root:
+        peaks = measured_peaks()
+        # dense int8 / FP8 tensor peak = 2 x the bf16 figure measured on this pool (the file has no 8-bit entry)
+        peak = 2.0 * peaks["bf16_tflops"]
+        ach = w.ops / (ms_local / args.steps * 1e-3) / 1e12
+        cpu_val, cores, sample, _ = cpu_sample(w, budget_s=12.0)
+        line = {"metric": w.metric, "value": value, "unit": w.unit, "n_gpus": rep.world, "steps": args.steps, "warmup": max(3, args.warmup),
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype,
+                "data": "synthetic",
+                "config": {"workload": w.name, "M": w.n, "N": w.n, "K": w.n, "b_layout": "[K,N] row-major (ONNX)",
+                           "l2": f"{nsets} operand sets rotated ({nsets * set_bytes / 2**20:.0f} MiB > 126 MiB L2)",
+                           "kernel": plan.kernel, "replicas": rep.world},
+                "clocks": clocks, "gpu_launches": int(launches),
+                "e2e": {"value": e2e_val, "unit": w.unit, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e2e_steps},
+                "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": w.unit, "frac": ach / peak,
+                             "traffic": NCU_TRAFFIC_BYTES.get(w.name),
+                             "peak_source": f"2 x bf16_tflops of {peaks['source']} MEASURED_PEAKS.json (no 8-bit figure there); nominal dense 4500"},
+                "cpu_baseline": {"value": cpu_val, "unit": w.unit, "cores": cores, "kind": "port", "sample": sample}}
+    plan.close()
+    ctx.close()
+    replicas.shutdown(rep)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="qlinear_matmul_4096", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]()
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_ours(args, w)
+
+
+if __name__ == "__main__":
+    main()

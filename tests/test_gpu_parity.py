@@ -1,0 +1,352 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU checker and the golden fixtures.
+
+Bars: bit-exact for int8 paths; |got-want| <= 1e-5*max(|want|, rms) for fp32; 2e-2 relative +
+1e-2 absolute for bf16 / FP8.  Everything here needs a B200.
+"""
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import graph_runner as gr
+from oracle_api import Oracle, bf16_bits_to_f32
+from sofie_b200 import lib as L
+
+pytestmark = pytest.mark.gpu
+GOLDEN = sorted(p.stem for p in (Path(__file__).parent / "golden").glob("*.npz"))
+DEV = "cuda:0"
+
+
+def close_f32(got, want, rel=1e-5):
+    floor = float(np.sqrt(np.mean(np.square(want)))) if want.size else 0.0
+    return bool(np.all(np.abs(got - want) <= rel * np.maximum(np.abs(want), floor) + 1e-30))
+
+
+def close_lowp(got, want):
+    return bool(np.all(np.abs(got - want) <= 2e-2 * np.abs(want) + 1e-2))
+
+
+@pytest.fixture(scope="module")
+def ctx(b200_lib):
+    from sofie_b200.ops import Context
+    c = Context(0)
+    yield c
+    c.close()
+
+
+@pytest.fixture(scope="module")
+def oracle(oracle_lib):
+    return Oracle(oracle_lib)
+
+
+@pytest.fixture(scope="module")
+def backend(b200_lib):
+    return gr.B200Backend()
+
+
+# ---- the reference's own test models --------------------------------------------------------
+@pytest.mark.parametrize("name", GOLDEN)
+def test_golden_models(name, backend):
+    fx = gr.load_fixture(name)
+    for tag in ("A", "B"):
+        if f"out{tag}" not in fx:
+            continue
+        ins = [fx[k] for k in sorted(fx) if k.startswith(f"in{tag}")]
+        got = gr.run_graph(fx, ins, backend)
+        want = fx[f"out{tag}"]
+        assert got.shape == want.shape
+        assert close_f32(got, want), f"{name}/{tag}: max abs diff {np.abs(got - want).max():.3g}"
+    if "expected" in fx:
+        ins = [fx[k] for k in sorted(fx) if k.startswith("inA")]
+        assert np.abs(gr.run_graph(fx, ins, backend) - fx["expected"]).max() <= 2e-4
+
+
+# ---- int8 QLinearMatMul: bit-exact --------------------------------------------------------------
+def run_gemm(ctx, a, b, M, N, K, in_dt, out_dt, trans_a=False, trans_b=False, batch=1, precise=True, expect=None, **ep_kw):
+    from sofie_b200.ops import GemmPlan, make_epilogue
+    ta, tb = torch.from_numpy(a).to(DEV).view(in_dt), torch.from_numpy(b).to(DEV).view(in_dt)
+    y = torch.zeros((batch, M, N) if batch > 1 else (M, N), dtype=out_dt, device=DEV)
+    plan = GemmPlan(ctx, M, N, K, in_dt, out_dt, trans_a=trans_a, trans_b=trans_b, batch=batch,
+                    stride_a=(M * K if batch > 1 else 0), stride_b=(K * N if batch > 1 else 0), stride_y=(M * N if batch > 1 else 0),
+                    precise=precise)
+    dev_kw = {k: (torch.from_numpy(v).to(DEV) if isinstance(v, np.ndarray) else v) for k, v in ep_kw.items()}
+    ep, keep = make_epilogue(**dev_kw)
+    plan.enqueue(ta, tb, y, ep)
+    ctx.sync()
+    if expect is not None:
+        assert plan.kernel == expect, plan.kernel
+    plan.close()
+    return y
+
+
+MULT = float(np.float32(np.float32(0.02) * np.float32(0.01)) / np.float32(0.5))
+
+
+@pytest.mark.parametrize("M,N,K,ta,tb,kernel", [
+    (256, 384, 512, False, False, "umma"), (256, 384, 512, False, True, "umma"), (256, 384, 512, True, False, "umma"),
+    (1000, 700, 400, False, True, "umma"), (1000, 704, 400, False, False, "umma"), (1, 1, 16, False, True, "umma"),
+    (130, 50, 33, False, True, "simt"), (7, 300, 1, False, False, "simt"), (129, 257, 4096, False, False, "simt"), (129, 272, 4096, False, False, "umma"),
+])
+def test_qlinear_matmul_bit_exact(ctx, oracle, M, N, K, ta, tb, kernel):
+    rng = np.random.default_rng(M * 7 + N * 3 + K)
+    a = rng.integers(-127, 128, size=(K, M) if ta else (M, K), dtype=np.int8)
+    b = rng.integers(-127, 128, size=(N, K) if tb else (K, N), dtype=np.int8)
+    want = oracle.gemm(a, b, M, N, K, L.I8, L.I8, ta, tb, ep=oracle.epilogue(alpha=MULT))
+    got = run_gemm(ctx, a, b, M, N, K, torch.int8, torch.int8, ta, tb, alpha=MULT, expect=kernel).cpu().numpy()
+    assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size} differ"
+    want32 = oracle.gemm(a, b, M, N, K, L.I8, L.I32, ta, tb)
+    got32 = run_gemm(ctx, a, b, M, N, K, torch.int8, torch.int32, ta, tb).cpu().numpy()
+    assert np.array_equal(got32, want32)
+
+
+def test_qlinear_per_channel_bias_relu_zero_point(ctx, oracle):
+    M, N, K = 384, 320, 640
+    rng = np.random.default_rng(11)
+    a = rng.integers(-127, 128, size=(M, K), dtype=np.int8)
+    b = rng.integers(-127, 128, size=(K, N), dtype=np.int8)
+    cs = (rng.random(N, dtype=np.float32) * 1e-3 + 1e-4).astype(np.float32)
+    bias = rng.integers(-50000, 50000, size=N, dtype=np.int32)
+    for out_dt, odt, zp in ((torch.int8, L.I8, -7), (torch.uint8, L.U8, 128)):
+        want = oracle.gemm(a, b, M, N, K, L.I8, odt, ep=oracle.epilogue(col_scale=cs, bias=bias, act=L.ACT_RELU, out_zero_point=zp))
+        got = run_gemm(ctx, a, b, M, N, K, torch.int8, out_dt, col_scale=cs, bias=bias, act=L.ACT_RELU, out_zero_point=zp).cpu().numpy()
+        assert np.array_equal(got, want)
+
+
+def test_qlinear_batched_and_shared_weight(ctx, oracle):
+    from sofie_b200.ops import GemmPlan, make_epilogue
+    B, M, N, K = 5, 200, 136, 256
+    rng = np.random.default_rng(3)
+    a = rng.integers(-127, 128, size=(B, M, K), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(N, K), dtype=np.int8)
+    want = oracle.gemm(a, w, M, N, K, L.I8, L.I32, False, True, batch=B, stride_b=0)
+    ta, tw = torch.from_numpy(a).to(DEV), torch.from_numpy(w).to(DEV)
+    y = torch.zeros((B, M, N), dtype=torch.int32, device=DEV)
+    plan = GemmPlan(ctx, M, N, K, torch.int8, torch.int32, trans_b=True, batch=B, stride_a=M * K, stride_b=0, stride_y=M * N)
+    plan.enqueue(ta, tw, y)
+    ctx.sync()
+    assert np.array_equal(y.cpu().numpy(), want)
+
+
+def test_empty_and_invalid(ctx):
+    from sofie_b200.ops import GemmPlan
+    y = torch.zeros((0, 8), dtype=torch.int8, device=DEV)
+    a = torch.zeros((0, 16), dtype=torch.int8, device=DEV)
+    b = torch.zeros((16, 8), dtype=torch.int8, device=DEV)
+    plan = GemmPlan(ctx, 0, 8, 16, torch.int8, torch.int8)
+    plan.enqueue(a, b, y)  # empty output: nothing is launched
+    ctx.sync()
+    with pytest.raises(L.SofieB200Error):
+        GemmPlan(ctx, 8, 8, 8, torch.bfloat16, torch.int32)  # int32 output needs int8 operands
+    with pytest.raises(L.SofieB200Error):
+        GemmPlan(ctx, 8, 8, 8, torch.int8, torch.int8, lda=4)  # pitch smaller than the row
+
+
+def test_qlinear_matmul_4096_sampled_rows(ctx, oracle):
+    """The benchmark configuration at full size: 96 sampled rows of the output, bit for bit."""
+    n = 4096
+    rng = np.random.default_rng(1)
+    a = rng.integers(-127, 128, size=(n, n), dtype=np.int8)
+    b = rng.integers(-127, 128, size=(n, n), dtype=np.int8)
+    got = run_gemm(ctx, a, b, n, n, n, torch.int8, torch.int8, alpha=MULT, expect="umma").cpu().numpy()
+    rows = np.concatenate([np.arange(32), rng.choice(np.arange(32, n), size=64, replace=False)])
+    want = oracle.gemm(np.ascontiguousarray(a[rows]), b, len(rows), n, n, L.I8, L.I8, ep=oracle.epilogue(alpha=MULT))
+    assert np.array_equal(got[rows], want)
+    # size-independent property: the int32 product is linear in A
+    got32 = run_gemm(ctx, a, b, n, n, n, torch.int8, torch.int32).cpu().numpy().astype(np.int64)
+    a2 = (a.astype(np.int16) // 2).astype(np.int8)
+    r = (a.astype(np.int16) - 2 * a2.astype(np.int16)).astype(np.int8)
+    g2 = run_gemm(ctx, a2, b, n, n, n, torch.int8, torch.int32).cpu().numpy().astype(np.int64)
+    gr_ = run_gemm(ctx, r, b, n, n, n, torch.int8, torch.int32).cpu().numpy().astype(np.int64)
+    assert np.array_equal(got32, 2 * g2 + gr_)
+
+
+# ---- FP8 / bf16 / fp32 contractions -------------------------------------------------------------
+def fp8_operands(rng, M, N, K, tb):
+    a = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32))
+    b = torch.from_numpy(rng.standard_normal((N, K) if tb else (K, N)).astype(np.float32))
+    sa = (a.abs().amax(dim=1) / 448.0)
+    sb = (b.abs().amax(dim=1 if tb else 0) / 448.0)
+    a8 = (a / sa[:, None]).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    b8 = (b / (sb[:, None] if tb else sb[None, :])).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    return a8, b8, sa.numpy(), sb.numpy()
+
+
+@pytest.mark.parametrize("M,N,K,tb", [(512, 768, 1024, False), (300, 200, 528, True)])
+def test_fp8_gemm_scales_bias_gelu(ctx, oracle, M, N, K, tb):
+    rng = np.random.default_rng(M + N)
+    a8, b8, sa, sb = fp8_operands(rng, M, N, K, tb)
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    want = bf16_bits_to_f32(oracle.gemm(a8, b8, M, N, K, L.F8E4M3, L.BF16, False, tb,
+                                        ep=oracle.epilogue(row_scale=sa, col_scale=sb, bias=bias, act=L.ACT_GELU_ERF)))
+    got = run_gemm(ctx, a8, b8, M, N, K, torch.float8_e4m3fn, torch.bfloat16, False, tb, row_scale=sa, col_scale=sb, bias=bias,
+                   act=L.ACT_GELU_ERF, expect="umma").float().cpu().numpy()
+    assert close_lowp(got, want), np.abs(got - want).max()
+
+
+def test_fp8_gemm_8192_sampled_rows(ctx, oracle):
+    n = 8192
+    rng = np.random.default_rng(2)
+    a8, b8, sa, sb = fp8_operands(rng, n, n, n, False)
+    bias = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    got = run_gemm(ctx, a8, b8, n, n, n, torch.float8_e4m3fn, torch.bfloat16, row_scale=sa, col_scale=sb, bias=bias,
+                   act=L.ACT_GELU_ERF, expect="umma").float().cpu().numpy()
+    rows = rng.choice(n, size=16, replace=False)
+    want = bf16_bits_to_f32(oracle.gemm(np.ascontiguousarray(a8[rows]), b8, 16, n, n, L.F8E4M3, L.BF16,
+                                        ep=oracle.epilogue(row_scale=np.ascontiguousarray(sa[rows]), col_scale=sb, bias=bias, act=L.ACT_GELU_ERF)))
+    assert close_lowp(got[rows], want), np.abs(got[rows] - want).max()
+
+
+@pytest.mark.parametrize("M,N,K,ta,tb,batch", [(256, 512, 320, False, False, 1), (200, 130, 64, False, True, 4), (128, 64, 128, False, False, 6),
+                                                (264, 128, 72, True, True, 1)])
+def test_bf16_gemm(ctx, oracle, M, N, K, ta, tb, batch):
+    rng = np.random.default_rng(K)
+    a = torch.from_numpy(rng.standard_normal((batch, K, M) if ta else (batch, M, K)).astype(np.float32)).to(torch.bfloat16)
+    b = torch.from_numpy(rng.standard_normal((batch, N, K) if tb else (batch, K, N)).astype(np.float32)).to(torch.bfloat16)
+    an, bn = a.view(torch.int16).numpy().view(np.uint16), b.view(torch.int16).numpy().view(np.uint16)
+    want = oracle.gemm(an, bn, M, N, K, L.BF16, L.F32, ta, tb, batch=batch)
+    got = run_gemm(ctx, an.view(np.int16), bn.view(np.int16), M, N, K, torch.bfloat16, torch.float32, ta, tb, batch=batch, expect="umma").cpu().numpy()
+    assert close_lowp(got.reshape(want.shape), want)
+    assert np.abs(got.reshape(want.shape) - want).max() <= 1e-3 * np.abs(want).max()  # fp32 accumulation: far inside the bf16 bar
+
+
+@pytest.mark.parametrize("M,N,K,ta,tb", [(1024, 256, 64, False, False), (100, 37, 19, True, False), (64, 10, 256, False, True)])
+def test_fp32_gemm_bias_relu(ctx, oracle, M, N, K, ta, tb):
+    rng = np.random.default_rng(N)
+    a = rng.standard_normal((K, M) if ta else (M, K)).astype(np.float32)
+    b = rng.standard_normal((N, K) if tb else (K, N)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    want = oracle.gemm(a, b, M, N, K, L.F32, L.F32, ta, tb, ep=oracle.epilogue(bias=bias, act=L.ACT_RELU))
+    got = run_gemm(ctx, a, b, M, N, K, torch.float32, torch.float32, ta, tb, bias=bias, act=L.ACT_RELU).cpu().numpy()
+    assert close_f32(got, want), np.abs(got - want).max()
+
+
+# ---- convolution -----------------------------------------------------------------------------------
+def run_conv(ctx, x, w, desc, ho, wo, out_dt, **ep_kw):
+    from sofie_b200.ops import make_epilogue
+    lib = ctx._lib
+    tx, tw = torch.from_numpy(x).to(DEV), torch.from_numpy(w).to(DEV)
+    h = C.c_void_p()
+    L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(desc), tw.data_ptr(), C.byref(h)), "conv_plan_create")
+    ws = torch.empty(max(16, lib.sofie_b200_conv_workspace_bytes(h)), dtype=torch.uint8, device=DEV)
+    y = torch.zeros((desc.N, desc.K, ho, wo), dtype=out_dt, device=DEV)
+    dev_kw = {k: (torch.from_numpy(v).to(DEV) if isinstance(v, np.ndarray) else v) for k, v in ep_kw.items()}
+    ep, keep = make_epilogue(**dev_kw)
+    L.check(lib.sofie_b200_conv_enqueue(h, tx.data_ptr(), y.data_ptr(), ws.data_ptr(), C.byref(ep)), "conv_enqueue")
+    ctx.sync()
+    lib.sofie_b200_conv_plan_destroy(h)
+    return y.cpu().numpy()
+
+
+@pytest.mark.parametrize("N,Ci,H,W,Co,st,g", [(2, 64, 28, 28, 128, 1, 1), (3, 32, 30, 26, 64, 2, 1), (2, 16, 9, 11, 32, 1, 4), (1, 3, 32, 32, 64, 1, 1)])
+def test_qlinear_conv_bit_exact(ctx, oracle, N, Ci, H, W, Co, st, g):
+    rng = np.random.default_rng(Ci + Co)
+    x = rng.integers(-127, 128, size=(N, Ci, H, W), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(Co, Ci // g, 3, 3), dtype=np.int8)
+    geo = dict(pads=[1, 1, 1, 1], strides=[st, st], dil=[1, 1], group=g)
+    d = gr.conv_desc(geo, x.shape, w.shape, L.I8, L.I8)
+    ho, wo = C.c_int64(), C.c_int64()
+    assert ctx._lib.sofie_b200_conv_out_shape(C.byref(d), C.byref(ho), C.byref(wo)) == 0
+    cs = (rng.random(Co, dtype=np.float32) * 2e-4 + 5e-5).astype(np.float32)  # a_scale*w_scale[c]/y_scale
+    bias = rng.integers(-20000, 20000, size=Co, dtype=np.int32)
+    want = oracle.conv(x, w, d, ho.value, wo.value, ep=oracle.epilogue(col_scale=cs, bias=bias, act=L.ACT_RELU))
+    got = run_conv(ctx, x, w, d, ho.value, wo.value, torch.int8, col_scale=cs, bias=bias, act=L.ACT_RELU)
+    assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size}"
+
+
+def test_conv_fp32_with_folded_batchnorm(ctx, oracle):
+    rng = np.random.default_rng(9)
+    x = rng.random((2, 8, 20, 20), dtype=np.float32)
+    w = (rng.standard_normal((16, 8, 3, 3)) * np.sqrt(2.0 / 72)).astype(np.float32)
+    geo = dict(pads=[1, 1, 1, 1], strides=[2, 2], dil=[1, 1], group=1)
+    d = gr.conv_desc(geo, x.shape, w.shape)
+    gamma, beta = rng.random(16, dtype=np.float32) + 0.5, (rng.standard_normal(16) * 0.1).astype(np.float32)
+    mean, var = (rng.standard_normal(16) * 0.1).astype(np.float32), rng.random(16, dtype=np.float32) + 0.5
+    fs = (gamma / np.sqrt(var + np.float32(1e-5))).astype(np.float32)
+    shift = (beta - mean * fs).astype(np.float32)
+    want = oracle.conv(x, w, d, 10, 10, ep=oracle.epilogue(col_scale=fs, bias=shift, act=L.ACT_RELU))
+    got = run_conv(ctx, x, w, d, 10, 10, torch.float32, col_scale=fs, bias=shift, act=L.ACT_RELU)
+    assert close_f32(got, want), np.abs(got - want).max()
+
+
+# ---- row-wise and elementwise operators ---------------------------------------------------------------
+@pytest.mark.parametrize("rows,cols", [(1000, 512), (333, 128), (17, 100), (64, 4096), (5, 10000), (4096, 8), (1, 1), (3, 2049)])
+def test_layernorm_softmax_fp32(ctx, oracle, rows, cols):
+    rng = np.random.default_rng(rows + cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    g, b = rng.standard_normal(cols).astype(np.float32), rng.standard_normal(cols).astype(np.float32)
+    tx = torch.from_numpy(x).to(DEV)
+    ty = torch.empty_like(tx)
+    ctx.layernorm(tx, ty, torch.from_numpy(g).to(DEV), torch.from_numpy(b).to(DEV), 1e-5)
+    ctx.sync()
+    want = oracle.layernorm(x, g, b, 1e-5)
+    assert np.abs(ty.cpu().numpy() - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+    for log in (False, True):
+        ctx.softmax(tx, ty, log_softmax=log)
+        ctx.sync()
+        want = oracle.softmax(x, log=log)
+        assert np.abs(ty.cpu().numpy() - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("rows,cols", [(2048, 512), (4096, 128), (9, 72)])
+def test_layernorm_softmax_bf16(ctx, oracle, rows, cols):
+    rng = np.random.default_rng(cols)
+    tx = torch.from_numpy(rng.standard_normal((rows, cols)).astype(np.float32)).to(torch.bfloat16)
+    xn = tx.view(torch.int16).numpy().view(np.uint16)
+    g, b = np.ones(cols, dtype=np.float32), np.zeros(cols, dtype=np.float32)
+    dx = tx.to(DEV)
+    dy = torch.empty_like(dx)
+    ctx.layernorm(dx, dy, torch.from_numpy(g).to(DEV), torch.from_numpy(b).to(DEV), 1e-5)
+    ctx.sync()
+    assert close_lowp(dy.float().cpu().numpy(), bf16_bits_to_f32(oracle.layernorm(xn, g, b, 1e-5, L.BF16)))
+    ctx.softmax(dx, dy)
+    ctx.sync()
+    assert close_lowp(dy.float().cpu().numpy(), bf16_bits_to_f32(oracle.softmax(xn, L.BF16)))
+
+
+def test_elementwise_operators(ctx, oracle):
+    rng = np.random.default_rng(4)
+    x = (rng.standard_normal(100003) * 3).astype(np.float32)
+    tx = torch.from_numpy(x).to(DEV)
+    ty = torch.empty_like(tx)
+    for act, aa in ((L.ACT_RELU, 0.0), (L.ACT_GELU_ERF, 0.0), (L.ACT_GELU_TANH, 0.0), (L.ACT_LEAKY_RELU, 0.1), (L.ACT_SIGMOID, 0.0)):
+        ctx.unary(tx, ty, act, aa)
+        ctx.sync()
+        want = oracle.unary(x, act, aa)
+        assert np.abs(ty.cpu().numpy() - want).max() <= 1e-6 * max(1.0, np.abs(want).max()), act
+    a = rng.standard_normal((65, 1000)).astype(np.float32)
+    b = rng.standard_normal(1000).astype(np.float32) + 3.0
+    ta, tb = torch.from_numpy(a).to(DEV), torch.from_numpy(b).to(DEV)
+    tz = torch.empty_like(ta)
+    for op in range(4):
+        ctx.binary(ta, tb, tz, op)
+        ctx.sync()
+        assert np.array_equal(tz.cpu().numpy(), oracle.binary(a, b, op)), op
+
+
+def test_quantize_dequantize_convert_pool(ctx, oracle):
+    rng = np.random.default_rng(6)
+    x = (rng.standard_normal((4, 6, 5, 7)) * 2).astype(np.float32)
+    scale = (rng.random(6, dtype=np.float32) * 0.05 + 0.01).astype(np.float32)
+    zp = rng.integers(-5, 5, size=6, dtype=np.int32)
+    tx = torch.from_numpy(x).to(DEV)
+    q = torch.zeros(x.shape, dtype=torch.int8, device=DEV)
+    ctx.quantize(tx, q, torch.from_numpy(scale).to(DEV), torch.from_numpy(zp).to(DEV), channels=6, inner=35)
+    ctx.sync()
+    wq = oracle.quantize(x, scale, zp, L.I8, 6, 35)
+    assert np.array_equal(q.cpu().numpy(), wq)
+    back = torch.empty_like(tx)
+    ctx.dequantize(q, back, torch.from_numpy(scale).to(DEV), torch.from_numpy(zp).to(DEV), channels=6, inner=35)
+    ctx.sync()
+    assert np.array_equal(back.cpu().numpy(), oracle.dequantize(wq, scale, zp, L.I8, 6, 35))
+    pooled = torch.empty((4, 6), dtype=torch.float32, device=DEV)
+    ctx.global_avgpool(tx, pooled)
+    ctx.sync()
+    assert np.abs(pooled.cpu().numpy() - oracle.global_avgpool(x)).max() <= 1e-6
+    m = (rng.standard_normal((50, 64)) * 30).astype(np.float32)
+    rs = (np.abs(m).max(axis=1) / 448.0).astype(np.float32)
+    t8 = torch.zeros((50, 64), dtype=torch.float8_e4m3fn, device=DEV)
+    ctx.convert(torch.from_numpy(m).to(DEV), t8, torch.from_numpy(rs).to(DEV))
+    ctx.sync()
+    assert np.array_equal(t8.view(torch.uint8).cpu().numpy(), oracle.convert(m, L.F32, L.F8E4M3, rs))
