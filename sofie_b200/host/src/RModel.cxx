@@ -1,0 +1,688 @@
+// RModel: model IR, operator initialisation, epilogue fusion, arena planning and emission of the
+// Session header for the B200 target (see SOFIE_B200/RModel.hxx).
+#include "SOFIE_B200/RModel.hxx"
+
+#include <fstream>
+#include <iomanip>
+#include <iostream>
+#include <limits>
+#include <sstream>
+
+#include "SOFIE_B200/operators/OperatorList.hxx"
+
+namespace SOFIE_B200 {
+
+RModel::RModel(std::string name, std::string parsedtime) : fName(std::move(name)), fParseTime(std::move(parsedtime))
+{
+   // a file name may be given: keep the stem, as the reference does for "model.onnx"
+   auto slash = fName.find_last_of("/\\");
+   if (slash != std::string::npos) fName = fName.substr(slash + 1);
+   auto dot = fName.find_last_of('.');
+   if (dot != std::string::npos) fName = fName.substr(0, dot);
+   fName = UTILITY::Clean_name(fName);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// model building
+// ---------------------------------------------------------------------------------------------------
+void RModel::AddInputTensorInfo(std::string input_name, ETensorType type, std::vector<Dim> shape)
+{
+   input_name = UTILITY::Clean_name(input_name);
+   if (CheckIfTensorAlreadyExist(input_name))
+      throw std::runtime_error("SOFIE: input tensor with name " + input_name + " already exists \n");
+   fInputDimShapes[input_name] = shape;
+   std::vector<size_t> s;
+   for (auto &d : shape) s.push_back(d.dim);
+   fInputTensorInfos[input_name] = TensorInfo{type, s};
+}
+
+void RModel::AddInputTensorInfo(std::string input_name, ETensorType type, std::vector<size_t> shape)
+{
+   std::vector<Dim> d(shape.begin(), shape.end());
+   AddInputTensorInfo(std::move(input_name), type, std::move(d));
+}
+
+void RModel::AddInputTensorName(std::string name) { fInputTensorNames.emplace_back(UTILITY::Clean_name(name)); }
+
+void RModel::AddInitializedTensor(std::string tensor_name, ETensorType type, std::vector<std::size_t> shape, std::shared_ptr<void> data)
+{
+   tensor_name = UTILITY::Clean_name(tensor_name);
+   if (CheckIfTensorAlreadyExist(tensor_name))
+      throw std::runtime_error("SOFIE: initialized tensor with name " + tensor_name + " already exists \n");
+   fInitializedTensors[tensor_name] = InitializedTensor{type, std::move(shape), std::move(data), false};
+   fInitializedOrder.push_back(tensor_name);
+}
+
+void RModel::AddInitializedTensor(const std::string &tensor_name, ETensorType type, const std::vector<std::size_t> &shape, void *raw_data)
+{
+   const size_t bytes = ConvertShapeToLength(shape) * GetTypeSize(type);
+   std::shared_ptr<void> p(malloc(bytes + 1), free);
+   std::memcpy(p.get(), raw_data, bytes);
+   AddInitializedTensor(tensor_name, type, shape, p);
+}
+
+void RModel::AddConstantTensor(std::string tensor_name, ETensorType type, std::vector<std::size_t> shape, std::shared_ptr<void> data)
+{
+   AddInitializedTensor(tensor_name, type, std::move(shape), std::move(data));
+   fInitializedTensors[UTILITY::Clean_name(tensor_name)].constant = true;
+}
+
+void RModel::AddIntermediateTensor(std::string tensor_name, ETensorType type, std::vector<std::size_t> shape)
+{
+   tensor_name = UTILITY::Clean_name(tensor_name);
+   if (CheckIfTensorAlreadyExist(tensor_name))
+      throw std::runtime_error("SOFIE: intermediate tensor with name " + tensor_name + " already exists \n");
+   fIntermediateTensorInfos[tensor_name] = TensorInfo{type, std::move(shape)};
+}
+
+bool RModel::AddAliasTensor(const std::string &tensor_name, const std::string &orig_tensor_name)
+{
+   const std::string a = UTILITY::Clean_name(tensor_name), o = UTILITY::Clean_name(orig_tensor_name);
+   if (!CheckIfTensorAlreadyExist(o)) return false;
+   fAliasTensors[a] = ResolveAliasTensor(o);
+   return true;
+}
+
+std::string RModel::ResolveAliasTensor(const std::string &name) const
+{
+   std::string n = name;
+   for (auto it = fAliasTensors.find(n); it != fAliasTensors.end(); it = fAliasTensors.find(n)) n = it->second;
+   return n;
+}
+
+void RModel::AddOperator(std::unique_ptr<ROperator> op, int order_execution)
+{
+   if (order_execution >= 0 && size_t(order_execution) <= fOperators.size()) fOperators.insert(fOperators.begin() + order_execution, std::move(op));
+   else fOperators.push_back(std::move(op));
+}
+
+void RModel::AddOutputTensorNameList(std::vector<std::string> names)
+{
+   fOutputTensorNames.clear();
+   for (auto &n : names) fOutputTensorNames.emplace_back(UTILITY::Clean_name(n));
+}
+
+void RModel::UpdateOutputTensorList(std::vector<std::string> curr, std::vector<std::string> mod)
+{
+   for (size_t i = 0; i < curr.size(); ++i)
+      for (auto &o : fOutputTensorNames)
+         if (o == UTILITY::Clean_name(curr[i])) o = UTILITY::Clean_name(mod[i]);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// queries
+// ---------------------------------------------------------------------------------------------------
+bool RModel::CheckIfTensorAlreadyExist(std::string n) const
+{
+   n = UTILITY::Clean_name(n);
+   return fInputTensorInfos.count(n) || fInitializedTensors.count(n) || fIntermediateTensorInfos.count(n);
+}
+bool RModel::IsInitializedTensor(const std::string &name) const { return fInitializedTensors.count(UTILITY::Clean_name(name)) != 0; }
+bool RModel::IsConstantTensor(const std::string &name) const
+{
+   auto it = fInitializedTensors.find(UTILITY::Clean_name(name));
+   return it != fInitializedTensors.end() && it->second.constant;
+}
+bool RModel::IsInputTensor(const std::string &name) const { return fInputTensorInfos.count(UTILITY::Clean_name(name)) != 0; }
+bool RModel::IsOutputTensor(const std::string &name) const
+{
+   const std::string n = UTILITY::Clean_name(name);
+   return std::find(fOutputTensorNames.begin(), fOutputTensorNames.end(), n) != fOutputTensorNames.end();
+}
+
+const std::vector<size_t> &RModel::GetTensorShape(const std::string &name) const
+{
+   const std::string n = UTILITY::Clean_name(name);
+   if (auto it = fInitializedTensors.find(n); it != fInitializedTensors.end()) return it->second.shape;
+   if (auto it = fInputTensorInfos.find(n); it != fInputTensorInfos.end()) return it->second.shape;
+   if (auto it = fIntermediateTensorInfos.find(n); it != fIntermediateTensorInfos.end()) return it->second.shape;
+   throw std::runtime_error("SOFIE tensor [" + n + "] for which the shape is requested is not found");
+}
+
+ETensorType RModel::GetTensorType(const std::string &name) const
+{
+   const std::string n = UTILITY::Clean_name(name);
+   if (auto it = fInitializedTensors.find(n); it != fInitializedTensors.end()) return it->second.type;
+   if (auto it = fInputTensorInfos.find(n); it != fInputTensorInfos.end()) return it->second.type;
+   if (auto it = fIntermediateTensorInfos.find(n); it != fIntermediateTensorInfos.end()) return it->second.type;
+   throw std::runtime_error("SOFIE tensor [" + n + "] for which the type is requested is not found");
+}
+
+std::shared_ptr<void> RModel::GetInitializedTensorData(const std::string &name) const
+{
+   auto it = fInitializedTensors.find(UTILITY::Clean_name(name));
+   if (it == fInitializedTensors.end()) throw std::runtime_error("SOFIE tensor [" + name + "] for which the data is requested is not found");
+   return it->second.data;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// initialisation: shapes, then epilogue fusion
+// ---------------------------------------------------------------------------------------------------
+void RModel::Initialize(int batchSize, bool verbose)
+{
+   if (fIsInitialized) return;
+   fBatchSize = batchSize;
+   for (auto &[name, dims] : fInputDimShapes) {
+      std::vector<size_t> s;
+      for (auto &d : dims) {
+         if (!d.isParam) { s.push_back(d.dim); continue; }
+         // input_size, batch_size, bs take the batch size (core/src/RModel.cxx:676-685)
+         if ((d.param == "input_size" || d.param == "batch_size" || d.param == "bs") && batchSize > 0) s.push_back(size_t(batchSize));
+         else if (d.dim > 0) s.push_back(d.dim);
+         else
+            throw std::runtime_error("SOFIE_B200: input " + name + " has the symbolic dimension " + d.param +
+                                     "; the B200 target needs static shapes (pass a batch size for input_size / batch_size / bs)");
+      }
+      fInputTensorInfos[name].shape = s;
+   }
+   for (auto &n : fInputTensorNames)
+      if (!fInputTensorInfos.count(n)) throw std::runtime_error("SOFIE: input tensor " + n + " has no type and shape information");
+   size_t i = 0;
+   for (auto &op : fOperators) {
+      if (verbose) std::cout << "[SOFIE_B200 generator] initializing operator " << i << " " << typeid(*op).name() << std::endl;
+      op->Initialize(*this);
+      ++i;
+   }
+   for (auto &o : fOutputTensorNames)
+      if (!CheckIfTensorAlreadyExist(o)) throw std::runtime_error("SOFIE: output tensor " + o + " is not produced by any operator");
+   fIsInitialized = true;
+}
+
+namespace {
+ROperator_B200 *AsB200(ROperator *op) { return dynamic_cast<ROperator_B200 *>(op); }
+}  // namespace
+
+bool RModel::CheckGPUOperators() const
+{
+   for (auto &op : fOperators)
+      if (!dynamic_cast<ROperator_B200 *>(op.get())) return false;
+   return true;
+}
+
+// Which epilogues fold into which contraction.  Legality is the reference's: the producer's output
+// has exactly one consumer and is not a graph output (core/src/RModel_Fusion_ALPAKA.cxx:376-415).
+// The reference folds only Relu / LeakyRelu into Gemm (and needs a bias for Relu, a limit of its BLAS
+// epilogues); here any activation, a following inference BatchNormalization (as column scale + shift)
+// and a residual Add fold into Gemm / Conv / the quantised contractions, in that order of appearance.
+void RModel::FuseOperators()
+{
+   auto consumers = [&](const std::string &t) {
+      size_t n = 0;
+      for (size_t k = 0; k < fOperators.size(); ++k) {
+         if (fSkippedOperators.count(k)) continue;
+         for (auto &in : fOperators[k]->GetOpInputTensors())
+            if (in == t) ++n;
+      }
+      return n;
+   };
+   for (size_t i = 0; i < fOperators.size(); ++i) {
+      if (fSkippedOperators.count(i)) continue;
+      auto *prod = AsB200(fOperators[i].get());
+      if (!prod || !prod->HasFusableEpilogue()) continue;
+      for (size_t j = i + 1; j < fOperators.size(); ++j) {
+         if (fSkippedOperators.count(j)) continue;
+         if (prod->GetOpOutputTensors().size() != 1) break;
+         const std::string out = prod->GetOpOutputTensors()[0];
+         if (consumers(out) != 1 || IsOutputTensor(out)) break;
+         ROperator *next = fOperators[j].get();
+         const auto &nin = next->GetOpInputTensors();
+         if (std::find(nin.begin(), nin.end(), out) == nin.end()) break;  // only the operator that follows directly
+         bool fused = false;
+         std::string what;
+         if (auto *u = dynamic_cast<ROperator_Unary *>(next)) {
+            fused = prod->FuseActivation(u->Activation(), u->GetAlpha(), u->GetOpOutputTensors()[0]);
+            what = "activation";
+         } else if (auto *bn = dynamic_cast<ROperator_BatchNormalization<float> *>(next)) {
+            const bool isContraction = !dynamic_cast<ROperator_BatchNormalization<float> *>(fOperators[i].get());
+            if (isContraction && bn->NameX() == out) {
+               std::string s, t;
+               bn->MakeScaleShift(*this, s, t);
+               fused = prod->FuseScaleShift(*this, s, t, bn->NameY());
+               if (fused && bn->GetActivationType() == EActivationType::RELU) prod->FuseActivation(EActivationType::RELU, 0.f, bn->NameY());
+               what = "BatchNormalization as column scale + shift";
+            }
+         } else if (auto *add = dynamic_cast<ROperator_BasicBinary<float, EBasicBinaryOperator::Add> *>(next)) {
+            const std::string other = add->NameA() == out ? add->NameB() : add->NameA();
+            if (other != out) {
+               fused = prod->FuseResidual(*this, other, add->GetOpOutputTensors()[0]);
+               what = "residual Add";
+            }
+         }
+         if (!fused) break;
+         fIntermediateTensorInfos.erase(out);
+         fSkippedOperators.insert(j);
+         fFusionLog.push_back("op_" + std::to_string(i) + " <- op_" + std::to_string(j) + " (" + what + ")");
+      }
+   }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// arena
+// ---------------------------------------------------------------------------------------------------
+void RModel::PlanArena()
+{
+   fRegions.clear();
+   const int64_t nOps = int64_t(fOperators.size());
+   std::set<std::string> usedWeights;
+   std::map<std::string, std::pair<int64_t, int64_t>> life;  // pooled tensors: [begin, end)
+   auto root = [&](const std::string &n) { return ResolveAliasTensor(n); };
+   std::set<std::string> outputRoots;
+   for (auto &o : fOutputTensorNames) outputRoots.insert(root(o));
+   for (int64_t k = 0; k < nOps; ++k) {
+      if (fSkippedOperators.count(size_t(k))) continue;
+      for (auto &in : fOperators[k]->GetOpInputTensors()) {
+         const std::string r = root(in);
+         if (IsInitializedTensor(r)) { if (!IsConstantTensor(r)) usedWeights.insert(r); continue; }
+         if (auto it = life.find(r); it != life.end()) it->second.second = std::max(it->second.second, k + 1);
+      }
+      for (auto &o : fOperators[k]->GetOpOutputTensors()) {
+         const std::string r = root(o);
+         if (IsInitializedTensor(r) || IsInputTensor(r) || outputRoots.count(r)) continue;
+         if (!life.count(r)) life[r] = {k, k + 1};
+      }
+   }
+   // graph outputs that are weights or folded constants still need device storage
+   for (auto &r : outputRoots)
+      if (IsInitializedTensor(r)) usedWeights.insert(r);
+
+   int64_t off = 0;
+   auto place = [&](const std::string &name, int64_t bytes, const char *kind) {
+      fRegions.push_back({name, off, bytes, 0, nOps + 1, kind});
+      off += AlignUp(bytes);
+   };
+   for (auto &n : fInitializedOrder)
+      if (usedWeights.count(n)) {
+         auto &t = fInitializedTensors.at(n);
+         place(n, int64_t(ConvertShapeToLength(t.shape) * GetTypeSize(t.type)), "weight");
+      }
+   fWeightBytes = off;
+   for (auto &n : fInputTensorNames) {
+      auto &t = fInputTensorInfos.at(n);
+      place(n, int64_t(ConvertShapeToLength(t.shape) * GetTypeSize(t.type)), "input");
+   }
+   for (auto &r : outputRoots)
+      if (!IsInitializedTensor(r) && !IsInputTensor(r)) {
+         auto &t = fIntermediateTensorInfos.at(r);
+         place(r, int64_t(ConvertShapeToLength(t.shape) * GetTypeSize(t.type)), "output");
+      }
+   // pooled: intermediates by lifetime, operator scratch for the one step that uses it
+   std::vector<TensorLifeInfo> lives;
+   std::vector<ArenaRegion> pooled;
+   fUnplannedBytes = 0;
+   for (auto &[n, be] : life) {
+      auto &t = fIntermediateTensorInfos.at(n);
+      const int64_t bytes = int64_t(ConvertShapeToLength(t.shape) * GetTypeSize(t.type));
+      lives.push_back({be.first, be.second, bytes});
+      pooled.push_back({n, 0, bytes, be.first, be.second, "intermediate"});
+      fUnplannedBytes += AlignUp(bytes);
+   }
+   for (int64_t k = 0; k < nOps; ++k) {
+      if (fSkippedOperators.count(size_t(k))) continue;
+      if (auto *b = AsB200(fOperators[k].get()))
+         for (auto &s : b->GetDeviceScratch_GPU_B200()) {
+            lives.push_back({k, k + 1, int64_t(s.bytes)});
+            pooled.push_back({s.name, 0, int64_t(s.bytes), k, k + 1, "scratch"});
+            fUnplannedBytes += AlignUp(int64_t(s.bytes));
+         }
+   }
+   MemoryResult res = OrganizeMemory(lives);
+   for (size_t i = 0; i < pooled.size(); ++i) {
+      pooled[i].offset = off + res.offsets[i];
+      fRegions.push_back(pooled[i]);
+   }
+   fPoolBytes = res.total_bytes;
+   fArenaBytes = off + res.total_bytes;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// emission
+// ---------------------------------------------------------------------------------------------------
+void RModel::Generate(std::underlying_type_t<Options>, int, bool)
+{
+   throw std::runtime_error("SOFIE_B200::RModel::Generate: the CPU target belongs to the reference generator; use GenerateGPU_B200 "
+                            "(this generator has no CPU path)");
+}
+
+void RModel::GenerateGPU_B200(std::underlying_type_t<Options> options, int batchSize, bool verbose)
+{
+   fOptions = options;
+   const auto unsupported = Options::kGNN | Options::kGNNComponent | Options::kLowRankFactorize | Options::kStridedInput | Options::kNoSession |
+                            Options::kSafetensorsWeightFile | Options::kKernelOnly;
+   if (options & unsupported)
+      throw std::runtime_error("SOFIE_B200::GenerateGPU_B200: an option outside the B200 target was requested (GNN, low-rank, strided input, "
+                               "no-session, safetensors and kernel-only generation are not part of it)");
+   Initialize(batchSize, verbose);
+   for (size_t i = 0; i < fOperators.size(); ++i)
+      if (!AsB200(fOperators[i].get()))
+         throw std::runtime_error("SOFIE_B200: operator " + std::to_string(i) + " has no B200 implementation");
+   FuseOperators();
+   PlanArena();
+   fGC = GenerateSessionCode_GPU_B200();
+}
+
+namespace {
+
+std::string PtrType(ETensorType t) { return ConvertTypeToString(t) + " *"; }
+
+template <class T>
+void WriteValues(std::ostream &o, const void *data, size_t n, bool asInt)
+{
+   const T *p = static_cast<const T *>(data);
+   for (size_t i = 0; i < n; ++i) {
+      if (asInt) o << long(p[i]);
+      else o << p[i];
+      o << (i + 1 < n ? " " : "");
+   }
+}
+
+void WriteTensorText(std::ostream &o, const InitializedTensor &t)
+{
+   const size_t n = ConvertShapeToLength(t.shape);
+   switch (t.type) {
+   case ETensorType::FLOAT: {
+      // max_digits10 digits, subnormals flushed to zero: the reference's text format (core/src/RModel.cxx:1936-1951)
+      o << std::setprecision(std::numeric_limits<float>::max_digits10);
+      const float *p = static_cast<const float *>(t.data.get());
+      for (size_t i = 0; i < n; ++i) {
+         float v = p[i];
+         if (v != 0.f && std::abs(v) < std::numeric_limits<float>::min()) v = 0.f;
+         o << v << (i + 1 < n ? " " : "");
+      }
+      break;
+   }
+   case ETensorType::INT8: WriteValues<int8_t>(o, t.data.get(), n, true); break;
+   case ETensorType::UINT8: case ETensorType::FLOAT8E4M3FN: case ETensorType::BOOL: WriteValues<uint8_t>(o, t.data.get(), n, true); break;
+   case ETensorType::BFLOAT16: WriteValues<uint16_t>(o, t.data.get(), n, true); break;
+   case ETensorType::INT32: WriteValues<int32_t>(o, t.data.get(), n, true); break;
+   case ETensorType::INT64: WriteValues<int64_t>(o, t.data.get(), n, true); break;
+   default: throw std::runtime_error("SOFIE_B200: tensor type cannot be written to the weight file");
+   }
+}
+
+}  // namespace
+
+std::string RModel::GenerateSessionCode_GPU_B200()
+{
+   const bool extStream = fOptions & static_cast<std::underlying_type_t<Options>>(Options::kExternalStream);
+   const bool customMem = fOptions & static_cast<std::underlying_type_t<Options>>(Options::kCustomMemory);
+   const bool profile = fOptions & static_cast<std::underlying_type_t<Options>>(Options::kProfile);
+   const bool debug = fOptions & static_cast<std::underlying_type_t<Options>>(Options::kDebug);
+   const bool noWeightFile = fOptions & static_cast<std::underlying_type_t<Options>>(Options::kNoWeightFile);
+
+   std::map<std::string, const ArenaRegion *> region;
+   for (auto &r : fRegions) region[r.name] = &r;
+   auto typeOf = [&](const std::string &n) { return GetTensorType(n); };
+
+   std::stringstream o;
+   std::string guard = fName;
+   for (auto &c : guard) c = char(std::toupper(static_cast<unsigned char>(c)));
+   o << "// Code generated automatically by SOFIE_B200 (B200 / sm_100a target) from the model " << fName << "\n";
+   o << "// Link with libsofie_b200 and the CUDA runtime.\n";
+   o << "#ifndef SOFIE_B200_" << guard << "\n#define SOFIE_B200_" << guard << "\n\n";
+   o << "#include <cuda_runtime.h>\n#include <cstdint>\n#include <cstdio>\n#include <fstream>\n#include <limits>\n#include <stdexcept>\n#include <string>\n#include <vector>\n";
+   o << "#include \"sofie_b200.h\"\n\nnamespace SOFIE_" << fName << " {\n\n";
+   if (customMem) {
+      o << "// One block for weights, inputs, outputs and the pooled intermediates: alloc is called once by the\n"
+           "// constructor, dealloc once by the destructor (Options::kCustomMemory).\n"
+           "struct MemoryProvider {\n   void *(*alloc)(size_t bytes, void *user);\n   void (*dealloc)(void *block, void *user);\n   void *user;\n};\n\n";
+   }
+   if (noWeightFile) {
+      for (auto &r : fRegions) {
+         if (r.kind != "weight") continue;
+         auto &t = fInitializedTensors.at(r.name);
+         o << "static const " << ConvertTypeToString(t.type) << " fWeights_" << r.name << "[] = {";
+         std::stringstream vals;
+         WriteTensorText(vals, t);
+         std::string v = vals.str();
+         for (auto &c : v) if (c == ' ') c = ',';
+         o << v << "};\n";
+      }
+      o << "\n";
+   }
+   o << "struct Session {\n";
+   o << "   static constexpr size_t kArenaBytes = " << fArenaBytes << ";\n";
+   o << "   static constexpr size_t kWeightBytes = " << fWeightBytes << ";\n";
+   o << "   static constexpr size_t kPoolBytes = " << fPoolBytes << ";        // pooled intermediates + scratch, planned by lifetime\n";
+   o << "   static constexpr size_t kUnplannedPoolBytes = " << fUnplannedBytes << ";  // the same tensors without reuse\n";
+   o << "   cudaStream_t stream = nullptr;\n   bool fOwnStream = false;\n   sofie_b200_ctx *ctx = nullptr;\n   char *fArena = nullptr;\n";
+   if (customMem) o << "   MemoryProvider fProvider{};\n";
+   o << "\n   // tensors: pointers into the arena\n";
+   for (auto &r : fRegions) {
+      const std::string t = r.kind == "scratch" ? std::string("char *") : PtrType(typeOf(r.name));
+      const std::string member = r.kind == "input" ? "fInputStage_" + r.name : "tensor_" + r.name;
+      o << "   " << t << member << " = nullptr;  // " << r.kind << ", offset " << r.offset << ", " << r.bytes << " bytes";
+      if (r.kind == "intermediate" || r.kind == "scratch") o << ", alive on steps [" << r.begin << "," << r.end << ")";
+      o << "\n";
+   }
+   o << "\n   // per-operator state\n";
+   for (size_t i = 0; i < fOperators.size(); ++i)
+      if (!fSkippedOperators.count(i)) o << AsB200(fOperators[i].get())->GenerateSessionMembersCode_GPU_B200(std::to_string(i));
+   if (profile) {
+      o << "   std::vector<cudaEvent_t> fProfEvents;\n   std::vector<double> fProfTotalMs;\n   size_t fProfCalls = 0;\n";
+   }
+
+   o << R"(
+   static void Check(int rc, const char *what)
+   {
+      if (rc != 0) throw std::runtime_error(std::string("SOFIE_B200 ") + what + ": " + sofie_b200_status_string(rc) + ": " + sofie_b200_last_error());
+   }
+   static void CheckCuda(cudaError_t e, const char *what)
+   {
+      if (e != cudaSuccess) throw std::runtime_error(std::string("SOFIE_B200 ") + what + ": " + cudaGetErrorString(e));
+   }
+   template <class T>
+   static void ReadTensorFromStream(std::istream &is, std::vector<T> &target, const std::string &expectedName, size_t expectedLength)
+   {
+      std::string name;
+      size_t length = 0;
+      is >> name >> length;
+      if (name != expectedName)
+         throw std::runtime_error("sofie failed to read the correct tensor name; expected name is " + expectedName + " , read " + name);
+      if (length != expectedLength)
+         throw std::runtime_error("sofie failed to read the correct tensor size; expected size is " + std::to_string(expectedLength) + " , read " + std::to_string(length));
+      target.resize(length);
+      for (size_t i = 0; i < length; ++i) {
+         if constexpr (sizeof(T) == 1) { int v; is >> v; target[i] = T(v); }
+         else if constexpr (std::is_floating_point<T>::value) {
+            std::string tok; is >> tok;
+            target[i] = tok == "inf" ? std::numeric_limits<T>::infinity() : tok == "-inf" ? -std::numeric_limits<T>::infinity()
+                        : tok == "nan" ? std::numeric_limits<T>::quiet_NaN() : T(std::stod(tok));
+         } else is >> target[i];
+      }
+      if (is.fail()) throw std::runtime_error("sofie failed to read the values for tensor " + expectedName);
+   }
+)";
+
+   // ---- InitSession
+   o << "\n   void InitSession(const std::string &filename)\n   {\n";
+   o << "      int device = 0;\n      CheckCuda(cudaGetDevice(&device), \"cudaGetDevice\");\n";
+   o << "      Check(sofie_b200_ctx_create(&ctx, device, stream), \"ctx_create\");\n";
+   if (customMem) {
+      o << "      fArena = static_cast<char *>(fProvider.alloc(kArenaBytes, fProvider.user));\n";
+      o << "      if (!fArena) throw std::runtime_error(\"SOFIE_B200 MemoryProvider::alloc returned null\");\n";
+      o << "      if (reinterpret_cast<uintptr_t>(fArena) % 256) throw std::runtime_error(\"SOFIE_B200 MemoryProvider block is not 256-byte aligned\");\n";
+   } else {
+      o << "      CheckCuda(cudaMalloc(reinterpret_cast<void **>(&fArena), kArenaBytes ? kArenaBytes : 256), \"arena allocation\");\n";
+   }
+   for (auto &r : fRegions) {
+      const std::string t = r.kind == "scratch" ? std::string("char *") : PtrType(typeOf(r.name));
+      const std::string member = r.kind == "input" ? "fInputStage_" + r.name : "tensor_" + r.name;
+      o << "      " << member << " = reinterpret_cast<" << t << ">(fArena + " << r.offset << ");\n";
+   }
+   if (debug) o << "      ValidateMemory();\n";
+   bool anyWeight = false;
+   for (auto &r : fRegions) anyWeight |= r.kind == "weight";
+   if (anyWeight) {
+      if (!noWeightFile) {
+         o << "      std::ifstream f(filename);\n      if (!f.is_open()) throw std::runtime_error(\"sofie failed to open file \" + filename + \" for input weights\");\n";
+      } else {
+         o << "      (void)filename;\n";
+      }
+      for (auto &r : fRegions) {
+         if (r.kind != "weight") continue;
+         auto &t = fInitializedTensors.at(r.name);
+         const std::string ct = ConvertTypeToString(t.type);
+         const size_t len = ConvertShapeToLength(t.shape);
+         if (!noWeightFile) {
+            o << "      { std::vector<" << ct << "> h; ReadTensorFromStream(f, h, \"tensor_" << r.name << "\", " << len << ");\n";
+            o << "        CheckCuda(cudaMemcpyAsync(tensor_" << r.name << ", h.data(), " << r.bytes
+              << ", cudaMemcpyHostToDevice, stream), \"weight upload\"); CheckCuda(cudaStreamSynchronize(stream), \"weight upload\"); }\n";
+         } else {
+            o << "      CheckCuda(cudaMemcpyAsync(tensor_" << r.name << ", fWeights_" << r.name << ", " << r.bytes
+              << ", cudaMemcpyHostToDevice, stream), \"weight upload\");\n";
+         }
+      }
+      o << "      CheckCuda(cudaStreamSynchronize(stream), \"weight upload\");\n";
+   } else {
+      o << "      (void)filename;\n";
+   }
+   for (size_t i = 0; i < fOperators.size(); ++i)
+      if (!fSkippedOperators.count(i)) o << AsB200(fOperators[i].get())->GenerateInitCode_GPU_B200(std::to_string(i));
+   if (profile) {
+      o << "      fProfEvents.resize(" << fOperators.size() + 1 << ");\n      for (auto &e : fProfEvents) CheckCuda(cudaEventCreate(&e), \"event\");\n";
+      o << "      fProfTotalMs.assign(" << fOperators.size() << ", 0.0);\n";
+   }
+   o << "      Check(sofie_b200_ctx_sync(ctx), \"Session initialisation\");\n";
+   o << "   }\n\n";
+
+   // ---- constructors / destructor
+   const std::string defFile = noWeightFile ? "\"\"" : "\"" + fName + ".dat\"";
+   const std::string prov = customMem ? "MemoryProvider provider, " : "";
+   const std::string provInit = customMem ? "fProvider = provider; " : "";
+   o << "   Session(" << prov << "std::string filename = " << defFile << ")\n   {\n      " << provInit
+     << "CheckCuda(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), \"stream\");\n      fOwnStream = true;\n      InitSession(filename);\n   }\n";
+   if (extStream) {
+      o << "   // the stream is borrowed: it must outlive the Session and is never destroyed here\n";
+      o << "   Session(" << prov << "cudaStream_t externalStream, std::string filename = " << defFile << ")\n   {\n      " << provInit
+        << "stream = externalStream;\n      InitSession(filename);\n   }\n";
+   }
+   o << "   Session(const Session &) = delete;\n   Session &operator=(const Session &) = delete;\n";
+   o << "   ~Session()\n   {\n      if (stream || ctx) cudaStreamSynchronize(stream);\n";
+   for (size_t i = 0; i < fOperators.size(); ++i)
+      if (!fSkippedOperators.count(i)) o << AsB200(fOperators[i].get())->GenerateDestroyCode_GPU_B200(std::to_string(i));
+   if (profile) o << "      for (auto &e : fProfEvents) cudaEventDestroy(e);\n";
+   o << "      if (ctx) sofie_b200_ctx_destroy(ctx);\n";
+   if (customMem) o << "      if (fArena) fProvider.dealloc(fArena, fProvider.user);\n";
+   else o << "      if (fArena) cudaFree(fArena);\n";
+   o << "      if (fOwnStream && stream) cudaStreamDestroy(stream);\n   }\n\n";
+
+   // ---- _infer_impl
+   std::string params, args, hostParams;
+   for (size_t i = 0; i < fInputTensorNames.size(); ++i) {
+      const auto &n = fInputTensorNames[i];
+      const std::string ct = ConvertTypeToString(typeOf(n));
+      params += (i ? ", " : "") + std::string("const ") + ct + " *tensor_" + n;
+      hostParams += (i ? ", " : "") + std::string("const ") + ct + " *host_" + n;
+      args += (i ? ", " : "") + std::string("tensor_") + n;
+   }
+   o << "   // records the whole inference on the stream; device pointers in, nothing is synchronised\n";
+   o << "   void _infer_impl(" << params << ")\n   {\n";
+   for (size_t i = 0; i < fOperators.size(); ++i) {
+      if (fSkippedOperators.count(i)) continue;
+      auto *op = AsB200(fOperators[i].get());
+      if (profile) o << "      CheckCuda(cudaEventRecord(fProfEvents[" << i << "], stream), \"event\");\n";
+      if (op->IsAlias()) {
+         const std::string out = op->GetOpOutputTensors()[0], r = ResolveAliasTensor(out);
+         o << "      " << PtrType(typeOf(out)) << "tensor_" << out << " = const_cast<" << PtrType(typeOf(out)) << ">(tensor_" << r << ");  // alias\n";
+      }
+      o << op->Generate_GPU_B200(std::to_string(i));
+   }
+   if (profile) o << "      CheckCuda(cudaEventRecord(fProfEvents[" << fOperators.size() << "], stream), \"event\");\n";
+   o << "   }\n\n";
+
+   // ---- infer surface
+   auto outMember = [&](const std::string &n) {
+      const std::string r = ResolveAliasTensor(n);
+      return IsInputTensor(r) ? std::string() : "tensor_" + r;
+   };
+   const std::string out0 = fOutputTensorNames.empty() ? "" : fOutputTensorNames[0];
+   const std::string outT = out0.empty() ? "void" : ConvertTypeToString(typeOf(out0));
+   o << "   // device pointers in; the returned device pointer is owned by the Session and overwritten by the next call\n";
+   o << "   " << outT << " *infer_nosync(" << params << ")\n   {\n      _infer_impl(" << args << ");\n      return " << outMember(out0) << ";\n   }\n";
+   o << "   " << outT << " *infer(" << params << ")\n   {\n      " << outT << " *r = infer_nosync(" << args << ");\n"
+     << "      Check(sofie_b200_ctx_sync(ctx), \"infer\");\n";
+   if (profile) {
+      o << "      for (size_t i = 0; i + 1 < fProfEvents.size(); ++i) { float ms = 0; if (cudaEventElapsedTime(&ms, fProfEvents[i], fProfEvents[i + 1]) == cudaSuccess) fProfTotalMs[i] += ms; }\n      ++fProfCalls;\n";
+   }
+   o << "      return r;\n   }\n";
+   o << "   // output i of the graph (device pointer), valid after infer()\n   const void *output(size_t i) const\n   {\n      switch (i) {\n";
+   for (size_t i = 0; i < fOutputTensorNames.size(); ++i) o << "      case " << i << ": return " << outMember(fOutputTensorNames[i]) << ";\n";
+   o << "      default: throw std::runtime_error(\"SOFIE_B200 Session::output: index out of range\");\n      }\n   }\n";
+   o << "   // host pointers in, host vector out: copies in, runs, copies the first output back\n";
+   o << "   std::vector<" << outT << "> infer_host(" << hostParams << ")\n   {\n";
+   for (auto &n : fInputTensorNames) {
+      o << "      CheckCuda(cudaMemcpyAsync(fInputStage_" << n << ", host_" << n << ", " << region.at(n)->bytes
+        << ", cudaMemcpyHostToDevice, stream), \"input upload\");\n";
+   }
+   std::string stageArgs;
+   for (size_t i = 0; i < fInputTensorNames.size(); ++i) stageArgs += (i ? ", " : "") + std::string("fInputStage_") + fInputTensorNames[i];
+   const size_t outLen = out0.empty() ? 0 : ConvertShapeToLength(GetTensorShape(out0));
+   o << "      " << outT << " *d = infer_nosync(" << stageArgs << ");\n";
+   o << "      std::vector<" << outT << "> h(" << outLen << ");\n";
+   o << "      CheckCuda(cudaMemcpyAsync(h.data(), d, " << outLen << " * sizeof(" << outT << "), cudaMemcpyDeviceToHost, stream), \"output download\");\n";
+   o << "      Check(sofie_b200_ctx_sync(ctx), \"infer_host\");\n      return h;\n   }\n";
+   o << "   // zeroes the pooled intermediates (the reference's resetState)\n";
+   o << "   void resetState()\n   {\n      CheckCuda(cudaMemsetAsync(fArena + (kArenaBytes - kPoolBytes), 0, kPoolBytes, stream), \"resetState\");\n   }\n";
+   o << "   size_t GetIntermediateMemoryPoolSize() const { return kPoolBytes; }\n";
+   o << "   size_t GetArenaSize() const { return kArenaBytes; }\n";
+   o << "   long long GetLaunchCount() const { return sofie_b200_ctx_launch_count(ctx); }\n";
+   if (profile) {
+      o << "   double GetOpAvgTime(size_t op) const { return fProfCalls ? fProfTotalMs.at(op) / double(fProfCalls) : 0.0; }\n";
+      o << "   void PrintProfilingResults() const\n   {\n      for (size_t i = 0; i < fProfTotalMs.size(); ++i) if (fProfTotalMs[i] > 0) std::printf(\"op_%zu : %.4f ms\\n\", i, GetOpAvgTime(i));\n   }\n";
+   }
+   if (debug) {
+      o << "   // alignment and overlap-while-alive check of the arena regions (the reference's ValidateMemory)\n";
+      o << "   void ValidateMemory() const\n   {\n      struct R { const char *name; size_t off, bytes; long b, e; };\n      static const R regions[] = {\n";
+      for (auto &r : fRegions) o << "         {\"" << r.name << "\", " << r.offset << ", " << r.bytes << ", " << r.begin << ", " << r.end << "},\n";
+      o << "      };\n      const size_t n = sizeof(regions) / sizeof(regions[0]);\n"
+           "      for (size_t i = 0; i < n; ++i) {\n"
+           "         if (regions[i].off % 256) throw std::runtime_error(std::string(\"SOFIE_B200 arena region not 256-byte aligned: \") + regions[i].name);\n"
+           "         if (regions[i].off + regions[i].bytes > kArenaBytes) throw std::runtime_error(std::string(\"SOFIE_B200 arena region out of bounds: \") + regions[i].name);\n"
+           "         for (size_t j = 0; j < i; ++j) {\n"
+           "            const bool alive = regions[i].b < regions[j].e && regions[j].b < regions[i].e;\n"
+           "            const bool overlap = regions[i].off < regions[j].off + regions[j].bytes && regions[j].off < regions[i].off + regions[i].bytes;\n"
+           "            if (alive && overlap && regions[i].bytes && regions[j].bytes)\n"
+           "               throw std::runtime_error(std::string(\"SOFIE_B200 arena regions overlap while alive: \") + regions[i].name + \" / \" + regions[j].name);\n"
+           "         }\n      }\n"
+           "      std::printf(\"[SOFIE debug] arena %zu bytes, %zu regions validated\\n\", size_t(kArenaBytes), n);\n   }\n";
+   }
+   o << "};\n\n}  // namespace SOFIE_" << fName << "\n\n#endif  // SOFIE_B200_" << guard << "\n";
+   return o.str();
+}
+
+void RModel::WriteWeightFile(const std::string &filename) const
+{
+   std::ofstream f(filename);
+   if (!f.is_open()) throw std::runtime_error("sofie-b200 failed to open file " + filename + " for tensor weight data");
+   for (auto &r : fRegions) {
+      if (r.kind != "weight") continue;
+      auto &t = fInitializedTensors.at(r.name);
+      f << "tensor_" << r.name << " " << ConvertShapeToLength(t.shape) << "\n";
+      WriteTensorText(f, t);
+      f << "\n";
+   }
+   if (f.fail()) throw std::runtime_error("sofie-b200 failed to write tensor weight data to " + filename);
+}
+
+void RModel::OutputGenerated(std::string filename, bool append)
+{
+   if (fGC.empty()) throw std::runtime_error("SOFIE_B200::OutputGenerated: nothing generated yet; call GenerateGPU_B200 first");
+   if (filename.empty()) filename = fName + ".hxx";
+   std::ofstream f(filename, append ? std::ios::app : std::ios::out);
+   if (!f.is_open()) throw std::runtime_error("sofie-b200 failed to open file " + filename + " for output");
+   f << fGC;
+   f.close();
+   if (!(fOptions & static_cast<std::underlying_type_t<Options>>(Options::kNoWeightFile))) {
+      std::string dat = filename;
+      auto dot = dat.find_last_of('.');
+      if (dot != std::string::npos) dat = dat.substr(0, dot);
+      // the Session's default weight file name is <model>.dat, next to the header
+      auto slash = dat.find_last_of("/\\");
+      const std::string dir = slash == std::string::npos ? "" : dat.substr(0, slash + 1);
+      WriteWeightFile(dir + fName + ".dat");
+   }
+}
+
+void RModel::PrintGenerated() const { std::cout << fGC; }
+
+}  // namespace SOFIE_B200

@@ -1,0 +1,50 @@
+// sofie_b200_emit: ONNX file -> Session header for the B200 target (+ weight file), the counterpart
+// of the reference's emitter programs (tests/templates/EmitFromONNX_GPU_ALPAKA.cxx.in:9-17).
+//
+//   sofie_b200_emit <model.onnx> <out.hxx> [--batch N] [--external-stream] [--custom-memory]
+//                   [--profile] [--debug] [--no-weight-file] [--check]
+//
+// Prints a one-line JSON report of what generation decided (fusions, arena size) on stdout.
+#include <cstring>
+#include <iostream>
+
+#include "SOFIE_B200/RModelParser_ONNX.hxx"
+
+using namespace SOFIE_B200;
+
+int main(int argc, char **argv)
+{
+   if (argc < 3) {
+      std::cerr << "usage: sofie_b200_emit <model.onnx> <out.hxx> [--batch N] [--external-stream] [--custom-memory] [--profile] [--debug] "
+                   "[--no-weight-file] [--check]\n";
+      return 2;
+   }
+   std::underlying_type_t<Options> opts = 0;
+   int batch = -1;
+   bool checkOnly = false;
+   for (int i = 3; i < argc; ++i) {
+      if (!std::strcmp(argv[i], "--batch") && i + 1 < argc) batch = std::atoi(argv[++i]);
+      else if (!std::strcmp(argv[i], "--external-stream")) opts = opts | Options::kExternalStream;
+      else if (!std::strcmp(argv[i], "--custom-memory")) opts = opts | Options::kCustomMemory;
+      else if (!std::strcmp(argv[i], "--profile")) opts = opts | Options::kProfile;
+      else if (!std::strcmp(argv[i], "--debug")) opts = opts | Options::kDebug;
+      else if (!std::strcmp(argv[i], "--no-weight-file")) opts = opts | Options::kNoWeightFile;
+      else if (!std::strcmp(argv[i], "--check")) checkOnly = true;
+      else { std::cerr << "unknown option " << argv[i] << "\n"; return 2; }
+   }
+   try {
+      RModelParser_ONNX parser;
+      if (checkOnly) return parser.CheckModel(argv[1], true) ? 0 : 1;
+      RModel model = parser.Parse(argv[1]);
+      model.GenerateGPU_B200(opts, batch);
+      model.OutputGenerated(argv[2]);
+      std::cout << "{\"model\": \"" << model.GetName() << "\", \"operators\": " << model.GetNumberOfOperators() << ", \"fusions\": [";
+      for (size_t i = 0; i < model.GetFusionLog().size(); ++i) std::cout << (i ? ", " : "") << "\"" << model.GetFusionLog()[i] << "\"";
+      std::cout << "], \"arena_bytes\": " << model.GetArenaBytes() << ", \"pool_bytes\": " << model.GetIntermediateMemoryPoolSize()
+                << ", \"unplanned_pool_bytes\": " << model.GetUnplannedIntermediateBytes() << ", \"regions\": " << model.GetArenaRegions().size() << "}\n";
+   } catch (const std::exception &e) {
+      std::cerr << e.what() << "\n";
+      return 1;
+   }
+   return 0;
+}

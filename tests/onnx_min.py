@@ -196,3 +196,78 @@ def load(path: str) -> Graph:
             outputs.append(_value_info(val)[0])
     inputs = [(n, s) for n, s in inputs if n not in inits]
     return Graph(nodes, inits, inputs, outputs)
+
+
+# ---- writer: the inverse of load(), used to hand the fixtures' graphs to the C++ front-end ----------
+def _enc_varint(v: int) -> bytes:
+    v &= (1 << 64) - 1
+    out = bytearray()
+    while True:
+        b = v & 0x7F
+        v >>= 7
+        out.append(b | (0x80 if v else 0))
+        if not v:
+            return bytes(out)
+
+
+def _field(num: int, wt: int, payload: bytes) -> bytes:
+    key = _enc_varint((num << 3) | wt)
+    if wt == 2:
+        return key + _enc_varint(len(payload)) + payload
+    return key + payload
+
+
+_ONNX_DT = {np.dtype(np.float32): 1, np.dtype(np.uint8): 2, np.dtype(np.int8): 3, np.dtype(np.int32): 6, np.dtype(np.int64): 7}
+
+
+def _enc_tensor(name: str, arr: np.ndarray, data_type: int | None = None) -> bytes:
+    arr = np.ascontiguousarray(arr)
+    out = b"".join(_field(1, 0, _enc_varint(int(d))) for d in arr.shape)
+    out += _field(2, 0, _enc_varint(data_type if data_type is not None else _ONNX_DT[arr.dtype]))
+    out += _field(8, 2, name.encode())
+    out += _field(9, 2, arr.tobytes())
+    return out
+
+
+def _enc_attr(name: str, v) -> bytes:
+    out = _field(1, 2, name.encode())
+    if isinstance(v, float):
+        out += _field(2, 5, struct.pack("<f", v)) + _field(20, 0, _enc_varint(1))
+    elif isinstance(v, bool) or isinstance(v, int):
+        out += _field(3, 0, _enc_varint(int(v))) + _field(20, 0, _enc_varint(2))
+    elif isinstance(v, str):
+        out += _field(4, 2, v.encode()) + _field(20, 0, _enc_varint(3))
+    elif isinstance(v, (list, tuple)) and v and isinstance(v[0], float):
+        out += b"".join(_field(7, 5, struct.pack("<f", x)) for x in v) + _field(20, 0, _enc_varint(6))
+    elif isinstance(v, (list, tuple)):
+        out += b"".join(_field(8, 0, _enc_varint(int(x))) for x in v) + _field(20, 0, _enc_varint(7))
+    else:
+        raise TypeError(f"attribute {name}: {type(v)}")
+    return out
+
+
+def _enc_value_info(name: str, shape, elem_type: int = 1) -> bytes:
+    dims = b"".join(_field(1, 2, _field(1, 0, _enc_varint(int(d))) if not isinstance(d, str) else _field(2, 2, d.encode())) for d in shape)
+    tensor_type = _field(1, 0, _enc_varint(elem_type)) + _field(2, 2, dims)
+    return _field(1, 2, name.encode()) + _field(2, 2, _field(1, 2, tensor_type))
+
+
+def save(path: str, nodes: list, initializers: dict, inputs: list, outputs: list, input_types: dict | None = None,
+         initializer_types: dict | None = None) -> None:
+    """Writes an ONNX file.  nodes: [{"op", "in", "out", "attrs"}]; inputs: [(name, shape)]; outputs: [name]."""
+    g = b""
+    for n in nodes:
+        body = b"".join(_field(1, 2, i.encode()) for i in n["in"]) + b"".join(_field(2, 2, o.encode()) for o in n["out"])
+        body += _field(4, 2, n["op"].encode())
+        body += b"".join(_field(5, 2, _enc_attr(k, v)) for k, v in n.get("attrs", {}).items())
+        g += _field(1, 2, body)
+    g += _field(2, 2, b"graph")
+    for k, v in initializers.items():
+        g += _field(5, 2, _enc_tensor(k, v, (initializer_types or {}).get(k)))
+    for name, shape in inputs:
+        g += _field(11, 2, _enc_value_info(name, shape, (input_types or {}).get(name, 1)))
+    for name in outputs:
+        g += _field(12, 2, _enc_value_info(name, []))
+    model = _field(1, 0, _enc_varint(8)) + _field(7, 2, g) + _field(8, 2, _field(2, 0, _enc_varint(17)))
+    with open(path, "wb") as f:
+        f.write(model)
