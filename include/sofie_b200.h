@@ -234,6 +234,25 @@ int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan);
 int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, void *workspace,
                             const sofie_b200_epilogue *ep);
 
+/* (No counterpart in the reference.)  The same convolution for hosts that forbid device allocation
+ * once they are configured -- fixed-memory-budget services such as online event filters, which carve up
+ * GPU memory at start-up and must not see a cudaMalloc (device-wide serialisation, late out-of-memory
+ * failures) from inside their event loop.  No plan, no workspace argument: the padded weights and the
+ * unfolded input go to a 16 MiB array that is part of the library image, so nothing is allocated or
+ * freed, on the device or by any library, in this call.
+ *   - Every GPU that loads the library holds those 16 MiB until the process exits.
+ *   - A convolution whose padded weights plus unfolded input ([groups][N][Ho*Wo][C/groups*R*S rounded
+ *     up to 16 bytes] elements) exceed 16 MiB returns SOFIE_B200_ERR_TOO_LARGE.
+ *   - The first call on each device looks the array's address up (cudaGetSymbolAddress, with that device
+ *     current) and caches it; make that first call before any stream capture begins.
+ *   - The array is shared by every call on the device and keeps the last call's bytes; a call writes all
+ *     it reads, so no clearing is needed, but calls that may overlap on the GPU (other streams, other
+ *     contexts) race on it.  Calls on one stream are safe.
+ * X, W ([K, C/groups, R, S] in x_dtype), Y and the epilogue vectors are device pointers as in
+ * sofie_b200_conv_enqueue; results are identical to the plan-based call. */
+int sofie_b200_conv_enqueue_noalloc(sofie_b200_ctx *ctx, const sofie_b200_conv_desc *desc, const void *X,
+                                    const void *W, void *Y, const sofie_b200_epilogue *ep);
+
 /* ---- memory-bound operators the fusion pass leaves ----------------------------------- */
 
 /* LayerNormalization over the last `cols` elements of each of `rows` rows

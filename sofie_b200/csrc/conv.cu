@@ -7,6 +7,8 @@
 // One unfold kernel and one batched contraction per group replace the reference's host loop of
 // per-image Im2ColKernel + blas.matmul launches (ROperator_Conv.hxx:1002-1103).  The K order
 // (c, r, s) is the reference's (ROperator_Conv.hxx:456-476), so weights need no permutation.
+#include <mutex>
+
 #include "gemm.cuh"
 
 struct sofie_b200_conv_plan {
@@ -205,3 +207,150 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
 }
 
 }  // extern "C"
+
+// -----------------------------------------------------------------------------------------------
+// Convolution for callers that must not allocate
+// -----------------------------------------------------------------------------------------------
+// Some hosts of this library run their inference loop under a rule of "no device allocation after
+// configuration": online event filters and other fixed-budget services partition GPU memory once,
+// at start-up, and treat any later cudaMalloc as a fault, because it serialises the device, can
+// fail from fragmentation hours into a run, and is not allowed from the callback contexts they
+// call us from.  The regular path needs two device buffers per convolution (the padded weights
+// owned by the plan, and the unfolded-input workspace the caller provides).  The entry point below
+// needs neither: both live in one fixed array that is part of the library image.
+//
+// Cost and limits: every GPU on which the library is loaded carries the array (16 MiB) from load to
+// exit, used or not.  A call whose padded weights plus unfolded input exceed it is refused.  All
+// calls on a device share the array, so two calls that can overlap on the GPU (different streams,
+// different contexts) race on it; calls on one stream are ordered and safe.  The array keeps the
+// previous call's bytes: nothing in it is assumed to be zero, each call writes every byte it later
+// reads (padding columns included).
+namespace sb200 {
+
+constexpr size_t kConvStaticScratchBytes = size_t(16) << 20;
+static __device__ __align__(256) unsigned char g_conv_static_scratch[kConvStaticScratchBytes];
+
+// In host code `g_conv_static_scratch` is only a handle for the symbol, not a device address.  The
+// address is looked up once per device, with that device current, and cached.
+constexpr int kMaxDevices = 64;
+static void *g_conv_static_ptr[kMaxDevices] = {};
+static std::mutex g_conv_static_mutex;
+
+static int conv_static_scratch(int device, unsigned char **out) {
+  if (device < 0 || device >= kMaxDevices) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: device index %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_conv_static_mutex);
+  if (!g_conv_static_ptr[device]) {
+    void *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_conv_static_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(SOFIE_B200_ERR_CUDA, "conv_enqueue_noalloc: cudaGetSymbolAddress failed on device %d: %s", device, cudaGetErrorString(e));
+    g_conv_static_ptr[device] = p;
+  }
+  *out = static_cast<unsigned char *>(g_conv_static_ptr[device]);
+  return 0;
+}
+
+}  // namespace sb200
+
+extern "C" int sofie_b200_conv_enqueue_noalloc(sofie_b200_ctx *ctx, const sofie_b200_conv_desc *desc, const void *X,
+                                               const void *W, void *Y, const sofie_b200_epilogue *ep) {
+  if (!ctx || !desc) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: NULL argument");
+  sofie_b200_conv_desc d = *desc;
+  if (d.groups < 1) d.groups = 1;
+  if (d.N < 0 || d.C < 1 || d.H < 1 || d.W < 1 || d.K < 1 || d.R < 1 || d.S < 1)
+    return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: bad extent");
+  if (d.C % d.groups || d.K % d.groups)
+    return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: channels %lld / filters %lld not divisible by groups %d", (long long)d.C, (long long)d.K, d.groups);
+  if (d.x_dtype != SOFIE_B200_F32 && d.x_dtype != SOFIE_B200_I8)
+    return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: input type %d not supported (F32, I8)", d.x_dtype);
+  int64_t Ho, Wo;
+  int rc = conv_out_shape(d, &Ho, &Wo);
+  if (rc) return rc;
+  if (d.N == 0) return 0;
+  if (!X || !W || !Y) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: NULL tensor");
+
+  const int es = dtype_size(d.x_dtype);
+  const int64_t cg = d.C / d.groups, kg = d.K / d.groups, pix = Ho * Wo;
+  const int64_t kdim = cg * d.R * d.S, vec = 16 / es;
+  const int64_t kpad = (kdim + vec - 1) / vec * vec;
+  const size_t w_bytes = (size_t)((d.K * kpad * es + 255) / 256 * 256);
+  const size_t x_bytes = (size_t)((int64_t)d.groups * d.N * pix * kpad * es);
+  if (w_bytes + x_bytes > kConvStaticScratchBytes)
+    return fail(SOFIE_B200_ERR_TOO_LARGE,
+                "conv_enqueue_noalloc: this convolution needs %zu bytes of scratch (padded weights %zu + unfolded input %zu); "
+                "the static scratch holds %zu bytes -- use the plan-based entry points with a caller workspace",
+                w_bytes + x_bytes, w_bytes, x_bytes, kConvStaticScratchBytes);
+
+  SB_CUDA(cudaSetDevice(ctx->device));
+  unsigned char *scratch = nullptr;
+  if ((rc = conv_static_scratch(ctx->device, &scratch))) return rc;
+  unsigned char *w_padded = scratch, *xcol = scratch + w_bytes;
+
+  // 1. weights to a 16-byte row pitch, 2. unfold the whole batch; both rewrite every byte the contraction reads
+  const long long wtotal = d.K * kpad;
+  const unsigned wgrid = (unsigned)std::min<long long>((wtotal + 255) / 256, (long long)ctx->sm_count * 16);
+  const long long xtotal = (long long)d.groups * d.N * pix * (kpad / vec);
+  const unsigned xgrid = (unsigned)std::min<long long>((xtotal + 255) / 256, (long long)ctx->sm_count * 32);
+  if (d.x_dtype == SOFIE_B200_F32) {
+    pad_weights_kernel<float><<<wgrid, 256, 0, ctx->stream>>>((const float *)W, (float *)w_padded, d.K, kdim, kpad);
+    unfold_kernel<float, 4><<<xgrid, 256, 0, ctx->stream>>>((const float *)X, (float *)xcol, d, Ho, Wo, cg, kdim, kpad, 0.f);
+  } else {
+    pad_weights_kernel<int8_t><<<wgrid, 256, 0, ctx->stream>>>((const int8_t *)W, (int8_t *)w_padded, d.K, kdim, kpad);
+    unfold_kernel<int8_t, 16><<<xgrid, 256, 0, ctx->stream>>>((const int8_t *)X, (int8_t *)xcol, d, Ho, Wo, cg, kdim, kpad, (int8_t)d.x_zero_point);
+  }
+  SB_CUDA(cudaGetLastError());
+  ctx->launches += 2;
+
+  // 3. the contraction, planned on the stack (no heap, no device memory)
+  sofie_b200_gemm_plan gp;
+  gp.ctx = ctx;
+  sofie_b200_gemm_desc &g = gp.desc;
+  g.M = kg; g.N = pix; g.K = kpad; g.batch = d.N;
+  g.trans_a = 0; g.trans_b = 1;
+  g.ab_dtype = d.x_dtype; g.y_dtype = d.y_dtype;
+  g.lda = kpad; g.ldb = kpad; g.ldy = pix;
+  g.stride_a = 0; g.stride_b = pix * kpad; g.stride_y = d.K * pix;
+  g.stride_c = 0; g.stride_r = d.K * pix;
+  g.precise = d.precise;
+  switch (d.y_dtype) {
+    case SOFIE_B200_F32: case SOFIE_B200_BF16: case SOFIE_B200_I8: case SOFIE_B200_U8: break;
+    case SOFIE_B200_I32:
+      if (d.x_dtype != SOFIE_B200_I8) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: I32 output needs I8 input");
+      break;
+    default: return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: output type %d not supported", d.y_dtype);
+  }
+  if (!(d.x_dtype == SOFIE_B200_F32 && d.precise != 0)) {
+    rc = umma_plan_init(&gp);
+    if (rc < 0) return rc;
+    gp.use_umma = (rc == 0);
+  }
+
+  sofie_b200_epilogue e{};
+  e.alpha = 1.f; e.beta = 1.f; e.out_scale = 1.f;
+  if (ep) {
+    if (ep->row_scale) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: row_scale has no meaning for a convolution");
+    e = *ep;
+    e.row_scale = ep->col_scale;  // output channels are accumulator rows, as in sofie_b200_conv_enqueue
+    e.col_scale = nullptr;
+    switch (ep->bias_mode) {
+      case SOFIE_B200_BIAS_NONE: case SOFIE_B200_BIAS_SCALAR_F32: break;
+      case SOFIE_B200_BIAS_COL_F32: e.bias_mode = SOFIE_B200_BIAS_ROW_F32; break;
+      case SOFIE_B200_BIAS_COL_I32: e.bias_mode = SOFIE_B200_BIAS_ROW_I32; break;
+      default: return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: bias_mode %d not supported for a convolution", ep->bias_mode);
+    }
+    e.ldr = pix;
+  }
+  const int ys = dtype_size(d.y_dtype);
+  for (int grp = 0; grp < d.groups; ++grp) {
+    sofie_b200_epilogue eg = e;
+    if (eg.row_scale) eg.row_scale += grp * kg;
+    if (eg.bias && eg.bias_mode != SOFIE_B200_BIAS_SCALAR_F32) eg.bias = (const char *)eg.bias + (size_t)grp * kg * 4;
+    if (eg.residual) eg.residual = (const char *)eg.residual + (size_t)grp * kg * pix * dtype_size(eg.residual_dtype);
+    const unsigned char *a = w_padded + (size_t)grp * kg * kpad * es;
+    const unsigned char *b = xcol + (size_t)grp * d.N * pix * kpad * es;
+    char *y = (char *)Y + (size_t)grp * kg * pix * ys;
+    rc = sofie_b200_gemm_enqueue(&gp, a, b, y, &eg);
+    if (rc) return rc;
+  }
+  return 0;
+}
