@@ -41,6 +41,8 @@ L2_BYTES = 126 * 1024 * 1024
 NCU_TRAFFIC_BYTES = {
     "qlinear_matmul_4096": 33.64e6 + 0.03e6,  # profiles/umma_gemm_i8_qlinear_matmul_4096.md
     "fp8_gemm_8192": None,
+    "layernorm_bf16_65536x512": None,
+    "softmax_bf16_524288x128": None,
 }
 
 
@@ -225,6 +227,7 @@ def load_oracle():
         subprocess.run(["make", "-C", str(ROOT / "oracle"), "oracle"], check=True, capture_output=True)
     lib = C.CDLL(str(so))
     lib.so_threads.restype = C.c_int
+    lib.so_set_threads(os.cpu_count() or 1)  # torchrun exports OMP_NUM_THREADS=1; the CPU arm gets every host core
     return lib
 
 
@@ -361,6 +364,115 @@ def run_ours(args, w) -> None:
         print(json.dumps(line), flush=True)
 
 
+class RowOp:
+    """LayerNormalization / Softmax over bf16 rows: the HBM-bound operators of the transformer configuration."""
+
+    def __init__(self, kind: str, rows: int, cols: int, name: str):
+        self.kind, self.rows, self.cols, self.name = kind, rows, cols, name
+        self.metric = f"{kind} bf16 {rows}x{cols} effective bandwidth"
+        self.unit, self.dtype = "GB/s", "bf16"
+        self.bytes_alg = 2.0 * rows * cols * 2  # read once + write once
+
+
+def run_rowop(args, w) -> None:
+    import torch
+    from sofie_b200 import lib as L
+    from sofie_b200 import replicas
+    from sofie_b200.ops import Context
+
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        lib = load_oracle()
+        rows = min(w.rows, 8192)
+        x = (np.random.default_rng(1).standard_normal((rows, w.cols)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+        y = np.zeros_like(x)
+        g, b = np.ones(w.cols, dtype=np.float32), np.zeros(w.cols, dtype=np.float32)
+        def cpu_step():
+            t0 = time.perf_counter()
+            if w.kind == "layernorm":
+                lib.so_layernorm(x.ctypes.data_as(C.c_void_p), y.ctypes.data_as(C.c_void_p), L.BF16, L.BF16, C.c_int64(rows), C.c_int64(w.cols),
+                                 g.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p), C.c_float(1e-5), None, None)
+            else:
+                lib.so_softmax(x.ctypes.data_as(C.c_void_p), y.ctypes.data_as(C.c_void_p), L.BF16, L.BF16, C.c_int64(rows), C.c_int64(w.cols), 0)
+            return time.perf_counter() - t0
+        for _ in range(args.warmup):
+            cpu_step()
+        t = sum(cpu_step() for _ in range(args.steps))
+        val = 2.0 * rows * w.cols * 2 * args.steps / t / 1e9
+        print(json.dumps({"impl": "reference", "metric": w.metric, "value": val, "unit": w.unit, "n_gpus": args.gpus, "steps": args.steps,
+                          "warmup": args.warmup, "ms_per_step": 1e3 * t / max(1, args.steps), "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": w.dtype, "data": "synthetic", "config": {"workload": w.name},
+                          "cpu_baseline": {"value": val, "unit": w.unit, "cores": 1, "kind": "port", "sample": f"each step = {rows} of {w.rows} rows"},
+                          "e2e": {"value": val, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+        return
+
+    rep = replicas.init_from_env("nccl")
+    torch.cuda.set_device(rep.local_rank)
+    dev = f"cuda:{rep.local_rank}"
+    ctx = Context(rep.local_rank)
+    nsets = int(max(3, np.ceil(1.6 * L2_BYTES / w.bytes_alg)))
+    xs = [torch.randn(w.rows, w.cols, device=dev).to(torch.bfloat16) for _ in range(nsets)]
+    ys = [torch.empty_like(x) for x in xs]
+    g, b = torch.ones(w.cols, device=dev), torch.zeros(w.cols, device=dev)
+
+    def step(i):
+        if w.kind == "layernorm":
+            ctx.layernorm(xs[i % nsets], ys[i % nsets], g, b, 1e-5)
+        else:
+            ctx.softmax(xs[i % nsets], ys[i % nsets])
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    ctx.sync()
+    sampler = ClockSampler(rep.local_rank)
+    replicas.barrier(rep)
+    torch.cuda.synchronize()
+    l0 = ctx.launches
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms_local = e0.elapsed_time(e1)
+    ms = replicas.max_over_ranks(rep, ms_local)
+    launches = ctx.launches - l0
+    value = rep.world * w.bytes_alg * args.steps / (ms * 1e-3) / 1e9
+    hx = xs[0].cpu().pin_memory()
+    hy = torch.empty_like(hx).pin_memory()
+    e2e_steps = max(3, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        xs[0].copy_(hx, non_blocking=True)
+        step(0)
+        hy.copy_(ys[0], non_blocking=True)
+        ctx.sync()
+        torch.cuda.synchronize()
+    t_e2e = replicas.max_over_ranks(rep, time.perf_counter() - t0)
+    if rep.is_root:
+        peaks = measured_peaks()
+        ach = w.bytes_alg / (ms_local / args.steps * 1e-3) / 1e9
+        print(json.dumps({"metric": w.metric, "value": value, "unit": w.unit, "n_gpus": rep.world, "steps": args.steps, "warmup": max(3, args.warmup),
+                          "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype,
+                          "data": "synthetic", "config": {"workload": w.name, "rows": w.rows, "cols": w.cols,
+                                                          "l2": f"{nsets} tensor pairs rotated ({nsets * w.bytes_alg / 2**20:.0f} MiB > 126 MiB L2)"},
+                          "clocks": clocks, "gpu_launches": int(launches),
+                          "e2e": {"value": rep.world * w.bytes_alg * e2e_steps / t_e2e / 1e9, "unit": w.unit,
+                                  "h2d_bytes_per_step": int(w.bytes_alg / 2), "d2h_bytes_per_step": int(w.bytes_alg / 2), "steps": e2e_steps},
+                          "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                                       "traffic": NCU_TRAFFIC_BYTES.get(w.name), "peak_source": f"hbm_gbs of {peaks['source']} MEASURED_PEAKS.json"}}),
+              flush=True)
+    ctx.close()
+    replicas.shutdown(rep)
+
+
+WORKLOADS["layernorm_bf16_65536x512"] = lambda: RowOp("layernorm", 65536, 512, "layernorm_bf16_65536x512")
+WORKLOADS["softmax_bf16_524288x128"] = lambda: RowOp("softmax", 524288, 128, "softmax_bf16_524288x128")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -370,7 +482,9 @@ def main() -> None:
     ap.add_argument("--workload", default="qlinear_matmul_4096", choices=sorted(WORKLOADS))
     args = ap.parse_args()
     w = WORKLOADS[args.workload]()
-    if args.impl == "reference":
+    if isinstance(w, RowOp):
+        run_rowop(args, w)
+    elif args.impl == "reference":
         run_reference(args, w)
     else:
         run_ours(args, w)

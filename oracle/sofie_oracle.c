@@ -19,6 +19,14 @@ int so_threads(void) {
 #endif
 }
 
+void so_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* ---------------------------------------------------------------------------------------------
  * element conversions
  * ------------------------------------------------------------------------------------------- */

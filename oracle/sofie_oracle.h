@@ -26,6 +26,7 @@ extern "C" {
 
 /* Number of threads the contraction loops use (OpenMP if compiled with it, else 1). */
 int so_threads(void);
+void so_set_threads(int n);
 
 /* Y = epilogue(op(A) x op(B)), batched; semantics of sofie_b200_gemm_desc / sofie_b200_epilogue.
  * Host pointers.  Gemm: ROperator_Gemm.hxx:419-741 + Gemm_Call (SOFIE_common_helpers.cxx:296-323):

@@ -250,8 +250,12 @@ static int launch_rows(sofie_b200_ctx *ctx, const void *x, void *y, long long ro
                        ((uintptr_t)y % (sizeof(TOut) * E > 16 ? 16 : sizeof(TOut) * E) == 0);
   const long long chunks = (cols + E - 1) / E;
   if (aligned && chunks <= 32 * 16) {
+    // Lanes per row: as few as keep <= 8 chunks (128 bytes) per lane, so that each lane has several
+    // independent 16-byte loads in flight and the reductions stay short; widened again when there
+    // are too few rows to fill the machine.
     int G = 4;
-    while (G < 32 && G < chunks) G <<= 1;
+    while (G < 32 && (chunks + G - 1) / G > 8) G <<= 1;
+    while (G < 32 && G < chunks && rows * G < (long long)ctx->sm_count * 2048) G <<= 1;
     const int ch = (int)((chunks + G - 1) / G);
     const int groups_per_cta = 256 / G;
     long long ctas = (rows + groups_per_cta - 1) / groups_per_cta;
