@@ -30,6 +30,8 @@ struct UmmaParams {
   int a_box_mn, b_box_mn;          // MN elements covered by one box of an MN-major operand
   int a_bcast, b_bcast;            // operand shared by the whole batch
   int vec_ok;                      // 16-byte vector stores of 32-column chunks are aligned
+  int pair;                        // 1: CTA-pair kernel (cluster of 2, tcgen05 cta_group::2, 256 x bn tile per pair)
+  int b_rows;                      // N extent of the B slice one CTA stages: bn, or bn/2 in pair mode
   EpiParams ep;
   int *status;
 };
@@ -64,6 +66,9 @@ namespace sb200 {
 // gemm_umma.cu
 int umma_plan_init(sofie_b200_gemm_plan *plan);          // 0 if the tcgen05 path applies, 1 if not, <0 error
 int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep);
+// gemm_umma2.cu (CTA-pair kernel)
+int umma_pair_set_smem(int kind, size_t smem_bytes);
+int umma_pair_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u);
 // gemm_simt.cu
 int simt_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep);
 }  // namespace sb200

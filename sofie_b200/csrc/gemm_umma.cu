@@ -22,223 +22,15 @@
 // memory, writes a DeviceStatus code to the ctx status word, and all roles fall through to the
 // common exit where tensor memory is freed.
 #include <cudaTypedefs.h>
+#include <cstdlib>
 #include <mutex>
 
 #include "gemm.cuh"
 #include "ptx.cuh"
+#include "umma_store.cuh"
 
 namespace sb200 {
 using namespace ptx;
-
-__device__ __forceinline__ void raise_abort(volatile int *abort_flag, int *status, int code) {
-  *abort_flag = 1;
-  atomicCAS(status, 0, code);
-}
-
-__device__ __forceinline__ void st_v4(void *p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  *reinterpret_cast<uint4 *>(p) = make_uint4(a, b, c, d);
-}
-
-// Applies the fused epilogue to one 32-column chunk of one accumulator row and stores it.
-//
-// The work is staged as passes over a register array, with every data-independent decision
-// (which scales exist, which activation, which output type) taken once per chunk OUTSIDE the
-// unrolled per-element loops: a warp cannot overlap instructions across a branch, so uniform
-// branches inside the element loop would serialise the whole epilogue.  Absent scales multiply
-// by 1.0f and an absent bias adds 0.0f; both are exact, so the value equals the documented
-// step-by-step formula (sofie_b200_epilogue) bit for bit.
-__device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t (&raw)[32], long long b, long long row,
-                                            int col0, int ncols, bool vec) {
-  const bool full = ncols == 32;
-  const long long off = b * ep.stride_y + row * ep.ldy + col0;
-
-  if (ep.y_dtype == SOFIE_B200_I32) {  // raw integer accumulator (+ int32 bias)
-    int a[32];
-#pragma unroll
-    for (int c = 0; c < 32; ++c) a[c] = (int)raw[c];
-    if (ep.bias_mode == SOFIE_B200_BIAS_COL_I32) {
-#pragma unroll
-      for (int c = 0; c < 32; ++c) a[c] += (full || c < ncols) ? ((const int *)ep.bias)[col0 + c] : 0;
-    } else if (ep.bias_mode == SOFIE_B200_BIAS_ROW_I32) {
-      const int br = ((const int *)ep.bias)[row];
-#pragma unroll
-      for (int c = 0; c < 32; ++c) a[c] += br;
-    }
-    int *y = (int *)ep.Y + off;
-    if (vec && full) {
-#pragma unroll
-      for (int c = 0; c < 32; c += 4) st_v4(y + c, a[c], a[c + 1], a[c + 2], a[c + 3]);
-    } else {
-#pragma unroll
-      for (int c = 0; c < 32; ++c)
-        if (c < ncols) y[c] = a[c];
-    }
-    return;
-  }
-
-  float v[32];
-  // 1. accumulator -> fp32
-  if (ep.acc_is_int) {
-    if (ep.bias_mode == SOFIE_B200_BIAS_COL_I32) {
-#pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = (float)((int)raw[c] + ((full || c < ncols) ? ((const int *)ep.bias)[col0 + c] : 0));
-    } else {
-      const int br = ep.bias_mode == SOFIE_B200_BIAS_ROW_I32 ? ((const int *)ep.bias)[row] : 0;
-#pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = (float)((int)raw[c] + br);
-    }
-  } else {
-#pragma unroll
-    for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(raw[c]);
-  }
-  // 2. scales, in the documented order: row, column, alpha
-  if (ep.row_scale) {
-    const float rs = ep.row_scale[row];
-#pragma unroll
-    for (int c = 0; c < 32; ++c) v[c] = __fmul_rn(v[c], rs);
-  }
-  if (ep.col_scale) {
-    if (full && ep.params_aligned) {
-#pragma unroll
-      for (int c = 0; c < 32; c += 4) {
-        const float4 s4 = *reinterpret_cast<const float4 *>(ep.col_scale + col0 + c);  // col0 % 32 == 0
-        v[c] = __fmul_rn(v[c], s4.x); v[c + 1] = __fmul_rn(v[c + 1], s4.y);
-        v[c + 2] = __fmul_rn(v[c + 2], s4.z); v[c + 3] = __fmul_rn(v[c + 3], s4.w);
-      }
-    } else {
-#pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = __fmul_rn(v[c], c < ncols ? ep.col_scale[col0 + c] : 1.f);
-    }
-  }
-  if (ep.alpha != 1.f) {
-#pragma unroll
-    for (int c = 0; c < 32; ++c) v[c] = __fmul_rn(v[c], ep.alpha);
-  }
-  // 3. additive terms
-  switch (ep.bias_mode) {
-    case SOFIE_B200_BIAS_COL_F32:
-      if (full && ep.params_aligned) {
-#pragma unroll
-        for (int c = 0; c < 32; c += 4) {
-          const float4 b4 = *reinterpret_cast<const float4 *>((const float *)ep.bias + col0 + c);
-          v[c] = __fadd_rn(v[c], b4.x); v[c + 1] = __fadd_rn(v[c + 1], b4.y);
-          v[c + 2] = __fadd_rn(v[c + 2], b4.z); v[c + 3] = __fadd_rn(v[c + 3], b4.w);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 32; ++c)
-          if (c < ncols) v[c] = __fadd_rn(v[c], ((const float *)ep.bias)[col0 + c]);
-      }
-      break;
-    case SOFIE_B200_BIAS_ROW_F32: {
-      const float br = ((const float *)ep.bias)[row];
-#pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = __fadd_rn(v[c], br);
-      break;
-    }
-    case SOFIE_B200_BIAS_SCALAR_F32: {
-      const float bs = ((const float *)ep.bias)[0];
-#pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = __fadd_rn(v[c], bs);
-      break;
-    }
-    case SOFIE_B200_BIAS_FULL_F32: {
-      const float *cr = (const float *)ep.bias + b * ep.stride_c + row * ep.ldc + col0;
-#pragma unroll
-      for (int c = 0; c < 32; ++c)
-        if (full || c < ncols) v[c] = __fadd_rn(v[c], __fmul_rn(ep.beta, cr[c]));
-      break;
-    }
-    default: break;
-  }
-  if (ep.residual) {
-    const long long roff = b * ep.stride_r + row * ep.ldr + col0;
-    if (ep.residual_dtype == SOFIE_B200_BF16) {
-      const __nv_bfloat16 *r = (const __nv_bfloat16 *)ep.residual + roff;
-#pragma unroll
-      for (int c = 0; c < 32; ++c)
-        if (full || c < ncols) v[c] = __fadd_rn(v[c], __bfloat162float(r[c]));
-    } else {
-      const float *r = (const float *)ep.residual + roff;
-#pragma unroll
-      for (int c = 0; c < 32; ++c)
-        if (full || c < ncols) v[c] = __fadd_rn(v[c], r[c]);
-    }
-  }
-  // 4. activation
-  switch (ep.act) {
-    case SOFIE_B200_ACT_NONE: break;
-    case SOFIE_B200_ACT_RELU:
-#pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_RELU, 0.f);
-      break;
-    case SOFIE_B200_ACT_GELU_ERF:
-#pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_GELU_ERF, 0.f);
-      break;
-    default:
-#pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], ep.act, ep.act_alpha);
-      break;
-  }
-  // 5. convert and store
-  if (ep.y_dtype == SOFIE_B200_F32) {
-    float *y = (float *)ep.Y + off;
-    if (vec && full) {
-#pragma unroll
-      for (int c = 0; c < 32; c += 4)
-        st_v4(y + c, __float_as_uint(v[c]), __float_as_uint(v[c + 1]), __float_as_uint(v[c + 2]), __float_as_uint(v[c + 3]));
-    } else {
-#pragma unroll
-      for (int c = 0; c < 32; ++c)
-        if (c < ncols) y[c] = v[c];
-    }
-  } else if (ep.y_dtype == SOFIE_B200_BF16) {
-    __nv_bfloat16 *y = (__nv_bfloat16 *)ep.Y + off;
-    if (vec && full) {
-#pragma unroll
-      for (int c = 0; c < 32; c += 8) {
-        uint32_t w[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          __nv_bfloat162 h2 = __floats2bfloat162_rn(v[c + 2 * u], v[c + 2 * u + 1]);
-          w[u] = *reinterpret_cast<uint32_t *>(&h2);
-        }
-        st_v4(y + c, w[0], w[1], w[2], w[3]);
-      }
-    } else {
-#pragma unroll
-      for (int c = 0; c < 32; ++c)
-        if (c < ncols) y[c] = __float2bfloat16_rn(v[c]);
-    }
-  } else {  // I8 / U8: ONNX rounding (half to even), zero point, saturate
-    const float lo = ep.y_dtype == SOFIE_B200_I8 ? -128.f : 0.f;
-    const float hi = ep.y_dtype == SOFIE_B200_I8 ? 127.f : 255.f;
-    const float zp = (float)ep.out_zp;
-    if (ep.out_scale != 1.f) {
-#pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = __fdiv_rn(v[c], ep.out_scale);
-    }
-    uint32_t q[32];
-#pragma unroll
-    for (int c = 0; c < 32; ++c) q[c] = (uint32_t)(int)fminf(fmaxf(rintf(v[c]) + zp, lo), hi) & 0xffu;
-    uint8_t *y = (uint8_t *)ep.Y + off;
-    if (vec && full) {
-#pragma unroll
-      for (int c = 0; c < 32; c += 16) {
-        uint32_t w[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          w[u] = q[c + 4 * u] | (q[c + 4 * u + 1] << 8) | (q[c + 4 * u + 2] << 16) | (q[c + 4 * u + 3] << 24);
-        st_v4(y + c, w[0], w[1], w[2], w[3]);
-      }
-    } else {
-#pragma unroll
-      for (int c = 0; c < 32; ++c)
-        if (c < ncols) y[c] = (uint8_t)q[c];
-    }
-  }
-}
 
 template <int KIND>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
@@ -449,6 +241,7 @@ static int encode_map(CUtensorMap *tm, int dtype, const void *base, uint64_t d0,
 
 static int pick_bn(long long N, long long tiles_m, long long batch, int sms, int min_bn) {
   // Per-tile time model: MMA time grows with bn, shared-memory operand traffic with 128 + bn.
+  // (`sms` is the number of concurrent tiles: SMs, or SM pairs in pair mode.)
   const int cand[4] = {256, 128, 64, 32};
   int best = 256;
   double best_cost = 1e300;
@@ -484,15 +277,28 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
 
   plan->kind = kind;
   u.M = (int)d.M; u.N = (int)d.N; u.K = (int)d.K; u.batch = (int)d.batch;
-  u.tiles_m = (int)((d.M + UMMA_BM - 1) / UMMA_BM);
-  // an MN-major B tile is made of 128-byte-wide TMA boxes, so bn*es must reach 128
-  u.bn = pick_bn(d.N, u.tiles_m, d.batch, plan->ctx->sm_count, d.trans_b ? 32 : 128 / es);
+  // CTA-pair mode: two SMs share a 256 x bn tile, each staging its 128 rows of A and half of the B
+  // slice, which cuts the operand bytes per SM and deepens the shared-memory ring.  Worth it when
+  // the problem has at least a wave of pair tiles; SOFIE_B200_PAIR=0/1 overrides the choice.
+  const int sms = plan->ctx->sm_count;
+  u.pair = 0;
+  {
+    const long long pair_tiles = ((d.M + 255) / 256) * ((d.N + 255) / 256) * d.batch;
+    (void)pair_tiles;
+    if (const char *e = getenv("SOFIE_B200_PAIR")) u.pair = (atoi(e) != 0 && d.M >= 256 && d.N >= 64) ? 1 : 0;
+  }
+  const int tile_m = u.pair ? 2 * UMMA_BM : UMMA_BM;
+  u.tiles_m = (int)((d.M + tile_m - 1) / tile_m);
+  // an MN-major B slice is made of 128-byte-wide TMA boxes, so the slice one CTA stages must reach 128 bytes
+  const int min_bn = (d.trans_b ? 32 : 128 / es) * (u.pair ? 2 : 1);
+  u.bn = pick_bn(d.N, u.tiles_m, d.batch, u.pair ? sms / 2 : sms, min_bn < 64 && u.pair ? 64 : min_bn);
+  u.b_rows = u.pair ? u.bn / 2 : u.bn;
   u.tiles_n = (int)((d.N + u.bn - 1) / u.bn);
   u.num_tiles = (long long)u.tiles_m * u.tiles_n * d.batch;
   u.kb_elems = UMMA_STAGE_K_BYTES / es;
   u.num_kb = (int)((d.K + u.kb_elems - 1) / u.kb_elems);
   u.a_stage_bytes = UMMA_BM * UMMA_STAGE_K_BYTES;
-  u.b_stage_bytes = u.bn * UMMA_STAGE_K_BYTES;
+  u.b_stage_bytes = u.b_rows * UMMA_STAGE_K_BYTES;
   u.tmem_cols = 32;
   while (u.tmem_cols < 2u * u.bn) u.tmem_cols <<= 1;
 
@@ -520,7 +326,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
          u.a_boxes = (UMMA_BM * es) / 128; u.a_box_bytes = panel_bytes; u.a_box_mn = 128 / es; }
   if (!u.b_mn) { u.b_desc_lo = 1u << 16; u.b_kadv = 32u >> 4; u.b_boxes = 1; u.b_box_bytes = u.b_stage_bytes; u.b_box_mn = 0; }
   else { u.b_desc_lo = ((panel_bytes >> 4) & 0x3fffu) << 16; u.b_kadv = (k_rows_per_mma * 128u) >> 4;
-         u.b_boxes = (u.bn * es) / 128; u.b_box_bytes = panel_bytes; u.b_box_mn = 128 / es;
+         u.b_boxes = (u.b_rows * es) / 128; u.b_box_bytes = panel_bytes; u.b_box_mn = 128 / es;
          if (u.b_boxes < 1) return 1; }
 
   // Instruction descriptor: D format [4,6), A format [7,10), B format [10,13), A major bit 15,
@@ -533,14 +339,16 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
     default: cfmt = 1; abfmt = 2; break;         // F32 accumulate, TF32
   }
   u.idesc = (cfmt << 4) | (abfmt << 7) | (abfmt << 10) | ((uint32_t)u.a_mn << 15) | ((uint32_t)u.b_mn << 16) |
-            ((uint32_t)(u.bn >> 3) << 17) | ((uint32_t)(UMMA_BM >> 4) << 24);
+            ((uint32_t)(u.bn >> 3) << 17) | ((uint32_t)(tile_m >> 4) << 24);
 
   const int ys = dtype_size(d.y_dtype);
   u.vec_ok = ((d.ldy * ys) % 16 == 0) && ((d.stride_y * ys) % 16 == 0);
   u.status = plan->ctx->d_status;
 
   long long grid = u.num_tiles < plan->ctx->sm_count ? u.num_tiles : plan->ctx->sm_count;
+  if (u.pair) grid = 2 * (u.num_tiles < sms / 2 ? u.num_tiles : sms / 2);
   plan->grid = (int)grid;
+  if (u.pair) return umma_pair_set_smem(kind, plan->smem_bytes);
 
   cudaError_t e = cudaSuccess;
   switch (kind) {
@@ -580,7 +388,7 @@ static int build_maps(sofie_b200_gemm_plan *plan, const void *A, const void *B) 
     if (!u.b_mn) {
       uint64_t s2 = d.batch > 1 && !u.b_bcast ? (uint64_t)d.stride_b * es : (uint64_t)d.N * d.ldb * es;
       rc = encode_map(&plan->tm_b, d.ab_dtype, B, (uint64_t)d.K, (uint64_t)d.N, nb, (uint64_t)d.ldb * es, s2,
-                      (uint32_t)u.kb_elems, (uint32_t)u.bn);
+                      (uint32_t)u.kb_elems, (uint32_t)u.b_rows);
     } else {
       uint64_t s2 = d.batch > 1 && !u.b_bcast ? (uint64_t)d.stride_b * es : (uint64_t)d.K * d.ldb * es;
       rc = encode_map(&plan->tm_b, d.ab_dtype, B, (uint64_t)d.N, (uint64_t)d.K, nb, (uint64_t)d.ldb * es, s2,
@@ -598,6 +406,7 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
   UmmaParams u = plan->up;
   u.ep = ep;
   if (((uintptr_t)ep.Y % 16) != 0) u.vec_ok = 0;
+  if (u.pair) return umma_pair_launch(plan, u);
   cudaStream_t st = plan->ctx->stream;
   dim3 grid(plan->grid), block(UMMA_THREADS);
   switch (plan->kind) {

@@ -73,9 +73,29 @@ __device__ __forceinline__ float group_max(float v, int G) {
   return v;
 }
 
+// A 16-byte chunk kept as loaded (bf16 stays packed: two values per register), unpacked at each use.
+// Holding the row packed halves the registers a lane needs, which doubles the CTAs per SM and with
+// them the bytes in flight -- the kernel is bound by memory latency, not by arithmetic.
+__device__ __forceinline__ uint4 ld_raw16(const void *p) { return *reinterpret_cast<const uint4 *>(p); }
+template <typename T> __device__ __forceinline__ void unpack16(const uint4 &r, float *v);
+template <> __device__ __forceinline__ void unpack16<float>(const uint4 &r, float *v) {
+  v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y); v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
+}
+template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4 &r, float *v) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <typename T> __device__ __forceinline__ uint4 fill16(bool minus_inf);
+template <> __device__ __forceinline__ uint4 fill16<float>(bool mi) { const uint32_t u = mi ? 0xff800000u : 0u; return make_uint4(u, u, u, u); }
+template <> __device__ __forceinline__ uint4 fill16<__nv_bfloat16>(bool mi) { const uint32_t u = mi ? 0xff80ff80u : 0u; return make_uint4(u, u, u, u); }
+
 // MODE 0: LayerNorm, 1: Softmax, 2: LogSoftmax.  CH = 16-byte chunks cached per lane.
 template <typename TIn, typename TOut, int CH, int MODE>
-__global__ void __launch_bounds__(256) row_group_kernel(const TIn *__restrict__ x, TOut *__restrict__ y, long long rows,
+__global__ void __launch_bounds__(256, (MODE == 0 ? (CH >= 16 ? 2 : (CH >= 8 && sizeof(TIn) == 4 ? 3 : 4)) : (CH >= 8 ? 2 : 3))) row_group_kernel(const TIn *__restrict__ x, TOut *__restrict__ y, long long rows,
                                                         int cols, int G, const float *__restrict__ scale,
                                                         const float *__restrict__ bias, float eps,
                                                         float *__restrict__ mean_out, float *__restrict__ invstd_out) {
@@ -92,30 +112,31 @@ __global__ void __launch_bounds__(256) row_group_kernel(const TIn *__restrict__ 
     const long long row = gid0 + it * gstride;
     const bool live = row < rows;
     const TIn *xr = x + row * (long long)cols;
-    float v[CH][E];
+    uint4 r[CH];
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
       const int col = (c * G + gl) * E;
-      if (live && col < cols) Vec16<TIn>::load(xr + col, v[c]);
-      else {
-#pragma unroll
-        for (int e = 0; e < E; ++e) v[c][e] = MODE == 0 ? 0.f : -INFINITY;
-      }
+      r[c] = (live && col < cols) ? ld_raw16(xr + col) : fill16<TIn>(MODE != 0);
     }
     if constexpr (MODE == 0) {
       float s = 0.f;
 #pragma unroll
-      for (int c = 0; c < CH; ++c)
+      for (int c = 0; c < CH; ++c) {
+        float v[E];
+        unpack16<TIn>(r[c], v);
 #pragma unroll
-        for (int e = 0; e < E; ++e) s += v[c][e];
+        for (int e = 0; e < E; ++e) s += v[e];
+      }
       const float mean = group_sum(s, G) * inv_n;
       float q = 0.f;
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
         const int col = (c * G + gl) * E;
         if (col < cols) {
+          float v[E];
+          unpack16<TIn>(r[c], v);
 #pragma unroll
-          for (int e = 0; e < E; ++e) { float d = v[c][e] - mean; q += d * d; }
+          for (int e = 0; e < E; ++e) { float d = v[e] - mean; q += d * d; }
         }
       }
       const float var = group_sum(q, G) * inv_n;
@@ -126,12 +147,20 @@ __global__ void __launch_bounds__(256) row_group_kernel(const TIn *__restrict__ 
         for (int c = 0; c < CH; ++c) {
           const int col = (c * G + gl) * E;
           if (col < cols) {
-            float o[E];
+            float v[E], o[E], sc[E], bi[E];
+            unpack16<TIn>(r[c], v);
+#pragma unroll
+            for (int e = 0; e < E; e += 4) {  // scale / bias: 128-bit loads (cols % E == 0 and 16-byte aligned, checked by the host)
+              const float4 s4 = scale ? *reinterpret_cast<const float4 *>(scale + col + e) : make_float4(1.f, 1.f, 1.f, 1.f);
+              const float4 b4 = bias ? *reinterpret_cast<const float4 *>(bias + col + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+              sc[e] = s4.x; sc[e + 1] = s4.y; sc[e + 2] = s4.z; sc[e + 3] = s4.w;
+              bi[e] = b4.x; bi[e + 1] = b4.y; bi[e + 2] = b4.z; bi[e + 3] = b4.w;
+            }
 #pragma unroll
             for (int e = 0; e < E; ++e) {
-              const float dlt = v[c][e] - mean;  // scale * invStd * (x - mean) + bias, left to right
-              float t = scale ? (scale[col + e] * inv) * dlt : inv * dlt;
-              if (bias) t += bias[col + e];
+              const float dlt = v[e] - mean;  // scale * invStd * (x - mean) + bias, left to right
+              float t = scale ? (sc[e] * inv) * dlt : inv * dlt;
+              if (bias) t += bi[e];
               o[e] = t;
             }
             store_chunk_as<TOut, E>(yr + col, o);
@@ -143,11 +172,15 @@ __global__ void __launch_bounds__(256) row_group_kernel(const TIn *__restrict__ 
         }
       }
     } else {
+      // Softmax keeps the row unpacked: exp(x - max) is computed once and reused for the output
+      float v[CH][E];
       float m = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < CH; ++c)
+      for (int c = 0; c < CH; ++c) {
+        unpack16<TIn>(r[c], v[c]);
 #pragma unroll
         for (int e = 0; e < E; ++e) m = fmaxf(m, v[c][e]);
+      }
       m = group_max(m, G);
       float s = 0.f;
 #pragma unroll
@@ -162,7 +195,7 @@ __global__ void __launch_bounds__(256) row_group_kernel(const TIn *__restrict__ 
         }
       }
       s = group_sum(s, G);
-      const float r = MODE == 1 ? 1.f / s : logf(s);
+      const float rr = MODE == 1 ? 1.f / s : logf(s);
       if (live) {
         TOut *yr = y + row * (long long)cols;
 #pragma unroll
@@ -171,7 +204,7 @@ __global__ void __launch_bounds__(256) row_group_kernel(const TIn *__restrict__ 
           if (col < cols) {
             float o[E];
 #pragma unroll
-            for (int e = 0; e < E; ++e) o[e] = MODE == 1 ? v[c][e] * r : v[c][e] - r;
+            for (int e = 0; e < E; ++e) o[e] = MODE == 1 ? v[c][e] * rr : v[c][e] - rr;
             store_chunk_as<TOut, E>(yr + col, o);
           }
         }
@@ -246,7 +279,7 @@ static int launch_rows(sofie_b200_ctx *ctx, const void *x, void *y, long long ro
                        const float *bias, float eps, float *mean_out, float *invstd_out) {
   constexpr int E = Vec16<TIn>::E;
   cudaStream_t st = ctx->stream;
-  const bool aligned = (cols % E == 0) && ((uintptr_t)x % 16 == 0) &&
+  const bool aligned = (cols % E == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)scale % 16 == 0) && ((uintptr_t)bias % 16 == 0) &&
                        ((uintptr_t)y % (sizeof(TOut) * E > 16 ? 16 : sizeof(TOut) * E) == 0);
   const long long chunks = (cols + E - 1) / E;
   if (aligned && chunks <= 32 * 16) {
