@@ -297,7 +297,13 @@ int sofie_b200_dequantize_enqueue(sofie_b200_ctx *ctx, const void *q, float *x, 
                                   const float *scale, const int32_t *zero_point, int64_t channels,
                                   int64_t inner);
 
-/* Type conversion between F32, BF16 and F8E4M3 (saturating round-to-nearest-even), with an
+/* Transpose (ROperator_Transpose, core/inc/SOFIE/operators/ROperator_Transpose.hxx:32-36): output dimension d
+ * is input dimension perm[d]; rank 1..4, any element type (moved as opaque words).  The head split / merge
+ * of attention ([B,S,H,D] <-> [B,H,S,D]) keeps the innermost dimension and runs on 16-byte vectors. */
+int sofie_b200_transpose_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t dtype, int32_t rank,
+                                 const int64_t *in_shape, const int32_t *perm);
+
+/* Type conversion between F32, BF16 and F8E4M3 (saturating round-to-nearest-even; I8 as a source too), with an
  * optional per-row scale: y[r,c] = cvt(x[r,c] / row_scale[r]) (row_scale may be NULL). */
 int sofie_b200_convert_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t x_dtype, int32_t y_dtype,
                                int64_t rows, int64_t cols, const float *row_scale);

@@ -151,14 +151,13 @@ int sofie_b200_gemm_plan_create(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc 
     if (rc < 0) { delete plan; return rc; }
     plan->use_umma = (rc == 0);
   }
-  ctx->live_plans++;
   *out = plan;
   return 0;
 }
 
 int sofie_b200_gemm_plan_destroy(sofie_b200_gemm_plan *plan) {
   if (!plan) return 0;
-  plan->ctx->live_plans--;
+  // the plan holds no reference into the ctx that needs undoing: a plan may be destroyed after its ctx
   delete plan;
   return 0;
 }

@@ -57,7 +57,6 @@ struct sofie_b200_ctx {
   // staging for the *_host helpers (grown on demand)
   void *stage[3] = {nullptr, nullptr, nullptr};
   size_t stage_bytes[3] = {0, 0, 0};
-  int live_plans = 0;
 };
 
 namespace sb200 {

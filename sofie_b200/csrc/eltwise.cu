@@ -163,6 +163,7 @@ template <typename T> __device__ __forceinline__ float cv_ld(const T *p);
 template <> __device__ __forceinline__ float cv_ld<float>(const float *p) { return *p; }
 template <> __device__ __forceinline__ float cv_ld<__nv_bfloat16>(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
 template <> __device__ __forceinline__ float cv_ld<__nv_fp8_e4m3>(const __nv_fp8_e4m3 *p) { return (float)*p; }
+template <> __device__ __forceinline__ float cv_ld<int8_t>(const int8_t *p) { return (float)*p; }
 template <typename T> __device__ __forceinline__ void cv_st(T *p, float v);
 template <> __device__ __forceinline__ void cv_st<float>(float *p, float v) { *p = v; }
 template <> __device__ __forceinline__ void cv_st<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
@@ -191,6 +192,28 @@ static int convert_to(sofie_b200_ctx *ctx, const void *x, void *y, int yd, long 
     default: return fail(SOFIE_B200_ERR_INVALID, "convert_enqueue: output type %d not supported", yd);
   }
   return 0;
+}
+
+// ---- Transpose (rank <= 4 permutation) --------------------------------------------------------------
+// y[o0,o1,o2,o3] = x[...] with output dimension d taken from input dimension perm[d].  Elements are
+// moved as opaque words of `es` bytes; when the innermost dimension stays innermost the copy runs on
+// 16-byte vectors (contiguous runs on both sides), otherwise element by element with coalesced writes.
+struct PermuteParams {
+  long long out_dim[4];
+  long long in_stride[4];  // stride (in units) of the input dimension feeding each output dimension
+  long long total;         // units to move
+};
+
+template <typename U>
+__global__ void __launch_bounds__(256) permute_kernel(const U *__restrict__ x, U *__restrict__ y, PermuteParams p) {
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long long)gridDim.x * blockDim.x;
+  for (long long i = tid; i < p.total; i += nth) {
+    long long r = i;
+    const long long i3 = r % p.out_dim[3]; r /= p.out_dim[3];
+    const long long i2 = r % p.out_dim[2]; r /= p.out_dim[2];
+    const long long i1 = r % p.out_dim[1]; r /= p.out_dim[1];
+    y[i] = x[r * p.in_stride[0] + i1 * p.in_stride[1] + i2 * p.in_stride[2] + i3 * p.in_stride[3]];
+  }
 }
 
 }  // namespace sb200
@@ -297,6 +320,48 @@ int sofie_b200_dequantize_enqueue(sofie_b200_ctx *ctx, const void *q, float *x, 
   SB_LAUNCHED();
 }
 
+int sofie_b200_transpose_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t dtype, int32_t rank,
+                                 const int64_t *in_shape, const int32_t *perm) {
+  SB_PRELUDE("transpose_enqueue");
+  if (rank < 1 || rank > 4 || !in_shape || !perm) return fail(SOFIE_B200_ERR_INVALID, "transpose_enqueue: rank 1..4 with shape and permutation expected");
+  const int es = dtype_size(dtype);
+  if (!es) return fail(SOFIE_B200_ERR_INVALID, "transpose_enqueue: type %d unknown", dtype);
+  // left-pad to rank 4
+  long long ishape[4] = {1, 1, 1, 1}, istride[4];
+  int pm[4] = {0, 1, 2, 3};
+  const int pad = 4 - rank;
+  bool seen[4] = {false, false, false, false};
+  for (int d = 0; d < rank; ++d) {
+    if (in_shape[d] < 0 || perm[d] < 0 || perm[d] >= rank || seen[perm[d]]) return fail(SOFIE_B200_ERR_INVALID, "transpose_enqueue: bad shape or permutation");
+    seen[perm[d]] = true;
+    ishape[pad + d] = in_shape[d];
+    pm[pad + d] = pad + perm[d];
+  }
+  istride[3] = 1;
+  for (int d = 2; d >= 0; --d) istride[d] = istride[d + 1] * ishape[d + 1];
+  PermuteParams p;
+  long long total = 1;
+  for (int d = 0; d < 4; ++d) { p.out_dim[d] = ishape[pm[d]]; p.in_stride[d] = istride[pm[d]]; total *= p.out_dim[d]; }
+  if (total == 0) return 0;
+  if (!x || !y) return fail(SOFIE_B200_ERR_INVALID, "transpose_enqueue: NULL tensor");
+  // innermost dimension unchanged: move 16-byte words when everything is aligned to them
+  const long long inner_bytes = p.out_dim[3] * es;
+  if (pm[3] == 3 && inner_bytes % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
+    const long long w = 16 / es;
+    p.out_dim[3] /= w;
+    for (int d = 0; d < 3; ++d) p.in_stride[d] /= w;
+    p.total = total / w;
+    permute_kernel<uint4><<<grid_for(ctx, p.total, 256), 256, 0, ctx->stream>>>((const uint4 *)x, (uint4 *)y, p);
+  } else {
+    p.total = total;
+    const unsigned g = grid_for(ctx, total, 256);
+    if (es == 1) permute_kernel<uint8_t><<<g, 256, 0, ctx->stream>>>((const uint8_t *)x, (uint8_t *)y, p);
+    else if (es == 2) permute_kernel<uint16_t><<<g, 256, 0, ctx->stream>>>((const uint16_t *)x, (uint16_t *)y, p);
+    else permute_kernel<uint32_t><<<g, 256, 0, ctx->stream>>>((const uint32_t *)x, (uint32_t *)y, p);
+  }
+  SB_LAUNCHED();
+}
+
 int sofie_b200_convert_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t x_dtype, int32_t y_dtype,
                                int64_t rows, int64_t cols, const float *row_scale) {
   SB_PRELUDE("convert_enqueue");
@@ -308,6 +373,7 @@ int sofie_b200_convert_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int3
     case SOFIE_B200_F32: rc = convert_to<float>(ctx, x, y, y_dtype, rows, cols, row_scale); break;
     case SOFIE_B200_BF16: rc = convert_to<__nv_bfloat16>(ctx, x, y, y_dtype, rows, cols, row_scale); break;
     case SOFIE_B200_F8E4M3: rc = convert_to<__nv_fp8_e4m3>(ctx, x, y, y_dtype, rows, cols, row_scale); break;
+    case SOFIE_B200_I8: rc = convert_to<int8_t>(ctx, x, y, y_dtype, rows, cols, row_scale); break;
     default: return fail(SOFIE_B200_ERR_INVALID, "convert_enqueue: input type %d not supported", x_dtype);
   }
   if (rc) return rc;

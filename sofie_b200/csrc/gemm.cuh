@@ -14,6 +14,8 @@ struct UmmaParams {
   int M, N, K, batch;
   int tiles_m, tiles_n;
   long long num_tiles;
+  long long split_from, num_items;  // work items: tiles below split_from whole, the rest as two N halves each
+  uint32_t idesc_half;              // instruction descriptor with N = bn/2
   int num_kb;          // K blocks of kb_elems elements
   int kb_elems;        // K elements per stage (128 bytes / element size)
   int bn;              // N extent of the tile and of each MMA (32, 64, 128 or 256)
@@ -68,6 +70,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan);          // 0 if the tcgen05 pat
 int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep);
 // gemm_umma2.cu (CTA-pair kernel)
 int umma_pair_set_smem(int kind, size_t smem_bytes);
+int umma_pair_max_clusters(int kind, size_t smem_bytes, int *out);
 int umma_pair_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u);
 // gemm_simt.cu
 int simt_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep);

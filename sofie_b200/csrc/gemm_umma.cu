@@ -32,6 +32,21 @@
 namespace sb200 {
 using namespace ptx;
 
+// Work items: whole tiles first; the tiles of a short last wave are split into two N halves so that
+// twice as many SMs share them (each half is an MMA of N = bn/2 into the same accumulator columns).
+__device__ __forceinline__ void decode_item(const UmmaParams &p, long long w, long long &tile, int &n_off, int &n_len,
+                                            uint32_t &idesc) {
+  if (w < p.split_from) {
+    tile = w; n_off = 0; n_len = p.bn; idesc = p.idesc;
+  } else {
+    const long long x = w - p.split_from;
+    tile = p.split_from + (x >> 1);
+    n_len = p.bn >> 1;
+    n_off = (int)(x & 1) * n_len;
+    idesc = p.idesc_half;
+  }
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
@@ -85,11 +100,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      for (long long w = blockIdx.x; w < p.num_items && ok; w += gridDim.x) {
+        long long t; int n_off, n_len; uint32_t idesc;
+        decode_item(p, w, t, n_off, n_len, idesc);
         const int b = (int)(t / tiles_per_batch);
         const int r = (int)(t % tiles_per_batch);
         const int m0 = (r % p.tiles_m) * UMMA_BM;
-        const int n0 = (r / p.tiles_m) * p.bn;
+        const int n0 = (r / p.tiles_m) * p.bn + n_off;  // a half item still loads a full-width B slice
         const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
@@ -129,7 +146,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      for (long long w = blockIdx.x; w < p.num_items && ok; w += gridDim.x) {
+        long long t; int n_off, n_len; uint32_t idesc;
+        decode_item(p, w, t, n_off, n_len, idesc);
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) {
           raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_EMPTY);
           break;
@@ -151,7 +170,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           for (int k = 0; k < 4; ++k) {
             const uint64_t ad = ((uint64_t)p.a_desc_hi << 32) | (uint64_t)(a_lo + k * p.a_kadv);
             const uint64_t bd = ((uint64_t)p.b_desc_hi << 32) | (uint64_t)(b_lo + k * p.b_kadv);
-            umma<KIND>(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+            umma<KIND>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           tc_commit(bar_empty + 8 * stage);  // stage may be refilled once these MMAs have read it
           if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
@@ -165,11 +184,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     // ------------------------------ epilogue -----------------------------------------
     const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
     uint32_t acc = 0, acc_phase = 0;
-    for (long long t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+    for (long long w = blockIdx.x; w < p.num_items; w += gridDim.x) {
+      long long t; int n_off, n_len; uint32_t idesc;
+      decode_item(p, w, t, n_off, n_len, idesc);
       const int b = (int)(t / tiles_per_batch);
       const int r = (int)(t % tiles_per_batch);
       const int m0 = (r % p.tiles_m) * UMMA_BM;
-      const int n0 = (r / p.tiles_m) * p.bn;
+      const int n0 = (r / p.tiles_m) * p.bn + n_off;
       if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
         raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_FULL);
         break;
@@ -177,7 +198,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * p.bn;
-      for (int c = 0; c < p.bn; c += 32) {
+      for (int c = 0; c < n_len; c += 32) {
         if (n0 + c >= p.N) break;  // warp-uniform
         uint32_t raw[32];
         tmem_ld_x32(taddr + c, raw);
@@ -345,10 +366,31 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.vec_ok = ((d.ldy * ys) % 16 == 0) && ((d.stride_y * ys) % 16 == 0);
   u.status = plan->ctx->d_status;
 
+  // Short last wave: split its tiles in two N halves (see decode_item).  Only when at least one full wave
+  // precedes it and the halves still fit one wave.
+  u.split_from = u.num_tiles;
+  u.num_items = u.num_tiles;
+  u.idesc_half = (u.idesc & ~(0x3fu << 17)) | ((uint32_t)(u.bn >> 4) << 17);
+  if (!u.pair && u.bn >= 64 && u.num_tiles > sms) {
+    const long long tail = u.num_tiles % sms;
+    if (tail > 0 && 2 * tail <= sms && !getenv("SOFIE_B200_NO_TAIL_SPLIT")) {
+      u.split_from = u.num_tiles - tail;
+      u.num_items = u.num_tiles + tail;
+    }
+  }
   long long grid = u.num_tiles < plan->ctx->sm_count ? u.num_tiles : plan->ctx->sm_count;
   if (u.pair) grid = 2 * (u.num_tiles < sms / 2 ? u.num_tiles : sms / 2);
   plan->grid = (int)grid;
-  if (u.pair) return umma_pair_set_smem(kind, plan->smem_bytes);
+  if (u.pair) {
+    int rc = umma_pair_set_smem(kind, plan->smem_bytes);
+    if (rc) return rc;
+    int clusters = 0;
+    if ((rc = umma_pair_max_clusters(kind, plan->smem_bytes, &clusters))) return rc;
+    if (clusters < 1) return 1;
+    if (getenv("SOFIE_B200_DEBUG")) fprintf(stderr, "[sofie_b200] pair kernel: %d CTA pairs resident at once (%d SMs)\n", clusters, sms);
+    if (plan->grid > 2 * clusters) plan->grid = 2 * clusters;
+    return 0;
+  }
 
   cudaError_t e = cudaSuccess;
   switch (kind) {

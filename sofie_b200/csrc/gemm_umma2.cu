@@ -220,6 +220,31 @@ int umma_pair_set_smem(int kind, size_t smem_bytes) {
   return 0;
 }
 
+// How many CTA pairs the device can hold at once with this much shared memory: the persistent tile
+// schedule needs every pair of the grid resident from the start.
+int umma_pair_max_clusters(int kind, size_t smem_bytes, int *out) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2, 1, 1);
+  cfg.blockDim = dim3(UMMA_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  cudaError_t e = cudaSuccess;
+  switch (kind) {
+    case KIND_I8: e = cudaOccupancyMaxActiveClusters(&n, umma_pair_gemm_kernel<KIND_I8>, &cfg); break;
+    case KIND_F8: e = cudaOccupancyMaxActiveClusters(&n, umma_pair_gemm_kernel<KIND_F8>, &cfg); break;
+    case KIND_F16: e = cudaOccupancyMaxActiveClusters(&n, umma_pair_gemm_kernel<KIND_F16>, &cfg); break;
+    default: e = cudaOccupancyMaxActiveClusters(&n, umma_pair_gemm_kernel<KIND_TF32>, &cfg); break;
+  }
+  if (e != cudaSuccess) return fail(SOFIE_B200_ERR_CUDA, "cudaOccupancyMaxActiveClusters: %s", cudaGetErrorString(e));
+  *out = n;
+  return 0;
+}
+
 int umma_pair_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u) {
   // the cluster shape is part of the kernel (__cluster_dims__), so a plain launch forms the pairs
   cudaStream_t st = plan->ctx->stream;

@@ -114,6 +114,12 @@ class Context:
                                                         _ptr(scale), _ptr(zero_point), channels, inner),
                 "dequantize_enqueue")
 
+    def transpose(self, x, y, perm):
+        shape = (C.c_int64 * x.dim())(*x.shape)
+        pm = (C.c_int32 * x.dim())(*perm)
+        L.check(self._lib.sofie_b200_transpose_enqueue(self._h, _ptr(x), _ptr(y), dtype_code(x.dtype), x.dim(), shape, pm),
+                "transpose_enqueue")
+
     def convert(self, x, y, row_scale=None):
         cols = x.shape[-1]
         rows = x.numel() // cols if cols else 0
