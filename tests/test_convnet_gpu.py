@@ -1,0 +1,104 @@
+"""Conv-net configuration (8 Conv3x3 layers 64-64-128-128-256-256-512-512, strides 1,2,1,2,1,2,1,2, each with a
+folded BatchNormalization and Relu, global average pool, Gemm 512 -> 1000) at a reduced batch and image size,
+in its fp32 and per-channel int8 (QLinearConv) variants, through the C ABI against the CPU restatement.
+fp32: 1e-5 relative with an rms floor per layer output chain end; int8: every layer bit-exact.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import graph_runner as gr
+from oracle_api import Oracle
+from sofie_b200 import lib as L
+from test_gpu_parity import run_conv, run_gemm, close_f32
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+CHANNELS = [3, 64, 64, 128, 128, 256, 256, 512, 512]
+STRIDES = [1, 2, 1, 2, 1, 2, 1, 2]
+BATCH, IMG, CLASSES = 2, 32, 1000
+
+
+def geometry(stride):
+    return dict(pads=[1, 1, 1, 1], strides=[stride, stride], dil=[1, 1], group=1)
+
+
+def out_hw(ctx, d):
+    ho, wo = C.c_int64(), C.c_int64()
+    assert ctx._lib.sofie_b200_conv_out_shape(C.byref(d), C.byref(ho), C.byref(wo)) == 0
+    return ho.value, wo.value
+
+
+@pytest.fixture(scope="module")
+def ctx(b200_lib):
+    from sofie_b200.ops import Context
+    c = Context(0)
+    yield c
+    c.close()
+
+
+def make_fp32_net(rng):
+    layers = []
+    for i in range(8):
+        cin, cout = CHANNELS[i], CHANNELS[i + 1]
+        w = (rng.standard_normal((cout, cin, 3, 3)) * np.sqrt(2.0 / (cin * 9))).astype(np.float32)   # He-normal
+        gamma, beta = (rng.random(cout) + 0.5).astype(np.float32), (rng.standard_normal(cout) * 0.1).astype(np.float32)
+        mean, var = (rng.standard_normal(cout) * 0.1).astype(np.float32), (rng.random(cout) + 0.5).astype(np.float32)
+        scale = (gamma / np.sqrt(var + np.float32(1e-5))).astype(np.float32)      # BatchNormalization folded:
+        shift = (beta - mean * scale).astype(np.float32)                           # y*scale + shift per channel
+        layers.append((w, scale, shift))
+    fc_w = (rng.standard_normal((512, CLASSES)) * np.sqrt(2.0 / 512)).astype(np.float32)
+    fc_b = np.zeros(CLASSES, dtype=np.float32)
+    return layers, fc_w, fc_b
+
+
+def test_convnet_fp32(ctx, oracle_lib):
+    o = Oracle(oracle_lib)
+    rng = np.random.default_rng(21)
+    layers, fc_w, fc_b = make_fp32_net(rng)
+    x_ref = rng.random((BATCH, 3, IMG, IMG), dtype=np.float32)
+    x_gpu = x_ref
+    for (w, scale, shift), st in zip(layers, STRIDES):
+        d = gr.conv_desc(geometry(st), x_ref.shape, w.shape)
+        ho, wo = out_hw(ctx, d)
+        x_ref = o.conv(x_ref, w, d, ho, wo, ep=o.epilogue(col_scale=scale, bias=shift, act=L.ACT_RELU))
+        x_gpu = run_conv(ctx, np.ascontiguousarray(x_gpu), w, d, ho, wo, torch.float32, col_scale=scale, bias=shift, act=L.ACT_RELU)
+        assert close_f32(x_gpu, x_ref, rel=2e-5), f"stride {st}: {np.abs(x_gpu - x_ref).max():.3g}"
+    pooled_ref = o.global_avgpool(x_ref)
+    tp = torch.empty((BATCH, 512), dtype=torch.float32, device=DEV)
+    ctx.global_avgpool(torch.from_numpy(x_gpu).to(DEV), tp)
+    ctx.sync()
+    pooled_gpu = tp.cpu().numpy()
+    want = o.gemm(pooled_ref, fc_w, BATCH, CLASSES, 512, L.F32, L.F32, ep=o.epilogue(bias=fc_b))
+    got = run_gemm(ctx, pooled_gpu, fc_w, BATCH, CLASSES, 512, torch.float32, torch.float32, bias=fc_b).cpu().numpy()
+    assert close_f32(got, want, rel=5e-5), np.abs(got - want).max()
+
+
+def test_convnet_int8_every_layer_bit_exact(ctx, oracle_lib):
+    o = Oracle(oracle_lib)
+    rng = np.random.default_rng(22)
+    x = rng.integers(0, 128, size=(BATCH, 3, IMG, IMG), dtype=np.int8)   # quantised U(0,1) input, scale 1/127
+    x_gpu = x
+    a_scale = np.float32(1.0 / 127.0)
+    for i, st in enumerate(STRIDES):
+        cin, cout = CHANNELS[i], CHANNELS[i + 1]
+        wf = rng.standard_normal((cout, cin, 3, 3)) * np.sqrt(2.0 / (cin * 9))
+        w_scale = (np.abs(wf).reshape(cout, -1).max(axis=1) / 127.0).astype(np.float32)          # per output channel
+        w = np.clip(np.rint(wf / w_scale[:, None, None, None]), -127, 127).astype(np.int8)
+        y_scale = np.float32(0.05)
+        mult = (a_scale * w_scale / y_scale).astype(np.float32)                                 # fp32, left to right
+        bias = rng.integers(-2000, 2000, size=cout, dtype=np.int32)                              # folded BN shift at scale a*w[c]
+        d = gr.conv_desc(geometry(st), x.shape, w.shape, L.I8, L.I8)
+        ho, wo = out_hw(ctx, d)
+        x = o.conv(x, w, d, ho, wo, ep=o.epilogue(col_scale=mult, bias=bias, act=L.ACT_RELU))
+        x_gpu = run_conv(ctx, np.ascontiguousarray(x_gpu), w, d, ho, wo, torch.int8, col_scale=mult, bias=bias, act=L.ACT_RELU)
+        assert np.array_equal(x_gpu, x), f"layer {i}: {(x_gpu != x).sum()} of {x.size} differ"
+        assert x.max() > 0   # the layer is not dead
+        a_scale = y_scale
+    pooled = o.global_avgpool(x, L.I8)
+    tp = torch.empty((BATCH, 512), dtype=torch.float32, device=DEV)
+    ctx.global_avgpool(torch.from_numpy(x_gpu).to(DEV), tp)
+    ctx.sync()
+    assert np.abs(tp.cpu().numpy() - pooled).max() <= 1e-5 * max(1.0, np.abs(pooled).max())
