@@ -202,7 +202,10 @@ int sofie_b200_gemm_plan_create(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc 
                                 sofie_b200_gemm_plan **out);
 int sofie_b200_gemm_plan_destroy(sofie_b200_gemm_plan *plan);
 
-/* Name of the kernel family the plan selected: "umma" (tcgen05 + TMEM + TMA) or "simt". */
+/* Name of the kernel family the plan selected: "umma" (tcgen05 + TMEM + TMA), "umma3x" (fp32 operands as
+ * error-compensated 3xTF32: split operands, a tcgen05 kernel that sums short K chunks in registers because the
+ * tensor core's fp32 accumulation truncates; chosen for F32 at precise = 1 from SOFIE_B200_SPLIT_MIN_FLOPS up)
+ * or "simt" (CUDA cores). */
 const char *sofie_b200_gemm_plan_kernel(const sofie_b200_gemm_plan *plan);
 
 /* Enqueues the contraction with its fused epilogue on the ctx's stream: the replacement of
@@ -228,8 +231,15 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
 int sofie_b200_conv_plan_destroy(sofie_b200_conv_plan *plan);
 /* Output extent per ROperator_Conv.hxx:123-262. */
 int sofie_b200_conv_out_shape(const sofie_b200_conv_desc *desc, int64_t *Ho, int64_t *Wo);
-/* Bytes of caller-provided scratch the plan needs per enqueue (0 if none). */
+/* Bytes of caller-provided scratch the plan needs per enqueue (0 if none): the unfolded input,
+ * [groups][N][Ho*Wo][kpad] elements with kpad = C/groups*R*S rounded up to 16 bytes -- times three for an
+ * F32 convolution at precise = 1 of at least SOFIE_B200_SPLIT_MIN_FLOPS (2 * K/groups * Ho*Wo * kpad * N),
+ * which runs as error-compensated 3xTF32 on the tensor cores and unfolds into three K segments.  The Im2Col
+ * scratch of the reference is per image (ROperator_Conv.hxx:1002-1103); this one covers the batch. */
+#define SOFIE_B200_SPLIT_MIN_FLOPS 4e8
 int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan);
+/* Kernel family of the plan's contraction, as sofie_b200_gemm_plan_kernel reports it. */
+const char *sofie_b200_conv_plan_kernel(const sofie_b200_conv_plan *plan);
 /* Enqueues Y = epilogue(conv(X, W)); columns of the epilogue are output channels. */
 int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, void *workspace,
                             const sofie_b200_epilogue *ep);
@@ -249,7 +259,8 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
  *     it reads, so no clearing is needed, but calls that may overlap on the GPU (other streams, other
  *     contexts) race on it.  Calls on one stream are safe.
  * X, W ([K, C/groups, R, S] in x_dtype), Y and the epilogue vectors are device pointers as in
- * sofie_b200_conv_enqueue; results are identical to the plan-based call. */
+ * sofie_b200_conv_enqueue; integer results are identical to the plan-based call, F32 ones agree within the 1e-5
+ * bar (this call always uses the fp32 FMA kernel for F32 at precise = 1). */
 int sofie_b200_conv_enqueue_noalloc(sofie_b200_ctx *ctx, const sofie_b200_conv_desc *desc, const void *X,
                                     const void *W, void *Y, const sofie_b200_epilogue *ep);
 

@@ -1,5 +1,6 @@
 // C ABI: context, error reporting and the contraction plan / enqueue entry points.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "gemm.cuh"
@@ -39,6 +40,23 @@ static const char *kDeviceWait[] = {"ok", "TMA producer: no free shared-memory s
 }  // namespace sb200
 
 using namespace sb200;
+
+namespace sb200 {
+// A TF32 plan over already split K-major operands (K = 3*ks) that runs the chunk-promotion kernel.
+// Returns 1 when the tensor path does not apply to the shape.
+int gemm_plan_create_promote(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, sofie_b200_gemm_plan **out) {
+  *out = nullptr;
+  sofie_b200_gemm_plan *in = new sofie_b200_gemm_plan();
+  in->ctx = ctx;
+  in->desc = g;
+  in->promote = 1;   // sum short K chunks in registers: the tensor core's own fp32 adds truncate
+  const int rc = umma_plan_init(in);
+  if (rc) { delete in; return rc; }
+  in->use_umma = 1;
+  *out = in;
+  return 0;
+}
+}  // namespace sb200
 
 extern "C" {
 
@@ -151,6 +169,32 @@ int sofie_b200_gemm_plan_create(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc 
     if (rc < 0) { delete plan; return rc; }
     plan->use_umma = (rc == 0);
   }
+  // fp32 at fp32 accuracy: large problems go to the tensor cores as 3xTF32 (gemm_split.cu), the rest to fp32 FMA
+  if (d.ab_dtype == SOFIE_B200_F32 && d.precise != 0 && d.M > 0 && d.N > 0 && d.K > 0 && d.batch <= 65535 &&
+      2.0 * (double)d.M * (double)d.N * (double)d.K * (double)d.batch >= SPLIT_MIN_FLOPS && !getenv("SOFIE_B200_NO_3XTF32")) {
+    const long long ks = (d.K + 3) / 4 * 4;
+    sofie_b200_gemm_desc g = d;
+    const bool a_bcast = d.batch > 1 && d.stride_a == 0, b_bcast = d.batch > 1 && d.stride_b == 0;
+    g.K = 3 * ks; g.trans_a = 0; g.trans_b = 1; g.lda = 3 * ks; g.ldb = 3 * ks; g.precise = 0;
+    g.stride_a = a_bcast ? 0 : d.M * 3 * ks;
+    g.stride_b = b_bcast ? 0 : d.N * 3 * ks;
+    sofie_b200_gemm_plan *in = nullptr;
+    int rc = gemm_plan_create_promote(ctx, g, &in);
+    if (rc < 0) { delete plan; return rc; }
+    if (rc == 0) {
+      const size_t abytes = (size_t)(a_bcast ? 1 : d.batch) * d.M * 3 * ks * sizeof(float);
+      const size_t bbytes = (size_t)(b_bcast ? 1 : d.batch) * d.N * 3 * ks * sizeof(float);
+      if (cudaMalloc(&plan->split_a, abytes) != cudaSuccess || cudaMalloc(&plan->split_b, bbytes) != cudaSuccess) {
+        cudaGetLastError();
+        if (plan->split_a) cudaFree(plan->split_a);
+        plan->split_a = nullptr;
+        delete in;   // not enough memory for the split operands: stay on the fp32 FMA kernel
+      } else {
+        plan->inner = in;
+        plan->ks = ks;
+      }
+    }
+  }
   *out = plan;
   return 0;
 }
@@ -158,12 +202,16 @@ int sofie_b200_gemm_plan_create(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc 
 int sofie_b200_gemm_plan_destroy(sofie_b200_gemm_plan *plan) {
   if (!plan) return 0;
   // the plan holds no reference into the ctx that needs undoing: a plan may be destroyed after its ctx
+  if (plan->split_a) cudaFree(plan->split_a);
+  if (plan->split_b) cudaFree(plan->split_b);
+  delete plan->inner;
   delete plan;
   return 0;
 }
 
 const char *sofie_b200_gemm_plan_kernel(const sofie_b200_gemm_plan *plan) {
   if (!plan) return "";
+  if (plan->inner || (plan->promote && plan->use_umma)) return "umma3x";
   return plan->use_umma ? "umma" : "simt";
 }
 
@@ -216,6 +264,13 @@ int sofie_b200_gemm_enqueue(sofie_b200_gemm_plan *plan, const void *A, const voi
   int rc = make_epi(plan, Y, ep, &e);
   if (rc) return rc;
   SB_CUDA(cudaSetDevice(plan->ctx->device));
+  if (plan->inner) {
+    sofie_b200_ctx *ctx = plan->ctx;
+    const bool a_bcast = d.batch > 1 && d.stride_a == 0, b_bcast = d.batch > 1 && d.stride_b == 0;
+    if ((rc = split3_enqueue(ctx, (const float *)A, plan->split_a, d.M, d.K, plan->ks, d.lda, a_bcast ? 1 : d.batch, d.stride_a, d.trans_a ? 1 : 0, 0))) return rc;
+    if ((rc = split3_enqueue(ctx, (const float *)B, plan->split_b, d.N, d.K, plan->ks, d.ldb, b_bcast ? 1 : d.batch, d.stride_b, d.trans_b ? 0 : 1, 1))) return rc;
+    return umma_enqueue(plan->inner, plan->split_a, plan->split_b, e);
+  }
   if (plan->use_umma && d.K > 0) return umma_enqueue(plan, A, B, e);
   return simt_enqueue(plan, A, B, e);
 }

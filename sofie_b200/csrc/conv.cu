@@ -17,7 +17,8 @@ struct sofie_b200_conv_plan {
   int64_t Ho = 0, Wo = 0;
   int64_t cg = 0, kg = 0;      // input channels / output channels per group
   int64_t kdim = 0, kpad = 0;  // C/g*R*S and its padded pitch
-  void *w_padded = nullptr;    // [K, kpad] device copy of the weights
+  void *w_padded = nullptr;    // [K, kpad] device copy of the weights ([K, 3*kpad] hi|lo|hi in split mode)
+  int split = 0;               // fp32 at fp32 accuracy on the tensor cores: operands carry three K segments (gemm_split.cu)
   sofie_b200_gemm_plan *gemm = nullptr;
 };
 
@@ -68,6 +69,44 @@ __global__ void __launch_bounds__(256) unfold_kernel(const T *__restrict__ x, T 
   }
 }
 
+// fp32 input unfolded straight into the split form of the B operand: xcol[g][n][pix][hi | hi | lo], each segment kpad wide.
+__global__ void __launch_bounds__(256) unfold_split_kernel(const float *__restrict__ x, float *__restrict__ xcol, sofie_b200_conv_desc d,
+                                                           long long Ho, long long Wo, long long cg, long long kdim, long long kpad) {
+  const long long chunks = kpad / 4;
+  const long long pix = Ho * Wo;
+  const long long total = (long long)d.groups * d.N * pix * chunks;
+  const long long rs = d.R * d.S;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long ch = i % chunks;
+    long long t = i / chunks;
+    const long long row = t;   // (g, n, pix) flattened: one row of the B operand
+    const long long p = t % pix; t /= pix;
+    const long long n = t % d.N;
+    const long long g = t / d.N;
+    const long long oh = p / Wo, ow = p % Wo;
+    const long long ih0 = oh * d.stride_h - d.pad_top, iw0 = ow * d.stride_w - d.pad_left;
+    const float *xg = x + (n * d.C + g * cg) * d.H * d.W;
+    __align__(16) float hi[4], lo[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const long long k = ch * 4 + e;
+      float val = 0.f;
+      if (k < kdim) {
+        const long long c = k / rs, q = k % rs;
+        const long long r = q / d.S, s = q % d.S;
+        const long long ih = ih0 + r * d.dil_h, iw = iw0 + s * d.dil_w;
+        if (ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) val = xg[(c * d.H + ih) * d.W + iw];
+      }
+      hi[e] = tf32_rn(val);
+      lo[e] = tf32_rn(__fsub_rn(val, hi[e]));
+    }
+    float *o = xcol + row * 3 * kpad + ch * 4;
+    *reinterpret_cast<uint4 *>(o) = *reinterpret_cast<const uint4 *>(hi);
+    *reinterpret_cast<uint4 *>(o + kpad) = *reinterpret_cast<const uint4 *>(hi);
+    *reinterpret_cast<uint4 *>(o + 2 * kpad) = *reinterpret_cast<const uint4 *>(lo);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) pad_weights_kernel(const T *__restrict__ w, T *__restrict__ wp, long long rows, long long kdim,
                                                           long long kpad) {
@@ -112,12 +151,35 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   p->kdim = p->cg * d.R * d.S;
   const int64_t vec = 16 / es;
   p->kpad = (p->kdim + vec - 1) / vec * vec;
-  if (cudaMalloc(&p->w_padded, (size_t)(d.K * p->kpad * es)) != cudaSuccess) {
+  // fp32 at fp32 accuracy: large convolutions run as 3xTF32 on the tensor cores, with the weights split once here and
+  // the input split by the unfold kernel; small ones stay on the fp32 FMA kernel.
+  const int64_t images = d.N > 0 ? d.N : 1;
+  sofie_b200_gemm_desc g{};
+  g.M = p->kg; g.N = Ho * Wo; g.batch = images;
+  g.trans_a = 0; g.trans_b = 1;
+  g.ab_dtype = d.x_dtype; g.y_dtype = d.y_dtype;
+  g.ldy = Ho * Wo; g.stride_a = 0; g.stride_y = d.K * Ho * Wo; g.stride_r = d.K * Ho * Wo;
+  if (d.x_dtype == SOFIE_B200_F32 && d.precise != 0 && images <= 65535 && !getenv("SOFIE_B200_NO_3XTF32") &&
+      2.0 * (double)p->kg * (double)(Ho * Wo) * (double)p->kpad * (double)images >= SPLIT_MIN_FLOPS) {
+    g.K = 3 * p->kpad; g.lda = g.ldb = 3 * p->kpad; g.stride_b = Ho * Wo * 3 * p->kpad; g.precise = 0;
+    rc = gemm_plan_create_promote(ctx, g, &p->gemm);
+    if (rc < 0) { delete p; return rc; }
+    p->split = (rc == 0);
+  }
+  const int64_t kw = p->split ? 3 * p->kpad : p->kpad;   // pitch of one weight row / one unfolded pixel
+  if (cudaMalloc(&p->w_padded, (size_t)(d.K * kw * es)) != cudaSuccess) {
+    if (p->gemm) sofie_b200_gemm_plan_destroy(p->gemm);
     delete p;
     return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: allocating padded weights failed: %s", cudaGetErrorString(cudaGetLastError()));
   }
   const long long total = d.K * p->kpad;
   const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 16);
+  if (p->split) {
+    rc = split3_enqueue(ctx, (const float *)W, (float *)p->w_padded, d.K, p->kdim, p->kpad, p->kdim, 1, 0, 0, 0);
+    if (rc) { sofie_b200_gemm_plan_destroy(p->gemm); cudaFree(p->w_padded); delete p; return rc; }
+    *out = p;
+    return 0;
+  }
   if (d.x_dtype == SOFIE_B200_F32)
     pad_weights_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float *)W, (float *)p->w_padded, d.K, p->kdim, p->kpad);
   else
@@ -126,13 +188,7 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   if (e != cudaSuccess) { cudaFree(p->w_padded); delete p; return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: %s", cudaGetErrorString(e)); }
   ctx->launches++;
 
-  sofie_b200_gemm_desc g{};
-  g.M = p->kg; g.N = Ho * Wo; g.K = p->kpad; g.batch = d.N > 0 ? d.N : 1;
-  g.trans_a = 0; g.trans_b = 1;
-  g.ab_dtype = d.x_dtype; g.y_dtype = d.y_dtype;
-  g.lda = p->kpad; g.ldb = p->kpad; g.ldy = Ho * Wo;
-  g.stride_a = 0; g.stride_b = Ho * Wo * p->kpad; g.stride_y = d.K * Ho * Wo;
-  g.stride_r = d.K * Ho * Wo;
+  g.K = p->kpad; g.lda = p->kpad; g.ldb = p->kpad; g.stride_b = Ho * Wo * p->kpad;
   g.precise = d.precise;
   rc = sofie_b200_gemm_plan_create(ctx, &g, &p->gemm);
   if (rc) { cudaFree(p->w_padded); delete p; return rc; }
@@ -149,9 +205,13 @@ int sofie_b200_conv_plan_destroy(sofie_b200_conv_plan *plan) {
   return 0;
 }
 
+const char *sofie_b200_conv_plan_kernel(const sofie_b200_conv_plan *plan) {
+  return plan ? sofie_b200_gemm_plan_kernel(plan->gemm) : "";
+}
+
 int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan) {
   if (!plan) return 0;
-  return (int64_t)plan->d.groups * plan->d.N * plan->Ho * plan->Wo * plan->kpad * dtype_size(plan->d.x_dtype);
+  return (int64_t)plan->d.groups * plan->d.N * plan->Ho * plan->Wo * plan->kpad * (plan->split ? 3 : 1) * dtype_size(plan->d.x_dtype);
 }
 
 int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, void *workspace,
@@ -167,7 +227,9 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
   const long long pix = plan->Ho * plan->Wo;
   const long long total = (long long)d.groups * d.N * pix * (plan->kpad / (16 / es));
   const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 32);
-  if (d.x_dtype == SOFIE_B200_F32)
+  if (plan->split)
+    unfold_split_kernel<<<grid, 256, 0, ctx->stream>>>((const float *)X, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad);
+  else if (d.x_dtype == SOFIE_B200_F32)
     unfold_kernel<float, 4><<<grid, 256, 0, ctx->stream>>>((const float *)X, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, 0.f);
   else
     unfold_kernel<int8_t, 16><<<grid, 256, 0, ctx->stream>>>((const int8_t *)X, (int8_t *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, (int8_t)d.x_zero_point);
@@ -197,8 +259,9 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
     if (eg.row_scale) eg.row_scale += g * plan->kg;
     if (eg.bias && eg.bias_mode != SOFIE_B200_BIAS_SCALAR_F32) eg.bias = (const char *)eg.bias + (size_t)g * plan->kg * 4;
     if (eg.residual) eg.residual = (const char *)eg.residual + (size_t)g * plan->kg * pix * dtype_size(eg.residual_dtype);
-    const char *a = (const char *)plan->w_padded + (size_t)g * plan->kg * plan->kpad * es;
-    const char *b = (const char *)workspace + (size_t)g * d.N * pix * plan->kpad * es;
+    const long long kw = plan->split ? 3 * plan->kpad : plan->kpad;
+    const char *a = (const char *)plan->w_padded + (size_t)g * plan->kg * kw * es;
+    const char *b = (const char *)workspace + (size_t)g * d.N * pix * kw * es;
     char *y = (char *)Y + (size_t)g * plan->kg * pix * ys;
     int rc = sofie_b200_gemm_enqueue(plan->gemm, a, b, y, &eg);
     if (rc) return rc;

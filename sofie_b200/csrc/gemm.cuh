@@ -33,10 +33,21 @@ struct UmmaParams {
   int a_bcast, b_bcast;            // operand shared by the whole batch
   int vec_ok;                      // 16-byte vector stores of 32-column chunks are aligned
   int pair;                        // 1: CTA-pair kernel (cluster of 2, tcgen05 cta_group::2, 256 x bn tile per pair)
+  int promote_chunk;               // chunk-promotion kernel: K blocks per tensor-memory accumulation
   int b_rows;                      // N extent of the B slice one CTA stages: bn, or bn/2 in pair mode
   EpiParams ep;
   int *status;
 };
+
+// x rounded to the nearest TF32 value (ties away from zero); values whose rounding would overflow are truncated
+__device__ __forceinline__ float tf32_rn(float x) {
+  const uint32_t b = __float_as_uint(x);
+  const uint32_t r = ((b & 0x7f800000u) >= 0x7f000000u) ? b : b + 0x1000u;
+  return __uint_as_float(r & 0xffffe000u);
+}
+
+// Problems below this many flops stay on the fp32 FMA kernel (the split passes would dominate).
+constexpr double SPLIT_MIN_FLOPS = 4e8;
 
 struct SimtParams {
   const void *A, *B;
@@ -59,9 +70,11 @@ struct sofie_b200_gemm_plan {
   // tensor maps are rebuilt only when an operand pointer changes
   const void *cached_a = nullptr, *cached_b = nullptr;
   CUtensorMap tm_a{}, tm_b{};
-  // 3xTF32 split scratch (precise F32 on the tensor path)
-  void *split_a = nullptr, *split_b = nullptr;
-  const void *split_src_b = nullptr;
+  // fp32-accurate tensor path (3xTF32): split operands [rows, 3*ks] and the TF32 plan that multiplies them
+  sofie_b200_gemm_plan *inner = nullptr;
+  float *split_a = nullptr, *split_b = nullptr;
+  long long ks = 0;
+  int promote = 0;                 // this (inner TF32) plan runs the chunk-promotion kernel
 };
 
 namespace sb200 {
@@ -72,6 +85,14 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
 int umma_pair_set_smem(int kind, size_t smem_bytes);
 int umma_pair_max_clusters(int kind, size_t smem_bytes, int *out);
 int umma_pair_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u);
+// gemm_umma3x.cu (TF32 kernel that sums short K chunks in registers)
+int umma_promote_set_smem(size_t smem_bytes);
+int umma_promote_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u);
+// api.cu
+int gemm_plan_create_promote(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, sofie_b200_gemm_plan **out);
+// gemm_split.cu
+int split3_enqueue(sofie_b200_ctx *ctx, const float *src, float *dst, long long rows, long long K, long long Ks, long long ld,
+                   long long batch, long long batch_stride, int mn, int pattern);
 // gemm_simt.cu
 int simt_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep);
 }  // namespace sb200

@@ -260,14 +260,14 @@ static int encode_map(CUtensorMap *tm, int dtype, const void *base, uint64_t d0,
   return 0;
 }
 
-static int pick_bn(long long N, long long tiles_m, long long batch, int sms, int min_bn) {
+static int pick_bn(long long N, long long tiles_m, long long batch, int sms, int min_bn, int max_bn = 256) {
   // Per-tile time model: MMA time grows with bn, shared-memory operand traffic with 128 + bn.
   // (`sms` is the number of concurrent tiles: SMs, or SM pairs in pair mode.)
   const int cand[4] = {256, 128, 64, 32};
-  int best = 256;
+  int best = max_bn >= min_bn ? max_bn : 256;
   double best_cost = 1e300;
   for (int bn : cand) {
-    if (bn < min_bn) continue;
+    if (bn < min_bn || (bn > max_bn && max_bn >= min_bn)) continue;
     long long tiles = tiles_m * ((N + bn - 1) / bn) * batch;
     long long waves = (tiles + sms - 1) / sms;
     double per_tile = bn > 0.67 * (128 + bn) ? (double)bn : 0.67 * (128 + bn);
@@ -306,13 +306,15 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   {
     const long long pair_tiles = ((d.M + 255) / 256) * ((d.N + 255) / 256) * d.batch;
     (void)pair_tiles;
-    if (const char *e = getenv("SOFIE_B200_PAIR")) u.pair = (atoi(e) != 0 && d.M >= 256 && d.N >= 64) ? 1 : 0;
+    if (const char *e = getenv("SOFIE_B200_PAIR"); e && !plan->promote) u.pair = (atoi(e) != 0 && d.M >= 256 && d.N >= 64) ? 1 : 0;
   }
   const int tile_m = u.pair ? 2 * UMMA_BM : UMMA_BM;
   u.tiles_m = (int)((d.M + tile_m - 1) / tile_m);
   // an MN-major B slice is made of 128-byte-wide TMA boxes, so the slice one CTA stages must reach 128 bytes
   const int min_bn = (d.trans_b ? 32 : 128 / es) * (u.pair ? 2 : 1);
-  u.bn = pick_bn(d.N, u.tiles_m, d.batch, u.pair ? sms / 2 : sms, min_bn < 64 && u.pair ? 64 : min_bn);
+  u.bn = pick_bn(d.N, u.tiles_m, d.batch, u.pair ? sms / 2 : sms, min_bn < 64 && (u.pair || plan->promote) ? 64 : min_bn);
+  u.promote_chunk = 8;   // 32 MMA steps per accumulation: truncation bias below 2e-6 relative even for same-sign data
+  if (const char *e = getenv("SOFIE_B200_PROMOTE_CHUNK")) { const int c = atoi(e); if (c >= 1 && c <= 64) u.promote_chunk = c; }
   u.b_rows = u.pair ? u.bn / 2 : u.bn;
   u.tiles_n = (int)((d.N + u.bn - 1) / u.bn);
   u.num_tiles = (long long)u.tiles_m * u.tiles_n * d.batch;
@@ -371,7 +373,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.split_from = u.num_tiles;
   u.num_items = u.num_tiles;
   u.idesc_half = (u.idesc & ~(0x3fu << 17)) | ((uint32_t)(u.bn >> 4) << 17);
-  if (!u.pair && u.bn >= 64 && u.num_tiles > sms) {
+  if (!u.pair && !plan->promote && u.bn >= 64 && u.num_tiles > sms) {
     const long long tail = u.num_tiles % sms;
     if (tail > 0 && 2 * tail <= sms && !getenv("SOFIE_B200_NO_TAIL_SPLIT")) {
       u.split_from = u.num_tiles - tail;
@@ -391,6 +393,8 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
     if (plan->grid > 2 * clusters) plan->grid = 2 * clusters;
     return 0;
   }
+
+  if (plan->promote) return umma_promote_set_smem(plan->smem_bytes);
 
   cudaError_t e = cudaSuccess;
   switch (kind) {
@@ -449,6 +453,7 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
   u.ep = ep;
   if (((uintptr_t)ep.Y % 16) != 0) u.vec_ok = 0;
   if (u.pair) return umma_pair_launch(plan, u);
+  if (plan->promote) return umma_promote_launch(plan, u);
   cudaStream_t st = plan->ctx->stream;
   dim3 grid(plan->grid), block(UMMA_THREADS);
   switch (plan->kind) {

@@ -1,0 +1,213 @@
+// TF32 contraction with chunk promotion, the kernel behind the fp32-accurate ("umma3x") path.
+//
+// The tensor core adds into its fp32 accumulator with truncation, so a long K accumulates a bias that
+// grows linearly with the number of MMA steps (measured: 2e-5 relative at K' = 3000), too much for the
+// 1e-5 bar of the fp32 models.  Here the MMA issuer accumulates only CHUNK K-blocks (16 MMA steps) at
+// a time into one of two tensor-memory accumulators; the epilogue warps drain each finished chunk into
+// registers and add the chunks there with round-to-nearest, overlapping the next chunk's MMAs.  The error
+// no longer depends on K.  Same roles, rings and bounded waits as umma_gemm_kernel; operands are the
+// K-major split matrices written by split3_kernel.  The tile is 128 x bn, bn in {64, 128, 256}; eight
+// epilogue warps (two per tensor-memory lane quarter, each owning half of the columns) keep one fp32
+// register per accumulator element, so bn = 256 fits and the shared-memory operand traffic per MMA
+// stays that of the plain kernel.
+#include <cudaTypedefs.h>
+
+#include "gemm.cuh"
+#include "ptx.cuh"
+#include "umma_store.cuh"
+
+namespace sb200 {
+using namespace ptx;
+
+constexpr int PROMOTE_THREADS = 320;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: epilogue
+constexpr int PROMOTE_HALF_MAX = 128; // accumulator columns (= fp32 sum registers) per epilogue thread
+
+__global__ void __launch_bounds__(PROMOTE_THREADS, 1)
+umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                         const __grid_constant__ UmmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t *smem = smem_raw + pad;
+
+  const int stages = p.stages;
+  const uint32_t smem_a = smem_u32(smem);
+  const uint32_t smem_b = smem_a + stages * p.a_stage_bytes;
+  uint8_t *tail = smem + stages * (p.a_stage_bytes + p.b_stage_bytes);
+  const uint32_t bar_full = smem_u32(tail);
+  const uint32_t bar_empty = bar_full + 8 * stages;
+  const uint32_t bar_tfull = bar_empty + 8 * stages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail + 16 * stages + 32);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_tfull + 8 * i, 1);
+      mbar_init(bar_tempty + 8 * i, 8);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;
+  const int chunk = p.promote_chunk;   // K-blocks (of 32 floats) per tensor-memory accumulation
+  const int num_chunks = (p.num_kb + chunk - 1) / chunk;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        const int b = (int)(t / tiles_per_batch);
+        const int r = (int)(t % tiles_per_batch);
+        const int m0 = (r % p.tiles_m) * UMMA_BM;
+        const int n0 = (r / p.tiles_m) * p.bn;
+        const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+            raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_EMPTY);
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_arrive_expect_tx(full, p.a_stage_bytes + p.b_stage_bytes);
+          tma_load_3d(smem_a + stage * p.a_stage_bytes, &tm_a, full, kb * p.kb_elems, m0, ba);
+          tma_load_3d(smem_b + stage * p.b_stage_bytes, &tm_b, full, kb * p.kb_elems, n0, bb);
+          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer();
+        while (globaltimer() - t0 < 200000ull) {}
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {  // ---- MMA issuer: one tensor-memory accumulation per chunk of K-blocks
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+        for (int ch = 0; ch < num_chunks && ok; ++ch) {
+          if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) {
+            raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_EMPTY);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * p.bn;
+          const int kb0 = ch * chunk, kb_end = min(p.num_kb, kb0 + chunk);
+          for (int kb = kb0; kb < kb_end; ++kb) {
+            if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+              raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_FULL);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t a_lo = p.a_desc_lo | (((smem_a + stage * p.a_stage_bytes) >> 4) & 0x3fffu);
+            const uint32_t b_lo = p.b_desc_lo | (((smem_b + stage * p.b_stage_bytes) >> 4) & 0x3fffu);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint64_t ad = ((uint64_t)p.a_desc_hi << 32) | (uint64_t)(a_lo + k * p.a_kadv);
+              const uint64_t bd = ((uint64_t)p.b_desc_hi << 32) | (uint64_t)(b_lo + k * p.b_kadv);
+              umma<KIND_TF32>(d_tmem, ad, bd, p.idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+            }
+            tc_commit(bar_empty + 8 * stage);
+            if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
+          }
+          if (!ok) break;
+          tc_commit(bar_tfull + 8 * acc);
+          if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+      }
+    }
+  } else {
+    // ---- epilogue: sum the chunks in registers (round to nearest), then the fused epilogue
+    const int quad = warp & 3;               // tensor-memory lanes 32*quad .. 32*quad+31
+    const int half_cols = p.bn >> 1;
+    const int col_base = ((warp - 2) >> 2) * half_cols;
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
+      const int b = (int)(t / tiles_per_batch);
+      const int r = (int)(t % tiles_per_batch);
+      const int m0 = (r % p.tiles_m) * UMMA_BM;
+      const int n0 = (r / p.tiles_m) * p.bn;
+      float sum[PROMOTE_HALF_MAX];
+#pragma unroll
+      for (int c = 0; c < PROMOTE_HALF_MAX; ++c) sum[c] = 0.f;
+      for (int ch = 0; ch < num_chunks; ++ch) {
+        if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+          raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_FULL);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * p.bn + col_base;
+#pragma unroll
+        for (int c = 0; c < PROMOTE_HALF_MAX; c += 32) {
+          if (c < half_cols) {
+            uint32_t raw[32];
+            tmem_ld_x32(taddr + c, raw);
+            tmem_ld_wait();
+#pragma unroll
+            for (int u = 0; u < 32; ++u) sum[c + u] = __fadd_rn(sum[c + u], __uint_as_float(raw[u]));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok) break;
+      const int row = m0 + quad * 32 + lane;
+#pragma unroll
+      for (int c = 0; c < PROMOTE_HALF_MAX; c += 32) {
+        const int col = n0 + col_base + c;
+        if (c < half_cols && col < p.N && row < p.M) {
+          uint32_t raw[32];
+#pragma unroll
+          for (int u = 0; u < 32; ++u) raw[u] = __float_as_uint(sum[c + u]);
+          store_chunk(p.ep, raw, b, row, col, min(32, p.N - col), p.vec_ok != 0);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+}
+
+int umma_promote_set_smem(size_t smem_bytes) {
+  cudaError_t e = cudaFuncSetAttribute(umma_tf32_promote_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+  if (e != cudaSuccess) return fail(SOFIE_B200_ERR_CUDA, "cudaFuncSetAttribute(promote kernel, smem=%zu): %s", smem_bytes, cudaGetErrorString(e));
+  return 0;
+}
+
+int umma_promote_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u) {
+  umma_tf32_promote_kernel<<<dim3(plan->grid), dim3(PROMOTE_THREADS), plan->smem_bytes, plan->ctx->stream>>>(plan->tm_a, plan->tm_b, u);
+  SB_CUDA(cudaGetLastError());
+  plan->ctx->launches++;
+  return 0;
+}
+
+}  // namespace sb200

@@ -85,7 +85,10 @@ inline size_t ConvWorkspaceBytes(const ConvGeometry &g, size_t elemSize)
    // [groups][N][Ho*Wo][kpad] with kpad = C/groups*R*S rounded up to 16 bytes (sofie_b200_conv_workspace_bytes)
    const size_t kdim = g.C / g.group * g.R * g.S, vec = 16 / elemSize;
    const size_t kpad = (kdim + vec - 1) / vec * vec;
-   return g.group * g.N * g.Ho * g.Wo * kpad * elemSize;
+   size_t bytes = g.group * g.N * g.Ho * g.Wo * kpad * elemSize;
+   // a large fp32 convolution runs as 3xTF32 and unfolds into three K segments (SOFIE_B200_SPLIT_MIN_FLOPS of sofie_b200.h)
+   if (elemSize == sizeof(float) && 2.0 * double(g.K / g.group) * double(g.Ho * g.Wo) * double(kpad) * double(g.N) >= 4e8) bytes *= 3;
+   return bytes;
 }
 
 template <typename T>
@@ -204,6 +207,8 @@ public:
       out << "      {  // Conv " << opName << ": " << ConvertShapeToString(fShapeX) << " * " << ConvertShapeToString(fShapeW) << "\n";
       out << ConvDescCode(fGeo, "SOFIE_B200_F32", "SOFIE_B200_F32", 0);
       out << "      Check(sofie_b200_conv_plan_create(ctx, &d, tensor_" << fNW << ", &plan_" << opName << "), \"Conv " << opName << ": plan\");\n";
+      out << "      if (sofie_b200_conv_workspace_bytes(plan_" << opName << ") > " << ConvWorkspaceBytes(fGeo, sizeof(float)) << "LL)\n"
+          << "         throw std::runtime_error(\"Conv " << opName << ": the library wants more scratch than the arena reserves\");\n";
       out << fEpi.InitCode("ep_" + opName);
       out << "      }\n";
       return out.str();

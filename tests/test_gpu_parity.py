@@ -223,12 +223,14 @@ def test_fp32_gemm_bias_relu(ctx, oracle, M, N, K, ta, tb):
 
 
 # ---- convolution -----------------------------------------------------------------------------------
-def run_conv(ctx, x, w, desc, ho, wo, out_dt, **ep_kw):
+def run_conv(ctx, x, w, desc, ho, wo, out_dt, expect=None, **ep_kw):
     from sofie_b200.ops import make_epilogue
     lib = ctx._lib
     tx, tw = torch.from_numpy(x).to(DEV), torch.from_numpy(w).to(DEV)
     h = C.c_void_p()
     L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(desc), tw.data_ptr(), C.byref(h)), "conv_plan_create")
+    if expect is not None:
+        assert lib.sofie_b200_conv_plan_kernel(h).decode() == expect
     ws = torch.empty(max(16, lib.sofie_b200_conv_workspace_bytes(h)), dtype=torch.uint8, device=DEV)
     y = torch.zeros((desc.N, desc.K, ho, wo), dtype=out_dt, device=DEV)
     dev_kw = {k: (torch.from_numpy(v).to(DEV) if isinstance(v, np.ndarray) else v) for k, v in ep_kw.items()}
@@ -268,6 +270,22 @@ def test_conv_fp32_with_folded_batchnorm(ctx, oracle):
     want = oracle.conv(x, w, d, 10, 10, ep=oracle.epilogue(col_scale=fs, bias=shift, act=L.ACT_RELU))
     got = run_conv(ctx, x, w, d, 10, 10, torch.float32, col_scale=fs, bias=shift, act=L.ACT_RELU)
     assert close_f32(got, want), np.abs(got - want).max()
+
+
+@pytest.mark.parametrize("N,Ci,H,W,Co,st,g,k", [(4, 64, 56, 56, 64, 1, 1, 3), (16, 96, 28, 28, 192, 1, 2, 3), (8, 3, 112, 112, 64, 2, 1, 7)])
+def test_conv_fp32_on_tensor_cores_meets_fp32_bar(ctx, oracle, N, Ci, H, W, Co, st, g, k):
+    """Large fp32 convolutions unfold into hi/lo TF32 segments and run as 3xTF32 (K = 27..576, not a multiple of 32)."""
+    rng = np.random.default_rng(N + Ci + Co)
+    x = rng.random((N, Ci, H, W), dtype=np.float32)                         # post-Relu-like: all one sign, the worst case for
+    w = np.abs(rng.standard_normal((Co, Ci // g, k, k)) * 0.1).astype(np.float32)   # a truncating accumulator
+    geo = dict(pads=[k // 2] * 4, strides=[st, st], dil=[1, 1], group=g)
+    d = gr.conv_desc(geo, x.shape, w.shape)
+    ho, wo = C.c_int64(), C.c_int64()
+    assert ctx._lib.sofie_b200_conv_out_shape(C.byref(d), C.byref(ho), C.byref(wo)) == 0
+    fs, shift = rng.random(Co, dtype=np.float32) + 0.5, (rng.standard_normal(Co) * 0.1).astype(np.float32)
+    want = oracle.conv(x, w, d, ho.value, wo.value, ep=oracle.epilogue(col_scale=fs, bias=shift, act=L.ACT_RELU))
+    got = run_conv(ctx, x, w, d, ho.value, wo.value, torch.float32, expect="umma3x", col_scale=fs, bias=shift, act=L.ACT_RELU)
+    assert close_f32(got, want), f"max abs {np.abs(got - want).max():.3g} at scale {np.abs(want).max():.3g}"
 
 
 # ---- row-wise and elementwise operators ---------------------------------------------------------------
@@ -350,3 +368,21 @@ def test_quantize_dequantize_convert_pool(ctx, oracle):
     ctx.convert(torch.from_numpy(m).to(DEV), t8, torch.from_numpy(rs).to(DEV))
     ctx.sync()
     assert np.array_equal(t8.view(torch.uint8).cpu().numpy(), oracle.convert(m, L.F32, L.F8E4M3, rs))
+
+
+# ---- fp32 at fp32 accuracy on the tensor cores (3xTF32) ---------------------------------------------------
+@pytest.mark.parametrize("M,N,K,ta,tb,batch", [(1024, 768, 1000, False, False, 1), (640, 512, 2304, False, True, 1), (512, 768, 515, True, False, 1),
+                                                (256, 320, 1152, False, True, 3), (384, 200, 8192, False, True, 1)])
+def test_fp32_gemm_3xtf32_meets_fp32_bar(ctx, oracle, M, N, K, ta, tb, batch):
+    rng = np.random.default_rng(M + K)
+    a = rng.standard_normal((batch, K, M) if ta else (batch, M, K)).astype(np.float32)
+    b = rng.standard_normal((batch, N, K) if tb else (batch, K, N)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32)
+    want = oracle.gemm(a, b, M, N, K, L.F32, L.F32, ta, tb, batch=batch, ep=oracle.epilogue(bias=bias, act=L.ACT_RELU))
+    got = run_gemm(ctx, a, b, M, N, K, torch.float32, torch.float32, ta, tb, batch=batch, bias=bias, act=L.ACT_RELU, expect="umma3x").cpu().numpy()
+    got = got.reshape(want.shape)
+    assert close_f32(got, want), f"max abs {np.abs(got - want).max():.3g} at scale {np.abs(want).max():.3g}"
+    # single-pass TF32 on the same inputs is far outside the bar: the compensation is what meets it
+    tf32 = run_gemm(ctx, a, b, M, N, K, torch.float32, torch.float32, ta, tb, batch=batch, bias=bias, act=L.ACT_RELU, precise=False).cpu().numpy()
+    if not ta and tb:
+        assert not close_f32(tf32.reshape(want.shape), want)
