@@ -226,6 +226,7 @@ static int make_epi(const sofie_b200_gemm_plan *plan, void *Y, const sofie_b200_
   o->alpha = 1.f; o->beta = 1.f; o->out_scale = 1.f;
   o->y_dtype = d.y_dtype;
   o->acc_is_int = d.ab_dtype == SOFIE_B200_I8;
+  o->params_aligned = 1; o->residual_aligned = 1; o->fast = 1;
   if (ep) {
     o->row_scale = ep->row_scale;
     o->col_scale = ep->col_scale;
@@ -242,6 +243,9 @@ static int make_epi(const sofie_b200_gemm_plan *plan, void *Y, const sofie_b200_
     o->out_scale = ep->out_scale == 0.f ? 1.f : ep->out_scale;
     o->out_zp = ep->out_zero_point;
     o->params_aligned = ((uintptr_t)ep->col_scale % 16 == 0) && ((uintptr_t)ep->bias % 16 == 0);
+    const int rs_ = dtype_size(ep->residual_dtype);
+    o->residual_aligned = ((uintptr_t)ep->residual % 16 == 0) && ((o->ldr * rs_) % 16 == 0) && ((o->stride_r * rs_) % 16 == 0);
+    o->fast = o->params_aligned && ep->bias_mode != SOFIE_B200_BIAS_FULL_F32;
     if (ep->bias_mode != SOFIE_B200_BIAS_NONE && !ep->bias)
       return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue: bias_mode %d with a NULL bias", ep->bias_mode);
     if ((ep->bias_mode == SOFIE_B200_BIAS_COL_I32 || ep->bias_mode == SOFIE_B200_BIAS_ROW_I32) && !o->acc_is_int)

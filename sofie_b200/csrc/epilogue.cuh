@@ -20,6 +20,8 @@ struct EpiParams {
   int bias_mode, act, out_zp, y_dtype, residual_dtype;
   int acc_is_int;
   int params_aligned;  // col_scale and a per-column bias are 16-byte aligned (vector loads allowed)
+  int residual_aligned;  // residual base, pitch and batch stride are multiples of 16 bytes
+  int fast;            // store_chunk_fast() applies: aligned per-column vectors, no full-matrix bias
 };
 
 __device__ __forceinline__ float act_apply(float v, int act, float act_alpha) {

@@ -3,11 +3,30 @@
 #include <cuda.h>
 #include "epilogue.cuh"
 
+// Built with -DSB200_ROLE_TIMERS, the first and last CTA print how many cycles each role spent waiting
+// (a debugging aid for the pipeline; never defined in the shipped library).
+#ifdef SB200_ROLE_TIMERS
+#define ROLE_TIMER(name) long long name = 0
+#define ROLE_WAIT(name, expr) [&] { const long long t0__ = clock64(); const bool r__ = (expr); name += clock64() - t0__; return r__; }()
+#define ROLE_SECTION_BEGIN() sec_t0 = clock64()
+#define ROLE_SECTION_END(name) name += clock64() - sec_t0
+#define ROLE_REPORT(...) if (blockIdx.x <= 1 || blockIdx.x >= gridDim.x - 2) printf(__VA_ARGS__)
+#else
+#define ROLE_TIMER(name)
+#define ROLE_WAIT(name, expr) (expr)
+#define ROLE_REPORT(...)
+#define ROLE_SECTION_BEGIN()
+#define ROLE_SECTION_END(name)
+#endif
+
 namespace sb200 {
 
 constexpr int UMMA_BM = 128;          // rows of one accumulator tile (TMEM lanes)
 constexpr int UMMA_STAGE_K_BYTES = 128;  // K extent of one shared-memory stage, in bytes (one 128B swizzle row)
-constexpr int UMMA_THREADS = 192;     // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int UMMA_TAIL_BYTES = 1024;  // barriers, TMEM slot and abort flag behind the stage ring; the epilogue staging follows
+constexpr int UMMA_EPI_WARPS = 8;     // two epilogue warps per tensor-memory lane quarter, alternating 32-column chunks
+constexpr int UMMA_THREADS = 64 + 32 * UMMA_EPI_WARPS;  // warp 0: TMA producer, warp 1: MMA issuer, then the epilogue warps
+constexpr int UMMA_PAIR_THREADS = 192; // CTA-pair kernel: four epilogue warps per CTA
 
 // Everything the tcgen05 kernel needs besides the two tensor maps.
 struct UmmaParams {
@@ -33,6 +52,10 @@ struct UmmaParams {
   int a_bcast, b_bcast;            // operand shared by the whole batch
   int vec_ok;                      // 16-byte vector stores of 32-column chunks are aligned
   int pair;                        // 1: CTA-pair kernel (cluster of 2, tcgen05 cta_group::2, 256 x bn tile per pair)
+  int raster_n;                    // tile order inside a batch: 0 = M index fastest, 1 = N index fastest
+  int y_tma;                       // the epilogue may store complete row segments through the tensor map of Y
+  int l2_ahead;                    // K blocks the L2 prefetch cursor runs in front of the loads (0 = off)
+  int commit_group;                // pair kernel: K blocks consumed between bursts of stage releases
   int promote_chunk;               // chunk-promotion kernel: K blocks per tensor-memory accumulation
   int b_rows;                      // N extent of the B slice one CTA stages: bn, or bn/2 in pair mode
   EpiParams ep;
@@ -48,6 +71,13 @@ __device__ __forceinline__ float tf32_rn(float x) {
 
 // Problems below this many flops stay on the fp32 FMA kernel (the split passes would dominate).
 constexpr double SPLIT_MIN_FLOPS = 4e8;
+
+// Tile r of a batch -> (M tile, N tile).  Consecutive tiles run at the same time on neighbouring SMs, so the index that
+// varies fastest decides which operand slice they share in L2 (see umma_plan_init for the choice).
+__device__ __forceinline__ void tile_mn(const UmmaParams &p, int r, int &tm, int &tn) {
+  if (p.raster_n) { tn = r % p.tiles_n; tm = r / p.tiles_n; }
+  else { tm = r % p.tiles_m; tn = r / p.tiles_m; }
+}
 
 struct SimtParams {
   const void *A, *B;
@@ -69,7 +99,8 @@ struct sofie_b200_gemm_plan {
   int grid = 0;
   // tensor maps are rebuilt only when an operand pointer changes
   const void *cached_a = nullptr, *cached_b = nullptr;
-  CUtensorMap tm_a{}, tm_b{};
+  CUtensorMap tm_a{}, tm_b{}, tm_y{};
+  const void *cached_y = nullptr;
   // fp32-accurate tensor path (3xTF32): split operands [rows, 3*ks] and the TF32 plan that multiplies them
   sofie_b200_gemm_plan *inner = nullptr;
   float *split_a = nullptr, *split_b = nullptr;

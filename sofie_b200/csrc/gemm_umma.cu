@@ -1,7 +1,7 @@
 // Contraction kernel for sm_100a: tcgen05.mma with the accumulator in tensor memory, operands
 // staged in 128B-swizzled shared memory by TMA, one persistent CTA per SM.
 //
-// Roles inside a CTA of 192 threads
+// Roles inside a CTA of 320 threads
 //   warp 0, lane 0 : TMA producer.  Fills a ring of `stages` shared-memory stages; each stage
 //                    holds a 128 x (128 bytes of K) slice of op(A) and a bn x (128 bytes of K)
 //                    slice of op(B).
@@ -9,9 +9,11 @@
 //                    TMEM accumulators (128 lanes x bn columns each); tcgen05.commit releases
 //                    the stage to the producer and, after the last K block, hands the accumulator
 //                    to the epilogue.
-//   warps 2-5      : epilogue.  tcgen05.ld 32 columns at a time (thread = row), apply the fused
-//                    epilogue (epilogue.cuh) and store with 16-byte vector stores.  The second
-//                    accumulator lets the epilogue of tile t overlap the main loop of tile t+1.
+//   warps 2-9      : epilogue, two warps per tensor-memory lane quarter taking alternate 32-column
+//                    chunks.  tcgen05.ld of the next chunk is in flight while the current one goes
+//                    through the fused epilogue (epilogue.cuh) and a shared-memory staging buffer that
+//                    turns row-per-lane data into coalesced 16-byte stores.  The second accumulator
+//                    lets the epilogue of tile t overlap the main loop of tile t+1.
 //
 // Data layout: a K-major operand (row-major [rows, K]) is one TMA box of rows x 128 bytes per
 // stage; an MN-major operand (row-major [K, cols]) is cols*es/128 boxes of (128 bytes x K-rows).
@@ -50,7 +52,7 @@ __device__ __forceinline__ void decode_item(const UmmaParams &p, long long w, lo
 template <int KIND>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                 const __grid_constant__ UmmaParams p) {
+                 const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;  // swizzle atoms are 1024-byte aligned
@@ -66,6 +68,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   const uint32_t bar_tempty = bar_tfull + 16;           // [2]
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail + 16 * stages + 32);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  const uint32_t epi_stage = smem_u32(tail) + UMMA_TAIL_BYTES;   // 4 KB per epilogue warp (coalesced_store)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -77,12 +80,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_tfull + 8 * i, 1);
-      mbar_init(bar_tempty + 8 * i, 4);  // one arrival per epilogue warp
+      mbar_init(bar_tempty + 8 * i, UMMA_EPI_WARPS);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tm_a);
     prefetch_tensormap(&tm_b);
+    if (p.y_tma) prefetch_tensormap(&tm_y);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
@@ -100,16 +104,52 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      ROLE_TIMER(w_empty);
+      ROLE_TIMER(t_begin);
+#ifdef SB200_ROLE_TIMERS
+      t_begin = clock64();
+#endif
+      // L2 prefetch cursor: runs `l2_ahead` K blocks in front of the loads (across tile boundaries), so that the
+      // loads that fill shared memory find their lines in L2 instead of waiting for DRAM with only a few stages
+      // of lookahead.
+      long long pf_w = blockIdx.x;
+      int pf_kb = 0, pf_m0 = 0, pf_n0 = 0, pf_ba = 0, pf_bb = 0;
+      bool pf_fresh = true;
+      auto prefetch_step = [&]() {
+        if (pf_w >= p.num_items) return;
+        if (pf_fresh) {
+          long long t; int n_off, n_len; uint32_t idesc;
+          decode_item(p, pf_w, t, n_off, n_len, idesc);
+          const int b = (int)(t / tiles_per_batch);
+          const int r = (int)(t % tiles_per_batch);
+          int tm, tn;
+          tile_mn(p, r, tm, tn);
+          pf_m0 = tm * UMMA_BM;
+          pf_n0 = tn * p.bn + n_off;
+          pf_ba = p.a_bcast ? 0 : b; pf_bb = p.b_bcast ? 0 : b;
+          pf_fresh = false;
+        }
+        const int k0 = pf_kb * p.kb_elems;
+        if (!p.a_mn) tma_prefetch_3d(&tm_a, k0, pf_m0, pf_ba);
+        else for (int x = 0; x < p.a_boxes; ++x) tma_prefetch_3d(&tm_a, pf_m0 + x * p.a_box_mn, k0, pf_ba);
+        if (!p.b_mn) tma_prefetch_3d(&tm_b, k0, pf_n0, pf_bb);
+        else for (int x = 0; x < p.b_boxes; ++x) tma_prefetch_3d(&tm_b, pf_n0 + x * p.b_box_mn, k0, pf_bb);
+        if (++pf_kb == p.num_kb) { pf_kb = 0; pf_w += gridDim.x; pf_fresh = true; }
+      };
+      for (int i = 0; i < p.l2_ahead; ++i) prefetch_step();
       for (long long w = blockIdx.x; w < p.num_items && ok; w += gridDim.x) {
         long long t; int n_off, n_len; uint32_t idesc;
         decode_item(p, w, t, n_off, n_len, idesc);
         const int b = (int)(t / tiles_per_batch);
         const int r = (int)(t % tiles_per_batch);
-        const int m0 = (r % p.tiles_m) * UMMA_BM;
-        const int n0 = (r / p.tiles_m) * p.bn + n_off;  // a half item still loads a full-width B slice
+        int tm, tn;
+        tile_mn(p, r, tm, tn);
+        const int m0 = tm * UMMA_BM;
+        const int n0 = tn * p.bn + n_off;  // a half item still loads a full-width B slice
         const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+          if (p.l2_ahead) prefetch_step();
+          if (!ROLE_WAIT(w_empty, mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag))) {
             raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_EMPTY);
             ok = false;
             break;
@@ -134,6 +174,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
         }
       }
+      ROLE_REPORT("[cta %d] producer: total %lld, waiting for a free stage %lld\n", blockIdx.x, clock64() - t_begin, w_empty);
       if (!ok) {
         // give copies that may still be in flight time to land before the CTA exits
         const uint64_t t0 = globaltimer();
@@ -146,73 +187,110 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
+      // descriptor words that do not change inside the loop, kept in registers (stage bases are multiples of 1024
+      // bytes inside a 227 KB window, so adding the stage offset never carries out of the 14-bit address field)
+      const uint64_t a_hi = (uint64_t)p.a_desc_hi << 32, b_hi = (uint64_t)p.b_desc_hi << 32;
+      const uint32_t a_lo0 = p.a_desc_lo | ((smem_a >> 4) & 0x3fffu), b_lo0 = p.b_desc_lo | ((smem_b >> 4) & 0x3fffu);
+      const uint32_t a_step = p.a_stage_bytes >> 4, b_step = p.b_stage_bytes >> 4;
+      const uint32_t a_kadv = p.a_kadv, b_kadv = p.b_kadv;
+      const int num_kb = p.num_kb;
+      ROLE_TIMER(w_full);
+      ROLE_TIMER(w_tempty);
+      ROLE_TIMER(c_fence);
+      ROLE_TIMER(c_mma);
+      ROLE_TIMER(c_commit);
+      ROLE_TIMER(sec_t0);
+      ROLE_TIMER(t_begin);
+#ifdef SB200_ROLE_TIMERS
+      t_begin = clock64();
+#endif
       for (long long w = blockIdx.x; w < p.num_items && ok; w += gridDim.x) {
         long long t; int n_off, n_len; uint32_t idesc;
         decode_item(p, w, t, n_off, n_len, idesc);
-        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) {
+        if (!ROLE_WAIT(w_tempty, mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag))) {
           raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_EMPTY);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * p.bn;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ROLE_WAIT(w_full, mbar_wait(bar_full + 8 * stage, phase, abort_flag))) {
             raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_FULL);
             ok = false;
             break;
           }
+          ROLE_SECTION_BEGIN();
           tc_fence_after();
-          const uint32_t sa = smem_a + stage * p.a_stage_bytes;
-          const uint32_t sb = smem_b + stage * p.b_stage_bytes;
-          const uint32_t a_lo = p.a_desc_lo | ((sa >> 4) & 0x3fffu);
-          const uint32_t b_lo = p.b_desc_lo | ((sb >> 4) & 0x3fffu);
+          ROLE_SECTION_END(c_fence);
+          const uint32_t a_lo = a_lo0 + stage * a_step;
+          const uint32_t b_lo = b_lo0 + stage * b_step;
+          ROLE_SECTION_BEGIN();
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint64_t ad = ((uint64_t)p.a_desc_hi << 32) | (uint64_t)(a_lo + k * p.a_kadv);
-            const uint64_t bd = ((uint64_t)p.b_desc_hi << 32) | (uint64_t)(b_lo + k * p.b_kadv);
+            const uint64_t ad = a_hi | (uint64_t)(a_lo + k * a_kadv);
+            const uint64_t bd = b_hi | (uint64_t)(b_lo + k * b_kadv);
             umma<KIND>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
           }
+          ROLE_SECTION_END(c_mma);
+          ROLE_SECTION_BEGIN();
           tc_commit(bar_empty + 8 * stage);  // stage may be refilled once these MMAs have read it
+          ROLE_SECTION_END(c_commit);
           if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         tc_commit(bar_tfull + 8 * acc);      // accumulator complete
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
+      ROLE_REPORT("[cta %d] mma issuer: total %lld, waiting for operands %lld, for a drained accumulator %lld\n", blockIdx.x,
+                  clock64() - t_begin, w_full, w_tempty);
+      ROLE_REPORT("[cta %d] mma issuer sections: fence %lld, issuing MMAs %lld, commits %lld\n", blockIdx.x, c_fence, c_mma, c_commit);
     }
   } else {
     // ------------------------------ epilogue -----------------------------------------
     const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
     uint32_t acc = 0, acc_phase = 0;
+    ROLE_TIMER(w_tfull);
+    ROLE_TIMER(c_ld);
+    ROLE_TIMER(c_st);
+    ROLE_TIMER(sec_t0);
+    ROLE_TIMER(t_begin);
+#ifdef SB200_ROLE_TIMERS
+    t_begin = clock64();
+#endif
     for (long long w = blockIdx.x; w < p.num_items; w += gridDim.x) {
       long long t; int n_off, n_len; uint32_t idesc;
       decode_item(p, w, t, n_off, n_len, idesc);
       const int b = (int)(t / tiles_per_batch);
       const int r = (int)(t % tiles_per_batch);
-      const int m0 = (r % p.tiles_m) * UMMA_BM;
-      const int n0 = (r / p.tiles_m) * p.bn + n_off;
-      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+      int tm, tn;
+      tile_mn(p, r, tm, tn);
+      const int m0 = tm * UMMA_BM;
+      const int n0 = tn * p.bn + n_off;
+      if (!ROLE_WAIT(w_tfull, mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag))) {
         raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_FULL);
         break;
       }
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * p.bn;
-      for (int c = 0; c < n_len; c += 32) {
-        if (n0 + c >= p.N) break;  // warp-uniform
-        uint32_t raw[32];
-        tmem_ld_x32(taddr + c, raw);
-        tmem_ld_wait();
-        if (row < p.M) {
-          const int ncols = min(32, p.N - (n0 + c));
-          store_chunk(p.ep, raw, b, row, n0 + c, ncols, p.vec_ok != 0);
-        }
-      }
+      const uint32_t my_stage = epi_stage + (uint32_t)(warp - 2) * 4096u;
+      const int c_end = min(n_len, p.N - n0);          // columns of this item that exist (warp-uniform)
+      ROLE_SECTION_BEGIN();
+      drain_accumulator<KIND == KIND_I8>(p.ep, taddr, c_end, (warp - 2) >> 2, 2, b, row, n0, p.vec_ok != 0, my_stage, p.M, p.y_tma ? &tm_y : nullptr);
+      ROLE_SECTION_END(c_st);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
+#ifdef SB200_ROLE_TIMERS
+    if (threadIdx.x == 64 && blockIdx.x == 0) {
+      printf("[cta 0] drain: tmem wait %lld, wait for buffer %lld, math+stage %lld, flush/issue %lld, final wait %lld\n", g_drain_cycles[0],
+             g_drain_cycles[1], g_drain_cycles[2], g_drain_cycles[3], g_drain_cycles[4]);
+      for (int i = 0; i < 6; ++i) g_drain_cycles[i] = 0;
+    }
+#endif
+    if (threadIdx.x == 64) { ROLE_REPORT("[cta %d] epilogue: total %lld, waiting for an accumulator %lld, tensor-memory loads %lld, epilogue math + stores %lld\n", blockIdx.x, clock64() - t_begin, w_tfull, c_ld, c_st); }
   }
 
   tc_fence_before();
@@ -245,6 +323,7 @@ static int encode_map(CUtensorMap *tm, int dtype, const void *base, uint64_t d0,
   CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_UINT8;
   if (dtype == SOFIE_B200_BF16) dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   if (dtype == SOFIE_B200_F32) dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  if (dtype == SOFIE_B200_I32) dt = CU_TENSOR_MAP_DATA_TYPE_INT32;
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
   cuuint32_t box[3] = {b0, b1, 1};
@@ -313,6 +392,20 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   // an MN-major B slice is made of 128-byte-wide TMA boxes, so the slice one CTA stages must reach 128 bytes
   const int min_bn = (d.trans_b ? 32 : 128 / es) * (u.pair ? 2 : 1);
   u.bn = pick_bn(d.N, u.tiles_m, d.batch, u.pair ? sms / 2 : sms, min_bn < 64 && (u.pair || plan->promote) ? 64 : min_bn);
+  // Tile order.  With the M index fastest the tiles in flight share one B slice and sweep A, so A is re-read from DRAM
+  // once per N tile unless it stays in L2; with the N index fastest it is B that is swept.  Take the cheaper one.
+  {
+    const double a_bytes = (double)d.M * d.K * es, b_bytes = (double)d.N * d.K * es, l2_fit = 48e6;
+    const double tiles_n = (double)((d.N + u.bn - 1) / u.bn);
+    const double cost_m = b_bytes + (a_bytes <= l2_fit ? a_bytes : tiles_n * a_bytes);
+    const double cost_n = a_bytes + (b_bytes <= l2_fit ? b_bytes : (double)u.tiles_m * b_bytes);
+    u.raster_n = (!u.pair && cost_n < cost_m) ? 1 : 0;
+    if (const char *e = getenv("SOFIE_B200_RASTER_N")) u.raster_n = (!u.pair && atoi(e) != 0) ? 1 : 0;
+  }
+  u.commit_group = 1;
+  u.l2_ahead = 0;
+  if (const char *e = getenv("SOFIE_B200_L2_AHEAD")) { const int c = atoi(e); if (c >= 0 && c <= 64) u.l2_ahead = c; }
+  if (const char *e = getenv("SOFIE_B200_PAIR_GROUP")) { const int c = atoi(e); if (c >= 1 && c <= 3) u.commit_group = c; }
   u.promote_chunk = 8;   // 32 MMA steps per accumulation: truncation bias below 2e-6 relative even for same-sign data
   if (const char *e = getenv("SOFIE_B200_PROMOTE_CHUNK")) { const int c = atoi(e); if (c >= 1 && c <= 64) u.promote_chunk = c; }
   u.b_rows = u.pair ? u.bn / 2 : u.bn;
@@ -325,12 +418,14 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.tmem_cols = 32;
   while (u.tmem_cols < 2u * u.bn) u.tmem_cols <<= 1;
 
-  const size_t budget = 227 * 1024 - 1024 /*alignment*/ - 512 /*barriers*/;
+  const size_t epi_bytes = (u.pair ? 4 : 8) * 4096;   // staging buffers of the epilogue warps
+  const size_t budget = 227 * 1024 - 1024 /*alignment*/ - UMMA_TAIL_BYTES /*barriers*/ - epi_bytes;
   int stages = (int)(budget / (u.a_stage_bytes + u.b_stage_bytes));
   if (stages > 8) stages = 8;
   if (stages < 2) return 1;
+  if (u.pair) stages = stages / u.commit_group * u.commit_group;   // release groups never straddle the ring's wrap
   u.stages = stages;
-  plan->smem_bytes = (size_t)stages * (u.a_stage_bytes + u.b_stage_bytes) + 1024 + 512;
+  plan->smem_bytes = (size_t)stages * (u.a_stage_bytes + u.b_stage_bytes) + 1024 + UMMA_TAIL_BYTES + epi_bytes;
 
   u.a_mn = d.trans_a ? 1 : 0;   // stored [K,M]: M contiguous
   u.b_mn = d.trans_b ? 0 : 1;   // stored [K,N]: N contiguous
@@ -452,15 +547,29 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
   UmmaParams u = plan->up;
   u.ep = ep;
   if (((uintptr_t)ep.Y % 16) != 0) u.vec_ok = 0;
+  // Tensor map of Y for the epilogue's bulk stores: box = one 128-byte row segment x the 32 rows of an epilogue warp.
+  u.y_tma = 0;
+  if (u.vec_ok && !u.pair && !plan->promote && !getenv("SOFIE_B200_NO_TMA_STORE")) {
+    const sofie_b200_gemm_desc &d = plan->desc;
+    const int ys = dtype_size(d.y_dtype);
+    if (ep.Y != plan->cached_y) {
+      const uint64_t s2 = d.batch > 1 ? (uint64_t)d.stride_y * ys : (uint64_t)d.M * d.ldy * ys;
+      rc = encode_map(&plan->tm_y, d.y_dtype, ep.Y, (uint64_t)d.N, (uint64_t)d.M, (uint64_t)d.batch, (uint64_t)d.ldy * ys, s2,
+                      (uint32_t)(128 / ys), 32);
+      if (rc) return rc;
+      plan->cached_y = ep.Y;
+    }
+    u.y_tma = 1;
+  }
   if (u.pair) return umma_pair_launch(plan, u);
   if (plan->promote) return umma_promote_launch(plan, u);
   cudaStream_t st = plan->ctx->stream;
   dim3 grid(plan->grid), block(UMMA_THREADS);
   switch (plan->kind) {
-    case KIND_I8: umma_gemm_kernel<KIND_I8><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, u); break;
-    case KIND_F8: umma_gemm_kernel<KIND_F8><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, u); break;
-    case KIND_F16: umma_gemm_kernel<KIND_F16><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, u); break;
-    default: umma_gemm_kernel<KIND_TF32><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, u); break;
+    case KIND_I8: umma_gemm_kernel<KIND_I8><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u); break;
+    case KIND_F8: umma_gemm_kernel<KIND_F8><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u); break;
+    case KIND_F16: umma_gemm_kernel<KIND_F16><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u); break;
+    default: umma_gemm_kernel<KIND_TF32><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u); break;
   }
   SB_CUDA(cudaGetLastError());
   plan->ctx->launches++;

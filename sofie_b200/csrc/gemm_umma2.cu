@@ -27,7 +27,7 @@ namespace sb200 {
 using namespace ptx;
 
 template <int KIND>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(UMMA_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(UMMA_PAIR_THREADS, 1)
 umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                       const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -45,6 +45,7 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
   const uint32_t bar_tempty = bar_tfull + 16;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail + 16 * stages + 32);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  const uint32_t epi_stage = smem_u32(tail) + UMMA_TAIL_BYTES;   // 4 KB per epilogue warp (coalesced_store)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -86,7 +87,14 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      ROLE_TIMER(w_empty);
+      ROLE_TIMER(t_begin);
+#ifdef SB200_ROLE_TIMERS
+      t_begin = clock64();
+#endif
       const uint32_t full_leader = mapa(bar_full, 0);
+      const uint32_t group = p.commit_group;
+      uint32_t gpos = 0;
       for (long long t = first; t < p.num_tiles && ok; t += step) {
         const int b = (int)(t / tiles_per_batch);
         const int r = (int)(t % tiles_per_batch);
@@ -94,11 +102,13 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         const int n0 = (r / p.tiles_m) * p.bn + (int)rank * p.b_rows;
         const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+          // the empty barrier of a release group is that of its first stage (see the MMA issuer)
+          if (gpos == 0 && !ROLE_WAIT(w_empty, mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag))) {
             raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_EMPTY);
             ok = false;
             break;
           }
+          if (++gpos == group) gpos = 0;
           const uint32_t full = full_leader + 8 * stage;
           if (leader) mbar_arrive_expect_tx(bar_full + 8 * stage, 2u * (p.a_stage_bytes + p.b_stage_bytes));
           const int k0 = kb * p.kb_elems;
@@ -117,6 +127,7 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
           if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
         }
       }
+      ROLE_REPORT("[cta %d] producer: total %lld, waiting for a free stage %lld\n", blockIdx.x, clock64() - t_begin, w_empty);
       if (!ok) {
         const uint64_t t0 = globaltimer();
         while (globaltimer() - t0 < 200000ull) {}
@@ -128,33 +139,61 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
+      ROLE_TIMER(w_full);
+      ROLE_TIMER(w_tempty);
+      ROLE_TIMER(c_fence);
+      ROLE_TIMER(c_mma);
+      ROLE_TIMER(c_commit);
+      ROLE_TIMER(sec_t0);
+      ROLE_TIMER(t_begin);
+#ifdef SB200_ROLE_TIMERS
+      t_begin = clock64();
+#endif
       const uint32_t empty_peer = mapa(bar_empty, peer), tfull_peer = mapa(bar_tfull, peer);
+      uint32_t gpos = 0;   // position of the current stage inside its release group
+      // descriptor words that do not change inside the loop, kept in registers
+      const uint64_t a_hi = (uint64_t)p.a_desc_hi << 32, b_hi = (uint64_t)p.b_desc_hi << 32;
+      const uint32_t a_lo0 = p.a_desc_lo | ((smem_a >> 4) & 0x3fffu), b_lo0 = p.b_desc_lo | ((smem_b >> 4) & 0x3fffu);
+      const uint32_t a_step = p.a_stage_bytes >> 4, b_step = p.b_stage_bytes >> 4;
+      const uint32_t a_kadv = p.a_kadv, b_kadv = p.b_kadv, idesc = p.idesc;
+      const int num_kb = p.num_kb;
+      const uint32_t group = p.commit_group;
       for (long long t = first; t < p.num_tiles && ok; t += step) {
-        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag)) {
+        if (!ROLE_WAIT(w_tempty, mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag))) {
           raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_EMPTY);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * p.bn;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ROLE_WAIT(w_full, mbar_wait(bar_full + 8 * stage, phase, abort_flag))) {
             raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_FULL);
             ok = false;
             break;
           }
+          ROLE_SECTION_BEGIN();
           tc_fence_after();
-          const uint32_t sa = smem_a + stage * p.a_stage_bytes;
-          const uint32_t sb = smem_b + stage * p.b_stage_bytes;
-          const uint32_t a_lo = p.a_desc_lo | ((sa >> 4) & 0x3fffu);
-          const uint32_t b_lo = p.b_desc_lo | ((sb >> 4) & 0x3fffu);
+          ROLE_SECTION_END(c_fence);
+          const uint32_t a_lo = a_lo0 + stage * a_step;
+          const uint32_t b_lo = b_lo0 + stage * b_step;
+          ROLE_SECTION_BEGIN();
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint64_t ad = ((uint64_t)p.a_desc_hi << 32) | (uint64_t)(a_lo + k * p.a_kadv);
-            const uint64_t bd = ((uint64_t)p.b_desc_hi << 32) | (uint64_t)(b_lo + k * p.b_kadv);
-            umma_pair<KIND>(d_tmem, ad, bd, p.idesc, (kb | k) != 0 ? 1u : 0u);
+            const uint64_t ad = a_hi | (uint64_t)(a_lo + k * a_kadv);
+            const uint64_t bd = b_hi | (uint64_t)(b_lo + k * b_kadv);
+            umma_pair<KIND>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          tc_commit_pair(bar_empty + 8 * stage);     // this CTA's producer may refill the stage
-          tc_commit_pair(empty_peer + 8 * stage);    // and so may the peer's
+          ROLE_SECTION_END(c_mma);
+          ROLE_SECTION_BEGIN();
+          // Stages are released in groups of `commit_group` consecutive stages that share the empty barrier of the
+          // group's first stage: a commit of a CTA pair is expensive for the tensor pipes of both SMs.
+          if (++gpos == group) {
+            const uint32_t first = bar_empty + 8 * (stage + 1 - group);
+            tc_commit_pair(first);                              // this CTA's producer may refill the group
+            tc_commit_pair(first + (empty_peer - bar_empty));    // and so may the peer's
+            gpos = 0;
+          }
+          ROLE_SECTION_END(c_commit);
           if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
@@ -162,39 +201,39 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         tc_commit_pair(tfull_peer + 8 * acc);
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
+      ROLE_REPORT("[cta %d] mma issuer: total %lld, waiting for operands %lld, for a drained accumulator %lld\n", blockIdx.x,
+                  clock64() - t_begin, w_full, w_tempty);
+      ROLE_REPORT("[cta %d] mma issuer sections: fence %lld, issuing MMAs %lld, commits %lld\n", blockIdx.x, c_fence, c_mma, c_commit);
     }
   } else {
     // ------------------------------ epilogue (each CTA: its own 128 rows) ------------------
     const int quad = warp & 3;
     uint32_t acc = 0, acc_phase = 0;
     const uint32_t tempty_leader = mapa(bar_tempty, 0);
+    ROLE_TIMER(w_tfull);
+    ROLE_TIMER(t_begin);
+#ifdef SB200_ROLE_TIMERS
+    t_begin = clock64();
+#endif
     for (long long t = first; t < p.num_tiles; t += step) {
       const int b = (int)(t / tiles_per_batch);
       const int r = (int)(t % tiles_per_batch);
       const int m0 = (r % p.tiles_m) * (2 * UMMA_BM) + (int)rank * UMMA_BM;
       const int n0 = (r / p.tiles_m) * p.bn;
-      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+      if (!ROLE_WAIT(w_tfull, mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag))) {
         raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_FULL);
         break;
       }
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * p.bn;
-      for (int c = 0; c < p.bn; c += 32) {
-        if (n0 + c >= p.N) break;
-        uint32_t raw[32];
-        tmem_ld_x32(taddr + c, raw);
-        tmem_ld_wait();
-        if (row < p.M) {
-          const int ncols = min(32, p.N - (n0 + c));
-          store_chunk(p.ep, raw, b, row, n0 + c, ncols, p.vec_ok != 0);
-        }
-      }
+      drain_accumulator<KIND == KIND_I8>(p.ep, taddr, min(p.bn, p.N - n0), 0, 1, b, row, n0, p.vec_ok != 0, epi_stage + (uint32_t)(warp - 2) * 4096u, p.M);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * acc);
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
+    if (threadIdx.x == 64) { ROLE_REPORT("[cta %d] epilogue: total %lld, waiting for an accumulator %lld\n", blockIdx.x, clock64() - t_begin, w_tfull); }
   }
 
   tc_fence_before();
@@ -225,7 +264,7 @@ int umma_pair_set_smem(int kind, size_t smem_bytes) {
 int umma_pair_max_clusters(int kind, size_t smem_bytes, int *out) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2, 1, 1);
-  cfg.blockDim = dim3(UMMA_THREADS, 1, 1);
+  cfg.blockDim = dim3(UMMA_PAIR_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem_bytes;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
@@ -248,7 +287,7 @@ int umma_pair_max_clusters(int kind, size_t smem_bytes, int *out) {
 int umma_pair_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u) {
   // the cluster shape is part of the kernel (__cluster_dims__), so a plain launch forms the pairs
   cudaStream_t st = plan->ctx->stream;
-  dim3 grid(plan->grid), block(UMMA_THREADS);
+  dim3 grid(plan->grid), block(UMMA_PAIR_THREADS);
   switch (plan->kind) {
     case KIND_I8: umma_pair_gemm_kernel<KIND_I8><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, u); break;
     case KIND_F8: umma_pair_gemm_kernel<KIND_F8><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, u); break;

@@ -40,6 +40,7 @@ umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   const uint32_t bar_tempty = bar_tfull + 16;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail + 16 * stages + 32);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  const uint32_t epi_stage = smem_u32(tail) + UMMA_TAIL_BYTES;   // 4 KB per epilogue warp (coalesced_store)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -77,8 +78,10 @@ umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       for (long long t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
         const int b = (int)(t / tiles_per_batch);
         const int r = (int)(t % tiles_per_batch);
-        const int m0 = (r % p.tiles_m) * UMMA_BM;
-        const int n0 = (r / p.tiles_m) * p.bn;
+        int tm, tn;
+        tile_mn(p, r, tm, tn);
+        const int m0 = tm * UMMA_BM;
+        const int n0 = tn * p.bn;
         const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
@@ -146,8 +149,10 @@ umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
     for (long long t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
       const int b = (int)(t / tiles_per_batch);
       const int r = (int)(t % tiles_per_batch);
-      const int m0 = (r % p.tiles_m) * UMMA_BM;
-      const int n0 = (r / p.tiles_m) * p.bn;
+      int tm, tn;
+      tile_mn(p, r, tm, tn);
+      const int m0 = tm * UMMA_BM;
+      const int n0 = tn * p.bn;
       float sum[PROMOTE_HALF_MAX];
 #pragma unroll
       for (int c = 0; c < PROMOTE_HALF_MAX; ++c) sum[c] = 0.f;
@@ -179,11 +184,14 @@ umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
 #pragma unroll
       for (int c = 0; c < PROMOTE_HALF_MAX; c += 32) {
         const int col = n0 + col_base + c;
-        if (c < half_cols && col < p.N && row < p.M) {
+        if (c < half_cols && col < p.N) {   // warp-uniform
           uint32_t raw[32];
 #pragma unroll
           for (int u = 0; u < 32; ++u) raw[u] = __float_as_uint(sum[c + u]);
-          store_chunk(p.ep, raw, b, row, col, min(32, p.N - col), p.vec_ok != 0);
+          const uint32_t my_stage = epi_stage + (uint32_t)(warp - 2) * 4096u;
+          if (store_chunk(p.ep, raw, b, row, col, min(32, p.N - col), p.vec_ok != 0, my_stage, p.M))
+            flush_staged(my_stage, y_address(p.ep, b, row - lane, col), p.ep.ldy * out_elem_bytes(p.ep.y_dtype),
+                         (int)max(0LL, min(32LL, (long long)p.M - (row - lane))), 2 * out_elem_bytes(p.ep.y_dtype));
         }
       }
     }

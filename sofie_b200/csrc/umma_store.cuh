@@ -15,6 +15,50 @@ __device__ __forceinline__ void st_v4(void *p, uint32_t a, uint32_t b, uint32_t 
   *reinterpret_cast<uint4 *>(p) = make_uint4(a, b, c, d);
 }
 
+// Coalesced stores of the epilogue.  In the accumulator a lane owns a ROW, so a direct 16-byte store per lane
+// touches 32 different 128-byte lines per instruction, the L1 spends 32 cycles on it, and rows are written in
+// pieces shorter than a line.  Instead the finished 16-byte units of up to 128 bytes per row (one 32-column
+// chunk of 4-byte outputs, two of 2-byte, four of 1-byte outputs) are collected in a per-warp staging buffer in
+// shared memory (32 rows x 128 bytes, XOR-swizzled: conflict-free both ways) and flushed with consecutive lanes
+// holding consecutive units of the same row: one store instruction then writes four whole 128-byte lines.
+//
+// stage_units: lane (= row) writes its U units of the chunk at unit offset `slot * U` of its row.
+template <int U>
+__device__ __forceinline__ void stage_units(uint32_t stage, const uint32_t (&w)[4 * U], int slot) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t my_row = stage + lane * 128;
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + (((slot * U + u) ^ (lane & 7)) << 4)), "r"(w[4 * u]),
+                 "r"(w[4 * u + 1]), "r"(w[4 * u + 2]), "r"(w[4 * u + 3])
+                 : "memory");
+  }
+}
+
+// flush_staged: writes the first `units` 16-byte units of each of the first `rows_valid` rows of the buffer to
+// y_row0 + row * ldy_bytes.  All lanes of the warp call it; the buffer may be refilled right after it returns.
+__device__ __forceinline__ void flush_staged(uint32_t stage, uint8_t *y_row0, long long ldy_bytes, int rows_valid, int units) {
+  const int lane = threadIdx.x & 31;
+  __syncwarp();   // every lane's units are in the buffer
+  const int u = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    uint32_t a, b, c, d;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(stage + r * 128 + ((u ^ (r & 7)) << 4)) : "memory");
+    if (r < rows_valid && u < units) st_v4(y_row0 + r * ldy_bytes + u * 16, a, b, c, d);
+  }
+  __syncwarp();   // reads done before anyone overwrites the buffer
+}
+
+// Chunks per 128-byte row segment for an output type: the group a warp stages before it flushes.
+__device__ __forceinline__ int chunks_per_flush(int y_dtype) {
+  return (y_dtype == SOFIE_B200_F32 || y_dtype == SOFIE_B200_I32) ? 1 : (y_dtype == SOFIE_B200_BF16 ? 2 : 4);
+}
+__device__ __forceinline__ int out_elem_bytes(int y_dtype) {
+  return (y_dtype == SOFIE_B200_F32 || y_dtype == SOFIE_B200_I32) ? 4 : (y_dtype == SOFIE_B200_BF16 ? 2 : 1);
+}
+
 // Applies the fused epilogue to one 32-column chunk of one accumulator row and stores it.
 //
 // The work is staged as passes over a register array, with every data-independent decision
@@ -23,10 +67,20 @@ __device__ __forceinline__ void st_v4(void *p, uint32_t a, uint32_t b, uint32_t 
 // branches inside the element loop would serialise the whole epilogue.  Absent scales multiply
 // by 1.0f and an absent bias adds 0.0f; both are exact, so the value equals the documented
 // step-by-step formula (sofie_b200_epilogue) bit for bit.
-__device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t (&raw)[32], long long b, long long row,
-                                            int col0, int ncols, bool vec) {
+//
+// `row` is this lane's row; lane 0 of the warp holds row `row - lane`.  With `stage` != 0 (shared-memory address of
+// the warp's 4 KB staging buffer) a full, aligned chunk is not stored but staged at position `slot` of the row's
+// 128-byte segment, the function returns true, and the caller flushes the buffer with flush_staged() once the
+// segment is complete; then EVERY lane of the warp must make the call (rows at or past `rows_total` are computed
+// but never stored).  Otherwise the chunk is stored directly and the function returns false.
+__device__ __forceinline__ bool store_chunk(const EpiParams &ep, const uint32_t (&raw)[32], long long b, long long row,
+                                            int col0, int ncols, bool vec, uint32_t stage = 0, long long rows_total = 0,
+                                            int slot = 0) {
   const bool full = ncols == 32;
   const long long off = b * ep.stride_y + row * ep.ldy + col0;
+  const bool staged = stage != 0 && vec && full;       // warp-uniform
+  if (!staged && stage != 0 && row >= rows_total) return false;   // direct path: rows past the end store nothing
+  const long long rr = (stage != 0 && row >= rows_total) ? rows_total - 1 : row;   // row whose per-row operands are read
 
   if (ep.y_dtype == SOFIE_B200_I32) {  // raw integer accumulator (+ int32 bias)
     int a[32];
@@ -36,12 +90,18 @@ __device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t 
 #pragma unroll
       for (int c = 0; c < 32; ++c) a[c] += (full || c < ncols) ? ((const int *)ep.bias)[col0 + c] : 0;
     } else if (ep.bias_mode == SOFIE_B200_BIAS_ROW_I32) {
-      const int br = ((const int *)ep.bias)[row];
+      const int br = ((const int *)ep.bias)[rr];
 #pragma unroll
       for (int c = 0; c < 32; ++c) a[c] += br;
     }
     int *y = (int *)ep.Y + off;
-    if (vec && full) {
+    if (staged) {
+      uint32_t w[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) w[c] = (uint32_t)a[c];
+      stage_units<8>(stage, w, slot);
+      return true;
+    } else if (vec && full) {
 #pragma unroll
       for (int c = 0; c < 32; c += 4) st_v4(y + c, a[c], a[c + 1], a[c + 2], a[c + 3]);
     } else {
@@ -49,7 +109,7 @@ __device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t 
       for (int c = 0; c < 32; ++c)
         if (c < ncols) y[c] = a[c];
     }
-    return;
+    return false;
   }
 
   float v[32];
@@ -59,7 +119,7 @@ __device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t 
 #pragma unroll
       for (int c = 0; c < 32; ++c) v[c] = (float)((int)raw[c] + ((full || c < ncols) ? ((const int *)ep.bias)[col0 + c] : 0));
     } else {
-      const int br = ep.bias_mode == SOFIE_B200_BIAS_ROW_I32 ? ((const int *)ep.bias)[row] : 0;
+      const int br = ep.bias_mode == SOFIE_B200_BIAS_ROW_I32 ? ((const int *)ep.bias)[rr] : 0;
 #pragma unroll
       for (int c = 0; c < 32; ++c) v[c] = (float)((int)raw[c] + br);
     }
@@ -69,7 +129,7 @@ __device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t 
   }
   // 2. scales, in the documented order: row, column, alpha
   if (ep.row_scale) {
-    const float rs = ep.row_scale[row];
+    const float rs = ep.row_scale[rr];
 #pragma unroll
     for (int c = 0; c < 32; ++c) v[c] = __fmul_rn(v[c], rs);
   }
@@ -107,7 +167,7 @@ __device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t 
       }
       break;
     case SOFIE_B200_BIAS_ROW_F32: {
-      const float br = ((const float *)ep.bias)[row];
+      const float br = ((const float *)ep.bias)[rr];
 #pragma unroll
       for (int c = 0; c < 32; ++c) v[c] = __fadd_rn(v[c], br);
       break;
@@ -119,7 +179,7 @@ __device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t 
       break;
     }
     case SOFIE_B200_BIAS_FULL_F32: {
-      const float *cr = (const float *)ep.bias + b * ep.stride_c + row * ep.ldc + col0;
+      const float *cr = (const float *)ep.bias + b * ep.stride_c + rr * ep.ldc + col0;
 #pragma unroll
       for (int c = 0; c < 32; ++c)
         if (full || c < ncols) v[c] = __fadd_rn(v[c], __fmul_rn(ep.beta, cr[c]));
@@ -128,7 +188,7 @@ __device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t 
     default: break;
   }
   if (ep.residual) {
-    const long long roff = b * ep.stride_r + row * ep.ldr + col0;
+    const long long roff = b * ep.stride_r + rr * ep.ldr + col0;
     if (ep.residual_dtype == SOFIE_B200_BF16) {
       const __nv_bfloat16 *r = (const __nv_bfloat16 *)ep.residual + roff;
 #pragma unroll
@@ -160,7 +220,13 @@ __device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t 
   // 5. convert and store
   if (ep.y_dtype == SOFIE_B200_F32) {
     float *y = (float *)ep.Y + off;
-    if (vec && full) {
+    if (staged) {
+      uint32_t w[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) w[c] = __float_as_uint(v[c]);
+      stage_units<8>(stage, w, slot);
+      return true;
+    } else if (vec && full) {
 #pragma unroll
       for (int c = 0; c < 32; c += 4)
         st_v4(y + c, __float_as_uint(v[c]), __float_as_uint(v[c + 1]), __float_as_uint(v[c + 2]), __float_as_uint(v[c + 3]));
@@ -171,7 +237,16 @@ __device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t 
     }
   } else if (ep.y_dtype == SOFIE_B200_BF16) {
     __nv_bfloat16 *y = (__nv_bfloat16 *)ep.Y + off;
-    if (vec && full) {
+    if (staged) {
+      uint32_t w[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * u], v[2 * u + 1]);
+        w[u] = *reinterpret_cast<uint32_t *>(&h2);
+      }
+      stage_units<4>(stage, w, slot);
+      return true;
+    } else if (vec && full) {
 #pragma unroll
       for (int c = 0; c < 32; c += 8) {
         uint32_t w[4];
@@ -199,7 +274,13 @@ __device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t 
 #pragma unroll
     for (int c = 0; c < 32; ++c) q[c] = (uint32_t)(int)fminf(fmaxf(rintf(v[c]) + zp, lo), hi) & 0xffu;
     uint8_t *y = (uint8_t *)ep.Y + off;
-    if (vec && full) {
+    if (staged) {
+      uint32_t w[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) w[u] = q[4 * u] | (q[4 * u + 1] << 8) | (q[4 * u + 2] << 16) | (q[4 * u + 3] << 24);
+      stage_units<2>(stage, w, slot);
+      return true;
+    } else if (vec && full) {
 #pragma unroll
       for (int c = 0; c < 32; c += 16) {
         uint32_t w[4];
@@ -213,6 +294,270 @@ __device__ __forceinline__ void store_chunk(const EpiParams &ep, const uint32_t 
       for (int c = 0; c < 32; ++c)
         if (c < ncols) y[c] = (uint8_t)q[c];
     }
+  }
+  return false;
+}
+
+// Neutral operands for features a launch does not use: the fast path below always multiplies by a column scale
+// and adds a column bias, and reads these instead of branching.  x * 1.0f and x + (-0.0f) return x bit for bit
+// (also for x = -0.0f, which + 0.0f would turn into +0.0f).
+__device__ __align__(16) const float g_epi_ones[32] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f,
+                                                       1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+__device__ __align__(16) const float g_epi_negzero[32] = {-0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f,
+                                                          -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f, -0.f};
+__device__ __align__(16) const int g_epi_izero[32] = {};
+
+// The fast path (epi_values_fast + epi_finish_fast): the same epilogue as store_chunk() for the common case -- a full 32-column chunk, staged, with 16-byte aligned
+// per-column vectors and no full-matrix bias -- written so that a launch takes almost no branches.  Every taken
+// branch costs an epilogue warp an instruction-fetch bubble that nothing hides (one or two warps per scheduler),
+// and a dozen "skip this feature" jumps per chunk made the epilogue slower than the main loop of a K = 512 tile.
+// Scales and biases are therefore always applied, with neutral operands when absent; only the residual, the
+// activation and the output type branch, and the rare cases are marked unlikely so they sit out of line.
+// Operation order and rounding are those of store_chunk(): the results are bit-identical.
+// Two fp32 values in one 64-bit register and the packed arithmetic of sm_100 on them: each half is rounded exactly
+// as the scalar instruction would round it, at half the instruction count.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// First half of the fast path: everything that reads the raw accumulator -- integer bias, conversion, the three
+// scales and the additive bias terms -- into v[32].  When it returns, `raw` is dead and the caller may already
+// load the next chunk into it.  Returns false when the chunk was finished here (int32 output: staged as is).
+template <bool ACC_INT>
+__device__ __forceinline__ bool epi_values_fast(const EpiParams &ep, const uint32_t (&raw)[32], float (&v)[32], long long rr, int col0,
+                                                uint32_t stage, int slot) {
+  const int mode = ep.bias_mode;
+  const int4 *bip = reinterpret_cast<const int4 *>(g_epi_izero);
+  int rbi = 0;
+  if (ACC_INT) {
+    if (mode == SOFIE_B200_BIAS_COL_I32) bip = reinterpret_cast<const int4 *>((const int *)ep.bias + col0);
+    if (mode == SOFIE_B200_BIAS_ROW_I32) rbi = ((const int *)ep.bias)[rr];
+  }
+  if (__builtin_expect(ep.y_dtype == SOFIE_B200_I32, 0)) {  // raw integer accumulator (+ int32 bias)
+    uint32_t w[32];
+#pragma unroll
+    for (int c = 0; c < 32; c += 4) {
+      const int4 bi = bip[c >> 2];
+      w[c] = (uint32_t)((int)raw[c] + bi.x + rbi); w[c + 1] = (uint32_t)((int)raw[c + 1] + bi.y + rbi);
+      w[c + 2] = (uint32_t)((int)raw[c + 2] + bi.z + rbi); w[c + 3] = (uint32_t)((int)raw[c + 3] + bi.w + rbi);
+    }
+    stage_units<8>(stage, w, slot);
+    return false;
+  }
+  float rs = 1.f;
+  if (ep.row_scale) rs = ep.row_scale[rr];
+  const float4 *csp = reinterpret_cast<const float4 *>(ep.col_scale ? ep.col_scale + col0 : g_epi_ones);
+  const float4 *bfp = reinterpret_cast<const float4 *>(mode == SOFIE_B200_BIAS_COL_F32 ? (const float *)ep.bias + col0 : g_epi_negzero);
+  float rbf = -0.f;
+  if (mode == SOFIE_B200_BIAS_ROW_F32) rbf = ((const float *)ep.bias)[rr];
+  if (mode == SOFIE_B200_BIAS_SCALAR_F32) rbf = ((const float *)ep.bias)[0];
+  const uint64_t rs2 = pack2(rs, rs), alpha2 = pack2(ep.alpha, ep.alpha), rbf2 = pack2(rbf, rbf);
+#pragma unroll
+  for (int c = 0; c < 32; c += 4) {
+    const float4 cs = csp[c >> 2], bf = bfp[c >> 2];
+    float x0, x1, x2, x3;
+    if (ACC_INT) {
+      const int4 bi = bip[c >> 2];
+      x0 = (float)((int)raw[c] + bi.x + rbi); x1 = (float)((int)raw[c + 1] + bi.y + rbi);
+      x2 = (float)((int)raw[c + 2] + bi.z + rbi); x3 = (float)((int)raw[c + 3] + bi.w + rbi);
+    } else {
+      x0 = __uint_as_float(raw[c]); x1 = __uint_as_float(raw[c + 1]); x2 = __uint_as_float(raw[c + 2]); x3 = __uint_as_float(raw[c + 3]);
+    }
+    const uint64_t a = fadd2(fadd2(fmul2(fmul2(fmul2(pack2(x0, x1), rs2), pack2(cs.x, cs.y)), alpha2), pack2(bf.x, bf.y)), rbf2);
+    const uint64_t d = fadd2(fadd2(fmul2(fmul2(fmul2(pack2(x2, x3), rs2), pack2(cs.z, cs.w)), alpha2), pack2(bf.z, bf.w)), rbf2);
+    unpack2(a, v[c], v[c + 1]);
+    unpack2(d, v[c + 2], v[c + 3]);
+  }
+  return true;
+}
+
+// Second half of the fast path: residual, activation, conversion to the output type, staging.
+__device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float (&v)[32], long long b, long long rr, int col0, uint32_t stage,
+                                                int slot) {
+  if (ep.residual) {
+    const long long roff = b * ep.stride_r + rr * ep.ldr + col0;
+    if (ep.residual_dtype == SOFIE_B200_BF16) {
+      if (ep.residual_aligned) {
+        const uint4 *r = reinterpret_cast<const uint4 *>((const __nv_bfloat16 *)ep.residual + roff);
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
+          const uint4 q = r[c >> 3];
+          const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {   // a bf16 is the upper half of the fp32 with the same value
+            v[c + 2 * u] = __fadd_rn(v[c + 2 * u], __uint_as_float(ww[u] << 16));
+            v[c + 2 * u + 1] = __fadd_rn(v[c + 2 * u + 1], __uint_as_float(ww[u] & 0xffff0000u));
+          }
+        }
+      } else {
+        const __nv_bfloat16 *r1 = (const __nv_bfloat16 *)ep.residual + roff;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] = __fadd_rn(v[c], __bfloat162float(r1[c]));
+      }
+    } else {
+      const float *r = (const float *)ep.residual + roff;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = __fadd_rn(v[c], r[c]);
+    }
+  }
+  if (ep.act != SOFIE_B200_ACT_NONE) {
+    if (ep.act == SOFIE_B200_ACT_RELU) {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_RELU, 0.f);
+    } else if (ep.act == SOFIE_B200_ACT_GELU_ERF) {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_GELU_ERF, 0.f);
+    } else {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], ep.act, ep.act_alpha);
+    }
+  }
+  if (ep.y_dtype == SOFIE_B200_BF16) {
+    uint32_t w[16];
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * u], v[2 * u + 1]);
+      w[u] = *reinterpret_cast<uint32_t *>(&h2);
+    }
+    stage_units<4>(stage, w, slot);
+  } else if (ep.y_dtype == SOFIE_B200_F32) {
+    uint32_t w[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) w[c] = __float_as_uint(v[c]);
+    stage_units<8>(stage, w, slot);
+  } else {  // I8 / U8: ONNX rounding (half to even), zero point, saturate
+    const int lo = ep.y_dtype == SOFIE_B200_I8 ? -128 : 0, hi = ep.y_dtype == SOFIE_B200_I8 ? 127 : 255;
+    const int zp = ep.out_zp;
+    if (__builtin_expect(ep.out_scale != 1.f, 0)) {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = __fdiv_rn(v[c], ep.out_scale);
+    }
+    // rint(v) + zp saturated to [lo, hi], in integers: v is first clamped to +-2^30 (far outside [lo - zp, hi - zp],
+    // NaN goes to -2^30 as fmaxf drops it, which saturates to lo like the float formula), so neither the conversion
+    // nor the addition can overflow.
+    int q[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) q[c] = min(max(__float2int_rn(fminf(fmaxf(v[c], -1073741824.f), 1073741824.f)) + zp, lo), hi);
+    uint32_t w[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const uint32_t lo2 = __byte_perm((uint32_t)q[4 * u], (uint32_t)q[4 * u + 1], 0x0040);      // bytes q0, q1
+      const uint32_t hi2 = __byte_perm((uint32_t)q[4 * u + 2], (uint32_t)q[4 * u + 3], 0x0040);  // bytes q2, q3
+      w[u] = __byte_perm(lo2, hi2, 0x5410);
+    }
+    stage_units<2>(stage, w, slot);
+  }
+}
+
+#ifdef SB200_ROLE_TIMERS
+// cycles thread 64 of CTA 0 spent in the parts of drain_accumulator (debug build only)
+__device__ long long g_drain_cycles[6];
+#define DRAIN_T0() const long long dt0__ = clock64()
+#define DRAIN_ADD(i) if (blockIdx.x == 0 && threadIdx.x == 64) g_drain_cycles[i] += clock64() - dt0__
+#else
+#define DRAIN_T0()
+#define DRAIN_ADD(i)
+#endif
+
+// Address of element (row0, col) of batch b of Y, in bytes.
+__device__ __forceinline__ uint8_t *y_address(const EpiParams &ep, long long b, long long row0, long long col) {
+  return (uint8_t *)ep.Y + (b * ep.stride_y + row0 * ep.ldy + col) * out_elem_bytes(ep.y_dtype);
+}
+
+// One epilogue warp drains its share of a finished accumulator: the 32 tensor-memory lanes at `taddr` (lane = row
+// `row` of Y), columns [0, c_end) of the tile that starts at column n0 of Y.  Chunks of 32 columns are taken in
+// groups of chunks_per_flush() consecutive chunks (one 128-byte row segment); this warp takes groups first_group,
+// first_group + group_stride, ...  The tcgen05.ld of the next chunk is in flight while the current one goes through
+// the epilogue.
+//
+// With a tensor map of Y (`tm_y`, 128B swizzle, box = 128 bytes x 32 rows: exactly the staging buffer's layout, which
+// must then be 1024-byte aligned) a complete row segment leaves as ONE bulk tensor store issued by lane 0: the TMA
+// unit clips rows past the end, and the warp's load/store unit is out of the picture.  The buffer is reused only
+// after the store has read it (bulk_wait_read_all before the next group is staged, and before the function returns).
+template <bool ACC_INT>
+__device__ __forceinline__ void drain_accumulator(const EpiParams &ep, uint32_t taddr, int c_end, int first_group, int group_stride,
+                                                  long long b, long long row, int n0, bool vec, uint32_t stage, long long rows_total,
+                                                  const CUtensorMap *tm_y = nullptr) {
+  const int G = chunks_per_flush(ep.y_dtype);
+  const int units_per_chunk = 2 * out_elem_bytes(ep.y_dtype);
+  const int nch = (c_end + 31) >> 5;
+  const long long row0 = row - (threadIdx.x & 31);
+  const long long left = rows_total - row0;
+  const int rows_valid = left < 0 ? 0 : (left > 32 ? 32 : (int)left);
+  const bool fast = vec && ep.fast && rows_valid > 0;
+  int ch = first_group * G, j = 0;   // current chunk and its position in its group
+  if (ch >= nch) return;
+  int units = 0, seg_col = 0;
+  bool store_pending = false;
+  // One register buffer: the fast path reads the raw accumulator only in its first half, so the tcgen05.ld of the
+  // next chunk is issued into the same registers right after that and flies during the second half and the flush.
+  uint32_t raw[32];
+  ptx::tmem_ld_x32(taddr + 32 * ch, raw);
+  while (true) {
+    { DRAIN_T0(); ptx::tmem_ld_wait(); DRAIN_ADD(0); }
+    int ch2 = ch + 1, j2 = j + 1;
+    if (j2 == G) { j2 = 0; ch2 += (group_stride - 1) * G; }
+    const bool has_next = ch2 < nch;
+    const int c = 32 * ch;
+    if (j == 0) {
+      units = 0; seg_col = c;
+      if (store_pending) {   // the previous segment's bulk store must have read the buffer before it is refilled
+        DRAIN_T0();
+        if ((threadIdx.x & 31) == 0) ptx::bulk_wait_read_all();
+        __syncwarp();
+        store_pending = false;
+        DRAIN_ADD(1);
+      }
+    }
+    { DRAIN_T0();
+      if (fast && c_end - c >= 32) {
+        const long long rr = row < rows_total ? row : rows_total - 1;   // rows past the end compute on the last row's operands
+        float v[32];
+        const bool more = epi_values_fast<ACC_INT>(ep, raw, v, rr, n0 + c, stage, j);
+        if (has_next) ptx::tmem_ld_x32(taddr + 32 * ch2, raw);
+        if (more) epi_finish_fast(ep, v, b, rr, n0 + c, stage, j);
+        units += units_per_chunk;
+      } else {
+        if (store_chunk(ep, raw, b, row, n0 + c, min(32, c_end - c), vec, stage, rows_total, j)) units += units_per_chunk;
+        if (has_next) ptx::tmem_ld_x32(taddr + 32 * ch2, raw);
+      }
+      DRAIN_ADD(2); }
+    if ((j == G - 1 || !has_next) && units > 0) {
+      DRAIN_T0();
+      if (tm_y != nullptr && units == 8) {
+        ptx::fence_proxy_async();   // this lane's staging writes become visible to the TMA unit
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) {
+          ptx::tma_store_3d(tm_y, stage, n0 + seg_col, (int)row0, (int)b);
+          ptx::bulk_commit_group();
+        }
+        store_pending = true;
+      } else {
+        flush_staged(stage, y_address(ep, b, row0, n0 + seg_col), ep.ldy * out_elem_bytes(ep.y_dtype), rows_valid, units);
+      }
+      DRAIN_ADD(3);
+    }
+    ch = ch2; j = j2;
+    if (!has_next) break;
+  }
+  if (store_pending) {
+    DRAIN_T0();
+    if ((threadIdx.x & 31) == 0) ptx::bulk_wait_read_all();
+    __syncwarp();
+    DRAIN_ADD(4);
   }
 }
 
