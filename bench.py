@@ -473,6 +473,120 @@ WORKLOADS["layernorm_bf16_65536x512"] = lambda: RowOp("layernorm", 65536, 512, "
 WORKLOADS["softmax_bf16_524288x128"] = lambda: RowOp("softmax", 524288, 128, "softmax_bf16_524288x128")
 
 
+class EncoderWorkload:
+    """Transformer encoder: 6 pre-LN layers, d_model 512, 8 heads, FFN 2048, Gelu, seq 128; bf16 activations, int8
+    per-channel weights dequantised in the contraction epilogue.  One step = one batch through all layers."""
+
+    def __init__(self, name: str, batch: int):
+        self.name, self.batch = name, batch
+        self.layers, self.seq, self.d_model, self.heads, self.ffn = 6, 128, 512, 8, 2048
+        self.metric = "transformer encoder inferences/s (sequences of 128 tokens)"
+        self.unit, self.dtype = "inferences/s", "bf16"
+
+
+def run_encoder(args, w) -> None:
+    import torch
+    import bench_encoder as be
+    from sofie_b200 import lib as L
+
+    flops = be.flops_per_sample(w.layers, w.seq, w.d_model, w.ffn)
+    rng = np.random.default_rng(7)
+    weights = be.make_weights(rng, w.layers, w.d_model, w.ffn)
+    config = {"workload": w.name, "layers": w.layers, "d_model": w.d_model, "heads": w.heads, "ffn": w.ffn, "seq_len": w.seq,
+              "batch_per_gpu": w.batch, "weights": "int8 per output channel, scale fused in the contraction epilogue",
+              "gflop_per_inference": flops / 1e9}
+
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        sys.path.insert(0, str(ROOT / "tests"))
+        from oracle_api import Oracle
+        load_oracle()   # builds the checker library if needed
+        o = Oracle(ROOT / "oracle" / "libsofie_oracle.so")
+        o.lib.so_threads.restype = C.c_int
+        o.lib.so_set_threads(os.cpu_count() or 1)
+        nb = 2   # sequences per CPU step: a bounded sample of the batch
+        x = be.f32_to_bf16_bits(rng.standard_normal((nb * w.seq, w.d_model)).astype(np.float32))
+        def cpu_step():
+            t0 = time.perf_counter()
+            be.encoder_oracle(o, x, weights, nb, w.seq, w.d_model, w.heads)
+            return time.perf_counter() - t0
+        for _ in range(min(args.warmup, 1)):
+            cpu_step()
+        steps = max(1, min(args.steps, 5))
+        t = sum(cpu_step() for _ in range(steps))
+        val = nb * steps / t
+        cores = int(o.lib.so_threads())
+        print(json.dumps({"impl": "reference", "metric": w.metric, "value": val, "unit": w.unit, "n_gpus": args.gpus, "steps": steps,
+                          "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * t / steps, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "f64 accumulate, bf16 tensors", "data": "synthetic", "config": config,
+                          "cpu_baseline": {"value": val, "unit": w.unit, "cores": cores, "kind": "port",
+                                           "sample": f"each step = {nb} of {w.batch} sequences through all {w.layers} layers"},
+                          "e2e": {"value": val, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+        return
+
+    from sofie_b200 import replicas
+    from sofie_b200.ops import Context
+    rep = replicas.init_from_env("nccl")
+    torch.cuda.set_device(rep.local_rank)
+    dev = f"cuda:{rep.local_rank}"
+    ctx = Context(rep.local_rank)
+    enc = be.EncoderB200(ctx, weights, w.batch, w.seq, w.d_model, w.heads, w.ffn, dev)
+    m = w.batch * w.seq
+    xs = [torch.randn(m, w.d_model, device=dev).to(torch.bfloat16) for _ in range(3)]   # activations per step: ~1.5 GB > L2
+    for i in range(max(3, args.warmup)):
+        enc(xs[i % 3])
+    ctx.sync()
+    sampler = ClockSampler(rep.local_rank)
+    replicas.barrier(rep)
+    torch.cuda.synchronize()
+    l0 = ctx.launches
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        enc(xs[i % 3])
+    e1.record()
+    torch.cuda.synchronize()
+    ctx.sync()
+    clocks = sampler.stop()
+    ms_local = e0.elapsed_time(e1)
+    ms = replicas.max_over_ranks(rep, ms_local)
+    launches = ctx.launches - l0
+    value = rep.world * w.batch * args.steps / (ms * 1e-3)
+    # end to end: tokens from pinned host memory in, final activations back out, every step
+    hx = xs[0].cpu().pin_memory()
+    hy = torch.empty_like(hx).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        xs[0].copy_(hx, non_blocking=True)
+        y = enc(xs[0])
+        hy.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+    t_e2e = replicas.max_over_ranks(rep, time.perf_counter() - t0)
+    if rep.is_root:
+        peaks = measured_peaks()
+        ach = flops * w.batch / (ms_local / args.steps * 1e-3) / 1e12
+        peak = peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]
+        print(json.dumps({"metric": w.metric, "value": value, "unit": w.unit, "n_gpus": rep.world, "steps": args.steps, "warmup": max(3, args.warmup),
+                          "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype,
+                          "data": "synthetic", "config": dict(config, l2="three input batches rotated; one step streams ~1.5 GB of activations (> 126 MiB L2)"),
+                          "clocks": clocks, "gpu_launches": int(launches),
+                          "e2e": {"value": rep.world * w.batch * e2e_steps / t_e2e, "unit": w.unit, "h2d_bytes_per_step": int(hx.numel() * 2),
+                                  "d2h_bytes_per_step": int(hy.numel() * 2), "steps": e2e_steps},
+                          "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+                                       "peak_source": f"bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS.json; whole step (all "
+                                                      f"{launches // max(1, args.steps)} launches), not one kernel"}}), flush=True)
+    enc.close()
+    ctx.close()
+    replicas.shutdown(rep)
+
+
+WORKLOADS["transformer_encoder_b512"] = lambda: EncoderWorkload("transformer_encoder_b512", 512)
+WORKLOADS["transformer_encoder_b64"] = lambda: EncoderWorkload("transformer_encoder_b64", 64)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -484,6 +598,8 @@ def main() -> None:
     w = WORKLOADS[args.workload]()
     if isinstance(w, RowOp):
         run_rowop(args, w)
+    elif isinstance(w, EncoderWorkload):
+        run_encoder(args, w)
     elif args.impl == "reference":
         run_reference(args, w)
     else:

@@ -264,6 +264,20 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
 int sofie_b200_conv_enqueue_noalloc(sofie_b200_ctx *ctx, const sofie_b200_conv_desc *desc, const void *X,
                                     const void *W, void *Y, const sofie_b200_epilogue *ep);
 
+/* ---- attention ------------------------------------------------------------------------- */
+
+/* Fused scaled-dot-product attention: out[b, :, h, :] = Softmax(scale * Q K^T) V for every batch b and head h, with
+ * Q, K, V read in place from the QKV projection's output, qkv [batch, seq, 3, heads, head_dim] (Q of all heads, then
+ * K, then V, per token), and out written as [batch, seq, heads * head_dim], the layout the output projection reads.
+ * One kernel replaces the graph the reference emits for an attention block -- Transpose, stacked MatMul
+ * (blas.gemmStridedBatched, ROperator_Gemm.hxx:991-1065), Softmax (ROperator_Softmax.hxx:204-342), stacked MatMul,
+ * Transpose -- whose scores and probabilities make five round trips through HBM.  Scores are kept in fp32, the
+ * probabilities are rounded to bf16 before the second contraction (as the unfused graph on bf16 tensors does).
+ * Supported: dtype SOFIE_B200_BF16, head_dim 64, 1 <= seq <= 128; anything else returns SOFIE_B200_ERR_INVALID and
+ * the caller emits the unfused operators. */
+int sofie_b200_attention_enqueue(sofie_b200_ctx *ctx, const void *qkv, void *out, int32_t dtype, int64_t batch,
+                                 int64_t seq, int32_t heads, int32_t head_dim, float scale);
+
 /* ---- memory-bound operators the fusion pass leaves ----------------------------------- */
 
 /* LayerNormalization over the last `cols` elements of each of `rows` rows

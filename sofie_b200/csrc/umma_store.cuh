@@ -333,6 +333,38 @@ __device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
   return r;
 }
 
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+// Gelu (erf form) of two values for outputs that are rounded to bf16 afterwards.  erff() costs some thirty instructions
+// per element, which made a Gelu epilogue slower than the main loop it follows; here erf(z), z = |x|/sqrt(2), is
+// 1 - 1/(1 + a1 z + ... + a6 z^6)^16 (Abramowitz & Stegun 7.1.28, |error| <= 3e-7, far below half a bf16 ulp of
+// any Gelu value that is not itself below 1e-5), evaluated on packed pairs with one reciprocal per element.
+__device__ __forceinline__ uint64_t gelu_erf_pair_lowp(uint64_t x2) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  const uint64_t z = pack2(fabsf(x0) * 0.7071067811865475f, fabsf(x1) * 0.7071067811865475f);
+  auto k = [](float c) { return pack2(c, c); };
+  uint64_t p = ffma2(z, k(0.0000430638f), k(0.0002765672f));
+  p = ffma2(p, z, k(0.0001520143f));
+  p = ffma2(p, z, k(0.0092705272f));
+  p = ffma2(p, z, k(0.0422820123f));
+  p = ffma2(p, z, k(0.0705230784f));
+  p = ffma2(p, z, k(1.0f));
+  p = fmul2(p, p); p = fmul2(p, p); p = fmul2(p, p); p = fmul2(p, p);   // ^16 (overflows to inf for |x| > ~25: erf = 1)
+  float d0, d1;
+  unpack2(p, d0, d1);
+  float r0, r1;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(d0));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(d1));
+  const float e0 = copysignf(1.f - r0, x0), e1 = copysignf(1.f - r1, x1);   // erf(x/sqrt(2))
+  const uint64_t h = fmul2(x2, k(0.5f));
+  return ffma2(h, pack2(e0, e1), h);   // 0.5 x (1 + erf)
+}
+
 // First half of the fast path: everything that reads the raw accumulator -- integer bias, conversion, the three
 // scales and the additive bias terms -- into v[32].  When it returns, `raw` is dead and the caller may already
 // load the next chunk into it.  Returns false when the chunk was finished here (int32 output: staged as is).
@@ -418,8 +450,13 @@ __device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float (&v)[
 #pragma unroll
       for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_RELU, 0.f);
     } else if (ep.act == SOFIE_B200_ACT_GELU_ERF) {
+      if (ep.y_dtype == SOFIE_B200_BF16) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_GELU_ERF, 0.f);
+        for (int c = 0; c < 32; c += 2) unpack2(gelu_erf_pair_lowp(pack2(v[c], v[c + 1])), v[c], v[c + 1]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_GELU_ERF, 0.f);
+      }
     } else {
 #pragma unroll
       for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], ep.act, ep.act_alpha);

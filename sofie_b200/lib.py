@@ -93,6 +93,7 @@ PROTOTYPES = {
     "sofie_b200_conv_plan_kernel": (C.c_char_p, [_P]),
     "sofie_b200_conv_enqueue": (C.c_int, [_P, _P, _P, _P, C.POINTER(Epilogue)]),
     "sofie_b200_conv_enqueue_noalloc": (C.c_int, [_P, C.POINTER(ConvDesc), _P, _P, _P, C.POINTER(Epilogue)]),
+    "sofie_b200_attention_enqueue": (C.c_int, [_P, _P, _P, _I32, _I64, _I64, _I32, _I32, _F]),
     "sofie_b200_layernorm_enqueue": (C.c_int, [_P, _P, _P, _I32, _I32, _I64, _I64, _P, _P, _F, _P, _P]),
     "sofie_b200_softmax_enqueue": (C.c_int, [_P, _P, _P, _I32, _I32, _I64, _I64, _I32]),
     "sofie_b200_unary_enqueue": (C.c_int, [_P, _P, _P, _I32, _I64, _I32, _F]),

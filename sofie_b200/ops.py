@@ -114,6 +114,11 @@ class Context:
                                                         _ptr(scale), _ptr(zero_point), channels, inner),
                 "dequantize_enqueue")
 
+    def attention(self, qkv, out, batch, seq, heads, head_dim, scale):
+        """qkv [batch, seq, 3, heads, head_dim] -> out [batch, seq, heads * head_dim] (fused Softmax(scale Q K^T) V)."""
+        L.check(self._lib.sofie_b200_attention_enqueue(self._h, _ptr(qkv), _ptr(out), dtype_code(qkv.dtype), batch, seq, heads, head_dim,
+                                                       float(scale)), "attention_enqueue")
+
     def transpose(self, x, y, perm):
         shape = (C.c_int64 * x.dim())(*x.shape)
         pm = (C.c_int32 * x.dim())(*perm)

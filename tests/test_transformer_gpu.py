@@ -17,124 +17,57 @@ B, S, D_MODEL, HEADS, FFN, LAYERS = 2, 128, 512, 8, 2048, 2
 DH = D_MODEL // HEADS
 
 
-def f32_to_bf16_bits(a):
-    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+@pytest.mark.parametrize("batch,seq,heads", [(2, 128, 8), (3, 77, 4), (1, 1, 2), (40, 128, 8)])
+def test_fused_attention_matches_unfused_checker(b200_lib, oracle_lib, batch, seq, heads):
+    """Softmax(Q K^T / 8) V per head from the packed QKV tensor, against the checker with the kernel's roundings."""
+    from sofie_b200.ops import Context
+    import bench_encoder as be
+    o = Oracle(oracle_lib)
+    dh = 64
+    rng = np.random.default_rng(batch * 1000 + seq)
+    qkv = be.f32_to_bf16_bits((rng.standard_normal((batch, seq, 3, heads, dh)) * 1.5).astype(np.float32))
+    want = bf16_bits_to_f32(be.attention_oracle(o, qkv, batch, seq, heads, dh, 0.125)).reshape(batch, seq, heads * dh)
+    ctx = Context(0)
+    tq = torch.from_numpy(qkv.view(np.int16)).to(DEV).view(torch.bfloat16)
+    out = torch.full((batch, seq, heads * dh), 7.0, dtype=torch.bfloat16, device=DEV)
+    n0 = ctx.launches
+    ctx.attention(tq, out, batch, seq, heads, dh, 0.125)
+    ctx.sync()
+    assert ctx.launches - n0 == 1
+    got = out.float().cpu().numpy()
+    err = np.abs(got - want)
+    assert np.all(err <= 2e-2 * np.abs(want) + 1e-2), f"max abs err {err.max():.4f}"
+    with pytest.raises(L.SofieB200Error):
+        ctx.attention(tq, out, batch, 129, heads, dh, 0.125)      # longer sequences: the caller emits the unfused graph
+    with pytest.raises(L.SofieB200Error):
+        ctx.attention(tq, out, batch, seq, heads, 32, 0.125)
+    ctx.close()
 
 
-def make_weights(rng):
-    def qlinear(n_out, n_in):
-        w = rng.standard_normal((n_out, n_in)).astype(np.float32) * 0.02
-        scale = (np.abs(w).max(axis=1) / 127.0).astype(np.float32)          # per output channel
-        q = np.clip(np.rint(w / scale[:, None]), -127, 127).astype(np.int8)
-        return q, scale, (rng.standard_normal(n_out) * 0.02).astype(np.float32)
-    layers = []
-    for _ in range(LAYERS):
-        layers.append({"qkv": qlinear(3 * D_MODEL, D_MODEL), "out": qlinear(D_MODEL, D_MODEL), "ff1": qlinear(FFN, D_MODEL),
-                       "ff2": qlinear(D_MODEL, FFN), "g1": np.ones(D_MODEL, np.float32), "b1": np.zeros(D_MODEL, np.float32),
-                       "g2": np.ones(D_MODEL, np.float32), "b2": np.zeros(D_MODEL, np.float32)})
-    return layers
-
-
-# ---- checker: numpy + oracle/libsofie_oracle.so on bf16 bit patterns -----------------------------------
-def encoder_oracle(o: Oracle, x, layers):
-    M = B * S
-    def linear(a, wq, scale, bias, act=L.ACT_NONE, residual=None):
-        w = f32_to_bf16_bits(wq.astype(np.float32))  # int8 values are exact in bf16
-        ep = o.epilogue(col_scale=scale, bias=bias, act=act, residual=residual, residual_dtype=L.BF16)
-        return o.gemm(a, w, M, wq.shape[0], wq.shape[1], L.BF16, L.BF16, False, True, ep=ep)
-    for ly in layers:
-        h = o.layernorm(x, ly["g1"], ly["b1"], 1e-5, L.BF16)
-        qkv = linear(h, *ly["qkv"])
-        t = np.ascontiguousarray(qkv.reshape(B, S, 3 * HEADS, DH).transpose(2, 0, 1, 3))   # [3H, B, S, DH]
-        q, k, v = (np.ascontiguousarray(t[i * HEADS:(i + 1) * HEADS]).reshape(HEADS * B, S, DH) for i in range(3))
-        sc = o.gemm(q, k, S, S, DH, L.BF16, L.BF16, False, True, batch=HEADS * B, ep=o.epilogue(alpha=1.0 / 8.0))
-        p = o.softmax(sc.reshape(-1, S), L.BF16).reshape(HEADS * B, S, S)
-        a = o.gemm(p, v, S, DH, S, L.BF16, L.BF16, False, False, batch=HEADS * B)
-        a = np.ascontiguousarray(a.reshape(HEADS, B, S, DH).transpose(1, 2, 0, 3)).reshape(M, D_MODEL)
-        x = linear(a, *ly["out"], residual=x)
-        h = o.layernorm(x, ly["g2"], ly["b2"], 1e-5, L.BF16)
-        f = linear(h, *ly["ff1"], act=L.ACT_GELU_ERF)
-        x = linear(f, *ly["ff2"], residual=x)
-    return x
-
-
-# ---- product path: libsofie_b200 through the C ABI ---------------------------------------------------------
-class EncoderB200:
-    def __init__(self, ctx, layers):
-        from sofie_b200.ops import GemmPlan
-        self.ctx, t = ctx, torch
-        M = B * S
-        self.layers = []
-        for ly in layers:
-            d = {}
-            for name in ("qkv", "out", "ff1", "ff2"):
-                wq, scale, bias = ly[name]
-                w8 = t.from_numpy(wq).to(DEV)
-                wb = t.empty(wq.shape, dtype=t.bfloat16, device=DEV)
-                ctx.convert(w8, wb)   # weights become bf16 once, at construction; the scale stays in the epilogue
-                d[name] = (wb, t.from_numpy(scale).to(DEV), t.from_numpy(bias).to(DEV),
-                           GemmPlan(ctx, M, wq.shape[0], wq.shape[1], t.bfloat16, t.bfloat16, trans_b=True))
-            for name in ("g1", "b1", "g2", "b2"):
-                d[name] = t.from_numpy(ly[name]).to(DEV)
-            self.layers.append(d)
-        hb = HEADS * B
-        self.qk = GemmPlan(ctx, S, S, DH, t.bfloat16, t.bfloat16, trans_b=True, batch=hb, stride_a=S * DH, stride_b=S * DH, stride_y=S * S)
-        self.pv = GemmPlan(ctx, S, DH, S, t.bfloat16, t.bfloat16, trans_b=False, batch=hb, stride_a=S * S, stride_b=S * DH, stride_y=S * DH)
-        assert self.qk.kernel == "umma" and self.pv.kernel == "umma"
-
-    def linear(self, a, layer, name, act=L.ACT_NONE, residual=None):
-        from sofie_b200.ops import make_epilogue
-        w, scale, bias, plan = layer[name]
-        y = torch.empty((a.shape[0], w.shape[0]), dtype=torch.bfloat16, device=DEV)
-        ep, keep = make_epilogue(col_scale=scale, bias=bias, act=act, residual=residual)
-        plan.enqueue(a, w, y, ep)
-        assert plan.kernel == "umma"
-        return y
-
-    def __call__(self, x):
-        from sofie_b200.ops import make_epilogue
-        ctx, t = self.ctx, torch
-        M = B * S
-        for ly in self.layers:
-            h = t.empty_like(x)
-            ctx.layernorm(x, h, ly["g1"], ly["b1"], 1e-5)
-            qkv = self.linear(h, ly, "qkv")
-            tq = t.empty((3 * HEADS, B, S, DH), dtype=t.bfloat16, device=DEV)
-            ctx.transpose(qkv.view(B, S, 3 * HEADS, DH), tq, (2, 0, 1, 3))
-            q, k, v = tq[:HEADS], tq[HEADS:2 * HEADS], tq[2 * HEADS:]
-            sc = t.empty((HEADS * B, S, S), dtype=t.bfloat16, device=DEV)
-            ep, _ = make_epilogue(alpha=1.0 / 8.0)
-            self.qk.enqueue(q, k, sc, ep)
-            p = t.empty_like(sc)
-            ctx.softmax(sc, p)
-            a = t.empty((HEADS, B, S, DH), dtype=t.bfloat16, device=DEV)
-            self.pv.enqueue(p, v, a)
-            am = t.empty((B, S, HEADS, DH), dtype=t.bfloat16, device=DEV)
-            ctx.transpose(a, am, (1, 2, 0, 3))
-            x = self.linear(am.view(M, D_MODEL), ly, "out", residual=x)
-            h2 = t.empty_like(x)
-            ctx.layernorm(x, h2, ly["g2"], ly["b2"], 1e-5)
-            f = self.linear(h2, ly, "ff1", act=L.ACT_GELU_ERF)
-            x = self.linear(f, ly, "ff2", residual=x)
-        ctx.sync()
-        return x
-
-
-def test_transformer_encoder_matches_checker(b200_lib, oracle_lib):
+@pytest.mark.parametrize("fused", [True, False])
+def test_transformer_encoder_matches_checker(b200_lib, oracle_lib, fused):
+    import bench_encoder as be
     from sofie_b200.ops import Context
     rng = np.random.default_rng(5)
-    layers = make_weights(rng)
-    x0 = f32_to_bf16_bits(rng.standard_normal((B * S, D_MODEL)).astype(np.float32))
-    want = bf16_bits_to_f32(encoder_oracle(Oracle(oracle_lib), x0, layers))
+    weights = be.make_weights(rng, LAYERS, D_MODEL, FFN)
+    x0 = be.f32_to_bf16_bits(rng.standard_normal((B * S, D_MODEL)).astype(np.float32))
+    want = bf16_bits_to_f32(be.encoder_oracle(Oracle(oracle_lib), x0, weights, B, S, D_MODEL, HEADS, fused_attention=fused))
     ctx = Context(0)
-    enc = EncoderB200(ctx, layers)
+    enc = be.EncoderB200(ctx, weights, B, S, D_MODEL, HEADS, FFN, DEV, fused_attention=fused)
     launches0 = ctx.launches
     xg = torch.from_numpy(x0.view(np.int16)).to(DEV).view(torch.bfloat16)
-    got = enc(xg).float().cpu().numpy()
-    assert ctx.launches - launches0 == LAYERS * 11   # 4 projections, 2 attention GEMMs, 2 LayerNorms, 1 Softmax, 2 transposes
+    y = enc(xg)
+    ctx.sync()
+    got = y.float().cpu().numpy()
+    assert ctx.launches - launches0 == LAYERS * (be.EncoderB200.LAUNCHES_PER_LAYER if fused else be.EncoderB200.LAUNCHES_PER_LAYER_UNFUSED)
     err = np.abs(got - want)
     assert np.all(err <= 2e-2 * np.abs(want) + 1e-2), f"max abs err {err.max():.4f}"
     assert np.isfinite(got).all() and np.abs(want).max() > 1.0
+    # a second call reuses every buffer and gives the same answer
+    y2 = enc(xg)
+    ctx.sync()
+    assert torch.equal(y2.float().cpu(), torch.from_numpy(got))
+    enc.close()
     ctx.close()
 
 
