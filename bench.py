@@ -587,6 +587,122 @@ WORKLOADS["transformer_encoder_b512"] = lambda: EncoderWorkload("transformer_enc
 WORKLOADS["transformer_encoder_b64"] = lambda: EncoderWorkload("transformer_encoder_b64", 64)
 
 
+class ConvNetWorkload:
+    """Conv net: 8 Conv3x3 (+ folded BatchNormalization + Relu) layers, global average pool, Gemm 512 -> 1000, on NCHW
+    3 x img x img inputs; fp32 or per-channel int8 (QLinearConv)."""
+
+    def __init__(self, name: str, batch: int, img: int, int8: bool):
+        self.name, self.batch, self.img, self.int8 = name, batch, img, int8
+        self.metric = f"conv net inferences/s ({img}x{img} images, {'int8 QLinearConv' if int8 else 'fp32'})"
+        self.unit, self.dtype = "inferences/s", ("int8" if int8 else "fp32 (3xTF32 on tcgen05 where large, fp32 FMA else)")
+
+
+def run_convnet(args, w) -> None:
+    import torch
+    import bench_convnet as bc
+
+    flops = bc.flops_per_image(w.img)
+    rng = np.random.default_rng(11)
+    weights = bc.make_weights(rng, w.int8)
+    config = {"workload": w.name, "batch_per_gpu": w.batch, "image": [3, w.img, w.img], "layers": "8 x Conv3x3+BN+Relu, avgpool, Gemm 512->1000",
+              "strides": bc.STRIDES, "gflop_per_inference": flops / 1e9}
+
+    def host_input(n):
+        x = rng.random((n, 3, w.img, w.img), dtype=np.float32)
+        return np.clip(np.rint(x * 127.0), 0, 127).astype(np.int8) if w.int8 else x
+
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        sys.path.insert(0, str(ROOT / "tests"))
+        from oracle_api import Oracle
+        load_oracle()
+        o = Oracle(ROOT / "oracle" / "libsofie_oracle.so")
+        o.lib.so_threads.restype = C.c_int
+        o.lib.so_set_threads(os.cpu_count() or 1)
+        x = host_input(1)
+        def cpu_step():
+            t0 = time.perf_counter()
+            bc.convnet_oracle(o, x, weights, w.int8)
+            return time.perf_counter() - t0
+        steps = max(1, min(args.steps, 3))
+        if args.warmup:
+            cpu_step()
+        t = sum(cpu_step() for _ in range(steps))
+        val = steps / t
+        print(json.dumps({"impl": "reference", "metric": w.metric, "value": val, "unit": w.unit, "n_gpus": args.gpus, "steps": steps,
+                          "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * t / steps, "higher_is_better": True, "scaling": "weak",
+                          "vs_baseline": None, "dtype": "int32 accumulate" if w.int8 else "f64 accumulate", "data": "synthetic", "config": config,
+                          "cpu_baseline": {"value": val, "unit": w.unit, "cores": int(o.lib.so_threads()), "kind": "port",
+                                           "sample": f"each step = 1 of {w.batch} images through the whole network"},
+                          "e2e": {"value": val, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}), flush=True)
+        return
+
+    from sofie_b200 import replicas
+    from sofie_b200.ops import Context
+    rep = replicas.init_from_env("nccl")
+    torch.cuda.set_device(rep.local_rank)
+    dev = f"cuda:{rep.local_rank}"
+    ctx = Context(rep.local_rank)
+    net = bc.ConvNetB200(ctx, weights, w.batch, w.img, w.int8, dev)
+    hx = torch.from_numpy(host_input(w.batch)).pin_memory()
+    x = hx.to(dev)
+    for _ in range(max(3, args.warmup)):
+        net(x)
+    ctx.sync()
+    sampler = ClockSampler(rep.local_rank)
+    replicas.barrier(rep)
+    torch.cuda.synchronize()
+    l0 = ctx.launches
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        net(x)
+    e1.record()
+    torch.cuda.synchronize()
+    ctx.sync()
+    clocks = sampler.stop()
+    ms_local = e0.elapsed_time(e1)
+    ms = replicas.max_over_ranks(rep, ms_local)
+    launches = ctx.launches - l0
+    value = rep.world * w.batch * args.steps / (ms * 1e-3)
+    hy = torch.empty((w.batch, bc.CLASSES), dtype=torch.float32).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        x.copy_(hx, non_blocking=True)
+        y = net(x)
+        hy.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+    t_e2e = replicas.max_over_ranks(rep, time.perf_counter() - t0)
+    if rep.is_root:
+        peaks = measured_peaks()
+        ach = flops * w.batch / (ms_local / args.steps * 1e-3) / 1e12
+        base = peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]
+        peak = 2.0 * base if w.int8 else base / 6.0
+        how = "2 x bf16_tflops_sustained (int8 dense)" if w.int8 else "bf16_tflops_sustained / 6 (TF32 is half the bf16 rate, 3xTF32 does three passes)"
+        print(json.dumps({"metric": w.metric, "value": value, "unit": w.unit, "n_gpus": rep.world, "steps": args.steps, "warmup": max(3, args.warmup),
+                          "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype,
+                          "data": "synthetic", "config": dict(config, contraction_kernels=net.kernels,
+                                                              l2="activations of one step are several GB (> 126 MiB L2)"),
+                          "clocks": clocks, "gpu_launches": int(launches),
+                          "e2e": {"value": rep.world * w.batch * e2e_steps / t_e2e, "unit": w.unit, "h2d_bytes_per_step": int(hx.numel() * hx.element_size()),
+                                  "d2h_bytes_per_step": int(hy.numel() * 4), "steps": e2e_steps},
+                          "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s" if not w.int8 else "TOP/s", "frac": ach / peak,
+                                       "traffic": None, "peak_source": f"{how} of {peaks['source']} MEASURED_PEAKS.json; whole step "
+                                                                       f"({launches // max(1, args.steps)} launches), not one kernel"}}), flush=True)
+    net.close()
+    ctx.close()
+    replicas.shutdown(rep)
+
+
+WORKLOADS["convnet_fp32_b256"] = lambda: ConvNetWorkload("convnet_fp32_b256", 256, 224, False)
+WORKLOADS["convnet_int8_b256"] = lambda: ConvNetWorkload("convnet_int8_b256", 256, 224, True)
+WORKLOADS["convnet_fp32_b32"] = lambda: ConvNetWorkload("convnet_fp32_b32", 32, 224, False)
+WORKLOADS["convnet_int8_b32"] = lambda: ConvNetWorkload("convnet_int8_b32", 32, 224, True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -600,6 +716,8 @@ def main() -> None:
         run_rowop(args, w)
     elif isinstance(w, EncoderWorkload):
         run_encoder(args, w)
+    elif isinstance(w, ConvNetWorkload):
+        run_convnet(args, w)
     elif args.impl == "reference":
         run_reference(args, w)
     else:

@@ -1,0 +1,138 @@
+"""The conv-net configuration on libsofie_b200, for bench.py.
+
+Eight Conv 3x3 (pad 1) layers 3-64-64-128-128-256-256-512-512 with strides 1,2,1,2,1,2,1,2, each with a folded
+BatchNormalization (per-channel scale and shift in the contraction epilogue) and Relu, global average pool,
+Gemm 512 -> 1000.  Two variants: fp32 (precise: 3xTF32 on the tensor cores where large enough) and per-channel
+int8 (QLinearConv: int32 accumulation, fp32 multiplier a_scale * w_scale[c] / y_scale, int32 bias, Relu, int8 out).
+Plans, weights and every activation buffer are created once; a step only enqueues kernels.
+
+`convnet_oracle` runs the same network through the CPU restatement (oracle/): the CPU arm of the benchmark.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+CHANNELS = [3, 64, 64, 128, 128, 256, 256, 512, 512]
+STRIDES = [1, 2, 1, 2, 1, 2, 1, 2]
+CLASSES = 1000
+Y_SCALE = np.float32(0.05)        # activation scale of every int8 layer output
+IN_SCALE = np.float32(1.0 / 127)  # U(0,1) input quantised to 0..127
+
+
+def conv_desc(n, c, h, w, k, stride, x_dtype, y_dtype):
+    from sofie_b200 import lib as L
+    d = L.ConvDesc()
+    d.N, d.C, d.H, d.W, d.K, d.R, d.S = n, c, h, w, k, 3, 3
+    d.pad_top = d.pad_left = d.pad_bottom = d.pad_right = 1
+    d.stride_h = d.stride_w = stride
+    d.dil_h = d.dil_w = 1
+    d.groups = 1
+    d.x_dtype, d.y_dtype, d.x_zero_point, d.precise = x_dtype, y_dtype, 0, 1
+    return d
+
+
+def make_weights(rng, int8: bool):
+    """He-normal conv weights, BatchNormalization parameters folded to scale/shift; the int8 variant quantises the
+    weights per output channel and turns the fold into a multiplier and an int32 bias."""
+    layers = []
+    a_scale = IN_SCALE
+    for i in range(8):
+        cin, cout = CHANNELS[i], CHANNELS[i + 1]
+        wf = (rng.standard_normal((cout, cin, 3, 3)) * np.sqrt(2.0 / (cin * 9))).astype(np.float32)
+        gamma, beta = (rng.random(cout) + 0.5).astype(np.float32), (rng.standard_normal(cout) * 0.1).astype(np.float32)
+        mean, var = (rng.standard_normal(cout) * 0.1).astype(np.float32), (rng.random(cout) + 0.5).astype(np.float32)
+        scale = (gamma / np.sqrt(var + np.float32(1e-5))).astype(np.float32)
+        shift = (beta - mean * scale).astype(np.float32)
+        if not int8:
+            layers.append(dict(w=wf, scale=scale, bias=shift))
+        else:
+            wfold = wf * scale[:, None, None, None]                     # BN scale folded into the weights before quantising
+            w_scale = (np.abs(wfold).reshape(cout, -1).max(axis=1) / 127.0).astype(np.float32)
+            wq = np.clip(np.rint(wfold / w_scale[:, None, None, None]), -127, 127).astype(np.int8)
+            mult = (a_scale * w_scale / Y_SCALE).astype(np.float32)
+            bias = np.rint(shift / (a_scale * w_scale)).astype(np.int32)   # shift at the accumulator's scale
+            layers.append(dict(w=wq, scale=mult, bias=bias))
+            a_scale = Y_SCALE
+    fc_w = (rng.standard_normal((512, CLASSES)) * np.sqrt(2.0 / 512)).astype(np.float32)
+    fc_b = np.zeros(CLASSES, dtype=np.float32)
+    return layers, fc_w, fc_b
+
+
+def flops_per_image(img: int) -> float:
+    f, hw = 0.0, img
+    for i, st in enumerate(STRIDES):
+        hw = (hw + 2 - 3) // st + 1
+        f += 2.0 * CHANNELS[i + 1] * hw * hw * CHANNELS[i] * 9
+    return f + 2.0 * 512 * CLASSES
+
+
+def convnet_oracle(o, x: np.ndarray, weights, int8: bool) -> np.ndarray:
+    """x: [n, 3, img, img] fp32 in [0,1) (fp32 variant) or int8 0..127 (int8 variant).  Returns [n, 1000] fp32 logits."""
+    from sofie_b200 import lib as L
+    layers, fc_w, fc_b = weights
+    dt = L.I8 if int8 else L.F32
+    for ly, st in zip(layers, STRIDES):
+        n, c, h, w = x.shape
+        d = conv_desc(n, c, h, w, ly["w"].shape[0], st, dt, dt)
+        ho = (h + 2 - 3) // st + 1
+        x = o.conv(x, ly["w"], d, ho, ho, ep=o.epilogue(col_scale=ly["scale"], bias=ly["bias"], act=L.ACT_RELU))
+    pooled = o.global_avgpool(x, dt) if int8 else o.global_avgpool(x)
+    ep = o.epilogue(alpha=float(Y_SCALE), bias=fc_b) if int8 else o.epilogue(bias=fc_b)
+    return o.gemm(np.ascontiguousarray(pooled, dtype=np.float32), fc_w, x.shape[0], CLASSES, 512, L.F32, L.F32, ep=ep)
+
+
+class ConvNetB200:
+    """The network on one GPU through the C ABI.  `ctx` is a sofie_b200.ops.Context on that GPU."""
+
+    LAUNCHES = 8 * 2 + 2   # unfold + contraction per layer, pool, classifier
+
+    def __init__(self, ctx, weights, batch: int, img: int, int8: bool, device: str):
+        import torch
+        from sofie_b200 import lib as L
+        from sofie_b200.ops import GemmPlan, make_epilogue
+        self.ctx, self.batch, self.int8 = ctx, batch, int8
+        self.lib = lib = ctx._lib
+        t = torch
+        adt = t.int8 if int8 else t.float32
+        code = L.I8 if int8 else L.F32
+        layers, fc_w, fc_b = weights
+        self.plans, self.eps, self.keep, self.acts, self.kernels = [], [], [], [], []
+        hw, ws_bytes = img, 16
+        self.x_in = t.empty((batch, 3, img, img), dtype=adt, device=device)
+        for ly, st, cin, cout in zip(layers, STRIDES, CHANNELS[:-1], CHANNELS[1:]):
+            d = conv_desc(batch, cin, hw, hw, cout, st, code, code)
+            w = t.from_numpy(ly["w"]).to(device)
+            h = C.c_void_p()
+            L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), w.data_ptr(), C.byref(h)), "conv_plan_create")
+            ws_bytes = max(ws_bytes, lib.sofie_b200_conv_workspace_bytes(h))
+            hw = (hw + 2 - 3) // st + 1
+            ep, keep = make_epilogue(col_scale=t.from_numpy(ly["scale"]).to(device), bias=t.from_numpy(ly["bias"]).to(device), act=L.ACT_RELU)
+            self.plans.append(h); self.eps.append(ep); self.keep.append((keep, w))
+            self.acts.append(t.empty((batch, cout, hw, hw), dtype=adt, device=device))
+            self.kernels.append(lib.sofie_b200_conv_plan_kernel(h).decode())
+        ctx.sync()   # weight re-layout kernels read `w`
+        self.workspace = t.empty(ws_bytes, dtype=t.uint8, device=device)
+        self.pooled = t.empty((batch, 512), dtype=t.float32, device=device)
+        self.logits = t.empty((batch, CLASSES), dtype=t.float32, device=device)
+        self.fc_w = t.from_numpy(fc_w).to(device)
+        self.fc = GemmPlan(ctx, batch, CLASSES, 512, t.float32, t.float32, trans_b=False)
+        self.fc_ep, k = make_epilogue(alpha=float(Y_SCALE) if int8 else 1.0, bias=t.from_numpy(fc_b).to(device))
+        self.keep.append(k)
+
+    def __call__(self, x):
+        """x: [batch, 3, img, img] on the device; returns the logits buffer (owned here, overwritten by the next call)."""
+        from sofie_b200 import lib as L
+        cur = x
+        for h, ep, y in zip(self.plans, self.eps, self.acts):
+            L.check(self.lib.sofie_b200_conv_enqueue(h, cur.data_ptr(), y.data_ptr(), self.workspace.data_ptr(), C.byref(ep)), "conv_enqueue")
+            cur = y
+        self.ctx.global_avgpool(cur, self.pooled)
+        self.fc.enqueue(self.pooled, self.fc_w, self.logits, self.fc_ep)
+        return self.logits
+
+    def close(self):
+        for h in self.plans:
+            self.lib.sofie_b200_conv_plan_destroy(h)
+        self.fc.close()

@@ -34,36 +34,60 @@ static int conv_out_shape(const sofie_b200_conv_desc &d, int64_t *Ho, int64_t *W
   return 0;
 }
 
+// Position of one 16-byte chunk of the unfolded matrix: which image / group / output pixel it belongs to and the
+// (channel, kernel row, kernel column) of its first element.  One 64-bit division per chunk, the rest in 32 bits;
+// the elements of the chunk then step (c, r, s) incrementally instead of dividing k for every element, which is
+// what made the first version of these kernels division-bound (233 GB/s on the int8 layers).
+struct UnfoldPos {
+  long long row;        // (g, n, pix) flattened: row of the B operand
+  unsigned ch;          // chunk inside the row
+  const void *xg;       // first input channel of the group in image n
+  int ih0, iw0;         // input coordinates of kernel element (0, 0)
+  unsigned c, r, s;     // decomposition of k = ch * VEC
+};
+template <typename T, int VEC>
+__device__ __forceinline__ UnfoldPos unfold_pos(const T *x, const sofie_b200_conv_desc &d, long long i, unsigned chunks, unsigned pix, unsigned Wo,
+                                                unsigned cg) {
+  UnfoldPos u;
+  u.row = i / chunks;
+  u.ch = (unsigned)(i - u.row * chunks);
+  const long long gn = u.row / pix;
+  const unsigned p = (unsigned)(u.row - gn * pix);
+  const unsigned n = (unsigned)(gn % d.N), g = (unsigned)(gn / d.N);
+  const unsigned oh = p / Wo, ow = p - oh * Wo;
+  u.ih0 = (int)(oh * d.stride_h) - d.pad_top;
+  u.iw0 = (int)(ow * d.stride_w) - d.pad_left;
+  u.xg = x + ((long long)n * d.C + (long long)g * cg) * d.H * d.W;
+  const unsigned S = (unsigned)d.S, rs = (unsigned)(d.R * d.S), k = u.ch * VEC;
+  u.c = k / rs;
+  const unsigned q = k - u.c * rs;
+  u.r = q / S;
+  u.s = q - u.r * S;
+  return u;
+}
+
 // xcol[g][n][pix][kpad]; one thread writes 16 bytes (VEC elements along k).
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256) unfold_kernel(const T *__restrict__ x, T *__restrict__ xcol, sofie_b200_conv_desc d,
                                                      long long Ho, long long Wo, long long cg, long long kdim, long long kpad,
                                                      T pad_value) {
-  const long long chunks = kpad / VEC;
-  const long long pix = Ho * Wo;
+  const unsigned chunks = (unsigned)(kpad / VEC), pix = (unsigned)(Ho * Wo);
   const long long total = (long long)d.groups * d.N * pix * chunks;
-  const long long rs = d.R * d.S;
+  const int H = (int)d.H, W = (int)d.W, R = (int)d.R, S = (int)d.S;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long ch = i % chunks;
-    long long t = i / chunks;
-    const long long p = t % pix; t /= pix;
-    const long long n = t % d.N;
-    const long long g = t / d.N;
-    const long long oh = p / Wo, ow = p % Wo;
-    const long long ih0 = oh * d.stride_h - d.pad_top, iw0 = ow * d.stride_w - d.pad_left;
-    const T *xg = x + (n * d.C + g * cg) * d.H * d.W;
+    const UnfoldPos u = unfold_pos<T, VEC>(x, d, i, chunks, pix, (unsigned)Wo, (unsigned)cg);
+    const T *xg = (const T *)u.xg;
+    int c = (int)u.c, r = (int)u.r, s = (int)u.s;
     __align__(16) T v[VEC];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
-      const long long k = ch * VEC + e;
       T val = (T)0;
-      if (k < kdim) {
-        const long long c = k / rs, q = k % rs;
-        const long long r = q / d.S, s = q % d.S;
-        const long long ih = ih0 + r * d.dil_h, iw = iw0 + s * d.dil_w;
-        val = (ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) ? xg[(c * d.H + ih) * d.W + iw] : pad_value;
+      if ((long long)u.ch * VEC + e < kdim) {
+        const int ih = u.ih0 + r * d.dil_h, iw = u.iw0 + s * d.dil_w;
+        val = (ih >= 0 && ih < H && iw >= 0 && iw < W) ? xg[((long long)c * H + ih) * W + iw] : pad_value;
       }
       v[e] = val;
+      if (++s == S) { s = 0; if (++r == R) { r = 0; ++c; } }
     }
     *reinterpret_cast<uint4 *>(xcol + i * VEC) = *reinterpret_cast<const uint4 *>(v);
   }
@@ -72,35 +96,26 @@ __global__ void __launch_bounds__(256) unfold_kernel(const T *__restrict__ x, T 
 // fp32 input unfolded straight into the split form of the B operand: xcol[g][n][pix][hi | hi | lo], each segment kpad wide.
 __global__ void __launch_bounds__(256) unfold_split_kernel(const float *__restrict__ x, float *__restrict__ xcol, sofie_b200_conv_desc d,
                                                            long long Ho, long long Wo, long long cg, long long kdim, long long kpad) {
-  const long long chunks = kpad / 4;
-  const long long pix = Ho * Wo;
+  const unsigned chunks = (unsigned)(kpad / 4), pix = (unsigned)(Ho * Wo);
   const long long total = (long long)d.groups * d.N * pix * chunks;
-  const long long rs = d.R * d.S;
+  const int H = (int)d.H, W = (int)d.W, R = (int)d.R, S = (int)d.S;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const long long ch = i % chunks;
-    long long t = i / chunks;
-    const long long row = t;   // (g, n, pix) flattened: one row of the B operand
-    const long long p = t % pix; t /= pix;
-    const long long n = t % d.N;
-    const long long g = t / d.N;
-    const long long oh = p / Wo, ow = p % Wo;
-    const long long ih0 = oh * d.stride_h - d.pad_top, iw0 = ow * d.stride_w - d.pad_left;
-    const float *xg = x + (n * d.C + g * cg) * d.H * d.W;
+    const UnfoldPos u = unfold_pos<float, 4>(x, d, i, chunks, pix, (unsigned)Wo, (unsigned)cg);
+    const float *xg = (const float *)u.xg;
+    int c = (int)u.c, r = (int)u.r, s = (int)u.s;
     __align__(16) float hi[4], lo[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const long long k = ch * 4 + e;
       float val = 0.f;
-      if (k < kdim) {
-        const long long c = k / rs, q = k % rs;
-        const long long r = q / d.S, s = q % d.S;
-        const long long ih = ih0 + r * d.dil_h, iw = iw0 + s * d.dil_w;
-        if (ih >= 0 && ih < d.H && iw >= 0 && iw < d.W) val = xg[(c * d.H + ih) * d.W + iw];
+      if ((long long)u.ch * 4 + e < kdim) {
+        const int ih = u.ih0 + r * d.dil_h, iw = u.iw0 + s * d.dil_w;
+        if (ih >= 0 && ih < H && iw >= 0 && iw < W) val = xg[((long long)c * H + ih) * W + iw];
       }
       hi[e] = tf32_rn(val);
       lo[e] = tf32_rn(__fsub_rn(val, hi[e]));
+      if (++s == S) { s = 0; if (++r == R) { r = 0; ++c; } }
     }
-    float *o = xcol + row * 3 * kpad + ch * 4;
+    float *o = xcol + u.row * 3 * kpad + u.ch * 4;
     *reinterpret_cast<uint4 *>(o) = *reinterpret_cast<const uint4 *>(hi);
     *reinterpret_cast<uint4 *>(o + kpad) = *reinterpret_cast<const uint4 *>(hi);
     *reinterpret_cast<uint4 *>(o + 2 * kpad) = *reinterpret_cast<const uint4 *>(lo);

@@ -23,6 +23,9 @@ namespace sb200 {
 
 constexpr int UMMA_BM = 128;          // rows of one accumulator tile (TMEM lanes)
 constexpr int UMMA_STAGE_K_BYTES = 128;  // K extent of one shared-memory stage, in bytes (one 128B swizzle row)
+// The opt-in limit is a property of the FUNCTION, shared by every plan that launches it: it is always set to the
+// device maximum, never to one plan's size (a later, smaller plan would otherwise make an earlier one unlaunchable).
+constexpr int UMMA_MAX_DYN_SMEM = 227 * 1024;
 constexpr int UMMA_TAIL_BYTES = 1024;  // barriers, TMEM slot and abort flag behind the stage ring; the epilogue staging follows
 constexpr int UMMA_EPI_WARPS = 8;     // two epilogue warps per tensor-memory lane quarter, alternating 32-column chunks
 constexpr int UMMA_THREADS = 64 + 32 * UMMA_EPI_WARPS;  // warp 0: TMA producer, warp 1: MMA issuer, then the epilogue warps

@@ -493,10 +493,10 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
 
   cudaError_t e = cudaSuccess;
   switch (kind) {
-    case KIND_I8: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan->smem_bytes); break;
-    case KIND_F8: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan->smem_bytes); break;
-    case KIND_F16: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan->smem_bytes); break;
-    default: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan->smem_bytes); break;
+    case KIND_I8: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM); break;
+    case KIND_F8: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM); break;
+    case KIND_F16: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM); break;
+    default: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM); break;
   }
   if (e != cudaSuccess) return fail(SOFIE_B200_ERR_CUDA, "cudaFuncSetAttribute(smem=%zu): %s", plan->smem_bytes, cudaGetErrorString(e));
   return 0;

@@ -250,10 +250,10 @@ umma_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
 int umma_pair_set_smem(int kind, size_t smem_bytes) {
   cudaError_t e = cudaSuccess;
   switch (kind) {
-    case KIND_I8: e = cudaFuncSetAttribute(umma_pair_gemm_kernel<KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes); break;
-    case KIND_F8: e = cudaFuncSetAttribute(umma_pair_gemm_kernel<KIND_F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes); break;
-    case KIND_F16: e = cudaFuncSetAttribute(umma_pair_gemm_kernel<KIND_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes); break;
-    default: e = cudaFuncSetAttribute(umma_pair_gemm_kernel<KIND_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes); break;
+    case KIND_I8: e = cudaFuncSetAttribute(umma_pair_gemm_kernel<KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM); break;
+    case KIND_F8: e = cudaFuncSetAttribute(umma_pair_gemm_kernel<KIND_F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM); break;
+    case KIND_F16: e = cudaFuncSetAttribute(umma_pair_gemm_kernel<KIND_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM); break;
+    default: e = cudaFuncSetAttribute(umma_pair_gemm_kernel<KIND_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM); break;
   }
   if (e != cudaSuccess) return fail(SOFIE_B200_ERR_CUDA, "cudaFuncSetAttribute(pair kernel, smem=%zu): %s", smem_bytes, cudaGetErrorString(e));
   return 0;

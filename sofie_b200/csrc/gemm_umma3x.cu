@@ -206,7 +206,7 @@ umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
 }
 
 int umma_promote_set_smem(size_t smem_bytes) {
-  cudaError_t e = cudaFuncSetAttribute(umma_tf32_promote_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+  cudaError_t e = cudaFuncSetAttribute(umma_tf32_promote_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM);
   if (e != cudaSuccess) return fail(SOFIE_B200_ERR_CUDA, "cudaFuncSetAttribute(promote kernel, smem=%zu): %s", smem_bytes, cudaGetErrorString(e));
   return 0;
 }

@@ -386,3 +386,18 @@ def test_fp32_gemm_3xtf32_meets_fp32_bar(ctx, oracle, M, N, K, ta, tb, batch):
     tf32 = run_gemm(ctx, a, b, M, N, K, torch.float32, torch.float32, ta, tb, batch=batch, bias=bias, act=L.ACT_RELU, precise=False).cpu().numpy()
     if not ta and tb:
         assert not close_f32(tf32.reshape(want.shape), want)
+
+
+def test_plans_of_different_sizes_coexist(ctx, oracle):
+    """A small plan created AFTER a large one must not make the large one unlaunchable (the shared-memory opt-in is per function)."""
+    from sofie_b200.ops import GemmPlan
+    rng = np.random.default_rng(2)
+    big = GemmPlan(ctx, 512, 512, 512, torch.int8, torch.int32, trans_b=True)      # bn = 256: the largest stage ring
+    small = GemmPlan(ctx, 128, 32, 64, torch.int8, torch.int32, trans_b=True)      # bn = 32
+    a = torch.from_numpy(rng.integers(-127, 128, size=(512, 512), dtype=np.int8)).to(DEV)
+    b = torch.from_numpy(rng.integers(-127, 128, size=(512, 512), dtype=np.int8)).to(DEV)
+    y = torch.zeros((512, 512), dtype=torch.int32, device=DEV)
+    big.enqueue(a, b, y)
+    ctx.sync()
+    assert torch.equal(y.cpu(), a.cpu().int() @ b.cpu().int().T)
+    big.close(); small.close()
