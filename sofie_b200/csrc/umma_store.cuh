@@ -314,62 +314,39 @@ __device__ __align__(16) const int g_epi_izero[32] = {};
 // Scales and biases are therefore always applied, with neutral operands when absent; only the residual, the
 // activation and the output type branch, and the rare cases are marked unlikely so they sit out of line.
 // Operation order and rounding are those of store_chunk(): the results are bit-identical.
-// Two fp32 values in one 64-bit register and the packed arithmetic of sm_100 on them: each half is rounded exactly
-// as the scalar instruction would round it, at half the instruction count.
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-
-__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
+// Packed fp32 arithmetic of sm_100 (two values per instruction, each half rounded exactly as the scalar instruction
+// would round it) on float2, which lets the compiler keep the pairs in aligned register pairs without moves.
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 dup2(float x) { return make_float2(x, x); }
 
 // Gelu (erf form) of two values for outputs that are rounded to bf16 afterwards.  erff() costs some thirty instructions
 // per element, which made a Gelu epilogue slower than the main loop it follows; here erf(z), z = |x|/sqrt(2), is
 // 1 - 1/(1 + a1 z + ... + a6 z^6)^16 (Abramowitz & Stegun 7.1.28, |error| <= 3e-7, far below half a bf16 ulp of
 // any Gelu value that is not itself below 1e-5), evaluated on packed pairs with one reciprocal per element.
-__device__ __forceinline__ uint64_t gelu_erf_pair_lowp(uint64_t x2) {
-  float x0, x1;
-  unpack2(x2, x0, x1);
-  const uint64_t z = pack2(fabsf(x0) * 0.7071067811865475f, fabsf(x1) * 0.7071067811865475f);
-  auto k = [](float c) { return pack2(c, c); };
-  uint64_t p = ffma2(z, k(0.0000430638f), k(0.0002765672f));
-  p = ffma2(p, z, k(0.0001520143f));
-  p = ffma2(p, z, k(0.0092705272f));
-  p = ffma2(p, z, k(0.0422820123f));
-  p = ffma2(p, z, k(0.0705230784f));
-  p = ffma2(p, z, k(1.0f));
+__device__ __forceinline__ float2 gelu_erf_pair_lowp(float2 x) {
+  const float2 z = make_float2(fabsf(x.x) * 0.7071067811865475f, fabsf(x.y) * 0.7071067811865475f);
+  float2 p = ffma2(z, dup2(0.0000430638f), dup2(0.0002765672f));
+  p = ffma2(p, z, dup2(0.0001520143f));
+  p = ffma2(p, z, dup2(0.0092705272f));
+  p = ffma2(p, z, dup2(0.0422820123f));
+  p = ffma2(p, z, dup2(0.0705230784f));
+  p = ffma2(p, z, dup2(1.0f));
   p = fmul2(p, p); p = fmul2(p, p); p = fmul2(p, p); p = fmul2(p, p);   // ^16 (overflows to inf for |x| > ~25: erf = 1)
-  float d0, d1;
-  unpack2(p, d0, d1);
   float r0, r1;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(d0));
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(d1));
-  const float e0 = copysignf(1.f - r0, x0), e1 = copysignf(1.f - r1, x1);   // erf(x/sqrt(2))
-  const uint64_t h = fmul2(x2, k(0.5f));
-  return ffma2(h, pack2(e0, e1), h);   // 0.5 x (1 + erf)
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(p.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(p.y));
+  const float2 e = make_float2(copysignf(1.f - r0, x.x), copysignf(1.f - r1, x.y));   // erf(x/sqrt(2))
+  const float2 h = fmul2(x, dup2(0.5f));
+  return ffma2(h, e, h);   // 0.5 x (1 + erf)
 }
 
 // First half of the fast path: everything that reads the raw accumulator -- integer bias, conversion, the three
 // scales and the additive bias terms -- into v[32].  When it returns, `raw` is dead and the caller may already
 // load the next chunk into it.  Returns false when the chunk was finished here (int32 output: staged as is).
 template <bool ACC_INT>
-__device__ __forceinline__ bool epi_values_fast(const EpiParams &ep, const uint32_t (&raw)[32], float (&v)[32], long long rr, int col0,
+__device__ __forceinline__ bool epi_values_fast(const EpiParams &ep, const uint32_t (&raw)[32], float2 (&v)[16], long long rr, int col0,
                                                 uint32_t stage, int slot) {
   const int mode = ep.bias_mode;
   const int4 *bip = reinterpret_cast<const int4 *>(g_epi_izero);
@@ -396,28 +373,27 @@ __device__ __forceinline__ bool epi_values_fast(const EpiParams &ep, const uint3
   float rbf = -0.f;
   if (mode == SOFIE_B200_BIAS_ROW_F32) rbf = ((const float *)ep.bias)[rr];
   if (mode == SOFIE_B200_BIAS_SCALAR_F32) rbf = ((const float *)ep.bias)[0];
-  const uint64_t rs2 = pack2(rs, rs), alpha2 = pack2(ep.alpha, ep.alpha), rbf2 = pack2(rbf, rbf);
+  const float2 rs2 = dup2(rs), alpha2 = dup2(ep.alpha), rbf2 = dup2(rbf);
 #pragma unroll
   for (int c = 0; c < 32; c += 4) {
     const float4 cs = csp[c >> 2], bf = bfp[c >> 2];
-    float x0, x1, x2, x3;
+    float2 xa, xb;
     if (ACC_INT) {
       const int4 bi = bip[c >> 2];
-      x0 = (float)((int)raw[c] + bi.x + rbi); x1 = (float)((int)raw[c + 1] + bi.y + rbi);
-      x2 = (float)((int)raw[c + 2] + bi.z + rbi); x3 = (float)((int)raw[c + 3] + bi.w + rbi);
+      xa = make_float2((float)((int)raw[c] + bi.x + rbi), (float)((int)raw[c + 1] + bi.y + rbi));
+      xb = make_float2((float)((int)raw[c + 2] + bi.z + rbi), (float)((int)raw[c + 3] + bi.w + rbi));
     } else {
-      x0 = __uint_as_float(raw[c]); x1 = __uint_as_float(raw[c + 1]); x2 = __uint_as_float(raw[c + 2]); x3 = __uint_as_float(raw[c + 3]);
+      xa = make_float2(__uint_as_float(raw[c]), __uint_as_float(raw[c + 1]));
+      xb = make_float2(__uint_as_float(raw[c + 2]), __uint_as_float(raw[c + 3]));
     }
-    const uint64_t a = fadd2(fadd2(fmul2(fmul2(fmul2(pack2(x0, x1), rs2), pack2(cs.x, cs.y)), alpha2), pack2(bf.x, bf.y)), rbf2);
-    const uint64_t d = fadd2(fadd2(fmul2(fmul2(fmul2(pack2(x2, x3), rs2), pack2(cs.z, cs.w)), alpha2), pack2(bf.z, bf.w)), rbf2);
-    unpack2(a, v[c], v[c + 1]);
-    unpack2(d, v[c + 2], v[c + 3]);
+    v[c >> 1] = fadd2(fadd2(fmul2(fmul2(fmul2(xa, rs2), make_float2(cs.x, cs.y)), alpha2), make_float2(bf.x, bf.y)), rbf2);
+    v[(c >> 1) + 1] = fadd2(fadd2(fmul2(fmul2(fmul2(xb, rs2), make_float2(cs.z, cs.w)), alpha2), make_float2(bf.z, bf.w)), rbf2);
   }
   return true;
 }
 
 // Second half of the fast path: residual, activation, conversion to the output type, staging.
-__device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float (&v)[32], long long b, long long rr, int col0, uint32_t stage,
+__device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)[16], long long b, long long rr, int col0, uint32_t stage,
                                                 int slot) {
   if (ep.residual) {
     const long long roff = b * ep.stride_r + rr * ep.ldr + col0;
@@ -429,65 +405,67 @@ __device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float (&v)[
           const uint4 q = r[c >> 3];
           const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {   // a bf16 is the upper half of the fp32 with the same value
-            v[c + 2 * u] = __fadd_rn(v[c + 2 * u], __uint_as_float(ww[u] << 16));
-            v[c + 2 * u + 1] = __fadd_rn(v[c + 2 * u + 1], __uint_as_float(ww[u] & 0xffff0000u));
-          }
+          for (int u = 0; u < 4; ++u)   // a bf16 is the upper half of the fp32 with the same value
+            v[(c >> 1) + u] = fadd2(v[(c >> 1) + u], make_float2(__uint_as_float(ww[u] << 16), __uint_as_float(ww[u] & 0xffff0000u)));
         }
       } else {
         const __nv_bfloat16 *r1 = (const __nv_bfloat16 *)ep.residual + roff;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) v[c] = __fadd_rn(v[c], __bfloat162float(r1[c]));
+        for (int u = 0; u < 16; ++u) v[u] = fadd2(v[u], make_float2(__bfloat162float(r1[2 * u]), __bfloat162float(r1[2 * u + 1])));
       }
     } else {
       const float *r = (const float *)ep.residual + roff;
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = __fadd_rn(v[c], r[c]);
+      for (int u = 0; u < 16; ++u) v[u] = fadd2(v[u], make_float2(r[2 * u], r[2 * u + 1]));
     }
   }
   if (ep.act != SOFIE_B200_ACT_NONE) {
     if (ep.act == SOFIE_B200_ACT_RELU) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_RELU, 0.f);
+      for (int u = 0; u < 16; ++u) v[u] = make_float2(act_apply(v[u].x, SOFIE_B200_ACT_RELU, 0.f), act_apply(v[u].y, SOFIE_B200_ACT_RELU, 0.f));
     } else if (ep.act == SOFIE_B200_ACT_GELU_ERF) {
       if (ep.y_dtype == SOFIE_B200_BF16) {
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) unpack2(gelu_erf_pair_lowp(pack2(v[c], v[c + 1])), v[c], v[c + 1]);
+        for (int u = 0; u < 16; ++u) v[u] = gelu_erf_pair_lowp(v[u]);
       } else {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_GELU_ERF, 0.f);
+        for (int u = 0; u < 16; ++u)
+          v[u] = make_float2(act_apply(v[u].x, SOFIE_B200_ACT_GELU_ERF, 0.f), act_apply(v[u].y, SOFIE_B200_ACT_GELU_ERF, 0.f));
       }
     } else {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], ep.act, ep.act_alpha);
+      for (int u = 0; u < 16; ++u) v[u] = make_float2(act_apply(v[u].x, ep.act, ep.act_alpha), act_apply(v[u].y, ep.act, ep.act_alpha));
     }
   }
   if (ep.y_dtype == SOFIE_B200_BF16) {
     uint32_t w[16];
 #pragma unroll
     for (int u = 0; u < 16; ++u) {
-      __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * u], v[2 * u + 1]);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(v[u].x, v[u].y);
       w[u] = *reinterpret_cast<uint32_t *>(&h2);
     }
     stage_units<4>(stage, w, slot);
   } else if (ep.y_dtype == SOFIE_B200_F32) {
     uint32_t w[32];
 #pragma unroll
-    for (int c = 0; c < 32; ++c) w[c] = __float_as_uint(v[c]);
+    for (int u = 0; u < 16; ++u) { w[2 * u] = __float_as_uint(v[u].x); w[2 * u + 1] = __float_as_uint(v[u].y); }
     stage_units<8>(stage, w, slot);
   } else {  // I8 / U8: ONNX rounding (half to even), zero point, saturate
     const int lo = ep.y_dtype == SOFIE_B200_I8 ? -128 : 0, hi = ep.y_dtype == SOFIE_B200_I8 ? 127 : 255;
     const int zp = ep.out_zp;
     if (__builtin_expect(ep.out_scale != 1.f, 0)) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = __fdiv_rn(v[c], ep.out_scale);
+      for (int u = 0; u < 16; ++u) v[u] = make_float2(__fdiv_rn(v[u].x, ep.out_scale), __fdiv_rn(v[u].y, ep.out_scale));
     }
     // rint(v) + zp saturated to [lo, hi], in integers: v is first clamped to +-2^30 (far outside [lo - zp, hi - zp],
     // NaN goes to -2^30 as fmaxf drops it, which saturates to lo like the float formula), so neither the conversion
     // nor the addition can overflow.
     int q[32];
 #pragma unroll
-    for (int c = 0; c < 32; ++c) q[c] = min(max(__float2int_rn(fminf(fmaxf(v[c], -1073741824.f), 1073741824.f)) + zp, lo), hi);
+    for (int u = 0; u < 16; ++u) {
+      q[2 * u] = min(max(__float2int_rn(fminf(fmaxf(v[u].x, -1073741824.f), 1073741824.f)) + zp, lo), hi);
+      q[2 * u + 1] = min(max(__float2int_rn(fminf(fmaxf(v[u].y, -1073741824.f), 1073741824.f)) + zp, lo), hi);
+    }
     uint32_t w[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -562,7 +540,7 @@ __device__ __forceinline__ void drain_accumulator(const EpiParams &ep, uint32_t 
     { DRAIN_T0();
       if (fast && c_end - c >= 32) {
         const long long rr = row < rows_total ? row : rows_total - 1;   // rows past the end compute on the last row's operands
-        float v[32];
+        float2 v[16];
         const bool more = epi_values_fast<ACC_INT>(ep, raw, v, rr, n0 + c, stage, j);
         if (has_next) ptx::tmem_ld_x32(taddr + 32 * ch2, raw);
         if (more) epi_finish_fast(ep, v, b, rr, n0 + c, stage, j);
