@@ -86,7 +86,7 @@ def convnet_oracle(o, x: np.ndarray, weights, int8: bool) -> np.ndarray:
 class ConvNetB200:
     """The network on one GPU through the C ABI.  `ctx` is a sofie_b200.ops.Context on that GPU."""
 
-    LAUNCHES = 8 * 2 + 2   # unfold + contraction per layer, pool, classifier
+    LAUNCHES = 8 * 2 + 7 + 2   # unfold + contraction per layer, channels-last copy of the input for layers 2-8, pool, classifier
 
     def __init__(self, ctx, weights, batch: int, img: int, int8: bool, device: str):
         import torch

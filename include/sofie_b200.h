@@ -234,7 +234,9 @@ int sofie_b200_conv_out_shape(const sofie_b200_conv_desc *desc, int64_t *Ho, int
 /* Bytes of caller-provided scratch the plan needs per enqueue (0 if none): the unfolded input,
  * [groups][N][Ho*Wo][kpad] elements with kpad = C/groups*R*S rounded up to 16 bytes -- times three for an
  * F32 convolution at precise = 1 of at least SOFIE_B200_SPLIT_MIN_FLOPS (2 * K/groups * Ho*Wo * kpad * N),
- * which runs as error-compensated 3xTF32 on the tensor cores and unfolds into three K segments.  The Im2Col
+ * which runs as error-compensated 3xTF32 on the tensor cores and unfolds into three K segments; plus a channels-last
+ * copy of the input (N*C*H*W elements, 256-byte aligned behind the unfolded matrix) when C/groups is a whole number
+ * of 16-byte vectors, from which the unfold is plain vector copies.  The Im2Col
  * scratch of the reference is per image (ROperator_Conv.hxx:1002-1103); this one covers the batch. */
 #define SOFIE_B200_SPLIT_MIN_FLOPS 4e8
 int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan);

@@ -88,6 +88,8 @@ inline size_t ConvWorkspaceBytes(const ConvGeometry &g, size_t elemSize)
    size_t bytes = g.group * g.N * g.Ho * g.Wo * kpad * elemSize;
    // a large fp32 convolution runs as 3xTF32 and unfolds into three K segments (SOFIE_B200_SPLIT_MIN_FLOPS of sofie_b200.h)
    if (elemSize == sizeof(float) && 2.0 * double(g.K / g.group) * double(g.Ho * g.Wo) * double(kpad) * double(g.N) >= 4e8) bytes *= 3;
+   // when the channels per group are whole 16-byte vectors the library unfolds from a channels-last copy of the input kept behind it
+   if ((g.C / g.group) % vec == 0) bytes = (bytes + 255) / 256 * 256 + g.N * g.C * g.H * g.W * elemSize;
    return bytes;
 }
 

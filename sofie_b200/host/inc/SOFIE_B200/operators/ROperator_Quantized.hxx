@@ -237,6 +237,8 @@ public:
       std::stringstream out;
       out << "      {  // QLinearConv " << opName << "\n" << ConvDescCode(fGeo, "SOFIE_B200_I8", ConvertTypeToRuntimeEnum(fTypeY), fXZp);
       out << "      Check(sofie_b200_conv_plan_create(ctx, &d, tensor_" << fNW << ", &plan_" << opName << "), \"QLinearConv " << opName << ": plan\");\n";
+      out << "      if (sofie_b200_conv_workspace_bytes(plan_" << opName << ") > " << ConvWorkspaceBytes(fGeo, 1) << "LL)\n"
+          << "         throw std::runtime_error(\"QLinearConv " << opName << ": the library wants more scratch than the arena reserves\");\n";
       out << fEpi.InitCode("ep_" + opName) << "      }\n";
       return out.str();
    }
