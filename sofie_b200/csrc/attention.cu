@@ -204,16 +204,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         break;
       }
       tc_fence_after();
-      uint32_t r[32];
-      // pass 1: row maximum over the keys that exist
+      // Two register buffers: the tcgen05.ld of the next 32 columns is in flight while the current ones are processed,
+      // and pass 2 starts loading before pass 1 has finished its arithmetic.
+      uint32_t ra[32], rb[32];
       float mx = -3.0e38f;
-#pragma unroll
-      for (int c = 0; c < 128; c += 32) {
-        tmem_ld_x32(t_s + c, r);
-        tmem_ld_wait();
+      auto max_of = [&](const uint32_t (&r)[32], int c) {
 #pragma unroll
         for (int u = 0; u < 32; ++u) mx = fmaxf(mx, (c + u < p.seq) ? __uint_as_float(r[u]) * p.scale_log2e : -3.0e38f);
-      }
+      };
+      // pass 1: row maximum over the keys that exist
+      tmem_ld_x32(t_s, ra);
+      tmem_ld_wait(); tmem_ld_x32(t_s + 32, rb); max_of(ra, 0);
+      tmem_ld_wait(); tmem_ld_x32(t_s + 64, ra); max_of(rb, 32);
+      tmem_ld_wait(); tmem_ld_x32(t_s + 96, rb); max_of(ra, 64);
+      tmem_ld_wait(); tmem_ld_x32(t_s, ra);      max_of(rb, 96);     // first chunk of pass 2 already on its way
       if (store_pending) {   // the previous output store of this warp must have read the buffer P is written to
         if (lane == 0) bulk_wait_read_all();
         __syncwarp();
@@ -222,10 +226,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       // pass 2: unnormalised probabilities as bf16 into shared memory, fp32 row sum
       const float off = mx;   // maximum of the scaled scores (any sign of the scale)
       float sum = 0.f;
-#pragma unroll
-      for (int c = 0; c < 128; c += 32) {
-        tmem_ld_x32(t_s + c, r);
-        tmem_ld_wait();
+      auto exp_store = [&](const uint32_t (&r)[32], int c) {
         uint32_t w[16];
 #pragma unroll
         for (int u = 0; u < 32; u += 2) {
@@ -244,7 +245,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile + (((u0 + u) ^ swz) << 4)), "r"(w[4 * u]), "r"(w[4 * u + 1]),
                        "r"(w[4 * u + 2]), "r"(w[4 * u + 3])
                        : "memory");
-      }
+      };
+      tmem_ld_wait(); tmem_ld_x32(t_s + 32, rb); exp_store(ra, 0);
+      tmem_ld_wait(); tmem_ld_x32(t_s + 64, ra); exp_store(rb, 32);
+      tmem_ld_wait(); tmem_ld_x32(t_s + 96, rb); exp_store(ra, 64);
+      tmem_ld_wait();                            exp_store(rb, 96);
       fence_proxy_async();   // generic-proxy writes of P become visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p + 8 * set);
@@ -256,15 +261,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
       tc_fence_after();
       const float inv = 1.f / sum;
       uint32_t w[32];
+      tmem_ld_x32(t_o, ra);
+      tmem_ld_x32(t_o + 32, rb);
+      tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < 64; c += 32) {
-        tmem_ld_x32(t_o + c, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int u = 0; u < 32; u += 2) {
-          __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[u]) * inv, __uint_as_float(r[u + 1]) * inv);
-          w[(c + u) >> 1] = *reinterpret_cast<uint32_t *>(&h2);
-        }
+      for (int u = 0; u < 32; u += 2) {
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(ra[u]) * inv, __uint_as_float(ra[u + 1]) * inv);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(rb[u]) * inv, __uint_as_float(rb[u + 1]) * inv);
+        w[u >> 1] = *reinterpret_cast<uint32_t *>(&h0);
+        w[16 + (u >> 1)] = *reinterpret_cast<uint32_t *>(&h1);
       }
       tc_fence_before();
       __syncwarp();

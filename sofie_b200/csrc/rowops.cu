@@ -89,6 +89,17 @@ template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4 
     v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
   }
 }
+// The same chunk as pairs of fp32 (the operands of the packed f32x2 instructions).
+template <typename T> __device__ __forceinline__ void unpack16_pairs(const uint4 &r, float2 *v);
+template <> __device__ __forceinline__ void unpack16_pairs<float>(const uint4 &r, float2 *v) {
+  v[0] = make_float2(__uint_as_float(r.x), __uint_as_float(r.y));
+  v[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
+}
+template <> __device__ __forceinline__ void unpack16_pairs<__nv_bfloat16>(const uint4 &r, float2 *v) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+}
 template <typename T> __device__ __forceinline__ uint4 fill16(bool minus_inf);
 template <> __device__ __forceinline__ uint4 fill16<float>(bool mi) { const uint32_t u = mi ? 0xff800000u : 0u; return make_uint4(u, u, u, u); }
 template <> __device__ __forceinline__ uint4 fill16<__nv_bfloat16>(bool mi) { const uint32_t u = mi ? 0xff80ff80u : 0u; return make_uint4(u, u, u, u); }
@@ -119,49 +130,61 @@ __global__ void __launch_bounds__(256, (MODE == 0 ? (CH >= 16 ? 2 : (CH >= 8 && 
       r[c] = (live && col < cols) ? ld_raw16(xr + col) : fill16<TIn>(MODE != 0);
     }
     if constexpr (MODE == 0) {
-      float s = 0.f;
+      // LayerNorm on pairs (packed fp32 arithmetic, two values per instruction, each half rounded as the scalar
+      // instruction would): the kernel kept the row packed to stay at 4 CTAs per SM and was half issue-bound
+      // from unpacking and scalar arithmetic in three passes.
+      constexpr int P = E / 2;
+      float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
-        float v[E];
-        unpack16<TIn>(r[c], v);
+        float2 v[P];
+        unpack16_pairs<TIn>(r[c], v);
 #pragma unroll
-        for (int e = 0; e < E; ++e) s += v[e];
+        for (int e = 0; e < P; ++e) s2 = __fadd2_rn(s2, v[e]);
       }
-      const float mean = group_sum(s, G) * inv_n;
-      float q = 0.f;
+      const float mean = group_sum(s2.x + s2.y, G) * inv_n;
+      const float2 nmean2 = make_float2(-mean, -mean);
+      float2 q2 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
         const int col = (c * G + gl) * E;
         if (col < cols) {
-          float v[E];
-          unpack16<TIn>(r[c], v);
+          float2 v[P];
+          unpack16_pairs<TIn>(r[c], v);
 #pragma unroll
-          for (int e = 0; e < E; ++e) { float d = v[e] - mean; q += d * d; }
+          for (int e = 0; e < P; ++e) { const float2 d = __fadd2_rn(v[e], nmean2); q2 = __ffma2_rn(d, d, q2); }
         }
       }
-      const float var = group_sum(q, G) * inv_n;
+      const float var = group_sum(q2.x + q2.y, G) * inv_n;
       const float inv = 1.f / sqrtf(var + eps);
+      const float2 inv2 = make_float2(inv, inv);
       if (live) {
         TOut *yr = y + row * (long long)cols;
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
           const int col = (c * G + gl) * E;
           if (col < cols) {
-            float v[E], o[E], sc[E], bi[E];
-            unpack16<TIn>(r[c], v);
+            float2 v[P];
+            float o[E];
+            unpack16_pairs<TIn>(r[c], v);
 #pragma unroll
             for (int e = 0; e < E; e += 4) {  // scale / bias: 128-bit loads (cols % E == 0 and 16-byte aligned, checked by the host)
               const float4 s4 = scale ? *reinterpret_cast<const float4 *>(scale + col + e) : make_float4(1.f, 1.f, 1.f, 1.f);
               const float4 b4 = bias ? *reinterpret_cast<const float4 *>(bias + col + e) : make_float4(0.f, 0.f, 0.f, 0.f);
-              sc[e] = s4.x; sc[e + 1] = s4.y; sc[e + 2] = s4.z; sc[e + 3] = s4.w;
-              bi[e] = b4.x; bi[e + 1] = b4.y; bi[e + 2] = b4.z; bi[e + 3] = b4.w;
-            }
-#pragma unroll
-            for (int e = 0; e < E; ++e) {
-              const float dlt = v[e] - mean;  // scale * invStd * (x - mean) + bias, left to right
-              float t = scale ? (sc[e] * inv) * dlt : inv * dlt;
-              if (bias) t += bi[e];
-              o[e] = t;
+              // scale * invStd * (x - mean) + bias, left to right, each step rounded
+              float2 t0 = __fadd2_rn(v[e / 2], nmean2), t1 = __fadd2_rn(v[e / 2 + 1], nmean2);
+              if (scale) {
+                t0 = __fmul2_rn(__fmul2_rn(make_float2(s4.x, s4.y), inv2), t0);
+                t1 = __fmul2_rn(__fmul2_rn(make_float2(s4.z, s4.w), inv2), t1);
+              } else {
+                t0 = __fmul2_rn(inv2, t0);
+                t1 = __fmul2_rn(inv2, t1);
+              }
+              if (bias) {
+                t0 = __fadd2_rn(t0, make_float2(b4.x, b4.y));
+                t1 = __fadd2_rn(t1, make_float2(b4.z, b4.w));
+              }
+              o[e] = t0.x; o[e + 1] = t0.y; o[e + 2] = t1.x; o[e + 3] = t1.y;
             }
             store_chunk_as<TOut, E>(yr + col, o);
           }
