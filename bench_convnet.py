@@ -21,7 +21,7 @@ Y_SCALE = np.float32(0.05)        # activation scale of every int8 layer output
 IN_SCALE = np.float32(1.0 / 127)  # U(0,1) input quantised to 0..127
 
 
-def conv_desc(n, c, h, w, k, stride, x_dtype, y_dtype):
+def conv_desc(n, c, h, w, k, stride, x_dtype, y_dtype, x_layout=0, y_layout=0):
     from sofie_b200 import lib as L
     d = L.ConvDesc()
     d.N, d.C, d.H, d.W, d.K, d.R, d.S = n, c, h, w, k, 3, 3
@@ -30,6 +30,7 @@ def conv_desc(n, c, h, w, k, stride, x_dtype, y_dtype):
     d.dil_h = d.dil_w = 1
     d.groups = 1
     d.x_dtype, d.y_dtype, d.x_zero_point, d.precise = x_dtype, y_dtype, 0, 1
+    d.x_layout, d.y_layout = x_layout, y_layout
     return d
 
 
@@ -86,9 +87,12 @@ def convnet_oracle(o, x: np.ndarray, weights, int8: bool) -> np.ndarray:
 class ConvNetB200:
     """The network on one GPU through the C ABI.  `ctx` is a sofie_b200.ops.Context on that GPU."""
 
-    LAUNCHES = 8 * 2 + 7 + 2   # unfold + contraction per layer, channels-last copy of the input for layers 2-8, pool, classifier
+    LAUNCHES = 8 * 2 + 2            # unfold + contraction per layer, pool, classifier
+    LAUNCHES_NCHW = 8 * 2 + 7 + 2   # every tensor NCHW: plus a channels-last copy of the input of layers 2-8
 
-    def __init__(self, ctx, weights, batch: int, img: int, int8: bool, device: str):
+    def __init__(self, ctx, weights, batch: int, img: int, int8: bool, device: str, channels_last: bool = True):
+        """channels_last: the activations between the convolutions are kept [N,H,W,C] (what a layout pass of the generator
+        would emit for a conv -> conv chain); the network's input and the last convolution's output stay NCHW."""
         import torch
         from sofie_b200 import lib as L
         from sofie_b200.ops import GemmPlan, make_epilogue
@@ -101,8 +105,9 @@ class ConvNetB200:
         self.plans, self.eps, self.keep, self.acts, self.kernels = [], [], [], [], []
         hw, ws_bytes = img, 16
         self.x_in = t.empty((batch, 3, img, img), dtype=adt, device=device)
-        for ly, st, cin, cout in zip(layers, STRIDES, CHANNELS[:-1], CHANNELS[1:]):
-            d = conv_desc(batch, cin, hw, hw, cout, st, code, code)
+        for i, (ly, st, cin, cout) in enumerate(zip(layers, STRIDES, CHANNELS[:-1], CHANNELS[1:])):
+            xl, yl = (1 if channels_last and i > 0 else 0), (1 if channels_last and i < 7 else 0)
+            d = conv_desc(batch, cin, hw, hw, cout, st, code, code, xl, yl)
             w = t.from_numpy(ly["w"]).to(device)
             h = C.c_void_p()
             L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), w.data_ptr(), C.byref(h)), "conv_plan_create")
@@ -110,7 +115,7 @@ class ConvNetB200:
             hw = (hw + 2 - 3) // st + 1
             ep, keep = make_epilogue(col_scale=t.from_numpy(ly["scale"]).to(device), bias=t.from_numpy(ly["bias"]).to(device), act=L.ACT_RELU)
             self.plans.append(h); self.eps.append(ep); self.keep.append((keep, w))
-            self.acts.append(t.empty((batch, cout, hw, hw), dtype=adt, device=device))
+            self.acts.append(t.empty((batch, hw, hw, cout) if yl else (batch, cout, hw, hw), dtype=adt, device=device))
             self.kernels.append(lib.sofie_b200_conv_plan_kernel(h).decode())
         ctx.sync()   # weight re-layout kernels read `w`
         self.workspace = t.empty(ws_bytes, dtype=t.uint8, device=device)

@@ -160,6 +160,12 @@ typedef struct sofie_b200_conv_desc {
   int32_t y_dtype;               /* F32, BF16 or I8           */
   int32_t x_zero_point;          /* I8 input zero point: padding is filled with it */
   int32_t precise;               /* as in sofie_b200_gemm_desc */
+  int32_t x_layout;              /* 0: X is [N,C,H,W] (the reference's layout); 1: X is channels-last, [N,H,W,C]      */
+  int32_t y_layout;              /* the same for Y (and for a residual in the epilogue).  Channels-last is for       */
+                                 /* conv -> conv chains: a generator keeps the chain channels-last and converts at   */
+                                 /* its ends; the unfold then needs no layout copy and output pixels, not channels,  */
+                                 /* fill the 128 accumulator rows.  x_layout = 1 needs C/groups to be a whole number */
+                                 /* of 16-byte vectors.                                                              */
 } sofie_b200_conv_desc;
 
 typedef struct sofie_b200_ctx sofie_b200_ctx;

@@ -19,6 +19,7 @@ struct sofie_b200_conv_plan {
   int64_t kdim = 0, kpad = 0;  // C/g*R*S and its padded pitch
   void *w_padded = nullptr;    // [K, kpad] device copy of the weights ([K, 3*kpad] hi|lo|hi in split mode)
   int split = 0;               // fp32 at fp32 accuracy on the tensor cores: operands carry three K segments (gemm_split.cu)
+  int pix_rows = 0;            // y_layout = channels-last: output pixels are the accumulator rows, the unfolded input is the A operand
   int nhwc = 0;                // channels-last unfold: the input is first transposed to [N, H, W, C] in the workspace and K runs
                                // (r, s, c), so every 16-byte chunk of the unfolded matrix is one aligned vector copy
   sofie_b200_gemm_plan *gemm = nullptr;
@@ -97,7 +98,7 @@ __global__ void __launch_bounds__(256) unfold_kernel(const T *__restrict__ x, T 
 
 // fp32 input unfolded straight into the split form of the B operand: xcol[g][n][pix][hi | hi | lo], each segment kpad wide.
 __global__ void __launch_bounds__(256) unfold_split_kernel(const float *__restrict__ x, float *__restrict__ xcol, sofie_b200_conv_desc d,
-                                                           long long Ho, long long Wo, long long cg, long long kdim, long long kpad) {
+                                                           long long Ho, long long Wo, long long cg, long long kdim, long long kpad, int a_side) {
   const unsigned chunks = (unsigned)(kpad / 4), pix = (unsigned)(Ho * Wo);
   const long long total = (long long)d.groups * d.N * pix * chunks;
   const int H = (int)d.H, W = (int)d.W, R = (int)d.R, S = (int)d.S;
@@ -117,10 +118,10 @@ __global__ void __launch_bounds__(256) unfold_split_kernel(const float *__restri
       lo[e] = tf32_rn(__fsub_rn(val, hi[e]));
       if (++s == S) { s = 0; if (++r == R) { r = 0; ++c; } }
     }
-    float *o = xcol + u.row * 3 * kpad + u.ch * 4;
+    float *o = xcol + u.row * 3 * kpad + u.ch * 4;   // B operand: hi | hi | lo; A operand (a_side): hi | lo | hi
     *reinterpret_cast<uint4 *>(o) = *reinterpret_cast<const uint4 *>(hi);
-    *reinterpret_cast<uint4 *>(o + kpad) = *reinterpret_cast<const uint4 *>(hi);
-    *reinterpret_cast<uint4 *>(o + 2 * kpad) = *reinterpret_cast<const uint4 *>(lo);
+    *reinterpret_cast<uint4 *>(o + kpad) = *reinterpret_cast<const uint4 *>(a_side ? lo : hi);
+    *reinterpret_cast<uint4 *>(o + 2 * kpad) = *reinterpret_cast<const uint4 *>(a_side ? hi : lo);
   }
 }
 
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(256) reorder_weights_kernel(const T *__restric
 // xcol[g][n][pix][(r, s, c)] from the channels-last input; one thread copies 16 bytes.  SPLIT writes hi | hi | lo.
 template <typename T, int VEC, bool SPLIT>
 __global__ void __launch_bounds__(256) unfold_nhwc_kernel(const T *__restrict__ x, T *__restrict__ xcol, sofie_b200_conv_desc d, long long Ho,
-                                                          long long Wo, long long cg, long long kdim, T pad_value) {
+                                                          long long Wo, long long cg, long long kdim, T pad_value, int a_side) {
   const unsigned chunks = (unsigned)(kdim / VEC), pix = (unsigned)(Ho * Wo), ccg = (unsigned)cg;
   const long long total = (long long)d.groups * d.N * pix * chunks;
   const int H = (int)d.H, W = (int)d.W, S = (int)d.S;
@@ -223,8 +224,8 @@ __global__ void __launch_bounds__(256) unfold_nhwc_kernel(const T *__restrict__ 
       }
       float *o = (float *)xcol + row * 3 * kdim + ch * 4;
       *reinterpret_cast<uint4 *>(o) = *reinterpret_cast<const uint4 *>(hi);
-      *reinterpret_cast<uint4 *>(o + kdim) = *reinterpret_cast<const uint4 *>(hi);
-      *reinterpret_cast<uint4 *>(o + 2 * kdim) = *reinterpret_cast<const uint4 *>(lo);
+      *reinterpret_cast<uint4 *>(o + kdim) = *reinterpret_cast<const uint4 *>(a_side ? lo : hi);
+      *reinterpret_cast<uint4 *>(o + 2 * kdim) = *reinterpret_cast<const uint4 *>(a_side ? hi : lo);
     }
   }
 }
@@ -262,12 +263,17 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
     return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: channels %lld / filters %lld not divisible by groups %d", (long long)d.C, (long long)d.K, d.groups);
   if (d.x_dtype != SOFIE_B200_F32 && d.x_dtype != SOFIE_B200_I8)
     return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: input type %d not supported (F32, I8)", d.x_dtype);
+  if ((d.x_layout != 0 && d.x_layout != 1) || (d.y_layout != 0 && d.y_layout != 1))
+    return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: layouts are 0 (NCHW) or 1 (channels-last)");
+  if (d.x_layout == 1 && (d.C / d.groups) % (16 / dtype_size(d.x_dtype)) != 0)
+    return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: a channels-last input needs C/groups to be a whole number of 16-byte vectors");
   int64_t Ho, Wo;
   int rc = conv_out_shape(d, &Ho, &Wo);
   if (rc) return rc;
   SB_CUDA(cudaSetDevice(ctx->device));
   const int es = dtype_size(d.x_dtype);
   sofie_b200_conv_plan *p = new sofie_b200_conv_plan();
+  p->pix_rows = d.y_layout == 1;
   p->ctx = ctx; p->d = d; p->Ho = Ho; p->Wo = Wo;
   p->cg = d.C / d.groups; p->kg = d.K / d.groups;
   p->kdim = p->cg * d.R * d.S;
@@ -277,19 +283,24 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   // the input split by the unfold kernel; small ones stay on the fp32 FMA kernel.
   const int64_t images = d.N > 0 ? d.N : 1;
   sofie_b200_gemm_desc g{};
-  g.M = p->kg; g.N = Ho * Wo; g.batch = images;
   g.trans_a = 0; g.trans_b = 1;
   g.ab_dtype = d.x_dtype; g.y_dtype = d.y_dtype;
-  g.ldy = Ho * Wo; g.stride_a = 0; g.stride_y = d.K * Ho * Wo; g.stride_r = d.K * Ho * Wo;
+  if (!p->pix_rows) {   // Y[n] = W x xcol[n]^T: channels are rows, one contraction per image (batched)
+    g.M = p->kg; g.N = Ho * Wo; g.batch = images;
+    g.ldy = Ho * Wo; g.stride_a = 0; g.stride_y = d.K * Ho * Wo; g.stride_r = d.K * Ho * Wo;
+  } else {              // Y = xcol x W^T: all output pixels of the batch are the rows, channels the columns (channels-last Y)
+    g.M = images * Ho * Wo; g.N = p->kg; g.batch = 1;
+    g.ldy = d.K;
+  }
   if (d.x_dtype == SOFIE_B200_F32 && d.precise != 0 && images <= 65535 && !getenv("SOFIE_B200_NO_3XTF32") &&
       2.0 * (double)p->kg * (double)(Ho * Wo) * (double)p->kpad * (double)images >= SPLIT_MIN_FLOPS) {
-    g.K = 3 * p->kpad; g.lda = g.ldb = 3 * p->kpad; g.stride_b = Ho * Wo * 3 * p->kpad; g.precise = 0;
+    g.K = 3 * p->kpad; g.lda = g.ldb = 3 * p->kpad; g.stride_b = p->pix_rows ? 0 : Ho * Wo * 3 * p->kpad; g.precise = 0;
     rc = gemm_plan_create_promote(ctx, g, &p->gemm);
     if (rc < 0) { delete p; return rc; }
     p->split = (rc == 0);
   }
   // channels-last unfold when the per-group channel count is a whole number of 16-byte vectors (then kpad == kdim)
-  p->nhwc = (p->cg % vec == 0 && d.N <= 65535 && !getenv("SOFIE_B200_NO_NHWC")) ? 1 : 0;
+  p->nhwc = (d.x_layout == 1 || (p->cg % vec == 0 && d.N <= 65535 && !getenv("SOFIE_B200_NO_NHWC"))) ? 1 : 0;
   const void *w_src = W;
   void *w_perm = nullptr;
   if (p->nhwc) {
@@ -317,7 +328,8 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   const long long total = d.K * p->kpad;
   const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 16);
   if (p->split) {
-    rc = split3_enqueue(ctx, (const float *)w_src, (float *)p->w_padded, d.K, p->kdim, p->kpad, p->kdim, 1, 0, 0, 0);
+    // the weights are the A operand (hi | lo | hi) when channels are rows, the B operand (hi | hi | lo) when pixels are
+    rc = split3_enqueue(ctx, (const float *)w_src, (float *)p->w_padded, d.K, p->kdim, p->kpad, p->kdim, 1, 0, 0, p->pix_rows ? 1 : 0);
     free_perm();
     if (rc) { sofie_b200_gemm_plan_destroy(p->gemm); cudaFree(p->w_padded); delete p; return rc; }
     *out = p;
@@ -332,7 +344,7 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   if (e != cudaSuccess) { cudaFree(p->w_padded); delete p; return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: %s", cudaGetErrorString(e)); }
   ctx->launches++;
 
-  g.K = p->kpad; g.lda = p->kpad; g.ldb = p->kpad; g.stride_b = Ho * Wo * p->kpad;
+  g.K = p->kpad; g.lda = p->kpad; g.ldb = p->kpad; g.stride_b = p->pix_rows ? 0 : Ho * Wo * p->kpad;
   g.precise = d.precise;
   rc = sofie_b200_gemm_plan_create(ctx, &g, &p->gemm);
   if (rc) { cudaFree(p->w_padded); delete p; return rc; }
@@ -357,7 +369,7 @@ int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan) {
   if (!plan) return 0;
   const int64_t es = dtype_size(plan->d.x_dtype);
   const int64_t xcol = (int64_t)plan->d.groups * plan->d.N * plan->Ho * plan->Wo * plan->kpad * (plan->split ? 3 : 1) * es;
-  if (!plan->nhwc) return xcol;
+  if (!plan->nhwc || plan->d.x_layout == 1) return xcol;   // a channels-last input needs no copy
   return (xcol + 255) / 256 * 256 + plan->d.N * plan->d.C * plan->d.H * plan->d.W * es;   // + the channels-last copy of the input
 }
 
@@ -378,6 +390,9 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
     const long long xcol_bytes = (long long)d.groups * d.N * pix * plan->kpad * (plan->split ? 3 : 1) * es;
     void *xl = (char *)workspace + (xcol_bytes + 255) / 256 * 256;
     const int HW = (int)(d.H * d.W), C_ = (int)d.C;
+    if (d.x_layout == 1) {
+      xl = const_cast<void *>(X);
+    } else {
     if (es == 1 && C_ % 4 == 0 && HW % 4 == 0)
       nchw_to_nhwc_bytes_kernel<<<dim3((HW + 127) / 128, (C_ + 63) / 64, (unsigned)d.N), 256, 0, ctx->stream>>>((const uint8_t *)X, (uint8_t *)xl, C_, HW);
     else if (es == 1)
@@ -386,14 +401,15 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
       nchw_to_nhwc_kernel<uint32_t><<<dim3((HW + 31) / 32, (C_ + 31) / 32, (unsigned)d.N), 256, 0, ctx->stream>>>((const uint32_t *)X, (uint32_t *)xl, C_, HW);
     SB_CUDA(cudaGetLastError());
     ctx->launches++;
+    }
     if (plan->split)
-      unfold_nhwc_kernel<float, 4, true><<<grid, 256, 0, ctx->stream>>>((const float *)xl, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, 0.f);
+      unfold_nhwc_kernel<float, 4, true><<<grid, 256, 0, ctx->stream>>>((const float *)xl, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, 0.f, plan->pix_rows);
     else if (es == 4)
-      unfold_nhwc_kernel<float, 4, false><<<grid, 256, 0, ctx->stream>>>((const float *)xl, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, 0.f);
+      unfold_nhwc_kernel<float, 4, false><<<grid, 256, 0, ctx->stream>>>((const float *)xl, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, 0.f, 0);
     else
-      unfold_nhwc_kernel<int8_t, 16, false><<<grid, 256, 0, ctx->stream>>>((const int8_t *)xl, (int8_t *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, (int8_t)d.x_zero_point);
+      unfold_nhwc_kernel<int8_t, 16, false><<<grid, 256, 0, ctx->stream>>>((const int8_t *)xl, (int8_t *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, (int8_t)d.x_zero_point, 0);
   } else if (plan->split)
-    unfold_split_kernel<<<grid, 256, 0, ctx->stream>>>((const float *)X, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad);
+    unfold_split_kernel<<<grid, 256, 0, ctx->stream>>>((const float *)X, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, plan->pix_rows);
   else if (d.x_dtype == SOFIE_B200_F32)
     unfold_kernel<float, 4><<<grid, 256, 0, ctx->stream>>>((const float *)X, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, 0.f);
   else
@@ -405,6 +421,30 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
   // (documented per column = per channel) become per-row vectors.
   sofie_b200_epilogue e{};
   e.alpha = 1.f; e.beta = 1.f; e.out_scale = 1.f;
+  const int ys = dtype_size(d.y_dtype);
+  if (plan->pix_rows) {
+    // Channels are accumulator columns: the caller's per-channel vectors apply as they are.
+    if (ep) {
+      if (ep->row_scale) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: row_scale has no meaning for a convolution");
+      if (ep->bias_mode == SOFIE_B200_BIAS_ROW_F32 || ep->bias_mode == SOFIE_B200_BIAS_ROW_I32 || ep->bias_mode == SOFIE_B200_BIAS_FULL_F32)
+        return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: bias_mode %d not supported for a convolution", ep->bias_mode);
+      e = *ep;
+      e.ldr = d.K;
+    }
+    const long long kw = plan->split ? 3 * plan->kpad : plan->kpad;
+    for (int g = 0; g < d.groups; ++g) {
+      sofie_b200_epilogue eg = e;
+      if (eg.col_scale) eg.col_scale += g * plan->kg;
+      if (eg.bias && eg.bias_mode != SOFIE_B200_BIAS_SCALAR_F32) eg.bias = (const char *)eg.bias + (size_t)g * plan->kg * 4;
+      if (eg.residual) eg.residual = (const char *)eg.residual + (size_t)g * plan->kg * dtype_size(eg.residual_dtype);
+      const char *a = (const char *)workspace + (size_t)g * d.N * pix * kw * es;
+      const char *b = (const char *)plan->w_padded + (size_t)g * plan->kg * kw * es;
+      char *y = (char *)Y + (size_t)g * plan->kg * ys;
+      int rc = sofie_b200_gemm_enqueue(plan->gemm, a, b, y, &eg);
+      if (rc) return rc;
+    }
+    return 0;
+  }
   if (ep) {
     if (ep->row_scale) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: row_scale has no meaning for a convolution");
     e = *ep;
@@ -418,7 +458,6 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
     }
     e.ldr = pix;
   }
-  const int ys = dtype_size(d.y_dtype);
   for (int g = 0; g < d.groups; ++g) {
     sofie_b200_epilogue eg = e;
     if (eg.row_scale) eg.row_scale += g * plan->kg;
@@ -483,6 +522,7 @@ static int conv_static_scratch(int device, unsigned char **out) {
 extern "C" int sofie_b200_conv_enqueue_noalloc(sofie_b200_ctx *ctx, const sofie_b200_conv_desc *desc, const void *X,
                                                const void *W, void *Y, const sofie_b200_epilogue *ep) {
   if (!ctx || !desc) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: NULL argument");
+  if (desc->x_layout != 0 || desc->y_layout != 0) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: only the NCHW layouts are supported");
   sofie_b200_conv_desc d = *desc;
   if (d.groups < 1) d.groups = 1;
   if (d.N < 0 || d.C < 1 || d.H < 1 || d.W < 1 || d.K < 1 || d.R < 1 || d.S < 1)

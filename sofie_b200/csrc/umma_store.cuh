@@ -345,41 +345,48 @@ __device__ __forceinline__ float2 gelu_erf_pair_lowp(float2 x) {
 // First half of the fast path: everything that reads the raw accumulator -- integer bias, conversion, the three
 // scales and the additive bias terms -- into v[32].  When it returns, `raw` is dead and the caller may already
 // load the next chunk into it.  Returns false when the chunk was finished here (int32 output: staged as is).
-template <bool ACC_INT>
-__device__ __forceinline__ bool epi_values_fast(const EpiParams &ep, const uint32_t (&raw)[32], float2 (&v)[16], long long rr, int col0,
+template <bool ACC_INT, int NC>
+__device__ __forceinline__ bool epi_values_fast(const EpiParams &ep, const uint32_t (&raw)[32 * NC], float2 (&v)[16 * NC], long long rr, int col0,
                                                 uint32_t stage, int slot) {
+  constexpr int W = 32 * NC;   // columns handled together: independent chains for the scheduler to interleave
   const int mode = ep.bias_mode;
   const int4 *bip = reinterpret_cast<const int4 *>(g_epi_izero);
   int rbi = 0;
+  int bi_step = 0;             // the neutral arrays are 32 entries long: they are re-read for every group of four columns
   if (ACC_INT) {
-    if (mode == SOFIE_B200_BIAS_COL_I32) bip = reinterpret_cast<const int4 *>((const int *)ep.bias + col0);
+    if (mode == SOFIE_B200_BIAS_COL_I32) { bip = reinterpret_cast<const int4 *>((const int *)ep.bias + col0); bi_step = 1; }
     if (mode == SOFIE_B200_BIAS_ROW_I32) rbi = ((const int *)ep.bias)[rr];
   }
   if (__builtin_expect(ep.y_dtype == SOFIE_B200_I32, 0)) {  // raw integer accumulator (+ int32 bias)
-    uint32_t w[32];
 #pragma unroll
-    for (int c = 0; c < 32; c += 4) {
-      const int4 bi = bip[c >> 2];
-      w[c] = (uint32_t)((int)raw[c] + bi.x + rbi); w[c + 1] = (uint32_t)((int)raw[c + 1] + bi.y + rbi);
-      w[c + 2] = (uint32_t)((int)raw[c + 2] + bi.z + rbi); w[c + 3] = (uint32_t)((int)raw[c + 3] + bi.w + rbi);
+    for (int i = 0; i < NC; ++i) {
+      uint32_t w[32];
+#pragma unroll
+      for (int c = 0; c < 32; c += 4) {
+        const int4 bi = bip[((32 * i + c) >> 2) * bi_step];
+        w[c] = (uint32_t)((int)raw[32 * i + c] + bi.x + rbi); w[c + 1] = (uint32_t)((int)raw[32 * i + c + 1] + bi.y + rbi);
+        w[c + 2] = (uint32_t)((int)raw[32 * i + c + 2] + bi.z + rbi); w[c + 3] = (uint32_t)((int)raw[32 * i + c + 3] + bi.w + rbi);
+      }
+      stage_units<8>(stage, w, slot + i);
     }
-    stage_units<8>(stage, w, slot);
     return false;
   }
   float rs = 1.f;
   if (ep.row_scale) rs = ep.row_scale[rr];
-  const float4 *csp = reinterpret_cast<const float4 *>(ep.col_scale ? ep.col_scale + col0 : g_epi_ones);
-  const float4 *bfp = reinterpret_cast<const float4 *>(mode == SOFIE_B200_BIAS_COL_F32 ? (const float *)ep.bias + col0 : g_epi_negzero);
+  const bool has_cs = ep.col_scale != nullptr, has_bf = mode == SOFIE_B200_BIAS_COL_F32;
+  const float4 *csp = reinterpret_cast<const float4 *>(has_cs ? ep.col_scale + col0 : g_epi_ones);
+  const float4 *bfp = reinterpret_cast<const float4 *>(has_bf ? (const float *)ep.bias + col0 : g_epi_negzero);
+  const int cs_step = has_cs ? 1 : 0, bf_step = has_bf ? 1 : 0;
   float rbf = -0.f;
   if (mode == SOFIE_B200_BIAS_ROW_F32) rbf = ((const float *)ep.bias)[rr];
   if (mode == SOFIE_B200_BIAS_SCALAR_F32) rbf = ((const float *)ep.bias)[0];
   const float2 rs2 = dup2(rs), alpha2 = dup2(ep.alpha), rbf2 = dup2(rbf);
 #pragma unroll
-  for (int c = 0; c < 32; c += 4) {
-    const float4 cs = csp[c >> 2], bf = bfp[c >> 2];
+  for (int c = 0; c < W; c += 4) {
+    const float4 cs = csp[(c >> 2) * cs_step], bf = bfp[(c >> 2) * bf_step];
     float2 xa, xb;
     if (ACC_INT) {
-      const int4 bi = bip[c >> 2];
+      const int4 bi = bip[(c >> 2) * bi_step];
       xa = make_float2((float)((int)raw[c] + bi.x + rbi), (float)((int)raw[c + 1] + bi.y + rbi));
       xb = make_float2((float)((int)raw[c + 2] + bi.z + rbi), (float)((int)raw[c + 3] + bi.w + rbi));
     } else {
@@ -393,15 +400,17 @@ __device__ __forceinline__ bool epi_values_fast(const EpiParams &ep, const uint3
 }
 
 // Second half of the fast path: residual, activation, conversion to the output type, staging.
-__device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)[16], long long b, long long rr, int col0, uint32_t stage,
+template <int NC>
+__device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)[16 * NC], long long b, long long rr, int col0, uint32_t stage,
                                                 int slot) {
+  constexpr int W = 32 * NC, P = 16 * NC;
   if (ep.residual) {
     const long long roff = b * ep.stride_r + rr * ep.ldr + col0;
     if (ep.residual_dtype == SOFIE_B200_BF16) {
       if (ep.residual_aligned) {
         const uint4 *r = reinterpret_cast<const uint4 *>((const __nv_bfloat16 *)ep.residual + roff);
 #pragma unroll
-        for (int c = 0; c < 32; c += 8) {
+        for (int c = 0; c < W; c += 8) {
           const uint4 q = r[c >> 3];
           const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -411,69 +420,78 @@ __device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)
       } else {
         const __nv_bfloat16 *r1 = (const __nv_bfloat16 *)ep.residual + roff;
 #pragma unroll
-        for (int u = 0; u < 16; ++u) v[u] = fadd2(v[u], make_float2(__bfloat162float(r1[2 * u]), __bfloat162float(r1[2 * u + 1])));
+        for (int u = 0; u < P; ++u) v[u] = fadd2(v[u], make_float2(__bfloat162float(r1[2 * u]), __bfloat162float(r1[2 * u + 1])));
       }
     } else {
       const float *r = (const float *)ep.residual + roff;
 #pragma unroll
-      for (int u = 0; u < 16; ++u) v[u] = fadd2(v[u], make_float2(r[2 * u], r[2 * u + 1]));
+      for (int u = 0; u < P; ++u) v[u] = fadd2(v[u], make_float2(r[2 * u], r[2 * u + 1]));
     }
   }
   if (ep.act != SOFIE_B200_ACT_NONE) {
     if (ep.act == SOFIE_B200_ACT_RELU) {
 #pragma unroll
-      for (int u = 0; u < 16; ++u) v[u] = make_float2(act_apply(v[u].x, SOFIE_B200_ACT_RELU, 0.f), act_apply(v[u].y, SOFIE_B200_ACT_RELU, 0.f));
+      for (int u = 0; u < P; ++u) v[u] = make_float2(act_apply(v[u].x, SOFIE_B200_ACT_RELU, 0.f), act_apply(v[u].y, SOFIE_B200_ACT_RELU, 0.f));
     } else if (ep.act == SOFIE_B200_ACT_GELU_ERF) {
       if (ep.y_dtype == SOFIE_B200_BF16) {
 #pragma unroll
-        for (int u = 0; u < 16; ++u) v[u] = gelu_erf_pair_lowp(v[u]);
+        for (int u = 0; u < P; ++u) v[u] = gelu_erf_pair_lowp(v[u]);
       } else {
 #pragma unroll
-        for (int u = 0; u < 16; ++u)
+        for (int u = 0; u < P; ++u)
           v[u] = make_float2(act_apply(v[u].x, SOFIE_B200_ACT_GELU_ERF, 0.f), act_apply(v[u].y, SOFIE_B200_ACT_GELU_ERF, 0.f));
       }
     } else {
 #pragma unroll
-      for (int u = 0; u < 16; ++u) v[u] = make_float2(act_apply(v[u].x, ep.act, ep.act_alpha), act_apply(v[u].y, ep.act, ep.act_alpha));
+      for (int u = 0; u < P; ++u) v[u] = make_float2(act_apply(v[u].x, ep.act, ep.act_alpha), act_apply(v[u].y, ep.act, ep.act_alpha));
     }
   }
   if (ep.y_dtype == SOFIE_B200_BF16) {
-    uint32_t w[16];
 #pragma unroll
-    for (int u = 0; u < 16; ++u) {
-      __nv_bfloat162 h2 = __floats2bfloat162_rn(v[u].x, v[u].y);
-      w[u] = *reinterpret_cast<uint32_t *>(&h2);
+    for (int i = 0; i < NC; ++i) {
+      uint32_t w[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[16 * i + u].x, v[16 * i + u].y);
+        w[u] = *reinterpret_cast<uint32_t *>(&h2);
+      }
+      stage_units<4>(stage, w, slot + i);
     }
-    stage_units<4>(stage, w, slot);
   } else if (ep.y_dtype == SOFIE_B200_F32) {
-    uint32_t w[32];
 #pragma unroll
-    for (int u = 0; u < 16; ++u) { w[2 * u] = __float_as_uint(v[u].x); w[2 * u + 1] = __float_as_uint(v[u].y); }
-    stage_units<8>(stage, w, slot);
+    for (int i = 0; i < NC; ++i) {
+      uint32_t w[32];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) { w[2 * u] = __float_as_uint(v[16 * i + u].x); w[2 * u + 1] = __float_as_uint(v[16 * i + u].y); }
+      stage_units<8>(stage, w, slot + i);
+    }
   } else {  // I8 / U8: ONNX rounding (half to even), zero point, saturate
     const int lo = ep.y_dtype == SOFIE_B200_I8 ? -128 : 0, hi = ep.y_dtype == SOFIE_B200_I8 ? 127 : 255;
     const int zp = ep.out_zp;
     if (__builtin_expect(ep.out_scale != 1.f, 0)) {
 #pragma unroll
-      for (int u = 0; u < 16; ++u) v[u] = make_float2(__fdiv_rn(v[u].x, ep.out_scale), __fdiv_rn(v[u].y, ep.out_scale));
+      for (int u = 0; u < P; ++u) v[u] = make_float2(__fdiv_rn(v[u].x, ep.out_scale), __fdiv_rn(v[u].y, ep.out_scale));
     }
     // rint(v) + zp saturated to [lo, hi], in integers: v is first clamped to +-2^30 (far outside [lo - zp, hi - zp],
     // NaN goes to -2^30 as fmaxf drops it, which saturates to lo like the float formula), so neither the conversion
     // nor the addition can overflow.
-    int q[32];
 #pragma unroll
-    for (int u = 0; u < 16; ++u) {
-      q[2 * u] = min(max(__float2int_rn(fminf(fmaxf(v[u].x, -1073741824.f), 1073741824.f)) + zp, lo), hi);
-      q[2 * u + 1] = min(max(__float2int_rn(fminf(fmaxf(v[u].y, -1073741824.f), 1073741824.f)) + zp, lo), hi);
-    }
-    uint32_t w[8];
+    for (int i = 0; i < NC; ++i) {
+      int q[32];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const uint32_t lo2 = __byte_perm((uint32_t)q[4 * u], (uint32_t)q[4 * u + 1], 0x0040);      // bytes q0, q1
-      const uint32_t hi2 = __byte_perm((uint32_t)q[4 * u + 2], (uint32_t)q[4 * u + 3], 0x0040);  // bytes q2, q3
-      w[u] = __byte_perm(lo2, hi2, 0x5410);
+      for (int u = 0; u < 16; ++u) {
+        q[2 * u] = min(max(__float2int_rn(fminf(fmaxf(v[16 * i + u].x, -1073741824.f), 1073741824.f)) + zp, lo), hi);
+        q[2 * u + 1] = min(max(__float2int_rn(fminf(fmaxf(v[16 * i + u].y, -1073741824.f), 1073741824.f)) + zp, lo), hi);
+      }
+      uint32_t w[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint32_t lo2 = __byte_perm((uint32_t)q[4 * u], (uint32_t)q[4 * u + 1], 0x0040);      // bytes q0, q1
+        const uint32_t hi2 = __byte_perm((uint32_t)q[4 * u + 2], (uint32_t)q[4 * u + 3], 0x0040);  // bytes q2, q3
+        w[u] = __byte_perm(lo2, hi2, 0x5410);
+      }
+      stage_units<2>(stage, w, slot + i);
     }
-    stage_units<2>(stage, w, slot);
   }
 }
 
@@ -518,14 +536,30 @@ __device__ __forceinline__ void drain_accumulator(const EpiParams &ep, uint32_t 
   int units = 0, seg_col = 0;
   bool store_pending = false;
   // One register buffer: the fast path reads the raw accumulator only in its first half, so the tcgen05.ld of the
-  // next chunk is issued into the same registers right after that and flies during the second half and the flush.
-  uint32_t raw[32];
-  ptx::tmem_ld_x32(taddr + 32 * ch, raw);
+  // next chunks is issued into the same registers right after that and flies during the second half and the flush.
+  // Where a row segment is two or more chunks (2- and 1-byte outputs) two chunks go through the fast path TOGETHER:
+  // an epilogue warp is alone or nearly alone on its scheduler, and two independent 32-column chains in one
+  // instruction stream hide the latencies that one chain leaves exposed.
+  uint32_t raw[64];
+  auto &raw_lo = reinterpret_cast<uint32_t (&)[32]>(raw[0]);
+  auto &raw_hi = reinterpret_cast<uint32_t (&)[32]>(raw[32]);
+  // (Measured dead end, kept compiled out: two chunks through the fast path together need ~200 registers; a CTA of 10
+  // warps gets 168 per thread, and the spills cost more than the interleaving wins.)
+  constexpr bool kTwoChunks = false;
+  const bool pair_ok = kTwoChunks && fast && G >= 2;
+  auto chunks_now = [&](int ch_, int j_) { return (pair_ok && (j_ & 1) == 0 && c_end - 32 * ch_ >= 64) ? 2 : 1; };
+  auto issue_loads = [&](int ch_, int np_) {
+    ptx::tmem_ld_x32(taddr + 32 * ch_, raw_lo);
+    if (np_ == 2) ptx::tmem_ld_x32(taddr + 32 * ch_ + 32, raw_hi);
+  };
+  int np = chunks_now(ch, j);
+  issue_loads(ch, np);
   while (true) {
     { DRAIN_T0(); ptx::tmem_ld_wait(); DRAIN_ADD(0); }
-    int ch2 = ch + 1, j2 = j + 1;
-    if (j2 == G) { j2 = 0; ch2 += (group_stride - 1) * G; }
+    int ch2 = ch + np, j2 = j + np;
+    if (j2 >= G) { j2 = 0; ch2 += (group_stride - 1) * G; }
     const bool has_next = ch2 < nch;
+    const int np2 = has_next ? chunks_now(ch2, j2) : 1;
     const int c = 32 * ch;
     if (j == 0) {
       units = 0; seg_col = c;
@@ -538,19 +572,26 @@ __device__ __forceinline__ void drain_accumulator(const EpiParams &ep, uint32_t 
       }
     }
     { DRAIN_T0();
-      if (fast && c_end - c >= 32) {
-        const long long rr = row < rows_total ? row : rows_total - 1;   // rows past the end compute on the last row's operands
+      const long long rr = row < rows_total ? row : rows_total - 1;   // rows past the end compute on the last row's operands
+      if (np == 2) {
+        float2 v[32];
+        const bool more = epi_values_fast<ACC_INT, 2>(ep, raw, v, rr, n0 + c, stage, j);
+        if (has_next) issue_loads(ch2, np2);
+        if (more) epi_finish_fast<2>(ep, v, b, rr, n0 + c, stage, j);
+        units += 2 * units_per_chunk;
+      } else if (fast && c_end - c >= 32) {
         float2 v[16];
-        const bool more = epi_values_fast<ACC_INT>(ep, raw, v, rr, n0 + c, stage, j);
-        if (has_next) ptx::tmem_ld_x32(taddr + 32 * ch2, raw);
-        if (more) epi_finish_fast(ep, v, b, rr, n0 + c, stage, j);
+        const bool more = epi_values_fast<ACC_INT, 1>(ep, raw_lo, v, rr, n0 + c, stage, j);
+        if (has_next) issue_loads(ch2, np2);
+        if (more) epi_finish_fast<1>(ep, v, b, rr, n0 + c, stage, j);
         units += units_per_chunk;
       } else {
-        if (store_chunk(ep, raw, b, row, n0 + c, min(32, c_end - c), vec, stage, rows_total, j)) units += units_per_chunk;
-        if (has_next) ptx::tmem_ld_x32(taddr + 32 * ch2, raw);
+        if (store_chunk(ep, raw_lo, b, row, n0 + c, min(32, c_end - c), vec, stage, rows_total, j)) units += units_per_chunk;
+        if (has_next) issue_loads(ch2, np2);
       }
       DRAIN_ADD(2); }
-    if ((j == G - 1 || !has_next) && units > 0) {
+    const int j_last = j + np - 1;
+    if ((j_last == G - 1 || !has_next) && units > 0) {
       DRAIN_T0();
       if (tm_y != nullptr && units == 8) {
         ptx::fence_proxy_async();   // this lane's staging writes become visible to the TMA unit
@@ -565,7 +606,7 @@ __device__ __forceinline__ void drain_accumulator(const EpiParams &ep, uint32_t 
       }
       DRAIN_ADD(3);
     }
-    ch = ch2; j = j2;
+    ch = ch2; j = j2; np = np2;
     if (!has_next) break;
   }
   if (store_pending) {

@@ -62,6 +62,7 @@ class ConvDesc(C.Structure):
         ("x_dtype", C.c_int32), ("y_dtype", C.c_int32),
         ("x_zero_point", C.c_int32),
         ("precise", C.c_int32),
+        ("x_layout", C.c_int32), ("y_layout", C.c_int32),
     ]
 
 

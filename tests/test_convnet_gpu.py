@@ -104,8 +104,9 @@ def test_convnet_int8_every_layer_bit_exact(ctx, oracle_lib):
     assert np.abs(tp.cpu().numpy() - pooled).max() <= 1e-5 * max(1.0, np.abs(pooled).max())
 
 
+@pytest.mark.parametrize("channels_last", [True, False])
 @pytest.mark.parametrize("int8", [False, True])
-def test_benchmark_network_object_matches_checker(ctx, oracle_lib, int8):
+def test_benchmark_network_object_matches_checker(ctx, oracle_lib, int8, channels_last):
     """bench_convnet.ConvNetB200 (plans and buffers created once, as the benchmark runs it) against the checker."""
     import bench_convnet as bc
     o = Oracle(oracle_lib)
@@ -115,12 +116,12 @@ def test_benchmark_network_object_matches_checker(ctx, oracle_lib, int8):
     if int8:
         x = np.clip(np.rint(x * 127.0), 0, 127).astype(np.int8)
     want = bc.convnet_oracle(o, x, weights, int8)
-    net = bc.ConvNetB200(ctx, weights, 3, 48, int8, DEV)
+    net = bc.ConvNetB200(ctx, weights, 3, 48, int8, DEV, channels_last=channels_last)
     n0 = ctx.launches
     for _ in range(2):   # the second call reuses every buffer
         got = net(torch.from_numpy(x).to(DEV))
         ctx.sync()
-    assert ctx.launches - n0 == 2 * bc.ConvNetB200.LAUNCHES
+    assert ctx.launches - n0 == 2 * (bc.ConvNetB200.LAUNCHES if channels_last else bc.ConvNetB200.LAUNCHES_NCHW)
     got = got.cpu().numpy()
     assert close_f32(got, want, rel=1e-4 if not int8 else 1e-5), np.abs(got - want).max()
     net.close()

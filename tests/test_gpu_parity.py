@@ -257,6 +257,56 @@ def test_qlinear_conv_bit_exact(ctx, oracle, N, Ci, H, W, Co, st, g):
     assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size}"
 
 
+@pytest.mark.parametrize("dtype", ["int8", "fp32", "fp32_tensor"])
+@pytest.mark.parametrize("xl,yl", [(0, 1), (1, 1), (1, 0)])
+def test_conv_channels_last_layouts(ctx, oracle, dtype, xl, yl):
+    """x_layout / y_layout = 1: the same convolution on [N,H,W,C] tensors (grouped, strided, with a residual in Y's layout)."""
+    from sofie_b200.ops import make_epilogue
+    lib = ctx._lib
+    int8 = dtype == "int8"
+    N, Ci, H, W, Co, g, st = (12, 64, 40, 36, 96, 2, 1) if dtype == "fp32_tensor" else (2, 32, 13, 10, 48, 2, 2)
+    rng = np.random.default_rng(xl * 2 + yl + (7 if int8 else 0))
+    if int8:
+        x = rng.integers(-127, 128, size=(N, Ci, H, W), dtype=np.int8)
+        w = rng.integers(-127, 128, size=(Co, Ci // g, 3, 3), dtype=np.int8)
+        cs = (rng.random(Co, dtype=np.float32) * 2e-4 + 5e-5).astype(np.float32)
+        bias = rng.integers(-20000, 20000, size=Co, dtype=np.int32)
+        code, tdt, res = L.I8, torch.int8, None
+    else:
+        x = rng.random((N, Ci, H, W), dtype=np.float32)
+        w = (rng.standard_normal((Co, Ci // g, 3, 3)) * 0.1).astype(np.float32)
+        cs = rng.random(Co, dtype=np.float32) + 0.5
+        bias = rng.standard_normal(Co).astype(np.float32)
+        code, tdt = L.F32, torch.float32
+    geo = dict(pads=[1, 1, 1, 1], strides=[st, st], dil=[1, 1], group=g)
+    d = gr.conv_desc(geo, x.shape, w.shape, code, code)
+    ho, wo = C.c_int64(), C.c_int64()
+    assert lib.sofie_b200_conv_out_shape(C.byref(d), C.byref(ho), C.byref(wo)) == 0
+    res = None if int8 else rng.standard_normal((N, Co, ho.value, wo.value)).astype(np.float32)
+    want = oracle.conv(x, w, d, ho.value, wo.value, ep=oracle.epilogue(col_scale=cs, bias=bias, act=L.ACT_RELU, residual=res))
+    d.x_layout, d.y_layout = xl, yl
+    to_dev = lambda a, cl: torch.from_numpy(np.ascontiguousarray(a.transpose(0, 2, 3, 1)) if cl else a).to(DEV)
+    tx, tw = to_dev(x, xl), torch.from_numpy(w).to(DEV)
+    h = C.c_void_p()
+    L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), tw.data_ptr(), C.byref(h)), "conv_plan_create")
+    if dtype == "fp32_tensor":
+        assert lib.sofie_b200_conv_plan_kernel(h).decode() == "umma3x"
+    ws = torch.empty(max(16, lib.sofie_b200_conv_workspace_bytes(h)), dtype=torch.uint8, device=DEV)
+    y = torch.zeros((N, ho.value, wo.value, Co) if yl else (N, Co, ho.value, wo.value), dtype=tdt, device=DEV)
+    ep, keep = make_epilogue(col_scale=torch.from_numpy(cs).to(DEV), bias=torch.from_numpy(bias).to(DEV), act=L.ACT_RELU,
+                             residual=None if res is None else to_dev(res, yl))
+    L.check(lib.sofie_b200_conv_enqueue(h, tx.data_ptr(), y.data_ptr(), ws.data_ptr(), C.byref(ep)), "conv_enqueue")
+    ctx.sync()
+    lib.sofie_b200_conv_plan_destroy(h)
+    got = y.cpu().numpy()
+    if yl:
+        got = got.transpose(0, 3, 1, 2)
+    if int8:
+        assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size}"
+    else:
+        assert close_f32(got, want), np.abs(got - want).max()
+
+
 def test_conv_fp32_with_folded_batchnorm(ctx, oracle):
     rng = np.random.default_rng(9)
     x = rng.random((2, 8, 20, 20), dtype=np.float32)
