@@ -238,9 +238,9 @@ int sofie_b200_conv_plan_destroy(sofie_b200_conv_plan *plan);
 /* Output extent per ROperator_Conv.hxx:123-262. */
 int sofie_b200_conv_out_shape(const sofie_b200_conv_desc *desc, int64_t *Ho, int64_t *Wo);
 /* Bytes of caller-provided scratch the plan needs per enqueue (0 if none): the unfolded input,
- * [groups][N][Ho*Wo][kpad] elements with kpad = C/groups*R*S rounded up to 16 bytes -- times three for an
- * F32 convolution at precise = 1 of at least SOFIE_B200_SPLIT_MIN_FLOPS (2 * K/groups * Ho*Wo * kpad * N),
- * which runs as error-compensated 3xTF32 on the tensor cores and unfolds into three K segments; plus a channels-last
+ * [groups][N][Ho*Wo][kpad] elements with kpad = C/groups*R*S rounded up to 16 bytes -- or, for an F32
+ * convolution at precise = 1 of at least SOFIE_B200_SPLIT_MIN_FLOPS (2 * K/groups * Ho*Wo * kpad * N), which runs
+ * as error-compensated 3xTF32 on the tensor cores, two segments (hi | lo) of C/groups*R*S rounded up to 32; plus a channels-last
  * copy of the input (N*C*H*W elements, 256-byte aligned behind the unfolded matrix) when C/groups is a whole number
  * of 16-byte vectors, from which the unfold is plain vector copies.  The Im2Col
  * scratch of the reference is per image (ROperator_Conv.hxx:1002-1103); this one covers the batch. */

@@ -42,7 +42,8 @@ static const char *kDeviceWait[] = {"ok", "TMA producer: no free shared-memory s
 using namespace sb200;
 
 namespace sb200 {
-// A TF32 plan over already split K-major operands (K = 3*ks) that runs the chunk-promotion kernel.
+// A TF32 plan over already split K-major operands (desc.K = 3*ks products; operands stored [hi | lo], lda = ldb = 2*ks)
+// that runs the chunk-promotion kernel.
 // Returns 1 when the tensor path does not apply to the shape.
 int gemm_plan_create_promote(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, sofie_b200_gemm_plan **out) {
   *out = nullptr;
@@ -50,6 +51,7 @@ int gemm_plan_create_promote(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g,
   in->ctx = ctx;
   in->desc = g;
   in->promote = 1;   // sum short K chunks in registers: the tensor core's own fp32 adds truncate
+  in->k_store = g.K / 3 * 2;
   const int rc = umma_plan_init(in);
   if (rc) { delete in; return rc; }
   in->use_umma = 1;
@@ -172,18 +174,18 @@ int sofie_b200_gemm_plan_create(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc 
   // fp32 at fp32 accuracy: large problems go to the tensor cores as 3xTF32 (gemm_split.cu), the rest to fp32 FMA
   if (d.ab_dtype == SOFIE_B200_F32 && d.precise != 0 && d.M > 0 && d.N > 0 && d.K > 0 && d.batch <= 65535 &&
       2.0 * (double)d.M * (double)d.N * (double)d.K * (double)d.batch >= SPLIT_MIN_FLOPS && !getenv("SOFIE_B200_NO_3XTF32")) {
-    const long long ks = (d.K + 3) / 4 * 4;
+    const long long ks = split_ks(d.K);
     sofie_b200_gemm_desc g = d;
     const bool a_bcast = d.batch > 1 && d.stride_a == 0, b_bcast = d.batch > 1 && d.stride_b == 0;
-    g.K = 3 * ks; g.trans_a = 0; g.trans_b = 1; g.lda = 3 * ks; g.ldb = 3 * ks; g.precise = 0;
-    g.stride_a = a_bcast ? 0 : d.M * 3 * ks;
-    g.stride_b = b_bcast ? 0 : d.N * 3 * ks;
+    g.K = 3 * ks; g.trans_a = 0; g.trans_b = 1; g.lda = 2 * ks; g.ldb = 2 * ks; g.precise = 0;
+    g.stride_a = a_bcast ? 0 : d.M * 2 * ks;
+    g.stride_b = b_bcast ? 0 : d.N * 2 * ks;
     sofie_b200_gemm_plan *in = nullptr;
     int rc = gemm_plan_create_promote(ctx, g, &in);
     if (rc < 0) { delete plan; return rc; }
     if (rc == 0) {
-      const size_t abytes = (size_t)(a_bcast ? 1 : d.batch) * d.M * 3 * ks * sizeof(float);
-      const size_t bbytes = (size_t)(b_bcast ? 1 : d.batch) * d.N * 3 * ks * sizeof(float);
+      const size_t abytes = (size_t)(a_bcast ? 1 : d.batch) * d.M * 2 * ks * sizeof(float);
+      const size_t bbytes = (size_t)(b_bcast ? 1 : d.batch) * d.N * 2 * ks * sizeof(float);
       if (cudaMalloc(&plan->split_a, abytes) != cudaSuccess || cudaMalloc(&plan->split_b, bbytes) != cudaSuccess) {
         cudaGetLastError();
         if (plan->split_a) cudaFree(plan->split_a);
@@ -271,8 +273,8 @@ int sofie_b200_gemm_enqueue(sofie_b200_gemm_plan *plan, const void *A, const voi
   if (plan->inner) {
     sofie_b200_ctx *ctx = plan->ctx;
     const bool a_bcast = d.batch > 1 && d.stride_a == 0, b_bcast = d.batch > 1 && d.stride_b == 0;
-    if ((rc = split3_enqueue(ctx, (const float *)A, plan->split_a, d.M, d.K, plan->ks, d.lda, a_bcast ? 1 : d.batch, d.stride_a, d.trans_a ? 1 : 0, 0))) return rc;
-    if ((rc = split3_enqueue(ctx, (const float *)B, plan->split_b, d.N, d.K, plan->ks, d.ldb, b_bcast ? 1 : d.batch, d.stride_b, d.trans_b ? 0 : 1, 1))) return rc;
+    if ((rc = split2_enqueue(ctx, (const float *)A, plan->split_a, d.M, d.K, plan->ks, d.lda, a_bcast ? 1 : d.batch, d.stride_a, d.trans_a ? 1 : 0))) return rc;
+    if ((rc = split2_enqueue(ctx, (const float *)B, plan->split_b, d.N, d.K, plan->ks, d.ldb, b_bcast ? 1 : d.batch, d.stride_b, d.trans_b ? 0 : 1))) return rc;
     return umma_enqueue(plan->inner, plan->split_a, plan->split_b, e);
   }
   if (plan->use_umma && d.K > 0) return umma_enqueue(plan, A, B, e);

@@ -17,8 +17,8 @@ struct sofie_b200_conv_plan {
   int64_t Ho = 0, Wo = 0;
   int64_t cg = 0, kg = 0;      // input channels / output channels per group
   int64_t kdim = 0, kpad = 0;  // C/g*R*S and its padded pitch
-  void *w_padded = nullptr;    // [K, kpad] device copy of the weights ([K, 3*kpad] hi|lo|hi in split mode)
-  int split = 0;               // fp32 at fp32 accuracy on the tensor cores: operands carry three K segments (gemm_split.cu)
+  void *w_padded = nullptr;    // [K, kpad] device copy of the weights ([K, 2*kpad] hi|lo in split mode)
+  int split = 0;               // fp32 at fp32 accuracy on the tensor cores: operands stored as hi | lo segments (gemm_split.cu)
   int pix_rows = 0;            // y_layout = channels-last: output pixels are the accumulator rows, the unfolded input is the A operand
   int nhwc = 0;                // channels-last unfold: the input is first transposed to [N, H, W, C] in the workspace and K runs
                                // (r, s, c), so every 16-byte chunk of the unfolded matrix is one aligned vector copy
@@ -96,9 +96,9 @@ __global__ void __launch_bounds__(256) unfold_kernel(const T *__restrict__ x, T 
   }
 }
 
-// fp32 input unfolded straight into the split form of the B operand: xcol[g][n][pix][hi | hi | lo], each segment kpad wide.
+// fp32 input unfolded straight into the split form of the operand: xcol[g][n][pix][hi | lo], each segment kpad wide.
 __global__ void __launch_bounds__(256) unfold_split_kernel(const float *__restrict__ x, float *__restrict__ xcol, sofie_b200_conv_desc d,
-                                                           long long Ho, long long Wo, long long cg, long long kdim, long long kpad, int a_side) {
+                                                           long long Ho, long long Wo, long long cg, long long kdim, long long kpad) {
   const unsigned chunks = (unsigned)(kpad / 4), pix = (unsigned)(Ho * Wo);
   const long long total = (long long)d.groups * d.N * pix * chunks;
   const int H = (int)d.H, W = (int)d.W, R = (int)d.R, S = (int)d.S;
@@ -118,10 +118,9 @@ __global__ void __launch_bounds__(256) unfold_split_kernel(const float *__restri
       lo[e] = tf32_rn(__fsub_rn(val, hi[e]));
       if (++s == S) { s = 0; if (++r == R) { r = 0; ++c; } }
     }
-    float *o = xcol + u.row * 3 * kpad + u.ch * 4;   // B operand: hi | hi | lo; A operand (a_side): hi | lo | hi
+    float *o = xcol + u.row * 2 * kpad + u.ch * 4;
     *reinterpret_cast<uint4 *>(o) = *reinterpret_cast<const uint4 *>(hi);
-    *reinterpret_cast<uint4 *>(o + kpad) = *reinterpret_cast<const uint4 *>(a_side ? lo : hi);
-    *reinterpret_cast<uint4 *>(o + 2 * kpad) = *reinterpret_cast<const uint4 *>(a_side ? hi : lo);
+    *reinterpret_cast<uint4 *>(o + kpad) = *reinterpret_cast<const uint4 *>(lo);
   }
 }
 
@@ -189,11 +188,12 @@ __global__ void __launch_bounds__(256) reorder_weights_kernel(const T *__restric
   }
 }
 
-// xcol[g][n][pix][(r, s, c)] from the channels-last input; one thread copies 16 bytes.  SPLIT writes hi | hi | lo.
+// xcol[g][n][pix][(r, s, c)] from the channels-last input; one thread copies 16 bytes.  SPLIT writes hi | lo, each kpad wide
+// (kpad = kdim rounded up to a K block of the TF32 kernel, zero filled); otherwise kpad == kdim.
 template <typename T, int VEC, bool SPLIT>
 __global__ void __launch_bounds__(256) unfold_nhwc_kernel(const T *__restrict__ x, T *__restrict__ xcol, sofie_b200_conv_desc d, long long Ho,
-                                                          long long Wo, long long cg, long long kdim, T pad_value, int a_side) {
-  const unsigned chunks = (unsigned)(kdim / VEC), pix = (unsigned)(Ho * Wo), ccg = (unsigned)cg;
+                                                          long long Wo, long long cg, long long kdim, long long kpad, T pad_value) {
+  const unsigned chunks = (unsigned)(kpad / VEC), pix = (unsigned)(Ho * Wo), ccg = (unsigned)cg;
   const long long total = (long long)d.groups * d.N * pix * chunks;
   const int H = (int)d.H, W = (int)d.W, S = (int)d.S;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -207,7 +207,10 @@ __global__ void __launch_bounds__(256) unfold_nhwc_kernel(const T *__restrict__ 
     const int r = (int)(q / S), s = (int)(q - (q / S) * S);
     const int ih = (int)(oh * d.stride_h) - d.pad_top + r * d.dil_h, iw = (int)(ow * d.stride_w) - d.pad_left + s * d.dil_w;
     __align__(16) T v[VEC];
-    if (ih >= 0 && ih < H && iw >= 0 && iw < W) {
+    if (k >= (unsigned)kdim) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) v[e] = (T)0;
+    } else if (ih >= 0 && ih < H && iw >= 0 && iw < W) {
       *reinterpret_cast<uint4 *>(v) = *reinterpret_cast<const uint4 *>(x + (((long long)n * H + ih) * W + iw) * d.C + g * ccg + c);
     } else {
 #pragma unroll
@@ -222,10 +225,9 @@ __global__ void __launch_bounds__(256) unfold_nhwc_kernel(const T *__restrict__ 
         hi[e] = tf32_rn((float)v[e]);
         lo[e] = tf32_rn(__fsub_rn((float)v[e], hi[e]));
       }
-      float *o = (float *)xcol + row * 3 * kdim + ch * 4;
+      float *o = (float *)xcol + row * 2 * kpad + ch * 4;
       *reinterpret_cast<uint4 *>(o) = *reinterpret_cast<const uint4 *>(hi);
-      *reinterpret_cast<uint4 *>(o + kdim) = *reinterpret_cast<const uint4 *>(a_side ? lo : hi);
-      *reinterpret_cast<uint4 *>(o + 2 * kdim) = *reinterpret_cast<const uint4 *>(a_side ? hi : lo);
+      *reinterpret_cast<uint4 *>(o + kpad) = *reinterpret_cast<const uint4 *>(lo);
     }
   }
 }
@@ -294,10 +296,12 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   }
   if (d.x_dtype == SOFIE_B200_F32 && d.precise != 0 && images <= 65535 && !getenv("SOFIE_B200_NO_3XTF32") &&
       2.0 * (double)p->kg * (double)(Ho * Wo) * (double)p->kpad * (double)images >= SPLIT_MIN_FLOPS) {
-    g.K = 3 * p->kpad; g.lda = g.ldb = 3 * p->kpad; g.stride_b = p->pix_rows ? 0 : Ho * Wo * 3 * p->kpad; g.precise = 0;
+    const int64_t ks = split_ks(p->kdim);   // operands stored hi | lo, each segment ks wide; the contraction runs over 3 * ks
+    g.K = 3 * ks; g.lda = g.ldb = 2 * ks; g.stride_b = p->pix_rows ? 0 : Ho * Wo * 2 * ks; g.precise = 0;
     rc = gemm_plan_create_promote(ctx, g, &p->gemm);
     if (rc < 0) { delete p; return rc; }
     p->split = (rc == 0);
+    if (p->split) p->kpad = ks;
   }
   // channels-last unfold when the per-group channel count is a whole number of 16-byte vectors (then kpad == kdim)
   p->nhwc = (d.x_layout == 1 || (p->cg % vec == 0 && d.N <= 65535 && !getenv("SOFIE_B200_NO_NHWC"))) ? 1 : 0;
@@ -318,7 +322,7 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   }
   // the re-layout buffer is only read by kernels enqueued below; it is freed once they have run
   auto free_perm = [&]() { if (w_perm) { cudaStreamSynchronize(ctx->stream); cudaFree(w_perm); w_perm = nullptr; } };
-  const int64_t kw = p->split ? 3 * p->kpad : p->kpad;   // pitch of one weight row / one unfolded pixel
+  const int64_t kw = p->split ? 2 * p->kpad : p->kpad;   // pitch of one weight row / one unfolded pixel
   if (cudaMalloc(&p->w_padded, (size_t)(d.K * kw * es)) != cudaSuccess) {
     free_perm();
     if (p->gemm) sofie_b200_gemm_plan_destroy(p->gemm);
@@ -328,8 +332,7 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   const long long total = d.K * p->kpad;
   const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 16);
   if (p->split) {
-    // the weights are the A operand (hi | lo | hi) when channels are rows, the B operand (hi | hi | lo) when pixels are
-    rc = split3_enqueue(ctx, (const float *)w_src, (float *)p->w_padded, d.K, p->kdim, p->kpad, p->kdim, 1, 0, 0, p->pix_rows ? 1 : 0);
+    rc = split2_enqueue(ctx, (const float *)w_src, (float *)p->w_padded, d.K, p->kdim, p->kpad, p->kdim, 1, 0, 0);
     free_perm();
     if (rc) { sofie_b200_gemm_plan_destroy(p->gemm); cudaFree(p->w_padded); delete p; return rc; }
     *out = p;
@@ -368,7 +371,7 @@ const char *sofie_b200_conv_plan_kernel(const sofie_b200_conv_plan *plan) {
 int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan) {
   if (!plan) return 0;
   const int64_t es = dtype_size(plan->d.x_dtype);
-  const int64_t xcol = (int64_t)plan->d.groups * plan->d.N * plan->Ho * plan->Wo * plan->kpad * (plan->split ? 3 : 1) * es;
+  const int64_t xcol = (int64_t)plan->d.groups * plan->d.N * plan->Ho * plan->Wo * plan->kpad * (plan->split ? 2 : 1) * es;
   if (!plan->nhwc || plan->d.x_layout == 1) return xcol;   // a channels-last input needs no copy
   return (xcol + 255) / 256 * 256 + plan->d.N * plan->d.C * plan->d.H * plan->d.W * es;   // + the channels-last copy of the input
 }
@@ -387,7 +390,7 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
   const long long total = (long long)d.groups * d.N * pix * (plan->kpad / (16 / es));
   const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 32);
   if (plan->nhwc) {
-    const long long xcol_bytes = (long long)d.groups * d.N * pix * plan->kpad * (plan->split ? 3 : 1) * es;
+    const long long xcol_bytes = (long long)d.groups * d.N * pix * plan->kpad * (plan->split ? 2 : 1) * es;
     void *xl = (char *)workspace + (xcol_bytes + 255) / 256 * 256;
     const int HW = (int)(d.H * d.W), C_ = (int)d.C;
     if (d.x_layout == 1) {
@@ -403,13 +406,13 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
     ctx->launches++;
     }
     if (plan->split)
-      unfold_nhwc_kernel<float, 4, true><<<grid, 256, 0, ctx->stream>>>((const float *)xl, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, 0.f, plan->pix_rows);
+      unfold_nhwc_kernel<float, 4, true><<<grid, 256, 0, ctx->stream>>>((const float *)xl, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, 0.f);
     else if (es == 4)
-      unfold_nhwc_kernel<float, 4, false><<<grid, 256, 0, ctx->stream>>>((const float *)xl, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, 0.f, 0);
+      unfold_nhwc_kernel<float, 4, false><<<grid, 256, 0, ctx->stream>>>((const float *)xl, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, 0.f);
     else
-      unfold_nhwc_kernel<int8_t, 16, false><<<grid, 256, 0, ctx->stream>>>((const int8_t *)xl, (int8_t *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, (int8_t)d.x_zero_point, 0);
+      unfold_nhwc_kernel<int8_t, 16, false><<<grid, 256, 0, ctx->stream>>>((const int8_t *)xl, (int8_t *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, (int8_t)d.x_zero_point);
   } else if (plan->split)
-    unfold_split_kernel<<<grid, 256, 0, ctx->stream>>>((const float *)X, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, plan->pix_rows);
+    unfold_split_kernel<<<grid, 256, 0, ctx->stream>>>((const float *)X, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad);
   else if (d.x_dtype == SOFIE_B200_F32)
     unfold_kernel<float, 4><<<grid, 256, 0, ctx->stream>>>((const float *)X, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, 0.f);
   else
@@ -431,7 +434,7 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
       e = *ep;
       e.ldr = d.K;
     }
-    const long long kw = plan->split ? 3 * plan->kpad : plan->kpad;
+    const long long kw = plan->split ? 2 * plan->kpad : plan->kpad;
     for (int g = 0; g < d.groups; ++g) {
       sofie_b200_epilogue eg = e;
       if (eg.col_scale) eg.col_scale += g * plan->kg;
@@ -463,7 +466,7 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
     if (eg.row_scale) eg.row_scale += g * plan->kg;
     if (eg.bias && eg.bias_mode != SOFIE_B200_BIAS_SCALAR_F32) eg.bias = (const char *)eg.bias + (size_t)g * plan->kg * 4;
     if (eg.residual) eg.residual = (const char *)eg.residual + (size_t)g * plan->kg * pix * dtype_size(eg.residual_dtype);
-    const long long kw = plan->split ? 3 * plan->kpad : plan->kpad;
+    const long long kw = plan->split ? 2 * plan->kpad : plan->kpad;
     const char *a = (const char *)plan->w_padded + (size_t)g * plan->kg * kw * es;
     const char *b = (const char *)workspace + (size_t)g * d.N * pix * kw * es;
     char *y = (char *)Y + (size_t)g * plan->kg * pix * ys;

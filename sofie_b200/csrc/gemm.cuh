@@ -59,6 +59,8 @@ struct UmmaParams {
   int y_tma;                       // the epilogue may store complete row segments through the tensor map of Y
   int l2_ahead;                    // K blocks the L2 prefetch cursor runs in front of the loads (0 = off)
   int commit_group;                // pair kernel: K blocks consumed between bursts of stage releases
+  int seg_kb;                      // chunk-promotion kernel: K blocks per split segment (ks / 32)
+  int a_seg_kb[3], b_seg_kb[3];    // K block at which each of the three product segments starts in the stored A / B (hi | lo)
   int promote_chunk;               // chunk-promotion kernel: K blocks per tensor-memory accumulation
   int b_rows;                      // N extent of the B slice one CTA stages: bn, or bn/2 in pair mode
   EpiParams ep;
@@ -74,6 +76,10 @@ __device__ __forceinline__ float tf32_rn(float x) {
 
 // Problems below this many flops stay on the fp32 FMA kernel (the split passes would dominate).
 constexpr double SPLIT_MIN_FLOPS = 4e8;
+// Split operands are stored as [hi | lo], each segment SPLIT_K_ALIGN-aligned in K (one K block of the TF32 kernel), so that
+// the three products hi*hi, lo*hi, hi*lo are whole K blocks whose A and B coordinates are looked up per segment.
+constexpr long long SPLIT_K_ALIGN = 32;
+inline long long split_ks(long long K) { return (K + SPLIT_K_ALIGN - 1) / SPLIT_K_ALIGN * SPLIT_K_ALIGN; }
 
 // Tile r of a batch -> (M tile, N tile).  Consecutive tiles run at the same time on neighbouring SMs, so the index that
 // varies fastest decides which operand slice they share in L2 (see umma_plan_init for the choice).
@@ -108,6 +114,7 @@ struct sofie_b200_gemm_plan {
   sofie_b200_gemm_plan *inner = nullptr;
   float *split_a = nullptr, *split_b = nullptr;
   long long ks = 0;
+  long long k_store = 0;           // K extent of the operands as stored (two segments) when it differs from desc.K (three products)
   int promote = 0;                 // this (inner TF32) plan runs the chunk-promotion kernel
 };
 
@@ -125,8 +132,8 @@ int umma_promote_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u);
 // api.cu
 int gemm_plan_create_promote(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, sofie_b200_gemm_plan **out);
 // gemm_split.cu
-int split3_enqueue(sofie_b200_ctx *ctx, const float *src, float *dst, long long rows, long long K, long long Ks, long long ld,
-                   long long batch, long long batch_stride, int mn, int pattern);
+int split2_enqueue(sofie_b200_ctx *ctx, const float *src, float *dst, long long rows, long long K, long long Ks, long long ld,
+                   long long batch, long long batch_stride, int mn);
 // gemm_simt.cu
 int simt_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep);
 }  // namespace sb200

@@ -402,6 +402,11 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
     u.raster_n = (!u.pair && cost_n < cost_m) ? 1 : 0;
     if (const char *e = getenv("SOFIE_B200_RASTER_N")) u.raster_n = (!u.pair && atoi(e) != 0) ? 1 : 0;
   }
+  if (plan->promote) {
+    u.seg_kb = (int)(d.K / 3 / SPLIT_K_ALIGN);
+    u.a_seg_kb[0] = 0; u.a_seg_kb[1] = u.seg_kb; u.a_seg_kb[2] = 0;         // A: hi, lo, hi
+    u.b_seg_kb[0] = 0; u.b_seg_kb[1] = 0; u.b_seg_kb[2] = u.seg_kb;         // B: hi, hi, lo
+  }
   u.commit_group = 1;
   u.l2_ahead = 0;
   if (const char *e = getenv("SOFIE_B200_L2_AHEAD")) { const int c = atoi(e); if (c >= 0 && c <= 64) u.l2_ahead = c; }
@@ -504,6 +509,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
 
 static int build_maps(sofie_b200_gemm_plan *plan, const void *A, const void *B) {
   const sofie_b200_gemm_desc &d = plan->desc;
+  const uint64_t kext = (uint64_t)(plan->k_store ? plan->k_store : d.K);   // K extent of the operands as stored
   const UmmaParams &u = plan->up;
   const int es = dtype_size(d.ab_dtype);
   if (A != plan->cached_a) {
@@ -512,7 +518,7 @@ static int build_maps(sofie_b200_gemm_plan *plan, const void *A, const void *B) 
     int rc;
     if (!u.a_mn) {
       uint64_t s2 = d.batch > 1 && !u.a_bcast ? (uint64_t)d.stride_a * es : (uint64_t)d.M * d.lda * es;
-      rc = encode_map(&plan->tm_a, d.ab_dtype, A, (uint64_t)d.K, (uint64_t)d.M, nb, (uint64_t)d.lda * es, s2,
+      rc = encode_map(&plan->tm_a, d.ab_dtype, A, kext, (uint64_t)d.M, nb, (uint64_t)d.lda * es, s2,
                       (uint32_t)u.kb_elems, UMMA_BM);
     } else {
       uint64_t s2 = d.batch > 1 && !u.a_bcast ? (uint64_t)d.stride_a * es : (uint64_t)d.K * d.lda * es;
@@ -528,7 +534,7 @@ static int build_maps(sofie_b200_gemm_plan *plan, const void *A, const void *B) 
     int rc;
     if (!u.b_mn) {
       uint64_t s2 = d.batch > 1 && !u.b_bcast ? (uint64_t)d.stride_b * es : (uint64_t)d.N * d.ldb * es;
-      rc = encode_map(&plan->tm_b, d.ab_dtype, B, (uint64_t)d.K, (uint64_t)d.N, nb, (uint64_t)d.ldb * es, s2,
+      rc = encode_map(&plan->tm_b, d.ab_dtype, B, kext, (uint64_t)d.N, nb, (uint64_t)d.ldb * es, s2,
                       (uint32_t)u.kb_elems, (uint32_t)u.b_rows);
     } else {
       uint64_t s2 = d.batch > 1 && !u.b_bcast ? (uint64_t)d.stride_b * es : (uint64_t)d.K * d.ldb * es;

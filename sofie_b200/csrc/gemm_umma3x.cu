@@ -6,7 +6,8 @@
 // a time into one of two tensor-memory accumulators; the epilogue warps drain each finished chunk into
 // registers and add the chunks there with round-to-nearest, overlapping the next chunk's MMAs.  The error
 // no longer depends on K.  Same roles, rings and bounded waits as umma_gemm_kernel; operands are the
-// K-major split matrices written by split3_kernel.  The tile is 128 x bn, bn in {64, 128, 256}; eight
+// K-major split matrices written by split2_kernel (each stored once as hi | lo; the producer maps the K blocks of the
+// three products hi*hi, lo*hi, hi*lo onto them).  The tile is 128 x bn, bn in {64, 128, 256}; eight
 // epilogue warps (two per tensor-memory lane quarter, each owning half of the columns) keep one fp32
 // register per accumulator element, so bn = 256 fits and the shared-memory operand traffic per MMA
 // stays that of the plain kernel.
@@ -91,8 +92,10 @@ umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           }
           const uint32_t full = bar_full + 8 * stage;
           mbar_arrive_expect_tx(full, p.a_stage_bytes + p.b_stage_bytes);
-          tma_load_3d(smem_a + stage * p.a_stage_bytes, &tm_a, full, kb * p.kb_elems, m0, ba);
-          tma_load_3d(smem_b + stage * p.b_stage_bytes, &tm_b, full, kb * p.kb_elems, n0, bb);
+          // K block kb of the three-product contraction -> K block of the stored [hi | lo] operand
+          const int seg = kb / p.seg_kb, off = kb - seg * p.seg_kb;
+          tma_load_3d(smem_a + stage * p.a_stage_bytes, &tm_a, full, (p.a_seg_kb[seg] + off) * p.kb_elems, m0, ba);
+          tma_load_3d(smem_b + stage * p.b_stage_bytes, &tm_b, full, (p.b_seg_kb[seg] + off) * p.kb_elems, n0, bb);
           if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
         }
       }

@@ -84,10 +84,11 @@ inline size_t ConvWorkspaceBytes(const ConvGeometry &g, size_t elemSize)
 {
    // [groups][N][Ho*Wo][kpad] with kpad = C/groups*R*S rounded up to 16 bytes (sofie_b200_conv_workspace_bytes)
    const size_t kdim = g.C / g.group * g.R * g.S, vec = 16 / elemSize;
-   const size_t kpad = (kdim + vec - 1) / vec * vec;
+   size_t kpad = (kdim + vec - 1) / vec * vec;
+   // a large fp32 convolution runs as 3xTF32 and unfolds into hi | lo segments of K rounded up to 32 (SOFIE_B200_SPLIT_MIN_FLOPS of sofie_b200.h)
+   const bool split = elemSize == sizeof(float) && 2.0 * double(g.K / g.group) * double(g.Ho * g.Wo) * double(kpad) * double(g.N) >= 4e8;
+   if (split) kpad = (kdim + 31) / 32 * 32 * 2;
    size_t bytes = g.group * g.N * g.Ho * g.Wo * kpad * elemSize;
-   // a large fp32 convolution runs as 3xTF32 and unfolds into three K segments (SOFIE_B200_SPLIT_MIN_FLOPS of sofie_b200.h)
-   if (elemSize == sizeof(float) && 2.0 * double(g.K / g.group) * double(g.Ho * g.Wo) * double(kpad) * double(g.N) >= 4e8) bytes *= 3;
    // when the channels per group are whole 16-byte vectors the library unfolds from a channels-last copy of the input kept behind it
    if ((g.C / g.group) % vec == 0) bytes = (bytes + 255) / 256 * 256 + g.N * g.C * g.H * g.W * elemSize;
    return bytes;
