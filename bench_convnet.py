@@ -87,8 +87,8 @@ def convnet_oracle(o, x: np.ndarray, weights, int8: bool) -> np.ndarray:
 class ConvNetB200:
     """The network on one GPU through the C ABI.  `ctx` is a sofie_b200.ops.Context on that GPU."""
 
-    LAUNCHES = 8 * 2 + 2            # unfold + contraction per layer, pool, classifier
-    LAUNCHES_NCHW = 8 * 2 + 7 + 2   # every tensor NCHW: plus a channels-last copy of the input of layers 2-8
+    LAUNCHES = 1 + 7 * 2 + 2        # direct first layer, unfold + contraction for layers 2-8, pool, classifier
+    LAUNCHES_NCHW = 1 + 7 * 3 + 2   # every tensor NCHW: plus a channels-last copy of the input of layers 2-8
 
     def __init__(self, ctx, weights, batch: int, img: int, int8: bool, device: str, channels_last: bool = True):
         """channels_last: the activations between the convolutions are kept [N,H,W,C] (what a layout pass of the generator

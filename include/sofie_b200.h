@@ -246,7 +246,8 @@ int sofie_b200_conv_out_shape(const sofie_b200_conv_desc *desc, int64_t *Ho, int
  * scratch of the reference is per image (ROperator_Conv.hxx:1002-1103); this one covers the batch. */
 #define SOFIE_B200_SPLIT_MIN_FLOPS 4e8
 int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan);
-/* Kernel family of the plan's contraction, as sofie_b200_gemm_plan_kernel reports it. */
+/* Kernel family of the plan's contraction, as sofie_b200_gemm_plan_kernel reports it, or "direct" for the 3-channel 3x3
+ * first layer (NCHW input, one group), which runs on the CUDA cores without unfold and needs no workspace. */
 const char *sofie_b200_conv_plan_kernel(const sofie_b200_conv_plan *plan);
 /* Enqueues Y = epilogue(conv(X, W)); columns of the epilogue are output channels. */
 int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, void *workspace,

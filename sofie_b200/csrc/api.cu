@@ -58,6 +58,9 @@ int gemm_plan_create_promote(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g,
   *out = in;
   return 0;
 }
+// Epilogue parameters of a contraction described by `d` writing to Y (for kernels outside this file that apply the
+// same fused epilogue: the direct convolution).
+int gemm_make_epi(const sofie_b200_gemm_desc &d, void *Y, const sofie_b200_epilogue *ep, EpiParams *o);
 }  // namespace sb200
 
 extern "C" {
@@ -217,8 +220,7 @@ const char *sofie_b200_gemm_plan_kernel(const sofie_b200_gemm_plan *plan) {
   return plan->use_umma ? "umma" : "simt";
 }
 
-static int make_epi(const sofie_b200_gemm_plan *plan, void *Y, const sofie_b200_epilogue *ep, EpiParams *o) {
-  const sofie_b200_gemm_desc &d = plan->desc;
+static int make_epi(const sofie_b200_gemm_desc &d, void *Y, const sofie_b200_epilogue *ep, EpiParams *o) {
   memset(o, 0, sizeof(*o));
   o->Y = Y;
   o->ldy = d.ldy;
@@ -260,6 +262,12 @@ static int make_epi(const sofie_b200_gemm_plan *plan, void *Y, const sofie_b200_
   return 0;
 }
 
+}  // extern "C"
+namespace sb200 {
+int gemm_make_epi(const sofie_b200_gemm_desc &d, void *Y, const sofie_b200_epilogue *ep, EpiParams *o) { return make_epi(d, Y, ep, o); }
+}
+extern "C" {
+
 int sofie_b200_gemm_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, void *Y,
                             const sofie_b200_epilogue *ep) {
   if (!plan) return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue: plan is NULL");
@@ -267,7 +275,7 @@ int sofie_b200_gemm_enqueue(sofie_b200_gemm_plan *plan, const void *A, const voi
   if (d.M == 0 || d.N == 0) return 0;  // empty output: nothing to enqueue
   if (!A || !B || !Y) return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue: NULL tensor pointer");
   EpiParams e;
-  int rc = make_epi(plan, Y, ep, &e);
+  int rc = make_epi(plan->desc, Y, ep, &e);
   if (rc) return rc;
   SB_CUDA(cudaSetDevice(plan->ctx->device));
   if (plan->inner) {

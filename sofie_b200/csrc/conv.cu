@@ -19,6 +19,8 @@ struct sofie_b200_conv_plan {
   int64_t kdim = 0, kpad = 0;  // C/g*R*S and its padded pitch
   void *w_padded = nullptr;    // [K, kpad] device copy of the weights ([K, 2*kpad] hi|lo in split mode)
   int split = 0;               // fp32 at fp32 accuracy on the tensor cores: operands stored as hi | lo segments (gemm_split.cu)
+  int direct = 0;              // 3-channel 3x3 first layer: direct kernel on the CUDA cores, no unfold, no contraction plan
+  sofie_b200_gemm_desc edesc{}; // direct mode: the contraction this convolution stands for (shapes and pitches of its epilogue)
   int pix_rows = 0;            // y_layout = channels-last: output pixels are the accumulator rows, the unfolded input is the A operand
   int nhwc = 0;                // channels-last unfold: the input is first transposed to [N, H, W, C] in the workspace and K runs
                                // (r, s, c), so every 16-byte chunk of the unfolded matrix is one aligned vector copy
@@ -232,6 +234,190 @@ __global__ void __launch_bounds__(256) unfold_nhwc_kernel(const T *__restrict__ 
   }
 }
 
+// ---- direct convolution for the 3-channel 3x3 first layer ----------------------------------------------------------
+// K = 27: as a contraction this layer is one K block per tile and all epilogue (2.9 of the int8 conv net's 8.5 ms for
+// 0.4 % of its flops, plus an unfold that writes 10x the image).  Here a thread owns one output pixel: its 27 inputs sit
+// in registers (int8: packed four to a word for dp4a), the weights are broadcast from shared memory channel by channel,
+// and every output goes through the scalar form of the fused epilogue (epi_value), so results equal the contraction's.
+// Channels-last output: 16 bytes of consecutive channels per store; NCHW: one coalesced store per channel.
+constexpr int DIRECT_KD = 27;   // K; padded per filter to 32 int8 (8 words: two 16-byte shared-memory loads) or 28 floats (seven)
+
+template <typename T> struct DirectAcc;
+template <> struct DirectAcc<int8_t> { using W = int; static constexpr int NW = 8; static constexpr int KW = 32; };
+template <> struct DirectAcc<float> { using W = float; static constexpr int NW = 28; static constexpr int KW = 28; };
+
+template <typename T, bool NHWC_OUT>
+__global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ x, const typename DirectAcc<T>::W *__restrict__ wq,
+                                                          sofie_b200_conv_desc d, int Ho, int Wo, EpiParams ep) {
+  using W = typename DirectAcc<T>::W;
+  constexpr int NW = DirectAcc<T>::NW;
+  extern __shared__ __align__(16) unsigned char dsm[];
+  W *ws = reinterpret_cast<W *>(dsm);   // [K filters][NW]
+  const int filters = (int)d.K;
+  for (int i = threadIdx.x; i < filters * NW; i += blockDim.x) ws[i] = wq[i];
+  // per-channel epilogue operands, read once per CTA: scale (or 1), additive fp32 bias (or -0: x + -0 = x bit for bit),
+  // int32 bias (or 0).  In either output layout exactly one of row_scale / col_scale and of the ROW / COL bias modes
+  // carries the per-channel vector, indexed by the channel.
+  float *sc = reinterpret_cast<float *>(ws + (size_t)filters * NW);
+  float *bf = sc + filters;
+  int *bi = reinterpret_cast<int *>(bf + filters);
+  for (int k = threadIdx.x; k < filters; k += blockDim.x) {
+    sc[k] = ep.row_scale ? ep.row_scale[k] : (ep.col_scale ? ep.col_scale[k] : 1.f);
+    const int m = ep.bias_mode;
+    bf[k] = (m == SOFIE_B200_BIAS_COL_F32 || m == SOFIE_B200_BIAS_ROW_F32) ? ((const float *)ep.bias)[k]
+                                                                               : (m == SOFIE_B200_BIAS_SCALAR_F32 ? ((const float *)ep.bias)[0] : -0.f);
+    bi[k] = (m == SOFIE_B200_BIAS_COL_I32 || m == SOFIE_B200_BIAS_ROW_I32) ? ((const int *)ep.bias)[k] : 0;
+  }
+  __syncthreads();
+  // Without a residual or a full-matrix bias the epilogue of output (pixel, channel k) is this, step for step what
+  // epi_value() computes; otherwise epi_value() itself is called.
+  const bool lean = ep.residual == nullptr && ep.bias_mode != SOFIE_B200_BIAS_FULL_F32;
+  const float alpha = ep.alpha;
+  const long long pix = (long long)Ho * Wo, total = d.N * pix;
+  const long long gp_raw = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // pixel of the whole batch
+  const bool valid = gp_raw < total;
+  const long long gp = valid ? gp_raw : total - 1;   // lanes past the end recompute the last pixel and store nothing
+  const long long n = gp / pix;
+  const int p = (int)(gp - n * pix), oh = p / Wo, ow = p - oh * Wo;
+  const int ih0 = oh * d.stride_h - d.pad_top, iw0 = ow * d.stride_w - d.pad_left;
+  const int H = (int)d.H, Wd = (int)d.W;
+  const T *xn = x + n * 3 * H * Wd;
+  W xin[NW];
+  {
+    T v[32];
+#pragma unroll
+    for (int i = 27; i < 32; ++i) v[i] = (T)0;
+#pragma unroll
+    for (int c = 0; c < 3; ++c)
+#pragma unroll
+      for (int r = 0; r < 3; ++r)
+#pragma unroll
+        for (int s2 = 0; s2 < 3; ++s2) {
+          const int ih = ih0 + r * d.dil_h, iw = iw0 + s2 * d.dil_w;
+          v[(c * 3 + r) * 3 + s2] = (ih >= 0 && ih < H && iw >= 0 && iw < Wd) ? xn[((long long)c * H + ih) * Wd + iw] : (T)d.x_zero_point;
+        }
+    if constexpr (sizeof(T) == 1) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        xin[i] = (int)((uint32_t)(uint8_t)v[4 * i] | ((uint32_t)(uint8_t)v[4 * i + 1] << 8) | ((uint32_t)(uint8_t)v[4 * i + 2] << 16) |
+                       ((uint32_t)(uint8_t)v[4 * i + 3] << 24));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 28; ++i) xin[i] = v[i];
+    }
+  }
+  // (b, i, j) of the contraction the epilogue parameters describe: channels-last Y: row = pixel of the batch, column = channel;
+  // NCHW Y: batch = image, row = channel, column = pixel
+  auto raw_of = [&](int k) -> uint32_t {
+    const W *wk = ws + k * NW;
+    if constexpr (sizeof(T) == 1) {
+      const int4 w0 = *reinterpret_cast<const int4 *>(wk), w1 = *reinterpret_cast<const int4 *>(wk + 4);
+      int acc = __dp4a(xin[0], w0.x, 0);
+      acc = __dp4a(xin[1], w0.y, acc); acc = __dp4a(xin[2], w0.z, acc); acc = __dp4a(xin[3], w0.w, acc);
+      acc = __dp4a(xin[4], w1.x, acc); acc = __dp4a(xin[5], w1.y, acc); acc = __dp4a(xin[6], w1.z, acc);
+      return (uint32_t)acc;   // the eighth word is padding
+    } else {
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < 27; ++i) acc = __fmaf_rn(xin[i], wk[i], acc);
+      return __float_as_uint(acc);
+    }
+  };
+  auto value_of = [&](int k, long long eb, long long ei, long long ej) -> float {
+    const uint32_t raw = raw_of(k);
+    if (!lean) return epi_value(ep, raw, eb, ei, ej);
+    float v = sizeof(T) == 1 ? (float)((int)raw + bi[k]) : __uint_as_float(raw);
+    v = __fadd_rn(__fmul_rn(__fmul_rn(v, sc[k]), alpha), bf[k]);
+    return act_apply(v, ep.act, ep.act_alpha);
+  };
+  if constexpr (!NHWC_OUT) {
+    if (valid) {
+      if (!lean || ep.y_dtype == SOFIE_B200_I32) {
+        for (int k = 0; k < filters; ++k) epi_store_one(ep, raw_of(k), n, k, p);
+      } else {   // one coalesced store per channel: consecutive lanes are consecutive pixels of the channel's plane
+        const long long o0 = n * ep.stride_y + p;
+        for (int k = 0; k < filters; ++k) {
+          const float v = value_of(k, n, k, p);
+          const long long o = o0 + (long long)k * ep.ldy;
+          if (ep.y_dtype == SOFIE_B200_F32) ((float *)ep.Y)[o] = v;
+          else if (ep.y_dtype == SOFIE_B200_BF16) ((__nv_bfloat16 *)ep.Y)[o] = __float2bfloat16_rn(v);
+          else if (ep.y_dtype == SOFIE_B200_I8) ((int8_t *)ep.Y)[o] = (int8_t)quantize_i(v, ep.out_scale, ep.out_zp, -128, 127);
+          else ((uint8_t *)ep.Y)[o] = (uint8_t)quantize_i(v, ep.out_scale, ep.out_zp, 0, 255);
+        }
+      }
+    }
+  } else {
+    const int ys = ep.y_dtype == SOFIE_B200_F32 || ep.y_dtype == SOFIE_B200_I32 ? 4 : (ep.y_dtype == SOFIE_B200_BF16 ? 2 : 1);
+    const int per = 16 / ys;   // channels per 16-byte store
+    const bool vec = (filters % per == 0) && (((uintptr_t)ep.Y | (uintptr_t)(ep.ldy * ys)) % 16 == 0) && ep.ldy == filters;
+    if (!vec || ep.y_dtype == SOFIE_B200_I32) {
+      if (valid)
+        for (int k = 0; k < filters; ++k) epi_store_one(ep, raw_of(k), 0, gp, k);
+      return;
+    }
+    // A warp's 32 pixels are 32 * filters * ys CONTIGUOUS bytes of a channels-last Y: each lane puts its pixel's channels
+    // into the warp's staging rows in shared memory, then the warp copies the block out 512 contiguous bytes per instruction
+    // (a lane storing its own 16-byte pieces wrote half sectors at a 64-byte stride: 0.28 TB/s on the int8 first layer).
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row_bytes = filters * ys;
+    unsigned char *stage = dsm + (size_t)filters * (NW * sizeof(W) + 12) + (size_t)warp * 32 * row_bytes;
+    unsigned char *srow = stage + (size_t)lane * row_bytes;
+    if (ys == 1) {
+      const int lo = ep.y_dtype == SOFIE_B200_I8 ? -128 : 0, hi = ep.y_dtype == SOFIE_B200_I8 ? 127 : 255;
+      for (int k0 = 0; k0 < filters; k0 += 16) {
+        uint32_t w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint32_t word = 0;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int k = k0 + 4 * u + e;
+            word |= ((uint32_t)quantize_i(value_of(k, 0, gp, k), ep.out_scale, ep.out_zp, lo, hi) & 0xffu) << (8 * e);
+          }
+          w[u] = word;
+        }
+        *reinterpret_cast<uint4 *>(srow + k0) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else if (ys == 2) {
+      for (int k0 = 0; k0 < filters; k0 += 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(value_of(k0 + 2 * u, 0, gp, k0 + 2 * u), value_of(k0 + 2 * u + 1, 0, gp, k0 + 2 * u + 1));
+          w[u] = *reinterpret_cast<uint32_t *>(&h2);
+        }
+        *reinterpret_cast<uint4 *>(srow + (size_t)k0 * 2) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+      for (int k0 = 0; k0 < filters; k0 += 4) {
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = value_of(k0 + e, 0, gp, k0 + e);
+        *reinterpret_cast<float4 *>(srow + (size_t)k0 * 4) = make_float4(v[0], v[1], v[2], v[3]);
+      }
+    }
+    __syncwarp();
+    const long long gp0 = gp_raw - lane;   // first pixel of this warp
+    const long long left = total - gp0;
+    const long long bytes_valid = (left >= 32 ? 32 : (left > 0 ? left : 0)) * row_bytes;
+    unsigned char *ydst = (unsigned char *)ep.Y + gp0 * row_bytes;
+    for (long long off = (long long)lane * 16; off < bytes_valid; off += 512)
+      *reinterpret_cast<uint4 *>(ydst + off) = *reinterpret_cast<const uint4 *>(stage + off);
+  }
+}
+
+// Weights [K, 3, 3, 3] -> [K][32 int8] or [K][28 floats], zero padded.
+template <typename T>
+__global__ void __launch_bounds__(256) direct_weights_kernel(const T *__restrict__ w, T *__restrict__ out, long long filters) {
+  constexpr int DIRECT_KW = DirectAcc<T>::KW;
+  const long long total = filters * DIRECT_KW;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long f = i / DIRECT_KW;
+    const int k = (int)(i - f * DIRECT_KW);
+    out[i] = k < DIRECT_KD ? w[f * DIRECT_KD + k] : (T)0;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) pad_weights_kernel(const T *__restrict__ w, T *__restrict__ wp, long long rows, long long kdim,
                                                           long long kpad) {
@@ -281,6 +467,27 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   p->kdim = p->cg * d.R * d.S;
   const int64_t vec = 16 / es;
   p->kpad = (p->kdim + vec - 1) / vec * vec;
+  if (d.groups == 1 && d.C == 3 && d.R == 3 && d.S == 3 && d.x_layout == 0 && d.K <= 256 && !getenv("SOFIE_B200_NO_DIRECT_CONV")) {
+    // the 3-channel first layer: direct kernel (see conv_direct_kernel); the plan only keeps the padded weights
+    p->direct = 1;
+    const int DIRECT_KW = es == 4 ? DirectAcc<float>::KW : DirectAcc<int8_t>::KW;
+    p->kpad = DIRECT_KW;
+    if (cudaMalloc(&p->w_padded, (size_t)(d.K * DIRECT_KW * es)) != cudaSuccess) {
+      delete p;
+      return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: allocating padded weights failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    const unsigned wg = (unsigned)((d.K * DIRECT_KW + 255) / 256);
+    if (es == 4) direct_weights_kernel<float><<<wg, 256, 0, ctx->stream>>>((const float *)W, (float *)p->w_padded, d.K);
+    else direct_weights_kernel<int8_t><<<wg, 256, 0, ctx->stream>>>((const int8_t *)W, (int8_t *)p->w_padded, d.K);
+    ctx->launches++;
+    sofie_b200_gemm_desc &e = p->edesc;   // the contraction whose epilogue is applied
+    e.ab_dtype = d.x_dtype; e.y_dtype = d.y_dtype; e.K = DIRECT_KD;
+    const int64_t imgs = d.N > 0 ? d.N : 1;
+    if (p->pix_rows) { e.M = imgs * Ho * Wo; e.N = d.K; e.batch = 1; e.ldy = d.K; }
+    else { e.M = d.K; e.N = Ho * Wo; e.batch = imgs; e.ldy = Ho * Wo; e.stride_y = d.K * Ho * Wo; e.stride_r = d.K * Ho * Wo; }
+    *out = p;
+    return 0;
+  }
   // fp32 at fp32 accuracy: large convolutions run as 3xTF32 on the tensor cores, with the weights split once here and
   // the input split by the unfold kernel; small ones stay on the fp32 FMA kernel.
   const int64_t images = d.N > 0 ? d.N : 1;
@@ -365,11 +572,13 @@ int sofie_b200_conv_plan_destroy(sofie_b200_conv_plan *plan) {
 }
 
 const char *sofie_b200_conv_plan_kernel(const sofie_b200_conv_plan *plan) {
-  return plan ? sofie_b200_gemm_plan_kernel(plan->gemm) : "";
+  if (!plan) return "";
+  return plan->direct ? "direct" : sofie_b200_gemm_plan_kernel(plan->gemm);
 }
 
 int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan) {
   if (!plan) return 0;
+  if (plan->direct) return 0;
   const int64_t es = dtype_size(plan->d.x_dtype);
   const int64_t xcol = (int64_t)plan->d.groups * plan->d.N * plan->Ho * plan->Wo * plan->kpad * (plan->split ? 2 : 1) * es;
   if (!plan->nhwc || plan->d.x_layout == 1) return xcol;   // a channels-last input needs no copy
@@ -381,6 +590,56 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
   if (!plan) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: plan is NULL");
   const sofie_b200_conv_desc &d = plan->d;
   if (d.N == 0) return 0;
+  if (plan->direct) {
+    if (!X || !Y) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: NULL tensor");
+    sofie_b200_ctx *ctx = plan->ctx;
+    SB_CUDA(cudaSetDevice(ctx->device));
+    const long long pix = plan->Ho * plan->Wo;
+    sofie_b200_epilogue e{};
+    e.alpha = 1.f; e.beta = 1.f; e.out_scale = 1.f;
+    if (ep) {
+      if (ep->row_scale) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: row_scale has no meaning for a convolution");
+      e = *ep;
+      if (plan->pix_rows) {
+        if (ep->bias_mode == SOFIE_B200_BIAS_ROW_F32 || ep->bias_mode == SOFIE_B200_BIAS_ROW_I32 || ep->bias_mode == SOFIE_B200_BIAS_FULL_F32)
+          return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: bias_mode %d not supported for a convolution", ep->bias_mode);
+        e.ldr = d.K;
+      } else {   // channels are the rows of the contraction this convolution stands for
+        e.row_scale = ep->col_scale;
+        e.col_scale = nullptr;
+        switch (ep->bias_mode) {
+          case SOFIE_B200_BIAS_NONE: case SOFIE_B200_BIAS_SCALAR_F32: break;
+          case SOFIE_B200_BIAS_COL_F32: e.bias_mode = SOFIE_B200_BIAS_ROW_F32; break;
+          case SOFIE_B200_BIAS_COL_I32: e.bias_mode = SOFIE_B200_BIAS_ROW_I32; break;
+          default: return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: bias_mode %d not supported for a convolution", ep->bias_mode);
+        }
+        e.ldr = pix;
+      }
+    }
+    EpiParams epi;
+    int rc = gemm_make_epi(plan->edesc, Y, &e, &epi);
+    if (rc) return rc;
+    const long long total = d.N * pix;
+    // channels-last output: 128 threads and a staging block of 32 pixels x K channels per warp behind the weights
+    const int threads = plan->pix_rows ? 128 : 256;
+    const unsigned grid = (unsigned)((total + threads - 1) / threads);
+    const size_t wsm = (size_t)d.K * ((d.x_dtype == SOFIE_B200_F32 ? 28 * sizeof(float) : 8 * sizeof(int)) + 12);   // weights + scale, bias, int bias
+    const size_t sm = wsm + (plan->pix_rows ? (size_t)(threads / 32) * 32 * d.K * dtype_size(d.y_dtype) : 0);
+    if (d.x_dtype == SOFIE_B200_F32) {
+      if (plan->pix_rows) {
+        SB_CUDA(cudaFuncSetAttribute(conv_direct_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        conv_direct_kernel<float, true><<<grid, threads, sm, ctx->stream>>>((const float *)X, (const float *)plan->w_padded, d, (int)plan->Ho, (int)plan->Wo, epi);
+      } else conv_direct_kernel<float, false><<<grid, threads, sm, ctx->stream>>>((const float *)X, (const float *)plan->w_padded, d, (int)plan->Ho, (int)plan->Wo, epi);
+    } else {
+      if (plan->pix_rows) {
+        SB_CUDA(cudaFuncSetAttribute(conv_direct_kernel<int8_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        conv_direct_kernel<int8_t, true><<<grid, threads, sm, ctx->stream>>>((const int8_t *)X, (const int *)plan->w_padded, d, (int)plan->Ho, (int)plan->Wo, epi);
+      } else conv_direct_kernel<int8_t, false><<<grid, threads, sm, ctx->stream>>>((const int8_t *)X, (const int *)plan->w_padded, d, (int)plan->Ho, (int)plan->Wo, epi);
+    }
+    SB_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return 0;
+  }
   if (!X || !Y || !workspace) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: NULL tensor or workspace");
   if ((uintptr_t)workspace % 16) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: workspace must be 16-byte aligned");
   sofie_b200_ctx *ctx = plan->ctx;

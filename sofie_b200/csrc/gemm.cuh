@@ -57,7 +57,6 @@ struct UmmaParams {
   int pair;                        // 1: CTA-pair kernel (cluster of 2, tcgen05 cta_group::2, 256 x bn tile per pair)
   int raster_n;                    // tile order inside a batch: 0 = M index fastest, 1 = N index fastest
   int y_tma;                       // the epilogue may store complete row segments through the tensor map of Y
-  int l2_ahead;                    // K blocks the L2 prefetch cursor runs in front of the loads (0 = off)
   int commit_group;                // pair kernel: K blocks consumed between bursts of stage releases
   int seg_kb;                      // chunk-promotion kernel: K blocks per split segment (ks / 32)
   int a_seg_kb[3], b_seg_kb[3];    // K block at which each of the three product segments starts in the stored A / B (hi | lo)
@@ -130,6 +129,7 @@ int umma_pair_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u);
 int umma_promote_set_smem(size_t smem_bytes);
 int umma_promote_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u);
 // api.cu
+int gemm_make_epi(const sofie_b200_gemm_desc &d, void *Y, const sofie_b200_epilogue *ep, EpiParams *o);
 int gemm_plan_create_promote(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, sofie_b200_gemm_plan **out);
 // gemm_split.cu
 int split2_enqueue(sofie_b200_ctx *ctx, const float *src, float *dst, long long rows, long long K, long long Ks, long long ld,

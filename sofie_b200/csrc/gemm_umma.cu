@@ -109,34 +109,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #ifdef SB200_ROLE_TIMERS
       t_begin = clock64();
 #endif
-      // L2 prefetch cursor: runs `l2_ahead` K blocks in front of the loads (across tile boundaries), so that the
-      // loads that fill shared memory find their lines in L2 instead of waiting for DRAM with only a few stages
-      // of lookahead.
-      long long pf_w = blockIdx.x;
-      int pf_kb = 0, pf_m0 = 0, pf_n0 = 0, pf_ba = 0, pf_bb = 0;
-      bool pf_fresh = true;
-      auto prefetch_step = [&]() {
-        if (pf_w >= p.num_items) return;
-        if (pf_fresh) {
-          long long t; int n_off, n_len; uint32_t idesc;
-          decode_item(p, pf_w, t, n_off, n_len, idesc);
-          const int b = (int)(t / tiles_per_batch);
-          const int r = (int)(t % tiles_per_batch);
-          int tm, tn;
-          tile_mn(p, r, tm, tn);
-          pf_m0 = tm * UMMA_BM;
-          pf_n0 = tn * p.bn + n_off;
-          pf_ba = p.a_bcast ? 0 : b; pf_bb = p.b_bcast ? 0 : b;
-          pf_fresh = false;
-        }
-        const int k0 = pf_kb * p.kb_elems;
-        if (!p.a_mn) tma_prefetch_3d(&tm_a, k0, pf_m0, pf_ba);
-        else for (int x = 0; x < p.a_boxes; ++x) tma_prefetch_3d(&tm_a, pf_m0 + x * p.a_box_mn, k0, pf_ba);
-        if (!p.b_mn) tma_prefetch_3d(&tm_b, k0, pf_n0, pf_bb);
-        else for (int x = 0; x < p.b_boxes; ++x) tma_prefetch_3d(&tm_b, pf_n0 + x * p.b_box_mn, k0, pf_bb);
-        if (++pf_kb == p.num_kb) { pf_kb = 0; pf_w += gridDim.x; pf_fresh = true; }
-      };
-      for (int i = 0; i < p.l2_ahead; ++i) prefetch_step();
       for (long long w = blockIdx.x; w < p.num_items && ok; w += gridDim.x) {
         long long t; int n_off, n_len; uint32_t idesc;
         decode_item(p, w, t, n_off, n_len, idesc);
@@ -148,7 +120,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int n0 = tn * p.bn + n_off;  // a half item still loads a full-width B slice
         const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (p.l2_ahead) prefetch_step();
           if (!ROLE_WAIT(w_empty, mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag))) {
             raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_EMPTY);
             ok = false;
@@ -408,8 +379,6 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
     u.b_seg_kb[0] = 0; u.b_seg_kb[1] = 0; u.b_seg_kb[2] = u.seg_kb;         // B: hi, hi, lo
   }
   u.commit_group = 1;
-  u.l2_ahead = 0;
-  if (const char *e = getenv("SOFIE_B200_L2_AHEAD")) { const int c = atoi(e); if (c >= 0 && c <= 64) u.l2_ahead = c; }
   if (const char *e = getenv("SOFIE_B200_PAIR_GROUP")) { const int c = atoi(e); if (c >= 1 && c <= 3) u.commit_group = c; }
   u.promote_chunk = 8;   // 32 MMA steps per accumulation: truncation bias below 2e-6 relative even for same-sign data
   if (const char *e = getenv("SOFIE_B200_PROMOTE_CHUNK")) { const int c = atoi(e); if (c >= 1 && c <= 64) u.promote_chunk = c; }

@@ -75,11 +75,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, uint
       : "memory");
 }
 
-// Asks the L2 to fetch a box ahead of time; nothing lands in shared memory and nothing is signalled.
-__device__ __forceinline__ void tma_prefetch_3d(const void *tmap, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(tmap), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-
 // Tiled store shared -> global (clipped at the tensor's bounds), tracked by the thread's bulk async-group.
 __device__ __forceinline__ void tma_store_3d(const void *tmap, uint32_t src, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tmap), "r"(src), "r"(c0),
