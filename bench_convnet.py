@@ -87,26 +87,32 @@ def convnet_oracle(o, x: np.ndarray, weights, int8: bool) -> np.ndarray:
 class ConvNetB200:
     """The network on one GPU through the C ABI.  `ctx` is a sofie_b200.ops.Context on that GPU."""
 
-    LAUNCHES = 1 + 7 * 2 + 2        # direct first layer, unfold + contraction for layers 2-8, pool, classifier
-    LAUNCHES_NCHW = 1 + 7 * 3 + 2   # every tensor NCHW: plus a channels-last copy of the input of layers 2-8
+    @property
+    def launches(self) -> int:
+        """Kernels one call enqueues: per convolution 1 (direct first layer; implicit convolution "umma_im2col"), else an
+        unfold and a contraction plus, for an NCHW input, its channels-last copy; then the pool and the classifier."""
+        n = 2
+        for kern, xl in zip(self.kernels, self.x_layouts):
+            n += 1 if kern in ("direct", "umma_im2col") else (2 if xl else 3)
+        return n
 
     def __init__(self, ctx, weights, batch: int, img: int, int8: bool, device: str, channels_last: bool = True):
         """channels_last: the activations between the convolutions are kept [N,H,W,C] (what a layout pass of the generator
-        would emit for a conv -> conv chain); the network's input and the last convolution's output stay NCHW."""
+        would emit for a conv -> conv chain, the pool reading the last one in that layout); the network's input stays NCHW."""
         import torch
         from sofie_b200 import lib as L
         from sofie_b200.ops import GemmPlan, make_epilogue
-        self.ctx, self.batch, self.int8 = ctx, batch, int8
+        self.ctx, self.batch, self.int8, self.channels_last = ctx, batch, int8, channels_last
         self.lib = lib = ctx._lib
         t = torch
         adt = t.int8 if int8 else t.float32
         code = L.I8 if int8 else L.F32
         layers, fc_w, fc_b = weights
-        self.plans, self.eps, self.keep, self.acts, self.kernels = [], [], [], [], []
+        self.plans, self.eps, self.keep, self.acts, self.kernels, self.x_layouts = [], [], [], [], [], []
         hw, ws_bytes = img, 16
         self.x_in = t.empty((batch, 3, img, img), dtype=adt, device=device)
         for i, (ly, st, cin, cout) in enumerate(zip(layers, STRIDES, CHANNELS[:-1], CHANNELS[1:])):
-            xl, yl = (1 if channels_last and i > 0 else 0), (1 if channels_last and i < 7 else 0)
+            xl, yl = (1 if channels_last and i > 0 else 0), (1 if channels_last else 0)
             d = conv_desc(batch, cin, hw, hw, cout, st, code, code, xl, yl)
             w = t.from_numpy(ly["w"]).to(device)
             h = C.c_void_p()
@@ -117,6 +123,7 @@ class ConvNetB200:
             self.plans.append(h); self.eps.append(ep); self.keep.append((keep, w))
             self.acts.append(t.empty((batch, hw, hw, cout) if yl else (batch, cout, hw, hw), dtype=adt, device=device))
             self.kernels.append(lib.sofie_b200_conv_plan_kernel(h).decode())
+            self.x_layouts.append(xl)
         ctx.sync()   # weight re-layout kernels read `w`
         self.workspace = t.empty(ws_bytes, dtype=t.uint8, device=device)
         self.pooled = t.empty((batch, 512), dtype=t.float32, device=device)
@@ -133,7 +140,10 @@ class ConvNetB200:
         for h, ep, y in zip(self.plans, self.eps, self.acts):
             L.check(self.lib.sofie_b200_conv_enqueue(h, cur.data_ptr(), y.data_ptr(), self.workspace.data_ptr(), C.byref(ep)), "conv_enqueue")
             cur = y
-        self.ctx.global_avgpool(cur, self.pooled)
+        if self.channels_last:
+            self.ctx.global_avgpool_nhwc(cur, self.pooled)
+        else:
+            self.ctx.global_avgpool(cur, self.pooled)
         self.fc.enqueue(self.pooled, self.fc_w, self.logits, self.fc_ep)
         return self.logits
 

@@ -322,6 +322,11 @@ int sofie_b200_batchnorm_enqueue(sofie_b200_ctx *ctx, const float *x, float *y, 
 int sofie_b200_global_avgpool_enqueue(sofie_b200_ctx *ctx, const void *x, float *y, int32_t x_dtype,
                                       int64_t nc, int64_t inner);
 
+/* The same GlobalAveragePool on a channels-last tensor [n, pixels, channels] (what a convolution with
+ * y_layout = 1 writes): y[n,c] = sum(x[n,:,c]) / pixels, summed in pixel order. */
+int sofie_b200_global_avgpool_nhwc_enqueue(sofie_b200_ctx *ctx, const void *x, float *y, int32_t x_dtype,
+                                           int64_t n, int64_t pixels, int64_t channels);
+
 /* QuantizeLinear / DequantizeLinear (ONNX): q = sat(rint(x/scale)+zp);  x = (q-zp)*scale.
  * Per-tensor when channels == 1, else per-channel with c = (i / inner) % channels. */
 int sofie_b200_quantize_enqueue(sofie_b200_ctx *ctx, const float *x, void *q, int32_t q_dtype, int64_t n,

@@ -58,6 +58,22 @@ int gemm_plan_create_promote(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g,
   *out = in;
   return 0;
 }
+// An implicit convolution as a contraction: A is the channels-last input read in im2col mode (g.M = output pixels of the
+// batch, g.K = R*S*C, g.lda unused), B the filters [g.N, g.K] with K ordered (filter row, filter column, channel).
+// Returns 1 when the tensor path does not apply.
+int gemm_plan_create_im2col(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, const Im2colDesc &ic, sofie_b200_gemm_plan **out) {
+  *out = nullptr;
+  sofie_b200_gemm_plan *in = new sofie_b200_gemm_plan();
+  in->ctx = ctx;
+  in->desc = g;
+  in->ic = ic;
+  in->kb_bytes = (ic.C * dtype_size(g.ab_dtype)) % 128 == 0 ? 128 : 64;
+  const int rc = umma_plan_init(in);
+  if (rc) { delete in; return rc; }
+  in->use_umma = 1;
+  *out = in;
+  return 0;
+}
 // Epilogue parameters of a contraction described by `d` writing to Y (for kernels outside this file that apply the
 // same fused epilogue: the direct convolution).
 int gemm_make_epi(const sofie_b200_gemm_desc &d, void *Y, const sofie_b200_epilogue *ep, EpiParams *o);
@@ -217,6 +233,7 @@ int sofie_b200_gemm_plan_destroy(sofie_b200_gemm_plan *plan) {
 const char *sofie_b200_gemm_plan_kernel(const sofie_b200_gemm_plan *plan) {
   if (!plan) return "";
   if (plan->inner || (plan->promote && plan->use_umma)) return "umma3x";
+  if (plan->ic.on) return "umma_im2col";
   return plan->use_umma ? "umma" : "simt";
 }
 

@@ -24,6 +24,8 @@ struct sofie_b200_conv_plan {
   int pix_rows = 0;            // y_layout = channels-last: output pixels are the accumulator rows, the unfolded input is the A operand
   int nhwc = 0;                // channels-last unfold: the input is first transposed to [N, H, W, C] in the workspace and K runs
                                // (r, s, c), so every 16-byte chunk of the unfolded matrix is one aligned vector copy
+  int implicit = 0;            // channels-last in and out on the tensor cores with no unfolded copy: the contraction's TMA producer reads
+                               // the input tensor itself in im2col mode (gemm_umma.cu); no workspace
   sofie_b200_gemm_plan *gemm = nullptr;
 };
 
@@ -488,6 +490,45 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
     *out = p;
     return 0;
   }
+  // Implicit convolution: both tensors channels-last, one group, the channels of a pixel a whole number of 64-byte K
+  // blocks, and padding that reads as zero (TMA fills out-of-range pixels with zeros, so a non-zero input zero point
+  // needs an unpadded convolution).  int8, or fp32 where single-pass TF32 was asked for.
+  {
+    const bool has_pad = d.pad_top || d.pad_bottom || d.pad_left || d.pad_right;
+    const bool type_ok = d.x_dtype == SOFIE_B200_I8 ? (d.x_zero_point == 0 || !has_pad) : d.precise == 0;
+    const int64_t rows = (d.N > 0 ? d.N : 1) * Ho * Wo;
+    if (d.groups == 1 && d.x_layout == 1 && d.y_layout == 1 && type_ok && (d.C * es) % 64 == 0 && rows < 0x7fffffffLL &&
+        d.K * p->kdim < 0x7fffffffLL && !getenv("SOFIE_B200_NO_IMPLICIT_CONV")) {
+      Im2colDesc ic;
+      ic.on = 1; ic.N = d.N > 0 ? d.N : 1; ic.H = d.H; ic.W = d.W; ic.C = d.C; ic.Ho = Ho; ic.Wo = Wo;
+      ic.R = (int)d.R; ic.S = (int)d.S; ic.pt = (int)d.pad_top; ic.pl = (int)d.pad_left; ic.pb = (int)d.pad_bottom; ic.pr = (int)d.pad_right;
+      ic.sh = (int)d.stride_h; ic.sw = (int)d.stride_w; ic.dh = (int)d.dil_h; ic.dw = (int)d.dil_w;
+      sofie_b200_gemm_desc g{};
+      g.trans_a = 0; g.trans_b = 1; g.ab_dtype = d.x_dtype; g.y_dtype = d.y_dtype;
+      g.M = rows; g.N = d.K; g.K = p->kdim; g.batch = 1; g.lda = p->kdim; g.ldb = p->kdim; g.ldy = d.K; g.precise = 0;
+      const bool y_ok = d.y_dtype == SOFIE_B200_F32 || d.y_dtype == SOFIE_B200_BF16 || d.y_dtype == SOFIE_B200_I8 || d.y_dtype == SOFIE_B200_U8 ||
+                        (d.y_dtype == SOFIE_B200_I32 && d.x_dtype == SOFIE_B200_I8);
+      rc = y_ok ? gemm_plan_create_im2col(ctx, g, ic, &p->gemm) : 1;
+      if (rc < 0) { delete p; return rc; }
+      if (rc == 0) {
+        p->implicit = 1; p->nhwc = 1; p->kpad = p->kdim;
+        if (cudaMalloc(&p->w_padded, (size_t)(d.K * p->kdim * es)) != cudaSuccess) {
+          sofie_b200_gemm_plan_destroy(p->gemm);
+          delete p;
+          return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: allocating the filter buffer failed: %s", cudaGetErrorString(cudaGetLastError()));
+        }
+        const long long wt = d.K * p->kdim;
+        const unsigned wg = (unsigned)std::min<long long>((wt + 255) / 256, (long long)ctx->sm_count * 16);
+        if (es == 4) reorder_weights_kernel<float><<<wg, 256, 0, ctx->stream>>>((const float *)W, (float *)p->w_padded, d.K, (int)p->cg, (int)(d.R * d.S));
+        else reorder_weights_kernel<int8_t><<<wg, 256, 0, ctx->stream>>>((const int8_t *)W, (int8_t *)p->w_padded, d.K, (int)p->cg, (int)(d.R * d.S));
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) { sofie_b200_gemm_plan_destroy(p->gemm); cudaFree(p->w_padded); delete p; return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: %s", cudaGetErrorString(e)); }
+        ctx->launches++;
+        *out = p;
+        return 0;
+      }
+    }
+  }
   // fp32 at fp32 accuracy: large convolutions run as 3xTF32 on the tensor cores, with the weights split once here and
   // the input split by the unfold kernel; small ones stay on the fp32 FMA kernel.
   const int64_t images = d.N > 0 ? d.N : 1;
@@ -573,12 +614,12 @@ int sofie_b200_conv_plan_destroy(sofie_b200_conv_plan *plan) {
 
 const char *sofie_b200_conv_plan_kernel(const sofie_b200_conv_plan *plan) {
   if (!plan) return "";
-  return plan->direct ? "direct" : sofie_b200_gemm_plan_kernel(plan->gemm);
+  return plan->direct ? "direct" : sofie_b200_gemm_plan_kernel(plan->gemm);   // "umma_im2col": implicit convolution
 }
 
 int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan) {
   if (!plan) return 0;
-  if (plan->direct) return 0;
+  if (plan->direct || plan->implicit) return 0;
   const int64_t es = dtype_size(plan->d.x_dtype);
   const int64_t xcol = (int64_t)plan->d.groups * plan->d.N * plan->Ho * plan->Wo * plan->kpad * (plan->split ? 2 : 1) * es;
   if (!plan->nhwc || plan->d.x_layout == 1) return xcol;   // a channels-last input needs no copy
@@ -639,6 +680,19 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
     SB_CUDA(cudaGetLastError());
     ctx->launches++;
     return 0;
+  }
+  if (plan->implicit) {
+    if (!X || !Y) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: NULL tensor");
+    sofie_b200_epilogue e{};
+    e.alpha = 1.f; e.beta = 1.f; e.out_scale = 1.f;
+    if (ep) {
+      if (ep->row_scale) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: row_scale has no meaning for a convolution");
+      if (ep->bias_mode == SOFIE_B200_BIAS_ROW_F32 || ep->bias_mode == SOFIE_B200_BIAS_ROW_I32 || ep->bias_mode == SOFIE_B200_BIAS_FULL_F32)
+        return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: bias_mode %d not supported for a convolution", ep->bias_mode);
+      e = *ep;
+      e.ldr = d.K;
+    }
+    return sofie_b200_gemm_enqueue(plan->gemm, X, plan->w_padded, Y, &e);
   }
   if (!X || !Y || !workspace) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: NULL tensor or workspace");
   if ((uintptr_t)workspace % 16) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: workspace must be 16-byte aligned");

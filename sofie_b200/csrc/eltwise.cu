@@ -136,6 +136,17 @@ __global__ void __launch_bounds__(256) avgpool_kernel(const T *__restrict__ x, f
   }
 }
 
+// Channels-last planes: one thread per (image, channel); the threads of a warp read consecutive channels of one pixel.
+template <typename T>
+__global__ void __launch_bounds__(256) avgpool_nhwc_kernel(const T *__restrict__ x, float *__restrict__ y, long long n, long long pixels, long long c) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n * c) return;
+  const T *p = x + (i / c) * pixels * c + i % c;
+  float s = 0.f;
+  for (long long j = 0; j < pixels; ++j) s += pool_ld<T>(p + j * c);
+  y[i] = s / (float)pixels;
+}
+
 // ---- Quantize / Dequantize -------------------------------------------------------------------
 template <typename Q>
 __global__ void __launch_bounds__(256) quantize_kernel(const float *__restrict__ x, Q *__restrict__ q, long long n,
@@ -290,6 +301,21 @@ int sofie_b200_global_avgpool_enqueue(sofie_b200_ctx *ctx, const void *x, float 
   else if (x_dtype == SOFIE_B200_BF16) avgpool_kernel<__nv_bfloat16><<<g, 256, 0, ctx->stream>>>((const __nv_bfloat16 *)x, y, nc, inner);
   else if (x_dtype == SOFIE_B200_I8) avgpool_kernel<int8_t><<<g, 256, 0, ctx->stream>>>((const int8_t *)x, y, nc, inner);
   else return fail(SOFIE_B200_ERR_INVALID, "global_avgpool_enqueue: type %d not supported", x_dtype);
+  SB_LAUNCHED();
+}
+
+int sofie_b200_global_avgpool_nhwc_enqueue(sofie_b200_ctx *ctx, const void *x, float *y, int32_t x_dtype, int64_t n,
+                                           int64_t pixels, int64_t channels) {
+  SB_PRELUDE("global_avgpool_nhwc_enqueue");
+  if (n < 0 || pixels < 0 || channels < 0) return fail(SOFIE_B200_ERR_INVALID, "global_avgpool_nhwc_enqueue: negative extent");
+  if (n * channels == 0) return 0;
+  if (pixels == 0) return fail(SOFIE_B200_ERR_INVALID, "global_avgpool_nhwc_enqueue: empty plane");
+  if (!x || !y) return fail(SOFIE_B200_ERR_INVALID, "global_avgpool_nhwc_enqueue: NULL tensor");
+  const unsigned g = (unsigned)((n * channels + 255) / 256);
+  if (x_dtype == SOFIE_B200_F32) avgpool_nhwc_kernel<float><<<g, 256, 0, ctx->stream>>>((const float *)x, y, n, pixels, channels);
+  else if (x_dtype == SOFIE_B200_BF16) avgpool_nhwc_kernel<__nv_bfloat16><<<g, 256, 0, ctx->stream>>>((const __nv_bfloat16 *)x, y, n, pixels, channels);
+  else if (x_dtype == SOFIE_B200_I8) avgpool_nhwc_kernel<int8_t><<<g, 256, 0, ctx->stream>>>((const int8_t *)x, y, n, pixels, channels);
+  else return fail(SOFIE_B200_ERR_INVALID, "global_avgpool_nhwc_enqueue: type %d not supported", x_dtype);
   SB_LAUNCHED();
 }
 

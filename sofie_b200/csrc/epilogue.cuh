@@ -22,6 +22,7 @@ struct EpiParams {
   int params_aligned;  // col_scale and a per-column bias are 16-byte aligned (vector loads allowed)
   int residual_aligned;  // residual base, pitch and batch stride are multiples of 16 bytes
   int fast;            // store_chunk_fast() applies: aligned per-column vectors, no full-matrix bias
+  int seg_chunks;      // tcgen05 epilogue: 32-column chunks per flushed row segment (0: a whole 128-byte segment)
 };
 
 __device__ __forceinline__ float act_apply(float v, int act, float act_alpha) {

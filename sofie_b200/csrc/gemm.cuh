@@ -62,6 +62,14 @@ struct UmmaParams {
   int a_seg_kb[3], b_seg_kb[3];    // K block at which each of the three product segments starts in the stored A / B (hi | lo)
   int promote_chunk;               // chunk-promotion kernel: K blocks per tensor-memory accumulation
   int b_rows;                      // N extent of the B slice one CTA stages: bn, or bn/2 in pair mode
+  int kb_mmas;                     // MMAs (32 bytes of K each) per K block: 4, or 2 when a K block is 64 bytes
+  // Implicit convolution: A is a channels-last image tensor read through an im2col-mode tensor map; row m of A is output
+  // pixel m (image, then row, then column) and K block kb is (filter tap kb / ic_cblocks, channel block kb % ic_cblocks).
+  int im2col;
+  int ic_wo, ic_pix;               // output width, output pixels per image
+  int ic_sw, ic_sh, ic_pl, ic_pt;  // strides; left and top padding
+  int ic_dw, ic_dh, ic_s;          // dilations; filter width
+  int ic_cblocks;                  // K blocks per filter tap
   EpiParams ep;
   int *status;
 };
@@ -97,6 +105,15 @@ struct SimtParams {
 
 }  // namespace sb200
 
+namespace sb200 {
+// The convolution an implicit plan stands for (sofie_b200_gemm_plan::ic): A is the [N, H, W, C] input itself.
+struct Im2colDesc {
+  int on = 0;
+  long long N = 0, H = 0, W = 0, C = 0, Ho = 0, Wo = 0;
+  int R = 1, S = 1, pt = 0, pl = 0, pb = 0, pr = 0, sh = 1, sw = 1, dh = 1, dw = 1;
+};
+}  // namespace sb200
+
 struct sofie_b200_gemm_plan {
   sofie_b200_ctx *ctx = nullptr;
   sofie_b200_gemm_desc desc{};
@@ -109,12 +126,15 @@ struct sofie_b200_gemm_plan {
   const void *cached_a = nullptr, *cached_b = nullptr;
   CUtensorMap tm_a{}, tm_b{}, tm_y{};
   const void *cached_y = nullptr;
+  int cached_seg_div = 0;          // row-segment divisor the cached map of Y was built for
   // fp32-accurate tensor path (3xTF32): split operands [rows, 3*ks] and the TF32 plan that multiplies them
   sofie_b200_gemm_plan *inner = nullptr;
   float *split_a = nullptr, *split_b = nullptr;
   long long ks = 0;
   long long k_store = 0;           // K extent of the operands as stored (two segments) when it differs from desc.K (three products)
   int promote = 0;                 // this (inner TF32) plan runs the chunk-promotion kernel
+  sb200::Im2colDesc ic{};          // set: operand A is an image tensor read in im2col mode (implicit convolution)
+  int kb_bytes = 128;              // K extent of one shared-memory stage in bytes: 128 (128B swizzle) or 64 (64B swizzle)
 };
 
 namespace sb200 {
@@ -131,6 +151,7 @@ int umma_promote_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u);
 // api.cu
 int gemm_make_epi(const sofie_b200_gemm_desc &d, void *Y, const sofie_b200_epilogue *ep, EpiParams *o);
 int gemm_plan_create_promote(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, sofie_b200_gemm_plan **out);
+int gemm_plan_create_im2col(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, const Im2colDesc &ic, sofie_b200_gemm_plan **out);
 // gemm_split.cu
 int split2_enqueue(sofie_b200_ctx *ctx, const float *src, float *dst, long long rows, long long K, long long Ks, long long ld,
                    long long batch, long long batch_stride, int mn);

@@ -105,6 +105,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       ROLE_TIMER(w_empty);
+      ROLE_TIMER(c_expect);
+      ROLE_TIMER(c_load_a);
+      ROLE_TIMER(c_load_b);
+      ROLE_TIMER(sec_t0);
       ROLE_TIMER(t_begin);
 #ifdef SB200_ROLE_TIMERS
       t_begin = clock64();
@@ -119,6 +123,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int m0 = tm * UMMA_BM;
         const int n0 = tn * p.bn + n_off;  // a half item still loads a full-width B slice
         const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
+        // implicit convolution: the tile's first output pixel -> image and base pixel (tap (0, 0)) of its filter window
+        int ic_n = 0, ic_w = 0, ic_h = 0, tap_r = 0, tap_s = 0, cb = 0;
+        if (p.im2col) {
+          ic_n = m0 / p.ic_pix;
+          const int rem = m0 - ic_n * p.ic_pix, oh = rem / p.ic_wo;
+          ic_h = oh * p.ic_sh - p.ic_pt;
+          ic_w = (rem - oh * p.ic_wo) * p.ic_sw - p.ic_pl;
+        }
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!ROLE_WAIT(w_empty, mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag))) {
             raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_EMPTY);
@@ -126,26 +138,35 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             break;
           }
           const uint32_t full = bar_full + 8 * stage;
+          ROLE_SECTION_BEGIN();
           mbar_arrive_expect_tx(full, p.a_stage_bytes + p.b_stage_bytes);
+          ROLE_SECTION_END(c_expect);
           const int k0 = kb * p.kb_elems;
           const uint32_t sa = smem_a + stage * p.a_stage_bytes;
           const uint32_t sb = smem_b + stage * p.b_stage_bytes;
-          if (!p.a_mn) {
+          ROLE_SECTION_BEGIN();
+          if (p.im2col) {
+            tma_load_im2col_4d(sa, &tm_a, full, cb * p.kb_elems, ic_w, ic_h, ic_n, (uint16_t)(tap_s * p.ic_dw), (uint16_t)(tap_r * p.ic_dh));
+            if (++cb == p.ic_cblocks) { cb = 0; if (++tap_s == p.ic_s) { tap_s = 0; ++tap_r; } }
+          } else if (!p.a_mn) {
             tma_load_3d(sa, &tm_a, full, k0, m0, ba);
           } else {
             for (int x = 0; x < p.a_boxes; ++x)
               tma_load_3d(sa + x * p.a_box_bytes, &tm_a, full, m0 + x * p.a_box_mn, k0, ba);
           }
+          ROLE_SECTION_END(c_load_a);
+          ROLE_SECTION_BEGIN();
           if (!p.b_mn) {
             tma_load_3d(sb, &tm_b, full, k0, n0, bb);
           } else {
             for (int x = 0; x < p.b_boxes; ++x)
               tma_load_3d(sb + x * p.b_box_bytes, &tm_b, full, n0 + x * p.b_box_mn, k0, bb);
           }
+          ROLE_SECTION_END(c_load_b);
           if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
         }
       }
-      ROLE_REPORT("[cta %d] producer: total %lld, waiting for a free stage %lld\n", blockIdx.x, clock64() - t_begin, w_empty);
+      ROLE_REPORT("[cta %d] producer: total %lld, waiting for a free stage %lld, expect_tx %lld, issuing A loads %lld, B loads %lld\n", blockIdx.x, clock64() - t_begin, w_empty, c_expect, c_load_a, c_load_b);
       if (!ok) {
         // give copies that may still be in flight time to land before the CTA exits
         const uint64_t t0 = globaltimer();
@@ -164,7 +185,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const uint32_t a_lo0 = p.a_desc_lo | ((smem_a >> 4) & 0x3fffu), b_lo0 = p.b_desc_lo | ((smem_b >> 4) & 0x3fffu);
       const uint32_t a_step = p.a_stage_bytes >> 4, b_step = p.b_stage_bytes >> 4;
       const uint32_t a_kadv = p.a_kadv, b_kadv = p.b_kadv;
-      const int num_kb = p.num_kb;
+      const int num_kb = p.num_kb, kb_mmas = p.kb_mmas;
       ROLE_TIMER(w_full);
       ROLE_TIMER(w_tempty);
       ROLE_TIMER(c_fence);
@@ -198,6 +219,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           ROLE_SECTION_BEGIN();
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
+            if (k >= kb_mmas) break;
             const uint64_t ad = a_hi | (uint64_t)(a_lo + k * a_kadv);
             const uint64_t bd = b_hi | (uint64_t)(b_lo + k * b_kadv);
             umma<KIND>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
@@ -287,20 +309,56 @@ static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
   return fn;
 }
 
+static CUtensorMapDataType map_dtype(int dtype) {
+  if (dtype == SOFIE_B200_BF16) return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (dtype == SOFIE_B200_F32) return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  if (dtype == SOFIE_B200_I32) return CU_TENSOR_MAP_DATA_TYPE_INT32;
+  return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+}
+
+// im2col-mode map of a channels-last [N, H, W, C] tensor for one convolution: the bounding box holds the base pixels
+// (top-left taps) of all filter windows, traversed with the convolution's strides; one load fetches `kb_elems` channels of
+// 128 consecutive windows.
+static int encode_im2col(CUtensorMap *tm, int dtype, const void *base, const Im2colDesc &ic, uint32_t kb_elems, bool swizzle64) {
+  static PFN_cuTensorMapEncodeIm2col_v12000 enc = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      enc = reinterpret_cast<PFN_cuTensorMapEncodeIm2col_v12000>(sym);
+  });
+  if (!enc) return fail(SOFIE_B200_ERR_NO_DEVICE, "cuTensorMapEncodeIm2col entry point not available");
+  const uint64_t es = (uint64_t)dtype_size(dtype);
+  cuuint64_t dims[4] = {(cuuint64_t)ic.C, (cuuint64_t)ic.W, (cuuint64_t)ic.H, (cuuint64_t)ic.N};
+  cuuint64_t strides[3] = {(cuuint64_t)ic.C * es, (cuuint64_t)ic.W * ic.C * es, (cuuint64_t)ic.H * ic.W * ic.C * es};
+  int lower[2] = {-ic.pl, -ic.pt};                                             // {W, H}: first base pixel
+  int upper[2] = {ic.pr - (ic.S - 1) * ic.dw, ic.pb - (ic.R - 1) * ic.dh};    // last base pixel, from (W-1, H-1)
+  cuuint32_t estr[4] = {1, (cuuint32_t)ic.sw, (cuuint32_t)ic.sh, 1};
+  CUresult r = enc(tm, map_dtype(dtype), 4, const_cast<void *>(base), dims, strides, lower, upper, kb_elems, UMMA_BM, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(SOFIE_B200_ERR_CUDA, "cuTensorMapEncodeIm2col failed (%d): image %lldx%lldx%lldx%lld, box corners (%d,%d)/(%d,%d), strides %d,%d",
+                (int)r, ic.N, ic.H, ic.W, ic.C, lower[0], lower[1], upper[0], upper[1], ic.sw, ic.sh);
+  return 0;
+}
+
+static CUtensorMapSwizzle swizzle_mode(int bytes) {
+  return bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : (bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 static int encode_map(CUtensorMap *tm, int dtype, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
-                      uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1) {
+                      uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1, int swizzle_bytes = 128) {
   auto enc = get_encode();
   if (!enc) return fail(SOFIE_B200_ERR_NO_DEVICE, "cuTensorMapEncodeTiled entry point not available");
-  CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_UINT8;
-  if (dtype == SOFIE_B200_BF16) dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  if (dtype == SOFIE_B200_F32) dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  if (dtype == SOFIE_B200_I32) dt = CU_TENSOR_MAP_DATA_TYPE_INT32;
+  const CUtensorMapDataType dt = map_dtype(dtype);
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
   cuuint32_t box[3] = {b0, b1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(tm, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   swizzle_mode(swizzle_bytes), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(SOFIE_B200_ERR_CUDA,
@@ -339,7 +397,20 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
     default: return 1;
   }
   // TMA needs 16-byte multiples for every global stride.
-  if ((d.lda * es) % 16 || (d.ldb * es) % 16) return 1;
+  const Im2colDesc &ic = plan->ic;
+  if (((d.lda * es) % 16 && !ic.on) || (d.ldb * es) % 16) return 1;
+  const int kb_bytes = plan->kb_bytes;   // 64: the 64-byte swizzle, for implicit convolutions over 64 bytes of channels
+  if (kb_bytes != 128 && !(kb_bytes == 64 && ic.on)) return 1;
+  if (ic.on) {
+    // K runs over (filter row, filter column, channel); a K block never straddles two taps; B (the filters) is K-major
+    if (d.trans_a || !d.trans_b || d.batch != 1 || plan->promote || (ic.C * es) % kb_bytes || d.K != ic.R * ic.S * ic.C ||
+        d.M != ic.N * ic.Ho * ic.Wo)
+      return 1;
+    const int up_w = ic.pr - (ic.S - 1) * ic.dw, up_h = ic.pb - (ic.R - 1) * ic.dh;
+    if (ic.pl > 128 || ic.pt > 128 || up_w < -128 || up_w > 127 || up_h < -128 || up_h > 127 || ic.sw > 8 || ic.sh > 8 ||
+        (ic.S - 1) * ic.dw > 65535 || (ic.R - 1) * ic.dh > 65535)
+      return 1;
+  }
   if (d.batch > 1 && (((d.stride_a * es) % 16) || ((d.stride_b * es) % 16))) return 1;
   if (d.M <= 0 || d.N <= 0 || d.K <= 0) return 1;
   // TF32 operands are taken K-major only (an MN-major fp32 operand goes to the CUDA-core kernel)
@@ -356,7 +427,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   {
     const long long pair_tiles = ((d.M + 255) / 256) * ((d.N + 255) / 256) * d.batch;
     (void)pair_tiles;
-    if (const char *e = getenv("SOFIE_B200_PAIR"); e && !plan->promote) u.pair = (atoi(e) != 0 && d.M >= 256 && d.N >= 64) ? 1 : 0;
+    if (const char *e = getenv("SOFIE_B200_PAIR"); e && !plan->promote && !ic.on) u.pair = (atoi(e) != 0 && d.M >= 256 && d.N >= 64) ? 1 : 0;
   }
   const int tile_m = u.pair ? 2 * UMMA_BM : UMMA_BM;
   u.tiles_m = (int)((d.M + tile_m - 1) / tile_m);
@@ -385,17 +456,25 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.b_rows = u.pair ? u.bn / 2 : u.bn;
   u.tiles_n = (int)((d.N + u.bn - 1) / u.bn);
   u.num_tiles = (long long)u.tiles_m * u.tiles_n * d.batch;
-  u.kb_elems = UMMA_STAGE_K_BYTES / es;
+  u.kb_elems = kb_bytes / es;
+  u.kb_mmas = kb_bytes / 32;
   u.num_kb = (int)((d.K + u.kb_elems - 1) / u.kb_elems);
-  u.a_stage_bytes = UMMA_BM * UMMA_STAGE_K_BYTES;
-  u.b_stage_bytes = u.b_rows * UMMA_STAGE_K_BYTES;
+  u.a_stage_bytes = UMMA_BM * kb_bytes;
+  u.b_stage_bytes = u.b_rows * kb_bytes;
+  u.im2col = ic.on;
+  if (ic.on) {
+    u.ic_wo = (int)ic.Wo; u.ic_pix = (int)(ic.Ho * ic.Wo);
+    u.ic_sw = ic.sw; u.ic_sh = ic.sh; u.ic_pl = ic.pl; u.ic_pt = ic.pt;
+    u.ic_dw = ic.dw; u.ic_dh = ic.dh; u.ic_s = ic.S;
+    u.ic_cblocks = (int)(ic.C / u.kb_elems);
+  }
   u.tmem_cols = 32;
   while (u.tmem_cols < 2u * u.bn) u.tmem_cols <<= 1;
 
   const size_t epi_bytes = (u.pair ? 4 : 8) * 4096;   // staging buffers of the epilogue warps
   const size_t budget = 227 * 1024 - 1024 /*alignment*/ - UMMA_TAIL_BYTES /*barriers*/ - epi_bytes;
   int stages = (int)(budget / (u.a_stage_bytes + u.b_stage_bytes));
-  if (stages > 8) stages = 8;
+  if (stages > (kb_bytes == 64 ? 12 : 8)) stages = kb_bytes == 64 ? 12 : 8;
   if (stages < 2) return 1;
   if (u.pair) stages = stages / u.commit_group * u.commit_group;   // release groups never straddle the ring's wrap
   u.stages = stages;
@@ -406,9 +485,9 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.a_bcast = (d.batch > 1 && d.stride_a == 0);
   u.b_bcast = (d.batch > 1 && d.stride_b == 0);
 
-  // Shared-memory matrix descriptors (128B swizzle): stride byte offset = 1024 (one 8-row
-  // swizzle atom), descriptor version 1, layout type 2 (SWIZZLE_128B).
-  const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  // Shared-memory matrix descriptors: stride byte offset = one 8-row swizzle atom (1024 bytes with the 128-byte swizzle,
+  // 512 with the 64-byte one), descriptor version 1, layout type 2 (SWIZZLE_128B) or 4 (SWIZZLE_64B).
+  const uint32_t hi = ((8u * kb_bytes) >> 4) | (1u << 14) | ((kb_bytes == 64 ? 4u : 2u) << 29);
   u.a_desc_hi = hi;
   u.b_desc_hi = hi;
   const uint32_t panel_bytes = (uint32_t)u.kb_elems * 128u;  // one MN-major box: 128 bytes x K rows
@@ -485,7 +564,9 @@ static int build_maps(sofie_b200_gemm_plan *plan, const void *A, const void *B) 
     if ((uintptr_t)A % 16) return fail(SOFIE_B200_ERR_INVALID, "A must be 16-byte aligned for the tcgen05 path");
     const uint64_t nb = u.a_bcast ? 1 : (uint64_t)d.batch;
     int rc;
-    if (!u.a_mn) {
+    if (plan->ic.on) {
+      rc = encode_im2col(&plan->tm_a, d.ab_dtype, A, plan->ic, (uint32_t)u.kb_elems, plan->kb_bytes == 64);
+    } else if (!u.a_mn) {
       uint64_t s2 = d.batch > 1 && !u.a_bcast ? (uint64_t)d.stride_a * es : (uint64_t)d.M * d.lda * es;
       rc = encode_map(&plan->tm_a, d.ab_dtype, A, kext, (uint64_t)d.M, nb, (uint64_t)d.lda * es, s2,
                       (uint32_t)u.kb_elems, UMMA_BM);
@@ -504,7 +585,7 @@ static int build_maps(sofie_b200_gemm_plan *plan, const void *A, const void *B) 
     if (!u.b_mn) {
       uint64_t s2 = d.batch > 1 && !u.b_bcast ? (uint64_t)d.stride_b * es : (uint64_t)d.N * d.ldb * es;
       rc = encode_map(&plan->tm_b, d.ab_dtype, B, kext, (uint64_t)d.N, nb, (uint64_t)d.ldb * es, s2,
-                      (uint32_t)u.kb_elems, (uint32_t)u.b_rows);
+                      (uint32_t)u.kb_elems, (uint32_t)u.b_rows, plan->kb_bytes);
     } else {
       uint64_t s2 = d.batch > 1 && !u.b_bcast ? (uint64_t)d.stride_b * es : (uint64_t)d.K * d.ldb * es;
       rc = encode_map(&plan->tm_b, d.ab_dtype, B, (uint64_t)d.N, (uint64_t)d.K, nb, (uint64_t)d.ldb * es, s2,
@@ -524,15 +605,25 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
   if (((uintptr_t)ep.Y % 16) != 0) u.vec_ok = 0;
   // Tensor map of Y for the epilogue's bulk stores: box = one 128-byte row segment x the 32 rows of an epilogue warp.
   u.y_tma = 0;
+  // Row segments per flush: a 128-byte segment is 4 chunks of 1-byte and 2 of 2-byte outputs; a narrow tile then has a
+  // single segment and one of the two warps of each lane quarter would idle, so the segment is halved until there are two.
+  int seg_div = 1;
+  if (!u.pair && !plan->promote && !getenv("SOFIE_B200_FULL_SEGMENTS")) {
+    const int full = 4 / dtype_size(plan->desc.y_dtype);   // chunks per 128 bytes
+    int g = full;
+    while (g > 1 && (u.bn / 32) / g < 2) g >>= 1;
+    if (g < full) { u.ep.seg_chunks = g; seg_div = full / g; }
+  }
   if (u.vec_ok && !u.pair && !plan->promote && !getenv("SOFIE_B200_NO_TMA_STORE")) {
     const sofie_b200_gemm_desc &d = plan->desc;
     const int ys = dtype_size(d.y_dtype);
-    if (ep.Y != plan->cached_y) {
+    if (ep.Y != plan->cached_y || seg_div != plan->cached_seg_div) {
       const uint64_t s2 = d.batch > 1 ? (uint64_t)d.stride_y * ys : (uint64_t)d.M * d.ldy * ys;
       rc = encode_map(&plan->tm_y, d.y_dtype, ep.Y, (uint64_t)d.N, (uint64_t)d.M, (uint64_t)d.batch, (uint64_t)d.ldy * ys, s2,
-                      (uint32_t)(128 / ys), 32);
+                      (uint32_t)(128 / ys / seg_div), 32, 128 / seg_div);
       if (rc) return rc;
       plan->cached_y = ep.Y;
+      plan->cached_seg_div = seg_div;
     }
     u.y_tma = 1;
   }

@@ -75,6 +75,29 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, uint
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+               "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const void *tmap, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(tmap), "r"(src), "r"(c0),
+               "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+
+// im2col-mode load from a channels-last image tensor {C, W, H, N}: the map's pixels-per-column consecutive base pixels (W
+// fastest, then H, then N, inside the map's bounding box, stepping by its traversal strides) starting at base pixel (w, h)
+// of image n, each read at base + (w_off, h_off), channels c .. c + channels-per-pixel.  Positions outside the tensor read
+// as zeros, which is the convolution's padding.  The rows land like those of a tiled box: one pixel per shared-memory row.
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void *tmap, uint32_t bar, int c, int w, int h, int n,
+                                                   uint16_t w_off, uint16_t h_off) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+      ::"r"(dst), "l"(tmap), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(w_off), "h"(h_off)
+      : "memory");
+}
+
 // Tiled store shared -> global (clipped at the tensor's bounds), tracked by the thread's bulk async-group.
 __device__ __forceinline__ void tma_store_3d(const void *tmap, uint32_t src, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(tmap), "r"(src), "r"(c0),

@@ -22,14 +22,22 @@ __device__ __forceinline__ void st_v4(void *p, uint32_t a, uint32_t b, uint32_t 
 // shared memory (32 rows x 128 bytes, XOR-swizzled: conflict-free both ways) and flushed with consecutive lanes
 // holding consecutive units of the same row: one store instruction then writes four whole 128-byte lines.
 //
+// The row pitch of the buffer is 128 bytes, or 64 or 32 where a warp flushes shorter row segments (so that both warps of
+// a lane quarter have segments to work on when the tile is narrow).  The two low bits of the buffer's address -- it is
+// 1024-byte aligned -- carry the pitch: 128 >> code bytes.  Byte a of the buffer lives at a ^ (((a >> 7) & m) << 4) with
+// m = 7, 3, 1: the TMA unit's swizzle whose span equals the pitch (128B, 64B, 32B), so a bulk tensor store of a
+// (pitch x 32 rows) box through a map with that swizzle reads the rows back in order.
+__device__ __forceinline__ uint32_t stage_swizzle(uint32_t a, uint32_t code) { return a ^ (((a >> 7) & (7u >> code)) << 4); }
+
 // stage_units: lane (= row) writes its U units of the chunk at unit offset `slot * U` of its row.
 template <int U>
 __device__ __forceinline__ void stage_units(uint32_t stage, const uint32_t (&w)[4 * U], int slot) {
   const int lane = threadIdx.x & 31;
-  const uint32_t my_row = stage + lane * 128;
+  const uint32_t code = stage & 3u, base = stage & ~3u;
+  const uint32_t a0 = (uint32_t)lane * (128u >> code) + (uint32_t)(slot * U) * 16u;
 #pragma unroll
   for (int u = 0; u < U; ++u) {
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + (((slot * U + u) ^ (lane & 7)) << 4)), "r"(w[4 * u]),
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + stage_swizzle(a0 + u * 16, code)), "r"(w[4 * u]),
                  "r"(w[4 * u + 1]), "r"(w[4 * u + 2]), "r"(w[4 * u + 3])
                  : "memory");
   }
@@ -40,12 +48,12 @@ __device__ __forceinline__ void stage_units(uint32_t stage, const uint32_t (&w)[
 __device__ __forceinline__ void flush_staged(uint32_t stage, uint8_t *y_row0, long long ldy_bytes, int rows_valid, int units) {
   const int lane = threadIdx.x & 31;
   __syncwarp();   // every lane's units are in the buffer
-  const int u = lane & 7;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int r = i * 4 + (lane >> 3);
+  const uint32_t code = stage & 3u, base = stage & ~3u;
+  const int lg = 3 - (int)code;   // log2 of the units per buffer row
+  for (int i = 0; i < (8 >> code); ++i) {
+    const int idx = i * 32 + lane, r = idx >> lg, u = idx & ((1 << lg) - 1);
     uint32_t a, b, c, d;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(stage + r * 128 + ((u ^ (r & 7)) << 4)) : "memory");
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(base + stage_swizzle((uint32_t)(r * (128 >> code) + u * 16), code)) : "memory");
     if (r < rows_valid && u < units) st_v4(y_row0 + r * ldy_bytes + u * 16, a, b, c, d);
   }
   __syncwarp();   // reads done before anyone overwrites the buffer
@@ -472,16 +480,19 @@ __device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)
 #pragma unroll
       for (int u = 0; u < P; ++u) v[u] = make_float2(__fdiv_rn(v[u].x, ep.out_scale), __fdiv_rn(v[u].y, ep.out_scale));
     }
-    // rint(v) + zp saturated to [lo, hi], in integers: v is first clamped to +-2^30 (far outside [lo - zp, hi - zp],
-    // NaN goes to -2^30 as fmaxf drops it, which saturates to lo like the float formula), so neither the conversion
-    // nor the addition can overflow.
+    // rint(v) + zp saturated to [lo, hi].  Rounding is monotonic and the bounds are integers, so v is clamped FIRST, to
+    // [lo - zp, hi - zp] (NaN goes to the lower bound as fmaxf drops it, like the float formula's saturation), and then
+    // rounded half-to-even by adding 1.5 * 2^23: the sum's low mantissa bits are the integer.  Full-rate instructions only
+    // (a float-to-int conversion issues at a quarter of the rate).  |lo - zp|, |hi - zp| < 2^22 for any 8-bit zero point.
+    const float flo = (float)(lo - zp), fhi = (float)(hi - zp);
+    const int unmagic = zp - 0x4B400000;
 #pragma unroll
     for (int i = 0; i < NC; ++i) {
       int q[32];
 #pragma unroll
       for (int u = 0; u < 16; ++u) {
-        q[2 * u] = min(max(__float2int_rn(fminf(fmaxf(v[16 * i + u].x, -1073741824.f), 1073741824.f)) + zp, lo), hi);
-        q[2 * u + 1] = min(max(__float2int_rn(fminf(fmaxf(v[16 * i + u].y, -1073741824.f), 1073741824.f)) + zp, lo), hi);
+        q[2 * u] = __float_as_int(__fadd_rn(fminf(fmaxf(v[16 * i + u].x, flo), fhi), 12582912.f)) + unmagic;
+        q[2 * u + 1] = __float_as_int(__fadd_rn(fminf(fmaxf(v[16 * i + u].y, flo), fhi), 12582912.f)) + unmagic;
       }
       uint32_t w[8];
 #pragma unroll
@@ -524,7 +535,12 @@ template <bool ACC_INT>
 __device__ __forceinline__ void drain_accumulator(const EpiParams &ep, uint32_t taddr, int c_end, int first_group, int group_stride,
                                                   long long b, long long row, int n0, bool vec, uint32_t stage, long long rows_total,
                                                   const CUtensorMap *tm_y = nullptr) {
-  const int G = chunks_per_flush(ep.y_dtype);
+  // chunks per flushed row segment: a whole 128-byte segment, or what the plan asked for (EpiParams::seg_chunks: a half or
+  // a quarter of it, the staging buffer's row pitch shrinking with it -- see stage_units)
+  const int G_full = chunks_per_flush(ep.y_dtype);
+  const int G = ep.seg_chunks > 0 && ep.seg_chunks < G_full ? ep.seg_chunks : G_full;
+  stage |= (G == G_full) ? 0u : (2 * G == G_full ? 1u : 2u);
+  const int seg_units = 8 * G / G_full;   // 16-byte units of a complete segment
   const int units_per_chunk = 2 * out_elem_bytes(ep.y_dtype);
   const int nch = (c_end + 31) >> 5;
   const long long row0 = row - (threadIdx.x & 31);
@@ -593,11 +609,11 @@ __device__ __forceinline__ void drain_accumulator(const EpiParams &ep, uint32_t 
     const int j_last = j + np - 1;
     if ((j_last == G - 1 || !has_next) && units > 0) {
       DRAIN_T0();
-      if (tm_y != nullptr && units == 8) {
+      if (tm_y != nullptr && units == seg_units) {
         ptx::fence_proxy_async();   // this lane's staging writes become visible to the TMA unit
         __syncwarp();
         if ((threadIdx.x & 31) == 0) {
-          ptx::tma_store_3d(tm_y, stage, n0 + seg_col, (int)row0, (int)b);
+          ptx::tma_store_3d(tm_y, stage & ~3u, n0 + seg_col, (int)row0, (int)b);
           ptx::bulk_commit_group();
         }
         store_pending = true;

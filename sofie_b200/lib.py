@@ -101,6 +101,7 @@ PROTOTYPES = {
     "sofie_b200_binary_enqueue": (C.c_int, [_P, _P, _P, _P, _I32, _I64, _I64, _I32, _I32]),
     "sofie_b200_batchnorm_enqueue": (C.c_int, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _I32]),
     "sofie_b200_global_avgpool_enqueue": (C.c_int, [_P, _P, _P, _I32, _I64, _I64]),
+    "sofie_b200_global_avgpool_nhwc_enqueue": (C.c_int, [_P, _P, _P, _I32, _I64, _I64, _I64]),
     "sofie_b200_quantize_enqueue": (C.c_int, [_P, _P, _P, _I32, _I64, _P, _P, _I64, _I64]),
     "sofie_b200_dequantize_enqueue": (C.c_int, [_P, _P, _P, _I32, _I64, _P, _P, _I64, _I64]),
     "sofie_b200_transpose_enqueue": (C.c_int, [_P, _P, _P, _I32, _I32, C.POINTER(_I64), C.POINTER(_I32)]),

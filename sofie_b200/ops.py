@@ -104,6 +104,13 @@ class Context:
         L.check(self._lib.sofie_b200_global_avgpool_enqueue(self._h, _ptr(x), _ptr(y), dtype_code(x.dtype), nc,
                                                             inner), "global_avgpool_enqueue")
 
+    def global_avgpool_nhwc(self, x, y):
+        """x: channels-last [n, ..., c]; y: [n, c] fp32."""
+        n, c = x.shape[0], x.shape[-1]
+        pixels = x.numel() // (n * c) if n * c else 0
+        L.check(self._lib.sofie_b200_global_avgpool_nhwc_enqueue(self._h, _ptr(x), _ptr(y), dtype_code(x.dtype), n, pixels, c),
+                "global_avgpool_nhwc_enqueue")
+
     def quantize(self, x, q, scale, zero_point, channels=1, inner=1):
         L.check(self._lib.sofie_b200_quantize_enqueue(self._h, _ptr(x), _ptr(q), dtype_code(q.dtype), x.numel(),
                                                       _ptr(scale), _ptr(zero_point), channels, inner),

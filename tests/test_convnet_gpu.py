@@ -121,7 +121,10 @@ def test_benchmark_network_object_matches_checker(ctx, oracle_lib, int8, channel
     for _ in range(2):   # the second call reuses every buffer
         got = net(torch.from_numpy(x).to(DEV))
         ctx.sync()
-    assert ctx.launches - n0 == 2 * (bc.ConvNetB200.LAUNCHES if channels_last else bc.ConvNetB200.LAUNCHES_NCHW)
+    assert ctx.launches - n0 == 2 * net.launches
+    assert net.kernels[0] == "direct"
+    if channels_last and int8:   # conv -> conv on channels-last int8 tensors: no unfolded copy
+        assert net.kernels[1:] == ["umma_im2col"] * 7 and net.launches == 1 + 7 + 2
     got = got.cpu().numpy()
     assert close_f32(got, want, rel=1e-4 if not int8 else 1e-5), np.abs(got - want).max()
     net.close()

@@ -307,6 +307,85 @@ def test_conv_channels_last_layouts(ctx, oracle, dtype, xl, yl):
         assert close_f32(got, want), np.abs(got - want).max()
 
 
+IMPLICIT_CASES = {
+    # name: (N, C, H, W, K, R, S, pads [top, left, bottom, right], strides [h, w], dilations [h, w], x zero point)
+    "c64_3x3_tail": (2, 64, 13, 10, 48, 3, 3, [1, 1, 1, 1], [1, 1], [1, 1], 0),         # 64-byte K blocks, 260 pixels: a partial tile
+    "c128_3x3_stride2": (3, 128, 17, 12, 64, 3, 3, [1, 1, 1, 1], [2, 2], [1, 1], 0),    # 128-byte K blocks
+    "c64_asymmetric": (2, 64, 15, 11, 40, 3, 2, [2, 0, 1, 1], [2, 1], [1, 2], 0),       # every W / H parameter different
+    "c256_1x1_zero_point": (2, 256, 9, 7, 96, 1, 1, [0, 0, 0, 0], [1, 1], [1, 1], 3),   # no padding: a zero point is allowed
+    "c192_5x5_wide": (1, 192, 20, 33, 272, 5, 5, [2, 2, 2, 2], [1, 1], [1, 1], 0),      # 3 x 64-byte blocks per tap, two N tiles
+    "c64_many_tiles": (5, 64, 56, 56, 64, 3, 3, [1, 1, 1, 1], [1, 1], [1, 1], 0),       # more tiles than SMs, windows wrap rows and images
+    # stride 2 on even extents
+    "s2_c64_3x3": (2, 64, 16, 12, 48, 3, 3, [1, 1, 1, 1], [2, 2], [1, 1], 0),
+    "s2_c128_pads": (3, 128, 14, 10, 64, 3, 3, [0, 1, 1, 0], [2, 2], [1, 1], 0),
+    "s2_c64_5x5": (2, 64, 18, 20, 32, 5, 5, [2, 2, 2, 2], [2, 2], [1, 1], 0),
+    "s2_c256_1x1": (2, 256, 12, 8, 128, 1, 1, [0, 0, 0, 0], [2, 2], [1, 1], 5),
+    "s2_c64_dilated": (2, 64, 20, 16, 64, 3, 3, [2, 3, 2, 3], [2, 2], [2, 3], 0),
+    "s2_c64_many_tiles": (4, 64, 112, 112, 128, 3, 3, [1, 1, 1, 1], [2, 2], [1, 1], 0),
+}
+
+
+@pytest.mark.parametrize("case", list(IMPLICIT_CASES))
+def test_conv_implicit_int8(ctx, oracle, case):
+    """Channels-last int8 convolutions whose contraction reads the input tensor itself (im2col-mode TMA loads, no unfolded
+    copy, no workspace): bit-exact against the oracle's direct convolution."""
+    from sofie_b200.ops import make_epilogue
+    lib = ctx._lib
+    N, Ci, H, W, Co, R, S, pads, strides, dil, zp = IMPLICIT_CASES[case]
+    rng = np.random.default_rng(len(case) + Ci)
+    x = rng.integers(-127, 128, size=(N, Ci, H, W), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(Co, Ci, R, S), dtype=np.int8)
+    cs = (rng.random(Co, dtype=np.float32) * 1e-4 + 2e-5).astype(np.float32)
+    bias = rng.integers(-20000, 20000, size=Co, dtype=np.int32)
+    d = gr.conv_desc(dict(pads=pads, strides=strides, dil=dil, group=1), x.shape, w.shape, L.I8, L.I8)
+    d.x_zero_point = zp
+    ho, wo = C.c_int64(), C.c_int64()
+    assert lib.sofie_b200_conv_out_shape(C.byref(d), C.byref(ho), C.byref(wo)) == 0
+    want = oracle.conv(x, w, d, ho.value, wo.value, ep=oracle.epilogue(col_scale=cs, bias=bias, act=L.ACT_RELU))
+    d.x_layout = d.y_layout = 1
+    tx = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).to(DEV)
+    tw = torch.from_numpy(w).to(DEV)
+    h = C.c_void_p()
+    L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), tw.data_ptr(), C.byref(h)), "conv_plan_create")
+    assert lib.sofie_b200_conv_plan_kernel(h).decode() == "umma_im2col"
+    assert lib.sofie_b200_conv_workspace_bytes(h) == 0
+    y = torch.zeros((N, ho.value, wo.value, Co), dtype=torch.int8, device=DEV)
+    ep, keep = make_epilogue(col_scale=torch.from_numpy(cs).to(DEV), bias=torch.from_numpy(bias).to(DEV), act=L.ACT_RELU)
+    L.check(lib.sofie_b200_conv_enqueue(h, tx.data_ptr(), y.data_ptr(), None, C.byref(ep)), "conv_enqueue")
+    ctx.sync()
+    lib.sofie_b200_conv_plan_destroy(h)
+    got = y.cpu().numpy().transpose(0, 3, 1, 2)
+    assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size}"
+
+
+def test_conv_implicit_tf32(ctx, oracle):
+    """precise = 0 on fp32 channels-last tensors: single-pass TF32 through the same im2col-mode producer."""
+    from sofie_b200.ops import make_epilogue
+    lib = ctx._lib
+    N, Ci, H, W, Co = 2, 32, 14, 14, 64
+    rng = np.random.default_rng(5)
+    x = rng.random((N, Ci, H, W), dtype=np.float32)
+    w = (rng.standard_normal((Co, Ci, 3, 3)) * 0.1).astype(np.float32)
+    bias = rng.standard_normal(Co).astype(np.float32)
+    d = gr.conv_desc(dict(pads=[1, 1, 1, 1], strides=[1, 1], dil=[1, 1], group=1), x.shape, w.shape, L.F32, L.F32)
+    want = oracle.conv(x, w, d, H, W, ep=oracle.epilogue(bias=bias))
+    d.x_layout = d.y_layout = 1
+    d.precise = 0
+    tx = torch.from_numpy(np.ascontiguousarray(x.transpose(0, 2, 3, 1))).to(DEV)
+    tw = torch.from_numpy(w).to(DEV)
+    h = C.c_void_p()
+    L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), tw.data_ptr(), C.byref(h)), "conv_plan_create")
+    assert lib.sofie_b200_conv_plan_kernel(h).decode() == "umma_im2col"
+    y = torch.zeros((N, H, W, Co), dtype=torch.float32, device=DEV)
+    ep, keep = make_epilogue(bias=torch.from_numpy(bias).to(DEV))
+    L.check(lib.sofie_b200_conv_enqueue(h, tx.data_ptr(), y.data_ptr(), None, C.byref(ep)), "conv_enqueue")
+    ctx.sync()
+    lib.sofie_b200_conv_plan_destroy(h)
+    got = y.cpu().numpy().transpose(0, 3, 1, 2)
+    # TF32 operands (10-bit mantissa): the tolerance of the reduced-precision contractions
+    assert np.allclose(got, want, rtol=2e-2, atol=1e-2), np.abs(got - want).max()
+
+
 def test_conv_fp32_with_folded_batchnorm(ctx, oracle):
     rng = np.random.default_rng(9)
     x = rng.random((2, 8, 20, 20), dtype=np.float32)
@@ -412,6 +491,17 @@ def test_quantize_dequantize_convert_pool(ctx, oracle):
     ctx.global_avgpool(tx, pooled)
     ctx.sync()
     assert np.abs(pooled.cpu().numpy() - oracle.global_avgpool(x)).max() <= 1e-6
+    # the same pool on the channels-last copy of x (fp32), and on an int8 channels-last tensor (exact sums)
+    x4 = x.reshape(4, 6, 5, 7)
+    pooled_cl = torch.empty((4, 6), dtype=torch.float32, device=DEV)
+    ctx.global_avgpool_nhwc(torch.from_numpy(np.ascontiguousarray(x4.transpose(0, 2, 3, 1))).to(DEV), pooled_cl)
+    ctx.sync()
+    assert np.abs(pooled_cl.cpu().numpy() - oracle.global_avgpool(x)).max() <= 1e-6
+    xi = rng.integers(-128, 128, size=(3, 40, 9, 11), dtype=np.int8)
+    pooled_i = torch.empty((3, 40), dtype=torch.float32, device=DEV)
+    ctx.global_avgpool_nhwc(torch.from_numpy(np.ascontiguousarray(xi.transpose(0, 2, 3, 1))).to(DEV), pooled_i)
+    ctx.sync()
+    assert np.array_equal(pooled_i.cpu().numpy(), oracle.global_avgpool(xi, L.I8))
     m = (rng.standard_normal((50, 64)) * 30).astype(np.float32)
     rs = (np.abs(m).max(axis=1) / 448.0).astype(np.float32)
     t8 = torch.zeros((50, 64), dtype=torch.float8_e4m3fn, device=DEV)
