@@ -165,7 +165,8 @@ typedef struct sofie_b200_conv_desc {
                                  /* conv -> conv chains: a generator keeps the chain channels-last and converts at   */
                                  /* its ends; the unfold then needs no layout copy and output pixels, not channels,  */
                                  /* fill the 128 accumulator rows.  x_layout = 1 needs C/groups to be a whole number */
-                                 /* of 16-byte vectors.                                                              */
+                                 /* of 16-byte vectors.  Both = 1 selects the implicit convolution where it applies  */
+                                 /* (sofie_b200_conv_plan_kernel).                                                  */
 } sofie_b200_conv_desc;
 
 typedef struct sofie_b200_ctx sofie_b200_ctx;
@@ -246,8 +247,12 @@ int sofie_b200_conv_out_shape(const sofie_b200_conv_desc *desc, int64_t *Ho, int
  * scratch of the reference is per image (ROperator_Conv.hxx:1002-1103); this one covers the batch. */
 #define SOFIE_B200_SPLIT_MIN_FLOPS 4e8
 int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan);
-/* Kernel family of the plan's contraction, as sofie_b200_gemm_plan_kernel reports it, or "direct" for the 3-channel 3x3
- * first layer (NCHW input, one group), which runs on the CUDA cores without unfold and needs no workspace. */
+/* Kernel family of the plan's contraction, as sofie_b200_gemm_plan_kernel reports it, or one of the two forms that need no
+ * unfold and no workspace (workspace_bytes = 0, `workspace` may be NULL):
+ *   "direct"       the 3-channel 3x3 first layer (NCHW input, one group) on the CUDA cores;
+ *   "umma_im2col"  implicit convolution: x_layout = y_layout = 1, one group, I8 input (zero point 0, or no padding) or
+ *                  F32 at precise = 0, C * element size a multiple of 64 bytes -- the tensor-core contraction reads X
+ *                  itself through im2col-mode TMA loads. */
 const char *sofie_b200_conv_plan_kernel(const sofie_b200_conv_plan *plan);
 /* Enqueues Y = epilogue(conv(X, W)); columns of the epilogue are output channels. */
 int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, void *workspace,
