@@ -93,7 +93,7 @@ class ConvNetB200:
         unfold and a contraction plus, for an NCHW input, its channels-last copy; then the pool and the classifier."""
         n = 2
         for kern, xl in zip(self.kernels, self.x_layouts):
-            n += 1 if kern in ("direct", "umma_im2col") else (2 if xl else 3)
+            n += 1 if kern in ("direct", "umma_im2col", "umma3x_im2col") else (2 if xl else 3)
         return n
 
     def __init__(self, ctx, weights, batch: int, img: int, int8: bool, device: str, channels_last: bool = True):
@@ -112,7 +112,11 @@ class ConvNetB200:
         hw, ws_bytes = img, 16
         self.x_in = t.empty((batch, 3, img, img), dtype=adt, device=device)
         for i, (ly, st, cin, cout) in enumerate(zip(layers, STRIDES, CHANNELS[:-1], CHANNELS[1:])):
-            xl, yl = (1 if channels_last and i > 0 else 0), (1 if channels_last else 0)
+            # channels-last chain; the fp32 net passes TF32 pairs (layout 2: [N,H,W,2C], hi then lo channels) between the
+            # convolutions, which the 3xTF32 contraction reads without an unfold, and a plain channels-last tensor to the pool
+            inner = 1 if int8 else 2
+            xl = (inner if i > 0 else 0) if channels_last else 0
+            yl = (inner if i < 7 else 1) if channels_last else 0
             d = conv_desc(batch, cin, hw, hw, cout, st, code, code, xl, yl)
             w = t.from_numpy(ly["w"]).to(device)
             h = C.c_void_p()
@@ -121,7 +125,7 @@ class ConvNetB200:
             hw = (hw + 2 - 3) // st + 1
             ep, keep = make_epilogue(col_scale=t.from_numpy(ly["scale"]).to(device), bias=t.from_numpy(ly["bias"]).to(device), act=L.ACT_RELU)
             self.plans.append(h); self.eps.append(ep); self.keep.append((keep, w))
-            self.acts.append(t.empty((batch, hw, hw, cout) if yl else (batch, cout, hw, hw), dtype=adt, device=device))
+            self.acts.append(t.empty((batch, hw, hw, cout * (2 if yl == 2 else 1)) if yl else (batch, cout, hw, hw), dtype=adt, device=device))
             self.kernels.append(lib.sofie_b200_conv_plan_kernel(h).decode())
             self.x_layouts.append(xl)
         ctx.sync()   # weight re-layout kernels read `w`

@@ -74,6 +74,25 @@ int gemm_plan_create_im2col(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, 
   *out = in;
   return 0;
 }
+// The fp32-accurate implicit convolution: A is a channels-last tensor of TF32 pairs ([N, H, W, 2C]: hi channels, then lo
+// channels) read in im2col mode, B the filters [g.N, 2 * R*S*C] as hi | lo with K ordered (filter row, filter column,
+// channel), g.K = 3 * R*S*C products.  split_out: Y is written as TF32 pairs too (g.ldy = 2 * g.N).
+int gemm_plan_create_promote_im2col(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, const Im2colDesc &ic, int split_out,
+                                    sofie_b200_gemm_plan **out) {
+  *out = nullptr;
+  sofie_b200_gemm_plan *in = new sofie_b200_gemm_plan();
+  in->ctx = ctx;
+  in->desc = g;
+  in->promote = 1;
+  in->k_store = g.K / 3 * 2;
+  in->ic = ic;
+  in->split_out = split_out;
+  const int rc = umma_plan_init(in);
+  if (rc) { delete in; return rc; }
+  in->use_umma = 1;
+  *out = in;
+  return 0;
+}
 // Epilogue parameters of a contraction described by `d` writing to Y (for kernels outside this file that apply the
 // same fused epilogue: the direct convolution).
 int gemm_make_epi(const sofie_b200_gemm_desc &d, void *Y, const sofie_b200_epilogue *ep, EpiParams *o);
@@ -232,6 +251,7 @@ int sofie_b200_gemm_plan_destroy(sofie_b200_gemm_plan *plan) {
 
 const char *sofie_b200_gemm_plan_kernel(const sofie_b200_gemm_plan *plan) {
   if (!plan) return "";
+  if (plan->ic.on && plan->promote) return "umma3x_im2col";
   if (plan->inner || (plan->promote && plan->use_umma)) return "umma3x";
   if (plan->ic.on) return "umma_im2col";
   return plan->use_umma ? "umma" : "simt";

@@ -24,6 +24,7 @@ struct sofie_b200_conv_plan {
   int pix_rows = 0;            // y_layout = channels-last: output pixels are the accumulator rows, the unfolded input is the A operand
   int nhwc = 0;                // channels-last unfold: the input is first transposed to [N, H, W, C] in the workspace and K runs
                                // (r, s, c), so every 16-byte chunk of the unfolded matrix is one aligned vector copy
+  int pair_out = 0;            // y_layout = 2: Y is channels-last TF32 pairs, [N, Ho, Wo, 2K]
   int implicit = 0;            // channels-last in and out on the tensor cores with no unfolded copy: the contraction's TMA producer reads
                                // the input tensor itself in im2col mode (gemm_umma.cu); no workspace
   sofie_b200_gemm_plan *gemm = nullptr;
@@ -351,7 +352,8 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
   } else {
     const int ys = ep.y_dtype == SOFIE_B200_F32 || ep.y_dtype == SOFIE_B200_I32 ? 4 : (ep.y_dtype == SOFIE_B200_BF16 ? 2 : 1);
     const int per = 16 / ys;   // channels per 16-byte store
-    const bool vec = (filters % per == 0) && (((uintptr_t)ep.Y | (uintptr_t)(ep.ldy * ys)) % 16 == 0) && ep.ldy == filters;
+    const int pair = ep.split_out ? 2 : 1;   // fp32 output as TF32 pairs: hi channels, then lo channels
+    const bool vec = (filters % per == 0) && (((uintptr_t)ep.Y | (uintptr_t)(ep.ldy * ys)) % 16 == 0) && ep.ldy == (long long)filters * pair;
     if (!vec || ep.y_dtype == SOFIE_B200_I32) {
       if (valid)
         for (int k = 0; k < filters; ++k) epi_store_one(ep, raw_of(k), 0, gp, k);
@@ -361,7 +363,38 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
     // into the warp's staging rows in shared memory, then the warp copies the block out 512 contiguous bytes per instruction
     // (a lane storing its own 16-byte pieces wrote half sectors at a 64-byte stride: 0.28 TB/s on the int8 first layer).
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int row_bytes = filters * ys;
+    const int row_bytes = filters * ys * pair;
+    if (pair == 2) {
+      // TF32 pairs: 32 channels at a time.  A pixel's staging row is [32 hi | 32 lo] floats; the warp then writes each
+      // 128-byte run to its place (hi at channel k, lo at channel filters + k of the pixel's 2 * filters floats).
+      constexpr int KC = 32;
+      unsigned char *st = dsm + (size_t)filters * (NW * sizeof(W) + 12) + (size_t)warp * 32 * KC * 8;
+      const long long gp0 = gp_raw - lane;
+      for (int kc0 = 0; kc0 < filters; kc0 += KC) {
+        const int nk = min(KC, filters - kc0);
+        for (int k0 = 0; k0 < nk; k0 += 4) {
+          float v[4], h[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            v[e] = value_of(kc0 + k0 + e, 0, gp, kc0 + k0 + e);
+            h[e] = tf32_rn(v[e]);
+            v[e] = tf32_rn(__fsub_rn(v[e], h[e]));
+          }
+          *reinterpret_cast<float4 *>(st + (size_t)lane * KC * 8 + (size_t)k0 * 4) = make_float4(h[0], h[1], h[2], h[3]);
+          *reinterpret_cast<float4 *>(st + (size_t)lane * KC * 8 + (size_t)(KC + k0) * 4) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+        __syncwarp();
+        const int per_run = nk / 4;   // 16-byte pieces per run
+        for (int idx = lane; idx < 64 * per_run; idx += 32) {
+          const int run = idx / per_run, u = idx - run * per_run, px = run >> 1, which = run & 1;
+          if (gp0 + px < total)
+            *reinterpret_cast<uint4 *>((unsigned char *)ep.Y + (gp0 + px) * row_bytes + (size_t)(which * filters + kc0) * 4 + (size_t)u * 16) =
+                *reinterpret_cast<const uint4 *>(st + (size_t)px * KC * 8 + (size_t)which * KC * 4 + (size_t)u * 16);
+        }
+        __syncwarp();
+      }
+      return;
+    }
     unsigned char *stage = dsm + (size_t)filters * (NW * sizeof(W) + 12) + (size_t)warp * 32 * row_bytes;
     unsigned char *srow = stage + (size_t)lane * row_bytes;
     if (ys == 1) {
@@ -453,8 +486,14 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
     return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: channels %lld / filters %lld not divisible by groups %d", (long long)d.C, (long long)d.K, d.groups);
   if (d.x_dtype != SOFIE_B200_F32 && d.x_dtype != SOFIE_B200_I8)
     return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: input type %d not supported (F32, I8)", d.x_dtype);
-  if ((d.x_layout != 0 && d.x_layout != 1) || (d.y_layout != 0 && d.y_layout != 1))
-    return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: layouts are 0 (NCHW) or 1 (channels-last)");
+  if (d.x_layout < 0 || d.x_layout > 2 || d.y_layout < 0 || d.y_layout > 2)
+    return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: layouts are 0 (NCHW), 1 (channels-last) or 2 (channels-last TF32 pairs)");
+  if ((d.x_layout == 2 || d.y_layout == 2) && (d.x_dtype != SOFIE_B200_F32 || d.y_dtype != SOFIE_B200_F32 || d.precise == 0 || d.groups != 1))
+    return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: layout 2 (TF32 pairs) is for one-group F32 convolutions at precise = 1");
+  if (d.x_layout == 2 && d.C % 32 != 0)
+    return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: x_layout = 2 needs C to be a multiple of 32");
+  if (d.y_layout == 2 && d.K % 4 != 0)
+    return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: y_layout = 2 needs K to be a multiple of 4");
   if (d.x_layout == 1 && (d.C / d.groups) % (16 / dtype_size(d.x_dtype)) != 0)
     return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: a channels-last input needs C/groups to be a whole number of 16-byte vectors");
   int64_t Ho, Wo;
@@ -463,7 +502,8 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   SB_CUDA(cudaSetDevice(ctx->device));
   const int es = dtype_size(d.x_dtype);
   sofie_b200_conv_plan *p = new sofie_b200_conv_plan();
-  p->pix_rows = d.y_layout == 1;
+  p->pix_rows = d.y_layout != 0;
+  p->pair_out = d.y_layout == 2;
   p->ctx = ctx; p->d = d; p->Ho = Ho; p->Wo = Wo;
   p->cg = d.C / d.groups; p->kg = d.K / d.groups;
   p->kdim = p->cg * d.R * d.S;
@@ -485,11 +525,47 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
     sofie_b200_gemm_desc &e = p->edesc;   // the contraction whose epilogue is applied
     e.ab_dtype = d.x_dtype; e.y_dtype = d.y_dtype; e.K = DIRECT_KD;
     const int64_t imgs = d.N > 0 ? d.N : 1;
-    if (p->pix_rows) { e.M = imgs * Ho * Wo; e.N = d.K; e.batch = 1; e.ldy = d.K; }
+    if (p->pix_rows) { e.M = imgs * Ho * Wo; e.N = d.K; e.batch = 1; e.ldy = p->pair_out ? 2 * d.K : d.K; }
     else { e.M = d.K; e.N = Ho * Wo; e.batch = imgs; e.ldy = Ho * Wo; e.stride_y = d.K * Ho * Wo; e.stride_r = d.K * Ho * Wo; }
     *out = p;
     return 0;
   }
+  // fp32 at fp32 accuracy without an unfold: X is a channels-last tensor of TF32 pairs (written by a convolution with
+  // y_layout = 2), read in im2col mode by the chunk-promotion kernel; the filters are split once here.
+  if (d.x_layout == 2) {
+    if (d.y_layout == 0) { delete p; return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: x_layout = 2 needs a channels-last output (y_layout 1 or 2)"); }
+    const int64_t rows = (d.N > 0 ? d.N : 1) * Ho * Wo;
+    Im2colDesc ic;
+    ic.on = 1; ic.N = d.N > 0 ? d.N : 1; ic.H = d.H; ic.W = d.W; ic.C = d.C; ic.Cs = 2 * d.C; ic.Ho = Ho; ic.Wo = Wo;
+    ic.R = (int)d.R; ic.S = (int)d.S; ic.pt = (int)d.pad_top; ic.pl = (int)d.pad_left; ic.pb = (int)d.pad_bottom; ic.pr = (int)d.pad_right;
+    ic.sh = (int)d.stride_h; ic.sw = (int)d.stride_w; ic.dh = (int)d.dil_h; ic.dw = (int)d.dil_w;
+    sofie_b200_gemm_desc g{};
+    g.trans_a = 0; g.trans_b = 1; g.ab_dtype = SOFIE_B200_F32; g.y_dtype = SOFIE_B200_F32;
+    g.M = rows; g.N = d.K; g.K = 3 * p->kdim; g.batch = 1; g.lda = 2 * p->kdim; g.ldb = 2 * p->kdim;
+    g.ldy = p->pair_out ? 2 * d.K : d.K; g.precise = 0;
+    rc = (rows < 0x7fffffffLL && 3 * p->kdim < 0x7fffffffLL) ? gemm_plan_create_promote_im2col(ctx, g, ic, p->pair_out, &p->gemm) : 1;
+    if (rc) { delete p; return rc < 0 ? rc : fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: this convolution cannot run from a tensor of TF32 pairs (x_layout = 2)"); }
+    p->implicit = 1; p->nhwc = 1; p->split = 1; p->kpad = p->kdim;
+    void *w_perm = nullptr;
+    if (cudaMalloc(&w_perm, (size_t)(d.K * p->kdim * es)) != cudaSuccess || cudaMalloc(&p->w_padded, (size_t)(d.K * 2 * p->kdim * es)) != cudaSuccess) {
+      cudaGetLastError();
+      if (w_perm) cudaFree(w_perm);
+      sofie_b200_gemm_plan_destroy(p->gemm);
+      delete p;
+      return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: allocating the filter buffers failed");
+    }
+    const long long wt = d.K * p->kdim;
+    const unsigned wg = (unsigned)std::min<long long>((wt + 255) / 256, (long long)ctx->sm_count * 16);
+    reorder_weights_kernel<float><<<wg, 256, 0, ctx->stream>>>((const float *)W, (float *)w_perm, d.K, (int)p->cg, (int)(d.R * d.S));
+    ctx->launches++;
+    rc = split2_enqueue(ctx, (const float *)w_perm, (float *)p->w_padded, d.K, p->kdim, p->kdim, p->kdim, 1, 0, 0);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(w_perm);
+    if (rc) { sofie_b200_gemm_plan_destroy(p->gemm); cudaFree(p->w_padded); delete p; return rc; }
+    *out = p;
+    return 0;
+  }
+  if (d.y_layout == 2 && !p->direct) { delete p; return fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: y_layout = 2 needs x_layout = 2 or the 3-channel first layer"); }
   // Implicit convolution: both tensors channels-last, one group, the channels of a pixel a whole number of 64-byte K
   // blocks, and padding that reads as zero (TMA fills out-of-range pixels with zeros, so a non-zero input zero point
   // needs an unpadded convolution).  int8, or fp32 where single-pass TF32 was asked for.
@@ -631,6 +707,7 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
   if (!plan) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: plan is NULL");
   const sofie_b200_conv_desc &d = plan->d;
   if (d.N == 0) return 0;
+  if (plan->pair_out && ((uintptr_t)Y % 16) != 0) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: a TF32-pair output must be 16-byte aligned");
   if (plan->direct) {
     if (!X || !Y) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: NULL tensor");
     sofie_b200_ctx *ctx = plan->ctx;
@@ -665,7 +742,9 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
     const int threads = plan->pix_rows ? 128 : 256;
     const unsigned grid = (unsigned)((total + threads - 1) / threads);
     const size_t wsm = (size_t)d.K * ((d.x_dtype == SOFIE_B200_F32 ? 28 * sizeof(float) : 8 * sizeof(int)) + 12);   // weights + scale, bias, int bias
-    const size_t sm = wsm + (plan->pix_rows ? (size_t)(threads / 32) * 32 * d.K * dtype_size(d.y_dtype) : 0);
+    const size_t sm = wsm + (plan->pix_rows ? (plan->pair_out ? (size_t)(threads / 32) * 32 * 32 * 8   // pairs: 32 channels at a time
+                                                                 : (size_t)(threads / 32) * 32 * d.K * dtype_size(d.y_dtype)) : 0);
+    epi.split_out = plan->pair_out;
     if (d.x_dtype == SOFIE_B200_F32) {
       if (plan->pix_rows) {
         SB_CUDA(cudaFuncSetAttribute(conv_direct_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));

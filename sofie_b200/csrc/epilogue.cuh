@@ -23,6 +23,7 @@ struct EpiParams {
   int residual_aligned;  // residual base, pitch and batch stride are multiples of 16 bytes
   int fast;            // store_chunk_fast() applies: aligned per-column vectors, no full-matrix bias
   int seg_chunks;      // tcgen05 epilogue: 32-column chunks per flushed row segment (0: a whole 128-byte segment)
+  int split_out;       // fp32 output written as a TF32 pair: hi = tf32(v) at column j, lo = tf32(v - hi) at column N + j
 };
 
 __device__ __forceinline__ float act_apply(float v, int act, float act_alpha) {

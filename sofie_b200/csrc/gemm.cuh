@@ -61,6 +61,8 @@ struct UmmaParams {
   int seg_kb;                      // chunk-promotion kernel: K blocks per split segment (ks / 32)
   int a_seg_kb[3], b_seg_kb[3];    // K block at which each of the three product segments starts in the stored A / B (hi | lo)
   int promote_chunk;               // chunk-promotion kernel: K blocks per tensor-memory accumulation
+  int fused3;                      // chunk-promotion kernel: a stage holds A hi | A lo | B hi | B lo of one K block and feeds all three
+                                   // products (4 loads per 12 MMAs instead of 6); stage byte counts are the doubled ones
   int b_rows;                      // N extent of the B slice one CTA stages: bn, or bn/2 in pair mode
   int kb_mmas;                     // MMAs (32 bytes of K each) per K block: 4, or 2 when a K block is 64 bytes
   // Implicit convolution: A is a channels-last image tensor read through an im2col-mode tensor map; row m of A is output
@@ -70,6 +72,7 @@ struct UmmaParams {
   int ic_sw, ic_sh, ic_pl, ic_pt;  // strides; left and top padding
   int ic_dw, ic_dh, ic_s;          // dilations; filter width
   int ic_cblocks;                  // K blocks per filter tap
+  int ic_c;                        // channels per pixel (a tensor of TF32 pairs stores 2 * ic_c: hi channels, then lo)
   EpiParams ep;
   int *status;
 };
@@ -110,6 +113,7 @@ namespace sb200 {
 struct Im2colDesc {
   int on = 0;
   long long N = 0, H = 0, W = 0, C = 0, Ho = 0, Wo = 0;
+  long long Cs = 0;   // channels per pixel as stored, when not C: 2 * C for a tensor of TF32 pairs (hi channels, then lo channels)
   int R = 1, S = 1, pt = 0, pl = 0, pb = 0, pr = 0, sh = 1, sw = 1, dh = 1, dw = 1;
 };
 }  // namespace sb200
@@ -135,6 +139,7 @@ struct sofie_b200_gemm_plan {
   int promote = 0;                 // this (inner TF32) plan runs the chunk-promotion kernel
   sb200::Im2colDesc ic{};          // set: operand A is an image tensor read in im2col mode (implicit convolution)
   int kb_bytes = 128;              // K extent of one shared-memory stage in bytes: 128 (128B swizzle) or 64 (64B swizzle)
+  int split_out = 0;               // chunk-promotion kernel: write Y as TF32 pairs (EpiParams::split_out)
 };
 
 namespace sb200 {
@@ -152,6 +157,7 @@ int umma_promote_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u);
 int gemm_make_epi(const sofie_b200_gemm_desc &d, void *Y, const sofie_b200_epilogue *ep, EpiParams *o);
 int gemm_plan_create_promote(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, sofie_b200_gemm_plan **out);
 int gemm_plan_create_im2col(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, const Im2colDesc &ic, sofie_b200_gemm_plan **out);
+int gemm_plan_create_promote_im2col(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc &g, const Im2colDesc &ic, int split_out, sofie_b200_gemm_plan **out);
 // gemm_split.cu
 int split2_enqueue(sofie_b200_ctx *ctx, const float *src, float *dst, long long rows, long long K, long long Ks, long long ld,
                    long long batch, long long batch_stride, int mn);

@@ -330,8 +330,9 @@ static int encode_im2col(CUtensorMap *tm, int dtype, const void *base, const Im2
   });
   if (!enc) return fail(SOFIE_B200_ERR_NO_DEVICE, "cuTensorMapEncodeIm2col entry point not available");
   const uint64_t es = (uint64_t)dtype_size(dtype);
-  cuuint64_t dims[4] = {(cuuint64_t)ic.C, (cuuint64_t)ic.W, (cuuint64_t)ic.H, (cuuint64_t)ic.N};
-  cuuint64_t strides[3] = {(cuuint64_t)ic.C * es, (cuuint64_t)ic.W * ic.C * es, (cuuint64_t)ic.H * ic.W * ic.C * es};
+  const cuuint64_t cs = (cuuint64_t)(ic.Cs ? ic.Cs : ic.C);   // channels per pixel as stored
+  cuuint64_t dims[4] = {cs, (cuuint64_t)ic.W, (cuuint64_t)ic.H, (cuuint64_t)ic.N};
+  cuuint64_t strides[3] = {cs * es, (cuuint64_t)ic.W * cs * es, (cuuint64_t)ic.H * ic.W * cs * es};
   int lower[2] = {-ic.pl, -ic.pt};                                             // {W, H}: first base pixel
   int upper[2] = {ic.pr - (ic.S - 1) * ic.dw, ic.pb - (ic.R - 1) * ic.dh};    // last base pixel, from (W-1, H-1)
   cuuint32_t estr[4] = {1, (cuuint32_t)ic.sw, (cuuint32_t)ic.sh, 1};
@@ -403,8 +404,9 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   if (kb_bytes != 128 && !(kb_bytes == 64 && ic.on)) return 1;
   if (ic.on) {
     // K runs over (filter row, filter column, channel); a K block never straddles two taps; B (the filters) is K-major
-    if (d.trans_a || !d.trans_b || d.batch != 1 || plan->promote || (ic.C * es) % kb_bytes || d.K != ic.R * ic.S * ic.C ||
-        d.M != ic.N * ic.Ho * ic.Wo)
+    // (the chunk-promotion kernel runs the three TF32 products over a tensor of pairs: K = 3 * R*S*C)
+    if (d.trans_a || !d.trans_b || d.batch != 1 || (ic.C * es) % kb_bytes || d.K != (plan->promote ? 3 : 1) * ic.R * ic.S * ic.C ||
+        d.M != ic.N * ic.Ho * ic.Wo || (plan->promote && ic.Cs != 2 * ic.C))
       return 1;
     const int up_w = ic.pr - (ic.S - 1) * ic.dw, up_h = ic.pb - (ic.R - 1) * ic.dh;
     if (ic.pl > 128 || ic.pt > 128 || up_w < -128 || up_w > 127 || up_h < -128 || up_h > 127 || ic.sw > 8 || ic.sh > 8 ||
@@ -461,12 +463,17 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.num_kb = (int)((d.K + u.kb_elems - 1) / u.kb_elems);
   u.a_stage_bytes = UMMA_BM * kb_bytes;
   u.b_stage_bytes = u.b_rows * kb_bytes;
+  // Chunk-promotion kernel with a tile of at most 128 columns: hi and lo of both operands share a stage (three stages of
+  // 64 KB still fit), so each operand block is loaded once for its two products.  SOFIE_B200_NO_FUSED3=1 keeps one product per stage.
+  u.fused3 = (plan->promote && (u.bn <= 128 || getenv("SOFIE_B200_FUSED3_ALL")) && !getenv("SOFIE_B200_NO_FUSED3")) ? 1 : 0;
+  if (u.fused3) { u.a_stage_bytes *= 2; u.b_stage_bytes *= 2; }
   u.im2col = ic.on;
   if (ic.on) {
     u.ic_wo = (int)ic.Wo; u.ic_pix = (int)(ic.Ho * ic.Wo);
     u.ic_sw = ic.sw; u.ic_sh = ic.sh; u.ic_pl = ic.pl; u.ic_pt = ic.pt;
     u.ic_dw = ic.dw; u.ic_dh = ic.dh; u.ic_s = ic.S;
     u.ic_cblocks = (int)(ic.C / u.kb_elems);
+    u.ic_c = (int)ic.C;
   }
   u.tmem_cols = 32;
   while (u.tmem_cols < 2u * u.bn) u.tmem_cols <<= 1;
@@ -514,6 +521,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
 
   const int ys = dtype_size(d.y_dtype);
   u.vec_ok = ((d.ldy * ys) % 16 == 0) && ((d.stride_y * ys) % 16 == 0);
+  if (plan->split_out && ((d.N * ys) % 16 != 0 || d.ldy != 2 * d.N || d.y_dtype != SOFIE_B200_F32 || !plan->promote)) return 1;
   u.status = plan->ctx->d_status;
 
   // Short last wave: split its tiles in two N halves (see decode_item).  Only when at least one full wave
@@ -602,6 +610,7 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
   if (rc) return rc;
   UmmaParams u = plan->up;
   u.ep = ep;
+  u.ep.split_out = plan->split_out;
   if (((uintptr_t)ep.Y % 16) != 0) u.vec_ok = 0;
   // Tensor map of Y for the epilogue's bulk stores: box = one 128-byte row segment x the 32 rows of an epilogue warp.
   u.y_tma = 0;
@@ -614,12 +623,13 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
     while (g > 1 && (u.bn / 32) / g < 2) g >>= 1;
     if (g < full) { u.ep.seg_chunks = g; seg_div = full / g; }
   }
-  if (u.vec_ok && !u.pair && !plan->promote && !getenv("SOFIE_B200_NO_TMA_STORE")) {
+  if (u.vec_ok && !u.pair && !getenv("SOFIE_B200_NO_TMA_STORE")) {
     const sofie_b200_gemm_desc &d = plan->desc;
     const int ys = dtype_size(d.y_dtype);
     if (ep.Y != plan->cached_y || seg_div != plan->cached_seg_div) {
       const uint64_t s2 = d.batch > 1 ? (uint64_t)d.stride_y * ys : (uint64_t)d.M * d.ldy * ys;
-      rc = encode_map(&plan->tm_y, d.y_dtype, ep.Y, (uint64_t)d.N, (uint64_t)d.M, (uint64_t)d.batch, (uint64_t)d.ldy * ys, s2,
+      // (a TF32-pair output is 2 N columns wide: the lo halves follow the hi halves)
+      rc = encode_map(&plan->tm_y, d.y_dtype, ep.Y, (uint64_t)(plan->split_out ? 2 * d.N : d.N), (uint64_t)d.M, (uint64_t)d.batch, (uint64_t)d.ldy * ys, s2,
                       (uint32_t)(128 / ys / seg_div), 32, 128 / seg_div);
       if (rc) return rc;
       plan->cached_y = ep.Y;

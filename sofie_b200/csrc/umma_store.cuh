@@ -83,9 +83,11 @@ __device__ __forceinline__ int out_elem_bytes(int y_dtype) {
 // but never stored).  Otherwise the chunk is stored directly and the function returns false.
 __device__ __forceinline__ bool store_chunk(const EpiParams &ep, const uint32_t (&raw)[32], long long b, long long row,
                                             int col0, int ncols, bool vec, uint32_t stage = 0, long long rows_total = 0,
-                                            int slot = 0) {
+                                            int slot = 0, int split_part = 0) {
   const bool full = ncols == 32;
-  const long long off = b * ep.stride_y + row * ep.ldy + col0;
+  // split_part (fp32 output as a TF32 pair, EpiParams::split_out): 1 stores hi = tf32(v) at the element's own column,
+  // 2 stores lo = tf32(v - hi) at column N + j; the caller makes both calls (and flushes at the matching address)
+  const long long off = b * ep.stride_y + row * ep.ldy + col0 + (split_part == 2 ? ep.ldy / 2 : 0);
   const bool staged = stage != 0 && vec && full;       // warp-uniform
   if (!staged && stage != 0 && row >= rows_total) return false;   // direct path: rows past the end store nothing
   const long long rr = (stage != 0 && row >= rows_total) ? rows_total - 1 : row;   // row whose per-row operands are read
@@ -226,6 +228,13 @@ __device__ __forceinline__ bool store_chunk(const EpiParams &ep, const uint32_t 
       break;
   }
   // 5. convert and store
+  if (split_part != 0) {
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      const float h = tf32_rn(v[c]);
+      v[c] = split_part == 1 ? h : tf32_rn(__fsub_rn(v[c], h));
+    }
+  }
   if (ep.y_dtype == SOFIE_B200_F32) {
     float *y = (float *)ep.Y + off;
     if (staged) {
@@ -408,11 +417,13 @@ __device__ __forceinline__ bool epi_values_fast(const EpiParams &ep, const uint3
 }
 
 // Second half of the fast path: residual, activation, conversion to the output type, staging.
+// split_part (fp32 output as a TF32 pair, EpiParams::split_out): 1 stages hi = tf32(v); 2, called right after 1 on the same
+// v, stages lo = tf32(v - hi) and skips the residual and the activation, which call 1 has already applied to v.
 template <int NC>
 __device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)[16 * NC], long long b, long long rr, int col0, uint32_t stage,
-                                                int slot) {
+                                                int slot, int split_part = 0) {
   constexpr int W = 32 * NC, P = 16 * NC;
-  if (ep.residual) {
+  if (ep.residual && split_part != 2) {
     const long long roff = b * ep.stride_r + rr * ep.ldr + col0;
     if (ep.residual_dtype == SOFIE_B200_BF16) {
       if (ep.residual_aligned) {
@@ -436,7 +447,7 @@ __device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)
       for (int u = 0; u < P; ++u) v[u] = fadd2(v[u], make_float2(r[2 * u], r[2 * u + 1]));
     }
   }
-  if (ep.act != SOFIE_B200_ACT_NONE) {
+  if (ep.act != SOFIE_B200_ACT_NONE && split_part != 2) {
     if (ep.act == SOFIE_B200_ACT_RELU) {
 #pragma unroll
       for (int u = 0; u < P; ++u) v[u] = make_float2(act_apply(v[u].x, SOFIE_B200_ACT_RELU, 0.f), act_apply(v[u].y, SOFIE_B200_ACT_RELU, 0.f));
@@ -470,7 +481,15 @@ __device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)
     for (int i = 0; i < NC; ++i) {
       uint32_t w[32];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) { w[2 * u] = __float_as_uint(v[16 * i + u].x); w[2 * u + 1] = __float_as_uint(v[16 * i + u].y); }
+      for (int u = 0; u < 16; ++u) {
+        float x = v[16 * i + u].x, y = v[16 * i + u].y;
+        if (split_part != 0) {
+          const float hx = tf32_rn(x), hy = tf32_rn(y);
+          x = split_part == 1 ? hx : tf32_rn(__fsub_rn(x, hx));
+          y = split_part == 1 ? hy : tf32_rn(__fsub_rn(y, hy));
+        }
+        w[2 * u] = __float_as_uint(x); w[2 * u + 1] = __float_as_uint(y);
+      }
       stage_units<8>(stage, w, slot + i);
     }
   } else {  // I8 / U8: ONNX rounding (half to even), zero point, saturate

@@ -358,6 +358,90 @@ def test_conv_implicit_int8(ctx, oracle, case):
     assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size}"
 
 
+def tf32_rn(x):
+    """x rounded to the nearest TF32 value (ties away from zero), as the library splits fp32 operands."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = np.where((b & 0x7F800000) >= 0x7F000000, b, b + np.uint32(0x1000)) & np.uint32(0xFFFFE000)
+    return r.view(np.float32)
+
+
+PAIR_CASES = {
+    # name: (N, C, H, W, K, R, S, pads, strides, dilations, y_layout)
+    "c32_3x3_pairs_out": (2, 32, 14, 12, 64, 3, 3, [1, 1, 1, 1], [1, 1], [1, 1], 2),
+    "c64_3x3_stride2_plain_out": (3, 64, 16, 18, 96, 3, 3, [1, 1, 1, 1], [2, 2], [1, 1], 1),
+    "c96_asymmetric_pairs_out": (2, 96, 11, 13, 40, 2, 3, [0, 2, 1, 1], [1, 2], [2, 1], 2),
+    "c64_many_tiles_pairs_out": (4, 64, 56, 56, 128, 3, 3, [1, 1, 1, 1], [1, 1], [1, 1], 2),
+}
+
+
+@pytest.mark.parametrize("case", list(PAIR_CASES))
+def test_conv_fp32_from_tf32_pairs(ctx, oracle, case):
+    """x_layout = 2: fp32 convolution at the fp32 bar whose input is a channels-last tensor of TF32 pairs ([N,H,W,2C]: hi
+    channels, then lo channels), read in place by the 3xTF32 contraction (no unfold, no workspace); y_layout = 2 writes
+    the same form for the next convolution."""
+    from sofie_b200.ops import make_epilogue
+    lib = ctx._lib
+    N, Ci, H, W, Co, R, S, pads, strides, dil, yl = PAIR_CASES[case]
+    rng = np.random.default_rng(len(case))
+    x = (rng.random((N, Ci, H, W), dtype=np.float32) * 2).astype(np.float32)   # same-sign data: the hard case for a truncating accumulator
+    w = (rng.standard_normal((Co, Ci, R, S)) * 0.1).astype(np.float32)
+    cs = rng.random(Co, dtype=np.float32) + 0.5
+    bias = rng.standard_normal(Co).astype(np.float32)
+    d = gr.conv_desc(dict(pads=pads, strides=strides, dil=dil, group=1), x.shape, w.shape, L.F32, L.F32)
+    ho, wo = C.c_int64(), C.c_int64()
+    assert lib.sofie_b200_conv_out_shape(C.byref(d), C.byref(ho), C.byref(wo)) == 0
+    want = oracle.conv(x, w, d, ho.value, wo.value, ep=oracle.epilogue(col_scale=cs, bias=bias, act=L.ACT_RELU))
+    d.x_layout, d.y_layout = 2, yl
+    xcl = np.ascontiguousarray(x.transpose(0, 2, 3, 1))
+    hi = tf32_rn(xcl)
+    pairs = np.concatenate([hi, tf32_rn(xcl - hi)], axis=3)
+    tx, tw = torch.from_numpy(pairs).to(DEV), torch.from_numpy(w).to(DEV)
+    h = C.c_void_p()
+    L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), tw.data_ptr(), C.byref(h)), "conv_plan_create")
+    assert lib.sofie_b200_conv_plan_kernel(h).decode() == "umma3x_im2col"
+    assert lib.sofie_b200_conv_workspace_bytes(h) == 0
+    y = torch.zeros((N, ho.value, wo.value, Co * (2 if yl == 2 else 1)), dtype=torch.float32, device=DEV)
+    ep, keep = make_epilogue(col_scale=torch.from_numpy(cs).to(DEV), bias=torch.from_numpy(bias).to(DEV), act=L.ACT_RELU)
+    L.check(lib.sofie_b200_conv_enqueue(h, tx.data_ptr(), y.data_ptr(), None, C.byref(ep)), "conv_enqueue")
+    ctx.sync()
+    lib.sofie_b200_conv_plan_destroy(h)
+    got = y.cpu().numpy()
+    if yl == 2:
+        ghi, glo = got[..., :Co], got[..., Co:]
+        assert np.array_equal(ghi, tf32_rn(ghi)) and np.array_equal(glo, tf32_rn(glo))   # both halves are TF32 values
+        assert np.all(np.abs(glo) <= np.abs(ghi) * 2.0 ** -10 + 1e-37)                    # lo is the rounding remainder of hi
+        got = ghi + glo
+    got = got.transpose(0, 3, 1, 2)
+    assert close_f32(got, want), np.abs(got - want).max()
+
+
+def test_conv_first_layer_writes_tf32_pairs(ctx, oracle):
+    """The 3-channel first layer (direct kernel) with y_layout = 2."""
+    from sofie_b200.ops import make_epilogue
+    lib = ctx._lib
+    N, H, W, Co = 3, 20, 18, 64
+    rng = np.random.default_rng(12)
+    x = rng.random((N, 3, H, W), dtype=np.float32)
+    w = (rng.standard_normal((Co, 3, 3, 3)) * 0.3).astype(np.float32)
+    bias = rng.standard_normal(Co).astype(np.float32)
+    d = gr.conv_desc(dict(pads=[1, 1, 1, 1], strides=[1, 1], dil=[1, 1], group=1), x.shape, w.shape, L.F32, L.F32)
+    want = oracle.conv(x, w, d, H, W, ep=oracle.epilogue(bias=bias, act=L.ACT_RELU))
+    d.y_layout = 2
+    tx, tw = torch.from_numpy(x).to(DEV), torch.from_numpy(w).to(DEV)
+    h = C.c_void_p()
+    L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), tw.data_ptr(), C.byref(h)), "conv_plan_create")
+    assert lib.sofie_b200_conv_plan_kernel(h).decode() == "direct"
+    y = torch.zeros((N, H, W, 2 * Co), dtype=torch.float32, device=DEV)
+    ep, keep = make_epilogue(bias=torch.from_numpy(bias).to(DEV), act=L.ACT_RELU)
+    L.check(lib.sofie_b200_conv_enqueue(h, tx.data_ptr(), y.data_ptr(), None, C.byref(ep)), "conv_enqueue")
+    ctx.sync()
+    lib.sofie_b200_conv_plan_destroy(h)
+    got = y.cpu().numpy()
+    ghi, glo = got[..., :Co], got[..., Co:]
+    assert np.array_equal(ghi, tf32_rn(ghi)) and np.array_equal(glo, tf32_rn(glo))
+    assert close_f32((ghi + glo).transpose(0, 3, 1, 2), want), np.abs((ghi + glo).transpose(0, 3, 1, 2) - want).max()
+
+
 def test_conv_implicit_tf32(ctx, oracle):
     """precise = 0 on fp32 channels-last tensors: single-pass TF32 through the same im2col-mode producer."""
     from sofie_b200.ops import make_epilogue
