@@ -463,9 +463,11 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.num_kb = (int)((d.K + u.kb_elems - 1) / u.kb_elems);
   u.a_stage_bytes = UMMA_BM * kb_bytes;
   u.b_stage_bytes = u.b_rows * kb_bytes;
-  // Chunk-promotion kernel with a tile of at most 128 columns: hi and lo of both operands share a stage (three stages of
-  // 64 KB still fit), so each operand block is loaded once for its two products.  SOFIE_B200_NO_FUSED3=1 keeps one product per stage.
-  u.fused3 = (plan->promote && (u.bn <= 128 || getenv("SOFIE_B200_FUSED3_ALL")) && !getenv("SOFIE_B200_NO_FUSED3")) ? 1 : 0;
+  // Chunk-promotion kernel: hi and lo of both operands share a stage (64 KB for a 128-column tile: three stages; 96 KB
+  // for 256 columns: two), so each operand block is loaded once for its two products: 4 loads per 12 MMAs instead of 6.
+  // Measured faster in every shape, two-stage ring included (8192^3: 6.6 -> 6.05 ms).  SOFIE_B200_NO_FUSED3=1 keeps one
+  // product per stage.
+  u.fused3 = (plan->promote && !getenv("SOFIE_B200_NO_FUSED3")) ? 1 : 0;
   if (u.fused3) { u.a_stage_bytes *= 2; u.b_stage_bytes *= 2; }
   u.im2col = ic.on;
   if (ic.on) {

@@ -23,6 +23,60 @@ using namespace ptx;
 constexpr int PROMOTE_THREADS = 320;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: epilogue
 constexpr int PROMOTE_HALF_MAX = 128; // accumulator columns (= fp32 sum registers) per epilogue thread
 
+// Final step of a tile for one epilogue warp: the fused epilogue over this thread's `half_cols` sums (row `row`, columns
+// col0 ...), staged per 32-column chunk and written by bulk tensor stores (or coalesced vector stores without a map of Y).
+__device__ __noinline__ void promote_finish(const UmmaParams &p, const CUtensorMap *tm_y, const float *sum, int b, int row, int col0, int half_cols,
+                                            uint32_t my_stage) {
+  const int lane = threadIdx.x & 31;
+  bool store_pending = false;   // a bulk tensor store of the staging buffer may still be reading it
+  auto buffer_free = [&]() {
+    if (store_pending) {
+      if (lane == 0) bulk_wait_read_all();
+      __syncwarp();
+      store_pending = false;
+    }
+  };
+  for (int c = 0; c < half_cols; c += 32) {
+    const int col = col0 + c;
+    if (col >= p.N) break;   // warp-uniform
+    uint32_t raw[32];
+#pragma unroll
+    for (int u = 0; u < 32; ++u) raw[u] = __float_as_uint(sum[c + u]);
+    const int parts = p.ep.split_out ? 2 : 1;   // a TF32 pair: the hi pass, then the lo pass N columns further
+    const int rows_valid = (int)max(0LL, min(32LL, (long long)p.M - (row - lane)));
+    const long long ldy_bytes = p.ep.ldy * out_elem_bytes(p.ep.y_dtype);
+    if (p.vec_ok && p.ep.fast && p.N - col >= 32 && rows_valid > 0 && p.ep.y_dtype == SOFIE_B200_F32) {
+      // the branch-light epilogue of the plain kernel (same arithmetic, step for step)
+      const long long rr = row < p.M ? row : (long long)p.M - 1;
+      float2 v[16];
+      epi_values_fast<false, 1>(p.ep, raw, v, rr, col, my_stage, 0);
+      for (int part = 0; part < parts; ++part) {
+        buffer_free();
+        epi_finish_fast<1>(p.ep, v, b, rr, col, my_stage, 0, p.ep.split_out ? part + 1 : 0);
+        if (p.y_tma) {   // the 32 rows x 128 bytes leave as one bulk tensor store (rows past the end are clipped)
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(tm_y, my_stage, col + part * p.N, row - lane, b);
+            bulk_commit_group();
+          }
+          store_pending = true;
+        } else {
+          flush_staged(my_stage, y_address(p.ep, b, row - lane, col + part * p.N), ldy_bytes, rows_valid, 8);
+        }
+      }
+    } else {
+      buffer_free();
+      for (int part = 0; part < parts; ++part) {
+        const int sp = p.ep.split_out ? part + 1 : 0;
+        if (store_chunk(p.ep, raw, b, row, col, min(32, p.N - col), p.vec_ok != 0, my_stage, p.M, 0, sp))
+          flush_staged(my_stage, y_address(p.ep, b, row - lane, col + part * p.N), ldy_bytes, rows_valid, 2 * out_elem_bytes(p.ep.y_dtype));
+      }
+    }
+  }
+  buffer_free();
+}
+
 __global__ void __launch_bounds__(PROMOTE_THREADS, 1)
 umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                          const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ UmmaParams p) {
@@ -270,57 +324,13 @@ umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
       }
       if (!ok) break;
       ROLE_SECTION_BEGIN();
-      const int row = m0 + quad * 32 + lane;
-      bool store_pending = false;   // a bulk tensor store of the staging buffer may still be reading it
-      auto buffer_free = [&]() {
-        if (store_pending) {
-          if (lane == 0) bulk_wait_read_all();
-          __syncwarp();
-          store_pending = false;
-        }
-      };
+      // The sums go through local memory to a function of its own: it runs once per tile, and kept inline its registers
+      // (epilogue operands, staging) pushed part of `sum` out of the register file in the chunk loop above, which runs
+      // once per 8 K blocks.
+      float out[PROMOTE_HALF_MAX];
 #pragma unroll
-      for (int c = 0; c < PROMOTE_HALF_MAX; c += 32) {
-        const int col = n0 + col_base + c;
-        if (c < half_cols && col < p.N) {   // warp-uniform
-          uint32_t raw[32];
-#pragma unroll
-          for (int u = 0; u < 32; ++u) raw[u] = __float_as_uint(sum[c + u]);
-          const uint32_t my_stage = epi_stage + (uint32_t)(warp - 2) * 4096u;
-          const int parts = p.ep.split_out ? 2 : 1;   // a TF32 pair: the hi pass, then the lo pass N columns further
-          const int rows_valid = (int)max(0LL, min(32LL, (long long)p.M - (row - lane)));
-          const long long ldy_bytes = p.ep.ldy * out_elem_bytes(p.ep.y_dtype);
-          if (p.vec_ok && p.ep.fast && p.N - col >= 32 && rows_valid > 0 && p.ep.y_dtype == SOFIE_B200_F32) {
-            // the branch-light epilogue of the plain kernel (same arithmetic, step for step)
-            const long long rr = row < p.M ? row : (long long)p.M - 1;
-            float2 v[16];
-            epi_values_fast<false, 1>(p.ep, raw, v, rr, col, my_stage, 0);
-            for (int part = 0; part < parts; ++part) {
-              buffer_free();
-              epi_finish_fast<1>(p.ep, v, b, rr, col, my_stage, 0, p.ep.split_out ? part + 1 : 0);
-              if (p.y_tma) {   // the 32 rows x 128 bytes leave as one bulk tensor store (rows past the end are clipped)
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) {
-                  tma_store_3d(&tm_y, my_stage, col + part * p.N, row - lane, b);
-                  bulk_commit_group();
-                }
-                store_pending = true;
-              } else {
-                flush_staged(my_stage, y_address(p.ep, b, row - lane, col + part * p.N), ldy_bytes, rows_valid, 8);
-              }
-            }
-          } else {
-            buffer_free();
-            for (int part = 0; part < parts; ++part) {
-              const int sp = p.ep.split_out ? part + 1 : 0;
-              if (store_chunk(p.ep, raw, b, row, col, min(32, p.N - col), p.vec_ok != 0, my_stage, p.M, 0, sp))
-                flush_staged(my_stage, y_address(p.ep, b, row - lane, col + part * p.N), ldy_bytes, rows_valid, 2 * out_elem_bytes(p.ep.y_dtype));
-            }
-          }
-        }
-      }
-      buffer_free();
+      for (int c = 0; c < PROMOTE_HALF_MAX; ++c) out[c] = sum[c];
+      promote_finish(p, &tm_y, out, b, m0 + quad * 32 + lane, n0 + col_base, half_cols, epi_stage + (uint32_t)(warp - 2) * 4096u);
       ROLE_SECTION_END(c_final);
     }
     if (threadIdx.x == 64) { ROLE_REPORT("[cta %d] promote epilogue: total %lld, waiting for a chunk %lld, final epilogue + stores %lld\n", blockIdx.x, clock64() - t_begin, w_tfull, c_final); }
