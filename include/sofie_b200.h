@@ -167,6 +167,12 @@ typedef struct sofie_b200_conv_desc {
                                  /* fill the 128 accumulator rows.  x_layout = 1 needs C/groups to be a whole number */
                                  /* of 16-byte vectors.  Both = 1 selects the implicit convolution where it applies  */
                                  /* (sofie_b200_conv_plan_kernel).                                                  */
+                                 /* 2: channels-last TF32 pairs, [N,H,W,2C] fp32: for every pixel the C values       */
+                                 /* hi = tf32(x) and then the C values lo = tf32(x - hi) (tf32: rounded to a 10-bit  */
+                                 /* mantissa).  For chains of F32 convolutions at precise = 1: the 3xTF32 contraction */
+                                 /* reads such a tensor in place and writes one for the next layer.  x_layout = 2:   */
+                                 /* one group, C a multiple of 32, y_layout 1 or 2.  y_layout = 2: K a multiple of   */
+                                 /* 4, and x_layout = 2 or the 3-channel first layer.                                */
 } sofie_b200_conv_desc;
 
 typedef struct sofie_b200_ctx sofie_b200_ctx;
@@ -252,7 +258,8 @@ int64_t sofie_b200_conv_workspace_bytes(const sofie_b200_conv_plan *plan);
  *   "direct"       the 3-channel 3x3 first layer (NCHW input, one group) on the CUDA cores;
  *   "umma_im2col"  implicit convolution: x_layout = y_layout = 1, one group, I8 input (zero point 0, or no padding) or
  *                  F32 at precise = 0, C * element size a multiple of 64 bytes -- the tensor-core contraction reads X
- *                  itself through im2col-mode TMA loads. */
+ *                  itself through im2col-mode TMA loads;
+ *   "umma3x_im2col" the same for F32 at fp32 accuracy: x_layout = 2 (TF32 pairs), three TF32 products summed in fp32. */
 const char *sofie_b200_conv_plan_kernel(const sofie_b200_conv_plan *plan);
 /* Enqueues Y = epilogue(conv(X, W)); columns of the epilogue are output channels. */
 int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, void *workspace,
