@@ -399,6 +399,10 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
     unsigned char *srow = stage + (size_t)lane * row_bytes;
     if (ys == 1) {
       const int lo = ep.y_dtype == SOFIE_B200_I8 ? -128 : 0, hi = ep.y_dtype == SOFIE_B200_I8 ? 127 : 255;
+      // sat(rint(v / out_scale) + zp) as in quantize_i(), with the clamp first (the bounds are integers and rounding is
+      // monotonic) and the rounding as an addition of 1.5 * 2^23: no quarter-rate conversion instructions
+      const float flo = (float)(lo - ep.out_zp), fhi = (float)(hi - ep.out_zp), oscale = ep.out_scale;
+      const int unmagic = ep.out_zp - 0x4B400000;
       for (int k0 = 0; k0 < filters; k0 += 16) {
         uint32_t w[4];
 #pragma unroll
@@ -407,7 +411,10 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int k = k0 + 4 * u + e;
-            word |= ((uint32_t)quantize_i(value_of(k, 0, gp, k), ep.out_scale, ep.out_zp, lo, hi) & 0xffu) << (8 * e);
+            float v = value_of(k, 0, gp, k);
+            if (oscale != 1.f) v = __fdiv_rn(v, oscale);
+            const int q = __float_as_int(__fadd_rn(fminf(fmaxf(v, flo), fhi), 12582912.f)) + unmagic;
+            word |= ((uint32_t)q & 0xffu) << (8 * e);
           }
           w[u] = word;
         }
