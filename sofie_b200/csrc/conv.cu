@@ -249,6 +249,16 @@ template <typename T> struct DirectAcc;
 template <> struct DirectAcc<int8_t> { using W = int; static constexpr int NW = 8; static constexpr int KW = 32; };
 template <> struct DirectAcc<float> { using W = float; static constexpr int NW = 28; static constexpr int KW = 28; };
 
+// Activation chosen at compile time for the direct kernel's inner loops (0 none, 1 Relu, 2 whatever ep.act says): a switch
+// on ep.act per output costs several branches, and the loops are issue-bound.
+template <int ACT>
+__device__ __forceinline__ float direct_act(float v, const EpiParams &ep) {
+  if (ACT == 0) return v;
+  if (ACT == 1) return v > 0.f ? v : 0.f;
+  return act_apply(v, ep.act, ep.act_alpha);
+}
+template <int V> struct IntTag { static constexpr int value = V; };
+
 template <typename T, bool NHWC_OUT>
 __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ x, const typename DirectAcc<T>::W *__restrict__ wq,
                                                           sofie_b200_conv_desc d, int Ho, int Wo, EpiParams ep) {
@@ -261,15 +271,15 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
   // per-channel epilogue operands, read once per CTA: scale (or 1), additive fp32 bias (or -0: x + -0 = x bit for bit),
   // int32 bias (or 0).  In either output layout exactly one of row_scale / col_scale and of the ROW / COL bias modes
   // carries the per-channel vector, indexed by the channel.
-  float *sc = reinterpret_cast<float *>(ws + (size_t)filters * NW);
-  float *bf = sc + filters;
-  int *bi = reinterpret_cast<int *>(bf + filters);
+  // One 16-byte record per channel {scale, fp32 bias, int32 bias (as bits), unused}: one shared-memory load per output.
+  float4 *prm = reinterpret_cast<float4 *>(ws + (size_t)filters * NW);
   for (int k = threadIdx.x; k < filters; k += blockDim.x) {
-    sc[k] = ep.row_scale ? ep.row_scale[k] : (ep.col_scale ? ep.col_scale[k] : 1.f);
     const int m = ep.bias_mode;
-    bf[k] = (m == SOFIE_B200_BIAS_COL_F32 || m == SOFIE_B200_BIAS_ROW_F32) ? ((const float *)ep.bias)[k]
-                                                                               : (m == SOFIE_B200_BIAS_SCALAR_F32 ? ((const float *)ep.bias)[0] : -0.f);
-    bi[k] = (m == SOFIE_B200_BIAS_COL_I32 || m == SOFIE_B200_BIAS_ROW_I32) ? ((const int *)ep.bias)[k] : 0;
+    const float sc = ep.row_scale ? ep.row_scale[k] : (ep.col_scale ? ep.col_scale[k] : 1.f);
+    const float bf = (m == SOFIE_B200_BIAS_COL_F32 || m == SOFIE_B200_BIAS_ROW_F32) ? ((const float *)ep.bias)[k]
+                                                                                     : (m == SOFIE_B200_BIAS_SCALAR_F32 ? ((const float *)ep.bias)[0] : -0.f);
+    const int bi = (m == SOFIE_B200_BIAS_COL_I32 || m == SOFIE_B200_BIAS_ROW_I32) ? ((const int *)ep.bias)[k] : 0;
+    prm[k] = make_float4(sc, bf, __int_as_float(bi), 0.f);
   }
   __syncthreads();
   // Without a residual or a full-matrix bias the epilogue of output (pixel, channel k) is this, step for step what
@@ -326,12 +336,23 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
       return __float_as_uint(acc);
     }
   };
-  auto value_of = [&](int k, long long eb, long long ei, long long ej) -> float {
+  // the lean epilogue with the activation fixed at compile time (tag: IntTag<0|1|2>, see direct_act)
+  auto lean_value = [&](int k, auto tag) -> float {
     const uint32_t raw = raw_of(k);
-    if (!lean) return epi_value(ep, raw, eb, ei, ej);
-    float v = sizeof(T) == 1 ? (float)((int)raw + bi[k]) : __uint_as_float(raw);
-    v = __fadd_rn(__fmul_rn(__fmul_rn(v, sc[k]), alpha), bf[k]);
-    return act_apply(v, ep.act, ep.act_alpha);
+    const float4 pr = prm[k];
+    float v = sizeof(T) == 1 ? (float)((int)raw + __float_as_int(pr.z)) : __uint_as_float(raw);
+    v = __fadd_rn(__fmul_rn(__fmul_rn(v, pr.x), alpha), pr.y);
+    return direct_act<decltype(tag)::value>(v, ep);
+  };
+  auto value_of = [&](int k, long long eb, long long ei, long long ej) -> float {
+    if (!lean) return epi_value(ep, raw_of(k), eb, ei, ej);
+    return lean_value(k, IntTag<2>{});
+  };
+  // runs body(tag) with the tag of ep.act
+  auto with_act = [&](auto body) {
+    if (ep.act == SOFIE_B200_ACT_RELU) body(IntTag<1>{});
+    else if (ep.act == SOFIE_B200_ACT_NONE) body(IntTag<0>{});
+    else body(IntTag<2>{});
   };
   if constexpr (!NHWC_OUT) {
     if (valid) {
@@ -368,21 +389,25 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
       // TF32 pairs: 32 channels at a time.  A pixel's staging row is [32 hi | 32 lo] floats; the warp then writes each
       // 128-byte run to its place (hi at channel k, lo at channel filters + k of the pixel's 2 * filters floats).
       constexpr int KC = 32;
-      unsigned char *st = dsm + (size_t)filters * (NW * sizeof(W) + 12) + (size_t)warp * 32 * KC * 8;
+      unsigned char *st = dsm + (size_t)filters * (NW * sizeof(W) + 16) + (size_t)warp * 32 * KC * 8;
       const long long gp0 = gp_raw - lane;
       for (int kc0 = 0; kc0 < filters; kc0 += KC) {
         const int nk = min(KC, filters - kc0);
-        for (int k0 = 0; k0 < nk; k0 += 4) {
-          float v[4], h[4];
+        auto fill = [&](auto tag) {
+#pragma unroll 1
+          for (int k0 = 0; k0 < nk; k0 += 4) {
+            float v[4], h[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            v[e] = value_of(kc0 + k0 + e, 0, gp, kc0 + k0 + e);
-            h[e] = tf32_rn(v[e]);
-            v[e] = tf32_rn(__fsub_rn(v[e], h[e]));
+            for (int e = 0; e < 4; ++e) {
+              v[e] = lean ? lean_value(kc0 + k0 + e, tag) : value_of(kc0 + k0 + e, 0, gp, kc0 + k0 + e);
+              h[e] = tf32_rn(v[e]);
+              v[e] = tf32_rn(__fsub_rn(v[e], h[e]));
+            }
+            *reinterpret_cast<float4 *>(st + (size_t)lane * KC * 8 + (size_t)k0 * 4) = make_float4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<float4 *>(st + (size_t)lane * KC * 8 + (size_t)(KC + k0) * 4) = make_float4(v[0], v[1], v[2], v[3]);
           }
-          *reinterpret_cast<float4 *>(st + (size_t)lane * KC * 8 + (size_t)k0 * 4) = make_float4(h[0], h[1], h[2], h[3]);
-          *reinterpret_cast<float4 *>(st + (size_t)lane * KC * 8 + (size_t)(KC + k0) * 4) = make_float4(v[0], v[1], v[2], v[3]);
-        }
+        };
+        with_act(fill);
         __syncwarp();
         const int per_run = nk / 4;   // 16-byte pieces per run
         for (int idx = lane; idx < 64 * per_run; idx += 32) {
@@ -395,7 +420,7 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
       }
       return;
     }
-    unsigned char *stage = dsm + (size_t)filters * (NW * sizeof(W) + 12) + (size_t)warp * 32 * row_bytes;
+    unsigned char *stage = dsm + (size_t)filters * (NW * sizeof(W) + 16) + (size_t)warp * 32 * row_bytes;
     unsigned char *srow = stage + (size_t)lane * row_bytes;
     if (ys == 1) {
       const int lo = ep.y_dtype == SOFIE_B200_I8 ? -128 : 0, hi = ep.y_dtype == SOFIE_B200_I8 ? 127 : 255;
@@ -403,23 +428,27 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
       // monotonic) and the rounding as an addition of 1.5 * 2^23: no quarter-rate conversion instructions
       const float flo = (float)(lo - ep.out_zp), fhi = (float)(hi - ep.out_zp), oscale = ep.out_scale;
       const int unmagic = ep.out_zp - 0x4B400000;
-      for (int k0 = 0; k0 < filters; k0 += 16) {
-        uint32_t w[4];
+      auto fill = [&](auto tag) {
+        const bool plain = lean && oscale == 1.f;   // no division, no general epilogue
+#pragma unroll 1
+        for (int k0 = 0; k0 < filters; k0 += 16) {
+          uint32_t w[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint32_t word = 0;
+          for (int u = 0; u < 4; ++u) {
+            int q[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int k = k0 + 4 * u + e;
-            float v = value_of(k, 0, gp, k);
-            if (oscale != 1.f) v = __fdiv_rn(v, oscale);
-            const int q = __float_as_int(__fadd_rn(fminf(fmaxf(v, flo), fhi), 12582912.f)) + unmagic;
-            word |= ((uint32_t)q & 0xffu) << (8 * e);
+            for (int e = 0; e < 4; ++e) {
+              const int k = k0 + 4 * u + e;
+              float v = plain ? lean_value(k, tag) : value_of(k, 0, gp, k);
+              if (!plain && oscale != 1.f) v = __fdiv_rn(v, oscale);
+              q[e] = __float_as_int(__fadd_rn(fminf(fmaxf(v, flo), fhi), 12582912.f)) + unmagic;
+            }
+            w[u] = __byte_perm(__byte_perm((uint32_t)q[0], (uint32_t)q[1], 0x0040), __byte_perm((uint32_t)q[2], (uint32_t)q[3], 0x0040), 0x5410);
           }
-          w[u] = word;
+          *reinterpret_cast<uint4 *>(srow + k0) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        *reinterpret_cast<uint4 *>(srow + k0) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
+      };
+      with_act(fill);
     } else if (ys == 2) {
       for (int k0 = 0; k0 < filters; k0 += 8) {
         uint32_t w[4];
@@ -748,7 +777,7 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
     // channels-last output: 128 threads and a staging block of 32 pixels x K channels per warp behind the weights
     const int threads = plan->pix_rows ? 128 : 256;
     const unsigned grid = (unsigned)((total + threads - 1) / threads);
-    const size_t wsm = (size_t)d.K * ((d.x_dtype == SOFIE_B200_F32 ? 28 * sizeof(float) : 8 * sizeof(int)) + 12);   // weights + scale, bias, int bias
+    const size_t wsm = (size_t)d.K * ((d.x_dtype == SOFIE_B200_F32 ? 28 * sizeof(float) : 8 * sizeof(int)) + 16);   // weights + {scale, bias, int bias, -}
     const size_t sm = wsm + (plan->pix_rows ? (plan->pair_out ? (size_t)(threads / 32) * 32 * 32 * 8   // pairs: 32 channels at a time
                                                                  : (size_t)(threads / 32) * 32 * d.K * dtype_size(d.y_dtype)) : 0);
     epi.split_out = plan->pair_out;
