@@ -330,9 +330,17 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
       acc = __dp4a(xin[4], w1.x, acc); acc = __dp4a(xin[5], w1.y, acc); acc = __dp4a(xin[6], w1.z, acc);
       return (uint32_t)acc;   // the eighth word is padding
     } else {
+      // seven 16-byte loads (a filter's 28 floats are 16-byte aligned), the 27 FMAs in the order of the K index
+      const float4 *w4 = reinterpret_cast<const float4 *>(wk);
       float acc = 0.f;
 #pragma unroll
-      for (int i = 0; i < 27; ++i) acc = __fmaf_rn(xin[i], wk[i], acc);
+      for (int i = 0; i < 7; ++i) {
+        const float4 q = w4[i];
+        acc = __fmaf_rn(xin[4 * i], q.x, acc);
+        acc = __fmaf_rn(xin[4 * i + 1], q.y, acc);
+        acc = __fmaf_rn(xin[4 * i + 2], q.z, acc);
+        if (i < 6) acc = __fmaf_rn(xin[4 * i + 3], q.w, acc);
+      }
       return __float_as_uint(acc);
     }
   };
@@ -389,7 +397,8 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
       // TF32 pairs: 32 channels at a time.  A pixel's staging row is [32 hi | 32 lo] floats; the warp then writes each
       // 128-byte run to its place (hi at channel k, lo at channel filters + k of the pixel's 2 * filters floats).
       constexpr int KC = 32;
-      unsigned char *st = dsm + (size_t)filters * (NW * sizeof(W) + 16) + (size_t)warp * 32 * KC * 8;
+      constexpr int PITCH = KC * 8 + 16;   // 16 bytes of padding: lanes 256 bytes apart would all write the same banks
+      unsigned char *st = dsm + (size_t)filters * (NW * sizeof(W) + 16) + (size_t)warp * 32 * PITCH;
       const long long gp0 = gp_raw - lane;
       for (int kc0 = 0; kc0 < filters; kc0 += KC) {
         const int nk = min(KC, filters - kc0);
@@ -403,8 +412,8 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
               h[e] = tf32_rn(v[e]);
               v[e] = tf32_rn(__fsub_rn(v[e], h[e]));
             }
-            *reinterpret_cast<float4 *>(st + (size_t)lane * KC * 8 + (size_t)k0 * 4) = make_float4(h[0], h[1], h[2], h[3]);
-            *reinterpret_cast<float4 *>(st + (size_t)lane * KC * 8 + (size_t)(KC + k0) * 4) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4 *>(st + (size_t)lane * PITCH + (size_t)k0 * 4) = make_float4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<float4 *>(st + (size_t)lane * PITCH + (size_t)(KC + k0) * 4) = make_float4(v[0], v[1], v[2], v[3]);
           }
         };
         with_act(fill);
@@ -414,14 +423,15 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
           const int run = idx / per_run, u = idx - run * per_run, px = run >> 1, which = run & 1;
           if (gp0 + px < total)
             *reinterpret_cast<uint4 *>((unsigned char *)ep.Y + (gp0 + px) * row_bytes + (size_t)(which * filters + kc0) * 4 + (size_t)u * 16) =
-                *reinterpret_cast<const uint4 *>(st + (size_t)px * KC * 8 + (size_t)which * KC * 4 + (size_t)u * 16);
+                *reinterpret_cast<const uint4 *>(st + (size_t)px * PITCH + (size_t)which * KC * 4 + (size_t)u * 16);
         }
         __syncwarp();
       }
       return;
     }
-    unsigned char *stage = dsm + (size_t)filters * (NW * sizeof(W) + 16) + (size_t)warp * 32 * row_bytes;
-    unsigned char *srow = stage + (size_t)lane * row_bytes;
+    const int pitch = row_bytes + 16;   // padded staging rows: a power-of-two pitch puts every lane's store on the same banks
+    unsigned char *stage = dsm + (size_t)filters * (NW * sizeof(W) + 16) + (size_t)warp * 32 * pitch;
+    unsigned char *srow = stage + (size_t)lane * pitch;
     if (ys == 1) {
       const int lo = ep.y_dtype == SOFIE_B200_I8 ? -128 : 0, hi = ep.y_dtype == SOFIE_B200_I8 ? 127 : 255;
       // sat(rint(v / out_scale) + zp) as in quantize_i(), with the clamp first (the bounds are integers and rounding is
@@ -472,8 +482,10 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(const T *__restrict__ 
     const long long left = total - gp0;
     const long long bytes_valid = (left >= 32 ? 32 : (left > 0 ? left : 0)) * row_bytes;
     unsigned char *ydst = (unsigned char *)ep.Y + gp0 * row_bytes;
-    for (long long off = (long long)lane * 16; off < bytes_valid; off += 512)
-      *reinterpret_cast<uint4 *>(ydst + off) = *reinterpret_cast<const uint4 *>(stage + off);
+    for (long long off = (long long)lane * 16; off < bytes_valid; off += 512) {
+      const int r = (int)(off / row_bytes);
+      *reinterpret_cast<uint4 *>(ydst + off) = *reinterpret_cast<const uint4 *>(stage + (size_t)r * pitch + (off - (long long)r * row_bytes));
+    }
   }
 }
 
@@ -778,8 +790,8 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
     const int threads = plan->pix_rows ? 128 : 256;
     const unsigned grid = (unsigned)((total + threads - 1) / threads);
     const size_t wsm = (size_t)d.K * ((d.x_dtype == SOFIE_B200_F32 ? 28 * sizeof(float) : 8 * sizeof(int)) + 16);   // weights + {scale, bias, int bias, -}
-    const size_t sm = wsm + (plan->pix_rows ? (plan->pair_out ? (size_t)(threads / 32) * 32 * 32 * 8   // pairs: 32 channels at a time
-                                                                 : (size_t)(threads / 32) * 32 * d.K * dtype_size(d.y_dtype)) : 0);
+    const size_t sm = wsm + (plan->pix_rows ? (plan->pair_out ? (size_t)(threads / 32) * 32 * (32 * 8 + 16)   // pairs: 32 channels at a time
+                                                                 : (size_t)(threads / 32) * 32 * (d.K * dtype_size(d.y_dtype) + 16)) : 0);
     epi.split_out = plan->pair_out;
     if (d.x_dtype == SOFIE_B200_F32) {
       if (plan->pix_rows) {
