@@ -645,3 +645,38 @@ def test_plans_of_different_sizes_coexist(ctx, oracle):
     ctx.sync()
     assert torch.equal(y.cpu(), a.cpu().int() @ b.cpu().int().T)
     big.close(); small.close()
+
+
+def test_conv_layout_rules_and_empty_batch(ctx):
+    """Layout combinations the header rules out are refused at plan creation; an empty batch enqueues nothing."""
+    lib = ctx._lib
+    w64 = torch.zeros((64, 64, 3, 3), dtype=torch.float32, device=DEV)
+    w48 = torch.zeros((64, 48, 3, 3), dtype=torch.float32, device=DEV)
+    w8 = torch.zeros((64, 64, 3, 3), dtype=torch.int8, device=DEV)
+
+    def create(w, xshape, x_dtype, y_dtype, xl, yl, groups=1, precise=1):
+        d = gr.conv_desc(dict(pads=[1, 1, 1, 1], strides=[1, 1], dil=[1, 1], group=groups), xshape, tuple(w.shape), x_dtype, y_dtype)
+        d.x_layout, d.y_layout, d.precise = xl, yl, precise
+        h = C.c_void_p()
+        rc = lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), w.data_ptr(), C.byref(h))
+        return rc, h
+
+    for args in [
+        (w48, (2, 48, 8, 8), L.F32, L.F32, 2, 1),        # pairs need C % 32 == 0
+        (w64, (2, 64, 8, 8), L.F32, L.F32, 2, 0),        # pairs in, NCHW out
+        (w64, (2, 64, 8, 8), L.F32, L.F32, 1, 2),        # pairs out from a plain channels-last input
+        (w8, (2, 64, 8, 8), L.I8, L.I8, 2, 2),           # pairs are an fp32 format
+        (w64, (2, 64, 8, 8), L.F32, L.F32, 2, 2, 1, 0),  # ... at precise = 1 only
+        (w64, (2, 64, 8, 8), L.F32, L.F32, 3, 0),        # unknown layout
+    ]:
+        rc, h = create(*args)
+        assert rc == L.ERR_INVALID, (args[1:], rc)
+        assert h.value is None
+    # an empty batch: the plan is created, the enqueue is a no-op
+    n0 = ctx.launches
+    rc, h = create(w8, (0, 64, 8, 8), L.I8, L.I8, 1, 1)
+    assert rc == 0
+    created = ctx.launches - n0        # the filter re-layout at plan creation
+    assert lib.sofie_b200_conv_enqueue(h, None, None, None, None) == 0
+    assert ctx.launches - n0 == created
+    lib.sofie_b200_conv_plan_destroy(h)
