@@ -530,40 +530,61 @@ def run_encoder(args, w) -> None:
     rep = replicas.init_from_env("nccl")
     torch.cuda.set_device(rep.local_rank)
     dev = f"cuda:{rep.local_rank}"
-    ctx = Context(rep.local_rank)
+    # --cuda-graph: the step is captured once per input buffer on a side stream (an enqueue is nothing but kernel
+    # launches on the context's stream) and the timed loop replays the graphs
+    side = torch.cuda.Stream(device=dev) if args.cuda_graph else torch.cuda.current_stream(dev)
+    ctx = Context(rep.local_rank, stream=side)
     enc = be.EncoderB200(ctx, weights, w.batch, w.seq, w.d_model, w.heads, w.ffn, dev)
     m = w.batch * w.seq
     xs = [torch.randn(m, w.d_model, device=dev).to(torch.bfloat16) for _ in range(3)]   # activations per step: ~1.5 GB > L2
+    torch.cuda.synchronize()
     for i in range(max(3, args.warmup)):
         enc(xs[i % 3])
     ctx.sync()
+    step = lambda i: enc(xs[i % 3])
+    per_step = 0
+    if args.cuda_graph:
+        config["cuda_graph"] = True
+        graphs = []
+        for x in xs:
+            g, c0 = torch.cuda.CUDAGraph(), ctx.launches
+            with torch.cuda.graph(g, stream=side):
+                enc(x)
+            per_step = ctx.launches - c0
+            graphs.append(g)
+        step = lambda i: graphs[i % 3].replay()
     sampler = ClockSampler(rep.local_rank)
     replicas.barrier(rep)
     torch.cuda.synchronize()
     l0 = ctx.launches
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        enc(xs[i % 3])
-    e1.record()
+    with torch.cuda.stream(side):
+        if args.cuda_graph:
+            for i in range(3):
+                step(i)
+        e0.record()
+        for i in range(args.steps):
+            step(i)
+        e1.record()
     torch.cuda.synchronize()
     ctx.sync()
     clocks = sampler.stop()
     ms_local = e0.elapsed_time(e1)
     ms = replicas.max_over_ranks(rep, ms_local)
-    launches = ctx.launches - l0
+    launches = per_step * args.steps if args.cuda_graph else ctx.launches - l0
     value = rep.world * w.batch * args.steps / (ms * 1e-3)
     # end to end: tokens from pinned host memory in, final activations back out, every step
     hx = xs[0].cpu().pin_memory()
     hy = torch.empty_like(hx).pin_memory()
     e2e_steps = max(3, min(args.steps, 10))
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        xs[0].copy_(hx, non_blocking=True)
-        y = enc(xs[0])
-        hy.copy_(y, non_blocking=True)
-        torch.cuda.synchronize()
+    with torch.cuda.stream(side):   # the copies travel on the stream the step runs on
+        for _ in range(e2e_steps):
+            xs[0].copy_(hx, non_blocking=True)
+            y = enc(xs[0])
+            hy.copy_(y, non_blocking=True)
+            torch.cuda.synchronize()
     t_e2e = replicas.max_over_ranks(rep, time.perf_counter() - t0)
     if rep.is_root:
         peaks = measured_peaks()
@@ -710,6 +731,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="qlinear_matmul_4096", choices=sorted(WORKLOADS))
+    ap.add_argument("--cuda-graph", action="store_true", help="transformer_encoder_* only: replay the step from a CUDA graph")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]()
     if isinstance(w, RowOp):

@@ -71,6 +71,44 @@ def test_transformer_encoder_matches_checker(b200_lib, oracle_lib, fused):
     ctx.close()
 
 
+def test_encoder_step_replays_from_a_cuda_graph(b200_lib):
+    """Every enqueue of a step is a plain kernel launch on the context's stream (tensor maps travel by value in the
+    launch parameters, no allocation, no synchronisation), so a step can be captured once into a CUDA graph and
+    replayed: same bits as the eager step, one graph launch instead of 14 kernel launches."""
+    import bench_encoder as be
+    from sofie_b200.ops import Context
+    rng = np.random.default_rng(9)
+    weights = be.make_weights(rng, LAYERS, D_MODEL, FFN)
+    x0 = be.f32_to_bf16_bits(rng.standard_normal((B * S, D_MODEL)).astype(np.float32))
+    side = torch.cuda.Stream(device=DEV)
+    ctx = Context(0, stream=side)
+    enc = be.EncoderB200(ctx, weights, B, S, D_MODEL, HEADS, FFN, DEV, fused_attention=True)
+    xg = torch.from_numpy(x0.view(np.int16)).to(DEV).view(torch.bfloat16)
+    torch.cuda.synchronize()
+    eager = enc(xg).clone()          # also the warm-up: tensor maps are encoded, function attributes set
+    ctx.sync()
+    eager = eager.cpu()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        out = enc(xg)
+    out.zero_()
+    n0 = ctx.launches
+    graph.replay()
+    torch.cuda.synchronize()
+    assert ctx.launches == n0        # the replay goes through no enqueue
+    assert torch.equal(out.cpu(), eager)
+    xg.copy_(torch.from_numpy(be.f32_to_bf16_bits(rng.standard_normal((B * S, D_MODEL)).astype(np.float32)).view(np.int16)).to(DEV).view(torch.bfloat16))
+    graph.replay()                   # new input in the same buffer
+    torch.cuda.synchronize()
+    replayed = out.cpu().clone()
+    want = enc(xg)
+    ctx.sync()
+    assert torch.equal(replayed, want.cpu())
+    del graph
+    enc.close()
+    ctx.close()
+
+
 @pytest.mark.parametrize("shape,perm", [((2, 128, 24, 64), (2, 0, 1, 3)), ((8, 2, 128, 64), (1, 2, 0, 3)), ((5, 7, 9), (2, 0, 1)),
                                         ((33, 65), (1, 0)), ((3, 4, 5, 6), (3, 2, 1, 0))])
 def test_transpose(b200_lib, shape, perm):
