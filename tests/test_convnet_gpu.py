@@ -128,3 +128,62 @@ def test_benchmark_network_object_matches_checker(ctx, oracle_lib, int8, channel
     got = got.cpu().numpy()
     assert close_f32(got, want, rel=1e-4 if not int8 else 1e-5), np.abs(got - want).max()
     net.close()
+
+
+@pytest.mark.parametrize("int8", [True, False])
+def test_full_size_layer_two_data_paths_agree(ctx, int8, monkeypatch):
+    """Layer 3 of the benchmark network at its full size (256 images of 112 x 112 x 64 -> 128 channels, 473 GFLOP), too
+    large for the CPU checker: the implicit convolution (input read in place by im2col-mode TMA loads) against the
+    unfold + contraction path, which shares nothing with it up to the accumulator.  int8: every output bit for bit.
+    fp32: TF32 pairs read in place against the split unfold; the same three products, summed in different chunks."""
+    import bench_convnet as bc
+    from sofie_b200.ops import make_epilogue
+    lib = ctx._lib
+    n, c, hw, k = 256, 64, 112, 128
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    if int8:
+        x = torch.randint(-127, 128, (n, hw, hw, c), dtype=torch.int8, device=DEV, generator=gen)
+        w = torch.randint(-127, 128, (k, c, 3, 3), dtype=torch.int8, device=DEV, generator=gen)
+        ep_kw = dict(col_scale=torch.rand(k, device=DEV, generator=gen) * 1e-4 + 2e-5,
+                     bias=torch.randint(-20000, 20000, (k,), dtype=torch.int32, device=DEV, generator=gen), act=L.ACT_RELU)
+        code, dt = L.I8, torch.int8
+    else:
+        x = torch.rand((n, hw, hw, c), device=DEV, generator=gen)
+        w = torch.randn((k, c, 3, 3), device=DEV, generator=gen) * 0.05
+        ep_kw = dict(col_scale=torch.rand(k, device=DEV, generator=gen) + 0.5, bias=torch.randn(k, device=DEV, generator=gen), act=L.ACT_RELU)
+        code, dt = L.F32, torch.float32
+
+    def run(xl, xin, kernel, env=None):
+        if env:
+            monkeypatch.setenv(env, "1")
+        d = bc.conv_desc(n, c, hw, hw, k, 1, code, code, xl, 1)
+        h = C.c_void_p()
+        L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), w.data_ptr(), C.byref(h)), "conv_plan_create")
+        if env:
+            monkeypatch.delenv(env)
+        assert lib.sofie_b200_conv_plan_kernel(h).decode() == kernel
+        ws = torch.empty(max(16, lib.sofie_b200_conv_workspace_bytes(h)), dtype=torch.uint8, device=DEV)
+        y = torch.empty((n, hw, hw, k), dtype=dt, device=DEV)
+        ep, keep = make_epilogue(**ep_kw)
+        L.check(lib.sofie_b200_conv_enqueue(h, xin.data_ptr(), y.data_ptr(), ws.data_ptr(), C.byref(ep)), "conv_enqueue")
+        ctx.sync()
+        lib.sofie_b200_conv_plan_destroy(h)
+        del ws
+        return y
+
+    if int8:
+        a = run(1, x, "umma_im2col")
+        b = run(1, x, "umma", env="SOFIE_B200_NO_IMPLICIT_CONV")
+        assert torch.equal(a, b)
+        assert int((a != 0).sum()) > a.numel() // 10   # not a dead layer
+    else:
+        # the pairs, made on the device with the library's rounding (ties away from zero on the 13 dropped bits)
+        bits = x.view(torch.int32)
+        hi = ((bits + 0x1000) & ~0x1FFF).view(torch.float32)
+        rem = (x - hi).view(torch.int32)
+        lo = ((rem + 0x1000) & ~0x1FFF).view(torch.float32)
+        a = run(2, torch.cat([hi, lo], dim=3).contiguous(), "umma3x_im2col")
+        b = run(1, x, "umma3x")
+        err = (a - b).abs().max().item()
+        scale = b.abs().max().item()
+        assert err <= 2e-6 * scale, (err, scale)
