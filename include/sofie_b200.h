@@ -234,6 +234,15 @@ int sofie_b200_gemm_enqueue(sofie_b200_gemm_plan *plan, const void *A, const voi
 int sofie_b200_gemm_run_host(sofie_b200_gemm_plan *plan, const void *hostA, const void *hostB,
                              void *hostY, const sofie_b200_epilogue *ep);
 
+/* `count` independent contractions of the plan with HOST operands (a queue of inferences, the loop a caller of
+ * Session::infer runs over its events): hostA[i], hostB[i] -> hostY[i].  The copies travel on two streams of the
+ * context next to its compute stream, with two sets of device staging buffers: the host-to-device copy of inference
+ * i+1 and the device-to-host copy of inference i-1 overlap the contraction of inference i (PCIe is full duplex).
+ * Returns when every hostY[i] is written.  Pinned host memory is needed for the overlap (pageable memory works, serially).
+ * The same pointer may appear several times in hostA / hostB (a shared weight matrix is still copied every time). */
+int sofie_b200_gemm_run_host_many(sofie_b200_gemm_plan *plan, int64_t count, const void *const *hostA,
+                                  const void *const *hostB, void *const *hostY, const sofie_b200_epilogue *ep);
+
 /* ---- convolution ---------------------------------------------------------------------- */
 
 /* Registers a convolution and re-lays the weights once (the reference redoes its weight

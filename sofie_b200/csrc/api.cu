@@ -148,8 +148,17 @@ int sofie_b200_ctx_create(sofie_b200_ctx **out, int device, void *stream) {
 int sofie_b200_ctx_destroy(sofie_b200_ctx *ctx) {
   if (!ctx) return 0;
   cudaSetDevice(ctx->device);
-  for (int i = 0; i < 3; ++i)
+  for (int i = 0; i < 3; ++i) {
     if (ctx->stage[i]) cudaFree(ctx->stage[i]);
+    if (ctx->stage2[i]) cudaFree(ctx->stage2[i]);
+  }
+  if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
+  if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
+  for (int i = 0; i < 2; ++i) {
+    if (ctx->ev_in[i]) cudaEventDestroy(ctx->ev_in[i]);
+    if (ctx->ev_done[i]) cudaEventDestroy(ctx->ev_done[i]);
+    if (ctx->ev_out[i]) cudaEventDestroy(ctx->ev_out[i]);
+  }
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   delete ctx;
@@ -348,6 +357,64 @@ int sofie_b200_gemm_run_host(sofie_b200_gemm_plan *plan, const void *hostA, cons
   rc = sofie_b200_gemm_enqueue(plan, ctx->stage[0], ctx->stage[1], ctx->stage[2], ep);
   if (rc) return rc;
   SB_CUDA(cudaMemcpyAsync(hostY, ctx->stage[2], y_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  return sofie_b200_ctx_sync(ctx);
+}
+
+int sofie_b200_gemm_run_host_many(sofie_b200_gemm_plan *plan, int64_t count, const void *const *hostA, const void *const *hostB,
+                                  void *const *hostY, const sofie_b200_epilogue *ep) {
+  if (!plan || count < 0 || (count > 0 && (!hostA || !hostB || !hostY))) return fail(SOFIE_B200_ERR_INVALID, "gemm_run_host_many: NULL argument");
+  if (count == 0) return 0;
+  const sofie_b200_gemm_desc &d = plan->desc;
+  sofie_b200_ctx *ctx = plan->ctx;
+  const size_t es = dtype_size(d.ab_dtype), ys = dtype_size(d.y_dtype);
+  auto extent = [](int64_t rows, int64_t ld, int64_t batch, int64_t stride) -> size_t {
+    if (batch > 1 && stride != 0) return (size_t)((batch - 1) * stride + rows * ld);
+    return (size_t)(rows * ld);
+  };
+  const size_t bytes[3] = {extent(d.trans_a ? d.K : d.M, d.lda, d.batch, d.stride_a) * es,
+                           extent(d.trans_b ? d.N : d.K, d.ldb, d.batch, d.stride_b) * es, extent(d.M, d.ldy, d.batch, d.stride_y) * ys};
+  SB_CUDA(cudaSetDevice(ctx->device));
+  int rc;
+  for (int i = 0; i < 3; ++i) {
+    if ((rc = ensure_stage(ctx, i, bytes[i]))) return rc;
+    if (ctx->stage2_bytes[i] < bytes[i]) {
+      if (ctx->stage2[i]) SB_CUDA(cudaFree(ctx->stage2[i]));
+      ctx->stage2[i] = nullptr; ctx->stage2_bytes[i] = 0;
+      SB_CUDA(cudaMalloc(&ctx->stage2[i], bytes[i]));
+      ctx->stage2_bytes[i] = bytes[i];
+    }
+  }
+  if (!ctx->copy_in) {
+    SB_CUDA(cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
+    SB_CUDA(cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i) {
+      SB_CUDA(cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming));
+      SB_CUDA(cudaEventCreateWithFlags(&ctx->ev_done[i], cudaEventDisableTiming));
+      SB_CUDA(cudaEventCreateWithFlags(&ctx->ev_out[i], cudaEventDisableTiming));
+    }
+  }
+  // the copy streams start after whatever the compute stream has queued so far (earlier users of the staging buffers)
+  SB_CUDA(cudaEventRecord(ctx->ev_done[0], ctx->stream));
+  SB_CUDA(cudaStreamWaitEvent(ctx->copy_in, ctx->ev_done[0], 0));
+  SB_CUDA(cudaStreamWaitEvent(ctx->copy_out, ctx->ev_done[0], 0));
+  for (int64_t i = 0; i < count; ++i) {
+    if (!hostA[i] || !hostB[i] || !hostY[i]) return fail(SOFIE_B200_ERR_INVALID, "gemm_run_host_many: NULL operand %lld", (long long)i);
+    const int s = (int)(i & 1);
+    void *dA = s ? ctx->stage2[0] : ctx->stage[0], *dB = s ? ctx->stage2[1] : ctx->stage[1], *dY = s ? ctx->stage2[2] : ctx->stage[2];
+    if (i >= 2) SB_CUDA(cudaStreamWaitEvent(ctx->copy_in, ctx->ev_done[s], 0));   // the contraction two back has read this set
+    SB_CUDA(cudaMemcpyAsync(dA, hostA[i], bytes[0], cudaMemcpyHostToDevice, ctx->copy_in));
+    SB_CUDA(cudaMemcpyAsync(dB, hostB[i], bytes[1], cudaMemcpyHostToDevice, ctx->copy_in));
+    SB_CUDA(cudaEventRecord(ctx->ev_in[s], ctx->copy_in));
+    SB_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_in[s], 0));
+    if (i >= 2) SB_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->ev_out[s], 0));    // its Y has left for the host
+    if ((rc = sofie_b200_gemm_enqueue(plan, dA, dB, dY, ep))) return rc;
+    SB_CUDA(cudaEventRecord(ctx->ev_done[s], ctx->stream));
+    SB_CUDA(cudaStreamWaitEvent(ctx->copy_out, ctx->ev_done[s], 0));
+    SB_CUDA(cudaMemcpyAsync(hostY[i], dY, bytes[2], cudaMemcpyDeviceToHost, ctx->copy_out));
+    SB_CUDA(cudaEventRecord(ctx->ev_out[s], ctx->copy_out));
+  }
+  SB_CUDA(cudaStreamSynchronize(ctx->copy_out));
+  SB_CUDA(cudaStreamSynchronize(ctx->copy_in));
   return sofie_b200_ctx_sync(ctx);
 }
 

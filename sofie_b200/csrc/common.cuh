@@ -57,6 +57,11 @@ struct sofie_b200_ctx {
   // staging for the *_host helpers (grown on demand)
   void *stage[3] = {nullptr, nullptr, nullptr};
   size_t stage_bytes[3] = {0, 0, 0};
+  // sofie_b200_gemm_run_host_many: a second set of staging buffers, copy streams and events (created on first use)
+  void *stage2[3] = {nullptr, nullptr, nullptr};
+  size_t stage2_bytes[3] = {0, 0, 0};
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
 };
 
 namespace sb200 {

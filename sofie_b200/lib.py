@@ -87,6 +87,7 @@ PROTOTYPES = {
     "sofie_b200_gemm_plan_kernel": (C.c_char_p, [_P]),
     "sofie_b200_gemm_enqueue": (C.c_int, [_P, _P, _P, _P, C.POINTER(Epilogue)]),
     "sofie_b200_gemm_run_host": (C.c_int, [_P, _P, _P, _P, C.POINTER(Epilogue)]),
+    "sofie_b200_gemm_run_host_many": (C.c_int, [_P, _I64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(Epilogue)]),
     "sofie_b200_conv_plan_create": (C.c_int, [_P, C.POINTER(ConvDesc), _P, C.POINTER(_P)]),
     "sofie_b200_conv_plan_destroy": (C.c_int, [_P]),
     "sofie_b200_conv_out_shape": (C.c_int, [C.POINTER(ConvDesc), C.POINTER(_I64), C.POINTER(_I64)]),

@@ -202,6 +202,18 @@ class GemmPlan:
         L.check(self._lib.sofie_b200_gemm_run_host(self._h, hostA.data_ptr(), hostB.data_ptr(), hostY.data_ptr(), ep),
                 "gemm_run_host")
 
+    def run_host_many(self, hostA, hostB, hostY, epilogue: Optional[L.Epilogue] = None) -> None:
+        """Lists of host operands, one entry per inference: copies and contractions of successive inferences overlap."""
+        n = len(hostA)
+        if len(hostB) != n or len(hostY) != n:
+            raise ValueError("run_host_many takes three lists of the same length")
+        for t in (*hostA, *hostB, *hostY):
+            if t.is_cuda or not t.is_contiguous():
+                raise ValueError("run_host_many takes contiguous CPU tensors")
+        arr = lambda ts: (C.c_void_p * n)(*[t.data_ptr() for t in ts])
+        ep = C.byref(epilogue) if epilogue is not None else None
+        L.check(self._lib.sofie_b200_gemm_run_host_many(self._h, n, arr(hostA), arr(hostB), arr(hostY), ep), "gemm_run_host_many")
+
     def close(self) -> None:
         if self._h:
             self._lib.sofie_b200_gemm_plan_destroy(self._h)
