@@ -2,7 +2,7 @@
 // operands whose pitches or base addresses are not 16-byte multiples (TMA's rule), and fp32
 // products that must stay within 1e-5 of an fp32 BLAS (plain fp32 FMA, no TF32 rounding).
 // 64x64 output tile per CTA, 256 threads, 4x4 outputs per thread, K stepped by 16 through
-// shared memory.  The epilogue is the shared one (epilogue.cuh).
+// shared memory with the next step's operands prefetched into registers.  The epilogue is the shared one (epilogue.cuh).
 #include "gemm.cuh"
 
 namespace sb200 {
@@ -31,23 +31,36 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(const SimtParams p) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0;
 
-  for (long long k0 = 0; k0 < p.K; k0 += SK) {
-    for (int e = threadIdx.x; e < ST * SK; e += 256) {
+  // The global loads of K step k0 + SK are issued before the products of step k0 and land in registers meanwhile
+  // (four elements of each operand per thread and step).
+  constexpr int PER = ST * SK / 256;
+  acc_t ra[PER], rb[PER];
+  auto fetch = [&](long long k0) {
+#pragma unroll
+    for (int q = 0; q < PER; ++q) {
+      const int e = threadIdx.x + q * 256;
       int kk, mm;
       if (p.trans_a) { mm = e % ST; kk = e / ST; } else { kk = e % SK; mm = e / SK; }
-      long long m = m0 + mm, k = k0 + kk;
-      acc_t v = 0;
-      if (m < p.M && k < p.K) v = SimtIn<T>::cvt(p.trans_a ? A[k * p.lda + m] : A[m * p.lda + k]);
-      sA[kk][mm] = v;
-    }
-    for (int e = threadIdx.x; e < ST * SK; e += 256) {
-      int kk, nn;
+      const long long m = m0 + mm, k = k0 + kk;
+      ra[q] = (m < p.M && k < p.K) ? SimtIn<T>::cvt(p.trans_a ? A[k * p.lda + m] : A[m * p.lda + k]) : (acc_t)0;
+      int nn;
       if (p.trans_b) { kk = e % SK; nn = e / SK; } else { nn = e % ST; kk = e / ST; }
-      long long n = n0 + nn, k = k0 + kk;
-      acc_t v = 0;
-      if (n < p.N && k < p.K) v = SimtIn<T>::cvt(p.trans_b ? B[n * p.ldb + k] : B[k * p.ldb + n]);
-      sB[kk][nn] = v;
+      const long long n = n0 + nn, kb = k0 + kk;
+      rb[q] = (n < p.N && kb < p.K) ? SimtIn<T>::cvt(p.trans_b ? B[n * p.ldb + kb] : B[kb * p.ldb + n]) : (acc_t)0;
     }
+  };
+  fetch(0);
+  for (long long k0 = 0; k0 < p.K; k0 += SK) {
+#pragma unroll
+    for (int q = 0; q < PER; ++q) {
+      const int e = threadIdx.x + q * 256;
+      int kk, mm, nn;
+      if (p.trans_a) { mm = e % ST; kk = e / ST; } else { kk = e % SK; mm = e / SK; }
+      sA[kk][mm] = ra[q];
+      if (p.trans_b) { kk = e % SK; nn = e / SK; } else { nn = e % ST; kk = e / ST; }
+      sB[kk][nn] = rb[q];
+    }
+    if (k0 + SK < p.K) fetch(k0 + SK);
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < SK; ++kk) {
