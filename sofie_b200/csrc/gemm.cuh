@@ -28,7 +28,8 @@ constexpr int UMMA_STAGE_K_BYTES = 128;  // K extent of one shared-memory stage,
 constexpr int UMMA_MAX_DYN_SMEM = 227 * 1024;
 constexpr int UMMA_TAIL_BYTES = 1024;  // barriers, TMEM slot and abort flag behind the stage ring; the epilogue staging follows
 constexpr int UMMA_EPI_WARPS = 8;     // two epilogue warps per tensor-memory lane quarter, alternating 32-column chunks
-constexpr int UMMA_THREADS = 64 + 32 * UMMA_EPI_WARPS;  // warp 0: TMA producer, warp 1: MMA issuer, then the epilogue warps
+constexpr int UMMA_B_PRODUCER_WARP = 2 + UMMA_EPI_WARPS;  // the warp after the epilogue warps: TMA producer of operand B
+constexpr int UMMA_THREADS = 96 + 32 * UMMA_EPI_WARPS;   // warp 0: TMA producer (A), warp 1: MMA issuer, the epilogue warps, warp 10: producer (B)
 constexpr int UMMA_PAIR_THREADS = 192; // CTA-pair kernel: four epilogue warps per CTA
 
 // Everything the tcgen05 kernel needs besides the two tensor maps.
@@ -65,6 +66,9 @@ struct UmmaParams {
                                    // products (4 loads per 12 MMAs instead of 6); stage byte counts are the doubled ones
   int b_rows;                      // N extent of the B slice one CTA stages: bn, or bn/2 in pair mode
   int kb_mmas;                     // MMAs (32 bytes of K each) per K block: 4, or 2 when a K block is 64 bytes
+  int two_producers;               // operand B is loaded by a thread of its own (warp UMMA_B_PRODUCER_WARP): a thread is held by
+                                   // every TMA instruction until the unit takes it, and with 8-bit operands one thread issuing
+                                   // both operands' loads was the slowest stage of the pipeline
   // Implicit convolution: A is a channels-last image tensor read through an im2col-mode tensor map; row m of A is output
   // pixel m (image, then row, then column) and K block kb is (filter tap kb / ic_cblocks, channel block kb % ic_cblocks).
   int im2col;

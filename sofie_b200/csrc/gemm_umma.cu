@@ -1,10 +1,13 @@
 // Contraction kernel for sm_100a: tcgen05.mma with the accumulator in tensor memory, operands
 // staged in 128B-swizzled shared memory by TMA, one persistent CTA per SM.
 //
-// Roles inside a CTA of 320 threads
-//   warp 0, lane 0 : TMA producer.  Fills a ring of `stages` shared-memory stages; each stage
-//                    holds a 128 x (128 bytes of K) slice of op(A) and a bn x (128 bytes of K)
+// Roles inside a CTA of 352 threads
+//   warp 0, lane 0 : TMA producer of operand A.  Fills a ring of `stages` shared-memory stages; each
+//                    stage holds a 128 x (128 bytes of K) slice of op(A) and a bn x (128 bytes of K)
 //                    slice of op(B).
+//   warp 10, lane 0: TMA producer of operand B (a thread is held by every TMA instruction until the
+//                    unit has taken it -- 110 to 400 cycles -- and one thread issuing both operands'
+//                    loads fell behind 8-bit MMAs, which need a stage every 512 cycles).
 //   warp 1, lane 0 : MMA issuer.  Four tcgen05.mma (K = 32 bytes each) per stage into one of two
 //                    TMEM accumulators (128 lanes x bn columns each); tcgen05.commit releases
 //                    the stage to the producer and, after the last K block, hands the accumulator
@@ -75,7 +78,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_full + 8 * s, p.two_producers ? 2 : 1);   // one arrival (with its byte count) per producer
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -99,9 +102,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
   const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------------
-    if (lane == 0) {
+  if (warp == 0 || warp == UMMA_B_PRODUCER_WARP) {
+    // ------------------------------ TMA producers -----------------------------------
+    // warp 0 loads operand A, warp UMMA_B_PRODUCER_WARP operand B (or warp 0 both, and the other warp idles)
+    const bool do_a = warp == 0, do_b = p.two_producers ? warp != 0 : warp == 0;
+    if (lane == 0 && (do_a || do_b)) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       ROLE_TIMER(w_empty);
@@ -139,13 +144,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
           const uint32_t full = bar_full + 8 * stage;
           ROLE_SECTION_BEGIN();
-          mbar_arrive_expect_tx(full, p.a_stage_bytes + p.b_stage_bytes);
+          mbar_arrive_expect_tx(full, (do_a ? p.a_stage_bytes : 0u) + (do_b ? p.b_stage_bytes : 0u));
           ROLE_SECTION_END(c_expect);
           const int k0 = kb * p.kb_elems;
           const uint32_t sa = smem_a + stage * p.a_stage_bytes;
           const uint32_t sb = smem_b + stage * p.b_stage_bytes;
           ROLE_SECTION_BEGIN();
-          if (p.im2col) {
+          if (!do_a) {
+          } else if (p.im2col) {
             tma_load_im2col_4d(sa, &tm_a, full, cb * p.kb_elems, ic_w, ic_h, ic_n, (uint16_t)(tap_s * p.ic_dw), (uint16_t)(tap_r * p.ic_dh));
             if (++cb == p.ic_cblocks) { cb = 0; if (++tap_s == p.ic_s) { tap_s = 0; ++tap_r; } }
           } else if (!p.a_mn) {
@@ -156,7 +162,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
           ROLE_SECTION_END(c_load_a);
           ROLE_SECTION_BEGIN();
-          if (!p.b_mn) {
+          if (!do_b) {
+          } else if (!p.b_mn) {
             tma_load_3d(sb, &tm_b, full, k0, n0, bb);
           } else {
             for (int x = 0; x < p.b_boxes; ++x)
@@ -469,6 +476,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   // product per stage.
   u.fused3 = (plan->promote && !getenv("SOFIE_B200_NO_FUSED3")) ? 1 : 0;
   if (u.fused3) { u.a_stage_bytes *= 2; u.b_stage_bytes *= 2; }
+  u.two_producers = getenv("SOFIE_B200_ONE_PRODUCER") ? 0 : 1;
   u.im2col = ic.on;
   if (ic.on) {
     u.ic_wo = (int)ic.Wo; u.ic_pix = (int)(ic.Ho * ic.Wo);
