@@ -20,7 +20,11 @@
 namespace sb200 {
 using namespace ptx;
 
-constexpr int PROMOTE_THREADS = 320;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: epilogue
+// warp 0: TMA producer of A (with fused stages: of the hi block of A), warp 1: MMA issuer, warps 2-9: epilogue,
+// warp 10: producer of the lo block of A (fused stages only), warp 11: producer of B.  A thread is held by every TMA
+// instruction until the unit has taken it (400 cycles for an im2col-mode load of 128 pixels x 128 bytes), and one thread
+// issuing the four loads of a fused stage (1030 cycles) was slower than the stage's twelve MMAs (768 at 128 columns).
+constexpr int PROMOTE_THREADS = 384;
 constexpr int PROMOTE_HALF_MAX = 128; // accumulator columns (= fp32 sum registers) per epilogue thread
 
 // Final step of a tile for one epilogue warp: the fused epilogue over this thread's `half_cols` sums (row `row`, columns
@@ -102,7 +106,7 @@ umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_full + 8 * s, p.fused3 ? 3 : 2);   // one arrival (with its byte count) per active producer
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -130,8 +134,10 @@ umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
   const int num_chunks = (num_steps + chunk - 1) / chunk;
   const uint32_t a_half = p.a_stage_bytes >> 1, b_half = p.b_stage_bytes >> 1;   // fused stages: hi block, then lo block
 
-  if (warp == 0) {
-    if (lane == 0) {  // ---- TMA producer
+  if (warp == 0 || warp >= 10) {
+    // ---- TMA producers.  role 0: A (fused stages: its hi block), 1: the lo block of A (fused stages only), 2: B
+    const int role = warp == 0 ? 0 : warp - 9;
+    if (lane == 0 && (role != 1 || p.fused3)) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       ROLE_TIMER(w_empty);
@@ -166,24 +172,27 @@ umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
             break;
           }
           const uint32_t full = bar_full + 8 * stage;
-          mbar_arrive_expect_tx(full, p.a_stage_bytes + p.b_stage_bytes);
+          mbar_arrive_expect_tx(full, role == 2 ? p.b_stage_bytes : (p.fused3 ? a_half : p.a_stage_bytes));
           if (p.fused3) {   // K block kb of the stored operands: hi and lo of A, hi and lo of B
             const uint32_t sa = smem_a + stage * p.a_stage_bytes, sb = smem_b + stage * p.b_stage_bytes;
             ROLE_SECTION_BEGIN();
-            if (p.im2col) {
+            if (role == 2) {
+            } else if (p.im2col) {
               const int tap = kb / p.ic_cblocks, cb = kb - tap * p.ic_cblocks;
               const int tap_r = tap / p.ic_s, tap_s = tap - tap_r * p.ic_s;
               const uint16_t wo = (uint16_t)(tap_s * p.ic_dw), ho = (uint16_t)(tap_r * p.ic_dh);
-              tma_load_im2col_4d(sa, &tm_a, full, cb * p.kb_elems, ic_w, ic_h, ic_n, wo, ho);
-              tma_load_im2col_4d(sa + a_half, &tm_a, full, p.ic_c + cb * p.kb_elems, ic_w, ic_h, ic_n, wo, ho);
+              if (role == 0) tma_load_im2col_4d(sa, &tm_a, full, cb * p.kb_elems, ic_w, ic_h, ic_n, wo, ho);
+              else tma_load_im2col_4d(sa + a_half, &tm_a, full, p.ic_c + cb * p.kb_elems, ic_w, ic_h, ic_n, wo, ho);
             } else {
-              tma_load_3d(sa, &tm_a, full, kb * p.kb_elems, m0, ba);
-              tma_load_3d(sa + a_half, &tm_a, full, (p.seg_kb + kb) * p.kb_elems, m0, ba);
+              if (role == 0) tma_load_3d(sa, &tm_a, full, kb * p.kb_elems, m0, ba);
+              else tma_load_3d(sa + a_half, &tm_a, full, (p.seg_kb + kb) * p.kb_elems, m0, ba);
             }
             ROLE_SECTION_END(c_load_a);
             ROLE_SECTION_BEGIN();
-            tma_load_3d(sb, &tm_b, full, kb * p.kb_elems, n0, bb);
-            tma_load_3d(sb + b_half, &tm_b, full, (p.seg_kb + kb) * p.kb_elems, n0, bb);
+            if (role == 2) {
+              tma_load_3d(sb, &tm_b, full, kb * p.kb_elems, n0, bb);
+              tma_load_3d(sb + b_half, &tm_b, full, (p.seg_kb + kb) * p.kb_elems, n0, bb);
+            }
             ROLE_SECTION_END(c_load_b);
             if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
             continue;
@@ -191,7 +200,8 @@ umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           // K block kb of the three-product contraction -> K block of the stored [hi | lo] operand
           const int seg = kb / p.seg_kb, off = kb - seg * p.seg_kb;
           ROLE_SECTION_BEGIN();
-          if (p.im2col) {
+          if (role != 0) {
+          } else if (p.im2col) {
             // K block `off` of a segment is (filter tap off / cblocks, channel block off % cblocks); the lo channels of a
             // pixel follow its ic_c hi channels
             const int tap = off / p.ic_cblocks, cb = off - tap * p.ic_cblocks;
@@ -202,7 +212,7 @@ umma_tf32_promote_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_
           tma_load_3d(smem_a + stage * p.a_stage_bytes, &tm_a, full, (p.a_seg_kb[seg] + off) * p.kb_elems, m0, ba);
           ROLE_SECTION_END(c_load_a);
           ROLE_SECTION_BEGIN();
-          tma_load_3d(smem_b + stage * p.b_stage_bytes, &tm_b, full, (p.b_seg_kb[seg] + off) * p.kb_elems, n0, bb);
+          if (role == 2) tma_load_3d(smem_b + stage * p.b_stage_bytes, &tm_b, full, (p.b_seg_kb[seg] + off) * p.kb_elems, n0, bb);
           ROLE_SECTION_END(c_load_b);
           if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
         }
