@@ -235,7 +235,7 @@ int sofie_b200_gemm_run_host(sofie_b200_gemm_plan *plan, const void *hostA, cons
                              void *hostY, const sofie_b200_epilogue *ep);
 
 /* `count` independent contractions of the plan with HOST operands (a queue of inferences, the loop a caller of
- * Session::infer runs over its events): hostA[i], hostB[i] -> hostY[i].  The copies travel on two streams of the
+ * Session::infer, core/src/RModel.cxx:1303-1419, runs over its events): hostA[i], hostB[i] -> hostY[i].  The copies travel on two streams of the
  * context next to its compute stream, with two sets of device staging buffers: the host-to-device copy of inference
  * i+1 and the device-to-host copy of inference i-1 overlap the contraction of inference i (PCIe is full duplex).
  * Returns when every hostY[i] is written.  Pinned host memory is needed for the overlap (pageable memory works, serially).
@@ -343,8 +343,8 @@ int sofie_b200_batchnorm_enqueue(sofie_b200_ctx *ctx, const float *x, float *y, 
 int sofie_b200_global_avgpool_enqueue(sofie_b200_ctx *ctx, const void *x, float *y, int32_t x_dtype,
                                       int64_t nc, int64_t inner);
 
-/* The same GlobalAveragePool on a channels-last tensor [n, pixels, channels] (what a convolution with
- * y_layout = 1 writes): y[n,c] = sum(x[n,:,c]) / pixels, summed in pixel order. */
+/* The same GlobalAveragePool (ROperator_Pool.hxx:225-237,531-536) on a channels-last tensor [n, pixels, channels]
+ * (what a convolution with y_layout = 1 writes): y[n,c] = sum(x[n,:,c]) / pixels, summed in pixel order. */
 int sofie_b200_global_avgpool_nhwc_enqueue(sofie_b200_ctx *ctx, const void *x, float *y, int32_t x_dtype,
                                            int64_t n, int64_t pixels, int64_t channels);
 
