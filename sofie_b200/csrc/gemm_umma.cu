@@ -53,7 +53,7 @@ __device__ __forceinline__ void decode_item(const UmmaParams &p, long long w, lo
 }
 
 template <int KIND>
-__global__ void __launch_bounds__(UMMA_THREADS, 1)   // 10 warps are allocated as 12: 168 registers per thread is the most that fits
+__global__ void __launch_bounds__(UMMA_THREADS, 1)   // 11 warps are allocated as 12: 168 registers per thread is the most that fits
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
