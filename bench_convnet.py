@@ -21,7 +21,7 @@ Y_SCALE = np.float32(0.05)        # activation scale of every int8 layer output
 IN_SCALE = np.float32(1.0 / 127)  # U(0,1) input quantised to 0..127
 
 
-def conv_desc(n, c, h, w, k, stride, x_dtype, y_dtype, x_layout=0, y_layout=0):
+def conv_desc(n, c, h, w, k, stride, x_dtype, y_dtype, x_layout=0, y_layout=0, flags=0):
     from sofie_b200 import lib as L
     d = L.ConvDesc()
     d.N, d.C, d.H, d.W, d.K, d.R, d.S = n, c, h, w, k, 3, 3
@@ -30,7 +30,7 @@ def conv_desc(n, c, h, w, k, stride, x_dtype, y_dtype, x_layout=0, y_layout=0):
     d.dil_h = d.dil_w = 1
     d.groups = 1
     d.x_dtype, d.y_dtype, d.x_zero_point, d.precise = x_dtype, y_dtype, 0, 1
-    d.x_layout, d.y_layout = x_layout, y_layout
+    d.x_layout, d.y_layout, d.flags = x_layout, y_layout, flags
     return d
 
 

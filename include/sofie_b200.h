@@ -36,7 +36,7 @@
 extern "C" {
 #endif
 
-#define SOFIE_B200_ABI_VERSION 1
+#define SOFIE_B200_ABI_VERSION 2
 
 typedef enum sofie_b200_status {
   SOFIE_B200_OK = 0,
@@ -140,8 +140,24 @@ typedef struct sofie_b200_gemm_desc {
   int64_t stride_a, stride_b, stride_y; /* batch strides in elements */
   int64_t stride_c, stride_r;    /* batch strides of FULL_F32 C and of residual */
   int32_t precise;               /* F32 inputs: 1 = fp32-accurate path (default), 0 = single-pass TF32 */
-  int32_t reserved;
+  int32_t flags;                 /* sofie_b200_gemm_flags, 0 = none */
 } sofie_b200_gemm_desc;
+
+/* Flags of sofie_b200_gemm_desc.
+ *   B_CONSTANT  B is a weight (an ONNX initializer): its contents do not change while its address does not.  The
+ *               reference uploads weights once at Session construction (RModel_ALPAKA.cxx:1695-1707) and re-lays
+ *               convolution filters in a kernel of their own (ROperator_Conv.hxx:985-997); with this flag a plan
+ *               whose B is stored [K,N] keeps a K-major copy ([N,K], allocated at plan creation) that it fills on
+ *               the first enqueue and again whenever B's address changes.  The tensor-core kernel then stages every
+ *               B slice with one TMA box per K block instead of one per 128 bytes of columns.  Results are identical.
+ *   PAIR        run the CTA-pair form of the tensor-core kernel (two SMs share a 256 x bn tile through
+ *               tcgen05 cta_group::2) where the shape allows it; bits 8-9 then hold the number of K blocks per
+ *               release of shared-memory stages minus one.  The plain kernel is the default; the pair form is kept
+ *               for measurement. */
+typedef enum sofie_b200_gemm_flags {
+  SOFIE_B200_GEMM_B_CONSTANT = 1,
+  SOFIE_B200_GEMM_PAIR = 2
+} sofie_b200_gemm_flags;
 
 /*
  * Convolution over a whole NCHW batch as one implicit GEMM; replaces the reference's per-image
@@ -173,7 +189,16 @@ typedef struct sofie_b200_conv_desc {
                                  /* reads such a tensor in place and writes one for the next layer.  x_layout = 2:   */
                                  /* one group, C a multiple of 32, y_layout 1 or 2.  y_layout = 2: K a multiple of   */
                                  /* 4, and x_layout = 2 or the 3-channel first layer.                                */
+  int32_t flags;                 /* sofie_b200_conv_flags, 0 = none */
 } sofie_b200_conv_desc;
+
+/* Flags of sofie_b200_conv_desc.
+ *   UNFOLD      take the unfold + contraction path even where the implicit convolution applies (the two paths share
+ *               nothing up to the accumulator, which is what the parity tests use this for). */
+typedef enum sofie_b200_conv_flags {
+  SOFIE_B200_CONV_UNFOLD = 1
+} sofie_b200_conv_flags;
+
 
 typedef struct sofie_b200_ctx sofie_b200_ctx;
 typedef struct sofie_b200_gemm_plan sofie_b200_gemm_plan;
@@ -207,6 +232,14 @@ int sofie_b200_ctx_sync(sofie_b200_ctx *ctx);
 
 /* Number of kernels this ctx has launched so far (for launch accounting in benchmarks). */
 int64_t sofie_b200_ctx_launch_count(const sofie_b200_ctx *ctx);
+
+/* Self-test of the device-side error path (the reference has no counterpart: its kernels have no waits;
+ * the status word plays the role of the exceptions alpaka raises, RModel_ALPAKA.cxx:749-752).  Enqueues a
+ * one-thread kernel that waits, with the contraction kernels' own bounded wait, on a barrier nothing ever
+ * signals; after `limit_us` microseconds (1 .. 100000) it gives up, records its code in the status word and
+ * returns normally.  The next sofie_b200_ctx_sync() then returns SOFIE_B200_ERR_DEVICE_WAIT once, clears the
+ * word, and the context stays usable. */
+int sofie_b200_selftest_wait_timeout(sofie_b200_ctx *ctx, int64_t limit_us);
 
 /* ---- contractions -------------------------------------------------------------------- */
 
@@ -280,11 +313,17 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
  * failures) from inside their event loop.  No plan, no workspace argument: the padded weights and the
  * unfolded input go to a 16 MiB array that is part of the library image, so nothing is allocated or
  * freed, on the device or by any library, in this call.
- *   - Every GPU that loads the library holds those 16 MiB until the process exits.
+ *   - Every GPU that uses the library holds those 16 MiB until the process exits.  CUDA loads a module's code and
+ *     static arrays lazily, on first use: the 16 MiB are reserved by the first call of this function on a device,
+ *     and the first launch of each kernel it uses (int8 and fp32 paths have different ones) loads that kernel's
+ *     code.  So a host that forbids allocation after configuration makes one warm-up call per device for each
+ *     input type it will use, AT configuration time; from the second call on, device memory does not move.
  *   - A convolution whose padded weights plus unfolded input ([groups][N][Ho*Wo][C/groups*R*S rounded
  *     up to 16 bytes] elements) exceed 16 MiB returns SOFIE_B200_ERR_TOO_LARGE.
  *   - The first call on each device looks the array's address up (cudaGetSymbolAddress, with that device
  *     current) and caches it; make that first call before any stream capture begins.
+ *   - Every argument is checked before anything is enqueued: a refused call launches nothing and leaves the
+ *     array untouched.
  *   - The array is shared by every call on the device and keeps the last call's bytes; a call writes all
  *     it reads, so no clearing is needed, but calls that may overlap on the GPU (other streams, other
  *     contexts) race on it.  Calls on one stream are safe.

@@ -209,18 +209,33 @@ int sofie_b200_gemm_plan_create(sofie_b200_ctx *ctx, const sofie_b200_gemm_desc 
   SB_CUDA(cudaSetDevice(ctx->device));
   sofie_b200_gemm_plan *plan = new sofie_b200_gemm_plan();
   plan->ctx = ctx;
-  plan->desc = d;
   plan->use_umma = 0;
   // fp32 operands: the single-pass TF32 tensor path only on request; otherwise fp32 FMA.
   const bool want_umma = !(d.ab_dtype == SOFIE_B200_F32 && d.precise != 0);
+  // A constant B stored [K,N] becomes a K-major copy when the tensor-core kernel can take it (K rows of 16-byte multiples,
+  // dense source): one TMA box per K block instead of one per 128 bytes of columns.
+  const int es_ab = dtype_size(d.ab_dtype);
+  if ((d.flags & SOFIE_B200_GEMM_B_CONSTANT) && want_umma && !d.trans_b && d.M > 0 && d.N > 0 && d.K > 0 && (d.K * es_ab) % 16 == 0 &&
+      d.ldb == d.N && (d.batch == 1 || d.stride_b == 0 || d.stride_b == d.K * d.N)) {
+    const bool bcast = d.batch > 1 && d.stride_b == 0;
+    const size_t bytes = (size_t)(bcast ? 1 : d.batch) * d.N * d.K * es_ab;
+    if (cudaMalloc(&plan->b_kmajor, bytes) == cudaSuccess) {
+      plan->b_src_ld = d.ldb; plan->b_src_stride = d.stride_b;
+      d.trans_b = 1; d.ldb = d.K;
+    } else {
+      cudaGetLastError();   // no room for the copy: B is read as it is stored
+      plan->b_kmajor = nullptr;
+    }
+  }
+  plan->desc = d;
   if (want_umma && d.M > 0 && d.N > 0 && d.K > 0) {
     int rc = umma_plan_init(plan);
-    if (rc < 0) { delete plan; return rc; }
+    if (rc < 0) { if (plan->b_kmajor) cudaFree(plan->b_kmajor); delete plan; return rc; }
     plan->use_umma = (rc == 0);
   }
   // fp32 at fp32 accuracy: large problems go to the tensor cores as 3xTF32 (gemm_split.cu), the rest to fp32 FMA
   if (d.ab_dtype == SOFIE_B200_F32 && d.precise != 0 && d.M > 0 && d.N > 0 && d.K > 0 && d.batch <= 65535 &&
-      2.0 * (double)d.M * (double)d.N * (double)d.K * (double)d.batch >= SPLIT_MIN_FLOPS && !getenv("SOFIE_B200_NO_3XTF32")) {
+      2.0 * (double)d.M * (double)d.N * (double)d.K * (double)d.batch >= SPLIT_MIN_FLOPS) {
     const long long ks = split_ks(d.K);
     sofie_b200_gemm_desc g = d;
     const bool a_bcast = d.batch > 1 && d.stride_a == 0, b_bcast = d.batch > 1 && d.stride_b == 0;
@@ -253,6 +268,7 @@ int sofie_b200_gemm_plan_destroy(sofie_b200_gemm_plan *plan) {
   // the plan holds no reference into the ctx that needs undoing: a plan may be destroyed after its ctx
   if (plan->split_a) cudaFree(plan->split_a);
   if (plan->split_b) cudaFree(plan->split_b);
+  if (plan->b_kmajor) cudaFree(plan->b_kmajor);
   delete plan->inner;
   delete plan;
   return 0;
@@ -328,8 +344,23 @@ int sofie_b200_gemm_enqueue(sofie_b200_gemm_plan *plan, const void *A, const voi
     sofie_b200_ctx *ctx = plan->ctx;
     const bool a_bcast = d.batch > 1 && d.stride_a == 0, b_bcast = d.batch > 1 && d.stride_b == 0;
     if ((rc = split2_enqueue(ctx, (const float *)A, plan->split_a, d.M, d.K, plan->ks, d.lda, a_bcast ? 1 : d.batch, d.stride_a, d.trans_a ? 1 : 0))) return rc;
-    if ((rc = split2_enqueue(ctx, (const float *)B, plan->split_b, d.N, d.K, plan->ks, d.ldb, b_bcast ? 1 : d.batch, d.stride_b, d.trans_b ? 0 : 1))) return rc;
+    // a constant B is split once per address
+    if (!((d.flags & SOFIE_B200_GEMM_B_CONSTANT) && plan->split_b_src == B)) {
+      if ((rc = split2_enqueue(ctx, (const float *)B, plan->split_b, d.N, d.K, plan->ks, d.ldb, b_bcast ? 1 : d.batch, d.stride_b, d.trans_b ? 0 : 1))) return rc;
+      plan->split_b_src = (d.flags & SOFIE_B200_GEMM_B_CONSTANT) ? B : nullptr;
+    }
     return umma_enqueue(plan->inner, plan->split_a, plan->split_b, e);
+  }
+  if (plan->b_kmajor) {
+    if (plan->b_kmajor_src != B) {   // first enqueue, or the weight moved: [batch][K,N] -> [batch][N,K]
+      const bool bcast = d.batch > 1 && d.stride_b == 0;
+      const int64_t shape[3] = {bcast ? 1 : d.batch, d.K, d.N};
+      const int32_t perm[3] = {0, 2, 1};
+      if ((rc = sofie_b200_transpose_enqueue(plan->ctx, B, plan->b_kmajor, d.ab_dtype, 3, shape, perm))) return rc;
+      plan->b_kmajor_src = B;
+    }
+    if (plan->use_umma) return umma_enqueue(plan, A, plan->b_kmajor, e);
+    return simt_enqueue(plan, A, plan->b_kmajor, e);
   }
   if (plan->use_umma && d.K > 0) return umma_enqueue(plan, A, B, e);
   return simt_enqueue(plan, A, B, e);

@@ -511,6 +511,17 @@ __global__ void __launch_bounds__(256) pad_weights_kernel(const T *__restrict__ 
   }
 }
 
+// Dynamic shared memory of conv_direct_kernel: the filters with one record of epilogue operands per channel, and for a
+// channels-last output a staging block of 32 pixels per warp (TF32 pairs: 32 channels at a time).  A plan takes the
+// direct path only when this fits the opt-in limit; wider first layers unfold.
+constexpr size_t kDirectSmemLimit = 160 * 1024;
+static size_t direct_smem_bytes(const sofie_b200_conv_desc &d, bool pix_rows, bool pair_out) {
+  const size_t wsm = (size_t)d.K * ((d.x_dtype == SOFIE_B200_F32 ? 28 * sizeof(float) : 8 * sizeof(int)) + 16);
+  const int threads = pix_rows ? 128 : 256;
+  return wsm + (pix_rows ? (pair_out ? (size_t)(threads / 32) * 32 * (32 * 8 + 16)
+                                     : (size_t)(threads / 32) * 32 * (d.K * dtype_size(d.y_dtype) + 16)) : 0);
+}
+
 }  // namespace sb200
 
 using namespace sb200;
@@ -557,7 +568,8 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   p->kdim = p->cg * d.R * d.S;
   const int64_t vec = 16 / es;
   p->kpad = (p->kdim + vec - 1) / vec * vec;
-  if (d.groups == 1 && d.C == 3 && d.R == 3 && d.S == 3 && d.x_layout == 0 && d.K <= 256 && !getenv("SOFIE_B200_NO_DIRECT_CONV")) {
+  if (d.groups == 1 && d.C == 3 && d.R == 3 && d.S == 3 && d.x_layout == 0 && d.K <= 256 &&
+      direct_smem_bytes(d, p->pix_rows, p->pair_out) <= kDirectSmemLimit) {
     // the 3-channel first layer: direct kernel (see conv_direct_kernel); the plan only keeps the padded weights
     p->direct = 1;
     const int DIRECT_KW = es == 4 ? DirectAcc<float>::KW : DirectAcc<int8_t>::KW;
@@ -622,7 +634,7 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
     const bool type_ok = d.x_dtype == SOFIE_B200_I8 ? (d.x_zero_point == 0 || !has_pad) : d.precise == 0;
     const int64_t rows = (d.N > 0 ? d.N : 1) * Ho * Wo;
     if (d.groups == 1 && d.x_layout == 1 && d.y_layout == 1 && type_ok && (d.C * es) % 64 == 0 && rows < 0x7fffffffLL &&
-        d.K * p->kdim < 0x7fffffffLL && !getenv("SOFIE_B200_NO_IMPLICIT_CONV")) {
+        d.K * p->kdim < 0x7fffffffLL && !(d.flags & SOFIE_B200_CONV_UNFOLD)) {
       Im2colDesc ic;
       ic.on = 1; ic.N = d.N > 0 ? d.N : 1; ic.H = d.H; ic.W = d.W; ic.C = d.C; ic.Ho = Ho; ic.Wo = Wo;
       ic.R = (int)d.R; ic.S = (int)d.S; ic.pt = (int)d.pad_top; ic.pl = (int)d.pad_left; ic.pb = (int)d.pad_bottom; ic.pr = (int)d.pad_right;
@@ -666,7 +678,7 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
     g.M = images * Ho * Wo; g.N = p->kg; g.batch = 1;
     g.ldy = d.K;
   }
-  if (d.x_dtype == SOFIE_B200_F32 && d.precise != 0 && images <= 65535 && !getenv("SOFIE_B200_NO_3XTF32") &&
+  if (d.x_dtype == SOFIE_B200_F32 && d.precise != 0 && images <= 65535 &&
       2.0 * (double)p->kg * (double)(Ho * Wo) * (double)p->kpad * (double)images >= SPLIT_MIN_FLOPS) {
     const int64_t ks = split_ks(p->kdim);   // operands stored hi | lo, each segment ks wide; the contraction runs over 3 * ks
     g.K = 3 * ks; g.lda = g.ldb = 2 * ks; g.stride_b = p->pix_rows ? 0 : Ho * Wo * 2 * ks; g.precise = 0;
@@ -676,7 +688,7 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
     if (p->split) p->kpad = ks;
   }
   // channels-last unfold when the per-group channel count is a whole number of 16-byte vectors (then kpad == kdim)
-  p->nhwc = (d.x_layout == 1 || (p->cg % vec == 0 && d.N <= 65535 && !getenv("SOFIE_B200_NO_NHWC"))) ? 1 : 0;
+  p->nhwc = (d.x_layout == 1 || (p->cg % vec == 0 && d.N <= 65535)) ? 1 : 0;
   const void *w_src = W;
   void *w_perm = nullptr;
   if (p->nhwc) {
@@ -789,18 +801,16 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
     // channels-last output: 128 threads and a staging block of 32 pixels x K channels per warp behind the weights
     const int threads = plan->pix_rows ? 128 : 256;
     const unsigned grid = (unsigned)((total + threads - 1) / threads);
-    const size_t wsm = (size_t)d.K * ((d.x_dtype == SOFIE_B200_F32 ? 28 * sizeof(float) : 8 * sizeof(int)) + 16);   // weights + {scale, bias, int bias, -}
-    const size_t sm = wsm + (plan->pix_rows ? (plan->pair_out ? (size_t)(threads / 32) * 32 * (32 * 8 + 16)   // pairs: 32 channels at a time
-                                                                 : (size_t)(threads / 32) * 32 * (d.K * dtype_size(d.y_dtype) + 16)) : 0);
+    const size_t sm = direct_smem_bytes(d, plan->pix_rows, plan->pair_out);
     epi.split_out = plan->pair_out;
     if (d.x_dtype == SOFIE_B200_F32) {
       if (plan->pix_rows) {
-        SB_CUDA(cudaFuncSetAttribute(conv_direct_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_direct_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDirectSmemLimit));
         conv_direct_kernel<float, true><<<grid, threads, sm, ctx->stream>>>((const float *)X, (const float *)plan->w_padded, d, (int)plan->Ho, (int)plan->Wo, epi);
       } else conv_direct_kernel<float, false><<<grid, threads, sm, ctx->stream>>>((const float *)X, (const float *)plan->w_padded, d, (int)plan->Ho, (int)plan->Wo, epi);
     } else {
       if (plan->pix_rows) {
-        SB_CUDA(cudaFuncSetAttribute(conv_direct_kernel<int8_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        SB_CUDA(cudaFuncSetAttribute(conv_direct_kernel<int8_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDirectSmemLimit));
         conv_direct_kernel<int8_t, true><<<grid, threads, sm, ctx->stream>>>((const int8_t *)X, (const int *)plan->w_padded, d, (int)plan->Ho, (int)plan->Wo, epi);
       } else conv_direct_kernel<int8_t, false><<<grid, threads, sm, ctx->stream>>>((const int8_t *)X, (const int *)plan->w_padded, d, (int)plan->Ho, (int)plan->Wo, epi);
     }
@@ -992,10 +1002,55 @@ extern "C" int sofie_b200_conv_enqueue_noalloc(sofie_b200_ctx *ctx, const sofie_
                 "the static scratch holds %zu bytes -- use the plan-based entry points with a caller workspace",
                 w_bytes + x_bytes, w_bytes, x_bytes, kConvStaticScratchBytes);
 
+  // Every argument check comes before the first launch: a refused call enqueues nothing and leaves the shared array alone.
+  switch (d.y_dtype) {
+    case SOFIE_B200_F32: case SOFIE_B200_BF16: case SOFIE_B200_I8: case SOFIE_B200_U8: break;
+    case SOFIE_B200_I32:
+      if (d.x_dtype != SOFIE_B200_I8) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: I32 output needs I8 input");
+      break;
+    default: return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: output type %d not supported", d.y_dtype);
+  }
+  sofie_b200_epilogue e{};
+  e.alpha = 1.f; e.beta = 1.f; e.out_scale = 1.f;
+  if (ep) {
+    if (ep->row_scale) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: row_scale has no meaning for a convolution");
+    e = *ep;
+    e.row_scale = ep->col_scale;  // output channels are accumulator rows, as in sofie_b200_conv_enqueue
+    e.col_scale = nullptr;
+    switch (ep->bias_mode) {
+      case SOFIE_B200_BIAS_NONE: case SOFIE_B200_BIAS_SCALAR_F32: break;
+      case SOFIE_B200_BIAS_COL_F32: e.bias_mode = SOFIE_B200_BIAS_ROW_F32; break;
+      case SOFIE_B200_BIAS_COL_I32: e.bias_mode = SOFIE_B200_BIAS_ROW_I32; break;
+      default: return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: bias_mode %d not supported for a convolution", ep->bias_mode);
+    }
+    e.ldr = pix;
+  }
+
   SB_CUDA(cudaSetDevice(ctx->device));
   unsigned char *scratch = nullptr;
   if ((rc = conv_static_scratch(ctx->device, &scratch))) return rc;
   unsigned char *w_padded = scratch, *xcol = scratch + w_bytes;
+
+  // the contraction, planned on the stack (no heap, no device memory); planning can still refuse, so it also precedes the launches
+  sofie_b200_gemm_plan gp;
+  gp.ctx = ctx;
+  sofie_b200_gemm_desc &g = gp.desc;
+  g.M = kg; g.N = pix; g.K = kpad; g.batch = d.N;
+  g.trans_a = 0; g.trans_b = 1;
+  g.ab_dtype = d.x_dtype; g.y_dtype = d.y_dtype;
+  g.lda = kpad; g.ldb = kpad; g.ldy = pix;
+  g.stride_a = 0; g.stride_b = pix * kpad; g.stride_y = d.K * pix;
+  g.stride_c = 0; g.stride_r = d.K * pix;
+  g.precise = d.precise;
+  if (!(d.x_dtype == SOFIE_B200_F32 && d.precise != 0)) {
+    rc = umma_plan_init(&gp);
+    if (rc < 0) return rc;
+    gp.use_umma = (rc == 0);
+  }
+  {
+    EpiParams probe;   // the per-group epilogues below differ from this one only by pointer offsets
+    if ((rc = gemm_make_epi(g, Y, &e, &probe))) return rc;
+  }
 
   // 1. weights to a 16-byte row pitch, 2. unfold the whole batch; both rewrite every byte the contraction reads
   const long long wtotal = d.K * kpad;
@@ -1012,45 +1067,7 @@ extern "C" int sofie_b200_conv_enqueue_noalloc(sofie_b200_ctx *ctx, const sofie_
   SB_CUDA(cudaGetLastError());
   ctx->launches += 2;
 
-  // 3. the contraction, planned on the stack (no heap, no device memory)
-  sofie_b200_gemm_plan gp;
-  gp.ctx = ctx;
-  sofie_b200_gemm_desc &g = gp.desc;
-  g.M = kg; g.N = pix; g.K = kpad; g.batch = d.N;
-  g.trans_a = 0; g.trans_b = 1;
-  g.ab_dtype = d.x_dtype; g.y_dtype = d.y_dtype;
-  g.lda = kpad; g.ldb = kpad; g.ldy = pix;
-  g.stride_a = 0; g.stride_b = pix * kpad; g.stride_y = d.K * pix;
-  g.stride_c = 0; g.stride_r = d.K * pix;
-  g.precise = d.precise;
-  switch (d.y_dtype) {
-    case SOFIE_B200_F32: case SOFIE_B200_BF16: case SOFIE_B200_I8: case SOFIE_B200_U8: break;
-    case SOFIE_B200_I32:
-      if (d.x_dtype != SOFIE_B200_I8) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: I32 output needs I8 input");
-      break;
-    default: return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: output type %d not supported", d.y_dtype);
-  }
-  if (!(d.x_dtype == SOFIE_B200_F32 && d.precise != 0)) {
-    rc = umma_plan_init(&gp);
-    if (rc < 0) return rc;
-    gp.use_umma = (rc == 0);
-  }
-
-  sofie_b200_epilogue e{};
-  e.alpha = 1.f; e.beta = 1.f; e.out_scale = 1.f;
-  if (ep) {
-    if (ep->row_scale) return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: row_scale has no meaning for a convolution");
-    e = *ep;
-    e.row_scale = ep->col_scale;  // output channels are accumulator rows, as in sofie_b200_conv_enqueue
-    e.col_scale = nullptr;
-    switch (ep->bias_mode) {
-      case SOFIE_B200_BIAS_NONE: case SOFIE_B200_BIAS_SCALAR_F32: break;
-      case SOFIE_B200_BIAS_COL_F32: e.bias_mode = SOFIE_B200_BIAS_ROW_F32; break;
-      case SOFIE_B200_BIAS_COL_I32: e.bias_mode = SOFIE_B200_BIAS_ROW_I32; break;
-      default: return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue_noalloc: bias_mode %d not supported for a convolution", ep->bias_mode);
-    }
-    e.ldr = pix;
-  }
+  // 3. the contraction
   const int ys = dtype_size(d.y_dtype);
   for (int grp = 0; grp < d.groups; ++grp) {
     sofie_b200_epilogue eg = e;

@@ -1,7 +1,10 @@
 // The fused epilogue of every contraction kernel (tcgen05 and SIMT): one definition so that
 // all kernels round identically.  Each step is a separately rounded fp32 operation
 // (__fmul_rn/__fadd_rn block FMA contraction), which is what makes the int8 requantisation
-// reproducible bit for bit by a host restatement compiled with -ffp-contract=off.
+// reproducible bit for bit by a host restatement compiled with -ffp-contract=off.  The activations that call a
+// transcendental function (erff, tanhf, expf) are reproducible only as far as the two math libraries agree (a few
+// units in the last place): integer outputs behind Gelu or Sigmoid are held to one step of the output type,
+// everything behind Relu / LeakyRelu / no activation to exact equality.
 #pragma once
 #include "common.cuh"
 
@@ -36,13 +39,15 @@ __device__ __forceinline__ float act_apply(float v, int act, float act_alpha) {
       return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.f, erff(__fmul_rn(v, 0.7071067811865475f))));
     case SOFIE_B200_ACT_GELU_TANH: {
       // 0.5*x*(1+tanh(sqrt(2/pi)*(x+0.044715*x^3))), ROperator_Gelu.hxx:64-66
-      float x3 = v * v * v;
-      return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * x3)));
+      // every product and sum rounded on its own, in the order the expression is written in
+      const float x3 = __fmul_rn(__fmul_rn(v, v), v);
+      const float t = tanhf(__fmul_rn(0.7978845608028654f, __fadd_rn(v, __fmul_rn(0.044715f, x3))));
+      return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.f, t));
     }
     case SOFIE_B200_ACT_LEAKY_RELU:
       return v >= 0.f ? v : __fmul_rn(act_alpha, v);
     case SOFIE_B200_ACT_SIGMOID:
-      return 1.f / (1.f + expf(-v));
+      return __fdiv_rn(1.f, __fadd_rn(1.f, expf(-v)));
     default:
       return v;
   }

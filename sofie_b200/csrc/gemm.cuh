@@ -144,6 +144,12 @@ struct sofie_b200_gemm_plan {
   sb200::Im2colDesc ic{};          // set: operand A is an image tensor read in im2col mode (implicit convolution)
   int kb_bytes = 128;              // K extent of one shared-memory stage in bytes: 128 (128B swizzle) or 64 (64B swizzle)
   int split_out = 0;               // chunk-promotion kernel: write Y as TF32 pairs (EpiParams::split_out)
+  // SOFIE_B200_GEMM_B_CONSTANT: a weight B stored [K,N] is kept as a K-major copy [N,K] (b_kmajor, owned by the plan) that is
+  // refreshed when B's address changes; `desc` then describes the contraction on the copy (trans_b = 1, ldb = K)
+  void *b_kmajor = nullptr;
+  const void *b_kmajor_src = nullptr;
+  long long b_src_ld = 0, b_src_stride = 0;   // pitch and batch stride of B as the caller stores it
+  const void *split_b_src = nullptr;          // constant B whose hi | lo split is already in split_b
 };
 
 namespace sb200 {

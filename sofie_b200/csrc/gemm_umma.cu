@@ -428,16 +428,10 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
 
   plan->kind = kind;
   u.M = (int)d.M; u.N = (int)d.N; u.K = (int)d.K; u.batch = (int)d.batch;
-  // CTA-pair mode: two SMs share a 256 x bn tile, each staging its 128 rows of A and half of the B
-  // slice, which cuts the operand bytes per SM and deepens the shared-memory ring.  Worth it when
-  // the problem has at least a wave of pair tiles; SOFIE_B200_PAIR=0/1 overrides the choice.
+  // CTA-pair mode (on request, SOFIE_B200_GEMM_PAIR): two SMs share a 256 x bn tile, each staging its 128 rows of A and
+  // half of the B slice, which cuts the operand bytes per SM and deepens the shared-memory ring.
   const int sms = plan->ctx->sm_count;
-  u.pair = 0;
-  {
-    const long long pair_tiles = ((d.M + 255) / 256) * ((d.N + 255) / 256) * d.batch;
-    (void)pair_tiles;
-    if (const char *e = getenv("SOFIE_B200_PAIR"); e && !plan->promote && !ic.on) u.pair = (atoi(e) != 0 && d.M >= 256 && d.N >= 64) ? 1 : 0;
-  }
+  u.pair = ((d.flags & SOFIE_B200_GEMM_PAIR) && !plan->promote && !ic.on && d.M >= 256 && d.N >= 64) ? 1 : 0;
   const int tile_m = u.pair ? 2 * UMMA_BM : UMMA_BM;
   u.tiles_m = (int)((d.M + tile_m - 1) / tile_m);
   // an MN-major B slice is made of 128-byte-wide TMA boxes, so the slice one CTA stages must reach 128 bytes
@@ -451,17 +445,15 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
     const double cost_m = b_bytes + (a_bytes <= l2_fit ? a_bytes : tiles_n * a_bytes);
     const double cost_n = a_bytes + (b_bytes <= l2_fit ? b_bytes : (double)u.tiles_m * b_bytes);
     u.raster_n = (!u.pair && cost_n < cost_m) ? 1 : 0;
-    if (const char *e = getenv("SOFIE_B200_RASTER_N")) u.raster_n = (!u.pair && atoi(e) != 0) ? 1 : 0;
   }
   if (plan->promote) {
     u.seg_kb = (int)(d.K / 3 / SPLIT_K_ALIGN);
     u.a_seg_kb[0] = 0; u.a_seg_kb[1] = u.seg_kb; u.a_seg_kb[2] = 0;         // A: hi, lo, hi
     u.b_seg_kb[0] = 0; u.b_seg_kb[1] = 0; u.b_seg_kb[2] = u.seg_kb;         // B: hi, hi, lo
   }
-  u.commit_group = 1;
-  if (const char *e = getenv("SOFIE_B200_PAIR_GROUP")) { const int c = atoi(e); if (c >= 1 && c <= 3) u.commit_group = c; }
+  u.commit_group = 1 + ((d.flags >> 8) & 3);
+  if (u.commit_group > 3) u.commit_group = 3;
   u.promote_chunk = 8;   // 32 MMA steps per accumulation: truncation bias below 2e-6 relative even for same-sign data
-  if (const char *e = getenv("SOFIE_B200_PROMOTE_CHUNK")) { const int c = atoi(e); if (c >= 1 && c <= 64) u.promote_chunk = c; }
   u.b_rows = u.pair ? u.bn / 2 : u.bn;
   u.tiles_n = (int)((d.N + u.bn - 1) / u.bn);
   u.num_tiles = (long long)u.tiles_m * u.tiles_n * d.batch;
@@ -472,11 +464,10 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.b_stage_bytes = u.b_rows * kb_bytes;
   // Chunk-promotion kernel: hi and lo of both operands share a stage (64 KB for a 128-column tile: three stages; 96 KB
   // for 256 columns: two), so each operand block is loaded once for its two products: 4 loads per 12 MMAs instead of 6.
-  // Measured faster in every shape, two-stage ring included (8192^3: 6.6 -> 6.05 ms).  SOFIE_B200_NO_FUSED3=1 keeps one
-  // product per stage.
-  u.fused3 = (plan->promote && !getenv("SOFIE_B200_NO_FUSED3")) ? 1 : 0;
+  // Measured faster in every shape, two-stage ring included (8192^3: 6.6 -> 6.05 ms).
+  u.fused3 = plan->promote ? 1 : 0;
   if (u.fused3) { u.a_stage_bytes *= 2; u.b_stage_bytes *= 2; }
-  u.two_producers = getenv("SOFIE_B200_ONE_PRODUCER") ? 0 : 1;
+  u.two_producers = 1;
   u.im2col = ic.on;
   if (ic.on) {
     u.ic_wo = (int)ic.Wo; u.ic_pix = (int)(ic.Ho * ic.Wo);
@@ -541,7 +532,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.idesc_half = (u.idesc & ~(0x3fu << 17)) | ((uint32_t)(u.bn >> 4) << 17);
   if (!u.pair && !plan->promote && u.bn >= 64 && u.num_tiles > sms) {
     const long long tail = u.num_tiles % sms;
-    if (tail > 0 && 2 * tail <= sms && !getenv("SOFIE_B200_NO_TAIL_SPLIT")) {
+    if (tail > 0 && 2 * tail <= sms) {
       u.split_from = u.num_tiles - tail;
       u.num_items = u.num_tiles + tail;
     }
@@ -555,7 +546,6 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
     int clusters = 0;
     if ((rc = umma_pair_max_clusters(kind, plan->smem_bytes, &clusters))) return rc;
     if (clusters < 1) return 1;
-    if (getenv("SOFIE_B200_DEBUG")) fprintf(stderr, "[sofie_b200] pair kernel: %d CTA pairs resident at once (%d SMs)\n", clusters, sms);
     if (plan->grid > 2 * clusters) plan->grid = 2 * clusters;
     return 0;
   }
@@ -627,13 +617,13 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
   // Row segments per flush: a 128-byte segment is 4 chunks of 1-byte and 2 of 2-byte outputs; a narrow tile then has a
   // single segment and one of the two warps of each lane quarter would idle, so the segment is halved until there are two.
   int seg_div = 1;
-  if (!u.pair && !plan->promote && !getenv("SOFIE_B200_FULL_SEGMENTS")) {
+  if (!u.pair && !plan->promote) {
     const int full = 4 / dtype_size(plan->desc.y_dtype);   // chunks per 128 bytes
     int g = full;
     while (g > 1 && (u.bn / 32) / g < 2) g >>= 1;
     if (g < full) { u.ep.seg_chunks = g; seg_div = full / g; }
   }
-  if (u.vec_ok && !u.pair && !getenv("SOFIE_B200_NO_TMA_STORE")) {
+  if (u.vec_ok && !u.pair) {
     const sofie_b200_gemm_desc &d = plan->desc;
     const int ys = dtype_size(d.y_dtype);
     if (ep.Y != plan->cached_y || seg_div != plan->cached_seg_div) {

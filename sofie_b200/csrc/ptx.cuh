@@ -50,7 +50,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Bounded wait on an mbarrier phase.  Gives up when another role of the CTA has already
 // given up (abort flag in shared memory) or after about one second of polling, so that a
 // protocol bug ends the kernel with a status code instead of holding the GPU.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          uint64_t limit_ns = 1000000000ull) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -58,7 +59,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       uint64_t now = globaltimer();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > 1000000000ull) return false;
+      else if (now - t0 > limit_ns) return false;
     }
   }
 }

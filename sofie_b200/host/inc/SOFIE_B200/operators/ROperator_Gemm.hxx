@@ -230,6 +230,8 @@ public:
    {
       // y*s[c] + t[c] on top of acc*alpha + bias[c]: new column scale s, new bias bias*s + t
       if (fEpi.act != EActivationType::UNDEFINED || !fEpi.residual.empty() || fIsOutputConstant) return false;
+      // BatchNormalization's channel axis is dimension 1: the columns of a rank-2 product, but the ROWS of a stacked one
+      if (fShapeY.size() != 2) return false;
       if (!fEpi.bias.empty() && (fEpi.biasMode != "SOFIE_B200_BIAS_COL_F32" || !model.IsInitializedTensor(fEpi.bias))) return false;
       auto s = model.GetTensorData<float>(scale), t = model.GetTensorData<float>(shift);
       if (s.size() != fN || t.size() != fN) return false;

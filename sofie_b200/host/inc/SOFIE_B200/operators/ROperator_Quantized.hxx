@@ -168,8 +168,9 @@ public:
    bool HasFusableEpilogue() const override { return true; }
    bool FuseActivation(EActivationType act, float alpha, const std::string &newOutput) override
    {
-      // Relu on the quantised output equals clamping the float value at 0 before rounding when y_zp maps to 0
-      if (fEpi.act != EActivationType::UNDEFINED || act != EActivationType::RELU) return false;
+      // Relu on the quantised output equals clamping the float value at 0 before rounding only when the output zero
+      // point is 0: rint(max(v, 0)) + zp differs from max(rint(v) + zp, 0) otherwise
+      if (fEpi.act != EActivationType::UNDEFINED || act != EActivationType::RELU || fEpi.outZeroPoint != 0) return false;
       fEpi.act = act; fEpi.actAlpha = alpha;
       fNY = newOutput; fOutputTensorNames = {fNY};
       return true;

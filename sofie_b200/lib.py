@@ -17,6 +17,9 @@ F32, BF16, I8, F8E4M3, I32, U8 = range(6)
 ACT_NONE, ACT_RELU, ACT_GELU_ERF, ACT_GELU_TANH, ACT_LEAKY_RELU, ACT_SIGMOID = range(6)
 BIAS_NONE, BIAS_COL_F32, BIAS_ROW_F32, BIAS_SCALAR_F32, BIAS_COL_I32, BIAS_FULL_F32, BIAS_ROW_I32 = range(7)
 OK, ERR_INVALID, ERR_CUDA, ERR_DEVICE_WAIT, ERR_NO_DEVICE, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5
+ABI_VERSION = 2
+GEMM_B_CONSTANT, GEMM_PAIR = 1, 2
+CONV_UNFOLD = 1
 
 
 class Epilogue(C.Structure):
@@ -47,7 +50,7 @@ class GemmDesc(C.Structure):
         ("lda", C.c_int64), ("ldb", C.c_int64), ("ldy", C.c_int64),
         ("stride_a", C.c_int64), ("stride_b", C.c_int64), ("stride_y", C.c_int64),
         ("stride_c", C.c_int64), ("stride_r", C.c_int64),
-        ("precise", C.c_int32), ("reserved", C.c_int32),
+        ("precise", C.c_int32), ("flags", C.c_int32),
     ]
 
 
@@ -63,6 +66,7 @@ class ConvDesc(C.Structure):
         ("x_zero_point", C.c_int32),
         ("precise", C.c_int32),
         ("x_layout", C.c_int32), ("y_layout", C.c_int32),
+        ("flags", C.c_int32),
     ]
 
 
@@ -82,6 +86,7 @@ PROTOTYPES = {
     "sofie_b200_ctx_destroy": (C.c_int, [_P]),
     "sofie_b200_ctx_sync": (C.c_int, [_P]),
     "sofie_b200_ctx_launch_count": (_I64, [_P]),
+    "sofie_b200_selftest_wait_timeout": (C.c_int, [_P, _I64]),
     "sofie_b200_gemm_plan_create": (C.c_int, [_P, C.POINTER(GemmDesc), C.POINTER(_P)]),
     "sofie_b200_gemm_plan_destroy": (C.c_int, [_P]),
     "sofie_b200_gemm_plan_kernel": (C.c_char_p, [_P]),
@@ -135,7 +140,7 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)  # AttributeError if the symbol is not exported
         fn.restype = res
         fn.argtypes = args
-    if lib.sofie_b200_abi_version() != 1:
+    if lib.sofie_b200_abi_version() != ABI_VERSION:
         raise ImportError("libsofie_b200.so has a different ABI version than this binding")
     _lib = lib
     return lib

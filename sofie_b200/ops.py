@@ -168,7 +168,7 @@ class GemmPlan:
     """One registered contraction (sofie_b200_gemm_plan)."""
 
     def __init__(self, ctx: Context, M, N, K, ab_dtype, y_dtype, trans_a=False, trans_b=False, batch=1, lda=0,
-                 ldb=0, ldy=0, stride_a=0, stride_b=0, stride_y=0, stride_c=0, stride_r=0, precise=True):
+                 ldb=0, ldy=0, stride_a=0, stride_b=0, stride_y=0, stride_c=0, stride_r=0, precise=True, flags=0):
         self.ctx = ctx
         self._lib = ctx._lib
         d = L.GemmDesc()
@@ -180,6 +180,7 @@ class GemmPlan:
         d.stride_a, d.stride_b, d.stride_y = stride_a, stride_b, stride_y
         d.stride_c, d.stride_r = stride_c, stride_r
         d.precise = int(precise)
+        d.flags = int(flags)
         self.desc = d
         h = C.c_void_p()
         L.check(self._lib.sofie_b200_gemm_plan_create(ctx._h, C.byref(d), C.byref(h)), "gemm_plan_create")

@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import ctypes as C
 import json
+import os
 import re
 import sys
 from pathlib import Path
@@ -28,7 +29,9 @@ ROOT = HERE.parent.parent
 sys.path.insert(0, str(HERE.parent))
 import onnx_min  # noqa: E402
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2 and "SOFIE_REFERENCE" not in os.environ:
+    sys.exit("usage: make_golden.py <reference checkout>   (or SOFIE_REFERENCE=<path>)")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["SOFIE_REFERENCE"])
 ONNX_DIR = REF / "tests" / "models" / "onnx"
 GEN = ROOT / "oracle" / "_ref" / "gen"
 

@@ -42,7 +42,7 @@ def test_struct_layouts_match_header():
 
 
 def test_abi_version_and_status_strings(b200_lib):
-    assert b200_lib.sofie_b200_abi_version() == 1
+    assert b200_lib.sofie_b200_abi_version() == L.ABI_VERSION == 2
     assert b200_lib.sofie_b200_status_string(0) == b"ok"
     assert b"wait" in b200_lib.sofie_b200_status_string(L.ERR_DEVICE_WAIT)
 

@@ -153,14 +153,10 @@ def test_full_size_layer_two_data_paths_agree(ctx, int8, monkeypatch):
         ep_kw = dict(col_scale=torch.rand(k, device=DEV, generator=gen) + 0.5, bias=torch.randn(k, device=DEV, generator=gen), act=L.ACT_RELU)
         code, dt = L.F32, torch.float32
 
-    def run(xl, xin, kernel, env=None):
-        if env:
-            monkeypatch.setenv(env, "1")
-        d = bc.conv_desc(n, c, hw, hw, k, 1, code, code, xl, 1)
+    def run(xl, xin, kernel, flags=0):
+        d = bc.conv_desc(n, c, hw, hw, k, 1, code, code, xl, 1, flags)
         h = C.c_void_p()
         L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), w.data_ptr(), C.byref(h)), "conv_plan_create")
-        if env:
-            monkeypatch.delenv(env)
         assert lib.sofie_b200_conv_plan_kernel(h).decode() == kernel
         ws = torch.empty(max(16, lib.sofie_b200_conv_workspace_bytes(h)), dtype=torch.uint8, device=DEV)
         y = torch.empty((n, hw, hw, k), dtype=dt, device=DEV)
@@ -173,7 +169,7 @@ def test_full_size_layer_two_data_paths_agree(ctx, int8, monkeypatch):
 
     if int8:
         a = run(1, x, "umma_im2col")
-        b = run(1, x, "umma", env="SOFIE_B200_NO_IMPLICIT_CONV")
+        b = run(1, x, "umma", flags=L.CONV_UNFOLD)
         assert torch.equal(a, b)
         assert int((a != 0).sum()) > a.numel() // 10   # not a dead layer
     else:

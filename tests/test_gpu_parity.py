@@ -64,13 +64,13 @@ def test_golden_models(name, backend):
 
 
 # ---- int8 QLinearMatMul: bit-exact --------------------------------------------------------------
-def run_gemm(ctx, a, b, M, N, K, in_dt, out_dt, trans_a=False, trans_b=False, batch=1, precise=True, expect=None, **ep_kw):
+def run_gemm(ctx, a, b, M, N, K, in_dt, out_dt, trans_a=False, trans_b=False, batch=1, precise=True, expect=None, flags=0, **ep_kw):
     from sofie_b200.ops import GemmPlan, make_epilogue
     ta, tb = torch.from_numpy(a).to(DEV).view(in_dt), torch.from_numpy(b).to(DEV).view(in_dt)
     y = torch.zeros((batch, M, N) if batch > 1 else (M, N), dtype=out_dt, device=DEV)
     plan = GemmPlan(ctx, M, N, K, in_dt, out_dt, trans_a=trans_a, trans_b=trans_b, batch=batch,
                     stride_a=(M * K if batch > 1 else 0), stride_b=(K * N if batch > 1 else 0), stride_y=(M * N if batch > 1 else 0),
-                    precise=precise)
+                    precise=precise, flags=flags)
     dev_kw = {k: (torch.from_numpy(v).to(DEV) if isinstance(v, np.ndarray) else v) for k, v in ep_kw.items()}
     ep, keep = make_epilogue(**dev_kw)
     plan.enqueue(ta, tb, y, ep)
@@ -305,6 +305,33 @@ def test_conv_channels_last_layouts(ctx, oracle, dtype, xl, yl):
         assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size}"
     else:
         assert close_f32(got, want), np.abs(got - want).max()
+
+
+@pytest.mark.parametrize("K,kernel", [(64, "direct"), (256, "simt")])
+def test_three_channel_first_layer_channels_last_fp32(ctx, oracle, K, kernel):
+    """The 3-channel 3x3 first layer writing a channels-last F32 tensor: the direct kernel while its filters and staging
+    fit its shared memory (up to 252 filters), the unfold path for wider layers -- both must run and agree with the checker."""
+    from sofie_b200.ops import make_epilogue
+    lib = ctx._lib
+    rng = np.random.default_rng(K)
+    x = rng.random((2, 3, 20, 18), dtype=np.float32)
+    w = (rng.standard_normal((K, 3, 3, 3)) * 0.2).astype(np.float32)
+    bias = rng.standard_normal(K).astype(np.float32)
+    geo = dict(pads=[1, 1, 1, 1], strides=[1, 1], dil=[1, 1], group=1)
+    d = gr.conv_desc(geo, x.shape, w.shape, L.F32, L.F32)
+    want = oracle.conv(x, w, d, 20, 18, ep=oracle.epilogue(bias=bias, act=L.ACT_RELU))
+    d.y_layout = 1
+    tx, tw = torch.from_numpy(x).to(DEV), torch.from_numpy(w).to(DEV)
+    h = C.c_void_p()
+    L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), tw.data_ptr(), C.byref(h)), "conv_plan_create")
+    assert lib.sofie_b200_conv_plan_kernel(h).decode() == kernel
+    ws = torch.empty(max(16, lib.sofie_b200_conv_workspace_bytes(h)), dtype=torch.uint8, device=DEV)
+    y = torch.zeros((2, 20, 18, K), dtype=torch.float32, device=DEV)
+    ep, keep = make_epilogue(bias=torch.from_numpy(bias).to(DEV), act=L.ACT_RELU)
+    L.check(lib.sofie_b200_conv_enqueue(h, tx.data_ptr(), y.data_ptr(), ws.data_ptr(), C.byref(ep)), "conv_enqueue")
+    ctx.sync()
+    lib.sofie_b200_conv_plan_destroy(h)
+    assert close_f32(y.cpu().numpy().transpose(0, 3, 1, 2), want)
 
 
 IMPLICIT_CASES = {
@@ -612,24 +639,81 @@ def test_fp32_gemm_3xtf32_meets_fp32_bar(ctx, oracle, M, N, K, ta, tb, batch):
         assert not close_f32(tf32.reshape(want.shape), want)
 
 
-@pytest.mark.parametrize("group", ["1", "3"])
-def test_cta_pair_kernel_bit_exact(ctx, oracle, monkeypatch, group):
+@pytest.mark.parametrize("group", [1, 3])
+def test_cta_pair_kernel_bit_exact(ctx, oracle, group):
     """The opt-in CTA-pair kernel (cluster of 2, tcgen05 cta_group::2), with per-stage and grouped stage release."""
-    monkeypatch.setenv("SOFIE_B200_PAIR", "1")
-    monkeypatch.setenv("SOFIE_B200_PAIR_GROUP", group)
+    pair = L.GEMM_PAIR | ((group - 1) << 8)
     rng = np.random.default_rng(17)
     for (M, N, K, tb) in ((512, 512, 1024, True), (1000, 704, 400, False), (256, 64, 96, True)):
         a = rng.integers(-127, 128, size=(M, K), dtype=np.int8)
         b = rng.integers(-127, 128, size=(N, K) if tb else (K, N), dtype=np.int8)
         want = oracle.gemm(a, b, M, N, K, L.I8, L.I8, False, tb, ep=oracle.epilogue(alpha=MULT))
-        got = run_gemm(ctx, a, b, M, N, K, torch.int8, torch.int8, False, tb, alpha=MULT, expect="umma").cpu().numpy()
+        got = run_gemm(ctx, a, b, M, N, K, torch.int8, torch.int8, False, tb, alpha=MULT, expect="umma", flags=pair).cpu().numpy()
         assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size} differ"
     a = rng.standard_normal((384, 512)).astype(np.float32)
     b = rng.standard_normal((320, 512)).astype(np.float32)
     ab, bb = (a.view(np.uint32) >> 16).astype(np.uint16), (b.view(np.uint32) >> 16).astype(np.uint16)
     want = bf16_bits_to_f32(oracle.gemm(ab, bb, 384, 320, 512, L.BF16, L.BF16, False, True))
-    got = run_gemm(ctx, ab.view(np.int16), bb.view(np.int16), 384, 320, 512, torch.bfloat16, torch.bfloat16, False, True).float().cpu().numpy()
+    got = run_gemm(ctx, ab.view(np.int16), bb.view(np.int16), 384, 320, 512, torch.bfloat16, torch.bfloat16, False, True, flags=pair).float().cpu().numpy()
     assert close_lowp(got, want)
+
+
+def test_constant_weight_is_relaid_once_and_follows_its_address(ctx, oracle):
+    """SOFIE_B200_GEMM_B_CONSTANT: a weight stored [K,N] is kept as a K-major copy.  Same bits as without the flag; a
+    second weight at another address is picked up; the same address is not read again (the documented contract)."""
+    from sofie_b200.ops import GemmPlan, make_epilogue
+    rng = np.random.default_rng(23)
+    for (M, N, K, batch) in ((384, 320, 640, 1), (200, 272, 144, 3)):
+        a = rng.integers(-127, 128, size=(batch, M, K), dtype=np.int8)
+        b1 = rng.integers(-127, 128, size=(batch, K, N), dtype=np.int8)
+        b2 = rng.integers(-127, 128, size=(batch, K, N), dtype=np.int8)
+        plan = GemmPlan(ctx, M, N, K, torch.int8, torch.int8, batch=batch, stride_a=M * K if batch > 1 else 0,
+                        stride_b=K * N if batch > 1 else 0, stride_y=M * N if batch > 1 else 0, flags=L.GEMM_B_CONSTANT)
+        assert plan.kernel == "umma"
+        ta, t1, t2 = (torch.from_numpy(v).to(DEV) for v in (a, b1, b2))
+        y = torch.zeros((batch, M, N), dtype=torch.int8, device=DEV)
+        ep, keep = make_epilogue(alpha=MULT)
+        for tb, hb in ((t1, b1), (t2, b2), (t1, b1)):
+            plan.enqueue(ta, tb, y, ep)
+            ctx.sync()
+            want = oracle.gemm(a, hb, M, N, K, L.I8, L.I8, batch=batch, ep=oracle.epilogue(alpha=MULT)).reshape(batch, M, N)
+            assert np.array_equal(y.cpu().numpy(), want)
+        plan.close()
+    # bf16 weights, and fp32 at fp32 accuracy (the constant weight's hi | lo split is made once)
+    a = rng.standard_normal((512, 256)).astype(np.float32)
+    b = rng.standard_normal((256, 1024)).astype(np.float32)
+    ab, bb = (a.view(np.uint32) >> 16).astype(np.uint16), (b.view(np.uint32) >> 16).astype(np.uint16)
+    want = bf16_bits_to_f32(oracle.gemm(ab, bb, 512, 1024, 256, L.BF16, L.BF16))
+    got = run_gemm(ctx, ab.view(np.int16), bb.view(np.int16), 512, 1024, 256, torch.bfloat16, torch.bfloat16, flags=L.GEMM_B_CONSTANT, expect="umma")
+    assert close_lowp(got.float().cpu().numpy(), want)
+    plan = GemmPlan(ctx, 512, 1024, 256, torch.float32, torch.float32, flags=L.GEMM_B_CONSTANT)
+    assert plan.kernel == "umma3x"
+    ta, tb = torch.from_numpy(a).to(DEV), torch.from_numpy(b).to(DEV)
+    y = torch.zeros((512, 1024), dtype=torch.float32, device=DEV)
+    want = oracle.gemm(a, b, 512, 1024, 256, L.F32, L.F32)
+    for _ in range(2):
+        y.zero_()
+        plan.enqueue(ta, tb, y)
+        ctx.sync()
+        assert close_f32(y.cpu().numpy(), want)
+    plan.close()
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_survives(ctx, oracle):
+    """The kernels' bounded wait on a barrier that nothing signals gives up after its limit, the status word carries the
+    code to the next sync (once), and the context keeps working.  The waiting kernel returns normally."""
+    lib = ctx._lib
+    assert lib.sofie_b200_selftest_wait_timeout(ctx._h, 2000) == 0        # 2 ms
+    rc = lib.sofie_b200_ctx_sync(ctx._h)
+    assert rc == L.ERR_DEVICE_WAIT
+    assert "stage never filled" in lib.sofie_b200_last_error().decode()
+    assert lib.sofie_b200_ctx_sync(ctx._h) == 0                            # the word was cleared
+    assert lib.sofie_b200_selftest_wait_timeout(ctx._h, 0) == L.ERR_INVALID
+    rng = np.random.default_rng(5)
+    a = rng.integers(-127, 128, size=(256, 256), dtype=np.int8)
+    b = rng.integers(-127, 128, size=(256, 256), dtype=np.int8)
+    got = run_gemm(ctx, a, b, 256, 256, 256, torch.int8, torch.int32, expect="umma").cpu().numpy()
+    assert np.array_equal(got, a.astype(np.int32) @ b.astype(np.int32))
 
 
 def test_plans_of_different_sizes_coexist(ctx, oracle):

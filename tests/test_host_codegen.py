@@ -113,6 +113,27 @@ def test_a_shared_output_is_not_folded(emit, tmp_path):
     assert "sofie_b200_unary_enqueue" in (tmp_path / "m.hxx").read_text()
 
 
+def test_batchnorm_after_a_stacked_matmul_is_not_folded(emit, tmp_path):
+    # [B,S,S] product: BatchNormalization's channel axis is dimension 1, the ROWS of each product, so a per-column fold
+    # would scale the wrong axis even though the sizes match
+    rng = np.random.default_rng(4)
+    w = {"W": rng.standard_normal((6, 6)).astype(np.float32), "scale": rng.random(6).astype(np.float32) + 0.5,
+         "beta": rng.standard_normal(6).astype(np.float32), "mean": rng.standard_normal(6).astype(np.float32),
+         "var": rng.random(6).astype(np.float32) + 0.5}
+    nodes = [{"op": "MatMul", "in": ["X", "W"], "out": ["m"], "attrs": {}},
+             {"op": "BatchNormalization", "in": ["m", "scale", "beta", "mean", "var"], "out": ["Y"], "attrs": {"epsilon": 1e-5}}]
+    onnx_min.save(str(tmp_path / "m.onnx"), nodes, w, [("X", [2, 6, 6])], ["Y"])
+    rc, out, err = run_emit(emit, tmp_path / "m.onnx", tmp_path / "m.hxx")
+    assert rc == 0, err
+    assert json.loads(out)["fusions"] == []
+    assert "sofie_b200_batchnorm_enqueue" in (tmp_path / "m.hxx").read_text()
+    # the rank-2 product does fold
+    onnx_min.save(str(tmp_path / "n.onnx"), nodes, w, [("X", [5, 6])], ["Y"])
+    rc, out, err = run_emit(emit, tmp_path / "n.onnx", tmp_path / "n.hxx")
+    assert rc == 0, err
+    assert len(json.loads(out)["fusions"]) == 1 and "batchnorm_enqueue" not in (tmp_path / "n.hxx").read_text()
+
+
 def test_matmul_add_becomes_gemm_with_bias_and_transpose_is_absorbed(emit, tmp_path):
     rng = np.random.default_rng(2)
     w = {"Wt": rng.standard_normal((5, 8)).astype(np.float32), "b": rng.standard_normal(5).astype(np.float32)}
