@@ -347,6 +347,37 @@ int sofie_b200_conv_enqueue_noalloc(sofie_b200_ctx *ctx, const sofie_b200_conv_d
 int sofie_b200_attention_enqueue(sofie_b200_ctx *ctx, const void *qkv, void *out, int32_t dtype, int64_t batch,
                                  int64_t seq, int32_t heads, int32_t head_dim, float scale);
 
+/*
+ * Scaled dot-product attention, Y = Softmax(scale * Q K^T + mask) V per (batch, head): the reference's
+ * ROperator_SDPA (core/inc/SOFIE/operators/ROperator_SDPA.hxx:38-57 constructor, :81-139 shapes, :141-200 the CPU
+ * arithmetic this follows: dot * scale, + mask, max, exp, / sum, weighted sum; GPU form :203-330).
+ *   folded = 0   Q, K [batch, heads, seq, head_dim], V [.., v_head_dim], Y [batch, heads, seq, v_head_dim]
+ *   folded = 1   Q, K, V, Y are [batch, seq, heads * dim] (ROperator_SDPA's rank-3 form with num_heads); ldq / ldk / ldv are
+ *                the row pitches in elements of Q, K, V (0 = dense), so the three column blocks of one QKV projection
+ *                output are read in place; Y is dense.
+ *   mask         additive, [batch, heads, seq, seq] F32, or absent.  scale = 0 selects 1 / sqrt(head_dim).
+ * A plan selects the fused tcgen05 kernel ("attention": BF16, folded, no mask, head sizes 64, seq <= 128; no
+ * workspace) or the operator chain the reference emits for an attention block ("chain": batched contraction, Softmax,
+ * batched contraction, with the operands gathered per head in the caller's workspace).
+ */
+typedef struct sofie_b200_sdpa_desc {
+  int64_t batch, heads, seq, head_dim, v_head_dim;   /* v_head_dim 0 = head_dim */
+  int32_t dtype;                                     /* F32 or BF16 */
+  int32_t folded;
+  int32_t has_mask;
+  float scale;
+  int64_t ldq, ldk, ldv;
+} sofie_b200_sdpa_desc;
+typedef struct sofie_b200_sdpa_plan sofie_b200_sdpa_plan;
+int sofie_b200_sdpa_plan_create(sofie_b200_ctx *ctx, const sofie_b200_sdpa_desc *desc, sofie_b200_sdpa_plan **out);
+int sofie_b200_sdpa_plan_destroy(sofie_b200_sdpa_plan *plan);
+/* "attention" or "chain". */
+const char *sofie_b200_sdpa_plan_kernel(const sofie_b200_sdpa_plan *plan);
+/* Bytes of 256-byte aligned caller scratch an enqueue needs (0 for the fused kernel). */
+int64_t sofie_b200_sdpa_workspace_bytes(const sofie_b200_sdpa_plan *plan);
+int sofie_b200_sdpa_enqueue(sofie_b200_sdpa_plan *plan, const void *q, const void *k, const void *v, const void *mask, void *y,
+                            void *workspace);
+
 /* ---- memory-bound operators the fusion pass leaves ----------------------------------- */
 
 /* LayerNormalization over the last `cols` elements of each of `rows` rows
@@ -360,6 +391,10 @@ int sofie_b200_layernorm_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, in
 /* Softmax / LogSoftmax along the last axis (ROperator_Softmax.hxx:82-119). */
 int sofie_b200_softmax_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t x_dtype,
                                int32_t y_dtype, int64_t rows, int64_t cols, int32_t log_softmax);
+/* The same along any axis: x viewed as [outer, n, inner] and normalised over n (ROperator_Softmax.hxx:120-200, the
+ * generic-axis path, which divides by the sum).  F32 or BF16, x and y of one type. */
+int sofie_b200_softmax_axis_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t dtype, int64_t outer, int64_t n,
+                                    int64_t inner, int32_t log_softmax);
 
 /* Unary elementwise y = act(x) (ROperator_Relu.hxx:47-114, ROperator_Gelu.hxx:42-123,
  * ROperator_LeakyRelu.hxx).  F32 or BF16. */

@@ -5,9 +5,20 @@
 
 static int is_t(const char *t) { return *t == 't' || *t == 'T' || *t == 'c' || *t == 'C'; }
 
+/* For the TIMED CPU baseline the emitted code should run on a real BLAS.  ref_blas_use() hands this shim the
+ * sgemm_ entry point of a BLAS the process has loaded (MKL inside libtorch_cpu.so, an OpenBLAS); sgemm_ below then
+ * forwards to it.  Without that call the plain loops run: the golden fixtures are made with those, so that they do
+ * not depend on a library version. */
+typedef void (*sgemm_fn)(const char *, const char *, const int *, const int *, const int *, const float *, const float *, const int *,
+                         const float *, const int *, const float *, float *, const int *);
+static sgemm_fn g_sgemm = 0;
+void ref_blas_use(void *sgemm_entry) { g_sgemm = (sgemm_fn)sgemm_entry; }
+int ref_blas_is_external(void) { return g_sgemm != 0; }
+
 void sgemm_(const char *transa, const char *transb, const int *m, const int *n, const int *k, const float *alpha,
             const float *A, const int *lda, const float *B, const int *ldb, const float *beta, float *C, const int *ldc)
 {
+   if (g_sgemm) { g_sgemm(transa, transb, m, n, k, alpha, A, lda, B, ldb, beta, C, ldc); return; }
    const int ta = is_t(transa), tb = is_t(transb);
 #pragma omp parallel for schedule(static)
    for (int j = 0; j < *n; ++j)

@@ -306,6 +306,54 @@ int so_layernorm(const void *x, void *y, int xd, int yd, int64_t rows, int64_t c
   return 0;
 }
 
+int so_sdpa(const float *q, const float *k, const float *v, const float *mask, float *y, int64_t B, int64_t H, int64_t S, int64_t D,
+            int64_t Dv, float scale, int folded) {
+  if (scale == 0.f) scale = 1.f / sqrtf((float)D);
+  /* strides of the two layouts, ROperator_SDPA.hxx:118-135 */
+  const int64_t qk_b = folded ? S * H * D : H * S * D, qk_h = folded ? D : S * D, qk_s = folded ? H * D : D;
+  const int64_t vy_b = folded ? S * H * Dv : H * S * Dv, vy_h = folded ? Dv : S * Dv, vy_s = folded ? H * Dv : Dv;
+  float *scores = (float *)malloc(sizeof(float) * (size_t)(S > 0 ? S : 1));
+  if (!scores) return -1;
+  for (int64_t b = 0; b < B; ++b)
+    for (int64_t h = 0; h < H; ++h)
+      for (int64_t s = 0; s < S; ++s) {
+        const int64_t qb = b * qk_b + h * qk_h + s * qk_s;
+        for (int64_t j = 0; j < S; ++j) {
+          const int64_t kb = b * qk_b + h * qk_h + j * qk_s;
+          float dot = 0;
+          for (int64_t d = 0; d < D; ++d) dot += q[qb + d] * k[kb + d];
+          scores[j] = dot * scale;
+          if (mask) scores[j] += mask[((b * H + h) * S + s) * S + j];
+        }
+        float mx = scores[0];
+        for (int64_t j = 1; j < S; ++j) if (scores[j] > mx) mx = scores[j];
+        float sum = 0;
+        for (int64_t j = 0; j < S; ++j) { scores[j] = expf(scores[j] - mx); sum += scores[j]; }
+        for (int64_t j = 0; j < S; ++j) scores[j] /= sum;
+        for (int64_t d = 0; d < Dv; ++d) {
+          float acc = 0;
+          for (int64_t j = 0; j < S; ++j) acc += scores[j] * v[b * vy_b + h * vy_h + j * vy_s + d];
+          y[b * vy_b + h * vy_h + s * vy_s + d] = acc;
+        }
+      }
+  free(scores);
+  return 0;
+}
+
+int so_softmax_axis(const float *x, float *y, int64_t outer, int64_t n, int64_t inner, int log_softmax) {
+  for (int64_t o = 0; o < outer; ++o)
+    for (int64_t i = 0; i < inner; ++i) {
+      const float *xs = x + o * n * inner + i;
+      float *ys = y + o * n * inner + i;
+      float m = xs[0];
+      for (int64_t a = 1; a < n; ++a) if (xs[a * inner] > m) m = xs[a * inner];
+      float sum = 0.f;
+      for (int64_t a = 0; a < n; ++a) { ys[a * inner] = expf(xs[a * inner] - m); sum += ys[a * inner]; }
+      for (int64_t a = 0; a < n; ++a) ys[a * inner] = log_softmax ? (xs[a * inner] - m) - logf(sum) : ys[a * inner] / sum;
+    }
+  return 0;
+}
+
 int so_softmax(const void *x, void *y, int xd, int yd, int64_t rows, int64_t cols, int log_softmax) {
   for (int64_t r = 0; r < rows; ++r) {
     float m = -INFINITY;

@@ -44,6 +44,13 @@ int so_layernorm(const void *x, void *y, int x_dtype, int y_dtype, int64_t rows,
                  const float *bias, float eps, float *mean_out, float *invstd_out);
 /* ROperator_Softmax.hxx:97-118 (max, exp, sum, multiply by reciprocal). */
 int so_softmax(const void *x, void *y, int x_dtype, int y_dtype, int64_t rows, int64_t cols, int log_softmax);
+/* ROperator_SDPA.hxx:141-200, fp32, step for step: per (batch, head, query) dot * scale (+ mask), max, exp(s - max), / sum,
+ * weighted sum over V.  folded = 0: Q, K [B,H,S,D], V, Y [B,H,S,Dv]; folded = 1: [B,S,H*D] (ROperator_SDPA.hxx:103-129).
+ * mask [B,H,S,S] or NULL; scale 0 = 1/sqrt(D).  With softmax over an axis other than the last (so_softmax_axis) this is
+ * the general-axis path of ROperator_Softmax.hxx:120-200, which divides by the sum. */
+int so_sdpa(const float *q, const float *k, const float *v, const float *mask, float *y, int64_t B, int64_t H, int64_t S, int64_t D,
+            int64_t Dv, float scale, int folded);
+int so_softmax_axis(const float *x, float *y, int64_t outer, int64_t axis_len, int64_t inner, int log_softmax);
 /* ROperator_Relu.hxx / ROperator_Gelu.hxx:62-98 / LeakyRelu / Sigmoid, elementwise, F32 or BF16. */
 int so_unary(const void *x, void *y, int dtype, int64_t n, int act, float act_alpha);
 /* ROperator_BasicBinary.hxx:520-636 with trailing broadcast; op 0 Add 1 Sub 2 Mul 3 Div. */

@@ -1,12 +1,10 @@
-"""The conv-net configuration on libsofie_b200, for bench.py.
+"""The conv-net configuration on libsofie_b200: weights, work count and the device assembly.
 
 Eight Conv 3x3 (pad 1) layers 3-64-64-128-128-256-256-512-512 with strides 1,2,1,2,1,2,1,2, each with a folded
 BatchNormalization (per-channel scale and shift in the contraction epilogue) and Relu, global average pool,
 Gemm 512 -> 1000.  Two variants: fp32 (precise: 3xTF32 on the tensor cores where large enough) and per-channel
 int8 (QLinearConv: int32 accumulation, fp32 multiplier a_scale * w_scale[c] / y_scale, int32 bias, Relu, int8 out).
 Plans, weights and every activation buffer are created once; a step only enqueues kernels.
-
-`convnet_oracle` runs the same network through the CPU restatement (oracle/): the CPU arm of the benchmark.
 """
 from __future__ import annotations
 
@@ -34,18 +32,35 @@ def conv_desc(n, c, h, w, k, stride, x_dtype, y_dtype, x_layout=0, y_layout=0, f
     return d
 
 
-def make_weights(rng, int8: bool):
-    """He-normal conv weights, BatchNormalization parameters folded to scale/shift; the int8 variant quantises the
-    weights per output channel and turns the fold into a multiplier and an int32 bias."""
+def raw_parameters(seed: int):
+    """The fp32 network as ONNX would hold it, from the reproducible generator of sofie_b200/synth.py (oracle/ref_emit.cxx
+    builds the reference's model from the same draws): per layer He-normal weights N(0, sqrt(2/fan_in)) and the
+    BatchNormalization parameters gamma ~ U(0.5, 1.5), beta ~ N(0, 0.1), mean ~ N(0, 0.1), var ~ U(0.5, 1.5); the classifier
+    N(0, sqrt(2/512)) with a zero bias."""
+    from . import synth
     layers = []
-    a_scale = IN_SCALE
     for i in range(8):
         cin, cout = CHANNELS[i], CHANNELS[i + 1]
-        wf = (rng.standard_normal((cout, cin, 3, 3)) * np.sqrt(2.0 / (cin * 9))).astype(np.float32)
-        gamma, beta = (rng.random(cout) + 0.5).astype(np.float32), (rng.standard_normal(cout) * 0.1).astype(np.float32)
-        mean, var = (rng.standard_normal(cout) * 0.1).astype(np.float32), (rng.random(cout) + 0.5).astype(np.float32)
-        scale = (gamma / np.sqrt(var + np.float32(1e-5))).astype(np.float32)
-        shift = (beta - mean * scale).astype(np.float32)
+        ts = lambda j: synth.tensor_seed(seed, 10 * i + j)
+        layers.append(dict(w=synth.normal_f32(ts(0), (cout, cin, 3, 3), np.sqrt(2.0 / (cin * 9))),
+                           gamma=synth.uniform_f32(ts(1), cout, 0.5, 1.5), beta=synth.normal_f32(ts(2), cout, 0.1),
+                           mean=synth.normal_f32(ts(3), cout, 0.1), var=synth.uniform_f32(ts(4), cout, 0.5, 1.5)))
+    fc_w = synth.normal_f32(synth.tensor_seed(seed, 100), (512, CLASSES), np.sqrt(2.0 / 512))
+    return layers, fc_w, np.zeros(CLASSES, dtype=np.float32)
+
+
+def make_weights(seed: int, int8: bool):
+    """raw_parameters() with BatchNormalization folded to a per-channel scale and shift (the fold the generator's fusion
+    pass makes); the int8 variant quantises the weights per output channel and turns the fold into a multiplier and an
+    int32 bias."""
+    raw, fc_w, fc_b = raw_parameters(seed)
+    layers = []
+    a_scale = IN_SCALE
+    for i, r in enumerate(raw):
+        cout = CHANNELS[i + 1]
+        wf = r["w"]
+        scale = (r["gamma"] / np.sqrt(r["var"] + np.float32(1e-5))).astype(np.float32)
+        shift = (r["beta"] - r["mean"] * scale).astype(np.float32)
         if not int8:
             layers.append(dict(w=wf, scale=scale, bias=shift))
         else:
@@ -56,8 +71,6 @@ def make_weights(rng, int8: bool):
             bias = np.rint(shift / (a_scale * w_scale)).astype(np.int32)   # shift at the accumulator's scale
             layers.append(dict(w=wq, scale=mult, bias=bias))
             a_scale = Y_SCALE
-    fc_w = (rng.standard_normal((512, CLASSES)) * np.sqrt(2.0 / 512)).astype(np.float32)
-    fc_b = np.zeros(CLASSES, dtype=np.float32)
     return layers, fc_w, fc_b
 
 
@@ -67,21 +80,6 @@ def flops_per_image(img: int) -> float:
         hw = (hw + 2 - 3) // st + 1
         f += 2.0 * CHANNELS[i + 1] * hw * hw * CHANNELS[i] * 9
     return f + 2.0 * 512 * CLASSES
-
-
-def convnet_oracle(o, x: np.ndarray, weights, int8: bool) -> np.ndarray:
-    """x: [n, 3, img, img] fp32 in [0,1) (fp32 variant) or int8 0..127 (int8 variant).  Returns [n, 1000] fp32 logits."""
-    from sofie_b200 import lib as L
-    layers, fc_w, fc_b = weights
-    dt = L.I8 if int8 else L.F32
-    for ly, st in zip(layers, STRIDES):
-        n, c, h, w = x.shape
-        d = conv_desc(n, c, h, w, ly["w"].shape[0], st, dt, dt)
-        ho = (h + 2 - 3) // st + 1
-        x = o.conv(x, ly["w"], d, ho, ho, ep=o.epilogue(col_scale=ly["scale"], bias=ly["bias"], act=L.ACT_RELU))
-    pooled = o.global_avgpool(x, dt) if int8 else o.global_avgpool(x)
-    ep = o.epilogue(alpha=float(Y_SCALE), bias=fc_b) if int8 else o.epilogue(bias=fc_b)
-    return o.gemm(np.ascontiguousarray(pooled, dtype=np.float32), fc_w, x.shape[0], CLASSES, 512, L.F32, L.F32, ep=ep)
 
 
 class ConvNetB200:

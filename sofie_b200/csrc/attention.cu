@@ -1,7 +1,8 @@
 // Fused scaled-dot-product attention for sequences of up to 128 tokens and a head size of 64:
 //     out[b, :, h, :] = Softmax(scale * Q K^T) V      for every (batch b, head h) pair,
-// reading Q, K and V straight out of the QKV projection's output [batch, seq, 3, heads, 64] and writing the
-// layout the output projection reads, [batch, seq, heads * 64].  The scores never leave the SM: the chain
+// reading Q, K and V as [batch, seq, heads * 64] tensors with a row pitch of their own -- three tensors, or the three column
+// blocks of the QKV projection's output [batch, seq, 3, heads, 64], read in place -- and writing the layout the output
+// projection reads, [batch, seq, heads * 64] (the folded form of ROperator_SDPA, ROperator_SDPA.hxx:103-129).  The scores never leave the SM: the chain
 // of two batched contractions, a Softmax and two transposes (the graph the reference emits for an attention
 // block: stacked MatMul, ROperator_Gemm.hxx:991-1065; Softmax, ROperator_Softmax.hxx:204-342; Transpose) moved
 // 10x the bytes through HBM that Q, K, V and the output occupy.
@@ -19,6 +20,8 @@
 //                    to shared memory (the buffer P occupied) and leaves as one bulk tensor store per warp.
 // Every wait is bounded (ptx::mbar_wait); a wait that runs out raises the abort flag and a status code.
 #include <cudaTypedefs.h>
+#include <math.h>
+#include <algorithm>
 #include <mutex>
 
 #include "gemm.cuh"
@@ -49,7 +52,8 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 __global__ void __launch_bounds__(ATT_THREADS, 1)
-attention_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ AttnParams p) {
+attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                 const __grid_constant__ CUtensorMap tm_out, const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -83,7 +87,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
     }
     *abort_flag = 0;
     fence_barrier_init();
-    prefetch_tensormap(&tm_qkv);
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_v);
     prefetch_tensormap(&tm_out);
   }
   if (warp == 1) {
@@ -115,9 +121,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_qkv, const __grid_consta
         const uint32_t full = bar_full + 8 * st;
         mbar_arrive_expect_tx(full, ATT_STAGE_BYTES);
         const uint32_t dst = sm_stage + st * ATT_STAGE_BYTES;
-        tma_load_4d(dst, &tm_qkv, full, 0, h, 0, b);                               // Q
-        tma_load_4d(dst + ATT_TILE, &tm_qkv, full, 0, p.heads + h, 0, b);          // K
-        tma_load_4d(dst + 2 * ATT_TILE, &tm_qkv, full, 0, 2 * p.heads + h, 0, b);  // V
+        tma_load_4d(dst, &tm_q, full, 0, h, 0, b);
+        tma_load_4d(dst + ATT_TILE, &tm_k, full, 0, h, 0, b);
+        tma_load_4d(dst + 2 * ATT_TILE, &tm_v, full, 0, h, 0, b);
       }
       if (!ok) {
         const uint64_t t0 = globaltimer();
@@ -323,6 +329,160 @@ static int encode_4d(CUtensorMap *tm, const void *base, uint64_t d0, uint64_t d1
 
 using namespace sb200;
 
+namespace sb200 {
+// Q, K, V: [batch, seq, heads, 64] bf16 with row pitches ldq / ldk / ldv elements (a row = one token); out: [batch, seq, heads * 64].
+static int attention_launch(sofie_b200_ctx *ctx, const void *q, const void *k, const void *v, int64_t ldq, int64_t ldk, int64_t ldv, void *out,
+                            int64_t batch, int64_t seq, int32_t heads, float scale) {
+  const uint64_t dh = 64, es = 2, H = (uint64_t)heads, S = (uint64_t)seq, B = (uint64_t)batch;
+  CUtensorMap tm_q, tm_k, tm_v, tm_out;
+  // one box = the (up to) 128 token rows of one head
+  int rc;
+  if ((rc = encode_4d(&tm_q, q, dh, H, S, B, dh * es, (uint64_t)ldq * es, S * (uint64_t)ldq * es, 128))) return rc;
+  if ((rc = encode_4d(&tm_k, k, dh, H, S, B, dh * es, (uint64_t)ldk * es, S * (uint64_t)ldk * es, 128))) return rc;
+  if ((rc = encode_4d(&tm_v, v, dh, H, S, B, dh * es, (uint64_t)ldv * es, S * (uint64_t)ldv * es, 128))) return rc;
+  // out [batch, seq, heads, 64]: one box = 32 token rows of one head (one epilogue warp)
+  if ((rc = encode_4d(&tm_out, out, dh, H, S, B, dh * es, H * dh * es, S * H * dh * es, 32))) return rc;
+  SB_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM));   // per device
+  AttnParams p{};
+  p.batch = (int)batch; p.seq = (int)seq; p.heads = heads;
+  p.pairs = (long long)batch * heads;
+  p.scale_log2e = scale * 1.4426950408889634f;
+  p.status = ctx->d_status;
+  const long long grid = p.pairs < ctx->sm_count ? p.pairs : ctx->sm_count;
+  attention_kernel<<<dim3((unsigned)grid), dim3(ATT_THREADS), ATT_SMEM, ctx->stream>>>(tm_q, tm_k, tm_v, tm_out, p);
+  SB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return 0;
+}
+
+// [B, S, ld] rows holding [H, D] -> [B, H, S, D] (gather = true) or back (gather = false, ld = H * D)
+template <class T>
+__global__ void __launch_bounds__(256) heads_layout_kernel(const T *__restrict__ src, T *__restrict__ dst, long long B, long long H, long long S,
+                                                           long long D, long long ld, bool gather) {
+  const long long total = B * H * S * D;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long d = i % D, s = (i / D) % S, h = (i / (D * S)) % H, b = i / (D * S * H);
+    const long long folded = (b * S + s) * ld + h * D + d;
+    if (gather) dst[i] = src[folded];
+    else dst[folded] = src[i];
+  }
+}
+static int heads_layout(sofie_b200_ctx *ctx, const void *src, void *dst, int es, long long B, long long H, long long S, long long D, long long ld,
+                        bool gather) {
+  const long long total = B * H * S * D;
+  const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 16);
+  if (es == 4) heads_layout_kernel<uint32_t><<<grid, 256, 0, ctx->stream>>>((const uint32_t *)src, (uint32_t *)dst, B, H, S, D, ld, gather);
+  else heads_layout_kernel<uint16_t><<<grid, 256, 0, ctx->stream>>>((const uint16_t *)src, (uint16_t *)dst, B, H, S, D, ld, gather);
+  SB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return 0;
+}
+}  // namespace sb200
+
+struct sofie_b200_sdpa_plan {
+  sofie_b200_ctx *ctx = nullptr;
+  sofie_b200_sdpa_desc d{};
+  float scale = 0.f;
+  int fused = 0;                                   // the tcgen05 attention kernel applies
+  sofie_b200_gemm_plan *qk = nullptr, *pv = nullptr;   // chain: scores and weighted sum, batched over (batch, head)
+  int64_t off_q = 0, off_k = 0, off_v = 0, off_s = 0, off_o = 0, bytes = 0;   // workspace regions
+};
+
+extern "C" {
+
+int sofie_b200_sdpa_plan_create(sofie_b200_ctx *ctx, const sofie_b200_sdpa_desc *desc, sofie_b200_sdpa_plan **out) {
+  if (!ctx || !desc || !out) return fail(SOFIE_B200_ERR_INVALID, "sdpa_plan_create: NULL argument");
+  *out = nullptr;
+  sofie_b200_sdpa_desc d = *desc;
+  if (d.batch < 0 || d.heads < 1 || d.seq < 0 || d.head_dim < 1) return fail(SOFIE_B200_ERR_INVALID, "sdpa_plan_create: bad extent");
+  if (d.v_head_dim == 0) d.v_head_dim = d.head_dim;
+  if (d.dtype != SOFIE_B200_F32 && d.dtype != SOFIE_B200_BF16) return fail(SOFIE_B200_ERR_INVALID, "sdpa_plan_create: type %d not supported (F32, BF16)", d.dtype);
+  if (!d.folded && (d.ldq || d.ldk || d.ldv)) return fail(SOFIE_B200_ERR_INVALID, "sdpa_plan_create: row pitches belong to the folded layout");
+  if (d.ldq == 0) d.ldq = d.heads * d.head_dim;
+  if (d.ldk == 0) d.ldk = d.heads * d.head_dim;
+  if (d.ldv == 0) d.ldv = d.heads * d.v_head_dim;
+  if (d.ldq < d.heads * d.head_dim || d.ldk < d.heads * d.head_dim || d.ldv < d.heads * d.v_head_dim)
+    return fail(SOFIE_B200_ERR_INVALID, "sdpa_plan_create: a row pitch is smaller than heads * head size");
+  sofie_b200_sdpa_plan *p = new sofie_b200_sdpa_plan();
+  p->ctx = ctx; p->d = d;
+  p->scale = d.scale != 0.f ? d.scale : 1.f / sqrtf((float)d.head_dim);
+  const int es = dtype_size(d.dtype);
+  p->fused = d.dtype == SOFIE_B200_BF16 && d.folded && !d.has_mask && d.head_dim == 64 && d.v_head_dim == 64 && d.seq <= 128 &&
+             (d.ldq * es) % 16 == 0 && (d.ldk * es) % 16 == 0 && (d.ldv * es) % 16 == 0 && d.batch * d.heads < 0x7fffffffLL;
+  if (p->fused || d.batch == 0 || d.seq == 0) { *out = p; return 0; }
+  // chain: [B,H,S,D] operands (gathered from the folded layout into the workspace), scores [B*H, S, S], output
+  const int64_t bh = d.batch * d.heads;
+  auto region = [&](int64_t elems) { const int64_t o = p->bytes; p->bytes += (elems * es + 255) / 256 * 256; return o; };
+  if (d.folded) { p->off_q = region(bh * d.seq * d.head_dim); p->off_k = region(bh * d.seq * d.head_dim); p->off_v = region(bh * d.seq * d.v_head_dim);
+                  p->off_o = region(bh * d.seq * d.v_head_dim); }
+  p->off_s = region(bh * d.seq * d.seq);
+  sofie_b200_gemm_desc g{};
+  g.M = d.seq; g.N = d.seq; g.K = d.head_dim; g.batch = bh; g.trans_b = 1; g.ab_dtype = g.y_dtype = d.dtype;
+  g.stride_a = g.stride_b = d.seq * d.head_dim; g.stride_y = g.stride_c = d.seq * d.seq; g.precise = 1;
+  int rc = sofie_b200_gemm_plan_create(ctx, &g, &p->qk);
+  if (rc) { delete p; return rc; }
+  g.N = d.v_head_dim; g.K = d.seq; g.trans_b = 0;
+  g.stride_a = d.seq * d.seq; g.stride_b = g.stride_y = d.seq * d.v_head_dim; g.stride_c = 0;
+  rc = sofie_b200_gemm_plan_create(ctx, &g, &p->pv);
+  if (rc) { sofie_b200_gemm_plan_destroy(p->qk); delete p; return rc; }
+  *out = p;
+  return 0;
+}
+
+int sofie_b200_sdpa_plan_destroy(sofie_b200_sdpa_plan *plan) {
+  if (!plan) return 0;
+  if (plan->qk) sofie_b200_gemm_plan_destroy(plan->qk);
+  if (plan->pv) sofie_b200_gemm_plan_destroy(plan->pv);
+  delete plan;
+  return 0;
+}
+
+const char *sofie_b200_sdpa_plan_kernel(const sofie_b200_sdpa_plan *plan) { return !plan ? "" : (plan->fused ? "attention" : "chain"); }
+
+int64_t sofie_b200_sdpa_workspace_bytes(const sofie_b200_sdpa_plan *plan) { return plan ? plan->bytes : 0; }
+
+int sofie_b200_sdpa_enqueue(sofie_b200_sdpa_plan *plan, const void *q, const void *k, const void *v, const void *mask, void *y, void *workspace) {
+  if (!plan) return fail(SOFIE_B200_ERR_INVALID, "sdpa_enqueue: plan is NULL");
+  const sofie_b200_sdpa_desc &d = plan->d;
+  if (d.batch == 0 || d.seq == 0) return 0;
+  if (!q || !k || !v || !y) return fail(SOFIE_B200_ERR_INVALID, "sdpa_enqueue: NULL tensor pointer");
+  if ((d.has_mask != 0) != (mask != nullptr)) return fail(SOFIE_B200_ERR_INVALID, "sdpa_enqueue: the mask pointer does not match the plan");
+  sofie_b200_ctx *ctx = plan->ctx;
+  SB_CUDA(cudaSetDevice(ctx->device));
+  if (plan->fused) {
+    if (((uintptr_t)q % 16) || ((uintptr_t)k % 16) || ((uintptr_t)v % 16) || ((uintptr_t)y % 16))
+      return fail(SOFIE_B200_ERR_INVALID, "sdpa_enqueue: tensors must be 16-byte aligned");
+    return attention_launch(ctx, q, k, v, d.ldq, d.ldk, d.ldv, y, d.batch, d.seq, (int32_t)d.heads, plan->scale);
+  }
+  if (!workspace || ((uintptr_t)workspace % 256)) return fail(SOFIE_B200_ERR_INVALID, "sdpa_enqueue: this plan needs a 256-byte aligned workspace");
+  const int es = dtype_size(d.dtype);
+  char *ws = static_cast<char *>(workspace);
+  const void *q4 = q, *k4 = k, *v4 = v;
+  void *o4 = y;
+  int rc;
+  if (d.folded) {
+    if ((rc = heads_layout(ctx, q, ws + plan->off_q, es, d.batch, d.heads, d.seq, d.head_dim, d.ldq, true))) return rc;
+    if ((rc = heads_layout(ctx, k, ws + plan->off_k, es, d.batch, d.heads, d.seq, d.head_dim, d.ldk, true))) return rc;
+    if ((rc = heads_layout(ctx, v, ws + plan->off_v, es, d.batch, d.heads, d.seq, d.v_head_dim, d.ldv, true))) return rc;
+    q4 = ws + plan->off_q; k4 = ws + plan->off_k; v4 = ws + plan->off_v; o4 = ws + plan->off_o;
+  }
+  void *sc = ws + plan->off_s;
+  // scores = scale * Q K^T (+ mask), rounded as the reference's CPU code rounds them (dot * scale, then + mask: ROperator_SDPA.hxx:163-170)
+  sofie_b200_epilogue e{};
+  e.alpha = plan->scale; e.beta = 1.f; e.out_scale = 1.f;
+  if (mask) {
+    if (d.dtype != SOFIE_B200_F32) return fail(SOFIE_B200_ERR_INVALID, "sdpa_enqueue: a mask is supported for F32 tensors");
+    e.bias_mode = SOFIE_B200_BIAS_FULL_F32; e.bias = mask; e.ldc = d.seq;
+  }
+  if ((rc = sofie_b200_gemm_enqueue(plan->qk, q4, k4, sc, &e))) return rc;
+  if ((rc = sofie_b200_softmax_enqueue(ctx, sc, sc, d.dtype, d.dtype, d.batch * d.heads * d.seq, d.seq, 0))) return rc;
+  if ((rc = sofie_b200_gemm_enqueue(plan->pv, sc, v4, o4, nullptr))) return rc;
+  if (d.folded) return heads_layout(ctx, o4, y, es, d.batch, d.heads, d.seq, d.v_head_dim, d.heads * d.v_head_dim, false);
+  return 0;
+}
+
+}  // extern "C"
+
 extern "C" int sofie_b200_attention_enqueue(sofie_b200_ctx *ctx, const void *qkv, void *out, int32_t dtype, int64_t batch, int64_t seq,
                                             int32_t heads, int32_t head_dim, float scale) {
   if (!ctx) return fail(SOFIE_B200_ERR_INVALID, "attention_enqueue: ctx is NULL");
@@ -334,23 +494,8 @@ extern "C" int sofie_b200_attention_enqueue(sofie_b200_ctx *ctx, const void *qkv
   if (batch < 0 || heads < 1 || batch > 0x7fffffffLL / heads) return fail(SOFIE_B200_ERR_INVALID, "attention_enqueue: bad batch / heads");
   if (((uintptr_t)qkv % 16) || ((uintptr_t)out % 16)) return fail(SOFIE_B200_ERR_INVALID, "attention_enqueue: tensors must be 16-byte aligned");
   SB_CUDA(cudaSetDevice(ctx->device));
-  const uint64_t dh = 64, es = 2, H = (uint64_t)heads, S = (uint64_t)seq, B = (uint64_t)batch;
-  CUtensorMap tm_qkv, tm_out;
-  // qkv [batch, seq, 3 * heads, 64]: one box = the 128 token rows of one of Q / K / V of one head
-  int rc = encode_4d(&tm_qkv, qkv, dh, 3 * H, S, B, dh * es, 3 * H * dh * es, S * 3 * H * dh * es, 128);
-  if (rc) return rc;
-  // out [batch, seq, heads, 64]: one box = 32 token rows of one head (one epilogue warp)
-  rc = encode_4d(&tm_out, out, dh, H, S, B, dh * es, H * dh * es, S * H * dh * es, 32);
-  if (rc) return rc;
-  SB_CUDA(cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM));   // per device
-  AttnParams p{};
-  p.batch = (int)batch; p.seq = (int)seq; p.heads = heads;
-  p.pairs = (long long)batch * heads;
-  p.scale_log2e = scale * 1.4426950408889634f;
-  p.status = ctx->d_status;
-  const long long grid = p.pairs < ctx->sm_count ? p.pairs : ctx->sm_count;
-  attention_kernel<<<dim3((unsigned)grid), dim3(ATT_THREADS), ATT_SMEM, ctx->stream>>>(tm_qkv, tm_out, p);
-  SB_CUDA(cudaGetLastError());
-  ctx->launches++;
-  return 0;
+  // qkv [batch, seq, 3, heads, 64]: Q, K and V are the three column blocks of a row of 3 * heads * 64 elements
+  const int64_t hd = (int64_t)heads * 64;
+  const char *base = static_cast<const char *>(qkv);
+  return attention_launch(ctx, base, base + hd * 2, base + 2 * hd * 2, 3 * hd, 3 * hd, 3 * hd, out, batch, seq, heads, scale);
 }

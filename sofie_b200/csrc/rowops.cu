@@ -11,6 +11,8 @@
 // variance of x-mean), invStd = 1/sqrt(var+eps), y = scale*invStd*(x-mean)+bias
 // (ROperator_LayerNormalization.hxx:257-312); Softmax is max, exp(x-max), sum, multiply by the
 // reciprocal of the sum (ROperator_Softmax.hxx:97-118).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace sb200 {
@@ -347,6 +349,30 @@ static int dispatch_rows(sofie_b200_ctx *ctx, const void *x, void *y, int xd, in
   return fail(SOFIE_B200_ERR_INVALID, "row operator: types %d -> %d not supported (F32 and BF16 only)", xd, yd);
 }
 
+// Softmax / LogSoftmax along an axis that is not the last one: x viewed as [outer, n, inner], normalised over n.  One thread
+// per (outer, inner) column walks the axis three times (maximum, exp and sum, normalise); neighbouring threads hold
+// neighbouring inner positions, so every pass is coalesced.  The generic-axis path of the reference divides by the sum
+// (ROperator_Softmax.hxx:120-200), as this does.
+template <class T>
+__global__ void __launch_bounds__(256) softmax_axis_kernel(const T *__restrict__ x, T *__restrict__ y, long long outer, long long n, long long inner,
+                                                           int log_softmax) {
+  const long long total = outer * inner;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const long long o = t / inner, i = t - o * inner;
+    const T *xs = x + o * n * inner + i;
+    T *ys = y + o * n * inner + i;
+    float m = ld_as_float(xs);
+    for (long long a = 1; a < n; ++a) m = fmaxf(m, ld_as_float(xs + a * inner));
+    float sum = 0.f;
+    for (long long a = 0; a < n; ++a) sum += expf(ld_as_float(xs + a * inner) - m);
+    const float ls = logf(sum);
+    for (long long a = 0; a < n; ++a) {
+      const float v = ld_as_float(xs + a * inner) - m;
+      st_from_float(ys + a * inner, log_softmax ? v - ls : __fdiv_rn(expf(v), sum));
+    }
+  }
+}
+
 }  // namespace sb200
 
 using namespace sb200;
@@ -373,6 +399,25 @@ int sofie_b200_softmax_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int3
   SB_CUDA(cudaSetDevice(ctx->device));
   if (log_softmax) return dispatch_rows<2>(ctx, x, y, x_dtype, y_dtype, rows, cols, nullptr, nullptr, 0.f, nullptr, nullptr);
   return dispatch_rows<1>(ctx, x, y, x_dtype, y_dtype, rows, cols, nullptr, nullptr, 0.f, nullptr, nullptr);
+}
+
+int sofie_b200_softmax_axis_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t dtype, int64_t outer, int64_t n, int64_t inner,
+                                    int32_t log_softmax) {
+  if (!ctx) return fail(SOFIE_B200_ERR_INVALID, "softmax_axis_enqueue: ctx is NULL");
+  if (outer < 0 || n < 0 || inner < 0) return fail(SOFIE_B200_ERR_INVALID, "softmax_axis_enqueue: negative extent");
+  if (outer * n * inner == 0) return 0;
+  if (!x || !y) return fail(SOFIE_B200_ERR_INVALID, "softmax_axis_enqueue: NULL tensor");
+  SB_CUDA(cudaSetDevice(ctx->device));
+  if (inner == 1) return sofie_b200_softmax_enqueue(ctx, x, y, dtype, dtype, outer, n, log_softmax);
+  const long long total = outer * inner;
+  const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 16);
+  if (dtype == SOFIE_B200_F32) softmax_axis_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float *)x, (float *)y, outer, n, inner, log_softmax);
+  else if (dtype == SOFIE_B200_BF16)
+    softmax_axis_kernel<__nv_bfloat16><<<grid, 256, 0, ctx->stream>>>((const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, outer, n, inner, log_softmax);
+  else return fail(SOFIE_B200_ERR_INVALID, "softmax_axis_enqueue: type %d not supported (F32, BF16)", dtype);
+  SB_CUDA(cudaGetLastError());
+  ctx->launches++;
+  return 0;
 }
 
 }  // extern "C"

@@ -1,13 +1,10 @@
-"""The transformer-encoder configuration on libsofie_b200, for bench.py and the parity tests.
+"""The transformer-encoder configuration on libsofie_b200: weights, work count and the device assembly.
 
 Pre-LayerNorm encoder layers: LN -> QKV projection -> per-head Softmax(Q K^T / sqrt(d_h)) V -> output projection
 + residual -> LN -> FFN (Gelu) -> + residual.  Activations are bf16; the four projection weights of a layer are
 int8 with one fp32 scale per output channel, converted to bf16 once at construction, the scale applied as the
 column scale of the contraction's epilogue together with bias, Gelu and the residual add.  Every operator is one
 call of the C ABI (sofie_b200/ops.py); all buffers are allocated once, a step allocates nothing.
-
-`encoder_oracle` composes the same graph from the CPU restatement (oracle/), rounding to bf16 at the same tensor
-boundaries; it is the checker of the tests and the CPU arm of the benchmark.
 """
 from __future__ import annotations
 
@@ -20,17 +17,23 @@ def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
     return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
 
 
-def make_weights(rng, layers: int, d_model: int, ffn: int):
-    """int8 per-output-channel weights ~N(0, 0.02) with scale = absmax/127, fp32 biases, LN gamma 1 / beta 0."""
-    def qlinear(n_out, n_in):
-        w = rng.standard_normal((n_out, n_in)).astype(np.float32) * 0.02
-        scale = (np.abs(w).max(axis=1) / 127.0).astype(np.float32)
+def make_weights(seed: int, layers: int, d_model: int, ffn: int):
+    """int8 per-output-channel weights ~N(0, 0.02) with scale = absmax/127, fp32 biases ~N(0, 0.02), LN gamma 1 / beta 0,
+    from the reproducible generator of sofie_b200/synth.py (oracle/ref_emit.cxx builds the reference's fp32 model from the
+    same draws, with the weights dequantised: float(q) * scale)."""
+    from . import synth
+
+    def qlinear(sw, sb, n_out, n_in):
+        w = synth.normal_f32(sw, (n_out, n_in), 0.02)
+        scale = (np.abs(w).max(axis=1) / np.float32(127.0)).astype(np.float32)
         q = np.clip(np.rint(w / scale[:, None]), -127, 127).astype(np.int8)
-        return q, scale, (rng.standard_normal(n_out) * 0.02).astype(np.float32)
+        return q, scale, synth.normal_f32(sb, n_out, 0.02)
     out = []
-    for _ in range(layers):
-        out.append({"qkv": qlinear(3 * d_model, d_model), "out": qlinear(d_model, d_model), "ff1": qlinear(ffn, d_model),
-                    "ff2": qlinear(d_model, ffn), "g1": np.ones(d_model, np.float32), "b1": np.zeros(d_model, np.float32),
+    for l in range(layers):
+        ts = lambda j: synth.tensor_seed(seed, 10 * l + j)
+        out.append({"qkv": qlinear(ts(0), ts(1), 3 * d_model, d_model), "out": qlinear(ts(2), ts(3), d_model, d_model),
+                    "ff1": qlinear(ts(4), ts(5), ffn, d_model), "ff2": qlinear(ts(6), ts(7), d_model, ffn),
+                    "g1": np.ones(d_model, np.float32), "b1": np.zeros(d_model, np.float32),
                     "g2": np.ones(d_model, np.float32), "b2": np.zeros(d_model, np.float32)})
     return out
 
@@ -43,55 +46,6 @@ def flops_per_sample(layers: int, seq: int, d_model: int, ffn: int) -> float:
 
 def bf16_bits_to_f32(a: np.ndarray) -> np.ndarray:
     return (np.ascontiguousarray(a, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
-
-
-def attention_oracle(o, qkv_bits: np.ndarray, batch: int, seq: int, heads: int, dh: int, scale: float) -> np.ndarray:
-    """Checker of the fused attention kernel, with its roundings: fp32 scores, exp(scale*s - max) rounded to bf16
-    (unnormalised), second contraction on those, division by the sum of the rounded values, bf16 result.
-    qkv_bits: [batch, seq, 3, heads, dh] bf16 bit patterns; returns [batch*seq, heads*dh] bf16 bit patterns."""
-    from sofie_b200 import lib as L
-    t = np.ascontiguousarray(qkv_bits.reshape(batch, seq, 3 * heads, dh).transpose(2, 0, 1, 3))   # [3H, B, S, dh]
-    q, k, v = (np.ascontiguousarray(t[i * heads:(i + 1) * heads]).reshape(heads * batch, seq, dh) for i in range(3))
-    sc = o.gemm(q, k, seq, seq, dh, L.BF16, L.F32, False, True, batch=heads * batch).reshape(heads * batch, seq, seq)
-    z = sc.astype(np.float64) * scale
-    e = np.exp(z - z.max(axis=-1, keepdims=True)).astype(np.float32)
-    pb = f32_to_bf16_bits(e)
-    den = bf16_bits_to_f32(pb).astype(np.float64).sum(axis=-1, keepdims=True)
-    ov = o.gemm(pb, v, seq, dh, seq, L.BF16, L.F32, False, False, batch=heads * batch).reshape(heads * batch, seq, dh)
-    a = f32_to_bf16_bits((ov / den).astype(np.float32))
-    return np.ascontiguousarray(a.reshape(heads, batch, seq, dh).transpose(1, 2, 0, 3)).reshape(batch * seq, heads * dh)
-
-
-def encoder_oracle(o, x_bits: np.ndarray, weights, batch: int, seq: int, d_model: int, heads: int, fused_attention: bool = False):
-    """x_bits: [batch*seq, d_model] bf16 bit patterns.  Returns the output activations as bf16 bit patterns.
-    `fused_attention` selects the roundings of the fused attention kernel instead of those of the operator chain."""
-    from sofie_b200 import lib as L
-    dh = d_model // heads
-    m = batch * seq
-    x = x_bits
-
-    def linear(a, wq, scale, bias, act=L.ACT_NONE, residual=None):
-        w = f32_to_bf16_bits(wq.astype(np.float32))  # int8 values are exact in bf16
-        ep = o.epilogue(col_scale=scale, bias=bias, act=act, residual=residual, residual_dtype=L.BF16)
-        return o.gemm(a, w, m, wq.shape[0], wq.shape[1], L.BF16, L.BF16, False, True, ep=ep)
-
-    for ly in weights:
-        h = o.layernorm(x, ly["g1"], ly["b1"], 1e-5, L.BF16)
-        qkv = linear(h, *ly["qkv"])
-        if fused_attention:
-            a = attention_oracle(o, qkv, batch, seq, heads, dh, 1.0 / np.sqrt(dh))
-        else:
-            t = np.ascontiguousarray(qkv.reshape(batch, seq, 3 * heads, dh).transpose(2, 0, 1, 3))   # [3H, B, S, dh]
-            q, k, v = (np.ascontiguousarray(t[i * heads:(i + 1) * heads]).reshape(heads * batch, seq, dh) for i in range(3))
-            sc = o.gemm(q, k, seq, seq, dh, L.BF16, L.BF16, False, True, batch=heads * batch, ep=o.epilogue(alpha=1.0 / np.sqrt(dh)))
-            p = o.softmax(sc.reshape(-1, seq), L.BF16).reshape(heads * batch, seq, seq)
-            a = o.gemm(p, v, seq, dh, seq, L.BF16, L.BF16, False, False, batch=heads * batch)
-            a = np.ascontiguousarray(a.reshape(heads, batch, seq, dh).transpose(1, 2, 0, 3)).reshape(m, d_model)
-        x = linear(a, *ly["out"], residual=x)
-        h = o.layernorm(x, ly["g2"], ly["b2"], 1e-5, L.BF16)
-        f = linear(h, *ly["ff1"], act=L.ACT_GELU_ERF)
-        x = linear(f, *ly["ff2"], residual=x)
-    return x
 
 
 class EncoderB200:

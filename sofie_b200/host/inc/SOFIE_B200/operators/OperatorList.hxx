@@ -4,3 +4,4 @@
 #include "SOFIE_B200/operators/ROperator_Elementwise.hxx"
 #include "SOFIE_B200/operators/ROperator_Gemm.hxx"
 #include "SOFIE_B200/operators/ROperator_Quantized.hxx"
+#include "SOFIE_B200/operators/ROperator_Sequence.hxx"

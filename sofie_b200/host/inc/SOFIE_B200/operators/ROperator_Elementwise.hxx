@@ -285,6 +285,7 @@ class ROperator_Softmax final : public ROperator_B200 {
    std::string fNX, fNY;
    std::vector<size_t> fShape;
    bool fLogSoftmax;
+   size_t fAxis = 0;
    ETensorType fType = ETensorType::FLOAT;
 
 public:
@@ -301,8 +302,8 @@ public:
       fType = model.GetTensorType(fNX);
       const int64_t rank = int64_t(fShape.size());
       const int64_t axis = fAttrAxis < 0 ? fAttrAxis + rank : fAttrAxis;
-      if (axis != rank - 1)
-         throw std::runtime_error("SOFIE Softmax Op: only the last axis is on the B200 path (transpose first), got axis " + std::to_string(fAttrAxis));
+      if (axis < 0 || axis >= rank) throw std::runtime_error("SOFIE Softmax Op: axis " + std::to_string(fAttrAxis) + " out of range");
+      fAxis = size_t(axis);
       model.AddIntermediateTensor(fNY, fType, fShape);
    }
    std::string Generate_GPU_B200(std::string opName) override
@@ -311,6 +312,14 @@ public:
       const size_t cols = fShape.back(), rows = ConvertShapeToLength(fShape) / (cols ? cols : 1);
       std::stringstream out;
       out << "\n      //------ " << (fLogSoftmax ? "LogSoftmax " : "Softmax ") << opName << "\n";
+      if (fAxis + 1 != fShape.size()) {   // any other axis: [outer, n, inner] (ROperator_Softmax.hxx:120-200)
+         size_t outer = 1, inner = 1;
+         for (size_t i = 0; i < fAxis; ++i) outer *= fShape[i];
+         for (size_t i = fAxis + 1; i < fShape.size(); ++i) inner *= fShape[i];
+         out << "      Check(sofie_b200_softmax_axis_enqueue(ctx, tensor_" << fNX << ", tensor_" << fNY << ", " << ConvertTypeToRuntimeEnum(fType) << ", "
+             << outer << ", " << fShape[fAxis] << ", " << inner << ", " << (fLogSoftmax ? 1 : 0) << "), \"Softmax " << opName << "\");\n";
+         return out.str();
+      }
       out << "      Check(sofie_b200_softmax_enqueue(ctx, tensor_" << fNX << ", tensor_" << fNY << ", " << ConvertTypeToRuntimeEnum(fType) << ", "
           << ConvertTypeToRuntimeEnum(fType) << ", " << rows << ", " << cols << ", " << (fLogSoftmax ? 1 : 0) << "), \"Softmax " << opName << "\");\n";
       return out.str();

@@ -323,6 +323,16 @@ const std::map<std::string, Maker> &Makers()
        }},
       {"Softmax", [](const Node &n) -> std::unique_ptr<ROperator> { return std::make_unique<ROperator_Softmax>(Int(n, "axis", -1), n.input[0], n.output[0]); }},
       {"LogSoftmax", [](const Node &n) -> std::unique_ptr<ROperator> { return std::make_unique<ROperator_Softmax>(Int(n, "axis", -1), n.input[0], n.output[0], true); }},
+      {"ScaledDotProductAttention", [](const Node &n) -> std::unique_ptr<ROperator> {
+          // inputs and attributes of parsers/src/ParseSDPA.cxx:10-29
+          if (n.input.size() < 3) throw std::runtime_error("SOFIE ParseSDPA: need at least 3 inputs (query, key, value)");
+          return std::make_unique<ROperator_SDPA<float>>(n.input[0], n.input[1], n.input[2], n.output[0], In(n, 3), Float(n, "scale", 0.f),
+                                                         size_t(Int(n, "num_heads", 0)));
+       }},
+      {"Transpose", [](const Node &n) -> std::unique_ptr<ROperator> {
+          auto p = Ints(n, "perm");
+          return std::make_unique<ROperator_Transpose>(std::vector<int64_t>(p.begin(), p.end()), n.input[0], n.output[0]);
+       }},
       {"Add", [](const Node &n) -> std::unique_ptr<ROperator> { return std::make_unique<ROperator_BasicBinary<float, EBasicBinaryOperator::Add>>(n.input[0], n.input[1], n.output[0]); }},
       {"Sub", [](const Node &n) -> std::unique_ptr<ROperator> { return std::make_unique<ROperator_BasicBinary<float, EBasicBinaryOperator::Sub>>(n.input[0], n.input[1], n.output[0]); }},
       {"Mul", [](const Node &n) -> std::unique_ptr<ROperator> { return std::make_unique<ROperator_BasicBinary<float, EBasicBinaryOperator::Mul>>(n.input[0], n.input[1], n.output[0]); }},
@@ -362,7 +372,6 @@ std::vector<std::string> RModelParser_ONNX::GetRegisteredOperators()
 {
    std::vector<std::string> v;
    for (auto &kv : Makers()) v.push_back(kv.first);
-   v.push_back("Transpose (only as the trans flag of a MatMul)");
    v.push_back("Identity");
    return v;
 }
@@ -372,7 +381,7 @@ bool RModelParser_ONNX::CheckModel(std::string filename, bool verbose)
    Graph g = onnx_wire::LoadModel(filename);
    std::set<std::string> missing;
    for (auto &n : g.node)
-      if (!Makers().count(n.op_type) && n.op_type != "Identity" && n.op_type != "Transpose") missing.insert(n.op_type);
+      if (!Makers().count(n.op_type) && n.op_type != "Identity") missing.insert(n.op_type);
    if (verbose || !missing.empty())
       for (auto &m : missing) std::cout << "operator " << m << " is not supported" << std::endl;
    return missing.empty();
@@ -429,7 +438,7 @@ RModel RModelParser_ONNX::Parse(std::string filename, bool verbose)
             transposed[n.output[0]] = true;
             continue;
          }
-         throw std::runtime_error("SOFIE Operator type Transpose is supported on the B200 path only as the transposition of a MatMul operand");
+         // any other Transpose is an operator of its own (ROperator_Transpose)
       }
       // a fused consumer was already emitted together with its producer
       if (fuseInto.count(i)) continue;

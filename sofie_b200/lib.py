@@ -70,6 +70,14 @@ class ConvDesc(C.Structure):
     ]
 
 
+class SdpaDesc(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int64), ("heads", C.c_int64), ("seq", C.c_int64), ("head_dim", C.c_int64), ("v_head_dim", C.c_int64),
+        ("dtype", C.c_int32), ("folded", C.c_int32), ("has_mask", C.c_int32), ("scale", C.c_float),
+        ("ldq", C.c_int64), ("ldk", C.c_int64), ("ldv", C.c_int64),
+    ]
+
+
 class TensorLife(C.Structure):
     _fields_ = [("begin", C.c_int64), ("end", C.c_int64), ("size", C.c_int64)]
 
@@ -101,8 +109,14 @@ PROTOTYPES = {
     "sofie_b200_conv_enqueue": (C.c_int, [_P, _P, _P, _P, C.POINTER(Epilogue)]),
     "sofie_b200_conv_enqueue_noalloc": (C.c_int, [_P, C.POINTER(ConvDesc), _P, _P, _P, C.POINTER(Epilogue)]),
     "sofie_b200_attention_enqueue": (C.c_int, [_P, _P, _P, _I32, _I64, _I64, _I32, _I32, _F]),
+    "sofie_b200_sdpa_plan_create": (C.c_int, [_P, C.POINTER(SdpaDesc), C.POINTER(_P)]),
+    "sofie_b200_sdpa_plan_destroy": (C.c_int, [_P]),
+    "sofie_b200_sdpa_plan_kernel": (C.c_char_p, [_P]),
+    "sofie_b200_sdpa_workspace_bytes": (_I64, [_P]),
+    "sofie_b200_sdpa_enqueue": (C.c_int, [_P, _P, _P, _P, _P, _P, _P]),
     "sofie_b200_layernorm_enqueue": (C.c_int, [_P, _P, _P, _I32, _I32, _I64, _I64, _P, _P, _F, _P, _P]),
     "sofie_b200_softmax_enqueue": (C.c_int, [_P, _P, _P, _I32, _I32, _I64, _I64, _I32]),
+    "sofie_b200_softmax_axis_enqueue": (C.c_int, [_P, _P, _P, _I32, _I64, _I64, _I64, _I32]),
     "sofie_b200_unary_enqueue": (C.c_int, [_P, _P, _P, _I32, _I64, _I32, _F]),
     "sofie_b200_binary_enqueue": (C.c_int, [_P, _P, _P, _P, _I32, _I64, _I64, _I32, _I32]),
     "sofie_b200_batchnorm_enqueue": (C.c_int, [_P, _P, _P, _I64, _I64, _I64, _P, _P, _P, _I32]),

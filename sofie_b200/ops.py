@@ -6,6 +6,8 @@ libsofie_b200.so.  Tensors must live on the context's CUDA device.
 from __future__ import annotations
 
 import ctypes as C
+
+import numpy as np
 from typing import Optional
 
 import torch
@@ -82,6 +84,40 @@ class Context:
         L.check(self._lib.sofie_b200_softmax_enqueue(
             self._h, _ptr(x), _ptr(y), dtype_code(x.dtype), dtype_code(y.dtype), rows, cols, int(log_softmax)),
             "softmax_enqueue")
+
+    def softmax_axis(self, x, y, axis, log_softmax=False):
+        """Softmax over `axis` of a contiguous tensor (any axis)."""
+        axis = axis + x.dim() if axis < 0 else axis
+        outer = int(np.prod(x.shape[:axis])) if axis else 1
+        inner = int(np.prod(x.shape[axis + 1:])) if axis + 1 < x.dim() else 1
+        L.check(self._lib.sofie_b200_softmax_axis_enqueue(self._h, _ptr(x), _ptr(y), dtype_code(x.dtype), outer, x.shape[axis], inner,
+                                                          int(log_softmax)), "softmax_axis_enqueue")
+
+    def sdpa(self, q, k, v, y, mask=None, scale=0.0, heads=0, ldq=0, ldk=0, ldv=0):
+        """Scaled dot-product attention through an SDPA plan made for this call.  Rank-4 tensors are [B,H,S,D]; rank-3
+        tensors are folded [B,S,H*D] and need `heads` (ldq / ldk / ldv: row pitches when Q, K, V are column blocks of a
+        wider tensor).  Returns the kernel family that ran ("attention" or "chain")."""
+        import torch
+        d = L.SdpaDesc()
+        if q.dim() == 4:
+            d.batch, d.heads, d.seq, d.head_dim = q.shape
+            d.v_head_dim, d.folded = v.shape[3], 0
+        else:
+            d.batch, d.seq = q.shape[0], q.shape[1]
+            d.heads, d.folded = heads, 1
+            d.head_dim, d.v_head_dim = q.shape[2] // heads, y.shape[2] // heads
+            d.ldq, d.ldk, d.ldv = ldq, ldk, ldv
+        d.dtype, d.has_mask, d.scale = dtype_code(q.dtype), int(mask is not None), float(scale)
+        h = C.c_void_p()
+        L.check(self._lib.sofie_b200_sdpa_plan_create(self._h, C.byref(d), C.byref(h)), "sdpa_plan_create")
+        try:
+            ws = torch.empty(max(256, self._lib.sofie_b200_sdpa_workspace_bytes(h)), dtype=torch.uint8, device=q.device)
+            L.check(self._lib.sofie_b200_sdpa_enqueue(h, _ptr(q), _ptr(k), _ptr(v), _ptr(mask), _ptr(y), _ptr(ws)), "sdpa_enqueue")
+            kernel = self._lib.sofie_b200_sdpa_plan_kernel(h).decode()
+            self.sync()   # the workspace is released on return
+        finally:
+            self._lib.sofie_b200_sdpa_plan_destroy(h)
+        return kernel
 
     def unary(self, x, y, act, act_alpha=0.0):
         L.check(self._lib.sofie_b200_unary_enqueue(self._h, _ptr(x), _ptr(y), dtype_code(x.dtype), x.numel(), act,

@@ -56,7 +56,7 @@ def parse_ref_hxx(name: str) -> dict[str, np.ndarray]:
         if cand.exists():
             text = cand.read_text()
             out = {}
-            for m in re.finditer(r"float\s+(\w+)\s*\[\s*\]\s*=\s*\{([^}]*)\}", text, re.S):
+            for m in re.finditer(r"float\s+(\w+)\s*\[\s*\d*\s*\]\s*=\s*\{([^}]*)\}", text, re.S):
                 vals = [float(v.rstrip("fF")) for v in re.split(r"[,\s]+", m.group(2).strip()) if v]
                 out[m.group(1)] = np.array(vals, dtype=np.float32)
             return out
@@ -138,6 +138,21 @@ def main() -> None:
             else:
                 ins_a.append(rng.standard_normal(shp).astype(np.float32))
         ins_b = [rng.standard_normal(shp).astype(np.float32) for shp in shapes]
+        if name == "SDPA":      # the reference test's own operands (tests/alpaka/TestAlpakaSequenceOps.cxx: SDPA)
+            lit = parse_ref_hxx("SDPA_input")
+            ins_a = [lit[k].reshape(shp) for k, shp in zip(("Q", "K", "V"), shapes)]
+        if name == "SDPABig":   # the generator of the reference test (same file: SDPABig): an LCG, every fifth key masked
+            state = 12345
+            def rnd():
+                nonlocal state
+                state = (1103515245 * state + 12345) & 0xFFFFFFFF
+                return np.float32(np.float32(state & 0x7FFFFFFF) / np.float32(0x7FFFFFFF)) * np.float32(2.0) - np.float32(1.0)
+            n = int(np.prod(shapes[0]))
+            qkv = np.array([rnd() for _ in range(3 * n)], dtype=np.float32).reshape(n, 3)
+            mask = np.where(np.arange(int(np.prod(shapes[3]))) % 5 == 0, np.float32(-1e9), np.float32(0)).astype(np.float32)
+            ins_a = [qkv[:, 0].reshape(shapes[0]).copy(), qkv[:, 1].reshape(shapes[1]).copy(), qkv[:, 2].reshape(shapes[2]).copy(), mask.reshape(shapes[3])]
+            ins_b[3] = np.where(rng.random(shapes[3]) < 0.2, np.float32(-1e9), np.float32(0)).astype(np.float32)
+            ins_b[3][..., 0] = 0   # never a fully masked row
         out_a, out_b = ref_infer(name, ins_a), ref_infer(name, ins_b)
         arrays = {"graph": np.array(graph_json(g)), "outA": out_a, "outB": out_b}
         for i, (a, b) in enumerate(zip(ins_a, ins_b)):
@@ -145,7 +160,7 @@ def main() -> None:
         for k, v in g.initializers.items():
             arrays[f"w:{k}"] = v
         exp = parse_ref_hxx(name)
-        if exp and kind[0] in ("ones", "iota", "literal"):
+        if exp and (kind[0] in ("ones", "iota", "literal") or name == "SDPA"):
             first = next(iter(exp.values()))
             if first.size == out_a.size:
                 arrays["expected"] = first
@@ -174,6 +189,23 @@ def main() -> None:
         arrays[f"w:B{l}"] = w[f"B{l}"]
     np.savez_compressed(HERE / "MLP_C1.npz", **arrays)
     print("MLP_C1: out", arrays["outA"].size)
+
+    # The conv-net and transformer-encoder configurations at reduced size, built through the reference's C++ model API by
+    # oracle/ref_emit.cxx with weights from the reproducible generator (sofie_b200/synth.py): the fixtures hold only the
+    # input and what the reference's emitted code computed; the tests draw the same weights again.
+    sys.path.insert(0, str(ROOT))
+    from sofie_b200 import synth
+    from sofie_b200.encoder import bf16_bits_to_f32, f32_to_bf16_bits
+    (HERE / "configs").mkdir(exist_ok=True)
+    x = synth.uniform_f32(synth.tensor_seed(11, 900), (2, 3, 32, 32), 0.0, 1.0)
+    y = ref_infer("ConvNet_C4r", [x]).reshape(2, 1000)
+    np.savez_compressed(HERE / "configs" / "ConvNet_C4r.npz", x=x, y=y, seed=np.int64(11))
+    print("ConvNet_C4r: out", y.shape, "rms", float(np.sqrt(np.mean(y * y))))
+    # encoder input: N(0,1) tokens rounded to bf16 (the GPU path's activation type), given to the reference as fp32
+    xe = bf16_bits_to_f32(f32_to_bf16_bits(synth.normal_f32(synth.tensor_seed(7, 900), (2 * 128, 512), 1.0)))
+    ye = ref_infer("Encoder_C5r", [xe]).reshape(2 * 128, 512)
+    np.savez_compressed(HERE / "configs" / "Encoder_C5r.npz", x=xe, y=ye, seed=np.int64(7), layers=np.int64(2), batch=np.int64(2))
+    print("Encoder_C5r: out", ye.shape, "absmax", float(np.abs(ye).max()))
 
 
 if __name__ == "__main__":

@@ -136,6 +136,19 @@ class OracleBackend:
         self.lib.so_softmax(self._p(x), self._p(y), L.F32, L.F32, C.c_int64(x.size // cols), C.c_int64(cols), 0)
         return y
 
+    def softmax_axis(self, x, axis):
+        y = np.zeros_like(x)
+        outer, inner = int(np.prod(x.shape[:axis])), int(np.prod(x.shape[axis + 1:]))
+        self.lib.so_softmax_axis(self._p(x), self._p(y), C.c_int64(outer), C.c_int64(x.shape[axis]), C.c_int64(inner), 0)
+        return y
+
+    def sdpa(self, q, k, v, mask):
+        B, H, S, D = q.shape
+        y = np.zeros((B, H, S, v.shape[3]), dtype=np.float32)
+        self.lib.so_sdpa(self._p(q), self._p(k), self._p(v), self._p(mask), self._p(y), C.c_int64(B), C.c_int64(H), C.c_int64(S),
+                         C.c_int64(D), C.c_int64(v.shape[3]), C.c_float(0.0), 0)
+        return y
+
     def unary(self, x, act, act_alpha=0.0):
         y = np.zeros_like(x)
         self.lib.so_unary(self._p(x), self._p(y), L.F32, C.c_int64(x.size), act, C.c_float(act_alpha))
@@ -229,6 +242,17 @@ class B200Backend:
         self.ctx.sync()
         return y
 
+    def softmax_axis(self, x, axis):
+        y = self.torch.empty_like(x)
+        self.ctx.softmax_axis(x, y, axis)
+        self.ctx.sync()
+        return y
+
+    def sdpa(self, q, k, v, mask):
+        y = self.torch.empty((q.shape[0], q.shape[1], q.shape[2], v.shape[3]), dtype=q.dtype, device=q.device)
+        self.ctx.sdpa(q, k, v, y, mask=mask)
+        return y
+
     def unary(self, x, act, act_alpha=0.0):
         y = self.torch.empty_like(x)
         self.ctx.unary(x, y, act, act_alpha)
@@ -298,11 +322,10 @@ def run_graph(fx: dict, inputs: list, backend) -> np.ndarray:
             axis = axis + x.ndim if axis < 0 else axis
             if axis == x.ndim - 1:
                 y = backend.softmax_last(x, x.shape[-1])
-            else:  # move the axis last, normalise, move it back
-                perm = [d for d in range(x.ndim) if d != axis] + [axis]
-                inv = [perm.index(d) for d in range(x.ndim)]
-                xt = backend.transpose_copy(x, perm)
-                y = backend.transpose_copy(backend.softmax_last(xt, xt.shape[-1]), inv)
+            else:
+                y = backend.softmax_axis(x, axis)
+        elif op == "ScaledDotProductAttention":
+            y = backend.sdpa(ins[0], ins[1], ins[2], ins[3] if len(ins) > 3 else None)
         elif op in ACT_OF:
             y = backend.unary(ins[0], ACT_OF[op], float(at.get("alpha", 0.01)))
         elif op == "Gelu":

@@ -28,7 +28,8 @@ def test_library_exports_every_declared_symbol(b200_lib):
 
 def test_struct_layouts_match_header():
     # field order of the ctypes mirrors follows the header's declarations
-    for struct, cname in ((L.Epilogue, "sofie_b200_epilogue"), (L.GemmDesc, "sofie_b200_gemm_desc"), (L.ConvDesc, "sofie_b200_conv_desc")):
+    for struct, cname in ((L.Epilogue, "sofie_b200_epilogue"), (L.GemmDesc, "sofie_b200_gemm_desc"), (L.ConvDesc, "sofie_b200_conv_desc"),
+                          (L.SdpaDesc, "sofie_b200_sdpa_desc")):
         m = re.search(r"typedef struct " + cname + r" \{(.*?)\} " + cname, HEADER, re.S)
         body = re.sub(r"/\*.*?\*/", "", m.group(1), flags=re.S)
         fields = []

@@ -107,15 +107,16 @@ def test_convnet_int8_every_layer_bit_exact(ctx, oracle_lib):
 @pytest.mark.parametrize("channels_last", [True, False])
 @pytest.mark.parametrize("int8", [False, True])
 def test_benchmark_network_object_matches_checker(ctx, oracle_lib, int8, channels_last):
-    """bench_convnet.ConvNetB200 (plans and buffers created once, as the benchmark runs it) against the checker."""
-    import bench_convnet as bc
+    """sofie_b200.convnet.ConvNetB200 (plans and buffers created once, as the benchmark runs it) against the checker."""
+    import model_oracles as mo
+    from sofie_b200 import convnet as bc
     o = Oracle(oracle_lib)
     rng = np.random.default_rng(5)
-    weights = bc.make_weights(rng, int8)
+    weights = bc.make_weights(5, int8)
     x = rng.random((3, 3, 48, 48), dtype=np.float32)
     if int8:
         x = np.clip(np.rint(x * 127.0), 0, 127).astype(np.int8)
-    want = bc.convnet_oracle(o, x, weights, int8)
+    want = mo.convnet_oracle(o, x, weights, int8)
     net = bc.ConvNetB200(ctx, weights, 3, 48, int8, DEV, channels_last=channels_last)
     n0 = ctx.launches
     for _ in range(2):   # the second call reuses every buffer
@@ -136,7 +137,8 @@ def test_full_size_layer_two_data_paths_agree(ctx, int8, monkeypatch):
     large for the CPU checker: the implicit convolution (input read in place by im2col-mode TMA loads) against the
     unfold + contraction path, which shares nothing with it up to the accumulator.  int8: every output bit for bit.
     fp32: TF32 pairs read in place against the split unfold; the same three products, summed in different chunks."""
-    import bench_convnet as bc
+    import model_oracles as mo
+    from sofie_b200 import convnet as bc
     from sofie_b200.ops import make_epilogue
     lib = ctx._lib
     n, c, hw, k = 256, 64, 112, 128

@@ -21,12 +21,13 @@ DH = D_MODEL // HEADS
 def test_fused_attention_matches_unfused_checker(b200_lib, oracle_lib, batch, seq, heads):
     """Softmax(Q K^T / 8) V per head from the packed QKV tensor, against the checker with the kernel's roundings."""
     from sofie_b200.ops import Context
-    import bench_encoder as be
+    import model_oracles as mo
+    from sofie_b200 import encoder as be
     o = Oracle(oracle_lib)
     dh = 64
     rng = np.random.default_rng(batch * 1000 + seq)
     qkv = be.f32_to_bf16_bits((rng.standard_normal((batch, seq, 3, heads, dh)) * 1.5).astype(np.float32))
-    want = bf16_bits_to_f32(be.attention_oracle(o, qkv, batch, seq, heads, dh, 0.125)).reshape(batch, seq, heads * dh)
+    want = bf16_bits_to_f32(mo.attention_oracle(o, qkv, batch, seq, heads, dh, 0.125)).reshape(batch, seq, heads * dh)
     ctx = Context(0)
     tq = torch.from_numpy(qkv.view(np.int16)).to(DEV).view(torch.bfloat16)
     out = torch.full((batch, seq, heads * dh), 7.0, dtype=torch.bfloat16, device=DEV)
@@ -46,12 +47,13 @@ def test_fused_attention_matches_unfused_checker(b200_lib, oracle_lib, batch, se
 
 @pytest.mark.parametrize("fused", [True, False])
 def test_transformer_encoder_matches_checker(b200_lib, oracle_lib, fused):
-    import bench_encoder as be
+    import model_oracles as mo
+    from sofie_b200 import encoder as be
     from sofie_b200.ops import Context
     rng = np.random.default_rng(5)
-    weights = be.make_weights(rng, LAYERS, D_MODEL, FFN)
+    weights = be.make_weights(5, LAYERS, D_MODEL, FFN)
     x0 = be.f32_to_bf16_bits(rng.standard_normal((B * S, D_MODEL)).astype(np.float32))
-    want = bf16_bits_to_f32(be.encoder_oracle(Oracle(oracle_lib), x0, weights, B, S, D_MODEL, HEADS, fused_attention=fused))
+    want = bf16_bits_to_f32(mo.encoder_oracle(Oracle(oracle_lib), x0, weights, B, S, D_MODEL, HEADS, fused_attention=fused))
     ctx = Context(0)
     enc = be.EncoderB200(ctx, weights, B, S, D_MODEL, HEADS, FFN, DEV, fused_attention=fused)
     launches0 = ctx.launches
@@ -75,10 +77,11 @@ def test_encoder_step_replays_from_a_cuda_graph(b200_lib):
     """Every enqueue of a step is a plain kernel launch on the context's stream (tensor maps travel by value in the
     launch parameters, no allocation, no synchronisation), so a step can be captured once into a CUDA graph and
     replayed: same bits as the eager step, one graph launch instead of 14 kernel launches."""
-    import bench_encoder as be
+    import model_oracles as mo
+    from sofie_b200 import encoder as be
     from sofie_b200.ops import Context
     rng = np.random.default_rng(9)
-    weights = be.make_weights(rng, LAYERS, D_MODEL, FFN)
+    weights = be.make_weights(5, LAYERS, D_MODEL, FFN)
     x0 = be.f32_to_bf16_bits(rng.standard_normal((B * S, D_MODEL)).astype(np.float32))
     side = torch.cuda.Stream(device=DEV)
     ctx = Context(0, stream=side)
