@@ -680,17 +680,17 @@ def test_constant_weight_is_relaid_once_and_follows_its_address(ctx, oracle):
             assert np.array_equal(y.cpu().numpy(), want)
         plan.close()
     # bf16 weights, and fp32 at fp32 accuracy (the constant weight's hi | lo split is made once)
-    a = rng.standard_normal((512, 256)).astype(np.float32)
+    a = rng.standard_normal((1024, 256)).astype(np.float32)
     b = rng.standard_normal((256, 1024)).astype(np.float32)
     ab, bb = (a.view(np.uint32) >> 16).astype(np.uint16), (b.view(np.uint32) >> 16).astype(np.uint16)
-    want = bf16_bits_to_f32(oracle.gemm(ab, bb, 512, 1024, 256, L.BF16, L.BF16))
-    got = run_gemm(ctx, ab.view(np.int16), bb.view(np.int16), 512, 1024, 256, torch.bfloat16, torch.bfloat16, flags=L.GEMM_B_CONSTANT, expect="umma")
+    want = bf16_bits_to_f32(oracle.gemm(ab, bb, 1024, 1024, 256, L.BF16, L.BF16))
+    got = run_gemm(ctx, ab.view(np.int16), bb.view(np.int16), 1024, 1024, 256, torch.bfloat16, torch.bfloat16, flags=L.GEMM_B_CONSTANT, expect="umma")
     assert close_lowp(got.float().cpu().numpy(), want)
-    plan = GemmPlan(ctx, 512, 1024, 256, torch.float32, torch.float32, flags=L.GEMM_B_CONSTANT)
+    plan = GemmPlan(ctx, 1024, 1024, 256, torch.float32, torch.float32, flags=L.GEMM_B_CONSTANT)
     assert plan.kernel == "umma3x"
     ta, tb = torch.from_numpy(a).to(DEV), torch.from_numpy(b).to(DEV)
-    y = torch.zeros((512, 1024), dtype=torch.float32, device=DEV)
-    want = oracle.gemm(a, b, 512, 1024, 256, L.F32, L.F32)
+    y = torch.zeros((1024, 1024), dtype=torch.float32, device=DEV)
+    want = oracle.gemm(a, b, 1024, 1024, 256, L.F32, L.F32)
     for _ in range(2):
         y.zero_()
         plan.enqueue(ta, tb, y)
