@@ -149,14 +149,9 @@ typedef struct sofie_b200_gemm_desc {
  *               convolution filters in a kernel of their own (ROperator_Conv.hxx:985-997); with this flag a plan
  *               whose B is stored [K,N] keeps a K-major copy ([N,K], allocated at plan creation) that it fills on
  *               the first enqueue and again whenever B's address changes.  The tensor-core kernel then stages every
- *               B slice with one TMA box per K block instead of one per 128 bytes of columns.  Results are identical.
- *   PAIR        run the CTA-pair form of the tensor-core kernel (two SMs share a 256 x bn tile through
- *               tcgen05 cta_group::2) where the shape allows it; bits 8-9 then hold the number of K blocks per
- *               release of shared-memory stages minus one.  The plain kernel is the default; the pair form is kept
- *               for measurement. */
+ *               B slice with one TMA box per K block instead of one per 128 bytes of columns.  Results are identical. */
 typedef enum sofie_b200_gemm_flags {
-  SOFIE_B200_GEMM_B_CONSTANT = 1,
-  SOFIE_B200_GEMM_PAIR = 2
+  SOFIE_B200_GEMM_B_CONSTANT = 1
 } sofie_b200_gemm_flags;
 
 /*

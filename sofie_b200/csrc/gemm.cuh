@@ -30,7 +30,6 @@ constexpr int UMMA_TAIL_BYTES = 1024;  // barriers, TMEM slot and abort flag beh
 constexpr int UMMA_EPI_WARPS = 8;     // two epilogue warps per tensor-memory lane quarter, alternating 32-column chunks
 constexpr int UMMA_B_PRODUCER_WARP = 2 + UMMA_EPI_WARPS;  // the warp after the epilogue warps: TMA producer of operand B
 constexpr int UMMA_THREADS = 96 + 32 * UMMA_EPI_WARPS;   // warp 0: TMA producer (A), warp 1: MMA issuer, the epilogue warps, warp 10: producer (B)
-constexpr int UMMA_PAIR_THREADS = 192; // CTA-pair kernel: four epilogue warps per CTA
 
 // Everything the tcgen05 kernel needs besides the two tensor maps.
 struct UmmaParams {
@@ -55,16 +54,14 @@ struct UmmaParams {
   int a_box_mn, b_box_mn;          // MN elements covered by one box of an MN-major operand
   int a_bcast, b_bcast;            // operand shared by the whole batch
   int vec_ok;                      // 16-byte vector stores of 32-column chunks are aligned
-  int pair;                        // 1: CTA-pair kernel (cluster of 2, tcgen05 cta_group::2, 256 x bn tile per pair)
   int raster_n;                    // tile order inside a batch: 0 = M index fastest, 1 = N index fastest
   int y_tma;                       // the epilogue may store complete row segments through the tensor map of Y
-  int commit_group;                // pair kernel: K blocks consumed between bursts of stage releases
   int seg_kb;                      // chunk-promotion kernel: K blocks per split segment (ks / 32)
   int a_seg_kb[3], b_seg_kb[3];    // K block at which each of the three product segments starts in the stored A / B (hi | lo)
   int promote_chunk;               // chunk-promotion kernel: K blocks per tensor-memory accumulation
   int fused3;                      // chunk-promotion kernel: a stage holds A hi | A lo | B hi | B lo of one K block and feeds all three
                                    // products (4 loads per 12 MMAs instead of 6); stage byte counts are the doubled ones
-  int b_rows;                      // N extent of the B slice one CTA stages: bn, or bn/2 in pair mode
+  int b_rows;                      // N extent of the B slice one CTA stages (= bn)
   int kb_mmas;                     // MMAs (32 bytes of K each) per K block: 4, or 2 when a K block is 64 bytes
   int two_producers;               // operand B is loaded by a thread of its own (warp UMMA_B_PRODUCER_WARP): a thread is held by
                                    // every TMA instruction until the unit takes it, and with 8-bit operands one thread issuing
@@ -156,10 +153,6 @@ namespace sb200 {
 // gemm_umma.cu
 int umma_plan_init(sofie_b200_gemm_plan *plan);          // 0 if the tcgen05 path applies, 1 if not, <0 error
 int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep);
-// gemm_umma2.cu (CTA-pair kernel)
-int umma_pair_set_smem(int kind, size_t smem_bytes);
-int umma_pair_max_clusters(int kind, size_t smem_bytes, int *out);
-int umma_pair_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u);
 // gemm_umma3x.cu (TF32 kernel that sums short K chunks in registers)
 int umma_promote_set_smem(size_t smem_bytes);
 int umma_promote_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u);

@@ -428,15 +428,12 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
 
   plan->kind = kind;
   u.M = (int)d.M; u.N = (int)d.N; u.K = (int)d.K; u.batch = (int)d.batch;
-  // CTA-pair mode (on request, SOFIE_B200_GEMM_PAIR): two SMs share a 256 x bn tile, each staging its 128 rows of A and
-  // half of the B slice, which cuts the operand bytes per SM and deepens the shared-memory ring.
   const int sms = plan->ctx->sm_count;
-  u.pair = ((d.flags & SOFIE_B200_GEMM_PAIR) && !plan->promote && !ic.on && d.M >= 256 && d.N >= 64) ? 1 : 0;
-  const int tile_m = u.pair ? 2 * UMMA_BM : UMMA_BM;
+  const int tile_m = UMMA_BM;
   u.tiles_m = (int)((d.M + tile_m - 1) / tile_m);
   // an MN-major B slice is made of 128-byte-wide TMA boxes, so the slice one CTA stages must reach 128 bytes
-  const int min_bn = (d.trans_b ? 32 : 128 / es) * (u.pair ? 2 : 1);
-  u.bn = pick_bn(d.N, u.tiles_m, d.batch, u.pair ? sms / 2 : sms, min_bn < 64 && (u.pair || plan->promote) ? 64 : min_bn);
+  const int min_bn = d.trans_b ? 32 : 128 / es;
+  u.bn = pick_bn(d.N, u.tiles_m, d.batch, sms, min_bn < 64 && plan->promote ? 64 : min_bn);
   // Tile order.  With the M index fastest the tiles in flight share one B slice and sweep A, so A is re-read from DRAM
   // once per N tile unless it stays in L2; with the N index fastest it is B that is swept.  Take the cheaper one.
   {
@@ -444,17 +441,15 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
     const double tiles_n = (double)((d.N + u.bn - 1) / u.bn);
     const double cost_m = b_bytes + (a_bytes <= l2_fit ? a_bytes : tiles_n * a_bytes);
     const double cost_n = a_bytes + (b_bytes <= l2_fit ? b_bytes : (double)u.tiles_m * b_bytes);
-    u.raster_n = (!u.pair && cost_n < cost_m) ? 1 : 0;
+    u.raster_n = cost_n < cost_m ? 1 : 0;
   }
   if (plan->promote) {
     u.seg_kb = (int)(d.K / 3 / SPLIT_K_ALIGN);
     u.a_seg_kb[0] = 0; u.a_seg_kb[1] = u.seg_kb; u.a_seg_kb[2] = 0;         // A: hi, lo, hi
     u.b_seg_kb[0] = 0; u.b_seg_kb[1] = 0; u.b_seg_kb[2] = u.seg_kb;         // B: hi, hi, lo
   }
-  u.commit_group = 1 + ((d.flags >> 8) & 3);
-  if (u.commit_group > 3) u.commit_group = 3;
   u.promote_chunk = 8;   // 32 MMA steps per accumulation: truncation bias below 2e-6 relative even for same-sign data
-  u.b_rows = u.pair ? u.bn / 2 : u.bn;
+  u.b_rows = u.bn;
   u.tiles_n = (int)((d.N + u.bn - 1) / u.bn);
   u.num_tiles = (long long)u.tiles_m * u.tiles_n * d.batch;
   u.kb_elems = kb_bytes / es;
@@ -479,12 +474,11 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.tmem_cols = 32;
   while (u.tmem_cols < 2u * u.bn) u.tmem_cols <<= 1;
 
-  const size_t epi_bytes = (u.pair ? 4 : 8) * 4096;   // staging buffers of the epilogue warps
+  const size_t epi_bytes = 8 * 4096;   // staging buffers of the epilogue warps
   const size_t budget = 227 * 1024 - 1024 /*alignment*/ - UMMA_TAIL_BYTES /*barriers*/ - epi_bytes;
   int stages = (int)(budget / (u.a_stage_bytes + u.b_stage_bytes));
   if (stages > (kb_bytes == 64 ? 12 : 8)) stages = kb_bytes == 64 ? 12 : 8;
   if (stages < 2) return 1;
-  if (u.pair) stages = stages / u.commit_group * u.commit_group;   // release groups never straddle the ring's wrap
   u.stages = stages;
   plan->smem_bytes = (size_t)stages * (u.a_stage_bytes + u.b_stage_bytes) + 1024 + UMMA_TAIL_BYTES + epi_bytes;
 
@@ -530,7 +524,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.split_from = u.num_tiles;
   u.num_items = u.num_tiles;
   u.idesc_half = (u.idesc & ~(0x3fu << 17)) | ((uint32_t)(u.bn >> 4) << 17);
-  if (!u.pair && !plan->promote && u.bn >= 64 && u.num_tiles > sms) {
+  if (!plan->promote && u.bn >= 64 && u.num_tiles > sms) {
     const long long tail = u.num_tiles % sms;
     if (tail > 0 && 2 * tail <= sms) {
       u.split_from = u.num_tiles - tail;
@@ -538,18 +532,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
     }
   }
   long long grid = u.num_tiles < plan->ctx->sm_count ? u.num_tiles : plan->ctx->sm_count;
-  if (u.pair) grid = 2 * (u.num_tiles < sms / 2 ? u.num_tiles : sms / 2);
   plan->grid = (int)grid;
-  if (u.pair) {
-    int rc = umma_pair_set_smem(kind, plan->smem_bytes);
-    if (rc) return rc;
-    int clusters = 0;
-    if ((rc = umma_pair_max_clusters(kind, plan->smem_bytes, &clusters))) return rc;
-    if (clusters < 1) return 1;
-    if (plan->grid > 2 * clusters) plan->grid = 2 * clusters;
-    return 0;
-  }
-
   if (plan->promote) return umma_promote_set_smem(plan->smem_bytes);
 
   cudaError_t e = cudaSuccess;
@@ -617,13 +600,13 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
   // Row segments per flush: a 128-byte segment is 4 chunks of 1-byte and 2 of 2-byte outputs; a narrow tile then has a
   // single segment and one of the two warps of each lane quarter would idle, so the segment is halved until there are two.
   int seg_div = 1;
-  if (!u.pair && !plan->promote) {
+  if (!plan->promote) {
     const int full = 4 / dtype_size(plan->desc.y_dtype);   // chunks per 128 bytes
     int g = full;
     while (g > 1 && (u.bn / 32) / g < 2) g >>= 1;
     if (g < full) { u.ep.seg_chunks = g; seg_div = full / g; }
   }
-  if (u.vec_ok && !u.pair) {
+  if (u.vec_ok) {
     const sofie_b200_gemm_desc &d = plan->desc;
     const int ys = dtype_size(d.y_dtype);
     if (ep.Y != plan->cached_y || seg_div != plan->cached_seg_div) {
@@ -637,7 +620,6 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
     }
     u.y_tma = 1;
   }
-  if (u.pair) return umma_pair_launch(plan, u);
   if (plan->promote) return umma_promote_launch(plan, u);
   cudaStream_t st = plan->ctx->stream;
   dim3 grid(plan->grid), block(UMMA_THREADS);

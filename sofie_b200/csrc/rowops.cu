@@ -238,6 +238,104 @@ __global__ void __launch_bounds__(256, (MODE == 0 ? (CH >= 16 ? 2 : (CH >= 8 && 
   }
 }
 
+// LayerNorm, one warp per row, R rows per trip.  A lane owns the same CH 16-byte chunks of every row it sees, so its scale
+// and bias values are loaded ONCE into registers (the group kernel above re-loads them for every chunk of every row:
+// four 16-byte loads of parameters per 16-byte load of data, which made it issue-bound at half the memory bandwidth).
+// All 16-byte loads of the R rows of a trip are issued before the first use; the rows are unpacked to fp32 once and
+// the three passes (sum, squared deviations, output) run on registers; the R reductions of a pass interleave.
+template <typename TIn, typename TOut, int CH, int R>
+__global__ void __launch_bounds__(256, 2) layernorm_warp_kernel(const TIn *__restrict__ x, TOut *__restrict__ y, long long rows, int cols,
+                                                                const float *__restrict__ scale, const float *__restrict__ bias, float eps,
+                                                                float *__restrict__ mean_out, float *__restrict__ invstd_out) {
+  constexpr int E = Vec16<TIn>::E;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const float inv_n = 1.f / (float)cols;
+  float sc[CH][E], bi[CH][E];
+  bool have[CH];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int col = (c * 32 + lane) * E;
+    have[c] = col < cols;
+#pragma unroll
+    for (int e = 0; e < E; e += 4) {
+      const float4 s4 = (have[c] && scale) ? *reinterpret_cast<const float4 *>(scale + col + e) : make_float4(1.f, 1.f, 1.f, 1.f);
+      const float4 b4 = (have[c] && bias) ? *reinterpret_cast<const float4 *>(bias + col + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+      sc[c][e] = s4.x; sc[c][e + 1] = s4.y; sc[c][e + 2] = s4.z; sc[c][e + 3] = s4.w;
+      bi[c][e] = b4.x; bi[c][e + 1] = b4.y; bi[c][e + 2] = b4.z; bi[c][e + 3] = b4.w;
+    }
+  }
+  for (long long row0 = warp0 * R; row0 < rows; row0 += nwarps * R) {
+    uint4 raw[R][CH];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+        raw[r][c] = (row0 + r < rows && have[c]) ? ld_raw16(x + (row0 + r) * (long long)cols + (c * 32 + lane) * E) : fill16<TIn>(false);
+    // rows go through the arithmetic two at a time (registers: the raw rows of the trip stay packed until their turn)
+#pragma unroll
+    for (int r0 = 0; r0 < R; r0 += 2) {
+      float v[2][CH][E];
+      float s[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        s[r] = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          unpack16<TIn>(raw[r0 + r][c], v[r][c]);
+#pragma unroll
+          for (int e = 0; e < E; ++e) s[r] += v[r][c][e];
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) s[r] += __shfl_xor_sync(0xffffffffu, s[r], o);
+      float mean[2], q[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mean[r] = s[r] * inv_n;
+        q[r] = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+          if (have[c]) {
+#pragma unroll
+            for (int e = 0; e < E; ++e) { v[r][c][e] = __fsub_rn(v[r][c][e], mean[r]); q[r] = __fmaf_rn(v[r][c][e], v[r][c][e], q[r]); }
+          }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) q[r] += __shfl_xor_sync(0xffffffffu, q[r], o);
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const long long row = row0 + r0 + r;
+        if (row < rows) {
+          const float inv = 1.f / sqrtf(q[r] * inv_n + eps);
+          TOut *yr = y + row * (long long)cols;
+#pragma unroll
+          for (int c = 0; c < CH; ++c)
+            if (have[c]) {
+              float o[E];
+              // scale * invStd * (x - mean) + bias, left to right, each step rounded
+#pragma unroll
+              for (int e = 0; e < E; ++e) {
+                const float t = scale ? __fmul_rn(__fmul_rn(sc[c][e], inv), v[r][c][e]) : __fmul_rn(inv, v[r][c][e]);
+                o[e] = bias ? __fadd_rn(t, bi[c][e]) : t;
+              }
+              store_chunk_as<TOut, E>(yr + (c * 32 + lane) * E, o);
+            }
+          if (lane == 0) {
+            if (mean_out) mean_out[row] = mean[r];
+            if (invstd_out) invstd_out[row] = inv;
+          }
+        }
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ float ld_as_float(const float *p) { return *p; }
 __device__ __forceinline__ float ld_as_float(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
 __device__ __forceinline__ void st_from_float(float *p, float v) { *p = v; }
@@ -307,7 +405,18 @@ static int launch_rows(sofie_b200_ctx *ctx, const void *x, void *y, long long ro
   const bool aligned = (cols % E == 0) && ((uintptr_t)x % 16 == 0) && ((uintptr_t)scale % 16 == 0) && ((uintptr_t)bias % 16 == 0) &&
                        ((uintptr_t)y % (sizeof(TOut) * E > 16 ? 16 : sizeof(TOut) * E) == 0);
   const long long chunks = (cols + E - 1) / E;
-  if (aligned && chunks <= 32 * 16) {
+  if (MODE == 0 && aligned && chunks > 16 && chunks <= (sizeof(TIn) == 2 ? 64 : 128) && rows >= 4096) {
+    // rows of 16 to 128 chunks, enough of them to fill the machine: one warp per row, parameters in registers
+    const int ch = (int)((chunks + 31) / 32);
+    const unsigned grid = (unsigned)std::min<long long>((rows + 31) / 32, (long long)ctx->sm_count * 2);
+    const TIn *xi = (const TIn *)x;
+    TOut *yo = (TOut *)y;
+    if constexpr (MODE == 0) {
+      if (ch <= 1) layernorm_warp_kernel<TIn, TOut, 1, 4><<<grid, 256, 0, st>>>(xi, yo, rows, (int)cols, scale, bias, eps, mean_out, invstd_out);
+      else if (ch <= 2) layernorm_warp_kernel<TIn, TOut, 2, 4><<<grid, 256, 0, st>>>(xi, yo, rows, (int)cols, scale, bias, eps, mean_out, invstd_out);
+      else if constexpr (sizeof(TIn) == 4) layernorm_warp_kernel<TIn, TOut, 4, 2><<<grid, 256, 0, st>>>(xi, yo, rows, (int)cols, scale, bias, eps, mean_out, invstd_out);
+    }
+  } else if (aligned && chunks <= 32 * 16) {
     // Lanes per row: as few as keep <= 8 chunks (128 bytes) per lane, so that each lane has several
     // independent 16-byte loads in flight and the reductions stay short; widened again when there
     // are too few rows to fill the machine.

@@ -1,4 +1,4 @@
-// Epilogue store of the tcgen05 contraction kernels (single-CTA and CTA-pair): one 32-column chunk of
+// Epilogue store of the tcgen05 contraction kernels: one 32-column chunk of
 // one accumulator row through the fused epilogue to global memory.
 #pragma once
 #include "gemm.cuh"

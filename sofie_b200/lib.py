@@ -18,7 +18,7 @@ ACT_NONE, ACT_RELU, ACT_GELU_ERF, ACT_GELU_TANH, ACT_LEAKY_RELU, ACT_SIGMOID = r
 BIAS_NONE, BIAS_COL_F32, BIAS_ROW_F32, BIAS_SCALAR_F32, BIAS_COL_I32, BIAS_FULL_F32, BIAS_ROW_I32 = range(7)
 OK, ERR_INVALID, ERR_CUDA, ERR_DEVICE_WAIT, ERR_NO_DEVICE, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5
 ABI_VERSION = 2
-GEMM_B_CONSTANT, GEMM_PAIR = 1, 2
+GEMM_B_CONSTANT = 1
 CONV_UNFOLD = 1
 
 

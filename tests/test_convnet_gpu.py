@@ -185,3 +185,19 @@ def test_full_size_layer_two_data_paths_agree(ctx, int8, monkeypatch):
         err = (a - b).abs().max().item()
         scale = b.abs().max().item()
         assert err <= 2e-6 * scale, (err, scale)
+
+
+def test_network_matches_the_references_emitted_code(ctx):
+    """The fp32 network on 2 images of 32 x 32 against what the reference's own emitted CPU code computed (fixture made by
+    tests/golden/make_golden.py from oracle/_ref ConvNet_C4r; same weights through the reproducible generator)."""
+    from pathlib import Path
+    from sofie_b200 import convnet as bc
+    fx = np.load(Path(__file__).parent / "golden" / "configs" / "ConvNet_C4r.npz")
+    weights = bc.make_weights(int(fx["seed"]), False)
+    for channels_last in (True, False):
+        net = bc.ConvNetB200(ctx, weights, 2, 32, False, DEV, channels_last=channels_last)
+        got = net(torch.from_numpy(fx["x"]).to(DEV))
+        ctx.sync()
+        got = got.cpu().numpy()
+        net.close()
+        assert close_f32(got, fx["y"], rel=1e-5), (channels_last, np.abs(got - fx["y"]).max())

@@ -639,25 +639,6 @@ def test_fp32_gemm_3xtf32_meets_fp32_bar(ctx, oracle, M, N, K, ta, tb, batch):
         assert not close_f32(tf32.reshape(want.shape), want)
 
 
-@pytest.mark.parametrize("group", [1, 3])
-def test_cta_pair_kernel_bit_exact(ctx, oracle, group):
-    """The opt-in CTA-pair kernel (cluster of 2, tcgen05 cta_group::2), with per-stage and grouped stage release."""
-    pair = L.GEMM_PAIR | ((group - 1) << 8)
-    rng = np.random.default_rng(17)
-    for (M, N, K, tb) in ((512, 512, 1024, True), (1000, 704, 400, False), (256, 64, 96, True)):
-        a = rng.integers(-127, 128, size=(M, K), dtype=np.int8)
-        b = rng.integers(-127, 128, size=(N, K) if tb else (K, N), dtype=np.int8)
-        want = oracle.gemm(a, b, M, N, K, L.I8, L.I8, False, tb, ep=oracle.epilogue(alpha=MULT))
-        got = run_gemm(ctx, a, b, M, N, K, torch.int8, torch.int8, False, tb, alpha=MULT, expect="umma", flags=pair).cpu().numpy()
-        assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size} differ"
-    a = rng.standard_normal((384, 512)).astype(np.float32)
-    b = rng.standard_normal((320, 512)).astype(np.float32)
-    ab, bb = (a.view(np.uint32) >> 16).astype(np.uint16), (b.view(np.uint32) >> 16).astype(np.uint16)
-    want = bf16_bits_to_f32(oracle.gemm(ab, bb, 384, 320, 512, L.BF16, L.BF16, False, True))
-    got = run_gemm(ctx, ab.view(np.int16), bb.view(np.int16), 384, 320, 512, torch.bfloat16, torch.bfloat16, False, True, flags=pair).float().cpu().numpy()
-    assert close_lowp(got, want)
-
-
 def test_constant_weight_is_relaid_once_and_follows_its_address(ctx, oracle):
     """SOFIE_B200_GEMM_B_CONSTANT: a weight stored [K,N] is kept as a K-major copy.  Same bits as without the flag; a
     second weight at another address is picked up; the same address is not read again (the documented contract)."""

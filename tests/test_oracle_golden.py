@@ -47,3 +47,30 @@ def test_oracle_matches_checked_in_vectors(name, backend):
     # the checked-in vectors carry 4-6 significant digits; the reference compares at 1e-3 absolute
     # (tests/alpaka/TestAlpakaCommon.h:10); 2e-4 is what their printed precision allows
     assert np.abs(got - fx["expected"]).max() <= 2e-4
+
+
+# ---- the model configurations, pinned to the reference's emitted code at reduced size ---------------------------------
+CONFIGS = Path(__file__).parent / "golden" / "configs"
+
+
+def test_convnet_restatement_matches_reference_code(oracle_lib):
+    """8 x (Conv3x3 -> BatchNormalization + Relu), GlobalAveragePool, Gemm on 2 images of 32 x 32: the reference ran Conv and
+    BatchNormalization as separate operators; the restatement folds the normalisation into the convolution's epilogue."""
+    import model_oracles as mo
+    from oracle_api import Oracle
+    from sofie_b200 import convnet
+    fx = np.load(CONFIGS / "ConvNet_C4r.npz")
+    got = mo.convnet_oracle(Oracle(oracle_lib), fx["x"], convnet.make_weights(int(fx["seed"]), False), False)
+    assert close(got, fx["y"]), np.abs(got - fx["y"]).max()
+
+
+def test_encoder_restatement_matches_reference_code(oracle_lib):
+    """2 encoder layers, 2 sequences: the reference ran fp32 on the dequantised weights; the restatement keeps bf16 tensors
+    and int8 weights with the scale in the epilogue.  Bar of the low-precision path: 2e-2 relative + 1e-2 absolute."""
+    import model_oracles as mo
+    from oracle_api import Oracle, bf16_bits_to_f32
+    from sofie_b200 import encoder
+    fx = np.load(CONFIGS / "Encoder_C5r.npz")
+    w = encoder.make_weights(int(fx["seed"]), int(fx["layers"]), 512, 2048)
+    got = bf16_bits_to_f32(mo.encoder_oracle(Oracle(oracle_lib), encoder.f32_to_bf16_bits(fx["x"]), w, int(fx["batch"]), 128, 512, 8))
+    assert np.all(np.abs(got - fx["y"]) <= 2e-2 * np.abs(fx["y"]) + 1e-2), np.abs(got - fx["y"]).max()

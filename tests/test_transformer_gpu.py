@@ -124,3 +124,25 @@ def test_transpose(b200_lib, shape, perm):
         ctx.sync()
         assert torch.equal(y, x.permute(*perm).contiguous())
     ctx.close()
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_encoder_matches_the_references_emitted_code(b200_lib, fused):
+    """2 layers, 2 sequences, against the reference's emitted fp32 code run on the dequantised weights (fixture made by
+    tests/golden/make_golden.py from oracle/_ref Encoder_C5r, whose attention is the reference's ROperator_SDPA)."""
+    from pathlib import Path
+    from sofie_b200 import encoder as be
+    from sofie_b200.ops import Context
+    fx = np.load(Path(__file__).parent / "golden" / "configs" / "Encoder_C5r.npz")
+    batch, layers = int(fx["batch"]), int(fx["layers"])
+    weights = be.make_weights(int(fx["seed"]), layers, D_MODEL, FFN)
+    ctx = Context(0)
+    enc = be.EncoderB200(ctx, weights, batch, S, D_MODEL, HEADS, FFN, DEV, fused_attention=fused)
+    xg = torch.from_numpy(be.f32_to_bf16_bits(fx["x"]).view(np.int16)).to(DEV).view(torch.bfloat16)
+    got = enc(xg)
+    ctx.sync()
+    got = got.float().cpu().numpy()
+    enc.close()
+    ctx.close()
+    err = np.abs(got - fx["y"])
+    assert np.all(err <= 2e-2 * np.abs(fx["y"]) + 1e-2), f"max abs err {err.max():.4f}"
