@@ -108,6 +108,7 @@ private:
    void PlanArena();
    std::string GenerateSessionCode_GPU_B200();
    void WriteWeightFile(const std::string &filename) const;
+   void WriteSafetensorsFile(const std::string &filename) const;
 
    std::string fName = "model";
    std::string fParseTime;

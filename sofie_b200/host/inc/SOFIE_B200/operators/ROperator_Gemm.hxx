@@ -72,6 +72,7 @@ private:
    std::string fNA, fNB, fNC, fNY;
    EpilogueState fEpi;
    std::vector<size_t> fShapeA, fShapeB, fShapeC, fShapeY;
+   bool fBIsWeight = false;   // B is an initialized tensor (a weight)
    ETensorType fType = ETensorType::FLOAT, fTypeY = ETensorType::FLOAT;
    size_t fM = 0, fN = 0, fK = 0, fBatch = 1;
    int64_t fStrideA = 0, fStrideB = 0;
@@ -115,6 +116,7 @@ public:
          throw std::runtime_error("SOFIE Gemm Op Input Tensor " + fNC + " is not found in model");
       fShapeA = model.GetTensorShape(fNA);
       fShapeB = model.GetTensorShape(fNB);
+      fBIsWeight = model.IsInitializedTensor(fNB);
       fType = model.GetTensorType(fNA);
       if (model.GetTensorType(fNB) != fType)
          throw std::runtime_error("SOFIE Gemm Op: A and B have different element types");
@@ -293,6 +295,7 @@ public:
       out << "      d.stride_a = " << fStrideA << "; d.stride_b = " << fStrideB << "; d.stride_y = " << (fBatch > 1 ? fM * fN : 0)
           << "; d.stride_r = " << (fBatch > 1 ? fM * fN : 0) << ";\n";
       out << "      d.precise = " << (fPrecise ? 1 : 0) << ";\n";
+      if (fBIsWeight) out << "      d.flags = SOFIE_B200_GEMM_B_CONSTANT;  // B is an initializer: the plan may keep its own layout of it\n";
       out << "      Check(sofie_b200_gemm_plan_create(ctx, &d, &plan_" << opName << "), \"Gemm " << opName << ": plan\");\n";
       out << fEpi.InitCode("ep_" + opName);
       if (fEpi.biasMode == "SOFIE_B200_BIAS_FULL_F32") out << "      ep_" << opName << ".ldc = " << fN << ";\n";

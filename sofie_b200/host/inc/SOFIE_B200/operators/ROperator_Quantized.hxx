@@ -44,6 +44,7 @@ inline int ZeroPoint(RModel &m, const std::string &n)
 
 // ---- QLinearMatMul ---------------------------------------------------------------------------------
 class ROperator_QLinearMatMul final : public ROperator_B200 {
+   bool fBIsWeight = false;
    std::string fNA, fNAScale, fNAZp, fNB, fNBScale, fNBZp, fNYScale, fNYZp, fNY;
    std::vector<size_t> fShapeA, fShapeB, fShapeY;
    size_t fM = 0, fN = 0, fK = 0;
@@ -74,6 +75,7 @@ public:
       if (fShapeB.size() != 2 || fShapeA.size() < 2 || fShapeA.back() != fShapeB[0])
          throw std::runtime_error("SOFIE QLinearMatMul Op : invalid input shapes A " + ConvertShapeToString(fShapeA) + " B " + ConvertShapeToString(fShapeB));
       fK = fShapeB[0]; fN = fShapeB[1];
+      fBIsWeight = model.IsInitializedTensor(fNB);
       fM = ConvertShapeToLength(fShapeA) / fK;
       fShapeY = fShapeA;
       fShapeY.back() = fN;
@@ -121,6 +123,7 @@ public:
       out << "      {  // QLinearMatMul " << opName << "\n      sofie_b200_gemm_desc d{};\n";
       out << "      d.M = " << fM << "; d.N = " << fN << "; d.K = " << fK << "; d.batch = 1;\n";
       out << "      d.ab_dtype = SOFIE_B200_I8; d.y_dtype = " << ConvertTypeToRuntimeEnum(fTypeY) << ";\n";
+      if (fBIsWeight) out << "      d.flags = SOFIE_B200_GEMM_B_CONSTANT;  // B is an initializer: the plan keeps it K-major\n";
       out << "      Check(sofie_b200_gemm_plan_create(ctx, &d, &plan_" << opName << "), \"QLinearMatMul " << opName << ": plan\");\n";
       out << fEpi.InitCode("ep_" + opName) << "      }\n";
       return out.str();

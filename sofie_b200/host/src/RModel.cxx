@@ -347,10 +347,10 @@ void RModel::GenerateGPU_B200(std::underlying_type_t<Options> options, int batch
 {
    fOptions = options;
    const auto unsupported = Options::kGNN | Options::kGNNComponent | Options::kLowRankFactorize | Options::kStridedInput | Options::kNoSession |
-                            Options::kSafetensorsWeightFile | Options::kKernelOnly;
+                            Options::kKernelOnly;
    if (options & unsupported)
       throw std::runtime_error("SOFIE_B200::GenerateGPU_B200: an option outside the B200 target was requested (GNN, low-rank, strided input, "
-                               "no-session, safetensors and kernel-only generation are not part of it)");
+                               "no-session and kernel-only generation are not part of it)");
    Initialize(batchSize, verbose);
    for (size_t i = 0; i < fOperators.size(); ++i)
       if (!AsB200(fOperators[i].get()))
@@ -359,6 +359,8 @@ void RModel::GenerateGPU_B200(std::underlying_type_t<Options> options, int batch
    PlanArena();
    fGC = GenerateSessionCode_GPU_B200();
 }
+
+std::string SafetensorsDType(ETensorType type);
 
 namespace {
 
@@ -408,6 +410,7 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    const bool profile = fOptions & static_cast<std::underlying_type_t<Options>>(Options::kProfile);
    const bool debug = fOptions & static_cast<std::underlying_type_t<Options>>(Options::kDebug);
    const bool noWeightFile = fOptions & static_cast<std::underlying_type_t<Options>>(Options::kNoWeightFile);
+   const bool safetensors = !noWeightFile && (fOptions & static_cast<std::underlying_type_t<Options>>(Options::kSafetensorsWeightFile));
 
    std::map<std::string, const ArenaRegion *> region;
    for (auto &r : fRegions) region[r.name] = &r;
@@ -419,7 +422,7 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    o << "// Code generated automatically by SOFIE_B200 (B200 / sm_100a target) from the model " << fName << "\n";
    o << "// Link with libsofie_b200 and the CUDA runtime.\n";
    o << "#ifndef SOFIE_B200_" << guard << "\n#define SOFIE_B200_" << guard << "\n\n";
-   o << "#include <cuda_runtime.h>\n#include <cstdint>\n#include <cstdio>\n#include <fstream>\n#include <limits>\n#include <stdexcept>\n#include <string>\n#include <vector>\n";
+   o << "#include <cuda_runtime.h>\n#include <cstdint>\n#include <cstdio>\n#include <fstream>\n#include <iterator>\n#include <limits>\n#include <stdexcept>\n#include <string>\n#include <vector>\n";
    o << "#include \"sofie_b200.h\"\n\nnamespace SOFIE_" << fName << " {\n\n";
    if (customMem) {
       o << "// One block for weights, inputs, outputs and the pooled intermediates: alloc is called once by the\n"
@@ -460,6 +463,16 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    if (profile) {
       o << "   std::vector<cudaEvent_t> fProfEvents;\n   std::vector<double> fProfTotalMs;\n   size_t fProfCalls = 0;\n";
    }
+   const size_t nIn = fInputTensorNames.size();
+   o << "\n   // CUDA graphs of the inference body, one per set of input pointers seen (the two staging sets of infer_host_many);\n"
+        "   // the first call runs eagerly (plans finish their one-time work), the next one is captured, later ones replay\n";
+   o << "   struct CapturedGraph { cudaGraphExec_t exec = nullptr; const void *in[" << (nIn ? nIn : 1) << "] = {}; size_t age = 0; };\n";
+   o << "   CapturedGraph fGraphs[2];\n   bool fUseCudaGraph = " << (profile ? "false" : "true") << ";\n   size_t fCalls = 0;\n";
+   if (!customMem) {
+      o << "   // second staging set, output parking buffers, copy streams and events of infer_host_many (created on first use)\n";
+      o << "   char *fQueueMem = nullptr;\n   cudaStream_t fCopyIn = nullptr, fCopyOut = nullptr;\n"
+           "   cudaEvent_t fEvReady[2] = {}, fEvConsumed[2] = {}, fEvParked[2] = {}, fEvLeft[2] = {};\n";
+   }
 
    o << R"(
    static void Check(int rc, const char *what)
@@ -492,12 +505,43 @@ std::string RModel::GenerateSessionCode_GPU_B200()
       if (is.fail()) throw std::runtime_error("sofie failed to read the values for tensor " + expectedName);
    }
 )";
+   if (safetensors) {
+      o << R"(
+   // safetensors: 8-byte little-endian header size, a JSON header {"name": {"dtype": "..", "shape": [..], "data_offsets": [b, e]}, ..},
+   // then the raw little-endian payload.  Finds one tensor and checks its type and size; returns a pointer into the blob.
+   static const char *FindSafetensor(const std::string &blob, const std::string &name, const std::string &dtype, size_t bytes)
+   {
+      if (blob.size() < 8) throw std::runtime_error("sofie: truncated safetensors blob: missing JSON header size");
+      unsigned long long hs = 0;
+      for (int i = 0; i < 8; ++i) hs |= (unsigned long long)(static_cast<unsigned char>(blob[i])) << (8 * i);
+      if (hs > blob.size() - 8) throw std::runtime_error("sofie: truncated JSON header in safetensors blob");
+      const std::string header = blob.substr(8, hs);
+      const size_t at = header.find("\"" + name + "\":");
+      if (at == std::string::npos) throw std::runtime_error("sofie: tensor " + name + " not found in safetensors blob");
+      const size_t close = header.find('}', at);
+      const std::string entry = header.substr(at, close == std::string::npos ? std::string::npos : close - at);
+      const size_t dt = entry.find("\"dtype\":\"");
+      if (dt == std::string::npos) throw std::runtime_error("sofie: tensor " + name + " has no dtype in safetensors blob");
+      const std::string found = entry.substr(dt + 9, entry.find('"', dt + 9) - (dt + 9));
+      if (found != dtype) throw std::runtime_error("sofie: tensor " + name + " in safetensors blob has dtype " + found + " , expected " + dtype);
+      const size_t off = entry.find("\"data_offsets\":[");
+      if (off == std::string::npos) throw std::runtime_error("sofie: tensor " + name + " has no data_offsets in safetensors blob");
+      unsigned long long b = 0, e = 0;
+      if (std::sscanf(entry.c_str() + off + 16, "%llu,%llu", &b, &e) != 2 || e < b || 8 + hs + e > blob.size())
+         throw std::runtime_error("sofie: bad data_offsets for tensor " + name + " in safetensors blob");
+      if (e - b != bytes)
+         throw std::runtime_error("sofie: tensor " + name + " in safetensors blob has " + std::to_string(e - b) + " bytes , expected " + std::to_string(bytes));
+      return blob.data() + 8 + hs + b;
+   }
+)";
+   }
 
    // ---- InitSession
    o << "\n   void InitSession(const std::string &filename)\n   {\n";
    o << "      int device = 0;\n      CheckCuda(cudaGetDevice(&device), \"cudaGetDevice\");\n";
    o << "      Check(sofie_b200_ctx_create(&ctx, device, stream), \"ctx_create\");\n";
    if (customMem) {
+      o << "      if (!fProvider.alloc || !fProvider.dealloc) throw std::runtime_error(\"SOFIE_B200 MemoryProvider needs alloc and dealloc\");\n";
       o << "      fArena = static_cast<char *>(fProvider.alloc(kArenaBytes, fProvider.user));\n";
       o << "      if (!fArena) throw std::runtime_error(\"SOFIE_B200 MemoryProvider::alloc returned null\");\n";
       o << "      if (reinterpret_cast<uintptr_t>(fArena) % 256) throw std::runtime_error(\"SOFIE_B200 MemoryProvider block is not 256-byte aligned\");\n";
@@ -513,7 +557,10 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    bool anyWeight = false;
    for (auto &r : fRegions) anyWeight |= r.kind == "weight";
    if (anyWeight) {
-      if (!noWeightFile) {
+      if (safetensors) {
+         o << "      std::ifstream f(filename, std::ios::binary);\n      if (!f.is_open()) throw std::runtime_error(\"sofie failed to open file \" + filename + \" for input weights\");\n";
+         o << "      const std::string blob((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());\n";
+      } else if (!noWeightFile) {
          o << "      std::ifstream f(filename);\n      if (!f.is_open()) throw std::runtime_error(\"sofie failed to open file \" + filename + \" for input weights\");\n";
       } else {
          o << "      (void)filename;\n";
@@ -523,7 +570,11 @@ std::string RModel::GenerateSessionCode_GPU_B200()
          auto &t = fInitializedTensors.at(r.name);
          const std::string ct = ConvertTypeToString(t.type);
          const size_t len = ConvertShapeToLength(t.shape);
-         if (!noWeightFile) {
+         if (safetensors) {
+            o << "      CheckCuda(cudaMemcpyAsync(tensor_" << r.name << ", FindSafetensor(blob, \"tensor_" << r.name << "\", \"" << SafetensorsDType(t.type)
+              << "\", " << r.bytes << "), " << r.bytes << ", cudaMemcpyHostToDevice, stream), \"weight upload\");\n";
+            (void)len;
+         } else if (!noWeightFile) {
             o << "      { std::vector<" << ct << "> h; ReadTensorFromStream(f, h, \"tensor_" << r.name << "\", " << len << ");\n";
             o << "        CheckCuda(cudaMemcpyAsync(tensor_" << r.name << ", h.data(), " << r.bytes
               << ", cudaMemcpyHostToDevice, stream), \"weight upload\"); CheckCuda(cudaStreamSynchronize(stream), \"weight upload\"); }\n";
@@ -546,7 +597,7 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    o << "   }\n\n";
 
    // ---- constructors / destructor
-   const std::string defFile = noWeightFile ? "\"\"" : "\"" + fName + ".dat\"";
+   const std::string defFile = noWeightFile ? "\"\"" : "\"" + fName + (safetensors ? ".safetensors\"" : ".dat\"");
    const std::string prov = customMem ? "MemoryProvider provider, " : "";
    const std::string provInit = customMem ? "fProvider = provider; " : "";
    o << "   Session(" << prov << "std::string filename = " << defFile << ")\n   {\n      " << provInit
@@ -561,6 +612,12 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    for (size_t i = 0; i < fOperators.size(); ++i)
       if (!fSkippedOperators.count(i)) o << AsB200(fOperators[i].get())->GenerateDestroyCode_GPU_B200(std::to_string(i));
    if (profile) o << "      for (auto &e : fProfEvents) cudaEventDestroy(e);\n";
+   o << "      for (auto &g : fGraphs) if (g.exec) cudaGraphExecDestroy(g.exec);\n";
+   if (!customMem) {
+      o << "      if (fCopyIn) { cudaStreamSynchronize(fCopyIn); cudaStreamSynchronize(fCopyOut); cudaStreamDestroy(fCopyIn); cudaStreamDestroy(fCopyOut);\n"
+           "         for (int i = 0; i < 2; ++i) { cudaEventDestroy(fEvReady[i]); cudaEventDestroy(fEvConsumed[i]); cudaEventDestroy(fEvParked[i]); cudaEventDestroy(fEvLeft[i]); } }\n"
+           "      if (fQueueMem) cudaFree(fQueueMem);\n";
+   }
    o << "      if (ctx) sofie_b200_ctx_destroy(ctx);\n";
    if (customMem) o << "      if (fArena) fProvider.dealloc(fArena, fProvider.user);\n";
    else o << "      if (fArena) cudaFree(fArena);\n";
@@ -598,7 +655,38 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    const std::string out0 = fOutputTensorNames.empty() ? "" : fOutputTensorNames[0];
    const std::string outT = out0.empty() ? "void" : ConvertTypeToString(typeOf(out0));
    o << "   // device pointers in; the returned device pointer is owned by the Session and overwritten by the next call\n";
-   o << "   " << outT << " *infer_nosync(" << params << ")\n   {\n      _infer_impl(" << args << ");\n      return " << outMember(out0) << ";\n   }\n";
+   {
+      std::string same, remember, inArr;
+      for (size_t i = 0; i < nIn; ++i) {
+         same += " && g.in[" + std::to_string(i) + "] == tensor_" + fInputTensorNames[i];
+         remember += " slot->in[" + std::to_string(i) + "] = tensor_" + fInputTensorNames[i] + ";";
+      }
+      o << "   // with " << (profile ? "SetUseCudaGraph(true), " : "") << "the body is replayed from a CUDA graph (one launch instead of one per operator); a stream that is\n"
+           "   // already being captured by the caller just records the operators into the caller's graph\n";
+      o << "   void SetUseCudaGraph(bool on) { fUseCudaGraph = on; }\n";
+      o << "   void Enqueue(" << params << ")\n   {\n";
+      o << "      const size_t call = fCalls++;\n";
+      o << "      cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;\n";
+      o << "      if (!fUseCudaGraph || call == 0 || cudaStreamIsCapturing(stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) { _infer_impl(" << args << "); return; }\n";
+      o << "      CapturedGraph *slot = &fGraphs[0];\n";
+      o << "      for (auto &g : fGraphs) {\n";
+      o << "         if (g.exec" << same << ") { g.age = call; CheckCuda(cudaGraphLaunch(g.exec, stream), \"graph launch\"); return; }\n";
+      o << "         if (!g.exec || g.age < slot->age) slot = &g;\n";
+      o << "      }\n";
+      o << "      if (fGraphs[0].exec == nullptr) slot = &fGraphs[0]; else if (fGraphs[1].exec == nullptr) slot = &fGraphs[1];\n";
+      o << "      if (slot->exec) { cudaGraphExecDestroy(slot->exec); slot->exec = nullptr; }\n";
+      o << "      CheckCuda(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal), \"graph capture\");\n";
+      o << "      cudaGraph_t graph = nullptr;\n";
+      o << "      try { _infer_impl(" << args << "); } catch (...) { cudaStreamEndCapture(stream, &graph); if (graph) cudaGraphDestroy(graph); throw; }\n";
+      o << "      CheckCuda(cudaStreamEndCapture(stream, &graph), \"graph capture\");\n";
+      o << "      const cudaError_t ie = cudaGraphInstantiate(&slot->exec, graph, 0);\n";
+      o << "      cudaGraphDestroy(graph);\n";
+      o << "      CheckCuda(ie, \"graph instantiation\");\n";
+      o << "     " << remember << " slot->age = call;\n";
+      o << "      CheckCuda(cudaGraphLaunch(slot->exec, stream), \"graph launch\");\n";
+      o << "   }\n";
+   }
+   o << "   " << outT << " *infer_nosync(" << params << ")\n   {\n      Enqueue(" << args << ");\n      return " << outMember(out0) << ";\n   }\n";
    o << "   " << outT << " *infer(" << params << ")\n   {\n      " << outT << " *r = infer_nosync(" << args << ");\n"
      << "      Check(sofie_b200_ctx_sync(ctx), \"infer\");\n";
    if (profile) {
@@ -621,6 +709,55 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    o << "      std::vector<" << outT << "> h(" << outLen << ");\n";
    o << "      CheckCuda(cudaMemcpyAsync(h.data(), d, " << outLen << " * sizeof(" << outT << "), cudaMemcpyDeviceToHost, stream), \"output download\");\n";
    o << "      Check(sofie_b200_ctx_sync(ctx), \"infer_host\");\n      return h;\n   }\n";
+   if (!customMem && !out0.empty()) {
+      // a queue of inferences from host memory
+      size_t inBytes = 0;
+      std::vector<size_t> inOff;
+      for (auto &n : fInputTensorNames) { inOff.push_back(inBytes); inBytes += (region.at(n)->bytes + 255) / 256 * 256; }
+      const size_t outBytes = outLen * GetTypeSize(typeOf(out0)), outPad = (outBytes + 255) / 256 * 256;
+      std::string manyParams, stage0, stage1;
+      for (size_t i = 0; i < fInputTensorNames.size(); ++i) {
+         const auto &n = fInputTensorNames[i];
+         const std::string ct = ConvertTypeToString(typeOf(n));
+         manyParams += "const " + ct + " *const *hosts_" + n + ", ";
+         stage0 += (i ? ", " : "") + std::string("fInputStage_") + n;
+         stage1 += (i ? ", " : "") + std::string("reinterpret_cast<const ") + ct + " *>(fQueueMem + " + std::to_string(inOff[i]) + ")";
+      }
+      o << "   // A queue of `count` inferences from host memory (pinned memory lets the copies run beside the kernels): input i + 1 is\n"
+           "   // copied to the second staging set while inference i runs, and output i leaves through a parking buffer while inference\n"
+           "   // i + 1 runs.  host_out[i] receives the first output of inference i; returns when all of them are written.\n";
+      o << "   void infer_host_many(size_t count, " << manyParams << outT << " *const *host_out)\n   {\n";
+      o << "      if (!fCopyIn) {\n";
+      o << "         CheckCuda(cudaMalloc(reinterpret_cast<void **>(&fQueueMem), " << inBytes + 2 * outPad << "), \"queue buffers\");\n";
+      o << "         CheckCuda(cudaStreamCreateWithFlags(&fCopyIn, cudaStreamNonBlocking), \"stream\");\n";
+      o << "         CheckCuda(cudaStreamCreateWithFlags(&fCopyOut, cudaStreamNonBlocking), \"stream\");\n";
+      o << "         for (int i = 0; i < 2; ++i) for (cudaEvent_t *e : {&fEvReady[i], &fEvConsumed[i], &fEvParked[i], &fEvLeft[i]}) CheckCuda(cudaEventCreateWithFlags(e, cudaEventDisableTiming), \"event\");\n";
+      o << "      }\n";
+      o << "      CheckCuda(cudaStreamSynchronize(stream), \"queue start\");\n";
+      o << "      for (size_t i = 0; i < count; ++i) {\n";
+      o << "         const int s = int(i & 1);\n";
+      o << "         if (i >= 2) CheckCuda(cudaStreamWaitEvent(fCopyIn, fEvConsumed[s], 0), \"queue\");\n";
+      for (size_t i = 0; i < fInputTensorNames.size(); ++i) {
+         const auto &n = fInputTensorNames[i];
+         o << "         CheckCuda(cudaMemcpyAsync(s ? static_cast<void *>(fQueueMem + " << inOff[i] << ") : static_cast<void *>(fInputStage_" << n << "), hosts_" << n
+           << "[i], " << region.at(n)->bytes << ", cudaMemcpyHostToDevice, fCopyIn), \"input upload\");\n";
+      }
+      o << "         CheckCuda(cudaEventRecord(fEvReady[s], fCopyIn), \"queue\");\n";
+      o << "         CheckCuda(cudaStreamWaitEvent(stream, fEvReady[s], 0), \"queue\");\n";
+      o << "         " << outT << " *d = s ? infer_nosync(" << stage1 << ") : infer_nosync(" << stage0 << ");\n";
+      o << "         CheckCuda(cudaEventRecord(fEvConsumed[s], stream), \"queue\");\n";
+      o << "         char *park = fQueueMem + " << inBytes << " + size_t(s) * " << outPad << ";\n";
+      o << "         if (i >= 2) CheckCuda(cudaStreamWaitEvent(stream, fEvLeft[s], 0), \"queue\");\n";
+      o << "         CheckCuda(cudaMemcpyAsync(park, d, " << outBytes << ", cudaMemcpyDeviceToDevice, stream), \"output parking\");\n";
+      o << "         CheckCuda(cudaEventRecord(fEvParked[s], stream), \"queue\");\n";
+      o << "         CheckCuda(cudaStreamWaitEvent(fCopyOut, fEvParked[s], 0), \"queue\");\n";
+      o << "         CheckCuda(cudaMemcpyAsync(host_out[i], park, " << outBytes << ", cudaMemcpyDeviceToHost, fCopyOut), \"output download\");\n";
+      o << "         CheckCuda(cudaEventRecord(fEvLeft[s], fCopyOut), \"queue\");\n";
+      o << "      }\n";
+      o << "      CheckCuda(cudaStreamSynchronize(fCopyOut), \"queue end\");\n";
+      o << "      Check(sofie_b200_ctx_sync(ctx), \"infer_host_many\");\n";
+      o << "   }\n";
+   }
    o << "   // zeroes the pooled intermediates (the reference's resetState)\n";
    o << "   void resetState()\n   {\n      CheckCuda(cudaMemsetAsync(fArena + (kArenaBytes - kPoolBytes), 0, kPoolBytes, stream), \"resetState\");\n   }\n";
    o << "   size_t GetIntermediateMemoryPoolSize() const { return kPoolBytes; }\n";
@@ -648,6 +785,58 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    }
    o << "};\n\n}  // namespace SOFIE_" << fName << "\n\n#endif  // SOFIE_B200_" << guard << "\n";
    return o.str();
+}
+
+// safetensors type names: the reference's F32 / F64 / I64 (core/src/RModel.cxx:51-59) plus the low-precision types of this target
+std::string SafetensorsDType(ETensorType type)
+{
+   switch (type) {
+   case ETensorType::FLOAT: return "F32";
+   case ETensorType::DOUBLE: return "F64";
+   case ETensorType::INT64: return "I64";
+   case ETensorType::INT32: return "I32";
+   case ETensorType::INT8: return "I8";
+   case ETensorType::UINT8: return "U8";
+   case ETensorType::BOOL: return "BOOL";
+   case ETensorType::BFLOAT16: return "BF16";
+   case ETensorType::FLOAT8E4M3FN: return "F8_E4M3";
+   default: throw std::runtime_error("sofie tensor with type " + ConvertTypeToString(type) + " cannot be written to a safetensors file");
+   }
+}
+
+// Layout of the reference's writer (core/src/RModel.cxx:1967-2010): names sorted, header size as 8 little-endian bytes, JSON
+// header, payload in the same order with no padding.
+void RModel::WriteSafetensorsFile(const std::string &filename) const
+{
+   const std::uint16_t one = 1;
+   if (!*reinterpret_cast<const std::uint8_t *>(&one)) throw std::runtime_error("sofie: safetensors weights can only be written on a little-endian host");
+   std::vector<std::string> names;
+   for (auto &r : fRegions)
+      if (r.kind == "weight") names.push_back(r.name);
+   std::sort(names.begin(), names.end());
+   std::string header = "{";
+   std::uint64_t offset = 0;
+   for (size_t i = 0; i < names.size(); ++i) {
+      const auto &t = fInitializedTensors.at(names[i]);
+      const std::uint64_t nbytes = ConvertShapeToLength(t.shape) * GetTypeSize(t.type);
+      header += std::string(i ? "," : "") + "\"tensor_" + names[i] + "\":{\"dtype\":\"" + SafetensorsDType(t.type) + "\",\"shape\":[";
+      for (size_t d = 0; d < t.shape.size(); ++d) header += (d ? "," : "") + std::to_string(t.shape[d]);
+      header += "],\"data_offsets\":[" + std::to_string(offset) + "," + std::to_string(offset + nbytes) + "]}";
+      offset += nbytes;
+   }
+   header += "}";
+   std::ofstream f(filename, std::ios::binary);
+   if (!f.is_open()) throw std::runtime_error("sofie-b200 failed to open file " + filename + " for tensor weight data");
+   const std::uint64_t hs = header.size();
+   char sz[8];
+   for (int i = 0; i < 8; ++i) sz[i] = static_cast<char>((hs >> (8 * i)) & 0xff);
+   f.write(sz, 8);
+   f.write(header.data(), std::streamsize(header.size()));
+   for (auto &n : names) {
+      const auto &t = fInitializedTensors.at(n);
+      f.write(static_cast<const char *>(t.data.get()), std::streamsize(ConvertShapeToLength(t.shape) * GetTypeSize(t.type)));
+   }
+   if (f.fail()) throw std::runtime_error("sofie failed to write safetensors payload");
 }
 
 void RModel::WriteWeightFile(const std::string &filename) const
@@ -679,7 +868,8 @@ void RModel::OutputGenerated(std::string filename, bool append)
       // the Session's default weight file name is <model>.dat, next to the header
       auto slash = dat.find_last_of("/\\");
       const std::string dir = slash == std::string::npos ? "" : dat.substr(0, slash + 1);
-      WriteWeightFile(dir + fName + ".dat");
+      if (fOptions & static_cast<std::underlying_type_t<Options>>(Options::kSafetensorsWeightFile)) WriteSafetensorsFile(dir + fName + ".safetensors");
+      else WriteWeightFile(dir + fName + ".dat");
    }
 }
 

@@ -2,7 +2,7 @@
 // of the reference's emitter programs (tests/templates/EmitFromONNX_GPU_ALPAKA.cxx.in:9-17).
 //
 //   sofie_b200_emit <model.onnx> <out.hxx> [--batch N] [--external-stream] [--custom-memory]
-//                   [--profile] [--debug] [--no-weight-file] [--check]
+//                   [--profile] [--debug] [--no-weight-file] [--safetensors] [--check]
 //
 // Prints a one-line JSON report of what generation decided (fusions, arena size) on stdout.
 #include <cstring>
@@ -16,7 +16,7 @@ int main(int argc, char **argv)
 {
    if (argc < 3) {
       std::cerr << "usage: sofie_b200_emit <model.onnx> <out.hxx> [--batch N] [--external-stream] [--custom-memory] [--profile] [--debug] "
-                   "[--no-weight-file] [--check]\n";
+                   "[--no-weight-file] [--safetensors] [--check]\n";
       return 2;
    }
    std::underlying_type_t<Options> opts = 0;
@@ -29,6 +29,7 @@ int main(int argc, char **argv)
       else if (!std::strcmp(argv[i], "--profile")) opts = opts | Options::kProfile;
       else if (!std::strcmp(argv[i], "--debug")) opts = opts | Options::kDebug;
       else if (!std::strcmp(argv[i], "--no-weight-file")) opts = opts | Options::kNoWeightFile;
+      else if (!std::strcmp(argv[i], "--safetensors")) opts = opts | Options::kSafetensorsWeightFile;
       else if (!std::strcmp(argv[i], "--check")) checkOnly = true;
       else { std::cerr << "unknown option " << argv[i] << "\n"; return 2; }
    }

@@ -1,6 +1,7 @@
-"""Minimal reader of ONNX model files (protobuf wire format), enough for the pinned test models.
+"""Minimal reader and writer of ONNX model files (protobuf wire format): enough for the models of the test-suite and
+for the benchmark configurations, which are written as ONNX files and handed to the C++ generator.
 
-Test infrastructure.  The `onnx` Python package is not available, and the reference carries its
+The `onnx` Python package is not available, and the reference carries its
 own wire reader for the same reason (parsers/src/onnx.hxx:19-120).  Only the fields the hot-path
 models use are decoded: graph nodes with attributes, initializers (float/int64/int32, raw or typed
 storage), graph inputs and outputs with static shapes.

@@ -26,8 +26,8 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-sys.path.insert(0, str(HERE.parent))
-import onnx_min  # noqa: E402
+sys.path.insert(0, str(ROOT))
+from sofie_b200 import onnx_min  # noqa: E402
 
 if len(sys.argv) < 2 and "SOFIE_REFERENCE" not in os.environ:
     sys.exit("usage: make_golden.py <reference checkout>   (or SOFIE_REFERENCE=<path>)")

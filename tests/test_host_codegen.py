@@ -15,7 +15,7 @@ import numpy as np
 import pytest
 
 import graph_runner as gr
-import onnx_min
+from sofie_b200 import onnx_min
 from sofie_b200 import build as B
 
 ROOT = Path(__file__).resolve().parent.parent
@@ -56,7 +56,10 @@ def test_emit_and_compile_every_golden_model(name, emit, tmp_path):
     assert f"namespace SOFIE_{name}" in text and "struct Session" in text
     for member in ("infer(", "infer_nosync(", "_infer_impl(", "infer_host(", "resetState()"):
         assert member in text
-    assert "alpaka" not in text and "cudaMalloc(" in text and text.count("cudaMalloc(") == 1  # one arena allocation
+    # one arena allocation at construction; the only other one is the lazy queue buffer of infer_host_many
+    assert "alpaka" not in text and text.count('"arena allocation"') == 1 and text.count("cudaMalloc(") == 2 and '"queue buffers"' in text
+    for member in ("Enqueue(", "SetUseCudaGraph(", "infer_host_many(", "cudaGraphLaunch("):
+        assert member in text
     chk = syntax_check(tmp_path / f"{name}.hxx")
     assert chk.returncode == 0, chk.stderr[:2000]
 
@@ -241,3 +244,42 @@ def test_emitted_session_reproduces_reference_results(name, emit, tmp_path, b200
         floor = float(np.sqrt(np.mean(np.square(want))))
         assert np.all(np.abs(got - want) <= 1e-5 * np.maximum(np.abs(want), floor)), f"{name}/{tag}: {np.abs(got - want).max():.3g}"
         assert launches.value >= 1
+
+
+def test_safetensors_weight_file_round_trips_low_precision_types(emit, tmp_path):
+    """Options::kSafetensorsWeightFile: the generator writes <model>.safetensors in the reference's layout (8-byte header size,
+    JSON header with sorted names, raw payload; core/src/RModel.cxx:1967-2010) with I8, F32 and the other types of this
+    target; every weight must come back bit for bit, and the emitted Session must read that file."""
+    from safetensors import safe_open
+    rng = np.random.default_rng(9)
+    w = {"B": rng.integers(-127, 128, size=(64, 32), dtype=np.int8), "a_scale": np.array(0.02, dtype=np.float32),
+         "a_zp": np.array(0, dtype=np.int8), "b_scale": np.array(0.01, dtype=np.float32), "b_zp": np.array(0, dtype=np.int8),
+         "y_scale": np.array(0.5, dtype=np.float32), "y_zp": np.array(0, dtype=np.int8)}
+    nodes = [{"op": "QLinearMatMul", "in": ["A", "a_scale", "a_zp", "B", "b_scale", "b_zp", "y_scale", "y_zp"], "out": ["Y"], "attrs": {}}]
+    onnx_min.save(str(tmp_path / "q.onnx"), nodes, w, [("A", [16, 64])], ["Y"], input_types={"A": 3})
+    rc, out, err = run_emit(emit, tmp_path / "q.onnx", tmp_path / "q.hxx", "--safetensors")
+    assert rc == 0, err
+    assert not (tmp_path / "q.dat").exists()
+    with safe_open(str(tmp_path / "q.safetensors"), framework="numpy") as f:
+        assert "tensor_B" in f.keys()
+        assert np.array_equal(f.get_tensor("tensor_B"), w["B"]) and f.get_tensor("tensor_B").dtype == np.int8
+    text = (tmp_path / "q.hxx").read_text()
+    assert 'std::string filename = "q.safetensors"' in text and 'FindSafetensor(blob, "tensor_B", "I8", 2048)' in text
+    assert "ReadTensorFromStream(f" not in text
+    assert syntax_check(tmp_path / "q.hxx").returncode == 0
+    # bf16 and fp8 initializers: written as BF16 / F8_E4M3, payload bytes untouched
+    bits16 = rng.integers(0, 0x7F00, size=(8, 16)).astype(np.uint16)
+    bits8 = rng.integers(0, 0x70, size=(16, 8)).astype(np.uint8)
+    nodes = [{"op": "Add", "in": ["X", "W16"], "out": ["Y"], "attrs": {}}]
+    onnx_min.save(str(tmp_path / "b.onnx"), nodes, {"W16": bits16, "unused8": bits8}, [("X", [8, 16])], ["Y"], input_types={"X": 16},
+                  initializer_types={"W16": 16, "unused8": 17})
+    rc, out, err = run_emit(emit, tmp_path / "b.onnx", tmp_path / "b.hxx", "--safetensors")
+    assert rc == 0, err
+    raw = (tmp_path / "b.safetensors").read_bytes()
+    hs = int.from_bytes(raw[:8], "little")
+    header = json.loads(raw[8:8 + hs])
+    e = header["tensor_W16"]
+    assert e["dtype"] == "BF16" and e["shape"] == [8, 16]
+    assert raw[8 + hs + e["data_offsets"][0]:8 + hs + e["data_offsets"][1]] == bits16.tobytes()
+    if "tensor_unused8" in header:
+        assert header["tensor_unused8"]["dtype"] == "F8_E4M3"

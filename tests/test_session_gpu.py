@@ -1,0 +1,203 @@
+"""Emitted Sessions on the GPU beyond the fp32 golden models: quantised operators, the safetensors weight file, CUDA-graph
+replay, the pipelined host queue, and the external-stream / custom-memory options, modelled on the reference's own
+device tests (tests/alpaka/TestAlpakaExternalStream.cxx:5-45, tests/alpaka/TestAlpakaCustomMemory.cxx:113-183).
+
+Every model is written as an ONNX file, emitted by the C++ generator, compiled with g++ against include/sofie_b200.h and
+run through a small C wrapper; results are compared with the CPU checker (bit for bit for int8).
+"""
+import ctypes as C
+import subprocess
+
+import numpy as np
+import pytest
+
+import graph_runner as gr
+from oracle_api import Oracle
+from sofie_b200 import build as B
+from sofie_b200 import lib as L
+from sofie_b200 import onnx_min
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def emit():
+    return B.build_host()
+
+
+# infer_host three times (eager, captured, replayed) and a queue of 5 through infer_host_many: all results must agree
+TYPED_WRAPPER = """
+#include "{header}"
+#include <cstring>
+static std::string g_err;
+extern "C" const char *session_error() {{ return g_err.c_str(); }}
+extern "C" long session_run(const char *file, const {tin} *x, {tout} *out, long cap, long long *launches)
+{{
+   try {{
+      SOFIE_{name}::Session s(file);
+      std::vector<{tout}> y0 = s.infer_host(x);
+      const long long eager = s.GetLaunchCount();
+      std::vector<{tout}> y1 = s.infer_host(x), y2 = s.infer_host(x);
+      if (y1 != y0 || y2 != y0) {{ g_err = "graph capture / replay changed the result"; return -2; }}
+      launches[0] = eager;
+      launches[1] = s.GetLaunchCount();
+      std::vector<std::vector<{tout}>> q(5, std::vector<{tout}>(y0.size()));
+      const {tin} *ins[5] = {{x, x, x, x, x}};
+      {tout} *outs[5];
+      for (int i = 0; i < 5; ++i) outs[i] = q[i].data();
+      s.infer_host_many(5, ins, outs);
+      for (int i = 0; i < 5; ++i) if (q[i] != y0) {{ g_err = "infer_host_many differs from infer_host at " + std::to_string(i); return -3; }}
+      std::memcpy(out, y0.data(), sizeof({tout}) * (y0.size() < (size_t)cap ? y0.size() : (size_t)cap));
+      return (long)y0.size();
+   }} catch (const std::exception &e) {{ g_err = e.what(); return -1; }}
+}}
+"""
+
+
+def emit_and_load(emit, tmp_path, name, nodes, weights, inputs, outputs, wrapper, flags=(), **onnx_kw):
+    onnx_min.save(str(tmp_path / f"{name}.onnx"), nodes, weights, inputs, outputs, **onnx_kw)
+    r = subprocess.run([str(emit), str(tmp_path / f"{name}.onnx"), str(tmp_path / f"{name}.hxx"), *flags], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    so = B.compile_session(tmp_path / f"{name}.hxx", tmp_path / f"libsession_{name}.so", wrapper)
+    lib = C.CDLL(str(so))
+    lib.session_error.restype = C.c_char_p
+    return lib
+
+
+def test_qlinear_matmul_session_bit_exact_from_safetensors(emit, tmp_path, oracle_lib, b200_lib):
+    """A parsed QLinearMatMul model (per-column weight scales, non-zero input zero point, uint8 output) as an emitted
+    Session reading its int8 weights from a safetensors file."""
+    o = Oracle(oracle_lib)
+    rng = np.random.default_rng(31)
+    M, K, N = 200, 256, 144
+    a = rng.integers(-128, 128, size=(M, K), dtype=np.int8)
+    b = rng.integers(-127, 128, size=(K, N), dtype=np.int8)
+    a_scale, y_scale, a_zp, y_zp = np.float32(0.02), np.float32(0.4), 3, 120
+    b_scale = (rng.random(N, dtype=np.float32) * 0.01 + 0.005).astype(np.float32)
+    w = {"B": b, "a_scale": np.array(a_scale), "a_zp": np.array(a_zp, dtype=np.int8), "b_scale": b_scale, "b_zp": np.zeros(N, dtype=np.int8),
+         "y_scale": np.array(y_scale), "y_zp": np.array(y_zp, dtype=np.uint8)}
+    nodes = [{"op": "QLinearMatMul", "in": ["A", "a_scale", "a_zp", "B", "b_scale", "b_zp", "y_scale", "y_zp"], "out": ["Y"], "attrs": {}}]
+    src = TYPED_WRAPPER.format(header=tmp_path / "qmm.hxx", name="qmm", tin="int8_t", tout="uint8_t")
+    lib = emit_and_load(emit, tmp_path, "qmm", nodes, w, [("A", [M, K])], ["Y"], src, flags=("--safetensors",), input_types={"A": 3})
+    # checker: acc = sum (a - a_zp) b;  y = sat(rint(acc * (a_scale * b_scale[j] / y_scale)) + y_zp)
+    mult = (a_scale * b_scale / y_scale).astype(np.float32)
+    corr = (-a_zp * b.astype(np.int32).sum(axis=0)).astype(np.int32)
+    want = o.gemm(a, b, M, N, K, L.I8, L.U8, ep=o.epilogue(col_scale=mult, bias=corr, out_zero_point=y_zp))
+    got = np.zeros((M, N), dtype=np.uint8)
+    launches = (C.c_longlong * 2)()
+    n = lib.session_run(str(tmp_path / "qmm.safetensors").encode(), a.ctypes.data_as(C.c_void_p), got.ctypes.data_as(C.c_void_p), got.size, launches)
+    assert n == got.size, lib.session_error().decode()
+    assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size} differ"
+    # the first call enqueued the operators (and the one-time K-major copy of the weight); the captured call enqueued them
+    # once more; the replay enqueued nothing
+    assert launches[0] >= 1 and launches[1] - launches[0] <= launches[0]
+
+
+def test_qlinear_conv_session_bit_exact(emit, tmp_path, oracle_lib, b200_lib):
+    """QLinearConv (per-channel weight scales, int32 bias, input zero point) -> QLinearConv: a parsed two-layer int8 model."""
+    o = Oracle(oracle_lib)
+    rng = np.random.default_rng(32)
+    x = rng.integers(-100, 100, size=(2, 16, 12, 10), dtype=np.int8)
+    w1 = rng.integers(-127, 128, size=(32, 16, 3, 3), dtype=np.int8)
+    w2 = rng.integers(-127, 128, size=(16, 32, 1, 1), dtype=np.int8)
+    s1 = (rng.random(32, dtype=np.float32) * 0.01 + 0.002).astype(np.float32)
+    s2 = (rng.random(16, dtype=np.float32) * 0.01 + 0.002).astype(np.float32)
+    b1 = rng.integers(-3000, 3000, size=32, dtype=np.int32)
+    xs, h_s, ys, x_zp = np.float32(0.05), np.float32(0.9), np.float32(1.1), 4
+    w = {"w1": w1, "w2": w2, "s1": s1, "s2": s2, "b1": b1, "xs": np.array(xs), "hs": np.array(h_s), "ys": np.array(ys),
+         "xzp": np.array(x_zp, dtype=np.int8), "z8": np.array(0, dtype=np.int8), "wz1": np.zeros(32, dtype=np.int8), "wz2": np.zeros(16, dtype=np.int8)}
+    nodes = [{"op": "QLinearConv", "in": ["X", "xs", "xzp", "w1", "s1", "wz1", "hs", "z8", "b1"], "out": ["H"],
+              "attrs": {"kernel_shape": [3, 3], "pads": [1, 1, 1, 1], "strides": [2, 1]}},
+             {"op": "QLinearConv", "in": ["H", "hs", "z8", "w2", "s2", "wz2", "ys", "z8"], "out": ["Y"], "attrs": {"kernel_shape": [1, 1], "pads": [0, 0, 0, 0]}}]
+    src = TYPED_WRAPPER.format(header=tmp_path / "qconv.hxx", name="qconv", tin="int8_t", tout="int8_t")
+    lib = emit_and_load(emit, tmp_path, "qconv", nodes, w, [("X", list(x.shape))], ["Y"], src, input_types={"X": 3})
+    # checker: layer by layer, padding filled with the input zero point
+    g1 = gr.conv_geometry({"pads": [1, 1, 1, 1], "strides": [2, 1]}, x.shape, w1.shape)
+    d1 = gr.conv_desc(g1, x.shape, w1.shape, L.I8, L.I8)
+    d1.x_zero_point = x_zp
+    bias1 = (b1 - x_zp * w1.astype(np.int32).reshape(32, -1).sum(axis=1)).astype(np.int32)
+    h = o.conv(x, w1, d1, g1["ho"], g1["wo"], ep=o.epilogue(col_scale=(xs * s1 / h_s).astype(np.float32), bias=bias1))
+    g2 = gr.conv_geometry({"pads": [0, 0, 0, 0]}, h.shape, w2.shape)
+    d2 = gr.conv_desc(g2, h.shape, w2.shape, L.I8, L.I8)
+    want = o.conv(h, w2, d2, g2["ho"], g2["wo"], ep=o.epilogue(col_scale=(h_s * s2 / ys).astype(np.float32)))
+    got = np.zeros(want.shape, dtype=np.int8)
+    launches = (C.c_longlong * 2)()
+    n = lib.session_run(str(tmp_path / "qconv.dat").encode(), x.ctypes.data_as(C.c_void_p), got.ctypes.data_as(C.c_void_p), got.size, launches)
+    assert n == got.size, lib.session_error().decode()
+    assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size} differ"
+
+
+EXT_WRAPPER = """
+#include "{header}"
+#include <cstring>
+using namespace SOFIE_{name};
+static std::string g_err;
+extern "C" const char *session_error() {{ return g_err.c_str(); }}
+struct State {{ int allocs = 0, deallocs = 0; size_t bytes = 0; char *block = nullptr; }};
+static void *my_alloc(size_t bytes, void *user)
+{{
+   State *s = static_cast<State *>(user);
+   ++s->allocs;
+   s->bytes = bytes;
+   if (cudaMalloc(reinterpret_cast<void **>(&s->block), bytes + 4096) != cudaSuccess) return nullptr;
+   return s->block + 4096;   // not the start of an allocation: the Session must use exactly what it is given
+}}
+static void my_dealloc(void *, void *user)
+{{
+   State *s = static_cast<State *>(user);
+   ++s->deallocs;
+   cudaFree(s->block);
+}}
+static void *null_alloc(size_t, void *) {{ return nullptr; }}
+// counts: allocations, deallocations, block size == arena size, result inside the block, null block rejected, empty provider rejected
+extern "C" long session_run(const char *file, const float *x_host, long nx, float *out, long cap, int *counts)
+{{
+   cudaStream_t st = nullptr;
+   float *x_d = nullptr;
+   long n = -1;
+   try {{
+      if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess) throw std::runtime_error("stream");
+      if (cudaMalloc(reinterpret_cast<void **>(&x_d), sizeof(float) * nx) != cudaSuccess) throw std::runtime_error("malloc");
+      cudaMemcpy(x_d, x_host, sizeof(float) * nx, cudaMemcpyHostToDevice);
+      State state;
+      {{
+         MemoryProvider prov{{my_alloc, my_dealloc, &state}};
+         Session s(prov, st, file);
+         counts[0] = state.allocs;
+         counts[2] = state.bytes == s.GetArenaSize();
+         for (int rep = 0; rep < 3; ++rep) {{              // eager, captured on the caller's stream, replayed
+            float *r = s.infer_nosync(x_d);                 // records on the caller's stream only
+            if (cudaStreamSynchronize(st) != cudaSuccess) throw std::runtime_error("sync");
+            counts[3] = reinterpret_cast<char *>(r) >= state.block + 4096 && reinterpret_cast<char *>(r) < state.block + 4096 + state.bytes;
+            cudaMemcpy(out, r, sizeof(float) * cap, cudaMemcpyDeviceToHost);
+         }}
+         n = cap;
+      }}
+      counts[1] = state.deallocs;
+      State other;
+      try {{ MemoryProvider bad{{null_alloc, my_dealloc, &other}}; Session s2(bad, st, file); counts[4] = 0; }} catch (const std::runtime_error &) {{ counts[4] = 1; }}
+      try {{ MemoryProvider none{{}}; Session s3(none, st, file); counts[5] = 0; }} catch (const std::runtime_error &) {{ counts[5] = 1; }}
+   }} catch (const std::exception &e) {{ g_err = e.what(); n = -1; }}
+   if (x_d) cudaFree(x_d);
+   if (st) cudaStreamDestroy(st);
+   return n;
+}}
+"""
+
+
+def test_external_stream_and_custom_memory_session(emit, tmp_path, b200_lib):
+    """The reference's ExternalStreamGemmRelu model (ones [3,5] x 0.5 [5,4] + 1, Relu = 3.5) in a Session that borrows the
+    caller's stream and takes its one block of device memory from the caller's provider."""
+    w = {"W": np.full((5, 4), 0.5, dtype=np.float32), "B": np.ones(4, dtype=np.float32)}
+    nodes = [{"op": "Gemm", "in": ["X", "W", "B"], "out": ["G"], "attrs": {}}, {"op": "Relu", "in": ["G"], "out": ["Y"], "attrs": {}}]
+    src = EXT_WRAPPER.format(header=tmp_path / "ext.hxx", name="ext")
+    lib = emit_and_load(emit, tmp_path, "ext", nodes, w, [("X", [3, 5])], ["Y"], src, flags=("--external-stream", "--custom-memory"))
+    text = (tmp_path / "ext.hxx").read_text()
+    assert "cudaMalloc(" not in text          # no allocation of its own (the reference's GeneratedCodeHasNoAlpakaDeviceAllocation)
+    x = np.ones((3, 5), dtype=np.float32)
+    out = np.zeros(12, dtype=np.float32)
+    counts = (C.c_int * 6)()
+    n = lib.session_run(str(tmp_path / "ext.dat").encode(), x.ctypes.data_as(C.c_void_p), x.size, out.ctypes.data_as(C.c_void_p), out.size, counts)
+    assert n == 12, lib.session_error().decode()
+    assert np.all(np.abs(out - 3.5) <= 1e-6)
+    assert list(counts) == [1, 1, 1, 1, 1, 1], list(counts)
