@@ -136,3 +136,41 @@ class EncoderB200:
                 ly[name]["plan"].close()
         self.qk.close()
         self.pv.close()
+
+
+def onnx_model(weights, batch: int, seq: int, d_model: int, heads: int):
+    """The encoder as an ONNX graph for the C++ generator (sofie_b200/onnx_min.save): bf16 activations [batch*seq, d_model];
+    every projection is DequantizeLinear(int8 weight [out, in], per-output-channel scale) -> Gemm(transB = 1) with an fp32
+    bias; attention is Split -> Reshape -> ScaledDotProductAttention(num_heads) on the folded [batch, seq, d_model] layout.
+    Returns (nodes, initializers, inputs, outputs, input_types)."""
+    m = batch * seq
+    init = {"shape_bsd": np.array([batch, seq, d_model], dtype=np.int64), "shape_md": np.array([m, d_model], dtype=np.int64)}
+    nodes = []
+
+    def linear(x, name, l, out):
+        wq, scale, bias = weights[l][name]
+        init[f"{name}_q_{l}"], init[f"{name}_s_{l}"], init[f"{name}_b_{l}"] = wq, scale, bias
+        nodes.append({"op": "DequantizeLinear", "in": [f"{name}_q_{l}", f"{name}_s_{l}"], "out": [f"{name}_w_{l}"], "attrs": {"axis": 0}})
+        nodes.append({"op": "Gemm", "in": [x, f"{name}_w_{l}", f"{name}_b_{l}"], "out": [out], "attrs": {"transB": 1}})
+
+    x = "X"
+    for l, ly in enumerate(weights):
+        for k in ("g1", "b1", "g2", "b2"):
+            init[f"{k}_{l}"] = ly[k]
+        nodes.append({"op": "LayerNormalization", "in": [x, f"g1_{l}", f"b1_{l}"], "out": [f"h1_{l}"], "attrs": {"axis": -1, "epsilon": 1e-5}})
+        linear(f"h1_{l}", "qkv", l, f"qkv_{l}")
+        nodes.append({"op": "Split", "in": [f"qkv_{l}"], "out": [f"q_{l}", f"k_{l}", f"v_{l}"], "attrs": {"axis": 1}})
+        for t in "qkv":
+            nodes.append({"op": "Reshape", "in": [f"{t}_{l}", "shape_bsd"], "out": [f"{t}3_{l}"], "attrs": {}})
+        nodes.append({"op": "ScaledDotProductAttention", "in": [f"q3_{l}", f"k3_{l}", f"v3_{l}"], "out": [f"att3_{l}"], "attrs": {"num_heads": heads}})
+        nodes.append({"op": "Reshape", "in": [f"att3_{l}", "shape_md"], "out": [f"att_{l}"], "attrs": {}})
+        linear(f"att_{l}", "out", l, f"proj_{l}")
+        nodes.append({"op": "Add", "in": [f"proj_{l}", x], "out": [f"x1_{l}"], "attrs": {}})
+        nodes.append({"op": "LayerNormalization", "in": [f"x1_{l}", f"g2_{l}", f"b2_{l}"], "out": [f"h2_{l}"], "attrs": {"axis": -1, "epsilon": 1e-5}})
+        linear(f"h2_{l}", "ff1", l, f"f_{l}")
+        nodes.append({"op": "Gelu", "in": [f"f_{l}"], "out": [f"g_{l}"], "attrs": {}})
+        linear(f"g_{l}", "ff2", l, f"ff_{l}")
+        out = "Y" if l + 1 == len(weights) else f"x2_{l}"
+        nodes.append({"op": "Add", "in": [f"ff_{l}", f"x1_{l}"], "out": [out], "attrs": {}})
+        x = out
+    return nodes, init, [("X", [m, d_model])], ["Y"], {"X": 16}

@@ -105,6 +105,7 @@ public:
 
 private:
    void FuseOperators();
+   void FuseAttentionInputs();
    void PlanArena();
    std::string GenerateSessionCode_GPU_B200();
    void WriteWeightFile(const std::string &filename) const;

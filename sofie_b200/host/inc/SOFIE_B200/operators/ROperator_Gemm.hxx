@@ -9,6 +9,7 @@
 // Difference kept on purpose: a beta other than 1 multiplies C as ONNX defines it (the reference's
 // bias-broadcast branch drops it, :580).
 #pragma once
+#include <cstring>
 #include <iomanip>
 #include <sstream>
 
@@ -73,6 +74,8 @@ private:
    EpilogueState fEpi;
    std::vector<size_t> fShapeA, fShapeB, fShapeC, fShapeY;
    bool fBIsWeight = false;   // B is an initialized tensor (a weight)
+   std::string fNQuantB, fNQuantScale;   // see SetDequantisedWeight
+   int64_t fQuantAxis = 0;
    ETensorType fType = ETensorType::FLOAT, fTypeY = ETensorType::FLOAT;
    size_t fM = 0, fN = 0, fK = 0, fBatch = 1;
    int64_t fStrideA = 0, fStrideB = 0;
@@ -101,6 +104,14 @@ public:
    }
 
    bool HasBias() const { return !fNC.empty(); }
+   // B is DequantizeLinear(quantised INT8 initializer, per-output-channel scale): the weight-only quantised linear layer.
+   // With BFLOAT16 activations the int8 values become a BFLOAT16 initializer (exact: |q| <= 127) and the scale the column
+   // scale of the epilogue, so the dequantisation costs nothing at run time; with FLOAT activations the weight is folded
+   // to q * scale at generation (what the reference computes on dequantised weights).
+   void SetDequantisedWeight(const std::string &quantised, const std::string &scale, int64_t axis)
+   {
+      fNQuantB = UTILITY::Clean_name(quantised); fNQuantScale = UTILITY::Clean_name(scale); fQuantAxis = axis;
+   }
    EActivationType GetActivationType() const override { return fEpi.act; }
    // single-pass TF32 instead of the fp32-accurate path (off by default: parity bar is 1e-5)
    void SetPrecise(bool p) { fPrecise = p; }
@@ -110,6 +121,7 @@ public:
    {
       if (!model.CheckIfTensorAlreadyExist(fNA))
          throw std::runtime_error("SOFIE Gemm Op Input Tensor " + fNA + " is not found in model");
+      if (!fNQuantB.empty()) FoldDequantisedWeight(model);
       if (!model.CheckIfTensorAlreadyExist(fNB))
          throw std::runtime_error("SOFIE Gemm Op Input Tensor " + fNB + " is not found in model");
       if (!fNC.empty() && !model.CheckIfTensorAlreadyExist(fNC))
@@ -215,6 +227,38 @@ public:
          return;
       }
       model.AddIntermediateTensor(fNY, fTypeY, fShapeY);
+   }
+
+   void FoldDequantisedWeight(RModel &model)
+   {
+      if (!model.IsInitializedTensor(fNQuantB) || model.GetTensorType(fNQuantB) != ETensorType::INT8 || !model.IsInitializedTensor(fNQuantScale))
+         throw std::runtime_error("SOFIE Gemm Op: a dequantised weight needs an initialized INT8 tensor and an initialized scale");
+      const auto shape = model.GetTensorShape(fNQuantB);
+      if (shape.size() != 2) throw std::runtime_error("SOFIE Gemm Op: a dequantised weight must have rank 2");
+      const auto q = model.GetTensorData<int8_t>(fNQuantB);
+      const auto sc = model.GetTensorData<float>(fNQuantScale);
+      const size_t nAxis = fAttrTransB ? 0 : 1, n = shape[nAxis];
+      const int64_t axis = fQuantAxis < 0 ? fQuantAxis + 2 : fQuantAxis;
+      if (sc.size() != 1 && (sc.size() != n || size_t(axis) != nAxis))
+         throw std::runtime_error("SOFIE Gemm Op: the scale of a dequantised weight must be a scalar or run along the output channels");
+      auto scaleOf = [&](size_t r, size_t c) { return sc.size() == 1 ? sc[0] : sc[nAxis == 0 ? r : c]; };
+      if (model.GetTensorType(fNA) == ETensorType::BFLOAT16) {
+         std::vector<uint16_t> w(q.size());
+         for (size_t i = 0; i < q.size(); ++i) {
+            const float f = float(q[i]);
+            uint32_t u;
+            std::memcpy(&u, &f, 4);
+            w[i] = uint16_t(u >> 16);   // integers up to 127 fit the 8 significand bits exactly
+         }
+         model.AddInitializedTensor(fNB, ETensorType::BFLOAT16, shape, w);
+         if (sc.size() == 1) fAttrAlpha *= sc[0];
+         else { fEpi.colScale = fNQuantScale; fInputTensorNames.push_back(fNQuantScale); }
+      } else {
+         std::vector<float> w(q.size());
+         for (size_t r = 0; r < shape[0]; ++r)
+            for (size_t c = 0; c < shape[1]; ++c) w[r * shape[1] + c] = float(q[r * shape[1] + c]) * scaleOf(r, c);
+         model.AddInitializedTensor(fNB, ETensorType::FLOAT, shape, w);
+      }
    }
 
    // ---- fusion hooks ------------------------------------------------------------------------

@@ -332,6 +332,7 @@ public:
 
 // ---- ScaledGemm: FP8 e4m3 x e4m3 -> fp32, per-row / per-column scales, bias, activation -------------------------
 class ROperator_ScaledGemm final : public ROperator_B200 {
+   bool fBIsWeight = false;
    std::string fNA, fNB, fNRowScale, fNColScale, fNBias, fNY;
    int fTransB;
    EpilogueState fEpi;
@@ -371,6 +372,7 @@ public:
       if (fShapeA.size() != 2 || fShapeB.size() != 2) throw std::runtime_error("SOFIE ScaledGemm Op: rank-2 operands expected");
       fM = fShapeA[0]; fK = fShapeA[1];
       fN = fTransB ? fShapeB[0] : fShapeB[1];
+      fBIsWeight = model.IsInitializedTensor(fNB);
       if ((fTransB ? fShapeB[1] : fShapeB[0]) != fK) throw std::runtime_error("SOFIE ScaledGemm Op : invalid input shapes");
       if (!fNColScale.empty()) fEpi.colScale = fNColScale;
       if (!fNBias.empty()) { fEpi.bias = fNBias; fEpi.biasMode = "SOFIE_B200_BIAS_COL_F32"; }
@@ -387,6 +389,7 @@ public:
       out << "      {  // ScaledGemm " << opName << "\n      sofie_b200_gemm_desc d{};\n";
       out << "      d.M = " << fM << "; d.N = " << fN << "; d.K = " << fK << "; d.batch = 1; d.trans_b = " << fTransB << ";\n";
       out << "      d.ab_dtype = SOFIE_B200_F8E4M3; d.y_dtype = " << ConvertTypeToRuntimeEnum(fTypeY) << ";\n";
+      if (fBIsWeight) out << "      d.flags = SOFIE_B200_GEMM_B_CONSTANT;  // B is an initializer: the plan keeps it K-major\n";
       out << "      Check(sofie_b200_gemm_plan_create(ctx, &d, &plan_" << opName << "), \"ScaledGemm " << opName << ": plan\");\n";
       out << fEpi.InitCode("ep_" + opName);
       out << "      }\n";

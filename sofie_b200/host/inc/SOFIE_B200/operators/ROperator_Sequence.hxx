@@ -137,6 +137,81 @@ public:
    std::string GenerateDestroyCode_GPU_B200(std::string opName) override { return "      sofie_b200_sdpa_plan_destroy(plan_op_" + opName + ");\n"; }
 };
 
+// Split along one axis (the reference's ROperator_Split, core/inc/SOFIE/operators/ROperator_Split.hxx): the input viewed as
+// [outer, along * inner] and each output as a block of columns of it, copied with one strided device-to-device copy.  When
+// the outputs only feed a folded SDPA the fusion pass lets the attention kernel read the blocks in place and drops the copies.
+class ROperator_Split final : public ROperator_B200 {
+   int64_t fAxis;
+   std::string fNX, fNSplit;
+   std::vector<std::string> fNYs;
+   std::vector<size_t> fShapeX, fLens, fStarts;
+   size_t fOuter = 1, fInner = 1;
+   ETensorType fType = ETensorType::FLOAT;
+
+public:
+   ROperator_Split(int64_t axis, std::string nameX, std::string nameSplit, const std::vector<std::string> &namesY)
+      : fAxis(axis), fNX(UTILITY::Clean_name(nameX)), fNSplit(UTILITY::Clean_name(nameSplit))
+   {
+      for (auto &n : namesY) fNYs.push_back(UTILITY::Clean_name(n));
+      fInputTensorNames = {fNX};
+      fOutputTensorNames = fNYs;
+   }
+   void Initialize(RModel &model) override
+   {
+      if (!model.CheckIfTensorAlreadyExist(fNX)) throw std::runtime_error("SOFIE Split Op Input Tensor is not found in model");
+      fShapeX = model.GetTensorShape(fNX);
+      fType = model.GetTensorType(fNX);
+      const int64_t rank = int64_t(fShapeX.size());
+      const int64_t axis = fAxis < 0 ? fAxis + rank : fAxis;
+      if (axis < 0 || axis >= rank) throw std::runtime_error("SOFIE Split Op: axis out of range");
+      fAxis = axis;
+      const size_t along = fShapeX[size_t(axis)], parts = fNYs.size();
+      if (!fNSplit.empty()) {
+         if (!model.IsInitializedTensor(fNSplit)) throw std::runtime_error("SOFIE Split Op: the split sizes must be an initialized INT64 tensor");
+         for (auto v : model.GetTensorData<int64_t>(fNSplit)) fLens.push_back(size_t(v));
+         if (fLens.size() != parts) throw std::runtime_error("SOFIE Split Op: one split size per output expected");
+      } else {
+         if (parts == 0 || along % parts) throw std::runtime_error("SOFIE Split Op: the axis does not divide evenly among the outputs");
+         fLens.assign(parts, along / parts);
+      }
+      size_t start = 0;
+      for (size_t k = 0; k < parts; ++k) { fStarts.push_back(start); start += fLens[k]; }
+      if (start != along) throw std::runtime_error("SOFIE Split Op: the split sizes do not add up to the axis length");
+      fOuter = fInner = 1;
+      for (int64_t i = 0; i < axis; ++i) fOuter *= fShapeX[size_t(i)];
+      for (int64_t i = axis + 1; i < rank; ++i) fInner *= fShapeX[size_t(i)];
+      for (size_t k = 0; k < parts; ++k) {
+         auto shp = fShapeX;
+         shp[size_t(axis)] = fLens[k];
+         model.AddIntermediateTensor(fNYs[k], fType, shp);
+      }
+   }
+   // for the fusion pass: output k as a block of columns of the input seen as a matrix of `RowPitch` columns
+   const std::string &Input() const { return fNX; }
+   int OutputIndex(const std::string &name) const
+   {
+      for (size_t k = 0; k < fNYs.size(); ++k) if (fNYs[k] == name) return int(k);
+      return -1;
+   }
+   bool SplitsLastAxis() const { return fInner == 1; }
+   size_t RowPitch() const { return fShapeX.empty() ? 0 : fShapeX.back(); }
+   size_t ColumnStart(int k) const { return fStarts[size_t(k)]; }
+   std::string Generate_GPU_B200(std::string opName) override
+   {
+      opName = "op_" + opName;
+      const size_t es = GetTypeSize(fType), pitch = fShapeX[size_t(fAxis)] * fInner * es;
+      std::stringstream out;
+      out << "\n      //------ Split " << opName << " " << ConvertShapeToString(fShapeX) << " along axis " << fAxis << "\n";
+      for (size_t k = 0; k < fNYs.size(); ++k) {
+         const size_t width = fLens[k] * fInner * es;
+         if (width == 0 || fOuter == 0) continue;
+         out << "      CheckCuda(cudaMemcpy2DAsync(tensor_" << fNYs[k] << ", " << width << ", reinterpret_cast<const char *>(tensor_" << fNX << ") + "
+             << fStarts[k] * fInner * es << ", " << pitch << ", " << width << ", " << fOuter << ", cudaMemcpyDeviceToDevice, stream), \"Split " << opName << "\");\n";
+      }
+      return out.str();
+   }
+};
+
 class ROperator_Transpose final : public ROperator_B200 {
    std::vector<int64_t> fAttrPerm;
    std::string fNData, fNOutput;

@@ -256,6 +256,48 @@ void RModel::FuseOperators()
    }
 }
 
+// A folded SDPA whose Q, K or V is (a reshaped view of) an output of a Split along the last axis reads that block of
+// columns of the Split's input in place; operators whose outputs nobody reads any more (the Split, the Reshapes) are dropped.
+void RModel::FuseAttentionInputs()
+{
+   std::map<std::string, size_t> producer;
+   for (size_t k = 0; k < fOperators.size(); ++k)
+      if (!fSkippedOperators.count(k))
+         for (auto &o : fOperators[k]->GetOpOutputTensors()) producer[o] = k;
+   for (size_t k = 0; k < fOperators.size(); ++k) {
+      if (fSkippedOperators.count(k)) continue;
+      auto *sdpa = dynamic_cast<ROperator_SDPA<float> *>(fOperators[k].get());
+      if (!sdpa || !sdpa->IsFolded()) continue;
+      for (int which = 0; which < 3; ++which) {
+         const std::string in = ResolveAliasTensor(sdpa->GetOpInputTensors()[size_t(which)]);
+         auto it = producer.find(in);
+         if (it == producer.end()) continue;
+         auto *split = dynamic_cast<ROperator_Split *>(fOperators[it->second].get());
+         if (!split || !split->SplitsLastAxis()) continue;
+         const int idx = split->OutputIndex(in);
+         if (idx < 0) continue;
+         sdpa->ReadFromColumnBlock(which, split->Input(), split->ColumnStart(idx), split->RowPitch());
+         fFusionLog.push_back("op_" + std::to_string(k) + " reads " + in + " in place from " + split->Input());
+      }
+   }
+   // dead operators: no output is read by a live operator or is a graph output
+   for (bool changed = true; changed;) {
+      changed = false;
+      std::set<std::string> read;
+      for (size_t k = 0; k < fOperators.size(); ++k)
+         if (!fSkippedOperators.count(k))
+            for (auto &in : fOperators[k]->GetOpInputTensors()) { read.insert(in); read.insert(ResolveAliasTensor(in)); }
+      for (auto &o : fOutputTensorNames) { read.insert(o); read.insert(ResolveAliasTensor(o)); }
+      for (size_t k = 0; k < fOperators.size(); ++k) {
+         if (fSkippedOperators.count(k)) continue;
+         if (!dynamic_cast<ROperator_Split *>(fOperators[k].get()) && !(AsB200(fOperators[k].get()) && AsB200(fOperators[k].get())->IsAlias())) continue;
+         bool used = false;
+         for (auto &o : fOperators[k]->GetOpOutputTensors()) used = used || read.count(o);
+         if (!used) { fSkippedOperators.insert(k); changed = true; }
+      }
+   }
+}
+
 // ---------------------------------------------------------------------------------------------------
 // arena
 // ---------------------------------------------------------------------------------------------------
@@ -356,6 +398,7 @@ void RModel::GenerateGPU_B200(std::underlying_type_t<Options> options, int batch
       if (!AsB200(fOperators[i].get()))
          throw std::runtime_error("SOFIE_B200: operator " + std::to_string(i) + " has no B200 implementation");
    FuseOperators();
+   FuseAttentionInputs();
    PlanArena();
    fGC = GenerateSessionCode_GPU_B200();
 }

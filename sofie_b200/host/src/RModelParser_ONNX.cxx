@@ -329,6 +329,9 @@ const std::map<std::string, Maker> &Makers()
           return std::make_unique<ROperator_SDPA<float>>(n.input[0], n.input[1], n.input[2], n.output[0], In(n, 3), Float(n, "scale", 0.f),
                                                          size_t(Int(n, "num_heads", 0)));
        }},
+      {"Split", [](const Node &n) -> std::unique_ptr<ROperator> {
+          return std::make_unique<ROperator_Split>(Int(n, "axis", 0), n.input[0], In(n, 1), n.output);
+       }},
       {"Transpose", [](const Node &n) -> std::unique_ptr<ROperator> {
           auto p = Ints(n, "perm");
           return std::make_unique<ROperator_Transpose>(std::vector<int64_t>(p.begin(), p.end()), n.input[0], n.output[0]);
@@ -349,6 +352,12 @@ const std::map<std::string, Maker> &Makers()
           return std::make_unique<ROperator_QLinearConv>(Str(n, "auto_pad", "NOTSET"), Ints(n, "dilations"), size_t(Int(n, "group", 0)), Ints(n, "kernel_shape"),
                                                          Ints(n, "pads"), Ints(n, "strides"), n.input[0], n.input[1], n.input[2], n.input[3], n.input[4],
                                                          n.input[5], n.input[6], In(n, 7), In(n, 8), n.output[0]);
+       }},
+      {"ScaledGemm", [](const Node &n) -> std::unique_ptr<ROperator> {
+          // FP8 e4m3 product with per-row / per-column fp32 scales and a bias (no counterpart among the reference's operators):
+          // inputs A, B, row_scale, col_scale, bias (the last three optional); attributes transB, to (ONNX type of Y, default BFLOAT16)
+          return std::make_unique<ROperator_ScaledGemm>(int(Int(n, "transB", 0)), n.input[0], n.input[1], In(n, 2), In(n, 3), In(n, 4), n.output[0],
+                                                        static_cast<ETensorType>(Int(n, "to", 16)));
        }},
       {"QuantizeLinear", [](const Node &n) -> std::unique_ptr<ROperator> {
           return std::make_unique<ROperator_QuantizeLinear>(false, Int(n, "axis", 1), n.input[0], n.input[1], In(n, 2), n.output[0]);
@@ -412,6 +421,8 @@ RModel RModelParser_ONNX::Parse(std::string filename, bool verbose)
    std::map<std::string, std::string> rename;           // Identity outputs and absorbed Transposes
    std::map<std::string, bool> transposed;              // tensor is a last-two-axes transpose of rename[tensor]
    std::map<size_t, size_t> fuseInto;                   // consumer node index -> producer node index (MatMul+Add, Conv+Add)
+   struct Dequantised { std::string weight, scale; int64_t axis; };
+   std::map<std::string, Dequantised> dequantised;     // DequantizeLinear outputs folded into the contractions that read them
    auto resolve = [&](std::string n) {
       for (auto it = rename.find(n); it != rename.end(); it = rename.find(n)) n = it->second;
       return n;
@@ -425,6 +436,23 @@ RModel RModelParser_ONNX::Parse(std::string filename, bool verbose)
       const bool single = ch.size() == 1 && !graphOutputs.count(n.output[0]);
 
       if (n.op_type == "Identity") { rename[n.output[0]] = n.input[0]; continue; }
+      if (n.op_type == "DequantizeLinear" && initNames.count(resolve(n.input[0])) && n.input.size() >= 2 && initNames.count(resolve(n.input[1])) &&
+          (n.input.size() < 3 || n.input[2].empty() || initNames.count(resolve(n.input[2])))) {
+         // DequantizeLinear of a weight that only feeds contractions as their B operand: folded into those contractions
+         bool onlyB = !ch.empty() && !graphOutputs.count(n.output[0]);
+         for (auto c : ch) {
+            const Node &u = g.node[c];
+            onlyB = onlyB && (u.op_type == "MatMul" || u.op_type == "Gemm") && u.input.size() >= 2 && u.input[1] == n.output[0] && u.input[0] != n.output[0];
+         }
+         if (onlyB && model.GetTensorType(resolve(n.input[0])) == ETensorType::INT8) {
+            if (n.input.size() >= 3 && !n.input[2].empty()) {
+               auto zp = model.GetTensorData<int8_t>(resolve(n.input[2]));
+               for (auto z : zp) if (z != 0) throw std::runtime_error("SOFIE DequantizeLinear of a weight: only symmetric quantisation (zero point 0) is folded");
+            }
+            dequantised[n.output[0]] = {resolve(n.input[0]), resolve(n.input[1]), Int(n, "axis", 1)};
+            continue;
+         }
+      }
       if (n.op_type == "Transpose") {
          // only a transpose of the last two axes feeding MatMul nodes is absorbed (RModelParser_ONNX.cxx:1186-1197)
          auto perm = Ints(n, "perm");
@@ -461,12 +489,23 @@ RModel RModelParser_ONNX::Parse(std::string filename, bool verbose)
             const Node &add = g.node[ch[0]];
             const std::string other = resolve(add.input[0] == n.output[0] ? add.input[1] : add.input[0]);
             if (other != n.output[0] && model.CheckIfTensorAlreadyExist(other) && model.IsInitializedTensor(other)) {
-               model.AddOperator(std::make_unique<ROperator_Gemm<float>>(1.f, 1.f, ta, tb, n.input[0], n.input[1], other, add.output[0]));
+               auto op = std::make_unique<ROperator_Gemm<float>>(1.f, 1.f, ta, tb, n.input[0], n.input[1], other, add.output[0]);
+               if (auto dq = dequantised.find(n.input[1]); dq != dequantised.end()) op->SetDequantisedWeight(dq->second.weight, dq->second.scale, dq->second.axis);
+               model.AddOperator(std::move(op));
                fuseInto[ch[0]] = i;
                continue;
             }
          }
-         model.AddOperator(std::make_unique<ROperator_Gemm<float>>(1.f, 0.f, ta, tb, n.input[0], n.input[1], n.output[0]));
+         auto op = std::make_unique<ROperator_Gemm<float>>(1.f, 0.f, ta, tb, n.input[0], n.input[1], n.output[0]);
+         if (auto dq = dequantised.find(n.input[1]); dq != dequantised.end()) op->SetDequantisedWeight(dq->second.weight, dq->second.scale, dq->second.axis);
+         model.AddOperator(std::move(op));
+         continue;
+      }
+      if (n.op_type == "Gemm" && n.input.size() >= 2 && dequantised.count(n.input[1])) {
+         const auto &dq = dequantised.at(n.input[1]);
+         auto made = Makers().at("Gemm")(n);
+         static_cast<ROperator_Gemm<float> *>(made.get())->SetDequantisedWeight(dq.weight, dq.scale, dq.axis);
+         model.AddOperator(std::move(made));
          continue;
       }
       if (n.op_type == "Conv" && n.input.size() == 2 && single && g.node[ch[0]].op_type == "Add") {

@@ -201,3 +201,33 @@ def test_external_stream_and_custom_memory_session(emit, tmp_path, b200_lib):
     assert n == 12, lib.session_error().decode()
     assert np.all(np.abs(out - 3.5) <= 1e-6)
     assert list(counts) == [1, 1, 1, 1, 1, 1], list(counts)
+
+
+def test_encoder_configuration_from_the_generator_matches_the_reference(tmp_path, b200_lib):
+    """The transformer-encoder configuration as a parsed ONNX model (int8 weights behind DequantizeLinear, Split -> SDPA): the
+    generator folds the dequantisation, the Gelu and the residual adds into the contractions and lets the fused attention
+    kernel read Q, K, V in place -- 7 launches per layer -- and the emitted Session reproduces what the reference's own
+    emitted fp32 code computed on the dequantised weights (fixture of tests/golden/make_golden.py), at the bf16 bar."""
+    from pathlib import Path
+    from sofie_b200 import encoder as be
+    from sofie_b200.session import EmittedSession
+    fx = np.load(Path(__file__).parent / "golden" / "configs" / "Encoder_C5r.npz")
+    batch, layers = int(fx["batch"]), int(fx["layers"])
+    weights = be.make_weights(int(fx["seed"]), layers, 512, 2048)
+    nodes, init, ins, outs, in_types = be.onnx_model(weights, batch, 128, 512, 8)
+    sess = EmittedSession("encoder", nodes, init, ins, outs, tmp_path, input_types=in_types)
+    header = (tmp_path / "encoder.hxx").read_text()
+    assert "cudaMemcpy2DAsync(" not in header            # no Split copies: attention reads the projection's output in place
+    x = be.f32_to_bf16_bits(fx["x"])
+    y = np.zeros((batch * 128, 512), dtype=np.uint16)
+    l0 = sess.launches
+    assert sess.infer_host([x], y) == y.size
+    assert sess.launches - l0 == 7 * layers
+    got = be.bf16_bits_to_f32(y)
+    err = np.abs(got - fx["y"])
+    assert np.all(err <= 2e-2 * np.abs(fx["y"]) + 1e-2), f"max abs err {err.max():.4f}"
+    y2 = np.zeros_like(y)
+    sess.infer_host([x], y2)     # captured into a CUDA graph
+    sess.infer_host([x], y2)     # replayed
+    assert np.array_equal(y, y2)
+    sess.close()
