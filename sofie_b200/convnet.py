@@ -153,3 +153,46 @@ class ConvNetB200:
         for h in self.plans:
             self.lib.sofie_b200_conv_plan_destroy(h)
         self.fc.close()
+
+
+def onnx_model(seed: int, batch: int, img: int, int8: bool):
+    """The network as an ONNX graph for the C++ generator (sofie_b200/onnx_min.save).  fp32: Conv -> BatchNormalization -> Relu
+    per layer, as a framework exports it (the generator folds the normalisation and the Relu into the convolution and keeps
+    the chain channels-last).  int8: QLinearConv (per-channel weight scales, int32 bias) -> Relu per layer on int8 tensors
+    of scale Y_SCALE, then DequantizeLinear -> GlobalAveragePool; both end in Flatten -> Gemm 512 -> 1000.
+    Returns (nodes, initializers, inputs, outputs, input_types)."""
+    raw, fc_w, fc_b = raw_parameters(seed)
+    init = {"fc_w": fc_w, "fc_b": fc_b}
+    nodes = []
+    x = "X"
+    if not int8:
+        for i, (r, st) in enumerate(zip(raw, STRIDES)):
+            for k in ("w", "gamma", "beta", "mean", "var"):
+                init[f"{k}{i}"] = r[k]
+            nodes.append({"op": "Conv", "in": [x, f"w{i}"], "out": [f"c{i}"], "attrs": {"kernel_shape": [3, 3], "pads": [1, 1, 1, 1], "strides": [st, st]}})
+            nodes.append({"op": "BatchNormalization", "in": [f"c{i}", f"gamma{i}", f"beta{i}", f"mean{i}", f"var{i}"], "out": [f"n{i}"], "attrs": {"epsilon": 1e-5}})
+            nodes.append({"op": "Relu", "in": [f"n{i}"], "out": [f"r{i}"], "attrs": {}})
+            x = f"r{i}"
+        types = {}
+    else:
+        layers, _, _ = make_weights(seed, True)
+        init.update({"zp": np.array(0, dtype=np.int8), "in_scale": np.array(IN_SCALE), "act_scale": np.array(Y_SCALE)})
+        a_scale = IN_SCALE
+        for i, (ly, r, st) in enumerate(zip(layers, raw, STRIDES)):
+            cout = CHANNELS[i + 1]
+            bn_scale = (r["gamma"] / np.sqrt(r["var"] + np.float32(1e-5))).astype(np.float32)
+            wfold = r["w"] * bn_scale[:, None, None, None]
+            w_scale = (np.abs(wfold).reshape(cout, -1).max(axis=1) / 127.0).astype(np.float32)
+            init[f"wq{i}"], init[f"ws{i}"], init[f"wz{i}"], init[f"b{i}"] = ly["w"], w_scale, np.zeros(cout, dtype=np.int8), ly["bias"]
+            nodes.append({"op": "QLinearConv", "in": [x, "in_scale" if i == 0 else "act_scale", "zp", f"wq{i}", f"ws{i}", f"wz{i}", "act_scale", "zp", f"b{i}"],
+                          "out": [f"q{i}"], "attrs": {"kernel_shape": [3, 3], "pads": [1, 1, 1, 1], "strides": [st, st]}})
+            nodes.append({"op": "Relu", "in": [f"q{i}"], "out": [f"r{i}"], "attrs": {}})
+            x = f"r{i}"
+            a_scale = Y_SCALE
+        nodes.append({"op": "DequantizeLinear", "in": [x, "act_scale", "zp"], "out": ["deq"], "attrs": {}})
+        x = "deq"
+        types = {"X": 3}
+    nodes.append({"op": "GlobalAveragePool", "in": [x], "out": ["pool"], "attrs": {}})
+    nodes.append({"op": "Flatten", "in": ["pool"], "out": ["flat"], "attrs": {"axis": 1}})
+    nodes.append({"op": "Gemm", "in": ["flat", "fc_w", "fc_b"], "out": ["Y"], "attrs": {}})
+    return nodes, init, [("X", [batch, 3, img, img])], ["Y"], types

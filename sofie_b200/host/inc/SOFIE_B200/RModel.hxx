@@ -106,6 +106,8 @@ public:
 private:
    void FuseOperators();
    void FuseAttentionInputs();
+   void AssignConvLayouts();
+   void FuseDequantizePool();
    void PlanArena();
    std::string GenerateSessionCode_GPU_B200();
    void WriteWeightFile(const std::string &filename) const;
@@ -122,7 +124,8 @@ private:
    std::map<std::string, std::string> fAliasTensors;  // alias -> tensor whose storage it shares
    std::vector<std::string> fOutputTensorNames;
    std::vector<std::unique_ptr<ROperator>> fOperators;
-   std::set<size_t> fSkippedOperators;  // folded into a producer by the fusion pass
+   std::set<size_t> fSkippedOperators;
+   std::map<std::string, size_t> fStorageFactor;   // bytes per element multiplier of tensors in a wider storage layout  // folded into a producer by the fusion pass
 
    std::underlying_type_t<Options> fOptions = 0;
    bool fIsInitialized = false;

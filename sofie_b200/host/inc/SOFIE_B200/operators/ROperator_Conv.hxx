@@ -67,7 +67,22 @@ inline ConvGeometry ConvShapeInference(const std::vector<size_t> &x, const std::
    return g;
 }
 
-inline std::string ConvDescCode(const ConvGeometry &g, const std::string &xEnum, const std::string &yEnum, int xZeroPoint)
+// Layout of a convolution's tensors (sofie_b200_conv_desc::x_layout / y_layout): 0 NCHW, 1 channels-last, 2 channels-last TF32
+// pairs.  The reference keeps every tensor NCHW; the layout pass of RModel sets these for conv -> conv chains.
+class ConvLayoutHooks {
+public:
+   virtual ~ConvLayoutHooks() = default;
+   virtual const ConvGeometry &Geometry() const = 0;
+   virtual bool IsInt8() const = 0;
+   virtual int InputZeroPoint() const { return 0; }
+   virtual bool HasResidual() const = 0;
+   virtual const std::string &LayoutInput() const = 0;
+   virtual const std::string &LayoutOutput() const = 0;
+   virtual void SetLayouts(int xLayout, int yLayout) = 0;
+   int fXLayout = 0, fYLayout = 0;
+};
+
+inline std::string ConvDescCode(const ConvGeometry &g, const std::string &xEnum, const std::string &yEnum, int xZeroPoint, int xLayout = 0, int yLayout = 0)
 {
    std::stringstream out;
    out << "      sofie_b200_conv_desc d{};\n";
@@ -77,11 +92,28 @@ inline std::string ConvDescCode(const ConvGeometry &g, const std::string &xEnum,
    out << "      d.stride_h = " << g.strides[0] << "; d.stride_w = " << g.strides[1] << "; d.dil_h = " << g.dil[0] << "; d.dil_w = " << g.dil[1]
        << "; d.groups = " << g.group << ";\n";
    out << "      d.x_dtype = " << xEnum << "; d.y_dtype = " << yEnum << "; d.x_zero_point = " << xZeroPoint << "; d.precise = 1;\n";
+   if (xLayout || yLayout) out << "      d.x_layout = " << xLayout << "; d.y_layout = " << yLayout << ";\n";
    return out.str();
 }
 
-inline size_t ConvWorkspaceBytes(const ConvGeometry &g, size_t elemSize)
+// The library's plan selection restated (sofie_b200_conv_plan_kernel): the forms that need no workspace.
+inline bool ConvNeedsNoWorkspace(const ConvGeometry &g, size_t elemSize, size_t outElemSize, int xLayout, int yLayout, int xZeroPoint)
 {
+   // the 3-channel 3x3 first layer on the CUDA cores, while its filters and staging fit its shared memory
+   if (g.group == 1 && g.C == 3 && g.R == 3 && g.S == 3 && xLayout == 0 && g.K <= 256) {
+      const size_t wsm = g.K * ((elemSize == 4 ? 28 * 4 : 8 * 4) + 16);
+      const size_t stage = yLayout == 0 ? 0 : (yLayout == 2 ? 4 * 32 * (32 * 8 + 16) : 4 * 32 * (g.K * outElemSize + 16));
+      if (wsm + stage <= 160 * 1024) return true;
+   }
+   if (xLayout == 2) return true;   // TF32 pairs read in place
+   const bool hasPad = g.pads[0] || g.pads[1] || g.pads[2] || g.pads[3];
+   // implicit convolution: channels-last int8, a pixel a whole number of 64-byte blocks, padding that reads as zero
+   return xLayout == 1 && yLayout == 1 && g.group == 1 && elemSize == 1 && (g.C * elemSize) % 64 == 0 && (xZeroPoint == 0 || !hasPad);
+}
+
+inline size_t ConvWorkspaceBytes(const ConvGeometry &g, size_t elemSize, size_t outElemSize = 0, int xLayout = 0, int yLayout = 0, int xZeroPoint = 0)
+{
+   if (ConvNeedsNoWorkspace(g, elemSize, outElemSize ? outElemSize : elemSize, xLayout, yLayout, xZeroPoint)) return 0;
    // [groups][N][Ho*Wo][kpad] with kpad = C/groups*R*S rounded up to 16 bytes (sofie_b200_conv_workspace_bytes)
    const size_t kdim = g.C / g.group * g.R * g.S, vec = 16 / elemSize;
    size_t kpad = (kdim + vec - 1) / vec * vec;
@@ -90,12 +122,12 @@ inline size_t ConvWorkspaceBytes(const ConvGeometry &g, size_t elemSize)
    if (split) kpad = (kdim + 31) / 32 * 32 * 2;
    size_t bytes = g.group * g.N * g.Ho * g.Wo * kpad * elemSize;
    // when the channels per group are whole 16-byte vectors the library unfolds from a channels-last copy of the input kept behind it
-   if ((g.C / g.group) % vec == 0) bytes = (bytes + 255) / 256 * 256 + g.N * g.C * g.H * g.W * elemSize;
+   if ((g.C / g.group) % vec == 0 && xLayout == 0) bytes = (bytes + 255) / 256 * 256 + g.N * g.C * g.H * g.W * elemSize;
    return bytes;
 }
 
 template <typename T>
-class ROperator_Conv final : public ROperator_B200 {
+class ROperator_Conv final : public ROperator_B200, public ConvLayoutHooks {
    static_assert(std::is_same<T, float>::value, "ROperator_Conv<T>: T is float, as in the reference");
 
 private:
@@ -196,7 +228,19 @@ public:
       return true;
    }
 
-   std::vector<DeviceScratch> GetDeviceScratch_GPU_B200() const override { return {{fNY + "_xcol", ConvWorkspaceBytes(fGeo, sizeof(float))}}; }
+   // ---- layout pass
+   const ConvGeometry &Geometry() const override { return fGeo; }
+   bool IsInt8() const override { return false; }
+   bool HasResidual() const override { return !fEpi.residual.empty(); }
+   const std::string &LayoutInput() const override { return fNX; }
+   const std::string &LayoutOutput() const override { return fNY; }
+   void SetLayouts(int x, int y) override { fXLayout = x; fYLayout = y; }
+   size_t Workspace() const { return ConvWorkspaceBytes(fGeo, sizeof(float), sizeof(float), fXLayout, fYLayout, 0); }
+
+   std::vector<DeviceScratch> GetDeviceScratch_GPU_B200() const override
+   {
+      return Workspace() ? std::vector<DeviceScratch>{{fNY + "_xcol", Workspace()}} : std::vector<DeviceScratch>{};
+   }
 
    std::string GenerateSessionMembersCode_GPU_B200(std::string opName) override
    {
@@ -208,9 +252,9 @@ public:
       opName = "op_" + opName;
       std::stringstream out;
       out << "      {  // Conv " << opName << ": " << ConvertShapeToString(fShapeX) << " * " << ConvertShapeToString(fShapeW) << "\n";
-      out << ConvDescCode(fGeo, "SOFIE_B200_F32", "SOFIE_B200_F32", 0);
+      out << ConvDescCode(fGeo, "SOFIE_B200_F32", "SOFIE_B200_F32", 0, fXLayout, fYLayout);
       out << "      Check(sofie_b200_conv_plan_create(ctx, &d, tensor_" << fNW << ", &plan_" << opName << "), \"Conv " << opName << ": plan\");\n";
-      out << "      if (sofie_b200_conv_workspace_bytes(plan_" << opName << ") > " << ConvWorkspaceBytes(fGeo, sizeof(float)) << "LL)\n"
+      out << "      if (sofie_b200_conv_workspace_bytes(plan_" << opName << ") > " << Workspace() << "LL)\n"
           << "         throw std::runtime_error(\"Conv " << opName << ": the library wants more scratch than the arena reserves\");\n";
       out << fEpi.InitCode("ep_" + opName);
       out << "      }\n";
@@ -227,8 +271,8 @@ public:
          out << "      ep_" << opName << ".residual = tensor_" << fEpi.residual << "; ep_" << opName << ".residual_dtype = "
              << ConvertTypeToRuntimeEnum(fResidualType) << ";\n";
       out << fEpi.BindCode("ep_" + opName);
-      out << "      Check(sofie_b200_conv_enqueue(plan_" << opName << ", tensor_" << fNX << ", tensor_" << fNY << ", tensor_" << fNY
-          << "_xcol, &ep_" << opName << "), \"Conv " << opName << "\");\n";
+      out << "      Check(sofie_b200_conv_enqueue(plan_" << opName << ", tensor_" << fNX << ", tensor_" << fNY << ", "
+          << (Workspace() ? "tensor_" + fNY + "_xcol" : std::string("nullptr")) << ", &ep_" << opName << "), \"Conv " << opName << "\");\n";
       return out.str();
    }
    std::string GenerateDestroyCode_GPU_B200(std::string opName) override { return "      sofie_b200_conv_plan_destroy(plan_op_" + opName + ");\n"; }

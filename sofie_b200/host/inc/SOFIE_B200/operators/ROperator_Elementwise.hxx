@@ -40,7 +40,9 @@ public:
          throw std::runtime_error("SOFIE " + fOpLabel + " Op Input Tensor " + fNX + " is not found in model");
       fShape = model.GetTensorShape(fNX);
       fType = model.GetTensorType(fNX);
-      if (fType != ETensorType::FLOAT && fType != ETensorType::BFLOAT16)
+      // an integer Relu only exists folded into the quantised contraction before it (checked at emission)
+      const bool intRelu = fAct == EActivationType::RELU && (fType == ETensorType::INT8 || fType == ETensorType::UINT8);
+      if (fType != ETensorType::FLOAT && fType != ETensorType::BFLOAT16 && !intRelu)
          throw std::runtime_error("SOFIE " + fOpLabel + " Op: FLOAT or BFLOAT16 input expected");
       model.AddIntermediateTensor(fNY, fType, fShape);
    }
@@ -48,6 +50,8 @@ public:
    {
       opName = "op_" + opName;
       if (fShape.empty()) throw std::runtime_error("SOFIE " + fOpLabel + " operator called to Generate without being initialized first");
+      if (fType != ETensorType::FLOAT && fType != ETensorType::BFLOAT16)
+         throw std::runtime_error("SOFIE " + fOpLabel + " Op: an integer Relu must directly follow a quantised contraction with output zero point 0 (it is folded into it)");
       std::stringstream out;
       out << "\n      //------ " << fOpLabel << " " << opName << "\n";
       out << "      Check(sofie_b200_unary_enqueue(ctx, tensor_" << fNX << ", tensor_" << fNY << ", " << ConvertTypeToRuntimeEnum(fType) << ", "
@@ -334,6 +338,8 @@ class ROperator_Pool final : public ROperator_B200 {
    PoolOpMode fPoolMode;
    std::string fNX, fNY;
    std::vector<size_t> fShapeX;
+   bool fChannelsLast = false;   // the input is stored [N, H, W, C] (set by the layout pass behind a channels-last convolution)
+   ETensorType fTypeX = ETensorType::FLOAT;
 
 public:
    ROperator_Pool(PoolOpMode mode, std::string nameX, std::string nameY)
@@ -347,19 +353,30 @@ public:
       if (fPoolMode != GlobalAveragePool) throw std::runtime_error("SOFIE Pool Op: only GlobalAveragePool is on the B200 path");
       if (!model.CheckIfTensorAlreadyExist(fNX)) throw std::runtime_error("SOFIE Pool op Input Tensor " + fNX + " is not found in model");
       fShapeX = model.GetTensorShape(fNX);
-      if (fShapeX.size() < 3 || model.GetTensorType(fNX) != ETensorType::FLOAT) throw std::runtime_error("SOFIE Pool Op: FLOAT NC... input expected");
+      fTypeX = model.GetTensorType(fNX);
+      if (fShapeX.size() < 3 || fTypeX != ETensorType::FLOAT) throw std::runtime_error("SOFIE Pool Op: FLOAT NC... input expected");
       std::vector<size_t> y(fShapeX.size(), 1);
       y[0] = fShapeX[0]; y[1] = fShapeX[1];
       model.AddIntermediateTensor(fNY, ETensorType::FLOAT, y);
    }
+   const std::string &NameX() const { return fNX; }
+   void SetChannelsLast(bool on) { fChannelsLast = on; }
+   const std::string &NameY() const { return fNY; }
+   // read the quantised tensor a per-tensor DequantizeLinear was applied to (the scale moves to the consumer of the pool)
+   void ReadQuantised(const std::string &name, ETensorType type) { fNX = name; fTypeX = type; fInputTensorNames = {fNX}; }
    std::string Generate_GPU_B200(std::string opName) override
    {
       opName = "op_" + opName;
       size_t inner = 1;
       for (size_t i = 2; i < fShapeX.size(); ++i) inner *= fShapeX[i];
       std::stringstream out;
-      out << "\n      //------ GlobalAveragePool " << opName << "\n";
-      out << "      Check(sofie_b200_global_avgpool_enqueue(ctx, tensor_" << fNX << ", tensor_" << fNY << ", SOFIE_B200_F32, " << fShapeX[0] * fShapeX[1]
+      out << "\n      //------ GlobalAveragePool " << opName << (fChannelsLast ? " (channels-last input)" : "") << "\n";
+      if (fChannelsLast) {
+         out << "      Check(sofie_b200_global_avgpool_nhwc_enqueue(ctx, tensor_" << fNX << ", tensor_" << fNY << ", " << ConvertTypeToRuntimeEnum(fTypeX) << ", " << fShapeX[0] << ", "
+             << inner << ", " << fShapeX[1] << "), \"GlobalAveragePool " << opName << "\");\n";
+         return out.str();
+      }
+      out << "      Check(sofie_b200_global_avgpool_enqueue(ctx, tensor_" << fNX << ", tensor_" << fNY << ", " << ConvertTypeToRuntimeEnum(fTypeX) << ", " << fShapeX[0] * fShapeX[1]
           << ", " << inner << "), \"GlobalAveragePool " << opName << "\");\n";
       return out.str();
    }

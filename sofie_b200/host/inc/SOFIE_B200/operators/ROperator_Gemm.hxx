@@ -116,6 +116,9 @@ public:
    // single-pass TF32 instead of the fp32-accurate path (off by default: parity bar is 1e-5)
    void SetPrecise(bool p) { fPrecise = p; }
    const EpilogueState &GetEpilogue() const { return fEpi; }
+   const std::string &NameA() const { return fNA; }
+   // A was rescaled by a constant that is applied here instead (a per-tensor dequantisation moved behind a pooling)
+   void ScaleAlpha(float s) { fAttrAlpha *= s; fEpi.alpha *= s; }
 
    void Initialize(RModel &model) override
    {

@@ -142,7 +142,7 @@ public:
 };
 
 // ---- QLinearConv --------------------------------------------------------------------------------------
-class ROperator_QLinearConv final : public ROperator_B200 {
+class ROperator_QLinearConv final : public ROperator_B200, public ConvLayoutHooks {
    std::string fAttrAutopad;
    std::vector<size_t> fAttrDilations, fAttrKernelShape, fAttrPads, fAttrStrides;
    size_t fAttrGroup;
@@ -230,7 +230,20 @@ public:
       }
       model.AddIntermediateTensor(fNY, fTypeY, fShapeY);
    }
-   std::vector<DeviceScratch> GetDeviceScratch_GPU_B200() const override { return {{fNY + "_xcol", ConvWorkspaceBytes(fGeo, 1)}}; }
+   // ---- layout pass
+   const ConvGeometry &Geometry() const override { return fGeo; }
+   bool IsInt8() const override { return true; }
+   int InputZeroPoint() const override { return fXZp; }
+   bool HasResidual() const override { return !fEpi.residual.empty(); }
+   const std::string &LayoutInput() const override { return fNX; }
+   const std::string &LayoutOutput() const override { return fNY; }
+   void SetLayouts(int x, int y) override { fXLayout = x; fYLayout = y; }
+   size_t Workspace() const { return ConvWorkspaceBytes(fGeo, 1, 1, fXLayout, fYLayout, fXZp); }
+
+   std::vector<DeviceScratch> GetDeviceScratch_GPU_B200() const override
+   {
+      return Workspace() ? std::vector<DeviceScratch>{{fNY + "_xcol", Workspace()}} : std::vector<DeviceScratch>{};
+   }
    std::string GenerateSessionMembersCode_GPU_B200(std::string opName) override
    {
       return "   sofie_b200_conv_plan *plan_op_" + opName + " = nullptr;\n   sofie_b200_epilogue ep_op_" + opName + "{};\n";
@@ -239,9 +252,9 @@ public:
    {
       opName = "op_" + opName;
       std::stringstream out;
-      out << "      {  // QLinearConv " << opName << "\n" << ConvDescCode(fGeo, "SOFIE_B200_I8", ConvertTypeToRuntimeEnum(fTypeY), fXZp);
+      out << "      {  // QLinearConv " << opName << "\n" << ConvDescCode(fGeo, "SOFIE_B200_I8", ConvertTypeToRuntimeEnum(fTypeY), fXZp, fXLayout, fYLayout);
       out << "      Check(sofie_b200_conv_plan_create(ctx, &d, tensor_" << fNW << ", &plan_" << opName << "), \"QLinearConv " << opName << ": plan\");\n";
-      out << "      if (sofie_b200_conv_workspace_bytes(plan_" << opName << ") > " << ConvWorkspaceBytes(fGeo, 1) << "LL)\n"
+      out << "      if (sofie_b200_conv_workspace_bytes(plan_" << opName << ") > " << Workspace() << "LL)\n"
           << "         throw std::runtime_error(\"QLinearConv " << opName << ": the library wants more scratch than the arena reserves\");\n";
       out << fEpi.InitCode("ep_" + opName) << "      }\n";
       return out.str();
@@ -252,8 +265,8 @@ public:
       std::stringstream out;
       out << "\n      //--------- QLinearConv " << opName << " " << ConvertShapeToString(fShapeX) << " -> " << ConvertShapeToString(fShapeY) << "\n";
       out << fEpi.BindCode("ep_" + opName);
-      out << "      Check(sofie_b200_conv_enqueue(plan_" << opName << ", tensor_" << fNX << ", tensor_" << fNY << ", tensor_" << fNY << "_xcol, &ep_"
-          << opName << "), \"QLinearConv " << opName << "\");\n";
+      out << "      Check(sofie_b200_conv_enqueue(plan_" << opName << ", tensor_" << fNX << ", tensor_" << fNY << ", "
+          << (Workspace() ? "tensor_" + fNY + "_xcol" : std::string("nullptr")) << ", &ep_" << opName << "), \"QLinearConv " << opName << "\");\n";
       return out.str();
    }
    std::string GenerateDestroyCode_GPU_B200(std::string opName) override { return "      sofie_b200_conv_plan_destroy(plan_op_" + opName + ");\n"; }
@@ -279,6 +292,8 @@ public:
       fOutputTensorNames = {fNY};
    }
    bool IsDequantize() const { return fDequantize; }
+   bool IsPerTensor() const { return fChannels == 1; }
+   const std::string &NameY() const { return fNY; }
    const std::string &NameX() const { return fNX; }
    const std::string &NameScale() const { return fNScale; }
    const std::string &NameZp() const { return fNZp; }

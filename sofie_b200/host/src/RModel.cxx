@@ -298,6 +298,112 @@ void RModel::FuseAttentionInputs()
    }
 }
 
+// DequantizeLinear (per tensor, zero point 0) -> GlobalAveragePool -> [Flatten / Reshape] -> Gemm: the pool averages the
+// quantised values themselves and the scale becomes part of the Gemm's alpha (a mean is linear), which saves the pass
+// that would write the dequantised tensor.
+void RModel::FuseDequantizePool()
+{
+   auto soleReader = [&](const std::string &t) -> long {
+      long found = -1;
+      if (IsOutputTensor(t)) return -1;
+      for (size_t k = 0; k < fOperators.size(); ++k) {
+         if (fSkippedOperators.count(k)) continue;
+         for (auto &in : fOperators[k]->GetOpInputTensors())
+            if (in == t) { if (found >= 0) return -1; found = long(k); }
+      }
+      return found;
+   };
+   for (size_t k = 0; k < fOperators.size(); ++k) {
+      if (fSkippedOperators.count(k)) continue;
+      auto *dq = dynamic_cast<ROperator_QuantizeLinear *>(fOperators[k].get());
+      if (!dq || !dq->IsDequantize() || !dq->IsPerTensor() || GetTensorType(dq->NameX()) != ETensorType::INT8) continue;
+      if (!dq->NameZp().empty())
+         if (auto zp = GetTensorData<int8_t>(dq->NameZp()); !zp.empty() && zp[0] != 0) continue;
+      if (!IsInitializedTensor(dq->NameScale())) continue;
+      const long pk = soleReader(dq->NameY());
+      auto *pool = pk >= 0 ? dynamic_cast<ROperator_Pool<float> *>(fOperators[size_t(pk)].get()) : nullptr;
+      if (!pool) continue;
+      std::string t = pool->NameY();
+      long gk = soleReader(t);
+      while (gk >= 0 && AsB200(fOperators[size_t(gk)].get()) && AsB200(fOperators[size_t(gk)].get())->IsAlias()) {
+         t = fOperators[size_t(gk)]->GetOpOutputTensors()[0];
+         gk = soleReader(t);
+      }
+      auto *gemm = gk >= 0 ? dynamic_cast<ROperator_Gemm<float> *>(fOperators[size_t(gk)].get()) : nullptr;
+      if (!gemm || ResolveAliasTensor(gemm->NameA()) != ResolveAliasTensor(t)) continue;
+      pool->ReadQuantised(dq->NameX(), ETensorType::INT8);
+      gemm->ScaleAlpha(GetTensorData<float>(dq->NameScale())[0]);
+      fSkippedOperators.insert(k);
+      fFusionLog.push_back("op_" + std::to_string(pk) + " pools the quantised tensor; op_" + std::to_string(gk) + " applies the scale of op_" + std::to_string(k));
+   }
+}
+
+// Layout pass.  The reference keeps every tensor NCHW.  Here a convolution whose result is read by exactly one other
+// convolution hands it over channels-last (int8: plain; fp32: as TF32 pairs, which the 3xTF32 contraction reads in
+// place), so that the inner layers of a conv -> conv chain run as implicit convolutions without an unfolded copy, and a
+// GlobalAveragePool behind the chain reads the channels-last tensor directly.  The ends of a chain stay NCHW.
+void RModel::AssignConvLayouts()
+{
+   std::map<std::string, std::vector<size_t>> readers;
+   for (size_t k = 0; k < fOperators.size(); ++k)
+      if (!fSkippedOperators.count(k))
+         for (auto &in : fOperators[k]->GetOpInputTensors()) readers[in].push_back(k);
+   std::map<std::string, size_t> convOf;   // tensor -> convolution that writes it
+   for (size_t k = 0; k < fOperators.size(); ++k)
+      if (!fSkippedOperators.count(k))
+         if (auto *c = dynamic_cast<ConvLayoutHooks *>(fOperators[k].get())) convOf[c->LayoutOutput()] = k;
+   auto sole = [&](const std::string &t) -> ROperator * {
+      auto it = readers.find(t);
+      if (it == readers.end() || it->second.size() != 1 || IsOutputTensor(t)) return nullptr;
+      return fOperators[it->second[0]].get();
+   };
+   for (size_t k = 0; k < fOperators.size(); ++k) {
+      if (fSkippedOperators.count(k)) continue;
+      auto *c = dynamic_cast<ConvLayoutHooks *>(fOperators[k].get());
+      if (!c) continue;
+      const ConvGeometry &g = c->Geometry();
+      int y = 0;
+      if (!c->HasResidual()) {
+         ROperator *next = sole(c->LayoutOutput());
+         // a per-tensor DequantizeLinear is elementwise: it passes the layout through to what follows it
+         std::string t = c->LayoutOutput();
+         while (auto *dq = dynamic_cast<ROperator_QuantizeLinear *>(next)) {
+            if (!dq->IsDequantize() || !dq->IsPerTensor() || dq->NameX() != t) { next = nullptr; break; }
+            t = dq->NameY();
+            next = sole(t);
+         }
+         if (auto *n = dynamic_cast<ConvLayoutHooks *>(next); n && t == c->LayoutOutput() && n->LayoutInput() == t && n->IsInt8() == c->IsInt8()) {
+            const ConvGeometry &ng = n->Geometry();
+            if (c->IsInt8()) {
+               if ((ng.C / ng.group) % 16 == 0) y = 1;
+            } else {
+               const bool canWritePairs = c->fXLayout == 2 || ConvNeedsNoWorkspace(g, 4, 4, c->fXLayout, 2, 0);
+               if (g.group == 1 && ng.group == 1 && ng.C % 32 == 0 && g.K % 4 == 0 && canWritePairs) y = 2;
+               else if ((ng.C / ng.group) % 4 == 0) y = 1;
+            }
+            if (y) n->SetLayouts(y, n->fYLayout);
+         } else if (auto *pool = dynamic_cast<ROperator_Pool<float> *>(next); pool && pool->NameX() == t) {
+            y = 1;
+            pool->SetChannelsLast(true);
+         }
+      }
+      int x = c->fXLayout;
+      if (x == 2 && y == 0) {
+         // a tensor of TF32 pairs can only feed a convolution with a channels-last result: take the plain channels-last
+         // tensor from the producer instead
+         x = 1;
+         if (auto it = convOf.find(c->LayoutInput()); it != convOf.end()) {
+            auto *p = dynamic_cast<ConvLayoutHooks *>(fOperators[it->second].get());
+            p->SetLayouts(p->fXLayout, 1);
+            fStorageFactor.erase(c->LayoutInput());
+         }
+      }
+      c->SetLayouts(x, y);
+      if (y == 2) fStorageFactor[c->LayoutOutput()] = 2;
+      if (x || y) fFusionLog.push_back("op_" + std::to_string(k) + " layouts x " + std::to_string(x) + " y " + std::to_string(y));
+   }
+}
+
 // ---------------------------------------------------------------------------------------------------
 // arena
 // ---------------------------------------------------------------------------------------------------
@@ -353,7 +459,8 @@ void RModel::PlanArena()
    fUnplannedBytes = 0;
    for (auto &[n, be] : life) {
       auto &t = fIntermediateTensorInfos.at(n);
-      const int64_t bytes = int64_t(ConvertShapeToLength(t.shape) * GetTypeSize(t.type));
+      const size_t factor = fStorageFactor.count(n) ? fStorageFactor.at(n) : 1;   // a tensor of TF32 pairs holds two values per element
+      const int64_t bytes = int64_t(ConvertShapeToLength(t.shape) * GetTypeSize(t.type) * factor);
       lives.push_back({be.first, be.second, bytes});
       pooled.push_back({n, 0, bytes, be.first, be.second, "intermediate"});
       fUnplannedBytes += AlignUp(bytes);
@@ -399,6 +506,8 @@ void RModel::GenerateGPU_B200(std::underlying_type_t<Options> options, int batch
          throw std::runtime_error("SOFIE_B200: operator " + std::to_string(i) + " has no B200 implementation");
    FuseOperators();
    FuseAttentionInputs();
+   FuseDequantizePool();
+   AssignConvLayouts();
    PlanArena();
    fGC = GenerateSessionCode_GPU_B200();
 }

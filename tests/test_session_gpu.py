@@ -231,3 +231,35 @@ def test_encoder_configuration_from_the_generator_matches_the_reference(tmp_path
     sess.infer_host([x], y2)     # replayed
     assert np.array_equal(y, y2)
     sess.close()
+
+
+@pytest.mark.parametrize("int8", [False, True])
+def test_convnet_configuration_from_the_generator(tmp_path, oracle_lib, b200_lib, int8):
+    """The conv-net configuration as a parsed ONNX model.  fp32: Conv -> BatchNormalization -> Relu per layer, which the
+    generator folds and keeps channels-last as TF32 pairs (10 launches), against the reference's own emitted code (fixture
+    of tests/golden/make_golden.py) at 1e-5.  int8: QLinearConv -> Relu chains running as implicit convolutions, the final
+    DequantizeLinear folded behind the pooling, against the CPU checker."""
+    from pathlib import Path
+    import model_oracles as mo
+    from sofie_b200 import convnet as bc
+    from sofie_b200.session import EmittedSession
+    fx = np.load(Path(__file__).parent / "golden" / "configs" / "ConvNet_C4r.npz")
+    seed = int(fx["seed"])
+    nodes, init, ins, outs, in_types = bc.onnx_model(seed, 2, 32, int8)
+    sess = EmittedSession("convnet_i8" if int8 else "convnet_f32", nodes, init, ins, outs, tmp_path, input_types=in_types)
+    if int8:
+        x = np.clip(np.rint(fx["x"] * 127.0), 0, 127).astype(np.int8)
+        want = mo.convnet_oracle(Oracle(oracle_lib), x, bc.make_weights(seed, True), True)
+    else:
+        x, want = fx["x"], fx["y"]
+    y = np.zeros((2, 1000), dtype=np.float32)
+    l0 = sess.launches
+    assert sess.infer_host([x], y) == y.size
+    assert sess.launches - l0 == 10
+    floor = float(np.sqrt(np.mean(np.square(want))))
+    assert np.all(np.abs(y - want) <= 1e-5 * np.maximum(np.abs(want), floor)), np.abs(y - want).max()
+    y2 = np.zeros_like(y)
+    sess.infer_host([x], y2)
+    sess.infer_host([x], y2)     # replayed from the captured graph
+    assert np.array_equal(y, y2)
+    sess.close()
