@@ -247,11 +247,43 @@ def e2e_measure(torch, rep, compute, step, x_bufs, hx, hy, units_per_inference: 
             "d2h_bytes_per_step": int(hy.numel() * hy.element_size()), "inferences": n, "seconds": t}
 
 
+def session_e2e(torch, rep, sess, host_inputs, out_shape, out_dtype, units_per_inference: float, target_s: float = 1.0) -> dict:
+    """A queue of inferences through Session::infer_host_many of the emitted code: every inference's inputs come from pinned
+    host memory and its output goes back to pinned host memory (two output buffers in turn); weights were uploaded once, at
+    Session construction.  Returns the e2e record (value still in plain units per second)."""
+    from sofie_b200 import replicas
+    outs = [torch.empty(out_shape, dtype=out_dtype).pin_memory() for _ in range(2)]
+
+    def run(count):
+        t0 = time.perf_counter()
+        sess.infer_host_many([[t.data_ptr()] * count for t in host_inputs], [outs[k & 1].data_ptr() for k in range(count)])
+        return time.perf_counter() - t0
+    run(3)
+    t_probe = run(6) / 6
+    n = int(replicas.max_over_ranks(rep, float(max(6, min(4000, target_s / max(t_probe, 1e-6))))))
+    replicas.barrier(rep)
+    t = replicas.max_over_ranks(rep, run(n))
+    return {"value": rep.world * units_per_inference * n / t, "h2d_bytes_per_step": int(sum(x.numel() * x.element_size() for x in host_inputs)),
+            "d2h_bytes_per_step": int(outs[0].numel() * outs[0].element_size()), "inferences": n, "seconds": t,
+            "api": "Session::infer_host_many of the emitted code (ONNX model -> sofie_b200_emit -> g++); weights uploaded once at Session construction"}
+
+
 # ---------------------------------------------------------------------------------------------
 class Workload:
     name = metric = unit = dtype = ""
     scaling = "weak"
     unit_scale = 1.0        # value = units / seconds / unit_scale
+
+    def stream(self, torch, dev):
+        """The CUDA stream the passes are enqueued on (the timing events are recorded there)."""
+        return torch.cuda.current_stream(dev)
+
+    def sync(self):
+        self.ctx.sync()
+
+    def launches(self) -> int:
+        """Kernels enqueued so far."""
+        return self.ctx.launches
 
     def setup(self, torch, ctx, dev, rep): ...
     def one_pass(self, i): ...
@@ -368,27 +400,13 @@ class GemmWorkload(Workload):
     def e2e(self, torch, rep, compute):
         """Through the emitted Session's infer_host_many: A (and its row scales) from pinned host memory in, Y back out, per
         inference; the weights were uploaded once, when the Session was constructed."""
-        from sofie_b200 import replicas
         sess = self.session()
-        hx = torch.from_numpy(self.ha).pin_memory()
-        ins = [hx]
+        ins = [torch.from_numpy(self.ha).pin_memory()]
         if self.kind != "int8":
             ins.append(self.sa.pin_memory())
-        outs = [torch.empty((self.n, self.n), dtype=self.out_dt).pin_memory() for _ in range(2)]
-
-        def run(count):
-            t0 = time.perf_counter()
-            sess.infer_host_many([[t.data_ptr()] * count for t in ins], [outs[k & 1].data_ptr() for k in range(count)])
-            return time.perf_counter() - t0
-        run(3)
-        t_probe = run(6) / 6
-        n = int(replicas.max_over_ranks(rep, float(max(6, min(4000, 1.0 / max(t_probe, 1e-6))))))
-        replicas.barrier(rep)
-        t = replicas.max_over_ranks(rep, run(n))
-        h2d = sum(x.numel() * x.element_size() for x in ins)
-        r = {"value": rep.world * self.ops * n / t / 1e12, "unit": self.unit, "h2d_bytes_per_step": int(h2d),
-             "d2h_bytes_per_step": int(outs[0].numel() * outs[0].element_size()), "inferences": n, "seconds": t,
-             "api": "Session::infer_host_many of the emitted code (ONNX model -> sofie_b200_emit -> g++); weights uploaded once at Session construction"}
+        r = session_e2e(torch, rep, sess, ins, (self.n, self.n), self.out_dt, self.ops)
+        r["value"] /= 1e12
+        r["unit"] = self.unit
         sess.close()
         return r
 
@@ -550,7 +568,59 @@ class RowOpWorkload(Workload):
         self.xs = self.ys = None
 
 
-class EncoderWorkload(Workload):
+class SessionWorkload(Workload):
+    """A whole model through the generator: written as an ONNX file, emitted by sofie_b200_emit, compiled with g++, constructed,
+    and driven through the emitted Session -- infer_nosync on device-resident inputs for `value` (two input buffers in turn;
+    after the first, eager call the Session replays its CUDA graph: one graph launch per pass), infer_host_many for e2e."""
+
+    def model(self): ...            # -> (nodes, initializers, inputs, outputs, input_types)
+    def host_input(self): ...       # -> numpy array of one batch
+    out_shape, out_torch_dtype = None, None
+
+    def setup(self, torch, ctx, dev, rep):
+        import tempfile
+        from sofie_b200.session import EmittedSession
+        self.torch, self.ctx = torch, ctx
+        nodes, init, ins, outs, types = self.model()
+        self.sess = EmittedSession(self.name, nodes, init, ins, outs, tempfile.mkdtemp(prefix="sofie_b200_"), input_types=types)
+        self.hx = torch.from_numpy(self.host_input()).pin_memory()
+        self.xs = [self.hx.to(dev), torch.roll(self.hx, 1, 0).to(dev)]
+        torch.cuda.synchronize()
+        self._stream = torch.cuda.ExternalStream(self.sess.stream, device=dev)
+        l0 = self.sess.launches
+        self.sess.infer_nosync(self.xs[0].data_ptr())       # the eager call: every operator is one kernel launch
+        self.sess.sync()
+        self.kernels_per_pass = self.sess.launches - l0
+        self.passes = 0
+
+    def stream(self, torch, dev):
+        return self._stream
+
+    def sync(self):
+        self.sess.sync()
+
+    def launches(self):
+        return self.kernels_per_pass * self.passes   # kernels executed: a replayed graph runs the kernels of the eager call
+
+    def one_pass(self, i):
+        self.sess.infer_nosync(self.xs[i & 1].data_ptr())
+        self.passes += 1
+
+    def e2e(self, torch, rep, compute):
+        r = session_e2e(torch, rep, self.sess, [self.hx], self.out_shape, self.out_torch_dtype, self.units_per_pass())
+        r["unit"] = self.unit
+        return r
+
+    def session_config(self):
+        return {"session": "emitted by sofie_b200_emit from an ONNX model; passes replay the Session's CUDA graph",
+                "kernels_per_pass": self.kernels_per_pass, "generator_decisions": len(json.loads(self.sess.report)["fusions"])}
+
+    def close(self):
+        self.sess.close()
+        self.xs = None
+
+
+class EncoderWorkload(SessionWorkload):
     """Transformer encoder: 6 pre-LN layers, d_model 512, 8 heads, FFN 2048, Gelu, seq 128; bf16 activations, int8
     per-channel weights dequantised in the contraction epilogue.  One pass = one batch through all layers."""
 
@@ -560,39 +630,34 @@ class EncoderWorkload(Workload):
         self.metric = "transformer encoder inferences/s (sequences of 128 tokens)"
         self.unit, self.dtype = "inferences/s", "bf16"
 
-    def setup(self, torch, ctx, dev, rep):
+    def model(self):
         from sofie_b200 import encoder as be
-        self.torch, self.ctx, self.be = torch, ctx, be
         self.flops = be.flops_per_sample(self.layers, self.seq, self.d_model, self.ffn)
-        self.weights = be.make_weights(7, self.layers, self.d_model, self.ffn)
-        self.enc = be.EncoderB200(ctx, self.weights, self.batch, self.seq, self.d_model, self.heads, self.ffn, dev)
-        m = self.batch * self.seq
-        self.nsets = int(max(3, math.ceil(1.6 * L2_BYTES / (m * self.d_model * 2.0))))
-        self.xs = [torch.randn(m, self.d_model, device=dev).to(torch.bfloat16) for _ in range(self.nsets)]
+        return be.onnx_model(be.make_weights(7, self.layers, self.d_model, self.ffn), self.batch, self.seq, self.d_model, self.heads)
 
-    def one_pass(self, i):
-        self.enc(self.xs[i % self.nsets])
+    def host_input(self):
+        from sofie_b200 import encoder as be
+        x = np.random.default_rng(7).standard_normal((self.batch * self.seq, self.d_model)).astype(np.float32)
+        return be.f32_to_bf16_bits(x).view(np.int16)
+
+    def setup(self, torch, ctx, dev, rep):
+        self.out_shape, self.out_torch_dtype = (self.batch * self.seq, self.d_model), torch.int16
+        super().setup(torch, ctx, dev, rep)
 
     def units_per_pass(self):
         return float(self.batch)
 
     def config(self):
-        return {"workload": self.name, "layers": self.layers, "d_model": self.d_model, "heads": self.heads, "ffn": self.ffn, "seq_len": self.seq,
-                "batch_per_gpu": self.batch, "weights": "int8 per output channel, scale fused in the contraction epilogue",
-                "gflop_per_inference": self.flops / 1e9, "l2": f"{self.nsets} input batches rotated; the activations of one pass exceed the 126 MiB L2"
-                if self.batch >= 64 else f"{self.nsets} input batches rotated"}
+        return dict({"workload": self.name, "layers": self.layers, "d_model": self.d_model, "heads": self.heads, "ffn": self.ffn, "seq_len": self.seq,
+                     "batch_per_gpu": self.batch, "weights": "int8 per output channel behind DequantizeLinear; the scale is fused in the contraction epilogue",
+                     "gflop_per_inference": self.flops / 1e9,
+                     "l2": "two input batches in turn; the activations of one pass " + ("exceed" if self.batch >= 64 else "do not exceed") + " the 126 MiB L2"},
+                    **self.session_config())
 
     def roofline(self, s_per_pass, peaks, sustained, launches_per_pass):
         ach = self.flops * self.batch / s_per_pass / 1e12
         return tensor_roofline(ach, peaks, sustained, 1.0, "TFLOP/s", "bf16_tflops" + ("_sustained" if sustained else ""), None,
-                               f"; whole pass (all {launches_per_pass:.0f} launches), not one kernel")
-
-    def e2e(self, torch, rep, compute):
-        hx = self.xs[0].cpu().pin_memory()
-        hy = torch.empty_like(hx).pin_memory()
-        r = e2e_measure(torch, rep, compute, self.enc, self.xs[:2], hx, hy, float(self.batch))
-        r["unit"] = self.unit
-        return r
+                               f"; whole pass (all {launches_per_pass:.0f} kernels), not one kernel")
 
     def _cpu(self):
         """The reference's emitted fp32 code of the 6-layer encoder on the dequantised weights, 2 sequences per step."""
@@ -629,13 +694,9 @@ class EncoderWorkload(Workload):
     def reference_step(self):
         return self._cpu()
 
-    def close(self):
-        self.enc.close()
-        self.xs = None
 
-
-class ConvNetWorkload(Workload):
-    """Conv net: 8 Conv3x3 (+ folded BatchNormalization + Relu) layers, global average pool, Gemm 512 -> 1000, on NCHW
+class ConvNetWorkload(SessionWorkload):
+    """Conv net: 8 Conv3x3 (+ BatchNormalization + Relu) layers, global average pool, Gemm 512 -> 1000, on NCHW
     3 x img x img inputs; fp32 or per-channel int8 (QLinearConv).  One pass = one batch through the network."""
 
     def __init__(self, name: str, batch: int, img: int, int8: bool):
@@ -643,52 +704,44 @@ class ConvNetWorkload(Workload):
         self.metric = f"conv net inferences/s ({img}x{img} images, {'int8 QLinearConv' if int8 else 'fp32'})"
         self.unit, self.dtype = "inferences/s", ("int8" if int8 else "fp32 (3xTF32 on tcgen05 where large, fp32 FMA else)")
 
-    def host_input(self, n):
-        x = np.random.default_rng(11).random((n, 3, self.img, self.img), dtype=np.float32)
+    def model(self):
+        from sofie_b200 import convnet as bc
+        self.bc = bc
+        self.flops = bc.flops_per_image(self.img)
+        return bc.onnx_model(11, self.batch, self.img, self.int8)
+
+    def host_input(self, n=None):
+        x = np.random.default_rng(11).random((n or self.batch, 3, self.img, self.img), dtype=np.float32)
         return np.clip(np.rint(x * 127.0), 0, 127).astype(np.int8) if self.int8 else x
 
     def setup(self, torch, ctx, dev, rep):
-        from sofie_b200 import convnet as bc
-        self.torch, self.ctx, self.bc = torch, ctx, bc
-        self.flops = bc.flops_per_image(self.img)
-        self.weights = bc.make_weights(11, self.int8)
-        self.net = bc.ConvNetB200(ctx, self.weights, self.batch, self.img, self.int8, dev)
-        self.hx = torch.from_numpy(self.host_input(self.batch)).pin_memory()
-        self.x = self.hx.to(dev)
-
-    def one_pass(self, i):
-        self.net(self.x)
+        self.out_shape, self.out_torch_dtype = (self.batch, 1000), torch.float32
+        super().setup(torch, ctx, dev, rep)
 
     def units_per_pass(self):
         return float(self.batch)
 
     def config(self):
-        return {"workload": self.name, "batch_per_gpu": self.batch, "image": [3, self.img, self.img], "layers": "8 x Conv3x3+BN+Relu, avgpool, Gemm 512->1000",
-                "strides": self.bc.STRIDES, "gflop_per_inference": self.flops / 1e9, "contraction_kernels": self.net.kernels,
-                "l2": "the activations of one pass are several GB (> 126 MiB L2)"}
+        return dict({"workload": self.name, "batch_per_gpu": self.batch, "image": [3, self.img, self.img],
+                     "layers": "8 x Conv3x3+BN+Relu, avgpool, Gemm 512->1000", "strides": self.bc.STRIDES, "gflop_per_inference": self.flops / 1e9,
+                     "l2": "two input batches in turn; the activations of one pass are several GB (> 126 MiB L2)"}, **self.session_config())
 
     def roofline(self, s_per_pass, peaks, sustained, launches_per_pass):
         ach = self.flops * self.batch / s_per_pass / 1e12
         if self.int8:
             return tensor_roofline(ach, peaks, sustained, 2.0, "TOP/s", "2 x bf16_tflops" + ("_sustained" if sustained else "") + " (int8 dense)", None,
-                                   f"; whole pass ({launches_per_pass:.0f} launches), not one kernel")
+                                   f"; whole pass ({launches_per_pass:.0f} kernels), not one kernel")
         return tensor_roofline(ach, peaks, sustained, 1.0 / 6.0, "TFLOP/s", "bf16_tflops" + ("_sustained" if sustained else "") +
                                " / 6 (TF32 runs at half the bf16 rate and 3xTF32 makes three passes)", None,
-                               f"; whole pass ({launches_per_pass:.0f} launches), not one kernel")
-
-    def e2e(self, torch, rep, compute):
-        hy = torch.empty((self.batch, self.bc.CLASSES), dtype=torch.float32).pin_memory()
-        r = e2e_measure(torch, rep, compute, self.net, [self.x, torch.empty_like(self.x)], self.hx, hy, float(self.batch))
-        r["unit"] = self.unit
-        return r
+                               f"; whole pass ({launches_per_pass:.0f} kernels), not one kernel")
 
     def _cpu(self):
         if not self.int8:
             try:   # the reference's emitted fp32 code (Conv -> BatchNormalization+Relu unfused, as it emits them), 4 images per step
-                m = RefModel("ConvNet_C4t")
-                x = np.random.default_rng(11).random((4, 3, 224, 224), dtype=np.float32)
                 if self.img != 224:
                     raise FileNotFoundError("reference model is built for 224 x 224")
+                m = RefModel("ConvNet_C4t")
+                x = np.random.default_rng(11).random((4, 3, 224, 224), dtype=np.float32)
                 return (lambda: m.infer([x])), 4.0, {"kind": "reference", "cores": os.cpu_count(),
                                                      "sample": f"each step = 4 of {self.batch} images through the SOFIE-emitted fp32 code (oracle/_ref ConvNet_C4t); {m.blas}; "
                                                                "Im2col and BatchNormalization loops of the emitted code are single-threaded"}
@@ -719,10 +772,6 @@ class ConvNetWorkload(Workload):
 
     def reference_step(self):
         return self._cpu()
-
-    def close(self):
-        self.net.close()
-        self.x = None
 
 
 def make_workload(name: str, world: int) -> Workload:
@@ -758,12 +807,12 @@ ALSO = ["fp8_gemm_8192", "convnet_int8_b256", "convnet_fp32_b256", "transformer_
 def measure(torch, rep, ctx, dev, w: Workload, steps: int, warmup: int, seconds: float, cpu_budget: float) -> dict:
     """Warm-up, calibration of the passes per step, the timed region, end-to-end and (one GPU) the CPU baseline."""
     from sofie_b200 import replicas
-    stream = torch.cuda.current_stream(dev)
     w.setup(torch, ctx, dev, rep)
+    stream = w.stream(torch, dev)
     n_warm = max(3, warmup)
     for i in range(n_warm):
         w.one_pass(i)
-    ctx.sync()
+    w.sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for i in range(6):
@@ -776,11 +825,11 @@ def measure(torch, rep, ctx, dev, w: Workload, steps: int, warmup: int, seconds:
     # at least 200 ms of warm-up in all (the reference's rule, benchmark/src/WarmupUtil.hxx:25-39)
     for i in range(int(min(inner * steps, math.ceil(0.2 / t_pass)))):
         w.one_pass(i)
-    ctx.sync()
+    w.sync()
     sampler = ClockSampler(rep.local_rank)
     replicas.barrier(rep)
     torch.cuda.synchronize()
-    l0 = ctx.launches
+    l0 = w.launches()
     sampler.start()
     e0.record(stream)
     k = 0
@@ -791,8 +840,8 @@ def measure(torch, rep, ctx, dev, w: Workload, steps: int, warmup: int, seconds:
     e1.record(stream)
     torch.cuda.synchronize()
     clocks = sampler.stop()
-    ctx.sync()
-    launches = ctx.launches - l0
+    w.sync()
+    launches = w.launches() - l0
     ms_local = e0.elapsed_time(e1)
     replicas.barrier(rep)
     ms = replicas.max_over_ranks(rep, ms_local)
