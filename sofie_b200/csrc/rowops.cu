@@ -66,6 +66,11 @@ __device__ __forceinline__ void store_chunk_as(TOut *p, const float *v) {
   }
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float group_sum(float v, int G) {
   for (int o = G >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
@@ -108,7 +113,7 @@ template <> __device__ __forceinline__ uint4 fill16<__nv_bfloat16>(bool mi) { co
 
 // MODE 0: LayerNorm, 1: Softmax, 2: LogSoftmax.  CH = 16-byte chunks cached per lane.
 template <typename TIn, typename TOut, int CH, int MODE>
-__global__ void __launch_bounds__(256, (MODE == 0 ? (CH >= 16 ? 2 : (CH >= 8 && sizeof(TIn) == 4 ? 3 : 4)) : (CH >= 8 ? 2 : 3))) row_group_kernel(const TIn *__restrict__ x, TOut *__restrict__ y, long long rows,
+__global__ void __launch_bounds__(256, (MODE == 0 ? (CH >= 16 ? 2 : (CH >= 8 && sizeof(TIn) == 4 ? 3 : 4)) : (CH >= 8 ? 2 : (CH >= 4 && sizeof(TIn) == 4 ? 3 : 4)))) row_group_kernel(const TIn *__restrict__ x, TOut *__restrict__ y, long long rows,
                                                         int cols, int G, const float *__restrict__ scale,
                                                         const float *__restrict__ bias, float eps,
                                                         float *__restrict__ mean_out, float *__restrict__ invstd_out) {
@@ -214,8 +219,13 @@ __global__ void __launch_bounds__(256, (MODE == 0 ? (CH >= 16 ? 2 : (CH >= 8 && 
         if (col < cols) {
 #pragma unroll
           for (int e = 0; e < E; ++e) {
-            if constexpr (MODE == 1) { v[c][e] = expf(v[c][e] - m); s += v[c][e]; }
-            else { v[c][e] = v[c][e] - m; s += expf(v[c][e]); }
+            if constexpr (MODE == 1) {
+              // a result that is rounded to bf16 (8 significand bits) takes the hardware's base-2 exponential directly
+              // (2 ulp of fp32); fp32 results keep expf
+              if constexpr (sizeof(TOut) == 2) v[c][e] = fast_exp2(__fmaf_rn(v[c][e], 1.4426950408889634f, -m * 1.4426950408889634f));
+              else v[c][e] = expf(v[c][e] - m);
+              s += v[c][e];
+            } else { v[c][e] = v[c][e] - m; s += expf(v[c][e]); }
           }
         }
       }
@@ -266,13 +276,23 @@ __global__ void __launch_bounds__(256, 2) layernorm_warp_kernel(const TIn *__res
       bi[c][e] = b4.x; bi[c][e + 1] = b4.y; bi[c][e + 2] = b4.z; bi[c][e + 3] = b4.w;
     }
   }
+  // the loads of the next trip are issued before the arithmetic of the current one: a warp always has R * CH 16-byte loads in flight
+  uint4 nxt[R][CH];
+  auto fetch = [&](long long r0) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+        nxt[r][c] = (r0 + r < rows && have[c]) ? ld_raw16(x + (r0 + r) * (long long)cols + (c * 32 + lane) * E) : fill16<TIn>(false);
+  };
+  fetch(warp0 * R);
   for (long long row0 = warp0 * R; row0 < rows; row0 += nwarps * R) {
     uint4 raw[R][CH];
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
-      for (int c = 0; c < CH; ++c)
-        raw[r][c] = (row0 + r < rows && have[c]) ? ld_raw16(x + (row0 + r) * (long long)cols + (c * 32 + lane) * E) : fill16<TIn>(false);
+      for (int c = 0; c < CH; ++c) raw[r][c] = nxt[r][c];
+    fetch(row0 + nwarps * R);
     // rows go through the arithmetic two at a time (registers: the raw rows of the trip stay packed until their turn)
 #pragma unroll
     for (int r0 = 0; r0 < R; r0 += 2) {
@@ -413,7 +433,7 @@ static int launch_rows(sofie_b200_ctx *ctx, const void *x, void *y, long long ro
     TOut *yo = (TOut *)y;
     if constexpr (MODE == 0) {
       if (ch <= 1) layernorm_warp_kernel<TIn, TOut, 1, 4><<<grid, 256, 0, st>>>(xi, yo, rows, (int)cols, scale, bias, eps, mean_out, invstd_out);
-      else if (ch <= 2) layernorm_warp_kernel<TIn, TOut, 2, 4><<<grid, 256, 0, st>>>(xi, yo, rows, (int)cols, scale, bias, eps, mean_out, invstd_out);
+      else if (ch <= 2) layernorm_warp_kernel<TIn, TOut, 2, 2><<<grid, 256, 0, st>>>(xi, yo, rows, (int)cols, scale, bias, eps, mean_out, invstd_out);
       else if constexpr (sizeof(TIn) == 4) layernorm_warp_kernel<TIn, TOut, 4, 2><<<grid, 256, 0, st>>>(xi, yo, rows, (int)cols, scale, bias, eps, mean_out, invstd_out);
     }
   } else if (aligned && chunks <= 32 * 16) {
