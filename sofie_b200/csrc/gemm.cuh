@@ -27,9 +27,14 @@ constexpr int UMMA_STAGE_K_BYTES = 128;  // K extent of one shared-memory stage,
 // device maximum, never to one plan's size (a later, smaller plan would otherwise make an earlier one unlaunchable).
 constexpr int UMMA_MAX_DYN_SMEM = 227 * 1024;
 constexpr int UMMA_TAIL_BYTES = 1024;  // barriers, TMEM slot and abort flag behind the stage ring; the epilogue staging follows
-constexpr int UMMA_EPI_WARPS = 8;     // two epilogue warps per tensor-memory lane quarter, alternating 32-column chunks
-constexpr int UMMA_B_PRODUCER_WARP = 2 + UMMA_EPI_WARPS;  // the warp after the epilogue warps: TMA producer of operand B
-constexpr int UMMA_THREADS = 96 + 32 * UMMA_EPI_WARPS;   // warp 0: TMA producer (A), warp 1: MMA issuer, the epilogue warps, warp 10: producer (B)
+// Warp roles of the tcgen05 kernel: warp 0 TMA producer of operand A, warp 1 MMA issuer, warp 2 TMA producer of operand B,
+// warp 3 idle (it keeps the epilogue warps' index congruent to their tensor-memory lane quarter), then the epilogue warps.
+constexpr int UMMA_EPI_WARPS = 16;    // four epilogue warps per tensor-memory lane quarter, taking 64-byte row segments in turn
+constexpr int UMMA_B_PRODUCER_WARP = 2;
+constexpr int UMMA_FIRST_EPI_WARP = 4;
+constexpr int UMMA_THREADS = 32 * (UMMA_FIRST_EPI_WARP + UMMA_EPI_WARPS);
+constexpr int UMMA_MAX_ACCS = 4;      // accumulators in tensor memory (UmmaParams::accs: 2 or 4)
+constexpr int UMMA_EPI_STAGE_BYTES = 2048;   // staging buffer of one epilogue warp: 32 rows x 64 bytes
 
 // Everything the tcgen05 kernel needs besides the two tensor maps.
 struct UmmaParams {
@@ -63,6 +68,8 @@ struct UmmaParams {
                                    // products (4 loads per 12 MMAs instead of 6); stage byte counts are the doubled ones
   int b_rows;                      // N extent of the B slice one CTA stages (= bn)
   int kb_mmas;                     // MMAs (32 bytes of K each) per K block: 4, or 2 when a K block is 64 bytes
+  int accs;                        // accumulators in tensor memory: 2 or 4
+  int teams;                       // teams of epilogue warps, each draining a tile of its own: 1, 2 or 4, at most accs
   int two_producers;               // operand B is loaded by a thread of its own (warp UMMA_B_PRODUCER_WARP): a thread is held by
                                    // every TMA instruction until the unit takes it, and with 8-bit operands one thread issuing
                                    // both operands' loads was the slowest stage of the pipeline

@@ -1,22 +1,24 @@
 // Contraction kernel for sm_100a: tcgen05.mma with the accumulator in tensor memory, operands
 // staged in 128B-swizzled shared memory by TMA, one persistent CTA per SM.
 //
-// Roles inside a CTA of 352 threads
+// Roles inside a CTA of 640 threads (20 warps, 96 registers per thread)
 //   warp 0, lane 0 : TMA producer of operand A.  Fills a ring of `stages` shared-memory stages; each
 //                    stage holds a 128 x (128 bytes of K) slice of op(A) and a bn x (128 bytes of K)
 //                    slice of op(B).
-//   warp 10, lane 0: TMA producer of operand B (a thread is held by every TMA instruction until the
+//   warp 2, lane 0 : TMA producer of operand B (a thread is held by every TMA instruction until the
 //                    unit has taken it -- 110 to 400 cycles -- and one thread issuing both operands'
 //                    loads fell behind 8-bit MMAs, which need a stage every 512 cycles).
-//   warp 1, lane 0 : MMA issuer.  Four tcgen05.mma (K = 32 bytes each) per stage into one of two
+//   warp 1, lane 0 : MMA issuer.  Four tcgen05.mma (K = 32 bytes each) per stage into one of two or four
 //                    TMEM accumulators (128 lanes x bn columns each); tcgen05.commit releases
 //                    the stage to the producer and, after the last K block, hands the accumulator
 //                    to the epilogue.
-//   warps 2-9      : epilogue, two warps per tensor-memory lane quarter taking alternate 32-column
-//                    chunks.  tcgen05.ld of the next chunk is in flight while the current one goes
-//                    through the fused epilogue (epilogue.cuh) and a shared-memory staging buffer that
-//                    turns row-per-lane data into coalesced 16-byte stores.  The second accumulator
-//                    lets the epilogue of tile t overlap the main loop of tile t+1.
+//   warp 3         : idle (keeps the epilogue warps' index congruent to their tensor-memory lane quarter).
+//   warps 4-19     : epilogue, four warps per tensor-memory lane quarter, in one, two or four teams that
+//                    drain different tiles at the same time (umma_epi16.cuh).  A warp takes 64-byte row
+//                    segments of its 32 rows in steps of 16 columns: tcgen05.ld of the next step is in
+//                    flight while the current one goes through the fused epilogue into a swizzled staging
+//                    buffer, and a complete segment leaves as one bulk tensor store.  The epilogue is bound
+//                    by instruction issue, which is why it has sixteen warps and counts instructions.
 //
 // Data layout: a K-major operand (row-major [rows, K]) is one TMA box of rows x 128 bytes per
 // stage; an MN-major operand (row-major [K, cols]) is cols*es/128 boxes of (128 bytes x K-rows).
@@ -32,28 +34,39 @@
 
 #include "gemm.cuh"
 #include "ptx.cuh"
-#include "umma_store.cuh"
+#include "umma_epi16.cuh"
 
 namespace sb200 {
 using namespace ptx;
 
 // Work items: whole tiles first; the tiles of a short last wave are split into two N halves so that
 // twice as many SMs share them (each half is an MMA of N = bn/2 into the same accumulator columns).
-__device__ __forceinline__ void decode_item(const UmmaParams &p, long long w, long long &tile, int &n_off, int &n_len,
+__device__ __forceinline__ void decode_item(const UmmaParams &p, uint32_t w, uint32_t &tile, int &n_off, int &n_len,
                                             uint32_t &idesc) {
-  if (w < p.split_from) {
+  const uint32_t split_from = (uint32_t)p.split_from;
+  if (w < split_from) {
     tile = w; n_off = 0; n_len = p.bn; idesc = p.idesc;
   } else {
-    const long long x = w - p.split_from;
-    tile = p.split_from + (x >> 1);
+    const uint32_t x = w - split_from;
+    tile = split_from + (x >> 1);
     n_len = p.bn >> 1;
-    n_off = (int)(x & 1) * n_len;
+    n_off = (int)(x & 1u) * n_len;
     idesc = p.idesc_half;
   }
 }
 
+// Tile t of the whole problem -> batch and (M tile, N tile).  32-bit arithmetic (the host refuses plans with 2^31 items or
+// more): every epilogue warp does this once per tile, and 64-bit divisions were a third of a narrow tile's instructions.
+__device__ __forceinline__ void tile_coords(const UmmaParams &p, uint32_t t, uint32_t tiles_per_batch, int &b, int &tm, int &tn) {
+  uint32_t r = t;
+  b = 0;
+  if (p.batch > 1) { b = (int)(t / tiles_per_batch); r = t - (uint32_t)b * tiles_per_batch; }
+  if (p.raster_n) { const uint32_t q = r / (uint32_t)p.tiles_n; tm = (int)q; tn = (int)(r - q * (uint32_t)p.tiles_n); }
+  else { const uint32_t q = r / (uint32_t)p.tiles_m; tn = (int)q; tm = (int)(r - q * (uint32_t)p.tiles_m); }
+}
+
 template <int KIND>
-__global__ void __launch_bounds__(UMMA_THREADS, 1)   // 11 warps are allocated as 12: 168 registers per thread is the most that fits
+__global__ void __launch_bounds__(UMMA_THREADS, 1)   // 20 warps: 96 registers per thread
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ UmmaParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -67,11 +80,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   uint8_t *tail = smem + stages * (p.a_stage_bytes + p.b_stage_bytes);
   const uint32_t bar_full = smem_u32(tail);             // [stages]
   const uint32_t bar_empty = bar_full + 8 * stages;     // [stages]
-  const uint32_t bar_tfull = bar_empty + 8 * stages;    // [2]
-  const uint32_t bar_tempty = bar_tfull + 16;           // [2]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail + 16 * stages + 32);
+  const uint32_t bar_tfull = bar_empty + 8 * stages;    // [UMMA_MAX_ACCS]
+  const uint32_t bar_tempty = bar_tfull + 8 * UMMA_MAX_ACCS;   // [UMMA_MAX_ACCS]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail + 16 * stages + 16 * UMMA_MAX_ACCS);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
-  const uint32_t epi_stage = smem_u32(tail) + UMMA_TAIL_BYTES;   // 4 KB per epilogue warp (coalesced_store)
+  const uint32_t epi_stage = smem_u32(tail) + UMMA_TAIL_BYTES;   // UMMA_EPI_STAGE_BYTES per epilogue warp
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -81,9 +94,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       mbar_init(bar_full + 8 * s, p.two_producers ? 2 : 1);   // one arrival (with its byte count) per producer
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < p.accs; ++i) {
       mbar_init(bar_tfull + 8 * i, 1);
-      mbar_init(bar_tempty + 8 * i, UMMA_EPI_WARPS);  // one arrival per epilogue warp
+      mbar_init(bar_tempty + 8 * i, UMMA_EPI_WARPS / p.teams);  // one arrival per epilogue warp of the team that drains it
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -100,7 +113,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;
+  const uint32_t tiles_per_batch = (uint32_t)p.tiles_m * (uint32_t)p.tiles_n;
+  const uint32_t num_items = (uint32_t)p.num_items;
 
   if (warp == 0 || warp == UMMA_B_PRODUCER_WARP) {
     // ------------------------------ TMA producers -----------------------------------
@@ -118,13 +132,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #ifdef SB200_ROLE_TIMERS
       t_begin = clock64();
 #endif
-      for (long long w = blockIdx.x; w < p.num_items && ok; w += gridDim.x) {
-        long long t; int n_off, n_len; uint32_t idesc;
+      for (uint32_t w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
+        uint32_t t; int n_off, n_len; uint32_t idesc;
         decode_item(p, w, t, n_off, n_len, idesc);
-        const int b = (int)(t / tiles_per_batch);
-        const int r = (int)(t % tiles_per_batch);
-        int tm, tn;
-        tile_mn(p, r, tm, tn);
+        int b, tm, tn;
+        tile_coords(p, t, tiles_per_batch, b, tm, tn);
         const int m0 = tm * UMMA_BM;
         const int n0 = tn * p.bn + n_off;  // a half item still loads a full-width B slice
         const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
@@ -137,7 +149,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           ic_w = (rem - oh * p.ic_wo) * p.ic_sw - p.ic_pl;
         }
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!ROLE_WAIT(w_empty, mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag))) {
+          if (!ROLE_WAIT(w_empty, mbar_wait_relaxed(bar_empty + 8 * stage, phase ^ 1u, abort_flag))) {
             raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_EMPTY);
             ok = false;
             break;
@@ -203,10 +215,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #ifdef SB200_ROLE_TIMERS
       t_begin = clock64();
 #endif
-      for (long long w = blockIdx.x; w < p.num_items && ok; w += gridDim.x) {
-        long long t; int n_off, n_len; uint32_t idesc;
+      for (uint32_t w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
+        uint32_t t; int n_off, n_len; uint32_t idesc;
         decode_item(p, w, t, n_off, n_len, idesc);
-        if (!ROLE_WAIT(w_tempty, mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag))) {
+        if (!ROLE_WAIT(w_tempty, mbar_wait_relaxed(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag))) {
           raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_EMPTY);
           break;
         }
@@ -239,16 +251,28 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         if (!ok) break;
         tc_commit(bar_tfull + 8 * acc);      // accumulator complete
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        if (++acc == (uint32_t)p.accs) { acc = 0; acc_phase ^= 1u; }
       }
       ROLE_REPORT("[cta %d] mma issuer: total %lld, waiting for operands %lld, for a drained accumulator %lld\n", blockIdx.x,
                   clock64() - t_begin, w_full, w_tempty);
       ROLE_REPORT("[cta %d] mma issuer sections: fence %lld, issuing MMAs %lld, commits %lld\n", blockIdx.x, c_fence, c_mma, c_commit);
     }
-  } else {
+  } else if (warp >= UMMA_FIRST_EPI_WARP) {
     // ------------------------------ epilogue -----------------------------------------
     const int quad = warp & 3;  // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
-    uint32_t acc = 0, acc_phase = 0;
+    const int epi_warp = warp - UMMA_FIRST_EPI_WARP;
+    // The four groups of four warps (one warp per lane quarter) form p.teams teams; a team drains every p.teams-th tile
+    // of this CTA, its groups taking alternate row segments.  More teams = more tiles in the epilogue at once and fewer
+    // warps paying each tile's fixed costs (what a narrow or short-K tile needs); fewer teams = an accumulator is free
+    // again sooner (what a tile needs whose MMAs take as long as its epilogue).  umma_plan_init() picks.
+    const int group = epi_warp >> 2;
+    const int groups_per_team = (UMMA_EPI_WARPS / 4) / p.teams;
+    const uint32_t team = (uint32_t)(group / groups_per_team);
+    const int seg_first = group % groups_per_team;
+    const uint32_t acc_mask = (uint32_t)p.accs - 1u, acc_shift = (uint32_t)p.accs >> 1;   // accs is 2 or 4
+    const Epi16Warp ew = epi16_warp_init(p.ep, epi_stage + (uint32_t)epi_warp * UMMA_EPI_STAGE_BYTES);
+    const CUtensorMap *y_map = p.y_tma ? &tm_y : nullptr;
+    const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16);
     ROLE_TIMER(w_tfull);
     ROLE_TIMER(c_ld);
     ROLE_TIMER(c_st);
@@ -257,40 +281,30 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #ifdef SB200_ROLE_TIMERS
     t_begin = clock64();
 #endif
-    for (long long w = blockIdx.x; w < p.num_items; w += gridDim.x) {
-      long long t; int n_off, n_len; uint32_t idesc;
+    for (uint32_t i = team, w = blockIdx.x + team * gridDim.x; w < num_items; i += (uint32_t)p.teams, w += gridDim.x * (uint32_t)p.teams) {
+      const uint32_t acc = i & acc_mask, acc_phase = (i >> acc_shift) & 1u;   // tile i of this CTA: accumulator and its phase
+      const uint32_t taddr = taddr0 + acc * p.bn;
+      uint32_t t; int n_off, n_len; uint32_t idesc;
       decode_item(p, w, t, n_off, n_len, idesc);
-      const int b = (int)(t / tiles_per_batch);
-      const int r = (int)(t % tiles_per_batch);
-      int tm, tn;
-      tile_mn(p, r, tm, tn);
+      int b, tm, tn;
+      tile_coords(p, t, tiles_per_batch, b, tm, tn);
       const int m0 = tm * UMMA_BM;
       const int n0 = tn * p.bn + n_off;
-      if (!ROLE_WAIT(w_tfull, mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag))) {
+      if (!ROLE_WAIT(w_tfull, mbar_wait_relaxed(bar_tfull + 8 * acc, acc_phase, abort_flag))) {
         raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_FULL);
         break;
       }
       tc_fence_after();
       const int row = m0 + quad * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * p.bn;
-      const uint32_t my_stage = epi_stage + (uint32_t)(warp - 2) * 4096u;
       const int c_end = min(n_len, p.N - n0);          // columns of this item that exist (warp-uniform)
       ROLE_SECTION_BEGIN();
-      drain_accumulator<KIND == KIND_I8>(p.ep, taddr, c_end, (warp - 2) >> 2, 2, b, row, n0, p.vec_ok != 0, my_stage, p.M, p.y_tma ? &tm_y : nullptr);
+      drain16_any<KIND == KIND_I8>(p.ep, ew, taddr, c_end, seg_first, groups_per_team, b, row, n0, p.vec_ok != 0, p.M, y_map);
       ROLE_SECTION_END(c_st);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
-#ifdef SB200_ROLE_TIMERS
-    if (threadIdx.x == 64 && blockIdx.x == 0) {
-      printf("[cta 0] drain: tmem wait %lld, wait for buffer %lld, math+stage %lld, flush/issue %lld, final wait %lld\n", g_drain_cycles[0],
-             g_drain_cycles[1], g_drain_cycles[2], g_drain_cycles[3], g_drain_cycles[4]);
-      for (int i = 0; i < 6; ++i) g_drain_cycles[i] = 0;
-    }
-#endif
-    if (threadIdx.x == 64) { ROLE_REPORT("[cta %d] epilogue: total %lld, waiting for an accumulator %lld, tensor-memory loads %lld, epilogue math + stores %lld\n", blockIdx.x, clock64() - t_begin, w_tfull, c_ld, c_st); }
+    if (threadIdx.x == 32 * UMMA_FIRST_EPI_WARP) { ROLE_REPORT("[cta %d] epilogue: total %lld, waiting for an accumulator %lld, tensor-memory loads %lld, epilogue math + stores %lld\n", blockIdx.x, clock64() - t_begin, w_tfull, c_ld, c_st); }
   }
 
   tc_fence_before();
@@ -353,7 +367,7 @@ static int encode_im2col(CUtensorMap *tm, int dtype, const void *base, const Im2
 }
 
 static CUtensorMapSwizzle swizzle_mode(int bytes) {
-  return bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : (bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+  return bytes == 16 ? CU_TENSOR_MAP_SWIZZLE_NONE : (bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : (bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B));
 }
 
 static int encode_map(CUtensorMap *tm, int dtype, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
@@ -471,10 +485,31 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
     u.ic_cblocks = (int)(ic.C / u.kb_elems);
     u.ic_c = (int)ic.C;
   }
+  // Accumulators in tensor memory (512 columns): four where the tile is at most 128 columns wide, else two.  Teams of
+  // epilogue warps (see the kernel): the count that minimises a model of the time per tile -- the slowest of the MMAs,
+  // the epilogue (a fixed latency per tile and team on top of the issue-bound part), and the accumulators' turnaround.
+  // The constants are measurements: 6 output elements per cycle and SM through the epilogue, 1500 cycles per tile.
+  u.accs = u.bn <= 128 ? 4 : 2;
+  u.teams = 1;
+  if (plan->promote) {
+    u.accs = 2;
+  } else {
+    const double macs_per_clk = es == 1 ? 8192.0 : (es == 2 ? 4096.0 : 2048.0);
+    const double t_mma = 128.0 * u.bn * (double)u.num_kb * u.kb_elems / macs_per_clk;
+    const double t_epi = 128.0 * u.bn / 6.0, fixed = 1500.0;
+    double best = 0;
+    for (int t = 1; t <= u.accs; t *= 2) {
+      double period = t_mma;
+      if (t_epi + fixed / t > period) period = t_epi + fixed / t;
+      const double turn = (t_mma + t * t_epi + fixed) / u.accs;
+      if (turn > period) period = turn;
+      if (t == 1 || period < 0.97 * best) { best = period; u.teams = t; }
+    }
+  }
   u.tmem_cols = 32;
-  while (u.tmem_cols < 2u * u.bn) u.tmem_cols <<= 1;
+  while (u.tmem_cols < (uint32_t)u.accs * u.bn) u.tmem_cols <<= 1;
 
-  const size_t epi_bytes = 8 * 4096;   // staging buffers of the epilogue warps
+  const size_t epi_bytes = 32 * 1024;   // staging buffers of the epilogue warps (16 x 2 KB; the promotion kernel's 8 x 4 KB)
   const size_t budget = 227 * 1024 - 1024 /*alignment*/ - UMMA_TAIL_BYTES /*barriers*/ - epi_bytes;
   int stages = (int)(budget / (u.a_stage_bytes + u.b_stage_bytes));
   if (stages > (kb_bytes == 64 ? 12 : 8)) stages = kb_bytes == 64 ? 12 : 8;
@@ -531,6 +566,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
       u.num_items = u.num_tiles + tail;
     }
   }
+  if (u.num_items >= (1ll << 31)) return 1;   // the kernel counts work items in 32 bits
   long long grid = u.num_tiles < plan->ctx->sm_count ? u.num_tiles : plan->ctx->sm_count;
   plan->grid = (int)grid;
   if (plan->promote) return umma_promote_set_smem(plan->smem_bytes);
@@ -595,15 +631,16 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
   u.ep = ep;
   u.ep.split_out = plan->split_out;
   if (((uintptr_t)ep.Y % 16) != 0) u.vec_ok = 0;
-  // Tensor map of Y for the epilogue's bulk stores: box = one 128-byte row segment x the 32 rows of an epilogue warp.
+  // Tensor map of Y for the epilogue's bulk stores: box = one row segment x the 32 rows of an epilogue warp.  A segment is
+  // 64 bytes (128 in the promotion kernel): 4 steps of 16 columns of 1-byte outputs, 2 of 2-byte, 1 of 4-byte outputs.  A
+  // narrow tile then has fewer segments than the lane quarter has warps, so the segment is halved until every warp has one.
   u.y_tma = 0;
-  // Row segments per flush: a 128-byte segment is 4 chunks of 1-byte and 2 of 2-byte outputs; a narrow tile then has a
-  // single segment and one of the two warps of each lane quarter would idle, so the segment is halved until there are two.
+  const int seg_bytes = plan->promote ? 128 : 64;
   int seg_div = 1;
   if (!plan->promote) {
-    const int full = 4 / dtype_size(plan->desc.y_dtype);   // chunks per 128 bytes
+    const int full = 4 / dtype_size(plan->desc.y_dtype);   // steps per segment
     int g = full;
-    while (g > 1 && (u.bn / 32) / g < 2) g >>= 1;
+    while (g > 1 && (u.bn / 16) / g < (UMMA_EPI_WARPS / 4) / u.teams) g >>= 1;   // at least one segment per group of a team
     if (g < full) { u.ep.seg_chunks = g; seg_div = full / g; }
   }
   if (u.vec_ok) {
@@ -613,7 +650,7 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
       const uint64_t s2 = d.batch > 1 ? (uint64_t)d.stride_y * ys : (uint64_t)d.M * d.ldy * ys;
       // (a TF32-pair output is 2 N columns wide: the lo halves follow the hi halves)
       rc = encode_map(&plan->tm_y, d.y_dtype, ep.Y, (uint64_t)(plan->split_out ? 2 * d.N : d.N), (uint64_t)d.M, (uint64_t)d.batch, (uint64_t)d.ldy * ys, s2,
-                      (uint32_t)(128 / ys / seg_div), 32, 128 / seg_div);
+                      (uint32_t)(seg_bytes / ys / seg_div), 32, seg_bytes / seg_div);
       if (rc) return rc;
       plan->cached_y = ep.Y;
       plan->cached_seg_div = seg_div;

@@ -53,10 +53,10 @@ __device__ __noinline__ void promote_finish(const UmmaParams &p, const CUtensorM
       // the branch-light epilogue of the plain kernel (same arithmetic, step for step)
       const long long rr = row < p.M ? row : (long long)p.M - 1;
       float2 v[16];
-      epi_values_fast<false, 1>(p.ep, raw, v, rr, col, my_stage, 0);
+      epi_values_fast<false, 32>(p.ep, raw, v, rr, col, my_stage, 0);
       for (int part = 0; part < parts; ++part) {
         buffer_free();
-        epi_finish_fast<1>(p.ep, v, b, rr, col, my_stage, 0, p.ep.split_out ? part + 1 : 0);
+        epi_finish_fast<32>(p.ep, v, b, rr, col, my_stage, 0, p.ep.split_out ? part + 1 : 0);
         if (p.y_tma) {   // the 32 rows x 128 bytes leave as one bulk tensor store (rows past the end are clipped)
           fence_proxy_async();
           __syncwarp();

@@ -46,6 +46,22 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
+// The same with a suspend-time hint: the thread may stay suspended (issuing nothing) for up to `hint_ns` while the phase
+// is incomplete, and resumes when it completes.  A waiting role then leaves the issue slots of its scheduler to the
+// epilogue warps instead of spending them on polling.
+__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok;
+}
 
 // Bounded wait on an mbarrier phase.  Gives up when another role of the CTA has already
 // given up (abort flag in shared memory) or after about one second of polling, so that a
@@ -56,6 +72,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 255u) {
+      if (*abort_flag) return false;
+      uint64_t now = globaltimer();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) return false;
+    }
+  }
+}
+// The same for a wait that is usually long (a producer ahead of the consumer, the issuer ahead of the epilogue): polls
+// with a suspend-time hint, and so looks at the clock on every 16th failed poll.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                                  uint64_t limit_ns = 1000000000ull) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+    if ((it & 15u) == 15u) {
       if (*abort_flag) return false;
       uint64_t now = globaltimer();
       if (t0 == 0) t0 = now;
@@ -174,6 +206,16 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t *r) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t *r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }

@@ -81,10 +81,11 @@ __device__ __forceinline__ int out_elem_bytes(int y_dtype) {
 // 128-byte segment, the function returns true, and the caller flushes the buffer with flush_staged() once the
 // segment is complete; then EVERY lane of the warp must make the call (rows at or past `rows_total` are computed
 // but never stored).  Otherwise the chunk is stored directly and the function returns false.
-__device__ __forceinline__ bool store_chunk(const EpiParams &ep, const uint32_t (&raw)[32], long long b, long long row,
+template <int W = 32>
+__device__ __forceinline__ bool store_chunk(const EpiParams &ep, const uint32_t (&raw)[W], long long b, long long row,
                                             int col0, int ncols, bool vec, uint32_t stage = 0, long long rows_total = 0,
                                             int slot = 0, int split_part = 0) {
-  const bool full = ncols == 32;
+  const bool full = ncols == W;
   // split_part (fp32 output as a TF32 pair, EpiParams::split_out): 1 stores hi = tf32(v) at the element's own column,
   // 2 stores lo = tf32(v - hi) at column N + j; the caller makes both calls (and flushes at the matching address)
   const long long off = b * ep.stride_y + row * ep.ldy + col0 + (split_part == 2 ? ep.ldy / 2 : 0);
@@ -93,105 +94,105 @@ __device__ __forceinline__ bool store_chunk(const EpiParams &ep, const uint32_t 
   const long long rr = (stage != 0 && row >= rows_total) ? rows_total - 1 : row;   // row whose per-row operands are read
 
   if (ep.y_dtype == SOFIE_B200_I32) {  // raw integer accumulator (+ int32 bias)
-    int a[32];
+    int a[W];
 #pragma unroll
-    for (int c = 0; c < 32; ++c) a[c] = (int)raw[c];
+    for (int c = 0; c < W; ++c) a[c] = (int)raw[c];
     if (ep.bias_mode == SOFIE_B200_BIAS_COL_I32) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) a[c] += (full || c < ncols) ? ((const int *)ep.bias)[col0 + c] : 0;
+      for (int c = 0; c < W; ++c) a[c] += (full || c < ncols) ? ((const int *)ep.bias)[col0 + c] : 0;
     } else if (ep.bias_mode == SOFIE_B200_BIAS_ROW_I32) {
       const int br = ((const int *)ep.bias)[rr];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) a[c] += br;
+      for (int c = 0; c < W; ++c) a[c] += br;
     }
     int *y = (int *)ep.Y + off;
     if (staged) {
-      uint32_t w[32];
+      uint32_t w[W];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) w[c] = (uint32_t)a[c];
-      stage_units<8>(stage, w, slot);
+      for (int c = 0; c < W; ++c) w[c] = (uint32_t)a[c];
+      stage_units<W / 4>(stage, w, slot);
       return true;
     } else if (vec && full) {
 #pragma unroll
-      for (int c = 0; c < 32; c += 4) st_v4(y + c, a[c], a[c + 1], a[c + 2], a[c + 3]);
+      for (int c = 0; c < W; c += 4) st_v4(y + c, a[c], a[c + 1], a[c + 2], a[c + 3]);
     } else {
 #pragma unroll
-      for (int c = 0; c < 32; ++c)
+      for (int c = 0; c < W; ++c)
         if (c < ncols) y[c] = a[c];
     }
     return false;
   }
 
-  float v[32];
+  float v[W];
   // 1. accumulator -> fp32
   if (ep.acc_is_int) {
     if (ep.bias_mode == SOFIE_B200_BIAS_COL_I32) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = (float)((int)raw[c] + ((full || c < ncols) ? ((const int *)ep.bias)[col0 + c] : 0));
+      for (int c = 0; c < W; ++c) v[c] = (float)((int)raw[c] + ((full || c < ncols) ? ((const int *)ep.bias)[col0 + c] : 0));
     } else {
       const int br = ep.bias_mode == SOFIE_B200_BIAS_ROW_I32 ? ((const int *)ep.bias)[rr] : 0;
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = (float)((int)raw[c] + br);
+      for (int c = 0; c < W; ++c) v[c] = (float)((int)raw[c] + br);
     }
   } else {
 #pragma unroll
-    for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(raw[c]);
+    for (int c = 0; c < W; ++c) v[c] = __uint_as_float(raw[c]);
   }
   // 2. scales, in the documented order: row, column, alpha
   if (ep.row_scale) {
     const float rs = ep.row_scale[rr];
 #pragma unroll
-    for (int c = 0; c < 32; ++c) v[c] = __fmul_rn(v[c], rs);
+    for (int c = 0; c < W; ++c) v[c] = __fmul_rn(v[c], rs);
   }
   if (ep.col_scale) {
     if (full && ep.params_aligned) {
 #pragma unroll
-      for (int c = 0; c < 32; c += 4) {
+      for (int c = 0; c < W; c += 4) {
         const float4 s4 = *reinterpret_cast<const float4 *>(ep.col_scale + col0 + c);  // col0 % 32 == 0
         v[c] = __fmul_rn(v[c], s4.x); v[c + 1] = __fmul_rn(v[c + 1], s4.y);
         v[c + 2] = __fmul_rn(v[c + 2], s4.z); v[c + 3] = __fmul_rn(v[c + 3], s4.w);
       }
     } else {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = __fmul_rn(v[c], c < ncols ? ep.col_scale[col0 + c] : 1.f);
+      for (int c = 0; c < W; ++c) v[c] = __fmul_rn(v[c], c < ncols ? ep.col_scale[col0 + c] : 1.f);
     }
   }
   if (ep.alpha != 1.f) {
 #pragma unroll
-    for (int c = 0; c < 32; ++c) v[c] = __fmul_rn(v[c], ep.alpha);
+    for (int c = 0; c < W; ++c) v[c] = __fmul_rn(v[c], ep.alpha);
   }
   // 3. additive terms
   switch (ep.bias_mode) {
     case SOFIE_B200_BIAS_COL_F32:
       if (full && ep.params_aligned) {
 #pragma unroll
-        for (int c = 0; c < 32; c += 4) {
+        for (int c = 0; c < W; c += 4) {
           const float4 b4 = *reinterpret_cast<const float4 *>((const float *)ep.bias + col0 + c);
           v[c] = __fadd_rn(v[c], b4.x); v[c + 1] = __fadd_rn(v[c + 1], b4.y);
           v[c + 2] = __fadd_rn(v[c + 2], b4.z); v[c + 3] = __fadd_rn(v[c + 3], b4.w);
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < 32; ++c)
+        for (int c = 0; c < W; ++c)
           if (c < ncols) v[c] = __fadd_rn(v[c], ((const float *)ep.bias)[col0 + c]);
       }
       break;
     case SOFIE_B200_BIAS_ROW_F32: {
       const float br = ((const float *)ep.bias)[rr];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = __fadd_rn(v[c], br);
+      for (int c = 0; c < W; ++c) v[c] = __fadd_rn(v[c], br);
       break;
     }
     case SOFIE_B200_BIAS_SCALAR_F32: {
       const float bs = ((const float *)ep.bias)[0];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = __fadd_rn(v[c], bs);
+      for (int c = 0; c < W; ++c) v[c] = __fadd_rn(v[c], bs);
       break;
     }
     case SOFIE_B200_BIAS_FULL_F32: {
       const float *cr = (const float *)ep.bias + b * ep.stride_c + rr * ep.ldc + col0;
 #pragma unroll
-      for (int c = 0; c < 32; ++c)
+      for (int c = 0; c < W; ++c)
         if (full || c < ncols) v[c] = __fadd_rn(v[c], __fmul_rn(ep.beta, cr[c]));
       break;
     }
@@ -202,12 +203,12 @@ __device__ __forceinline__ bool store_chunk(const EpiParams &ep, const uint32_t 
     if (ep.residual_dtype == SOFIE_B200_BF16) {
       const __nv_bfloat16 *r = (const __nv_bfloat16 *)ep.residual + roff;
 #pragma unroll
-      for (int c = 0; c < 32; ++c)
+      for (int c = 0; c < W; ++c)
         if (full || c < ncols) v[c] = __fadd_rn(v[c], __bfloat162float(r[c]));
     } else {
       const float *r = (const float *)ep.residual + roff;
 #pragma unroll
-      for (int c = 0; c < 32; ++c)
+      for (int c = 0; c < W; ++c)
         if (full || c < ncols) v[c] = __fadd_rn(v[c], r[c]);
     }
   }
@@ -216,21 +217,21 @@ __device__ __forceinline__ bool store_chunk(const EpiParams &ep, const uint32_t 
     case SOFIE_B200_ACT_NONE: break;
     case SOFIE_B200_ACT_RELU:
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_RELU, 0.f);
+      for (int c = 0; c < W; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_RELU, 0.f);
       break;
     case SOFIE_B200_ACT_GELU_ERF:
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_GELU_ERF, 0.f);
+      for (int c = 0; c < W; ++c) v[c] = act_apply(v[c], SOFIE_B200_ACT_GELU_ERF, 0.f);
       break;
     default:
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = act_apply(v[c], ep.act, ep.act_alpha);
+      for (int c = 0; c < W; ++c) v[c] = act_apply(v[c], ep.act, ep.act_alpha);
       break;
   }
   // 5. convert and store
   if (split_part != 0) {
 #pragma unroll
-    for (int c = 0; c < 32; ++c) {
+    for (int c = 0; c < W; ++c) {
       const float h = tf32_rn(v[c]);
       v[c] = split_part == 1 ? h : tf32_rn(__fsub_rn(v[c], h));
     }
@@ -238,34 +239,34 @@ __device__ __forceinline__ bool store_chunk(const EpiParams &ep, const uint32_t 
   if (ep.y_dtype == SOFIE_B200_F32) {
     float *y = (float *)ep.Y + off;
     if (staged) {
-      uint32_t w[32];
+      uint32_t w[W];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) w[c] = __float_as_uint(v[c]);
-      stage_units<8>(stage, w, slot);
+      for (int c = 0; c < W; ++c) w[c] = __float_as_uint(v[c]);
+      stage_units<W / 4>(stage, w, slot);
       return true;
     } else if (vec && full) {
 #pragma unroll
-      for (int c = 0; c < 32; c += 4)
+      for (int c = 0; c < W; c += 4)
         st_v4(y + c, __float_as_uint(v[c]), __float_as_uint(v[c + 1]), __float_as_uint(v[c + 2]), __float_as_uint(v[c + 3]));
     } else {
 #pragma unroll
-      for (int c = 0; c < 32; ++c)
+      for (int c = 0; c < W; ++c)
         if (c < ncols) y[c] = v[c];
     }
   } else if (ep.y_dtype == SOFIE_B200_BF16) {
     __nv_bfloat16 *y = (__nv_bfloat16 *)ep.Y + off;
     if (staged) {
-      uint32_t w[16];
+      uint32_t w[W / 2];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) {
+      for (int u = 0; u < W / 2; ++u) {
         __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * u], v[2 * u + 1]);
         w[u] = *reinterpret_cast<uint32_t *>(&h2);
       }
-      stage_units<4>(stage, w, slot);
+      stage_units<W / 8>(stage, w, slot);
       return true;
     } else if (vec && full) {
 #pragma unroll
-      for (int c = 0; c < 32; c += 8) {
+      for (int c = 0; c < W; c += 8) {
         uint32_t w[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -276,7 +277,7 @@ __device__ __forceinline__ bool store_chunk(const EpiParams &ep, const uint32_t 
       }
     } else {
 #pragma unroll
-      for (int c = 0; c < 32; ++c)
+      for (int c = 0; c < W; ++c)
         if (c < ncols) y[c] = __float2bfloat16_rn(v[c]);
     }
   } else {  // I8 / U8: ONNX rounding (half to even), zero point, saturate
@@ -285,21 +286,21 @@ __device__ __forceinline__ bool store_chunk(const EpiParams &ep, const uint32_t 
     const float zp = (float)ep.out_zp;
     if (ep.out_scale != 1.f) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) v[c] = __fdiv_rn(v[c], ep.out_scale);
+      for (int c = 0; c < W; ++c) v[c] = __fdiv_rn(v[c], ep.out_scale);
     }
-    uint32_t q[32];
+    uint32_t q[W];
 #pragma unroll
-    for (int c = 0; c < 32; ++c) q[c] = (uint32_t)(int)fminf(fmaxf(rintf(v[c]) + zp, lo), hi) & 0xffu;
+    for (int c = 0; c < W; ++c) q[c] = (uint32_t)(int)fminf(fmaxf(rintf(v[c]) + zp, lo), hi) & 0xffu;
     uint8_t *y = (uint8_t *)ep.Y + off;
     if (staged) {
-      uint32_t w[8];
+      uint32_t w[W / 4];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) w[u] = q[4 * u] | (q[4 * u + 1] << 8) | (q[4 * u + 2] << 16) | (q[4 * u + 3] << 24);
-      stage_units<2>(stage, w, slot);
+      for (int u = 0; u < W / 4; ++u) w[u] = q[4 * u] | (q[4 * u + 1] << 8) | (q[4 * u + 2] << 16) | (q[4 * u + 3] << 24);
+      stage_units<W / 16>(stage, w, slot);
       return true;
     } else if (vec && full) {
 #pragma unroll
-      for (int c = 0; c < 32; c += 16) {
+      for (int c = 0; c < W; c += 16) {
         uint32_t w[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u)
@@ -308,7 +309,7 @@ __device__ __forceinline__ bool store_chunk(const EpiParams &ep, const uint32_t 
       }
     } else {
 #pragma unroll
-      for (int c = 0; c < 32; ++c)
+      for (int c = 0; c < W; ++c)
         if (c < ncols) y[c] = (uint8_t)q[c];
     }
   }
@@ -362,10 +363,9 @@ __device__ __forceinline__ float2 gelu_erf_pair_lowp(float2 x) {
 // First half of the fast path: everything that reads the raw accumulator -- integer bias, conversion, the three
 // scales and the additive bias terms -- into v[32].  When it returns, `raw` is dead and the caller may already
 // load the next chunk into it.  Returns false when the chunk was finished here (int32 output: staged as is).
-template <bool ACC_INT, int NC>
-__device__ __forceinline__ bool epi_values_fast(const EpiParams &ep, const uint32_t (&raw)[32 * NC], float2 (&v)[16 * NC], long long rr, int col0,
+template <bool ACC_INT, int W>   // W columns handled together (16, 32 or 64): independent chains for the scheduler to interleave
+__device__ __forceinline__ bool epi_values_fast(const EpiParams &ep, const uint32_t (&raw)[W], float2 (&v)[W / 2], long long rr, int col0,
                                                 uint32_t stage, int slot) {
-  constexpr int W = 32 * NC;   // columns handled together: independent chains for the scheduler to interleave
   const int mode = ep.bias_mode;
   const int4 *bip = reinterpret_cast<const int4 *>(g_epi_izero);
   int rbi = 0;
@@ -375,16 +375,17 @@ __device__ __forceinline__ bool epi_values_fast(const EpiParams &ep, const uint3
     if (mode == SOFIE_B200_BIAS_ROW_I32) rbi = ((const int *)ep.bias)[rr];
   }
   if (__builtin_expect(ep.y_dtype == SOFIE_B200_I32, 0)) {  // raw integer accumulator (+ int32 bias)
+    constexpr int CW = W < 32 ? W : 32;   // columns per staging call
 #pragma unroll
-    for (int i = 0; i < NC; ++i) {
-      uint32_t w[32];
+    for (int i = 0; i < W / CW; ++i) {
+      uint32_t w[CW];
 #pragma unroll
-      for (int c = 0; c < 32; c += 4) {
-        const int4 bi = bip[((32 * i + c) >> 2) * bi_step];
-        w[c] = (uint32_t)((int)raw[32 * i + c] + bi.x + rbi); w[c + 1] = (uint32_t)((int)raw[32 * i + c + 1] + bi.y + rbi);
-        w[c + 2] = (uint32_t)((int)raw[32 * i + c + 2] + bi.z + rbi); w[c + 3] = (uint32_t)((int)raw[32 * i + c + 3] + bi.w + rbi);
+      for (int c = 0; c < CW; c += 4) {
+        const int4 bi = bip[((CW * i + c) >> 2) * bi_step];
+        w[c] = (uint32_t)((int)raw[CW * i + c] + bi.x + rbi); w[c + 1] = (uint32_t)((int)raw[CW * i + c + 1] + bi.y + rbi);
+        w[c + 2] = (uint32_t)((int)raw[CW * i + c + 2] + bi.z + rbi); w[c + 3] = (uint32_t)((int)raw[CW * i + c + 3] + bi.w + rbi);
       }
-      stage_units<8>(stage, w, slot + i);
+      stage_units<CW / 4>(stage, w, slot + i);
     }
     return false;
   }
@@ -419,10 +420,10 @@ __device__ __forceinline__ bool epi_values_fast(const EpiParams &ep, const uint3
 // Second half of the fast path: residual, activation, conversion to the output type, staging.
 // split_part (fp32 output as a TF32 pair, EpiParams::split_out): 1 stages hi = tf32(v); 2, called right after 1 on the same
 // v, stages lo = tf32(v - hi) and skips the residual and the activation, which call 1 has already applied to v.
-template <int NC>
-__device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)[16 * NC], long long b, long long rr, int col0, uint32_t stage,
+template <int W>
+__device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)[W / 2], long long b, long long rr, int col0, uint32_t stage,
                                                 int slot, int split_part = 0) {
-  constexpr int W = 32 * NC, P = 16 * NC;
+  constexpr int P = W / 2, CW = W < 32 ? W : 32, NC = W / CW;   // pairs; columns per staging call; staging calls
   if (ep.residual && split_part != 2) {
     const long long roff = b * ep.stride_r + rr * ep.ldr + col0;
     if (ep.residual_dtype == SOFIE_B200_BF16) {
@@ -468,21 +469,21 @@ __device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)
   if (ep.y_dtype == SOFIE_B200_BF16) {
 #pragma unroll
     for (int i = 0; i < NC; ++i) {
-      uint32_t w[16];
+      uint32_t w[CW / 2];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[16 * i + u].x, v[16 * i + u].y);
+      for (int u = 0; u < CW / 2; ++u) {
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(v[CW / 2 * i + u].x, v[CW / 2 * i + u].y);
         w[u] = *reinterpret_cast<uint32_t *>(&h2);
       }
-      stage_units<4>(stage, w, slot + i);
+      stage_units<CW / 8>(stage, w, slot + i);
     }
   } else if (ep.y_dtype == SOFIE_B200_F32) {
 #pragma unroll
     for (int i = 0; i < NC; ++i) {
-      uint32_t w[32];
+      uint32_t w[CW];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        float x = v[16 * i + u].x, y = v[16 * i + u].y;
+      for (int u = 0; u < CW / 2; ++u) {
+        float x = v[CW / 2 * i + u].x, y = v[CW / 2 * i + u].y;
         if (split_part != 0) {
           const float hx = tf32_rn(x), hy = tf32_rn(y);
           x = split_part == 1 ? hx : tf32_rn(__fsub_rn(x, hx));
@@ -490,7 +491,7 @@ __device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)
         }
         w[2 * u] = __float_as_uint(x); w[2 * u + 1] = __float_as_uint(y);
       }
-      stage_units<8>(stage, w, slot + i);
+      stage_units<CW / 4>(stage, w, slot + i);
     }
   } else {  // I8 / U8: ONNX rounding (half to even), zero point, saturate
     const int lo = ep.y_dtype == SOFIE_B200_I8 ? -128 : 0, hi = ep.y_dtype == SOFIE_B200_I8 ? 127 : 255;
@@ -507,149 +508,27 @@ __device__ __forceinline__ void epi_finish_fast(const EpiParams &ep, float2 (&v)
     const int unmagic = zp - 0x4B400000;
 #pragma unroll
     for (int i = 0; i < NC; ++i) {
-      int q[32];
+      int q[CW];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        q[2 * u] = __float_as_int(__fadd_rn(fminf(fmaxf(v[16 * i + u].x, flo), fhi), 12582912.f)) + unmagic;
-        q[2 * u + 1] = __float_as_int(__fadd_rn(fminf(fmaxf(v[16 * i + u].y, flo), fhi), 12582912.f)) + unmagic;
+      for (int u = 0; u < CW / 2; ++u) {
+        q[2 * u] = __float_as_int(__fadd_rn(fminf(fmaxf(v[CW / 2 * i + u].x, flo), fhi), 12582912.f)) + unmagic;
+        q[2 * u + 1] = __float_as_int(__fadd_rn(fminf(fmaxf(v[CW / 2 * i + u].y, flo), fhi), 12582912.f)) + unmagic;
       }
-      uint32_t w[8];
+      uint32_t w[CW / 4];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      for (int u = 0; u < CW / 4; ++u) {
         const uint32_t lo2 = __byte_perm((uint32_t)q[4 * u], (uint32_t)q[4 * u + 1], 0x0040);      // bytes q0, q1
         const uint32_t hi2 = __byte_perm((uint32_t)q[4 * u + 2], (uint32_t)q[4 * u + 3], 0x0040);  // bytes q2, q3
         w[u] = __byte_perm(lo2, hi2, 0x5410);
       }
-      stage_units<2>(stage, w, slot + i);
+      stage_units<CW / 16>(stage, w, slot + i);
     }
   }
 }
-
-#ifdef SB200_ROLE_TIMERS
-// cycles thread 64 of CTA 0 spent in the parts of drain_accumulator (debug build only)
-__device__ long long g_drain_cycles[6];
-#define DRAIN_T0() const long long dt0__ = clock64()
-#define DRAIN_ADD(i) if (blockIdx.x == 0 && threadIdx.x == 64) g_drain_cycles[i] += clock64() - dt0__
-#else
-#define DRAIN_T0()
-#define DRAIN_ADD(i)
-#endif
 
 // Address of element (row0, col) of batch b of Y, in bytes.
 __device__ __forceinline__ uint8_t *y_address(const EpiParams &ep, long long b, long long row0, long long col) {
   return (uint8_t *)ep.Y + (b * ep.stride_y + row0 * ep.ldy + col) * out_elem_bytes(ep.y_dtype);
-}
-
-// One epilogue warp drains its share of a finished accumulator: the 32 tensor-memory lanes at `taddr` (lane = row
-// `row` of Y), columns [0, c_end) of the tile that starts at column n0 of Y.  Chunks of 32 columns are taken in
-// groups of chunks_per_flush() consecutive chunks (one 128-byte row segment); this warp takes groups first_group,
-// first_group + group_stride, ...  The tcgen05.ld of the next chunk is in flight while the current one goes through
-// the epilogue.
-//
-// With a tensor map of Y (`tm_y`, 128B swizzle, box = 128 bytes x 32 rows: exactly the staging buffer's layout, which
-// must then be 1024-byte aligned) a complete row segment leaves as ONE bulk tensor store issued by lane 0: the TMA
-// unit clips rows past the end, and the warp's load/store unit is out of the picture.  The buffer is reused only
-// after the store has read it (bulk_wait_read_all before the next group is staged, and before the function returns).
-template <bool ACC_INT>
-__device__ __forceinline__ void drain_accumulator(const EpiParams &ep, uint32_t taddr, int c_end, int first_group, int group_stride,
-                                                  long long b, long long row, int n0, bool vec, uint32_t stage, long long rows_total,
-                                                  const CUtensorMap *tm_y = nullptr) {
-  // chunks per flushed row segment: a whole 128-byte segment, or what the plan asked for (EpiParams::seg_chunks: a half or
-  // a quarter of it, the staging buffer's row pitch shrinking with it -- see stage_units)
-  const int G_full = chunks_per_flush(ep.y_dtype);
-  const int G = ep.seg_chunks > 0 && ep.seg_chunks < G_full ? ep.seg_chunks : G_full;
-  stage |= (G == G_full) ? 0u : (2 * G == G_full ? 1u : 2u);
-  const int seg_units = 8 * G / G_full;   // 16-byte units of a complete segment
-  const int units_per_chunk = 2 * out_elem_bytes(ep.y_dtype);
-  const int nch = (c_end + 31) >> 5;
-  const long long row0 = row - (threadIdx.x & 31);
-  const long long left = rows_total - row0;
-  const int rows_valid = left < 0 ? 0 : (left > 32 ? 32 : (int)left);
-  const bool fast = vec && ep.fast && rows_valid > 0;
-  int ch = first_group * G, j = 0;   // current chunk and its position in its group
-  if (ch >= nch) return;
-  int units = 0, seg_col = 0;
-  bool store_pending = false;
-  // One register buffer: the fast path reads the raw accumulator only in its first half, so the tcgen05.ld of the
-  // next chunks is issued into the same registers right after that and flies during the second half and the flush.
-  // Where a row segment is two or more chunks (2- and 1-byte outputs) two chunks go through the fast path TOGETHER:
-  // an epilogue warp is alone or nearly alone on its scheduler, and two independent 32-column chains in one
-  // instruction stream hide the latencies that one chain leaves exposed.
-  uint32_t raw[64];
-  auto &raw_lo = reinterpret_cast<uint32_t (&)[32]>(raw[0]);
-  auto &raw_hi = reinterpret_cast<uint32_t (&)[32]>(raw[32]);
-  // (Measured dead end, kept compiled out: two chunks through the fast path together need ~200 registers; a CTA of 10
-  // warps gets 168 per thread, and the spills cost more than the interleaving wins.)
-  constexpr bool kTwoChunks = false;
-  const bool pair_ok = kTwoChunks && fast && G >= 2;
-  auto chunks_now = [&](int ch_, int j_) { return (pair_ok && (j_ & 1) == 0 && c_end - 32 * ch_ >= 64) ? 2 : 1; };
-  auto issue_loads = [&](int ch_, int np_) {
-    ptx::tmem_ld_x32(taddr + 32 * ch_, raw_lo);
-    if (np_ == 2) ptx::tmem_ld_x32(taddr + 32 * ch_ + 32, raw_hi);
-  };
-  int np = chunks_now(ch, j);
-  issue_loads(ch, np);
-  while (true) {
-    { DRAIN_T0(); ptx::tmem_ld_wait(); DRAIN_ADD(0); }
-    int ch2 = ch + np, j2 = j + np;
-    if (j2 >= G) { j2 = 0; ch2 += (group_stride - 1) * G; }
-    const bool has_next = ch2 < nch;
-    const int np2 = has_next ? chunks_now(ch2, j2) : 1;
-    const int c = 32 * ch;
-    if (j == 0) {
-      units = 0; seg_col = c;
-      if (store_pending) {   // the previous segment's bulk store must have read the buffer before it is refilled
-        DRAIN_T0();
-        if ((threadIdx.x & 31) == 0) ptx::bulk_wait_read_all();
-        __syncwarp();
-        store_pending = false;
-        DRAIN_ADD(1);
-      }
-    }
-    { DRAIN_T0();
-      const long long rr = row < rows_total ? row : rows_total - 1;   // rows past the end compute on the last row's operands
-      if (np == 2) {
-        float2 v[32];
-        const bool more = epi_values_fast<ACC_INT, 2>(ep, raw, v, rr, n0 + c, stage, j);
-        if (has_next) issue_loads(ch2, np2);
-        if (more) epi_finish_fast<2>(ep, v, b, rr, n0 + c, stage, j);
-        units += 2 * units_per_chunk;
-      } else if (fast && c_end - c >= 32) {
-        float2 v[16];
-        const bool more = epi_values_fast<ACC_INT, 1>(ep, raw_lo, v, rr, n0 + c, stage, j);
-        if (has_next) issue_loads(ch2, np2);
-        if (more) epi_finish_fast<1>(ep, v, b, rr, n0 + c, stage, j);
-        units += units_per_chunk;
-      } else {
-        if (store_chunk(ep, raw_lo, b, row, n0 + c, min(32, c_end - c), vec, stage, rows_total, j)) units += units_per_chunk;
-        if (has_next) issue_loads(ch2, np2);
-      }
-      DRAIN_ADD(2); }
-    const int j_last = j + np - 1;
-    if ((j_last == G - 1 || !has_next) && units > 0) {
-      DRAIN_T0();
-      if (tm_y != nullptr && units == seg_units) {
-        ptx::fence_proxy_async();   // this lane's staging writes become visible to the TMA unit
-        __syncwarp();
-        if ((threadIdx.x & 31) == 0) {
-          ptx::tma_store_3d(tm_y, stage & ~3u, n0 + seg_col, (int)row0, (int)b);
-          ptx::bulk_commit_group();
-        }
-        store_pending = true;
-      } else {
-        flush_staged(stage, y_address(ep, b, row0, n0 + seg_col), ep.ldy * out_elem_bytes(ep.y_dtype), rows_valid, units);
-      }
-      DRAIN_ADD(3);
-    }
-    ch = ch2; j = j2; np = np2;
-    if (!has_next) break;
-  }
-  if (store_pending) {
-    DRAIN_T0();
-    if ((threadIdx.x & 31) == 0) ptx::bulk_wait_read_all();
-    __syncwarp();
-    DRAIN_ADD(4);
-  }
 }
 
 }  // namespace sb200
