@@ -68,13 +68,10 @@ struct UmmaParams {
                                    // products (4 loads per 12 MMAs instead of 6); stage byte counts are the doubled ones
   int b_rows;                      // N extent of the B slice one CTA stages (= bn)
   int kb_mmas;                     // MMAs (32 bytes of K each) per K block: 4, or 2 when a K block is 64 bytes
+  int prod_lanes;                  // TMA producer lanes per producer warp (1 to 4)
+  int b_resident;                  // all K blocks of operand B stay in shared memory (tiles_n == 1); the ring holds A only
   int accs;                        // accumulators in tensor memory: 2 or 4
   int teams;                       // teams of epilogue warps, each draining a tile of its own: 1, 2 or 4, at most accs
-  int two_producers;               // operand B is loaded by a thread of its own (warp UMMA_B_PRODUCER_WARP): a thread is held by
-                                   // every TMA instruction until the unit takes it, and with 8-bit operands one thread issuing
-                                   // both operands' loads was the slowest stage of the pipeline
-  // Implicit convolution: A is a channels-last image tensor read through an im2col-mode tensor map; row m of A is output
-  // pixel m (image, then row, then column) and K block kb is (filter tap kb / ic_cblocks, channel block kb % ic_cblocks).
   int im2col;
   int ic_wo, ic_pix;               // output width, output pixels per image
   int ic_sw, ic_sh, ic_pl, ic_pt;  // strides; left and top padding

@@ -77,12 +77,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   const int stages = p.stages;
   const uint32_t smem_a = smem_u32(smem);
   const uint32_t smem_b = smem_a + stages * p.a_stage_bytes;
-  uint8_t *tail = smem + stages * (p.a_stage_bytes + p.b_stage_bytes);
+  // operand B: a ring like A's, or -- resident -- all its K blocks, loaded once (tiles_n == 1: every tile uses the same B)
+  const int b_slots = p.b_resident ? p.num_kb : stages;
+  uint8_t *tail = smem + stages * p.a_stage_bytes + b_slots * p.b_stage_bytes;
   const uint32_t bar_full = smem_u32(tail);             // [stages]
   const uint32_t bar_empty = bar_full + 8 * stages;     // [stages]
   const uint32_t bar_tfull = bar_empty + 8 * stages;    // [UMMA_MAX_ACCS]
   const uint32_t bar_tempty = bar_tfull + 8 * UMMA_MAX_ACCS;   // [UMMA_MAX_ACCS]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail + 16 * stages + 16 * UMMA_MAX_ACCS);
+  const uint32_t bar_bres = bar_tempty + 8 * UMMA_MAX_ACCS;    // resident operand B has landed
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tail + 16 * stages + 16 * UMMA_MAX_ACCS + 8);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
   const uint32_t epi_stage = smem_u32(tail) + UMMA_TAIL_BYTES;   // UMMA_EPI_STAGE_BYTES per epilogue warp
 
@@ -91,13 +94,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(bar_full + 8 * s, p.two_producers ? 2 : 1);   // one arrival (with its byte count) per producer
+      mbar_init(bar_full + 8 * s, p.b_resident ? 1 : 2);   // one arrival (with its byte count) per operand that is loaded into the ring
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int i = 0; i < p.accs; ++i) {
       mbar_init(bar_tfull + 8 * i, 1);
       mbar_init(bar_tempty + 8 * i, UMMA_EPI_WARPS / p.teams);  // one arrival per epilogue warp of the team that drains it
     }
+    mbar_init(bar_bres, 1);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tm_a);
@@ -118,74 +122,89 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
   if (warp == 0 || warp == UMMA_B_PRODUCER_WARP) {
     // ------------------------------ TMA producers -----------------------------------
-    // warp 0 loads operand A, warp UMMA_B_PRODUCER_WARP operand B (or warp 0 both, and the other warp idles)
-    const bool do_a = warp == 0, do_b = p.two_producers ? warp != 0 : warp == 0;
-    if (lane == 0 && (do_a || do_b)) {
-      uint32_t stage = 0, phase = 0;
-      bool ok = true;
-      ROLE_TIMER(w_empty);
-      ROLE_TIMER(c_expect);
-      ROLE_TIMER(c_load_a);
-      ROLE_TIMER(c_load_b);
-      ROLE_TIMER(sec_t0);
-      ROLE_TIMER(t_begin);
-#ifdef SB200_ROLE_TIMERS
-      t_begin = clock64();
-#endif
-      for (uint32_t w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
-        uint32_t t; int n_off, n_len; uint32_t idesc;
-        decode_item(p, w, t, n_off, n_len, idesc);
-        int b, tm, tn;
-        tile_coords(p, t, tiles_per_batch, b, tm, tn);
-        const int m0 = tm * UMMA_BM;
-        const int n0 = tn * p.bn + n_off;  // a half item still loads a full-width B slice
-        const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
-        // implicit convolution: the tile's first output pixel -> image and base pixel (tap (0, 0)) of its filter window
-        int ic_n = 0, ic_w = 0, ic_h = 0, tap_r = 0, tap_s = 0, cb = 0;
-        if (p.im2col) {
-          ic_n = m0 / p.ic_pix;
-          const int rem = m0 - ic_n * p.ic_pix, oh = rem / p.ic_wo;
-          ic_h = oh * p.ic_sh - p.ic_pt;
-          ic_w = (rem - oh * p.ic_wo) * p.ic_sw - p.ic_pl;
+    // Warp 0 loads operand A; warp UMMA_B_PRODUCER_WARP loads operand B, or -- B resident -- loads it once and then takes
+    // a share of A.  The K blocks of all of this CTA's tiles form one sequence, and an operand's `PT` producer lanes (the
+    // first p.prod_lanes lanes of its one or two warps) take every PT-th block of it, in lockstep: what a thread does between
+    // two TMA instructions (barrier wait, byte count, coordinates: a few hundred cycles for one thread) is time the TMA unit
+    // idles, so one thread per operand capped a convolution with 64-byte K blocks at 60 % of the unit's rate.
+    const bool b_warp = warp != 0;
+    if (lane == 0 && p.b_resident && b_warp) {
+      // resident operand B: every K block once, one barrier for all of them
+      mbar_arrive_expect_tx(bar_bres, (uint32_t)p.num_kb * p.b_stage_bytes);
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        const uint32_t sb = smem_b + kb * p.b_stage_bytes;
+        const int k0 = kb * p.kb_elems;
+        if (!p.b_mn) {
+          tma_load_3d(sb, &tm_b, bar_bres, k0, 0, 0);
+        } else {
+          for (int x = 0; x < p.b_boxes; ++x) tma_load_3d(sb + x * p.b_box_bytes, &tm_b, bar_bres, x * p.b_box_mn, k0, 0);
         }
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!ROLE_WAIT(w_empty, mbar_wait_relaxed(bar_empty + 8 * stage, phase ^ 1u, abort_flag))) {
-            raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_EMPTY);
-            ok = false;
-            break;
+      }
+    }
+    __syncwarp();
+    const bool load_b = b_warp && !p.b_resident;     // this warp's operand
+    const int PL = p.prod_lanes;
+    const int PT = (!load_b && p.b_resident) ? 2 * PL : PL;   // producer lanes of this warp's operand, over all its warps
+    const int pi = lane + ((b_warp && p.b_resident) ? PL : 0);
+    if (lane < PL) {
+      // this lane's position in the sequence of K blocks: work item w, K block kbi of it, ring stage and its phase
+      uint32_t w = blockIdx.x, stage = (uint32_t)pi, phase = 0;
+      int kbi = pi;
+      bool ok = true, fresh = true;
+      int m0 = 0, n0 = 0, ba = 0, bb = 0, ic_n = 0, ic_w = 0, ic_h = 0;
+      while (true) {
+        while (kbi >= p.num_kb) { kbi -= p.num_kb; w += gridDim.x; fresh = true; }
+        if (w >= num_items) break;
+        if (fresh) {
+          fresh = false;
+          uint32_t t; int n_off, n_len; uint32_t idesc;
+          decode_item(p, w, t, n_off, n_len, idesc);
+          int b, tm, tn;
+          tile_coords(p, t, tiles_per_batch, b, tm, tn);
+          m0 = tm * UMMA_BM;
+          n0 = tn * p.bn + n_off;  // a half item still loads a full-width B slice
+          ba = p.a_bcast ? 0 : b; bb = p.b_bcast ? 0 : b;
+          if (p.im2col) {
+            // implicit convolution: the tile's first output pixel -> image and base pixel (tap (0, 0)) of its filter window
+            ic_n = m0 / p.ic_pix;
+            const int rem = m0 - ic_n * p.ic_pix, oh = rem / p.ic_wo;
+            ic_h = oh * p.ic_sh - p.ic_pt;
+            ic_w = (rem - oh * p.ic_wo) * p.ic_sw - p.ic_pl;
           }
-          const uint32_t full = bar_full + 8 * stage;
-          ROLE_SECTION_BEGIN();
-          mbar_arrive_expect_tx(full, (do_a ? p.a_stage_bytes : 0u) + (do_b ? p.b_stage_bytes : 0u));
-          ROLE_SECTION_END(c_expect);
-          const int k0 = kb * p.kb_elems;
+        }
+        if (!mbar_wait_relaxed(bar_empty + 8 * stage, phase ^ 1u, abort_flag)) {
+          raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_EMPTY);
+          ok = false;
+          break;
+        }
+        const uint32_t full = bar_full + 8 * stage;
+        const int k0 = kbi * p.kb_elems;
+        if (!load_b) {
+          mbar_arrive_expect_tx(full, p.a_stage_bytes);
           const uint32_t sa = smem_a + stage * p.a_stage_bytes;
-          const uint32_t sb = smem_b + stage * p.b_stage_bytes;
-          ROLE_SECTION_BEGIN();
-          if (!do_a) {
-          } else if (p.im2col) {
+          if (p.im2col) {
+            const int tap = kbi / p.ic_cblocks, cb = kbi - tap * p.ic_cblocks, tap_r = tap / p.ic_s, tap_s = tap - tap_r * p.ic_s;
             tma_load_im2col_4d(sa, &tm_a, full, cb * p.kb_elems, ic_w, ic_h, ic_n, (uint16_t)(tap_s * p.ic_dw), (uint16_t)(tap_r * p.ic_dh));
-            if (++cb == p.ic_cblocks) { cb = 0; if (++tap_s == p.ic_s) { tap_s = 0; ++tap_r; } }
           } else if (!p.a_mn) {
             tma_load_3d(sa, &tm_a, full, k0, m0, ba);
           } else {
             for (int x = 0; x < p.a_boxes; ++x)
               tma_load_3d(sa + x * p.a_box_bytes, &tm_a, full, m0 + x * p.a_box_mn, k0, ba);
           }
-          ROLE_SECTION_END(c_load_a);
-          ROLE_SECTION_BEGIN();
-          if (!do_b) {
-          } else if (!p.b_mn) {
+        } else {
+          mbar_arrive_expect_tx(full, p.b_stage_bytes);
+          const uint32_t sb = smem_b + stage * p.b_stage_bytes;
+          if (!p.b_mn) {
             tma_load_3d(sb, &tm_b, full, k0, n0, bb);
           } else {
             for (int x = 0; x < p.b_boxes; ++x)
               tma_load_3d(sb + x * p.b_box_bytes, &tm_b, full, n0 + x * p.b_box_mn, k0, bb);
           }
-          ROLE_SECTION_END(c_load_b);
-          if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
         }
+        kbi += PT;
+        stage += (uint32_t)PT;
+        if (stage >= (uint32_t)stages) { stage -= (uint32_t)stages; phase ^= 1u; }
       }
-      ROLE_REPORT("[cta %d] producer: total %lld, waiting for a free stage %lld, expect_tx %lld, issuing A loads %lld, B loads %lld\n", blockIdx.x, clock64() - t_begin, w_empty, c_expect, c_load_a, c_load_b);
       if (!ok) {
         // give copies that may still be in flight time to land before the CTA exits
         const uint64_t t0 = globaltimer();
@@ -215,6 +234,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #ifdef SB200_ROLE_TIMERS
       t_begin = clock64();
 #endif
+      if (p.b_resident && !mbar_wait(bar_bres, 0u, abort_flag)) {
+        raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_FULL);
+        ok = false;
+      }
       for (uint32_t w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
         uint32_t t; int n_off, n_len; uint32_t idesc;
         decode_item(p, w, t, n_off, n_len, idesc);
@@ -234,14 +257,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           tc_fence_after();
           ROLE_SECTION_END(c_fence);
           const uint32_t a_lo = a_lo0 + stage * a_step;
-          const uint32_t b_lo = b_lo0 + stage * b_step;
+          const uint32_t b_lo = b_lo0 + (p.b_resident ? (uint32_t)kb : stage) * b_step;
           ROLE_SECTION_BEGIN();
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             if (k >= kb_mmas) break;
             const uint64_t ad = a_hi | (uint64_t)(a_lo + k * a_kadv);
             const uint64_t bd = b_hi | (uint64_t)(b_lo + k * b_kadv);
+#ifndef SB200_SKIP_MMA
             umma<KIND>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+#endif
           }
           ROLE_SECTION_END(c_mma);
           ROLE_SECTION_BEGIN();
@@ -298,7 +323,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const int row = m0 + quad * 32 + lane;
       const int c_end = min(n_len, p.N - n0);          // columns of this item that exist (warp-uniform)
       ROLE_SECTION_BEGIN();
+#ifndef SB200_SKIP_EPI
       drain16_any<KIND == KIND_I8>(p.ep, ew, taddr, c_end, seg_first, groups_per_team, b, row, n0, p.vec_ok != 0, p.M, y_map);
+#endif
       ROLE_SECTION_END(c_st);
       tc_fence_before();
       __syncwarp();
@@ -476,7 +503,6 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   // Measured faster in every shape, two-stage ring included (8192^3: 6.6 -> 6.05 ms).
   u.fused3 = plan->promote ? 1 : 0;
   if (u.fused3) { u.a_stage_bytes *= 2; u.b_stage_bytes *= 2; }
-  u.two_producers = 1;
   u.im2col = ic.on;
   if (ic.on) {
     u.ic_wo = (int)ic.Wo; u.ic_pix = (int)(ic.Ho * ic.Wo);
@@ -511,11 +537,25 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
 
   const size_t epi_bytes = 32 * 1024;   // staging buffers of the epilogue warps (16 x 2 KB; the promotion kernel's 8 x 4 KB)
   const size_t budget = 227 * 1024 - 1024 /*alignment*/ - UMMA_TAIL_BYTES /*barriers*/ - epi_bytes;
-  int stages = (int)(budget / (u.a_stage_bytes + u.b_stage_bytes));
+  // Resident operand B: where one tile spans all of N and every batch uses the same B (the filters of a convolution with
+  // few output channels, a narrow weight matrix), all K blocks of B stay in shared memory for the whole kernel and the
+  // ring holds operand A only.  The TMA unit takes about two cycles per 64- or 128-byte row it moves, so with short K
+  // rows a tile's operand loads, not its MMAs, set the pace, and B's rows are a third to a half of them.
+  u.b_resident = 0;
+  const size_t b_all = (size_t)u.num_kb * u.b_stage_bytes;
+  if (!plan->promote && u.tiles_n == 1 && (d.batch == 1 || (d.batch > 1 && d.stride_b == 0)) && b_all + 6 * (size_t)u.a_stage_bytes <= budget &&
+      b_all < (1u << 20))
+    u.b_resident = 1;
+  int stages = u.b_resident ? (int)((budget - b_all) / u.a_stage_bytes) : (int)(budget / (u.a_stage_bytes + u.b_stage_bytes));
   if (stages > (kb_bytes == 64 ? 12 : 8)) stages = kb_bytes == 64 ? 12 : 8;
   if (stages < 2) return 1;
   u.stages = stages;
-  plan->smem_bytes = (size_t)stages * (u.a_stage_bytes + u.b_stage_bytes) + 1024 + UMMA_TAIL_BYTES + epi_bytes;
+  // producer lanes per warp: an operand's lanes together hold at most half the ring, so that the MMAs never wait for a
+  // lane that is itself waiting for a stage
+  u.prod_lanes = stages / (u.b_resident ? 4 : 2);
+  if (u.prod_lanes > 4) u.prod_lanes = 4;
+  if (u.prod_lanes < 1) u.prod_lanes = 1;
+  plan->smem_bytes = (size_t)stages * u.a_stage_bytes + (u.b_resident ? b_all : (size_t)stages * u.b_stage_bytes) + 1024 + UMMA_TAIL_BYTES + epi_bytes;
 
   u.a_mn = d.trans_a ? 1 : 0;   // stored [K,M]: M contiguous
   u.b_mn = d.trans_b ? 0 : 1;   // stored [K,N]: N contiguous
@@ -559,7 +599,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.split_from = u.num_tiles;
   u.num_items = u.num_tiles;
   u.idesc_half = (u.idesc & ~(0x3fu << 17)) | ((uint32_t)(u.bn >> 4) << 17);
-  if (!plan->promote && u.bn >= 64 && u.num_tiles > sms) {
+  if (!plan->promote && !u.b_resident && u.bn >= 64 && u.num_tiles > sms) {
     const long long tail = u.num_tiles % sms;
     if (tail > 0 && 2 * tail <= sms) {
       u.split_from = u.num_tiles - tail;

@@ -79,14 +79,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
-// The same for a wait that is usually long (a producer ahead of the consumer, the issuer ahead of the epilogue): polls
-// with a suspend-time hint, and so looks at the clock on every 16th failed poll.
+// The same for a wait that is usually long (a producer ahead of the consumer, the issuer ahead of the epilogue, epilogue
+// warps with no finished accumulator): after the first failed poll the warp SLEEPS between polls, 32 ns doubling to 256 ns.
+// A polling warp issues an instruction every few cycles; sixteen epilogue warps polling for an accumulator took the issue
+// slots that the single-thread producer and issuer roles on the same schedulers needed, and made operand-bound tiles slower.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                                   uint64_t limit_ns = 1000000000ull) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
+  uint32_t ns = 32;
   for (uint32_t it = 0;; ++it) {
-    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+    if (mbar_try_wait_hint(bar, parity, 1000u)) return true;
+    __nanosleep(ns);
+    if (ns < 256) ns <<= 1;
     if ((it & 15u) == 15u) {
       if (*abort_flag) return false;
       uint64_t now = globaltimer();

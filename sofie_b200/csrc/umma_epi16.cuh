@@ -35,6 +35,8 @@ __device__ __forceinline__ uint32_t epi16_flags(const EpiParams &ep) {
   return f;
 }
 
+constexpr uint32_t EPI16_DYNAMIC = 0x80000000u;
+
 enum { OUT16_F32 = 0, OUT16_BF16 = 1, OUT16_I8 = 2, OUT16_U8 = 3, OUT16_I32 = 4 };
 __device__ __forceinline__ int out16_class(int y_dtype) {
   return y_dtype == SOFIE_B200_F32 ? OUT16_F32 : y_dtype == SOFIE_B200_BF16 ? OUT16_BF16 : y_dtype == SOFIE_B200_I8 ? OUT16_I8
@@ -71,51 +73,50 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-// rint(v) + zp, saturated to the 8-bit output type, for four values -> four bytes (v0 lowest).  v + 1.5 * 2^23 holds
-// rint(v) in its low mantissa bits for |v| < 2^22 and is monotonic in v beyond that, as are the bits of a float read as a
-// signed integer; the saturating subtraction takes the exponent bits away and adds the zero point, and the packing
-// conversion saturates to [-128, 127] or [0, 255].  Full-rate instructions only.  (A NaN lands on a bound.)
+// rint(v) + zp, saturated to the 8-bit output type, for four values -> four bytes (v0 lowest).  v is first bounded below
+// by -2^22 (which also sends a NaN there, as the float formula's saturation does); then v + 1.5 * 2^23 holds rint(v) in
+// its low mantissa bits for |v| < 2^22 and is monotonic in v above that, as are the bits of a positive float read as an
+// integer; the integer addition takes the exponent bits away and adds the zero point, and the packing conversion
+// saturates to [-128, 127] or [0, 255].  Full-rate instructions only: 2.5 per element.  (A saturating integer subtraction
+// instead of the lower bound costs eight instructions: the target has none.)
 template <bool SIGNED>
 __device__ __forceinline__ uint32_t quantize4(float2 lo, float2 hi, int unmagic) {
   const float2 m = dup2(12582912.f);
-  const float2 a = fadd2(lo, m), b = fadd2(hi, m);
+  const float2 a = fadd2(make_float2(fmaxf(lo.x, -4194304.f), fmaxf(lo.y, -4194304.f)), m);
+  const float2 b = fadd2(make_float2(fmaxf(hi.x, -4194304.f), fmaxf(hi.y, -4194304.f)), m);
+  const int q0 = __float_as_int(a.x) - unmagic, q1 = __float_as_int(a.y) - unmagic, q2 = __float_as_int(b.x) - unmagic, q3 = __float_as_int(b.y) - unmagic;
   uint32_t out;
   if (SIGNED) {
     asm("{\n"
-        ".reg .s32 q0, q1, q2, q3;\n"
         ".reg .b32 h;\n"
-        "sub.sat.s32 q0, %1, %5;\n"
-        "sub.sat.s32 q1, %2, %5;\n"
-        "sub.sat.s32 q2, %3, %5;\n"
-        "sub.sat.s32 q3, %4, %5;\n"
-        "cvt.pack.sat.s8.s32.b32 h, q3, q2, 0;\n"
-        "cvt.pack.sat.s8.s32.b32 %0, q1, q0, h;\n"
+        "cvt.pack.sat.s8.s32.b32 h, %4, %3, 0;\n"
+        "cvt.pack.sat.s8.s32.b32 %0, %2, %1, h;\n"
         "}\n"
         : "=r"(out)
-        : "r"(__float_as_int(a.x)), "r"(__float_as_int(a.y)), "r"(__float_as_int(b.x)), "r"(__float_as_int(b.y)), "r"(unmagic));
+        : "r"(q0), "r"(q1), "r"(q2), "r"(q3));
   } else {
     asm("{\n"
-        ".reg .s32 q0, q1, q2, q3;\n"
         ".reg .b32 h;\n"
-        "sub.sat.s32 q0, %1, %5;\n"
-        "sub.sat.s32 q1, %2, %5;\n"
-        "sub.sat.s32 q2, %3, %5;\n"
-        "sub.sat.s32 q3, %4, %5;\n"
-        "cvt.pack.sat.u8.s32.b32 h, q3, q2, 0;\n"
-        "cvt.pack.sat.u8.s32.b32 %0, q1, q0, h;\n"
+        "cvt.pack.sat.u8.s32.b32 h, %4, %3, 0;\n"
+        "cvt.pack.sat.u8.s32.b32 %0, %2, %1, h;\n"
         "}\n"
         : "=r"(out)
-        : "r"(__float_as_int(a.x)), "r"(__float_as_int(a.y)), "r"(__float_as_int(b.x)), "r"(__float_as_int(b.y)), "r"(unmagic));
+        : "r"(q0), "r"(q1), "r"(q2), "r"(q3));
   }
   return out;
 }
 
 // One 16-column step of the fast path: raw accumulator -> output type -> staging buffer, at position `j` of the row
 // segment.  The next step's accumulator columns are requested into `raw` as soon as `raw` is dead.
-template <bool ACC_INT, int OUT>
+//
+// FL: the plan's EPI16_* mask as a compile-time constant, or EPI16_DYNAMIC to read it from `w`.  With the mask in a
+// register the compiler turns the short optional parts into predicated code, and a predicated-off instruction still
+// takes its issue slot: a step with only alpha set executed the loads and arithmetic of every other part as well, half
+// of its instructions.  The masks of the common epilogues are therefore instantiated (drain16_any picks per tile).
+template <bool ACC_INT, int OUT, uint32_t FL>
 __device__ __forceinline__ void epi16_step(const EpiParams &ep, const Epi16Warp &w, uint32_t (&raw)[16], uint32_t next_taddr, bool has_next,
                                            long long b, long long rr, int col0, int j) {
-  const uint32_t fl = w.fl;
+  const uint32_t fl = FL == EPI16_DYNAMIC ? w.fl : FL;
   constexpr int UNITS = OUT == OUT16_BF16 ? 2 : (OUT == OUT16_I8 || OUT == OUT16_U8) ? 1 : 4;   // 16-byte units per step
   const uint32_t o0 = ((uint32_t)(j * UNITS * 16)) ^ w.row_xor;
   if (ACC_INT) {
@@ -258,7 +259,7 @@ __device__ __forceinline__ void epi16_step(const EpiParams &ep, const Epi16Warp 
 // layout) a complete row segment leaves as ONE bulk tensor store issued by lane 0: the TMA unit clips rows past the end.
 // The buffer is reused only after the store has read it (bulk_wait_read_all before the next segment is staged, and before
 // the function returns).
-template <bool ACC_INT, int OUT>
+template <bool ACC_INT, int OUT, uint32_t FL>
 __device__ __forceinline__ void drain16(const EpiParams &ep, const Epi16Warp &w, uint32_t taddr, int c_end, int first_group, int group_stride,
                                         long long b, long long row, int n0, bool vec, long long rows_total, const CUtensorMap *tm_y) {
   const int G = w.steps_per_seg;
@@ -291,7 +292,7 @@ __device__ __forceinline__ void drain16(const EpiParams &ep, const Epi16Warp &w,
     }
     ptx::tmem_ld_wait();
     if (fast && c_end - c >= 16) {
-      epi16_step<ACC_INT, OUT>(ep, w, raw, taddr + 16 * st2, has_next, b, rr, n0 + c, j);
+      epi16_step<ACC_INT, OUT, FL>(ep, w, raw, taddr + 16 * st2, has_next, b, rr, n0 + c, j);
       units += UNITS;
     } else {
       if (store_chunk<16>(ep, raw, b, row, n0 + c, min(16, c_end - c), vec, w.stage, rows_total, j)) units += UNITS;
@@ -319,16 +320,39 @@ __device__ __forceinline__ void drain16(const EpiParams &ep, const Epi16Warp &w,
   }
 }
 
+// drain16 with the plan's mask as a constant where it is one of the common ones, else with the mask in a register.
+template <bool ACC_INT, int OUT>
+__device__ __forceinline__ void drain16_masks(const EpiParams &ep, const Epi16Warp &w, uint32_t taddr, int c_end, int first_group, int group_stride,
+                                              long long b, long long row, int n0, bool vec, long long rows_total, const CUtensorMap *tm_y) {
+#define SB200_DRAIN16(MASK)                                                                                                  \
+  if (w.fl == (MASK)) return drain16<ACC_INT, OUT, (MASK)>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y)
+  if (ACC_INT && (OUT == OUT16_I8 || OUT == OUT16_BF16)) {
+    SB200_DRAIN16(EPI16_ALPHA);                                   // QLinearMatMul with per-tensor scales
+    SB200_DRAIN16(EPI16_CS | EPI16_BI);                           // QLinearConv
+    SB200_DRAIN16(EPI16_CS | EPI16_BI | EPI16_ACT);               // ... with a fused activation
+  }
+  if (!ACC_INT && OUT == OUT16_BF16) {
+    SB200_DRAIN16(0u);
+    SB200_DRAIN16(EPI16_ALPHA);
+    SB200_DRAIN16(EPI16_CS | EPI16_BF);                           // dequantised weights, bias
+    SB200_DRAIN16(EPI16_CS | EPI16_BF | EPI16_ACT);
+    SB200_DRAIN16(EPI16_CS | EPI16_BF | EPI16_RES);
+    SB200_DRAIN16(EPI16_RS | EPI16_CS | EPI16_BF | EPI16_ACT);    // FP8 with row and column scales
+  }
+#undef SB200_DRAIN16
+  drain16<ACC_INT, OUT, EPI16_DYNAMIC>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y);
+}
+
 template <bool ACC_INT>
 __device__ __forceinline__ void drain16_any(const EpiParams &ep, const Epi16Warp &w, uint32_t taddr, int c_end, int first_group, int group_stride,
                                             long long b, long long row, int n0, bool vec, long long rows_total, const CUtensorMap *tm_y) {
   switch (w.out_class) {
-    case OUT16_F32: drain16<ACC_INT, OUT16_F32>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y); break;
-    case OUT16_BF16: drain16<ACC_INT, OUT16_BF16>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y); break;
-    case OUT16_I8: drain16<ACC_INT, OUT16_I8>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y); break;
-    case OUT16_U8: drain16<ACC_INT, OUT16_U8>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y); break;
+    case OUT16_F32: drain16_masks<ACC_INT, OUT16_F32>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y); break;
+    case OUT16_BF16: drain16_masks<ACC_INT, OUT16_BF16>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y); break;
+    case OUT16_I8: drain16_masks<ACC_INT, OUT16_I8>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y); break;
+    case OUT16_U8: drain16_masks<ACC_INT, OUT16_U8>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y); break;
     default:
-      if (ACC_INT) drain16<true, OUT16_I32>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y);
+      if (ACC_INT) drain16_masks<true, OUT16_I32>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y);
       break;
   }
 }
