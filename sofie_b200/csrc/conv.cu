@@ -568,7 +568,7 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   p->kdim = p->cg * d.R * d.S;
   const int64_t vec = 16 / es;
   p->kpad = (p->kdim + vec - 1) / vec * vec;
-  if (d.groups == 1 && d.C == 3 && d.R == 3 && d.S == 3 && d.x_layout == 0 && d.K <= 256 &&
+  if (d.groups == 1 && d.C == 3 && d.R == 3 && d.S == 3 && d.x_layout == 0 && d.K <= 256 && !(d.flags & SOFIE_B200_CONV_UNFOLD) &&
       direct_smem_bytes(d, p->pix_rows, p->pair_out) <= kDirectSmemLimit) {
     // the 3-channel first layer: direct kernel (see conv_direct_kernel); the plan only keeps the padded weights
     p->direct = 1;

@@ -352,12 +352,14 @@ __device__ __forceinline__ float2 gelu_erf_pair_lowp(float2 x) {
   p = ffma2(p, z, dup2(0.0705230784f));
   p = ffma2(p, z, dup2(1.0f));
   p = fmul2(p, p); p = fmul2(p, p); p = fmul2(p, p); p = fmul2(p, p);   // ^16 (overflows to inf for |x| > ~25: erf = 1)
-  float r0, r1;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(p.x));
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(p.y));
-  const float2 e = make_float2(copysignf(1.f - r0, x.x), copysignf(1.f - r1, x.y));   // erf(x/sqrt(2))
+  float2 r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.x) : "f"(p.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(p.y));
+  // 0.5 x (1 + sign(x) (1 - r)) = (h + |h|) - |h| r with h = x / 2: no sign transfer; h + |h| = max(x, 0) exactly, so a
+  // negative x, whose Gelu is the small number -|h| r, loses nothing to cancellation
   const float2 h = fmul2(x, dup2(0.5f));
-  return ffma2(h, e, h);   // 0.5 x (1 + erf)
+  const float2 nha = make_float2(-fabsf(h.x), -fabsf(h.y));
+  return ffma2(nha, r, make_float2(fmaxf(x.x, 0.f), fmaxf(x.y, 0.f)));
 }
 
 // First half of the fast path: everything that reads the raw accumulator -- integer bias, conversion, the three
