@@ -88,10 +88,11 @@ class ConvNetB200:
     @property
     def launches(self) -> int:
         """Kernels one call enqueues: per convolution 1 (direct first layer; implicit convolution "umma_im2col"), else an
-        unfold and a contraction plus, for an NCHW input, its channels-last copy; then the pool and the classifier."""
+        unfold and a contraction plus, for an NCHW input of whole 16-byte channel vectors, its channels-last copy (the
+        3-channel first layer unfolds straight from NCHW); then the pool and the classifier."""
         n = 2
-        for kern, xl in zip(self.kernels, self.x_layouts):
-            n += 1 if kern in ("direct", "umma_im2col", "umma3x_im2col") else (2 if xl else 3)
+        for i, (kern, xl) in enumerate(zip(self.kernels, self.x_layouts)):
+            n += 1 if kern in ("direct", "umma_im2col", "umma3x_im2col") else (2 if xl or i == 0 else 3)
         return n
 
     def __init__(self, ctx, weights, batch: int, img: int, int8: bool, device: str, channels_last: bool = True):

@@ -25,6 +25,7 @@ struct sofie_b200_conv_plan {
   int nhwc = 0;                // channels-last unfold: the input is first transposed to [N, H, W, C] in the workspace and K runs
                                // (r, s, c), so every 16-byte chunk of the unfolded matrix is one aligned vector copy
   int pair_out = 0;            // y_layout = 2: Y is channels-last TF32 pairs, [N, Ho, Wo, 2K]
+  int stem = 0;                // 3-channel 3x3 int8 first layer with a channels-last output: unfold_c3k3_kernel + tensor-core contraction
   int implicit = 0;            // channels-last in and out on the tensor cores with no unfolded copy: the contraction's TMA producer reads
                                // the input tensor itself in im2col mode (gemm_umma.cu); no workspace
   sofie_b200_gemm_plan *gemm = nullptr;
@@ -234,6 +235,57 @@ __global__ void __launch_bounds__(256) unfold_nhwc_kernel(const T *__restrict__ 
       *reinterpret_cast<uint4 *>(o) = *reinterpret_cast<const uint4 *>(hi);
       *reinterpret_cast<uint4 *>(o + kpad) = *reinterpret_cast<const uint4 *>(lo);
     }
+  }
+}
+
+// ---- 3-channel 3x3 first layer on the tensor cores ------------------------------------------------------------------
+// K = 27 is less than one MMA K step, so as a contraction this layer is all epilogue; the tensor-core kernel's epilogue
+// still writes 8-bit outputs several times faster than CUDA-core dot products do.  The unfolded matrix is [pixels][32]
+// bytes (K order (c, r, s) as the weights are stored, five bytes of padding): one thread gathers the 27 inputs of its
+// output pixel -- neighbouring lanes read neighbouring bytes of the same input rows -- and writes its row as two 16-byte
+// stores, so a warp writes 1 KB of consecutive memory.
+__global__ void __launch_bounds__(256) unfold_c3k3_kernel(const int8_t *__restrict__ x, uint4 *__restrict__ xcol, sofie_b200_conv_desc d, int Ho, int Wo) {
+  const long long pix = (long long)Ho * Wo, total = d.N * pix;
+  const long long gp = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gp >= total) return;
+  const long long n = gp / pix;
+  const int p = (int)(gp - n * pix), oh = p / Wo, ow = p - oh * Wo;
+  const int ih0 = oh * d.stride_h - d.pad_top, iw0 = ow * d.stride_w - d.pad_left;
+  const int H = (int)d.H, Wd = (int)d.W;
+  const int8_t *xn = x + n * 3 * H * Wd;
+  uint32_t w[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll
+  for (int c = 0; c < 3; ++c)
+#pragma unroll
+    for (int r = 0; r < 3; ++r)
+#pragma unroll
+      for (int s2 = 0; s2 < 3; ++s2) {
+        const int k = (c * 3 + r) * 3 + s2;
+        const int ih = ih0 + r * d.dil_h, iw = iw0 + s2 * d.dil_w;
+        const int8_t v = (ih >= 0 && ih < H && iw >= 0 && iw < Wd) ? xn[((long long)c * H + ih) * Wd + iw] : (int8_t)d.x_zero_point;
+        w[k >> 2] |= (uint32_t)(uint8_t)v << (8 * (k & 3));
+      }
+  xcol[2 * gp] = make_uint4(w[0], w[1], w[2], w[3]);
+  xcol[2 * gp + 1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+// ---- stride-2 implicit convolution over pixel pairs -------------------------------------------------------------------
+// A pixel of 64 bytes is half a 128-byte K block, and the TMA unit spends its time per ROW it moves, not per byte: a layer
+// with 64 int8 channels loaded nine 64-byte rows per output pixel at a quarter of the bandwidth 128-byte rows reach.  With a
+// horizontal stride of 2 (3 taps, left padding 1) the channels-last input [N, H, W, C] is read as [N, H, W/2, 2C] instead:
+// output column ow needs input columns 2ow-1, 2ow, 2ow+1 = the upper half of pair ow-1 and both halves of pair ow, i.e. a
+// two-tap, unit-stride convolution over pairs with zero weights for the lower half of the first tap.  Six 128-byte rows per
+// output pixel instead of nine 64-byte ones; a third more MMA work, which this layer has to spare.
+// Filters [K, C, R, 3] -> [K][R][2][2C].
+template <typename T>
+__global__ void __launch_bounds__(256) pair_weights_kernel(const T *__restrict__ w, T *__restrict__ out, long long filters, int C, int R) {
+  const long long per = (long long)R * 2 * 2 * C, total = filters * per;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long k = i / per;
+    const int rem = (int)(i - k * per), r = rem / (4 * C), sp = (rem / (2 * C)) & 1, cc = rem % (2 * C);
+    const int c = cc % C, upper = cc / C;
+    const int s = sp == 0 ? (upper ? 0 : -1) : (upper ? 2 : 1);   // original tap, -1: no such tap (zero weight)
+    out[i] = s < 0 ? (T)0 : w[((k * C + c) * R + r) * 3 + s];
   }
 }
 
@@ -568,7 +620,12 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
   p->kdim = p->cg * d.R * d.S;
   const int64_t vec = 16 / es;
   p->kpad = (p->kdim + vec - 1) / vec * vec;
-  if (d.groups == 1 && d.C == 3 && d.R == 3 && d.S == 3 && d.x_layout == 0 && d.K <= 256 && !(d.flags & SOFIE_B200_CONV_UNFOLD) &&
+  // The int8 first layer with a channels-last output goes to the tensor cores once there are enough output pixels to fill
+  // the machine with 128-pixel tiles (see unfold_c3k3_kernel); small ones and the fp32 layer take the direct kernel.
+  const bool first_layer = d.groups == 1 && d.C == 3 && d.R == 3 && d.S == 3 && d.x_layout == 0;
+  p->stem = first_layer && d.x_dtype == SOFIE_B200_I8 && d.y_layout == 1 && d.K % 16 == 0 && d.K <= 256 &&
+            (d.N > 0 ? d.N : 1) * Ho * Wo >= 16384 && !(d.flags & SOFIE_B200_CONV_UNFOLD);
+  if (first_layer && !p->stem && d.K <= 256 && !(d.flags & SOFIE_B200_CONV_UNFOLD) &&
       direct_smem_bytes(d, p->pix_rows, p->pair_out) <= kDirectSmemLimit) {
     // the 3-channel first layer: direct kernel (see conv_direct_kernel); the plan only keeps the padded weights
     p->direct = 1;
@@ -639,23 +696,33 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
       ic.on = 1; ic.N = d.N > 0 ? d.N : 1; ic.H = d.H; ic.W = d.W; ic.C = d.C; ic.Ho = Ho; ic.Wo = Wo;
       ic.R = (int)d.R; ic.S = (int)d.S; ic.pt = (int)d.pad_top; ic.pl = (int)d.pad_left; ic.pb = (int)d.pad_bottom; ic.pr = (int)d.pad_right;
       ic.sh = (int)d.stride_h; ic.sw = (int)d.stride_w; ic.dh = (int)d.dil_h; ic.dw = (int)d.dil_w;
+      // pixels of 64 bytes under a horizontal stride of 2: read pixel pairs (see pair_weights_kernel)
+      const bool pairs = d.C * es == 64 && d.stride_w == 2 && d.S == 3 && d.dil_w == 1 && d.pad_left == 1 && d.pad_right <= 1 && d.W % 2 == 0 &&
+                         Wo == d.W / 2;
+      int64_t kimp = p->kdim;
+      if (pairs) {
+        ic.W = d.W / 2; ic.C = 2 * d.C; ic.S = 2; ic.sw = 1; ic.pl = 1; ic.pr = 0;
+        kimp = d.R * 2 * 2 * d.C;
+      }
       sofie_b200_gemm_desc g{};
       g.trans_a = 0; g.trans_b = 1; g.ab_dtype = d.x_dtype; g.y_dtype = d.y_dtype;
-      g.M = rows; g.N = d.K; g.K = p->kdim; g.batch = 1; g.lda = p->kdim; g.ldb = p->kdim; g.ldy = d.K; g.precise = 0;
+      g.M = rows; g.N = d.K; g.K = kimp; g.batch = 1; g.lda = kimp; g.ldb = kimp; g.ldy = d.K; g.precise = 0;
       const bool y_ok = d.y_dtype == SOFIE_B200_F32 || d.y_dtype == SOFIE_B200_BF16 || d.y_dtype == SOFIE_B200_I8 || d.y_dtype == SOFIE_B200_U8 ||
                         (d.y_dtype == SOFIE_B200_I32 && d.x_dtype == SOFIE_B200_I8);
       rc = y_ok ? gemm_plan_create_im2col(ctx, g, ic, &p->gemm) : 1;
       if (rc < 0) { delete p; return rc; }
       if (rc == 0) {
         p->implicit = 1; p->nhwc = 1; p->kpad = p->kdim;
-        if (cudaMalloc(&p->w_padded, (size_t)(d.K * p->kdim * es)) != cudaSuccess) {
+        if (cudaMalloc(&p->w_padded, (size_t)(d.K * kimp * es)) != cudaSuccess) {
           sofie_b200_gemm_plan_destroy(p->gemm);
           delete p;
           return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: allocating the filter buffer failed: %s", cudaGetErrorString(cudaGetLastError()));
         }
-        const long long wt = d.K * p->kdim;
+        const long long wt = d.K * kimp;
         const unsigned wg = (unsigned)std::min<long long>((wt + 255) / 256, (long long)ctx->sm_count * 16);
-        if (es == 4) reorder_weights_kernel<float><<<wg, 256, 0, ctx->stream>>>((const float *)W, (float *)p->w_padded, d.K, (int)p->cg, (int)(d.R * d.S));
+        if (pairs && es == 4) pair_weights_kernel<float><<<wg, 256, 0, ctx->stream>>>((const float *)W, (float *)p->w_padded, d.K, (int)d.C, (int)d.R);
+        else if (pairs) pair_weights_kernel<int8_t><<<wg, 256, 0, ctx->stream>>>((const int8_t *)W, (int8_t *)p->w_padded, d.K, (int)d.C, (int)d.R);
+        else if (es == 4) reorder_weights_kernel<float><<<wg, 256, 0, ctx->stream>>>((const float *)W, (float *)p->w_padded, d.K, (int)p->cg, (int)(d.R * d.S));
         else reorder_weights_kernel<int8_t><<<wg, 256, 0, ctx->stream>>>((const int8_t *)W, (int8_t *)p->w_padded, d.K, (int)p->cg, (int)(d.R * d.S));
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { sofie_b200_gemm_plan_destroy(p->gemm); cudaFree(p->w_padded); delete p; return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: %s", cudaGetErrorString(e)); }
@@ -865,6 +932,8 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
     unfold_split_kernel<<<grid, 256, 0, ctx->stream>>>((const float *)X, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad);
   else if (d.x_dtype == SOFIE_B200_F32)
     unfold_kernel<float, 4><<<grid, 256, 0, ctx->stream>>>((const float *)X, (float *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, 0.f);
+  else if (plan->stem)
+    unfold_c3k3_kernel<<<(unsigned)((d.N * pix + 255) / 256), 256, 0, ctx->stream>>>((const int8_t *)X, (uint4 *)workspace, d, (int)plan->Ho, (int)plan->Wo);
   else
     unfold_kernel<int8_t, 16><<<grid, 256, 0, ctx->stream>>>((const int8_t *)X, (int8_t *)workspace, d, plan->Ho, plan->Wo, plan->cg, plan->kdim, plan->kpad, (int8_t)d.x_zero_point);
   SB_CUDA(cudaGetLastError());

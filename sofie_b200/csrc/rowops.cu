@@ -257,12 +257,14 @@ template <typename TIn, typename TOut, int CH, int R>
 __global__ void __launch_bounds__(256, 2) layernorm_warp_kernel(const TIn *__restrict__ x, TOut *__restrict__ y, long long rows, int cols,
                                                                 const float *__restrict__ scale, const float *__restrict__ bias, float eps,
                                                                 float *__restrict__ mean_out, float *__restrict__ invstd_out) {
-  constexpr int E = Vec16<TIn>::E;
+  constexpr int E = Vec16<TIn>::E, P = E / 2;   // elements and fp32 pairs per 16-byte chunk
   const int lane = threadIdx.x & 31;
   const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
   const float inv_n = 1.f / (float)cols;
-  float sc[CH][E], bi[CH][E];
+  // Arithmetic on pairs (packed fp32 instructions: two values per instruction, each half rounded as the scalar instruction
+  // rounds it): the kernel was bound by instruction issue at 0.77 of the copy bandwidth with scalar arithmetic.
+  float2 sc[CH][P], bi[CH][P];
   bool have[CH];
 #pragma unroll
   for (int c = 0; c < CH; ++c) {
@@ -272,8 +274,8 @@ __global__ void __launch_bounds__(256, 2) layernorm_warp_kernel(const TIn *__res
     for (int e = 0; e < E; e += 4) {
       const float4 s4 = (have[c] && scale) ? *reinterpret_cast<const float4 *>(scale + col + e) : make_float4(1.f, 1.f, 1.f, 1.f);
       const float4 b4 = (have[c] && bias) ? *reinterpret_cast<const float4 *>(bias + col + e) : make_float4(0.f, 0.f, 0.f, 0.f);
-      sc[c][e] = s4.x; sc[c][e + 1] = s4.y; sc[c][e + 2] = s4.z; sc[c][e + 3] = s4.w;
-      bi[c][e] = b4.x; bi[c][e + 1] = b4.y; bi[c][e + 2] = b4.z; bi[c][e + 3] = b4.w;
+      sc[c][e / 2] = make_float2(s4.x, s4.y); sc[c][e / 2 + 1] = make_float2(s4.z, s4.w);
+      bi[c][e / 2] = make_float2(b4.x, b4.y); bi[c][e / 2 + 1] = make_float2(b4.z, b4.w);
     }
   }
   // the loads of the next trip are issued before the arithmetic of the current one: a warp always has R * CH 16-byte loads in flight
@@ -296,17 +298,18 @@ __global__ void __launch_bounds__(256, 2) layernorm_warp_kernel(const TIn *__res
     // rows go through the arithmetic two at a time (registers: the raw rows of the trip stay packed until their turn)
 #pragma unroll
     for (int r0 = 0; r0 < R; r0 += 2) {
-      float v[2][CH][E];
+      float2 v[2][CH][P];
       float s[2];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        s[r] = 0.f;
+        float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
-          unpack16<TIn>(raw[r0 + r][c], v[r][c]);
+          unpack16_pairs<TIn>(raw[r0 + r][c], v[r][c]);
 #pragma unroll
-          for (int e = 0; e < E; ++e) s[r] += v[r][c][e];
+          for (int e = 0; e < P; ++e) s2 = __fadd2_rn(s2, v[r][c][e]);
         }
+        s[r] = s2.x + s2.y;
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1)
@@ -316,13 +319,15 @@ __global__ void __launch_bounds__(256, 2) layernorm_warp_kernel(const TIn *__res
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         mean[r] = s[r] * inv_n;
-        q[r] = 0.f;
+        const float2 nm = make_float2(-mean[r], -mean[r]);
+        float2 q2 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < CH; ++c)
           if (have[c]) {
 #pragma unroll
-            for (int e = 0; e < E; ++e) { v[r][c][e] = __fsub_rn(v[r][c][e], mean[r]); q[r] = __fmaf_rn(v[r][c][e], v[r][c][e], q[r]); }
+            for (int e = 0; e < P; ++e) { v[r][c][e] = __fadd2_rn(v[r][c][e], nm); q2 = __ffma2_rn(v[r][c][e], v[r][c][e], q2); }
           }
+        q[r] = q2.x + q2.y;
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1)
@@ -333,6 +338,7 @@ __global__ void __launch_bounds__(256, 2) layernorm_warp_kernel(const TIn *__res
         const long long row = row0 + r0 + r;
         if (row < rows) {
           const float inv = 1.f / sqrtf(q[r] * inv_n + eps);
+          const float2 inv2 = make_float2(inv, inv);
           TOut *yr = y + row * (long long)cols;
 #pragma unroll
           for (int c = 0; c < CH; ++c)
@@ -340,9 +346,10 @@ __global__ void __launch_bounds__(256, 2) layernorm_warp_kernel(const TIn *__res
               float o[E];
               // scale * invStd * (x - mean) + bias, left to right, each step rounded
 #pragma unroll
-              for (int e = 0; e < E; ++e) {
-                const float t = scale ? __fmul_rn(__fmul_rn(sc[c][e], inv), v[r][c][e]) : __fmul_rn(inv, v[r][c][e]);
-                o[e] = bias ? __fadd_rn(t, bi[c][e]) : t;
+              for (int e = 0; e < P; ++e) {
+                float2 t = scale ? __fmul2_rn(__fmul2_rn(sc[c][e], inv2), v[r][c][e]) : __fmul2_rn(inv2, v[r][c][e]);
+                if (bias) t = __fadd2_rn(t, bi[c][e]);
+                o[2 * e] = t.x; o[2 * e + 1] = t.y;
               }
               store_chunk_as<TOut, E>(yr + (c * 32 + lane) * E, o);
             }

@@ -74,16 +74,18 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 }
 
 // rint(v) + zp, saturated to the 8-bit output type, for four values -> four bytes (v0 lowest).  v is first bounded below
-// by -2^22 (which also sends a NaN there, as the float formula's saturation does); then v + 1.5 * 2^23 holds rint(v) in
+// by `lower`: -2^22 (which also sends a NaN there, as the float formula's saturation does), or 0 when a Relu precedes the
+// quantisation -- max(v, 0) is that Relu (a NaN and -0 both end as the integer 0 either way), so the activation costs no
+// instruction of its own; then v + 1.5 * 2^23 holds rint(v) in
 // its low mantissa bits for |v| < 2^22 and is monotonic in v above that, as are the bits of a positive float read as an
 // integer; the integer addition takes the exponent bits away and adds the zero point, and the packing conversion
 // saturates to [-128, 127] or [0, 255].  Full-rate instructions only: 2.5 per element.  (A saturating integer subtraction
 // instead of the lower bound costs eight instructions: the target has none.)
 template <bool SIGNED>
-__device__ __forceinline__ uint32_t quantize4(float2 lo, float2 hi, int unmagic) {
+__device__ __forceinline__ uint32_t quantize4(float2 lo, float2 hi, int unmagic, float lower) {
   const float2 m = dup2(12582912.f);
-  const float2 a = fadd2(make_float2(fmaxf(lo.x, -4194304.f), fmaxf(lo.y, -4194304.f)), m);
-  const float2 b = fadd2(make_float2(fmaxf(hi.x, -4194304.f), fmaxf(hi.y, -4194304.f)), m);
+  const float2 a = fadd2(make_float2(fmaxf(lo.x, lower), fmaxf(lo.y, lower)), m);
+  const float2 b = fadd2(make_float2(fmaxf(hi.x, lower), fmaxf(hi.y, lower)), m);
   const int q0 = __float_as_int(a.x) - unmagic, q1 = __float_as_int(a.y) - unmagic, q2 = __float_as_int(b.x) - unmagic, q3 = __float_as_int(b.y) - unmagic;
   uint32_t out;
   if (SIGNED) {
@@ -206,10 +208,16 @@ __device__ __forceinline__ void epi16_step(const EpiParams &ep, const Epi16Warp 
       for (int u = 0; u < 8; ++u) v[u] = fadd2(v[u], make_float2(r[2 * u], r[2 * u + 1]));
     }
   }
+  constexpr bool OUT8 = OUT == OUT16_I8 || OUT == OUT16_U8;
+  float q_lower = -4194304.f;   // lower bound of the 8-bit quantiser
   if (fl & EPI16_ACT) {
     if (ep.act == SOFIE_B200_ACT_RELU) {
+      if (OUT8 && !(fl & EPI16_OUT_SCALE)) {
+        q_lower = 0.f;          // the quantiser's lower bound is the Relu
+      } else {
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = make_float2(act_apply(v[u].x, SOFIE_B200_ACT_RELU, 0.f), act_apply(v[u].y, SOFIE_B200_ACT_RELU, 0.f));
+        for (int u = 0; u < 8; ++u) v[u] = make_float2(act_apply(v[u].x, SOFIE_B200_ACT_RELU, 0.f), act_apply(v[u].y, SOFIE_B200_ACT_RELU, 0.f));
+      }
     } else if (ep.act == SOFIE_B200_ACT_GELU_ERF) {
       if (OUT == OUT16_BF16) {
 #pragma unroll
@@ -246,7 +254,7 @@ __device__ __forceinline__ void epi16_step(const EpiParams &ep, const Epi16Warp 
     const int unmagic = 0x4B400000 - ep.out_zp;
     uint32_t p[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) p[u] = quantize4<OUT == OUT16_I8>(v[2 * u], v[2 * u + 1], unmagic);
+    for (int u = 0; u < 4; ++u) p[u] = quantize4<OUT == OUT16_I8>(v[2 * u], v[2 * u + 1], unmagic, q_lower);
     st_shared_v4(w.row_addr + o0, p[0], p[1], p[2], p[3]);
   }
 }

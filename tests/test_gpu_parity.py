@@ -334,6 +334,44 @@ def test_three_channel_first_layer_channels_last_fp32(ctx, oracle, K, kernel):
     assert close_f32(y.cpu().numpy().transpose(0, 3, 1, 2), want)
 
 
+@pytest.mark.parametrize("case", ["same", "stride2_zero_point", "dilated_ragged"])
+def test_three_channel_first_layer_int8_on_tensor_cores(ctx, oracle, case):
+    """The int8 3-channel 3x3 first layer with a channels-last output and enough output pixels: one gather kernel writes
+    the unfolded [pixels][32] matrix and the tensor-core contraction does the rest; bit-exact against the checker, also
+    with a zero point in the padding, a stride, a dilation and a last tile that is not full."""
+    from sofie_b200.ops import make_epilogue
+    lib = ctx._lib
+    N, H, W, K, pads, strides, dil, zp = {"same": (2, 96, 96, 64, [1, 1, 1, 1], [1, 1], [1, 1], 0),
+                                          "stride2_zero_point": (3, 161, 150, 32, [1, 1, 1, 1], [2, 2], [1, 1], -7),
+                                          "dilated_ragged": (2, 101, 99, 48, [2, 1, 0, 2], [1, 1], [2, 1], 0)}[case]
+    rng = np.random.default_rng(len(case))
+    x = rng.integers(-127, 128, size=(N, 3, H, W), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(K, 3, 3, 3), dtype=np.int8)
+    cs = (rng.random(K, dtype=np.float32) * 2e-3 + 2e-4).astype(np.float32)
+    bias = rng.integers(-2000, 2000, size=K, dtype=np.int32)
+    d = gr.conv_desc(dict(pads=pads, strides=strides, dil=dil, group=1), x.shape, w.shape, L.I8, L.I8)
+    d.x_zero_point = zp
+    ho, wo = C.c_int64(), C.c_int64()
+    assert lib.sofie_b200_conv_out_shape(C.byref(d), C.byref(ho), C.byref(wo)) == 0
+    want = oracle.conv(x, w, d, ho.value, wo.value, ep=oracle.epilogue(col_scale=cs, bias=bias, act=L.ACT_RELU))
+    d.y_layout = 1
+    tx, tw = torch.from_numpy(x).to(DEV), torch.from_numpy(w).to(DEV)
+    h = C.c_void_p()
+    L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), tw.data_ptr(), C.byref(h)), "conv_plan_create")
+    assert lib.sofie_b200_conv_plan_kernel(h).decode() == "umma"
+    assert lib.sofie_b200_conv_workspace_bytes(h) == N * ho.value * wo.value * 32
+    ws = torch.empty(lib.sofie_b200_conv_workspace_bytes(h), dtype=torch.uint8, device=DEV)
+    y = torch.zeros((N, ho.value, wo.value, K), dtype=torch.int8, device=DEV)
+    ep, keep = make_epilogue(col_scale=torch.from_numpy(cs).to(DEV), bias=torch.from_numpy(bias).to(DEV), act=L.ACT_RELU)
+    launches = ctx.launches
+    L.check(lib.sofie_b200_conv_enqueue(h, tx.data_ptr(), y.data_ptr(), ws.data_ptr(), C.byref(ep)), "conv_enqueue")
+    ctx.sync()
+    assert ctx.launches - launches == 2
+    lib.sofie_b200_conv_plan_destroy(h)
+    got = y.cpu().numpy().transpose(0, 3, 1, 2)
+    assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size}"
+
+
 IMPLICIT_CASES = {
     # name: (N, C, H, W, K, R, S, pads [top, left, bottom, right], strides [h, w], dilations [h, w], x zero point)
     "c64_3x3_tail": (2, 64, 13, 10, 48, 3, 3, [1, 1, 1, 1], [1, 1], [1, 1], 0),         # 64-byte K blocks, 260 pixels: a partial tile
@@ -349,6 +387,10 @@ IMPLICIT_CASES = {
     "s2_c256_1x1": (2, 256, 12, 8, 128, 1, 1, [0, 0, 0, 0], [2, 2], [1, 1], 5),
     "s2_c64_dilated": (2, 64, 20, 16, 64, 3, 3, [2, 3, 2, 3], [2, 2], [2, 3], 0),
     "s2_c64_many_tiles": (4, 64, 112, 112, 128, 3, 3, [1, 1, 1, 1], [2, 2], [1, 1], 0),
+    # 64-byte pixels under a horizontal stride of 2 are read as pixel pairs (two-tap convolution over [N, H, W/2, 2C])
+    "pairs_w_stride_only": (2, 64, 11, 14, 80, 3, 3, [1, 1, 1, 0], [1, 2], [1, 1], 0),
+    "pairs_two_rows": (2, 64, 9, 16, 32, 2, 3, [0, 1, 1, 1], [2, 2], [1, 1], 0),
+    "pairs_row_dilation": (3, 64, 20, 18, 64, 3, 3, [2, 1, 2, 1], [2, 2], [2, 1], 0),
 }
 
 
