@@ -203,10 +203,26 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // Two register buffers: the tcgen05.ld of the next 32 columns is in flight while the current ones are processed,
       // and pass 2 starts loading before pass 1 has finished its arithmetic.
       uint32_t ra[32], rb[32];
-      float mx = -3.0e38f;
+      // The Softmax chain is bound by instruction issue, so it counts instructions: the row maximum is taken over the RAW
+      // scores and scaled once (a positive scale keeps the order; a negative one takes the minimum), and only the 32-column
+      // chunk that holds the end of a short sequence pays for masking.
+      const bool pos = p.scale_log2e >= 0.f;
+      float mx = -3.0e38f, mn = 3.0e38f;
       auto max_of = [&](const uint32_t (&r)[32], int c) {
+        if (c + 32 <= p.seq) {
+          if (pos) {
 #pragma unroll
-        for (int u = 0; u < 32; ++u) mx = fmaxf(mx, (c + u < p.seq) ? __uint_as_float(r[u]) * p.scale_log2e : -3.0e38f);
+            for (int u = 0; u < 32; ++u) mx = fmaxf(mx, __uint_as_float(r[u]));
+          } else {
+#pragma unroll
+            for (int u = 0; u < 32; ++u) mn = fminf(mn, __uint_as_float(r[u]));
+          }
+        } else {
+#pragma unroll
+          for (int u = 0; u < 32; ++u) {
+            if (c + u < p.seq) { mx = fmaxf(mx, __uint_as_float(r[u])); mn = fminf(mn, __uint_as_float(r[u])); }
+          }
+        }
       };
       // pass 1: row maximum over the keys that exist
       tmem_ld_x32(t_s, ra);
@@ -220,19 +236,24 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         store_pending = false;
       }
       // pass 2: unnormalised probabilities as bf16 into shared memory, fp32 row sum
-      const float off = mx;   // maximum of the scaled scores (any sign of the scale)
-      float sum = 0.f;
+      const float off = (pos ? mx : mn) * p.scale_log2e;   // maximum of the scaled scores
+      float2 sum2 = make_float2(0.f, 0.f);
       auto exp_store = [&](const uint32_t (&r)[32], int c) {
         uint32_t w[16];
+        const bool full = c + 32 <= p.seq;
 #pragma unroll
         for (int u = 0; u < 32; u += 2) {
           float e0 = ex2_approx(__fmaf_rn(__uint_as_float(r[u]), p.scale_log2e, -off));
           float e1 = ex2_approx(__fmaf_rn(__uint_as_float(r[u + 1]), p.scale_log2e, -off));
-          if (c + u >= p.seq) e0 = 0.f;
-          if (c + u + 1 >= p.seq) e1 = 0.f;
+          if (!full) {
+            if (c + u >= p.seq) e0 = 0.f;
+            if (c + u + 1 >= p.seq) e1 = 0.f;
+          }
           __nv_bfloat162 h2 = __floats2bfloat162_rn(e0, e1);
-          sum += __bfloat162float(h2.x) + __bfloat162float(h2.y);   // the sum of what the second MMA will actually read
-          w[u >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+          const uint32_t hw = *reinterpret_cast<uint32_t *>(&h2);
+          // the sum of what the second MMA will actually read: both bf16 halves back as fp32, one packed add
+          sum2 = __fadd2_rn(sum2, make_float2(__uint_as_float(hw << 16), __uint_as_float(hw & 0xffff0000u)));
+          w[u >> 1] = hw;
         }
         const uint32_t tile = my_p + (c >> 6) * ATT_TILE;   // keys [0, 64) -> tile 0, [64, 128) -> tile 1
         const int u0 = (c & 32) >> 3;                       // first 16-byte unit of this chunk inside the 128-byte row
@@ -246,6 +267,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tmem_ld_wait(); tmem_ld_x32(t_s + 64, ra); exp_store(rb, 32);
       tmem_ld_wait(); tmem_ld_x32(t_s + 96, rb); exp_store(ra, 64);
       tmem_ld_wait();                            exp_store(rb, 96);
+      const float sum = sum2.x + sum2.y;
       fence_proxy_async();   // generic-proxy writes of P become visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p + 8 * set);

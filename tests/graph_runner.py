@@ -303,8 +303,21 @@ def run_graph(fx: dict, inputs: list, backend) -> np.ndarray:
             y = backend.gemm(ins[0], ins[1], bias, float(at.get("alpha", 1.0)), float(at.get("beta", 1.0)),
                              bool(at.get("transA", 0)), bool(at.get("transB", 0)), act, act_alpha)
         elif op == "Conv":
-            geo = conv_geometry(at, tuple(ins[0].shape), tuple(ins[1].shape))
-            y = backend.conv(ins[0], ins[1], ins[2] if len(ins) > 2 else None, geo, act, act_alpha)
+            x, w = ins[0], ins[1]
+            one_d = x.ndim == 3   # [N, C, L]: a 2-D convolution of height 1 (ROperator_Conv.hxx:123-262 treats the ranks alike)
+            if one_d:
+                x, w = x.reshape(x.shape[0], x.shape[1], 1, x.shape[2]), w.reshape(w.shape[0], w.shape[1], 1, w.shape[2])
+                at = dict(at)
+                for key, fill in (("dilations", 1), ("strides", 1)):
+                    if key in at:
+                        at[key] = [fill] + list(at[key])
+                if at.get("auto_pad", "NOTSET") == "NOTSET":
+                    b, e = at.get("pads", [1, 1])   # the pads-default quirk: no pads attribute means 1
+                    at["pads"] = [0, b, 0, e]
+            geo = conv_geometry(at, tuple(x.shape), tuple(w.shape))
+            y = backend.conv(x, w, ins[2] if len(ins) > 2 else None, geo, act, act_alpha)
+            if one_d:
+                y = y.reshape(y.shape[0], y.shape[1], y.shape[3])
         elif op == "BatchNormalization":
             y = backend.batchnorm(ins[0], ins[1], ins[2], ins[3], ins[4], float(at.get("epsilon", 1e-5)), act)
         elif op == "LayerNormalization":
