@@ -310,7 +310,10 @@ static int make_epi(const sofie_b200_gemm_desc &d, void *Y, const sofie_b200_epi
     o->out_zp = ep->out_zero_point;
     o->params_aligned = ((uintptr_t)ep->col_scale % 16 == 0) && ((uintptr_t)ep->bias % 16 == 0);
     const int rs_ = dtype_size(ep->residual_dtype);
-    o->residual_aligned = ((uintptr_t)ep->residual % 16 == 0) && ((o->ldr * rs_) % 16 == 0) && ((o->stride_r * rs_) % 16 == 0);
+    // 0: no alignment known, 1: base, pitch and batch stride are multiples of 16 bytes, 2: of 32 bytes
+    o->residual_aligned = 0;
+    for (int a = 16; a <= 32; a *= 2)
+      if (((uintptr_t)ep->residual % a == 0) && ((o->ldr * rs_) % a == 0) && ((o->stride_r * rs_) % a == 0)) o->residual_aligned = a / 16;
     o->fast = o->params_aligned && ep->bias_mode != SOFIE_B200_BIAS_FULL_F32;
     if (ep->bias_mode != SOFIE_B200_BIAS_NONE && !ep->bias)
       return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue: bias_mode %d with a NULL bias", ep->bias_mode);

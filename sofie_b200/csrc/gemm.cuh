@@ -70,7 +70,8 @@ struct UmmaParams {
   int kb_mmas;                     // MMAs (32 bytes of K each) per K block: 4, or 2 when a K block is 64 bytes
   int prod_lanes;                  // TMA producer lanes per producer warp (1 to 4)
   int b_resident;                  // all K blocks of operand B stay in shared memory (tiles_n == 1); the ring holds A only
-  int accs;                        // accumulators in tensor memory: 2 or 4
+  int accs;                        // accumulators in tensor memory: 1 (tall tiles), 2 or 4
+  int mh;                          // M halves of a tile: 1, or 2 = a tall 256 x bn tile whose two 128-row halves share every B slice
   int teams;                       // teams of epilogue warps, each draining a tile of its own: 1, 2 or 4, at most accs
   int im2col;
   int ic_wo, ic_pix;               // output width, output pixels per image

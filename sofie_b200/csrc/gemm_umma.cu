@@ -20,6 +20,12 @@
 //                    buffer, and a complete segment leaves as one bulk tensor store.  The epilogue is bound
 //                    by instruction issue, which is why it has sixteen warps and counts instructions.
 //
+// Tall tiles (UmmaParams::mh = 2): a 256 x 256 tile as two 128-row halves that share every B slice -- 64 KB of operands per
+// K block for twice the MMA work of a 128 x 256 tile's 48 KB.  The large contractions are bound by the bytes an SM can pull
+// from L2 per tensor-pipe cycle, not by the pipe; a tall tile needs a third fewer.  Both halves' accumulators fill tensor
+// memory, so there is no second accumulator and the epilogue of a tile does not overlap the next tile's MMAs: the plan
+// takes tall tiles only where K is long enough for that to be small change.
+//
 // Data layout: a K-major operand (row-major [rows, K]) is one TMA box of rows x 128 bytes per
 // stage; an MN-major operand (row-major [K, cols]) is cols*es/128 boxes of (128 bytes x K-rows).
 // Both land in the canonical 128B-swizzle layouts that the shared-memory matrix descriptors
@@ -161,7 +167,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           decode_item(p, w, t, n_off, n_len, idesc);
           int b, tm, tn;
           tile_coords(p, t, tiles_per_batch, b, tm, tn);
-          m0 = tm * UMMA_BM;
+          m0 = tm * UMMA_BM * p.mh;
           n0 = tn * p.bn + n_off;  // a half item still loads a full-width B slice
           ba = p.a_bcast ? 0 : b; bb = p.b_bcast ? 0 : b;
           if (p.im2col) {
@@ -223,6 +229,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const uint32_t a_lo0 = p.a_desc_lo | ((smem_a >> 4) & 0x3fffu), b_lo0 = p.b_desc_lo | ((smem_b >> 4) & 0x3fffu);
       const uint32_t a_step = p.a_stage_bytes >> 4, b_step = p.b_stage_bytes >> 4;
       const uint32_t a_kadv = p.a_kadv, b_kadv = p.b_kadv;
+      const uint64_t a_half = (uint64_t)(p.a_stage_bytes >> 5);   // half an A stage, in 16-byte units
       const int num_kb = p.num_kb, kb_mmas = p.kb_mmas;
       ROLE_TIMER(w_full);
       ROLE_TIMER(w_tempty);
@@ -246,7 +253,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * p.bn;
+        const uint32_t d_tmem = tmem_base + acc * (p.bn * p.mh);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ROLE_WAIT(w_full, mbar_wait(bar_full + 8 * stage, phase, abort_flag))) {
             raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_FULL);
@@ -266,6 +273,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const uint64_t bd = b_hi | (uint64_t)(b_lo + k * b_kadv);
 #ifndef SB200_SKIP_MMA
             umma<KIND>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            // tall tile: rows 128..255 of the A slice (the next 128 rows of the same box) against the same B slice
+            if (p.mh == 2) umma<KIND>(d_tmem + p.bn, ad + a_half, bd, idesc, (kb | k) != 0 ? 1u : 0u);
 #endif
           }
           ROLE_SECTION_END(c_mma);
@@ -294,7 +303,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const int groups_per_team = (UMMA_EPI_WARPS / 4) / p.teams;
     const uint32_t team = (uint32_t)(group / groups_per_team);
     const int seg_first = group % groups_per_team;
-    const uint32_t acc_mask = (uint32_t)p.accs - 1u, acc_shift = (uint32_t)p.accs >> 1;   // accs is 2 or 4
+    const uint32_t acc_mask = (uint32_t)p.accs - 1u, acc_shift = (uint32_t)p.accs >> 1;   // accs is 1, 2 or 4
     const Epi16Warp ew = epi16_warp_init(p.ep, epi_stage + (uint32_t)epi_warp * UMMA_EPI_STAGE_BYTES);
     const CUtensorMap *y_map = p.y_tma ? &tm_y : nullptr;
     const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -306,30 +315,41 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #ifdef SB200_ROLE_TIMERS
     t_begin = clock64();
 #endif
-    for (uint32_t i = team, w = blockIdx.x + team * gridDim.x; w < num_items; i += (uint32_t)p.teams, w += gridDim.x * (uint32_t)p.teams) {
+    // One trip per 128-row half of a tile (h: 0, and 1 for the lower half of a tall tile -- the next bn columns of tensor
+    // memory, rows 128 further): the accumulator is waited for before its first half and handed back after its last.
+    uint32_t i = team, w = blockIdx.x + team * gridDim.x;
+    int h = 0;
+    while (w < num_items) {
       const uint32_t acc = i & acc_mask, acc_phase = (i >> acc_shift) & 1u;   // tile i of this CTA: accumulator and its phase
-      const uint32_t taddr = taddr0 + acc * p.bn;
+      const uint32_t taddr = taddr0 + acc * (p.bn * p.mh) + h * p.bn;
       uint32_t t; int n_off, n_len; uint32_t idesc;
       decode_item(p, w, t, n_off, n_len, idesc);
       int b, tm, tn;
       tile_coords(p, t, tiles_per_batch, b, tm, tn);
-      const int m0 = tm * UMMA_BM;
+      const int m0 = (tm * p.mh + h) * UMMA_BM;
       const int n0 = tn * p.bn + n_off;
-      if (!ROLE_WAIT(w_tfull, mbar_wait_relaxed(bar_tfull + 8 * acc, acc_phase, abort_flag))) {
-        raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_FULL);
-        break;
+      if (h == 0) {
+        if (!ROLE_WAIT(w_tfull, mbar_wait_relaxed(bar_tfull + 8 * acc, acc_phase, abort_flag))) {
+          raise_abort(abort_flag, p.status, DEV_WAIT_TMEM_FULL);
+          break;
+        }
+        tc_fence_after();
       }
-      tc_fence_after();
       const int row = m0 + quad * 32 + lane;
       const int c_end = min(n_len, p.N - n0);          // columns of this item that exist (warp-uniform)
       ROLE_SECTION_BEGIN();
 #ifndef SB200_SKIP_EPI
-      drain16_any<KIND == KIND_I8>(p.ep, ew, taddr, c_end, seg_first, groups_per_team, b, row, n0, p.vec_ok != 0, p.M, y_map);
+      if (m0 < p.M) drain16_any<KIND == KIND_I8>(p.ep, ew, taddr, c_end, seg_first, groups_per_team, b, row, n0, p.vec_ok != 0, p.M, y_map);
 #endif
       ROLE_SECTION_END(c_st);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+      if (++h == p.mh) {
+        h = 0;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+        i += (uint32_t)p.teams;
+        w += gridDim.x * (uint32_t)p.teams;
+      }
     }
     if (threadIdx.x == 32 * UMMA_FIRST_EPI_WARP) { ROLE_REPORT("[cta %d] epilogue: total %lld, waiting for an accumulator %lld, tensor-memory loads %lld, epilogue math + stores %lld\n", blockIdx.x, clock64() - t_begin, w_tfull, c_ld, c_st); }
   }
@@ -475,6 +495,22 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   // an MN-major B slice is made of 128-byte-wide TMA boxes, so the slice one CTA stages must reach 128 bytes
   const int min_bn = d.trans_b ? 32 : 128 / es;
   u.bn = pick_bn(d.N, u.tiles_m, d.batch, sms, min_bn < 64 && plan->promote ? 64 : min_bn);
+  // Tall tiles (two 128-row halves per tile, see the top of this file) where a model of the kernel's time says they win:
+  // per tile the slower of the MMAs (128 cycles per 128 x 256 x 32-byte step) and the operand bytes at the 48 bytes per
+  // cycle an SM measured pulling from L2, times the waves of tiles; a tall tile adds its exposed epilogue (8 outputs a cycle).
+  u.mh = 1;
+  if (!plan->promote && !ic.on && !d.trans_a && u.bn == 256 && es <= 2 && d.M > UMMA_BM) {
+    const double nkb = (double)((d.K * es + kb_bytes - 1) / kb_bytes), tn = (double)((d.N + 255) / 256);
+    double t[3] = {0, 0, 0};
+    for (int mh = 1; mh <= 2; ++mh) {
+      const double tiles = (double)((d.M + 128 * mh - 1) / (128 * mh)) * tn * (double)d.batch;
+      const double waves = (double)(((long long)tiles + sms - 1) / sms);
+      const double t_mma = nkb * 4.0 * mh * 128.0, t_bw = nkb * (128.0 * mh + 256.0) * kb_bytes / 48.0;
+      t[mh] = waves * ((t_mma > t_bw ? t_mma : t_bw) + (mh == 2 ? 256.0 * 256.0 / 8.0 : 0.0));
+    }
+    if (t[2] < 0.85 * t[1]) u.mh = 2;
+  }
+  if (u.mh == 2) u.tiles_m = (int)((d.M + 2 * tile_m - 1) / (2 * tile_m));
   // Tile order.  With the M index fastest the tiles in flight share one B slice and sweep A, so A is re-read from DRAM
   // once per N tile unless it stays in L2; with the N index fastest it is B that is swept.  Take the cheaper one.
   {
@@ -496,7 +532,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.kb_elems = kb_bytes / es;
   u.kb_mmas = kb_bytes / 32;
   u.num_kb = (int)((d.K + u.kb_elems - 1) / u.kb_elems);
-  u.a_stage_bytes = UMMA_BM * kb_bytes;
+  u.a_stage_bytes = UMMA_BM * u.mh * kb_bytes;
   u.b_stage_bytes = u.b_rows * kb_bytes;
   // Chunk-promotion kernel: hi and lo of both operands share a stage (64 KB for a 128-column tile: three stages; 96 KB
   // for 256 columns: two), so each operand block is loaded once for its two products: 4 loads per 12 MMAs instead of 6.
@@ -519,6 +555,8 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.teams = 1;
   if (plan->promote) {
     u.accs = 2;
+  } else if (u.mh == 2) {
+    u.accs = 1;   // both halves' accumulators: all 512 columns
   } else {
     const double macs_per_clk = es == 1 ? 8192.0 : (es == 2 ? 4096.0 : 2048.0);
     const double t_mma = 128.0 * u.bn * (double)u.num_kb * u.kb_elems / macs_per_clk;
@@ -533,7 +571,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
     }
   }
   u.tmem_cols = 32;
-  while (u.tmem_cols < (uint32_t)u.accs * u.bn) u.tmem_cols <<= 1;
+  while (u.tmem_cols < (uint32_t)(u.accs * u.bn * u.mh)) u.tmem_cols <<= 1;
 
   const size_t epi_bytes = 32 * 1024;   // staging buffers of the epilogue warps (16 x 2 KB; the promotion kernel's 8 x 4 KB)
   const size_t budget = 227 * 1024 - 1024 /*alignment*/ - UMMA_TAIL_BYTES /*barriers*/ - epi_bytes;
@@ -543,7 +581,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   // rows a tile's operand loads, not its MMAs, set the pace, and B's rows are a third to a half of them.
   u.b_resident = 0;
   const size_t b_all = (size_t)u.num_kb * u.b_stage_bytes;
-  if (!plan->promote && u.tiles_n == 1 && (d.batch == 1 || (d.batch > 1 && d.stride_b == 0)) && b_all + 6 * (size_t)u.a_stage_bytes <= budget &&
+  if (!plan->promote && u.mh == 1 && u.tiles_n == 1 && (d.batch == 1 || (d.batch > 1 && d.stride_b == 0)) && b_all + 6 * (size_t)u.a_stage_bytes <= budget &&
       b_all < (1u << 20))
     u.b_resident = 1;
   int stages = u.b_resident ? (int)((budget - b_all) / u.a_stage_bytes) : (int)(budget / (u.a_stage_bytes + u.b_stage_bytes));
@@ -599,7 +637,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.split_from = u.num_tiles;
   u.num_items = u.num_tiles;
   u.idesc_half = (u.idesc & ~(0x3fu << 17)) | ((uint32_t)(u.bn >> 4) << 17);
-  if (!plan->promote && !u.b_resident && u.bn >= 64 && u.num_tiles > sms) {
+  if (!plan->promote && !u.b_resident && u.mh == 1 && u.bn >= 64 && u.num_tiles > sms) {
     const long long tail = u.num_tiles % sms;
     if (tail > 0 && 2 * tail <= sms) {
       u.split_from = u.num_tiles - tail;
@@ -636,7 +674,7 @@ static int build_maps(sofie_b200_gemm_plan *plan, const void *A, const void *B) 
     } else if (!u.a_mn) {
       uint64_t s2 = d.batch > 1 && !u.a_bcast ? (uint64_t)d.stride_a * es : (uint64_t)d.M * d.lda * es;
       rc = encode_map(&plan->tm_a, d.ab_dtype, A, kext, (uint64_t)d.M, nb, (uint64_t)d.lda * es, s2,
-                      (uint32_t)u.kb_elems, UMMA_BM);
+                      (uint32_t)u.kb_elems, (uint32_t)(UMMA_BM * u.mh));
     } else {
       uint64_t s2 = d.batch > 1 && !u.a_bcast ? (uint64_t)d.stride_a * es : (uint64_t)d.K * d.lda * es;
       rc = encode_map(&plan->tm_a, d.ab_dtype, A, (uint64_t)d.M, (uint64_t)d.K, nb, (uint64_t)d.lda * es, s2,

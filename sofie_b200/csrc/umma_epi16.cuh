@@ -187,7 +187,17 @@ __device__ __forceinline__ void epi16_step(const EpiParams &ep, const Epi16Warp 
   if (fl & EPI16_RES) {
     const long long roff = b * ep.stride_r + rr * ep.ldr + col0;
     if (ep.residual_dtype == SOFIE_B200_BF16) {
-      if (ep.residual_aligned) {
+      if (ep.residual_aligned == 2) {
+        // one 256-bit load: a lane reads its own row, so every load instruction touches 32 lines, and the load unit's
+        // time per line -- not latency -- made two 128-bit loads per step cost a third of a short-K tile's time
+        uint32_t ww[8];
+        asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(ww[0]), "=r"(ww[1]), "=r"(ww[2]), "=r"(ww[3]), "=r"(ww[4]), "=r"(ww[5]), "=r"(ww[6]), "=r"(ww[7])
+                     : "l"((const __nv_bfloat16 *)ep.residual + roff));
+#pragma unroll
+        for (int u = 0; u < 8; ++u)   // a bf16 is the upper half of the fp32 with the same value
+          v[u] = fadd2(v[u], make_float2(__uint_as_float(ww[u] << 16), __uint_as_float(ww[u] & 0xffff0000u)));
+      } else if (ep.residual_aligned) {
         const uint4 *r = reinterpret_cast<const uint4 *>((const __nv_bfloat16 *)ep.residual + roff);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {

@@ -99,8 +99,10 @@ inline std::string ConvDescCode(const ConvGeometry &g, const std::string &xEnum,
 // The library's plan selection restated (sofie_b200_conv_plan_kernel): the forms that need no workspace.
 inline bool ConvNeedsNoWorkspace(const ConvGeometry &g, size_t elemSize, size_t outElemSize, int xLayout, int yLayout, int xZeroPoint)
 {
-   // the 3-channel 3x3 first layer on the CUDA cores, while its filters and staging fit its shared memory
-   if (g.group == 1 && g.C == 3 && g.R == 3 && g.S == 3 && xLayout == 0 && g.K <= 256) {
+   // the 3-channel 3x3 first layer on the CUDA cores, while its filters and staging fit its shared memory -- except the int8
+   // layer with a channels-last output and at least 16384 output pixels, which unfolds to [pixels][32] for the tensor cores
+   const bool stem = elemSize == 1 && yLayout == 1 && g.K % 16 == 0 && g.N * g.Ho * g.Wo >= 16384;
+   if (g.group == 1 && g.C == 3 && g.R == 3 && g.S == 3 && xLayout == 0 && g.K <= 256 && !stem) {
       const size_t wsm = g.K * ((elemSize == 4 ? 28 * 4 : 8 * 4) + 16);
       const size_t stage = yLayout == 0 ? 0 : (yLayout == 2 ? 4 * 32 * (32 * 8 + 16) : 4 * 32 * (g.K * outElemSize + 16));
       if (wsm + stage <= 160 * 1024) return true;

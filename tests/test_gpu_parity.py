@@ -162,6 +162,24 @@ def test_qlinear_matmul_4096_sampled_rows(ctx, oracle):
     assert np.array_equal(got32, 2 * g2 + gr_)
 
 
+@pytest.mark.parametrize("M,tb", [(37500, True), (37786, False)])
+def test_tall_tiles_with_ragged_last_tile(ctx, oracle, M, tb):
+    """Long K, one tile across N and more row tiles than SMs: the plan takes 256-row tiles (two 128-row halves sharing every
+    B slice).  37500 rows leave a last tile whose lower half does not exist, 37786 one whose lower half has 26 rows.  The rows
+    of the last tiles and a random sample of the rest, bit for bit, with a per-channel epilogue."""
+    N, K = 256, 4096
+    rng = np.random.default_rng(M)
+    a = rng.integers(-127, 128, size=(M, K), dtype=np.int8)
+    b = rng.integers(-127, 128, size=(N, K) if tb else (K, N), dtype=np.int8)
+    cs = (rng.random(N, dtype=np.float32) * 2e-5 + 1e-5).astype(np.float32)
+    bias = rng.integers(-50000, 50000, size=N, dtype=np.int32)
+    got = run_gemm(ctx, a, b, M, N, K, torch.int8, torch.int8, False, tb, col_scale=cs, bias=bias, act=L.ACT_RELU, expect="umma").cpu().numpy()
+    rows = np.concatenate([np.arange(M - 420, M), rng.choice(M - 420, size=60, replace=False)])
+    want = oracle.gemm(np.ascontiguousarray(a[rows]), b, len(rows), N, K, L.I8, L.I8, False, tb,
+                       ep=oracle.epilogue(col_scale=cs, bias=bias, act=L.ACT_RELU))
+    assert np.array_equal(got[rows], want), f"{(got[rows] != want).sum()} of {want.size} differ"
+
+
 # ---- FP8 / bf16 / fp32 contractions -------------------------------------------------------------
 def fp8_operands(rng, M, N, K, tb):
     a = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32))

@@ -263,3 +263,24 @@ def test_convnet_configuration_from_the_generator(tmp_path, oracle_lib, b200_lib
     sess.infer_host([x], y2)     # replayed from the captured graph
     assert np.array_equal(y, y2)
     sess.close()
+
+
+def test_int8_convnet_session_with_the_first_layer_on_tensor_cores(tmp_path, oracle_lib, b200_lib):
+    """2 images of 96 x 96: 18432 output pixels, enough for the int8 first layer to take the unfold + tensor-core path
+    (two launches, a [pixels][32] scratch region the generator reserved in the arena) instead of the direct kernel;
+    the logits against the CPU checker, 11 launches."""
+    import model_oracles as mo
+    from sofie_b200 import convnet as bc
+    from sofie_b200.session import EmittedSession
+    seed = 11
+    nodes, init, ins, outs, in_types = bc.onnx_model(seed, 2, 96, True)
+    sess = EmittedSession("convnet_i8_96", nodes, init, ins, outs, tmp_path, input_types=in_types)
+    x = np.clip(np.rint(np.random.default_rng(seed).random((2, 3, 96, 96), dtype=np.float32) * 127.0), 0, 127).astype(np.int8)
+    want = mo.convnet_oracle(Oracle(oracle_lib), x, bc.make_weights(seed, True), True)
+    y = np.zeros((2, 1000), dtype=np.float32)
+    l0 = sess.launches
+    assert sess.infer_host([x], y) == y.size
+    assert sess.launches - l0 == 11
+    floor = float(np.sqrt(np.mean(np.square(want))))
+    assert np.all(np.abs(y - want) <= 1e-5 * np.maximum(np.abs(want), floor)), np.abs(y - want).max()
+    sess.close()
