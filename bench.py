@@ -49,7 +49,8 @@ L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures summarised
 # under profiles/ (None where no capture of that workload exists).
 NCU_TRAFFIC_BYTES = {
-    "qlinear_matmul_4096": 33.64e6 + 0.03e6,  # profiles/umma_gemm_i8_qlinear_matmul_4096.md
+    "qlinear_matmul_4096": 33.65e6 + 0.13e6,  # profiles/umma_gemm_i8_qlinear_matmul_4096.md
+    "fp8_gemm_8192": 339.3e6 + 111.1e6,       # profiles/umma_gemm_f8_gemm_8192.md
 }
 
 

@@ -60,6 +60,7 @@ struct UmmaParams {
   int a_bcast, b_bcast;            // operand shared by the whole batch
   int vec_ok;                      // 16-byte vector stores of 32-column chunks are aligned
   int raster_n;                    // tile order inside a batch: 0 = M index fastest, 1 = N index fastest
+  int rgroup;                      // > 0: tiles go in bands of this many N tiles, N index fastest inside a band (neither operand fits L2)
   int y_tma;                       // the epilogue may store complete row segments through the tensor map of Y
   int seg_kb;                      // chunk-promotion kernel: K blocks per split segment (ks / 32)
   int a_seg_kb[3], b_seg_kb[3];    // K block at which each of the three product segments starts in the stored A / B (hi | lo)

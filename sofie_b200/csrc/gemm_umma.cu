@@ -67,11 +67,19 @@ __device__ __forceinline__ void tile_coords(const UmmaParams &p, uint32_t t, uin
   uint32_t r = t;
   b = 0;
   if (p.batch > 1) { b = (int)(t / tiles_per_batch); r = t - (uint32_t)b * tiles_per_batch; }
-  if (p.raster_n) { const uint32_t q = r / (uint32_t)p.tiles_n; tm = (int)q; tn = (int)(r - q * (uint32_t)p.tiles_n); }
+  if (p.rgroup > 0) {
+    // bands of rgroup N tiles, N index fastest inside a band: the tiles in flight (one per SM) then share about sqrt(SMs)
+    // slices of each operand, which fit L2 together, and a band's B slices stay there while the band's M tiles go by
+    const uint32_t per = (uint32_t)p.tiles_m * (uint32_t)p.rgroup, band = r / per, rr = r - band * per;
+    const uint32_t left = (uint32_t)p.tiles_n - band * (uint32_t)p.rgroup, w = left < (uint32_t)p.rgroup ? left : (uint32_t)p.rgroup;
+    const uint32_t q = rr / w;
+    tm = (int)q; tn = (int)(band * (uint32_t)p.rgroup + (rr - q * w));
+  }
+  else if (p.raster_n) { const uint32_t q = r / (uint32_t)p.tiles_n; tm = (int)q; tn = (int)(r - q * (uint32_t)p.tiles_n); }
   else { const uint32_t q = r / (uint32_t)p.tiles_m; tn = (int)q; tm = (int)(r - q * (uint32_t)p.tiles_m); }
 }
 
-template <int KIND>
+template <int KIND, int MH>   // MH: M halves per tile (UmmaParams::mh), a template argument so that the one-half kernel pays nothing for the other
 __global__ void __launch_bounds__(UMMA_THREADS, 1)   // 20 warps: 96 registers per thread
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ UmmaParams p) {
@@ -167,7 +175,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           decode_item(p, w, t, n_off, n_len, idesc);
           int b, tm, tn;
           tile_coords(p, t, tiles_per_batch, b, tm, tn);
-          m0 = tm * UMMA_BM * p.mh;
+          m0 = tm * UMMA_BM * MH;
           n0 = tn * p.bn + n_off;  // a half item still loads a full-width B slice
           ba = p.a_bcast ? 0 : b; bb = p.b_bcast ? 0 : b;
           if (p.im2col) {
@@ -253,7 +261,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * (p.bn * p.mh);
+        const uint32_t d_tmem = tmem_base + acc * (p.bn * MH);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!ROLE_WAIT(w_full, mbar_wait(bar_full + 8 * stage, phase, abort_flag))) {
             raise_abort(abort_flag, p.status, DEV_WAIT_SMEM_FULL);
@@ -274,7 +282,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #ifndef SB200_SKIP_MMA
             umma<KIND>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
             // tall tile: rows 128..255 of the A slice (the next 128 rows of the same box) against the same B slice
-            if (p.mh == 2) umma<KIND>(d_tmem + p.bn, ad + a_half, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (MH == 2) umma<KIND>(d_tmem + p.bn, ad + a_half, bd, idesc, (kb | k) != 0 ? 1u : 0u);
 #endif
           }
           ROLE_SECTION_END(c_mma);
@@ -321,12 +329,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     int h = 0;
     while (w < num_items) {
       const uint32_t acc = i & acc_mask, acc_phase = (i >> acc_shift) & 1u;   // tile i of this CTA: accumulator and its phase
-      const uint32_t taddr = taddr0 + acc * (p.bn * p.mh) + h * p.bn;
+      const uint32_t taddr = taddr0 + acc * (p.bn * MH) + h * p.bn;
       uint32_t t; int n_off, n_len; uint32_t idesc;
       decode_item(p, w, t, n_off, n_len, idesc);
       int b, tm, tn;
       tile_coords(p, t, tiles_per_batch, b, tm, tn);
-      const int m0 = (tm * p.mh + h) * UMMA_BM;
+      const int m0 = (tm * MH + h) * UMMA_BM;
       const int n0 = tn * p.bn + n_off;
       if (h == 0) {
         if (!ROLE_WAIT(w_tfull, mbar_wait_relaxed(bar_tfull + 8 * acc, acc_phase, abort_flag))) {
@@ -342,7 +350,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       if (m0 < p.M) drain16_any<KIND == KIND_I8>(p.ep, ew, taddr, c_end, seg_first, groups_per_team, b, row, n0, p.vec_ok != 0, p.M, y_map);
 #endif
       ROLE_SECTION_END(c_st);
-      if (++h == p.mh) {
+      if (++h == MH) {
         h = 0;
         tc_fence_before();
         __syncwarp();
@@ -508,7 +516,10 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
       const double t_mma = nkb * 4.0 * mh * 128.0, t_bw = nkb * (128.0 * mh + 256.0) * kb_bytes / 48.0;
       t[mh] = waves * ((t_mma > t_bw ? t_mma : t_bw) + (mh == 2 ? 256.0 * 256.0 / 8.0 : 0.0));
     }
-    if (t[2] < 0.85 * t[1]) u.mh = 2;
+#ifndef SB200_TALL_RATIO
+#define SB200_TALL_RATIO 0.85
+#endif
+    if (t[2] < SB200_TALL_RATIO * t[1]) u.mh = 2;
   }
   if (u.mh == 2) u.tiles_m = (int)((d.M + 2 * tile_m - 1) / (2 * tile_m));
   // Tile order.  With the M index fastest the tiles in flight share one B slice and sweep A, so A is re-read from DRAM
@@ -519,6 +530,14 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
     const double cost_m = b_bytes + (a_bytes <= l2_fit ? a_bytes : tiles_n * a_bytes);
     const double cost_n = a_bytes + (b_bytes <= l2_fit ? b_bytes : (double)u.tiles_m * b_bytes);
     u.raster_n = cost_n < cost_m ? 1 : 0;
+    // Neither operand fits: either order re-reads one operand from DRAM once per wave of tiles (ncu on FP8 8192^3: 540 MB
+    // read for 134 MB of operands).  Bands of about sqrt(SMs) N tiles keep a wave's slices of both operands in L2.
+    u.rgroup = 0;
+    if (a_bytes > l2_fit && b_bytes > l2_fit && tiles_n >= 4 && u.tiles_m >= 4 && !ic.on) {
+      int g = 1;
+      while ((g + 1) * (g + 1) <= sms) ++g;
+      u.rgroup = g < (int)tiles_n ? g : (int)tiles_n;
+    }
   }
   if (plan->promote) {
     u.seg_kb = (int)(d.K / 3 / SPLIT_K_ALIGN);
@@ -650,12 +669,16 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   if (plan->promote) return umma_promote_set_smem(plan->smem_bytes);
 
   cudaError_t e = cudaSuccess;
+#define SB200_UMMA_ATTR(K) \
+  e = u.mh == 2 ? cudaFuncSetAttribute(umma_gemm_kernel<K, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM) \
+                : cudaFuncSetAttribute(umma_gemm_kernel<K, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM)
   switch (kind) {
-    case KIND_I8: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM); break;
-    case KIND_F8: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM); break;
-    case KIND_F16: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM); break;
-    default: e = cudaFuncSetAttribute(umma_gemm_kernel<KIND_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM); break;
+    case KIND_I8: SB200_UMMA_ATTR(KIND_I8); break;
+    case KIND_F8: SB200_UMMA_ATTR(KIND_F8); break;
+    case KIND_F16: SB200_UMMA_ATTR(KIND_F16); break;
+    default: SB200_UMMA_ATTR(KIND_TF32); break;
   }
+#undef SB200_UMMA_ATTR
   if (e != cudaSuccess) return fail(SOFIE_B200_ERR_CUDA, "cudaFuncSetAttribute(smem=%zu): %s", plan->smem_bytes, cudaGetErrorString(e));
   return 0;
 }
@@ -738,12 +761,16 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
   if (plan->promote) return umma_promote_launch(plan, u);
   cudaStream_t st = plan->ctx->stream;
   dim3 grid(plan->grid), block(UMMA_THREADS);
+#define SB200_UMMA_LAUNCH(K)                                                                             \
+  if (u.mh == 2) umma_gemm_kernel<K, 2><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u); \
+  else umma_gemm_kernel<K, 1><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u)
   switch (plan->kind) {
-    case KIND_I8: umma_gemm_kernel<KIND_I8><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u); break;
-    case KIND_F8: umma_gemm_kernel<KIND_F8><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u); break;
-    case KIND_F16: umma_gemm_kernel<KIND_F16><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u); break;
-    default: umma_gemm_kernel<KIND_TF32><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u); break;
+    case KIND_I8: SB200_UMMA_LAUNCH(KIND_I8); break;
+    case KIND_F8: SB200_UMMA_LAUNCH(KIND_F8); break;
+    case KIND_F16: SB200_UMMA_LAUNCH(KIND_F16); break;
+    default: SB200_UMMA_LAUNCH(KIND_TF32); break;
   }
+#undef SB200_UMMA_LAUNCH
   SB_CUDA(cudaGetLastError());
   plan->ctx->launches++;
   return 0;
