@@ -93,6 +93,8 @@ class ConvNetB200:
         n = 2
         for i, (kern, xl) in enumerate(zip(self.kernels, self.x_layouts)):
             n += 1 if kern in ("direct", "umma_im2col", "umma3x_im2col") else (2 if xl or i == 0 else 3)
+        if self.kernels[0] == "umma" and self.int8 and self.channels_last and self.first_pixels % 2 == 0:
+            n += 1   # the int8 first layer on the tensor cores packs 2 or 4 pixels per row: one kernel repeats its per-channel vectors
         return n
 
     def __init__(self, ctx, weights, batch: int, img: int, int8: bool, device: str, channels_last: bool = True):
@@ -102,6 +104,7 @@ class ConvNetB200:
         from sofie_b200 import lib as L
         from sofie_b200.ops import GemmPlan, make_epilogue
         self.ctx, self.batch, self.int8, self.channels_last = ctx, batch, int8, channels_last
+        self.first_pixels = batch * img * img
         self.lib = lib = ctx._lib
         t = torch
         adt = t.int8 if int8 else t.float32

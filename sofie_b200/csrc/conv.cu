@@ -26,6 +26,8 @@ struct sofie_b200_conv_plan {
                                // (r, s, c), so every 16-byte chunk of the unfolded matrix is one aligned vector copy
   int pair_out = 0;            // y_layout = 2: Y is channels-last TF32 pairs, [N, Ho, Wo, 2K]
   int stem = 0;                // 3-channel 3x3 int8 first layer with a channels-last output: unfold_c3k3_kernel + tensor-core contraction
+  int stem_pack = 1;           // output pixels per row of that contraction (1, 2 or 4; see stem_weights_kernel)
+  void *stem_vec = nullptr;    // stem_pack > 1: the per-channel epilogue vectors repeated per packed pixel, [2][stem_pack * K] words
   int implicit = 0;            // channels-last in and out on the tensor cores with no unfolded copy: the contraction's TMA producer reads
                                // the input tensor itself in im2col mode (gemm_umma.cu); no workspace
   sofie_b200_gemm_plan *gemm = nullptr;
@@ -267,6 +269,29 @@ __global__ void __launch_bounds__(256) unfold_c3k3_kernel(const int8_t *__restri
       }
   xcol[2 * gp] = make_uint4(w[0], w[1], w[2], w[3]);
   xcol[2 * gp + 1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+// As a contraction with one output pixel per row the first layer is [pixels, 32] x [32, K]: 128 x K tiles with a fraction of
+// one K block each, and the kernel's cost per TILE (one TMA load whose 128-byte box is a quarter data, the accumulator hand-over,
+// an epilogue warp's fixed work) sets the pace, not its arithmetic.  P consecutive pixels' rows are P * 32 contiguous bytes, and
+// their P * K outputs are contiguous in a channels-last Y, so the same memory is also the contraction
+// [pixels / P, P * 32] x [P * 32, P * K] with block-diagonal filters: a quarter of the tiles, full 128-byte rows, 256 columns.
+// Filters [K][32] -> [P * K][P * 32]: row q * K + k holds filter k in columns [32 q, 32 q + 32), zeros elsewhere.
+__global__ void __launch_bounds__(256) stem_weights_kernel(const int8_t *__restrict__ w, int8_t *__restrict__ out, int K, int P) {
+  const int total = P * K * P * 32;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int row = i / (P * 32), col = i - row * (P * 32);
+    const int q = row / K, k = row - q * K;
+    out[i] = (col >> 5) == q ? w[k * 32 + (col & 31)] : (int8_t)0;
+  }
+}
+// A per-channel vector of 4-byte words repeated P times (scale and bias of the packed contraction's P * K columns).
+__global__ void __launch_bounds__(256) repeat_words_kernel(const uint32_t *__restrict__ a, const uint32_t *__restrict__ b, uint32_t *__restrict__ out,
+                                                           int K, int P) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= P * K) return;
+  if (a) out[i] = a[i % K];
+  if (b) out[P * K + i] = b[i % K];
 }
 
 // ---- stride-2 implicit convolution over pixel pairs -------------------------------------------------------------------
@@ -800,8 +825,30 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
 
   g.K = p->kpad; g.lda = p->kpad; g.ldb = p->kpad; g.stride_b = p->pix_rows ? 0 : Ho * Wo * p->kpad;
   g.precise = d.precise;
+  if (p->stem) {
+    // P output pixels per row of the contraction (see stem_weights_kernel): as many as keep P * K columns within one tile
+    int P = 4;
+    while (P > 1 && (d.K * P > 256 || (images * Ho * Wo) % P != 0)) P >>= 1;
+    if (P > 1) {
+      void *wb = nullptr;
+      if (cudaMalloc(&wb, (size_t)(P * d.K) * (size_t)(P * 32)) != cudaSuccess || cudaMalloc(&p->stem_vec, (size_t)(2 * P * d.K) * 4) != cudaSuccess) {
+        cudaGetLastError();
+        if (wb) cudaFree(wb);
+        cudaFree(p->w_padded);
+        delete p;
+        return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: allocating the packed first-layer filters failed");
+      }
+      stem_weights_kernel<<<(unsigned)((P * d.K * P * 32 + 255) / 256), 256, 0, ctx->stream>>>((const int8_t *)p->w_padded, (int8_t *)wb, (int)d.K, P);
+      ctx->launches++;
+      cudaStreamSynchronize(ctx->stream);   // the unpacked copy is read by the kernel above
+      cudaFree(p->w_padded);
+      p->w_padded = wb;
+      p->stem_pack = P;
+      g.M = images * Ho * Wo / P; g.N = P * d.K; g.K = P * 32; g.lda = g.ldb = P * 32; g.ldy = P * d.K;
+    }
+  }
   rc = sofie_b200_gemm_plan_create(ctx, &g, &p->gemm);
-  if (rc) { cudaFree(p->w_padded); delete p; return rc; }
+  if (rc) { cudaFree(p->w_padded); if (p->stem_vec) cudaFree(p->stem_vec); delete p; return rc; }
   *out = p;
   return 0;
 }
@@ -811,6 +858,7 @@ int sofie_b200_conv_plan_destroy(sofie_b200_conv_plan *plan) {
   cudaSetDevice(plan->ctx->device);
   if (plan->gemm) sofie_b200_gemm_plan_destroy(plan->gemm);
   if (plan->w_padded) cudaFree(plan->w_padded);
+  if (plan->stem_vec) cudaFree(plan->stem_vec);
   delete plan;
   return 0;
 }
@@ -954,6 +1002,21 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
       e.ldr = d.K;
     }
     const long long kw = plan->split ? 2 * plan->kpad : plan->kpad;
+    if (plan->stem_pack > 1) {
+      // the packed contraction has stem_pack * K columns: its per-channel vectors are the caller's, repeated
+      const int P = plan->stem_pack, K = (int)d.K;
+      const bool per_channel_bias = e.bias && (e.bias_mode == SOFIE_B200_BIAS_COL_F32 || e.bias_mode == SOFIE_B200_BIAS_COL_I32);
+      if (e.col_scale || per_channel_bias) {
+        repeat_words_kernel<<<(unsigned)((P * K + 255) / 256), 256, 0, ctx->stream>>>((const uint32_t *)e.col_scale, per_channel_bias ? (const uint32_t *)e.bias : nullptr,
+                                                                                   (uint32_t *)plan->stem_vec, K, P);
+        SB_CUDA(cudaGetLastError());
+        ctx->launches++;
+        if (e.col_scale) e.col_scale = (const float *)plan->stem_vec;
+        if (per_channel_bias) e.bias = (const uint32_t *)plan->stem_vec + P * K;
+      }
+      e.ldr = (long long)P * K;
+      return sofie_b200_gemm_enqueue(plan->gemm, workspace, plan->w_padded, Y, &e);
+    }
     for (int g = 0; g < d.groups; ++g) {
       sofie_b200_epilogue eg = e;
       if (eg.col_scale) eg.col_scale += g * plan->kg;
