@@ -25,6 +25,10 @@ struct TensorLifeInfo {
 struct MemoryResult {
    int64_t total_bytes = 0;
    std::vector<int64_t> offsets;
+   // free space inside the footprint at the moment it last grew (the reference snapshots the same two figures there,
+   // MemoryPlanner.inc:119-126, and the emitted Session reports them and the fragmentation derived from them)
+   int64_t total_free_bytes = 0;
+   int64_t largest_free_block = 0;
 };
 
 constexpr int64_t kArenaAlignment = 256;
@@ -66,6 +70,12 @@ public:
          it->second += next->second;
          fBlocks.erase(next);
       }
+   }
+
+   void Stats(int64_t &total, int64_t &largest) const
+   {
+      total = largest = 0;
+      for (auto &b : fBlocks) { total += b.second; largest = std::max(largest, b.second); }
    }
 
 private:
@@ -111,6 +121,7 @@ inline MemoryResult OrganizeMemory(const std::vector<TensorLifeInfo> &tensors)
          if (off < 0) {
             off = res.total_bytes;
             res.total_bytes += need;
+            fl.Stats(res.total_free_bytes, res.largest_free_block);
          }
          res.offsets[e.idx] = off;
       }

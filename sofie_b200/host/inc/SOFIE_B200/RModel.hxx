@@ -133,6 +133,7 @@ private:
    std::string fGC;  // generated code
    std::vector<ArenaRegion> fRegions;
    int64_t fArenaBytes = 0, fPoolBytes = 0, fUnplannedBytes = 0, fWeightBytes = 0;
+   size_t fPoolFreeBytes = 0, fPoolLargestFree = 0;   // free space inside the pool when its footprint last grew
    std::vector<std::string> fFusionLog;
 };
 

@@ -480,6 +480,8 @@ void RModel::PlanArena()
       fRegions.push_back(pooled[i]);
    }
    fPoolBytes = res.total_bytes;
+   fPoolFreeBytes = size_t(res.total_free_bytes);
+   fPoolLargestFree = size_t(res.largest_free_block);
    fArenaBytes = off + res.total_bytes;
 }
 
@@ -574,7 +576,7 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    o << "// Code generated automatically by SOFIE_B200 (B200 / sm_100a target) from the model " << fName << "\n";
    o << "// Link with libsofie_b200 and the CUDA runtime.\n";
    o << "#ifndef SOFIE_B200_" << guard << "\n#define SOFIE_B200_" << guard << "\n\n";
-   o << "#include <cuda_runtime.h>\n#include <cstdint>\n#include <cstdio>\n#include <fstream>\n#include <iterator>\n#include <limits>\n#include <stdexcept>\n#include <string>\n#include <vector>\n";
+   o << "#include <cuda_runtime.h>\n#include <cstdint>\n#include <cstdio>\n#include <fstream>\n#include <iterator>\n#include <limits>\n#include <span>\n#include <stdexcept>\n#include <string>\n#include <vector>\n";
    o << "#include \"sofie_b200.h\"\n\nnamespace SOFIE_" << fName << " {\n\n";
    if (customMem) {
       o << "// One block for weights, inputs, outputs and the pooled intermediates: alloc is called once by the\n"
@@ -845,6 +847,24 @@ std::string RModel::GenerateSessionCode_GPU_B200()
       o << "      for (size_t i = 0; i + 1 < fProfEvents.size(); ++i) { float ms = 0; if (cudaEventElapsedTime(&ms, fProfEvents[i], fProfEvents[i + 1]) == cudaSuccess) fProfTotalMs[i] += ms; }\n      ++fProfCalls;\n";
    }
    o << "      return r;\n   }\n";
+   // the reference's span form (RModel_ALPAKA.cxx:814-838): views of the inputs in, results copied into the caller's output views
+   o << "   // runs the model on device pointers to the inputs, copies every output into the caller's device buffers and waits\n";
+   o << "   void infer(std::span<const void *const> inputs, std::span<void *const> outputs)\n   {\n";
+   o << "      if (inputs.size() != " << nIn << " || outputs.size() != " << fOutputTensorNames.size() << ") throw std::runtime_error(\"SOFIE_B200 Session::infer: expected " << nIn
+     << " input and " << fOutputTensorNames.size() << " output views\");\n";
+   {
+      std::string spanArgs;
+      for (size_t i = 0; i < nIn; ++i)
+         spanArgs += (i ? ", " : "") + std::string("static_cast<const ") + ConvertTypeToString(typeOf(fInputTensorNames[i])) + " *>(inputs[" + std::to_string(i) + "])";
+      o << "      Enqueue(" << spanArgs << ");\n";
+   }
+   for (size_t i = 0; i < fOutputTensorNames.size(); ++i) {
+      const std::string &n = fOutputTensorNames[i];
+      const std::string src = outMember(n).empty() ? "tensor_" + ResolveAliasTensor(n) : outMember(n);
+      o << "      CheckCuda(cudaMemcpyAsync(outputs[" << i << "], " << src << ", " << ConvertShapeToLength(GetTensorShape(n)) * GetTypeSize(typeOf(n))
+        << ", cudaMemcpyDeviceToDevice, stream), \"output copy\");\n";
+   }
+   o << "      Check(sofie_b200_ctx_sync(ctx), \"infer\");\n   }\n";
    o << "   // output i of the graph (device pointer), valid after infer()\n   const void *output(size_t i) const\n   {\n      switch (i) {\n";
    for (size_t i = 0; i < fOutputTensorNames.size(); ++i) o << "      case " << i << ": return " << outMember(fOutputTensorNames[i]) << ";\n";
    o << "      default: throw std::runtime_error(\"SOFIE_B200 Session::output: index out of range\");\n      }\n   }\n";
@@ -913,6 +933,10 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    o << "   // zeroes the pooled intermediates (the reference's resetState)\n";
    o << "   void resetState()\n   {\n      CheckCuda(cudaMemsetAsync(fArena + (kArenaBytes - kPoolBytes), 0, kPoolBytes, stream), \"resetState\");\n   }\n";
    o << "   size_t GetIntermediateMemoryPoolSize() const { return kPoolBytes; }\n";
+   o << "   // free space inside the pool when its footprint last grew, as the reference reports it (RModel_ALPAKA.cxx:1262-1269)\n";
+   o << "   size_t GetTotalFreeMemory() const { return " << fPoolFreeBytes << "; }\n";
+   o << "   size_t GetLargestFreeBlock() const { return " << fPoolLargestFree << "; }\n";
+   o << "   double GetFragmentation() const { return GetTotalFreeMemory() == 0 ? 0.0 : 1.0 - double(GetLargestFreeBlock()) / double(GetTotalFreeMemory()); }\n";
    o << "   size_t GetArenaSize() const { return kArenaBytes; }\n";
    o << "   long long GetLaunchCount() const { return sofie_b200_ctx_launch_count(ctx); }\n";
    if (profile) {

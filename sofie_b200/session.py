@@ -35,6 +35,17 @@ extern "C" const void *sess_infer_nosync(void *s, const void *const *in)
 {{
    try {{ return static_cast<S *>(s)->infer_nosync({dev_args}); }} catch (const std::exception &e) {{ g_err = e.what(); return nullptr; }}
 }}
+// the span form: device views of the inputs in, results copied into the caller's device buffers, returns when done
+extern "C" int sess_infer_span(void *s, const void *const *in, unsigned long long n_in, void *const *out, unsigned long long n_out)
+{{
+   try {{ static_cast<S *>(s)->infer(std::span<const void *const>(in, n_in), std::span<void *const>(out, n_out)); return 0; }}
+   catch (const std::exception &e) {{ g_err = e.what(); return -1; }}
+}}
+extern "C" void sess_pool_stats(void *s, unsigned long long *pool, unsigned long long *free_bytes, unsigned long long *largest, double *fragmentation)
+{{
+   const S *p = static_cast<S *>(s);
+   *pool = p->GetIntermediateMemoryPoolSize(); *free_bytes = p->GetTotalFreeMemory(); *largest = p->GetLargestFreeBlock(); *fragmentation = p->GetFragmentation();
+}}
 extern "C" int sess_sync(void *s)
 {{
    try {{ S::Check(sofie_b200_ctx_sync(static_cast<S *>(s)->ctx), "sync"); return 0; }} catch (const std::exception &e) {{ g_err = e.what(); return -1; }}
@@ -94,6 +105,8 @@ class EmittedSession:
         lib.sess_infer_nosync.restype = C.c_void_p
         lib.sess_infer_nosync.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
         lib.sess_sync.argtypes = [C.c_void_p]
+        lib.sess_infer_span.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_ulonglong, C.POINTER(C.c_void_p), C.c_ulonglong]
+        lib.sess_pool_stats.argtypes = [C.c_void_p, C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong), C.POINTER(C.c_double)]
         lib.sess_infer_host.restype = C.c_long
         lib.sess_infer_host.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p, C.c_long]
         lib.sess_infer_host_many.argtypes = [C.c_void_p, C.c_ulonglong, C.POINTER(C.POINTER(C.c_void_p)), C.POINTER(C.c_void_p)]
@@ -110,6 +123,19 @@ class EmittedSession:
         if not r:
             raise RuntimeError(f"Session {self.name}: {self.lib.sess_error().decode()}")
         return r
+
+    def infer_span(self, device_in_ptrs, device_out_ptrs) -> None:
+        """The Session's span form of infer: device pointers of the inputs and of caller-owned output buffers; returns when
+        the outputs are written."""
+        ins = (C.c_void_p * len(device_in_ptrs))(*device_in_ptrs)
+        outs = (C.c_void_p * len(device_out_ptrs))(*device_out_ptrs)
+        if self.lib.sess_infer_span(self.h, ins, len(device_in_ptrs), outs, len(device_out_ptrs)) != 0:
+            raise RuntimeError(f"Session {self.name}: {self.lib.sess_error().decode()}")
+
+    def pool_stats(self) -> dict:
+        pool, free, largest, frag = C.c_ulonglong(), C.c_ulonglong(), C.c_ulonglong(), C.c_double()
+        self.lib.sess_pool_stats(self.h, C.byref(pool), C.byref(free), C.byref(largest), C.byref(frag))
+        return {"pool": pool.value, "free": free.value, "largest_free": largest.value, "fragmentation": frag.value}
 
     def sync(self) -> None:
         if self.lib.sess_sync(self.h) != 0:

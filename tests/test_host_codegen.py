@@ -60,6 +60,10 @@ def test_emit_and_compile_every_golden_model(name, emit, tmp_path):
     assert "alpaka" not in text and text.count('"arena allocation"') == 1 and text.count("cudaMalloc(") == 2 and '"queue buffers"' in text
     for member in ("Enqueue(", "SetUseCudaGraph(", "infer_host_many(", "cudaGraphLaunch("):
         assert member in text
+    # the reference's span form of infer and its pool statistics (RModel_ALPAKA.cxx:814-838, 1262-1269)
+    for member in ("infer(std::span<const void *const> inputs, std::span<void *const> outputs)", "GetTotalFreeMemory()", "GetLargestFreeBlock()",
+                   "GetFragmentation()", "GetIntermediateMemoryPoolSize()"):
+        assert member in text
     chk = syntax_check(tmp_path / f"{name}.hxx")
     assert chk.returncode == 0, chk.stderr[:2000]
 

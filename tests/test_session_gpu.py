@@ -285,3 +285,31 @@ def test_int8_convnet_session_with_the_first_layer_on_tensor_cores(tmp_path, ora
     floor = float(np.sqrt(np.mean(np.square(want))))
     assert np.all(np.abs(y - want) <= 1e-5 * np.maximum(np.abs(want), floor)), np.abs(y - want).max()
     sess.close()
+
+
+def test_span_infer_and_pool_statistics(tmp_path, b200_lib):
+    """The span form of infer (device views in, results copied into caller-owned device buffers, as the reference's
+    infer(span<ViewConst>, span<View>)) against infer_host on the MLP, a wrong number of views refused, and the pool's
+    free-space figures of the reference's Session (pool size, free bytes and largest free block when the footprint last
+    grew, the fragmentation derived from them)."""
+    import torch
+    from sofie_b200.session import EmittedSession
+    rng = np.random.default_rng(3)
+    w1, w2 = (rng.standard_normal((64, 256)) * 0.1).astype(np.float32), (rng.standard_normal((256, 10)) * 0.1).astype(np.float32)
+    b1, b2 = rng.standard_normal(256).astype(np.float32), rng.standard_normal(10).astype(np.float32)
+    nodes = [{"op": "Gemm", "in": ["X", "w1", "b1"], "out": ["h"], "attrs": {}}, {"op": "Relu", "in": ["h"], "out": ["r"], "attrs": {}},
+             {"op": "Gemm", "in": ["r", "w2", "b2"], "out": ["Y"], "attrs": {}}]
+    sess = EmittedSession("mlp_span", nodes, {"w1": w1, "b1": b1, "w2": w2, "b2": b2}, [("X", [128, 64])], ["Y"], tmp_path)
+    x = rng.standard_normal((128, 64)).astype(np.float32)
+    want = np.zeros((128, 10), dtype=np.float32)
+    assert sess.infer_host([x], want) == want.size
+    assert np.allclose(want, np.maximum(x @ w1 + b1, 0) @ w2 + b2, rtol=1e-4, atol=1e-4)
+    dx = torch.from_numpy(x).cuda()
+    dy = torch.zeros((128, 10), dtype=torch.float32, device="cuda:0")
+    sess.infer_span([dx.data_ptr()], [dy.data_ptr()])
+    assert np.array_equal(dy.cpu().numpy(), want)
+    with pytest.raises(RuntimeError, match="expected 1 input and 1 output"):
+        sess.infer_span([dx.data_ptr(), dx.data_ptr()], [dy.data_ptr()])
+    st = sess.pool_stats()
+    assert st["pool"] > 0 and st["largest_free"] <= st["free"] <= st["pool"] and 0.0 <= st["fragmentation"] < 1.0
+    sess.close()
