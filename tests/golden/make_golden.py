@@ -11,7 +11,7 @@ the benchmark MLP, one <Name>.npz is written holding
             when the test that uses it feeds inA
   inB<i>, outB   a seeded N(0,1) input and the reference code's output for it
 
-usage:  make -C oracle ref && python tests/golden/make_golden.py [/root/reference]
+usage:  make -C oracle ref REF=<reference checkout> && python tests/golden/make_golden.py <reference checkout>
 """
 from __future__ import annotations
 
