@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(256, (MODE == 0 ? (CH >= 16 ? 2 : (CH >= 8 && 
 // All 16-byte loads of the R rows of a trip are issued before the first use; the rows are unpacked to fp32 once and
 // the three passes (sum, squared deviations, output) run on registers; the R reductions of a pass interleave.
 template <typename TIn, typename TOut, int CH, int R>
-__global__ void __launch_bounds__(256, 3) layernorm_warp_kernel(const TIn *__restrict__ x, TOut *__restrict__ y, long long rows, int cols,
+__global__ void __launch_bounds__(256, 2) layernorm_warp_kernel(const TIn *__restrict__ x, TOut *__restrict__ y, long long rows, int cols,
                                                                 const float *__restrict__ scale, const float *__restrict__ bias, float eps,
                                                                 float *__restrict__ mean_out, float *__restrict__ invstd_out) {
   constexpr int E = Vec16<TIn>::E, P = E / 2;   // elements and fp32 pairs per 16-byte chunk

@@ -52,9 +52,6 @@ struct Epi16Warp {
   int steps_per_seg;  // 16-column steps per flushed row segment
   int seg_units;      // 16-byte units of a complete segment
   int out_class;      // OUT16_*
-#ifdef SB200_EXP_DIRECT
-  bool direct_ok;     // this lane's row exists (experiment: 256-bit stores straight from registers)
-#endif
 };
 __device__ __forceinline__ Epi16Warp epi16_warp_init(const EpiParams &ep, uint32_t stage_base) {
   Epi16Warp w;
@@ -252,14 +249,6 @@ __device__ __forceinline__ void epi16_step(const EpiParams &ep, const Epi16Warp 
       __nv_bfloat162 h2 = __floats2bfloat162_rn(v[u].x, v[u].y);
       p[u] = *reinterpret_cast<uint32_t *>(&h2);
     }
-#ifdef SB200_EXP_DIRECT
-    {
-      __nv_bfloat16 *dst = (__nv_bfloat16 *)ep.Y + b * ep.stride_y + rr * ep.ldy + col0;
-      if (w.direct_ok) asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(p[0]), "r"(p[1]), "r"(p[2]), "r"(p[3]),
-                                    "r"(p[4]), "r"(p[5]), "r"(p[6]), "r"(p[7]) : "memory");
-      return;
-    }
-#endif
     st_shared_v4(w.row_addr + o0, p[0], p[1], p[2], p[3]);
     st_shared_v4(w.row_addr + (o0 ^ 16u), p[4], p[5], p[6], p[7]);
   } else if (OUT == OUT16_F32) {
@@ -303,11 +292,6 @@ __device__ __forceinline__ void drain16(const EpiParams &ep, const Epi16Warp &w,
   const long long rr = row < rows_total ? row : rows_total - 1;   // rows past the end compute on the last row's operands
   int units = 0, seg_col = 0;
   bool store_pending = false;
-#ifdef SB200_EXP_DIRECT
-  Epi16Warp wd = w;
-  wd.direct_ok = row < rows_total;
-  const bool direct = OUT == OUT16_BF16 && fast;
-#endif
   uint32_t raw[16];
   ptx::tmem_ld_x16(taddr + 16 * st, raw);
 #pragma unroll 1
@@ -326,13 +310,8 @@ __device__ __forceinline__ void drain16(const EpiParams &ep, const Epi16Warp &w,
     }
     ptx::tmem_ld_wait();
     if (fast && c_end - c >= 16) {
-#ifdef SB200_EXP_DIRECT
-      epi16_step<ACC_INT, OUT, FL>(ep, wd, raw, taddr + 16 * st2, has_next, b, rr, n0 + c, j);
-      if (!direct) units += UNITS;
-#else
       epi16_step<ACC_INT, OUT, FL>(ep, w, raw, taddr + 16 * st2, has_next, b, rr, n0 + c, j);
       units += UNITS;
-#endif
     } else {
       if (store_chunk<16>(ep, raw, b, row, n0 + c, min(16, c_end - c), vec, w.stage, rows_total, j)) units += UNITS;
       if (has_next) ptx::tmem_ld_x16(taddr + 16 * st2, raw);
