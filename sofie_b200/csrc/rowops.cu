@@ -435,7 +435,7 @@ static int launch_rows(sofie_b200_ctx *ctx, const void *x, void *y, long long ro
   if (MODE == 0 && aligned && chunks > 16 && chunks <= (sizeof(TIn) == 2 ? 64 : 128) && rows >= 4096) {
     // rows of 16 to 128 chunks, enough of them to fill the machine: one warp per row, parameters in registers
     const int ch = (int)((chunks + 31) / 32);
-    const unsigned grid = (unsigned)std::min<long long>((rows + 31) / 32, (long long)ctx->sm_count * 3);
+    const unsigned grid = (unsigned)std::min<long long>((rows + 31) / 32, (long long)ctx->sm_count * 2);
     const TIn *xi = (const TIn *)x;
     TOut *yo = (TOut *)y;
     if constexpr (MODE == 0) {
