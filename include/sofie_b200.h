@@ -432,6 +432,14 @@ int sofie_b200_dequantize_enqueue(sofie_b200_ctx *ctx, const void *q, float *x, 
 int sofie_b200_transpose_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t dtype, int32_t rank,
                                  const int64_t *in_shape, const int32_t *perm);
 
+/* The depth taps of a 3-D convolution as channels (the reference's Conv takes rank-5 inputs through the same im2col + matmul
+ * loop as rank-4 ones, ROperator_Conv.hxx:123-262 shapes, :406-642 code): x [n, c, d, hw] -> y [n * d_out, c * taps, hw] with
+ * y[(n, od), (c, t), :] = x[n, c, od * stride_d - pad_front + t * dil_d, :], zero outside the depth range.  A 3-D convolution is
+ * then this call, a 2-D convolution over n * d_out slices of c * taps channels (the weights [K, C, T, R, S] are [K, C * T, R, S]
+ * as stored) and a transpose of [n, d_out, K, Ho * Wo] to [n, K, d_out, Ho * Wo].  F32 or 8-bit elements. */
+int sofie_b200_depth_unfold_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t dtype, int64_t n, int64_t c, int64_t d, int64_t hw,
+                                    int64_t taps, int64_t d_out, int64_t stride_d, int64_t pad_front, int64_t dil_d);
+
 /* Type conversion between F32, BF16 and F8E4M3 (saturating round-to-nearest-even; I8 as a source too), with an
  * optional per-row scale: y[r,c] = cvt(x[r,c] / row_scale[r]) (row_scale may be NULL). */
 int sofie_b200_convert_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t x_dtype, int32_t y_dtype,

@@ -227,6 +227,20 @@ __global__ void __launch_bounds__(256) permute_kernel(const U *__restrict__ x, U
   }
 }
 
+// The depth taps of a 3-D convolution as channels: y[(n, od), (c, t), hw] = x[n, c, od * stride - pad + t * dil, hw], zero
+// outside the depth range.  With the taps there, a 3-D convolution over [N,C,D,H,W] is a 2-D one over N * Do slices of C * T
+// channels, and its weights [K, C, T, R, S] are the 2-D ones [K, C * T, R, S] as they lie in memory.
+template <typename W>
+__global__ void __launch_bounds__(256) depth_unfold_kernel(const W *__restrict__ x, W *__restrict__ y, long long total, long long c, long long d, long long hw,
+                                                           long long taps, long long d_out, long long stride_d, long long pad_front, long long dil_d) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long p = i % hw, ct = (i / hw) % (c * taps), nd = i / (hw * c * taps);
+    const long long t = ct % taps, ch = ct / taps, od = nd % d_out, n = nd / d_out;
+    const long long z = od * stride_d - pad_front + t * dil_d;
+    y[i] = (z >= 0 && z < d) ? x[((n * c + ch) * d + z) * hw + p] : (W)0;
+  }
+}
+
 }  // namespace sb200
 
 using namespace sb200;
@@ -343,6 +357,24 @@ int sofie_b200_dequantize_enqueue(sofie_b200_ctx *ctx, const void *q, float *x, 
   else if (q_dtype == SOFIE_B200_U8) dequantize_kernel<uint8_t><<<g, 256, 0, ctx->stream>>>((const uint8_t *)q, x, n, scale, zero_point, channels, inner);
   else if (q_dtype == SOFIE_B200_I32) dequantize_kernel<int><<<g, 256, 0, ctx->stream>>>((const int *)q, x, n, scale, zero_point, channels, inner);
   else return fail(SOFIE_B200_ERR_INVALID, "dequantize_enqueue: type %d not supported", q_dtype);
+  SB_LAUNCHED();
+}
+
+int sofie_b200_depth_unfold_enqueue(sofie_b200_ctx *ctx, const void *x, void *y, int32_t dtype, int64_t n, int64_t c, int64_t d, int64_t hw,
+                                    int64_t taps, int64_t d_out, int64_t stride_d, int64_t pad_front, int64_t dil_d) {
+  SB_PRELUDE("depth_unfold_enqueue");
+  const int es = dtype_size(dtype);
+  if (es != 1 && es != 4) return fail(SOFIE_B200_ERR_INVALID, "depth_unfold_enqueue: 1- and 4-byte element types only (type %d)", dtype);
+  if (n < 0 || c < 1 || d < 1 || hw < 1 || taps < 1 || d_out < 1 || stride_d < 1 || dil_d < 1 || pad_front < 0)
+    return fail(SOFIE_B200_ERR_INVALID, "depth_unfold_enqueue: bad extent");
+  const long long total = n * d_out * c * taps * hw;
+  if (total == 0) return 0;
+  if (!x || !y) return fail(SOFIE_B200_ERR_INVALID, "depth_unfold_enqueue: NULL tensor");
+  const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 32);
+  if (es == 4)
+    depth_unfold_kernel<uint32_t><<<grid, 256, 0, ctx->stream>>>((const uint32_t *)x, (uint32_t *)y, total, c, d, hw, taps, d_out, stride_d, pad_front, dil_d);
+  else
+    depth_unfold_kernel<uint8_t><<<grid, 256, 0, ctx->stream>>>((const uint8_t *)x, (uint8_t *)y, total, c, d, hw, taps, d_out, stride_d, pad_front, dil_d);
   SB_LAUNCHED();
 }
 

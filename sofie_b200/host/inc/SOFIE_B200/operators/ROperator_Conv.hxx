@@ -6,7 +6,9 @@
 // the reference's own default of pads = 1 when auto_pad is NOTSET and no pads are given.
 // Where the reference emits a host loop of per-image im2col + blas.matmul (:985-1103), this
 // operator emits one sofie_b200_conv_plan (weights re-laid once) and one enqueue over the batch.
-// 1-D and 2-D convolutions (a 1-D one is a 2-D one of height 1); 3-D is rejected.
+// 1-D and 2-D convolutions (a 1-D one is a 2-D one of height 1).  A 3-D convolution is emitted as three calls: the depth
+// taps are unfolded into channels (X [N,C,D,H,W] -> [N*Do, C*T, H, W]; the weights [K,C,T,R,S] are already [K, C*T, R, S] in
+// memory), the 2-D convolution runs over the N*Do slices, and the result [N*Do, K, Ho, Wo] is transposed to [N,K,Do,Ho,Wo].
 #pragma once
 #include "SOFIE_B200/operators/ROperator_Gemm.hxx"
 
@@ -16,6 +18,10 @@ struct ConvGeometry {
    size_t N = 0, C = 0, H = 1, W = 1, K = 0, R = 1, S = 1, Ho = 1, Wo = 1, group = 1;
    size_t pads[4] = {0, 0, 0, 0};  // top, left, bottom, right
    size_t strides[2] = {1, 1}, dil[2] = {1, 1};
+   // A 3-D convolution lowered to 2-D: N and C above are then N*Do and C*T of the 2-D convolution that runs; these are the
+   // extents of the original tensors and the depth taps.
+   size_t N3 = 0, C3 = 0, D = 1, T = 1, Do = 1, padFront = 0, padBack = 0, strideD = 1, dilD = 1;
+   bool Is3D() const { return N3 != 0; }
 };
 
 // Shape rules of ROperator_Conv.hxx:123-262 for rank-3 and rank-4 inputs.
@@ -24,8 +30,38 @@ inline ConvGeometry ConvShapeInference(const std::vector<size_t> &x, const std::
                                        std::vector<size_t> pads, std::vector<size_t> strides)
 {
    const size_t dim = x.size() - 2;
-   if (dim < 1 || dim > 2) throw std::runtime_error("SOFIE Conv Op Shape inference - only 1-D and 2-D convolutions are on the B200 path");
+   if (dim < 1 || dim > 3) throw std::runtime_error("SOFIE Conv Op Shape inference - invalid inputs ");
    if (w.size() - 2 != dim) throw std::runtime_error("SOFIE Conv Op Shape inference - invalid weights ");
+   if (dim == 3) {
+      // depth first (ROperator_Conv.hxx:123-262 treats the three spatial ranks alike), then the 2-D rules on the slices
+      const size_t T = kernel.empty() ? w[2] : kernel[0];
+      if (dilations.empty()) dilations = {1, 1, 1};
+      if (strides.empty()) strides = {1, 1, 1};
+      dilations.resize(3, 1); strides.resize(3, 1);
+      const size_t et = T + (dilations[0] - 1) * (T - 1);
+      size_t front = 0, back = 0;
+      std::vector<size_t> pads2;
+      if (autopad == "NOTSET") {
+         if (pads.empty()) pads = {1, 1, 1, 1, 1, 1};   // the reference's default
+         if (pads.size() != 6) throw std::runtime_error("SOFIE Conv Op Shape inference - invalid pads for a 3-D convolution");
+         front = pads[0]; back = pads[3];
+         pads2 = {pads[1], pads[2], pads[4], pads[5]};
+      } else if (autopad == "SAME_UPPER" || autopad == "SAME_LOWER") {
+         const size_t out = (x[2] + strides[0] - 1) / strides[0];
+         const long total = std::max(0L, long((out - 1) * strides[0] + et) - long(x[2]));
+         front = autopad == "SAME_UPPER" ? total / 2 : total - total / 2;
+         back = size_t(total) - front;
+      } else if (autopad != "VALID") {
+         throw std::runtime_error("SOFIE Conv Op invalid fAutopad");
+      }
+      if (x[2] + front + back < et) throw std::runtime_error("SOFIE Conv Op -  invalid values");
+      const size_t Do = (x[2] + front + back - et) / strides[0] + 1;
+      const size_t grp = group == 0 ? x[1] / w[1] : group;
+      ConvGeometry g = ConvShapeInference({x[0] * Do, x[1] * T, x[3], x[4]}, {w[0], w[1] * T, w[3], w[4]}, autopad, {dilations[1], dilations[2]}, grp,
+                                          kernel.empty() ? std::vector<size_t>{} : std::vector<size_t>{kernel[1], kernel[2]}, pads2, {strides[1], strides[2]});
+      g.N3 = x[0]; g.C3 = x[1]; g.D = x[2]; g.T = T; g.Do = Do; g.padFront = front; g.padBack = back; g.strideD = strides[0]; g.dilD = dilations[0];
+      return g;
+   }
    ConvGeometry g;
    g.N = x[0]; g.C = x[1]; g.K = w[0];
    g.group = group == 0 ? x[1] / w[1] : group;
@@ -175,9 +211,10 @@ public:
       if (!model.IsInitializedTensor(fNW))
          throw std::runtime_error("SOFIE Conv Op: the B200 path re-lays the weights at Session construction and needs them initialized");
       fGeo = ConvShapeInference(fShapeX, fShapeW, fAttrAutopad, fAttrDilations, fAttrGroup, fAttrKernelShape, fAttrPads, fAttrStrides);
-      if (fShapeW[1] * fGeo.group != fGeo.C)
+      if (fShapeW[1] * fGeo.group != (fGeo.Is3D() ? fGeo.C3 : fGeo.C))
          throw std::runtime_error("SOFIE Conv Op: weight channels x group does not match the input channels");
       fShapeY = fShapeX.size() == 3 ? std::vector<size_t>{fGeo.N, fGeo.K, fGeo.Wo} : std::vector<size_t>{fGeo.N, fGeo.K, fGeo.Ho, fGeo.Wo};
+      if (fGeo.Is3D()) fShapeY = {fGeo.N3, fGeo.K, fGeo.Do, fGeo.Ho, fGeo.Wo};
       if (!fNB.empty()) {
          if (!model.CheckIfTensorAlreadyExist(fNB)) throw std::runtime_error("SOFIE Conv op Input Tensor " + fNB + " is not found in model");
          if (ConvertShapeToLength(model.GetTensorShape(fNB)) != fGeo.K)
@@ -223,6 +260,7 @@ public:
    bool FuseResidual(RModel &model, const std::string &residual, const std::string &newOutput) override
    {
       if (fEpi.act != EActivationType::UNDEFINED || !fEpi.residual.empty()) return false;
+      if (fGeo.Is3D()) return false;   // the 2-D convolution of a lowered 3-D one writes [N*Do, K, Ho, Wo], not the residual's layout
       if (model.GetTensorShape(residual) != fShapeY || model.GetTensorType(residual) != ETensorType::FLOAT) return false;
       fEpi.residual = residual;
       fInputTensorNames.push_back(residual);
@@ -241,7 +279,13 @@ public:
 
    std::vector<DeviceScratch> GetDeviceScratch_GPU_B200() const override
    {
-      return Workspace() ? std::vector<DeviceScratch>{{fNY + "_xcol", Workspace()}} : std::vector<DeviceScratch>{};
+      std::vector<DeviceScratch> s;
+      if (Workspace()) s.push_back({fNY + "_xcol", Workspace()});
+      if (fGeo.Is3D()) {
+         s.push_back({fNY + "_slices", fGeo.N * fGeo.C * fGeo.H * fGeo.W * sizeof(float)});        // X with the depth taps as channels
+         s.push_back({fNY + "_planes", fGeo.N * fGeo.K * fGeo.Ho * fGeo.Wo * sizeof(float)});     // [N*Do, K, Ho, Wo]
+      }
+      return s;
    }
 
    std::string GenerateSessionMembersCode_GPU_B200(std::string opName) override
@@ -273,8 +317,21 @@ public:
          out << "      ep_" << opName << ".residual = tensor_" << fEpi.residual << "; ep_" << opName << ".residual_dtype = "
              << ConvertTypeToRuntimeEnum(fResidualType) << ";\n";
       out << fEpi.BindCode("ep_" + opName);
-      out << "      Check(sofie_b200_conv_enqueue(plan_" << opName << ", tensor_" << fNX << ", tensor_" << fNY << ", "
-          << (Workspace() ? "tensor_" + fNY + "_xcol" : std::string("nullptr")) << ", &ep_" << opName << "), \"Conv " << opName << "\");\n";
+      const std::string ws = Workspace() ? "tensor_" + fNY + "_xcol" : std::string("nullptr");
+      if (fGeo.Is3D()) {
+         out << "      Check(sofie_b200_depth_unfold_enqueue(ctx, tensor_" << fNX << ", tensor_" << fNY << "_slices, SOFIE_B200_F32, " << fGeo.N3 << ", " << fGeo.C3
+             << ", " << fGeo.D << ", " << fGeo.H * fGeo.W << ", " << fGeo.T << ", " << fGeo.Do << ", " << fGeo.strideD << ", " << fGeo.padFront << ", " << fGeo.dilD
+             << "), \"Conv " << opName << ": depth taps\");\n";
+         out << "      Check(sofie_b200_conv_enqueue(plan_" << opName << ", tensor_" << fNY << "_slices, tensor_" << fNY << "_planes, " << ws << ", &ep_" << opName
+             << "), \"Conv " << opName << "\");\n";
+         out << "      {\n         const int64_t shape[4] = {" << fGeo.N3 << ", " << fGeo.Do << ", " << fGeo.K << ", " << fGeo.Ho * fGeo.Wo << "};\n"
+             << "         const int32_t perm[4] = {0, 2, 1, 3};\n"
+             << "         Check(sofie_b200_transpose_enqueue(ctx, tensor_" << fNY << "_planes, tensor_" << fNY << ", SOFIE_B200_F32, 4, shape, perm), \"Conv " << opName
+             << ": depth to its place\");\n      }\n";
+         return out.str();
+      }
+      out << "      Check(sofie_b200_conv_enqueue(plan_" << opName << ", tensor_" << fNX << ", tensor_" << fNY << ", " << ws << ", &ep_" << opName << "), \"Conv "
+          << opName << "\");\n";
       return out.str();
    }
    std::string GenerateDestroyCode_GPU_B200(std::string opName) override { return "      sofie_b200_conv_plan_destroy(plan_op_" + opName + ");\n"; }

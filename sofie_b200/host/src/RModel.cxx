@@ -362,6 +362,7 @@ void RModel::AssignConvLayouts()
       auto *c = dynamic_cast<ConvLayoutHooks *>(fOperators[k].get());
       if (!c) continue;
       const ConvGeometry &g = c->Geometry();
+      if (g.Is3D()) continue;   // a lowered 3-D convolution keeps the reference's layout on both sides
       int y = 0;
       if (!c->HasResidual()) {
          ROperator *next = sole(c->LayoutOutput());
@@ -815,7 +816,7 @@ std::string RModel::GenerateSessionCode_GPU_B200()
          same += " && g.in[" + std::to_string(i) + "] == tensor_" + fInputTensorNames[i];
          remember += " slot->in[" + std::to_string(i) + "] = tensor_" + fInputTensorNames[i] + ";";
       }
-      o << "   // with " << (profile ? "SetUseCudaGraph(true), " : "") << "the body is replayed from a CUDA graph (one launch instead of one per operator); a stream that is\n"
+      o << "   // " << (profile ? "with SetUseCudaGraph(true) " : "after the first call ") << "the body is replayed from a CUDA graph (one launch instead of one per operator); a stream that is\n"
            "   // already being captured by the caller just records the operators into the caller's graph\n";
       o << "   void SetUseCudaGraph(bool on) { fUseCudaGraph = on; }\n";
       o << "   void Enqueue(" << params << ")\n   {\n";

@@ -125,6 +125,7 @@ PROTOTYPES = {
     "sofie_b200_quantize_enqueue": (C.c_int, [_P, _P, _P, _I32, _I64, _P, _P, _I64, _I64]),
     "sofie_b200_dequantize_enqueue": (C.c_int, [_P, _P, _P, _I32, _I64, _P, _P, _I64, _I64]),
     "sofie_b200_transpose_enqueue": (C.c_int, [_P, _P, _P, _I32, _I32, C.POINTER(_I64), C.POINTER(_I32)]),
+    "sofie_b200_depth_unfold_enqueue": (C.c_int, [_P, _P, _P, _I32, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64]),
     "sofie_b200_convert_enqueue": (C.c_int, [_P, _P, _P, _I32, _I32, _I64, _I64, _P]),
     "sofie_b200_plan_arena": (C.c_int, [C.POINTER(TensorLife), _I64, C.POINTER(_I64), C.POINTER(_I64)]),
 }

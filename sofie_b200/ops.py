@@ -162,6 +162,13 @@ class Context:
         L.check(self._lib.sofie_b200_attention_enqueue(self._h, _ptr(qkv), _ptr(out), dtype_code(qkv.dtype), batch, seq, heads, head_dim,
                                                        float(scale)), "attention_enqueue")
 
+    def depth_unfold(self, x, y, taps, d_out, stride_d=1, pad_front=0, dil_d=1):
+        """x [n, c, d, h, w] -> y [n * d_out, c * taps, h, w]: the depth taps of a 3-D convolution as channels."""
+        n, c, d = x.shape[:3]
+        hw = int(x[0, 0, 0].numel())
+        L.check(self._lib.sofie_b200_depth_unfold_enqueue(self._h, _ptr(x), _ptr(y), dtype_code(x.dtype), n, c, d, hw, taps, d_out, stride_d, pad_front, dil_d),
+                "depth_unfold_enqueue")
+
     def transpose(self, x, y, perm):
         shape = (C.c_int64 * x.dim())(*x.shape)
         pm = (C.c_int32 * x.dim())(*perm)

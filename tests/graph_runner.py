@@ -304,6 +304,33 @@ def run_graph(fx: dict, inputs: list, backend) -> np.ndarray:
                              bool(at.get("transA", 0)), bool(at.get("transB", 0)), act, act_alpha)
         elif op == "Conv":
             x, w = ins[0], ins[1]
+            three_d = x.ndim == 5
+            if three_d:
+                # [N, C, D, H, W]: the depth taps become channels (x [N*Do, C*T, H, W], w [K, C*T, R, S] as it lies in memory), a
+                # 2-D convolution runs over the slices and its result [N*Do, K, Ho, Wo] is transposed to [N, K, Do, Ho, Wo]
+                xn, wn = backend.to_numpy(x), backend.to_numpy(w)
+                N3, C3, D3 = xn.shape[:3]
+                T = wn.shape[2]
+                at = dict(at)
+                dil3, st3 = list(at.get("dilations", [1, 1, 1])), list(at.get("strides", [1, 1, 1]))
+                p3 = list(at.get("pads", [1] * 6)) if at.get("auto_pad", "NOTSET") == "NOTSET" else None
+                if p3 is None:
+                    raise NotImplementedError("auto_pad on a 3-D convolution")
+                et = T + (dil3[0] - 1) * (T - 1)
+                Do3 = (D3 + p3[0] + p3[3] - et) // st3[0] + 1
+                xs = np.zeros((N3, Do3, C3, T) + xn.shape[3:], dtype=xn.dtype)
+                for od in range(Do3):
+                    for t in range(T):
+                        z = od * st3[0] - p3[0] + t * dil3[0]
+                        if 0 <= z < D3:
+                            xs[:, od, :, t] = xn[:, :, z]
+                x = backend.to_backend(np.ascontiguousarray(xs.reshape((N3 * Do3, C3 * T) + xn.shape[3:])))
+                w = backend.to_backend(np.ascontiguousarray(wn.reshape((wn.shape[0], wn.shape[1] * T) + wn.shape[3:])))
+                at["dilations"], at["strides"], at["pads"] = dil3[1:], st3[1:], [p3[1], p3[2], p3[4], p3[5]]
+                if "kernel_shape" in at:
+                    at["kernel_shape"] = list(at["kernel_shape"])[1:]
+                if "group" not in at or not at["group"]:
+                    at["group"] = C3 // wn.shape[1]
             one_d = x.ndim == 3   # [N, C, L]: a 2-D convolution of height 1 (ROperator_Conv.hxx:123-262 treats the ranks alike)
             if one_d:
                 x, w = x.reshape(x.shape[0], x.shape[1], 1, x.shape[2]), w.reshape(w.shape[0], w.shape[1], 1, w.shape[2])
@@ -318,6 +345,9 @@ def run_graph(fx: dict, inputs: list, backend) -> np.ndarray:
             y = backend.conv(x, w, ins[2] if len(ins) > 2 else None, geo, act, act_alpha)
             if one_d:
                 y = y.reshape(y.shape[0], y.shape[1], y.shape[3])
+            if three_d:
+                yn = backend.to_numpy(y)
+                y = backend.to_backend(np.ascontiguousarray(yn.reshape((N3, Do3) + yn.shape[1:]).transpose(0, 2, 1, 3, 4)))
         elif op == "BatchNormalization":
             y = backend.batchnorm(ins[0], ins[1], ins[2], ins[3], ins[4], float(at.get("epsilon", 1e-5)), act)
         elif op == "LayerNormalization":

@@ -395,6 +395,26 @@ def test_three_channel_first_layer_int8_on_tensor_cores(ctx, oracle, case):
     assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size}"
 
 
+@pytest.mark.parametrize("dt", [torch.float32, torch.int8])
+def test_depth_taps_as_channels(ctx, dt):
+    """sofie_b200_depth_unfold_enqueue against the same gather in numpy: stride, dilation and padding in depth."""
+    rng = np.random.default_rng(5)
+    n, c, d, h, w, taps, stride, pad, dil = 2, 3, 7, 4, 5, 3, 2, 2, 2
+    d_out = (d + 2 * pad - (taps + (dil - 1) * (taps - 1))) // stride + 1
+    x = (rng.standard_normal((n, c, d, h, w)) * 50).astype(np.float32 if dt == torch.float32 else np.int8)
+    want = np.zeros((n, d_out, c, taps, h, w), dtype=x.dtype)
+    for od in range(d_out):
+        for t in range(taps):
+            z = od * stride - pad + t * dil
+            if 0 <= z < d:
+                want[:, od, :, t] = x[:, :, z]
+    tx = torch.from_numpy(x).to(DEV)
+    ty = torch.full((n * d_out, c * taps, h, w), 77, dtype=dt, device=DEV)
+    ctx.depth_unfold(tx, ty, taps, d_out, stride, pad, dil)
+    ctx.sync()
+    assert np.array_equal(ty.cpu().numpy(), want.reshape(n * d_out, c * taps, h, w))
+
+
 IMPLICIT_CASES = {
     # name: (N, C, H, W, K, R, S, pads [top, left, bottom, right], strides [h, w], dilations [h, w], x zero point)
     "c64_3x3_tail": (2, 64, 13, 10, 48, 3, 3, [1, 1, 1, 1], [1, 1], [1, 1], 0),         # 64-byte K blocks, 260 pixels: a partial tile
