@@ -255,6 +255,37 @@ const char *sofie_b200_gemm_plan_kernel(const sofie_b200_gemm_plan *plan);
 int sofie_b200_gemm_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, void *Y,
                             const sofie_b200_epilogue *ep);
 
+/* Another GPU's memory for sofie_b200_gemm_enqueue_peers (the reference has no counterpart: one device per Session,
+ * core/src/RModel_ALPAKA.cxx:1123-1132).  Two ways to a pointer this ctx's kernels may store to:
+ *  - one process driving several GPUs: sofie_b200_ctx_enable_peer(ctx, other_device) once, after which any device pointer
+ *    of `other_device` is valid in this ctx's kernels;
+ *  - one process per GPU: the owner exports a device pointer (anywhere inside a cudaMalloc'ed allocation) to a 72-byte handle,
+ *    sends the bytes to the other process by any means, which opens it and receives a device pointer to the same byte.
+ *    Close every opened pointer before the owner frees the allocation.  A handle is opened once per process; opening the
+ *    same allocation again returns the mapping that is already there. */
+typedef struct sofie_b200_peer_handle {
+  unsigned char ipc[64]; /* the CUDA IPC handle of the allocation */
+  uint64_t offset;       /* of the exported pointer inside it     */
+} sofie_b200_peer_handle;
+int sofie_b200_ctx_enable_peer(sofie_b200_ctx *ctx, int32_t peer_device);
+int sofie_b200_peer_export(sofie_b200_ctx *ctx, const void *dev_ptr, sofie_b200_peer_handle *out);
+int sofie_b200_peer_open(sofie_b200_ctx *ctx, const sofie_b200_peer_handle *handle, void **dev_ptr);
+int sofie_b200_peer_close(sofie_b200_ctx *ctx, void *dev_ptr);
+
+/* The same contraction with its result written to further buffers as well: the tensor-parallel column split of a large
+ * Gemm.  The reference runs one Session per device and has no such split (core/src/RModel_ALPAKA.cxx:1123-1132: one device per
+ * Session); the call replaces what a split would otherwise need after blas.gemm (ROperator_Gemm.hxx:1066-1088) -- an
+ * all-gather of the column shards.  Each rank holds the columns [n0, n0 + N) of the weight, enqueues its [M, N] contraction
+ * with Y pointing at column n0 of its own full-width result (ldy = the full width) and peer_Y[i] at the same column of every
+ * other rank's result, mapped into this process (CUDA IPC or symmetric memory); the epilogue stores every finished row
+ * segment to Y and to each peer_Y[i] with one bulk tensor store each (plain peer stores over NVLink; no multicast), so when
+ * all ranks' kernels have finished every rank holds the whole [M, full width] result.  The ranks still have to meet before
+ * reading it (a barrier or any collective on the stream).  n_peers 0..7.  Needs a plan on the tensor-core kernel with B as
+ * it is stored (no B_CONSTANT re-layout), N a multiple of 64, 16-byte aligned outputs, pitches and epilogue vectors, and floating-point operands (bf16, f16, FP8
+ * or fp32; the int8 kernels have no register left for it and return SOFIE_B200_ERR_INVALID). */
+int sofie_b200_gemm_enqueue_peers(sofie_b200_gemm_plan *plan, const void *A, const void *B, void *Y, void *const *peer_Y, int32_t n_peers,
+                                  const sofie_b200_epilogue *ep);
+
 /* Same contraction with HOST operands: copies A and B to ctx-owned device staging buffers,
  * runs the plan, copies Y back and waits.  This is the shape of Session::infer on host data
  * (the CPU Session's infer(const float*), core/src/RModel.cxx:1303-1419).  Epilogue vectors

@@ -159,6 +159,7 @@ int sofie_b200_ctx_destroy(sofie_b200_ctx *ctx) {
     if (ctx->ev_done[i]) cudaEventDestroy(ctx->ev_done[i]);
     if (ctx->ev_out[i]) cudaEventDestroy(ctx->ev_out[i]);
   }
+  for (auto &m : ctx->peer_mappings) cudaIpcCloseMemHandle(m.base);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   delete ctx;
@@ -367,6 +368,28 @@ int sofie_b200_gemm_enqueue(sofie_b200_gemm_plan *plan, const void *A, const voi
   }
   if (plan->use_umma && d.K > 0) return umma_enqueue(plan, A, B, e);
   return simt_enqueue(plan, A, B, e);
+}
+
+int sofie_b200_gemm_enqueue_peers(sofie_b200_gemm_plan *plan, const void *A, const void *B, void *Y, void *const *peer_Y, int32_t n_peers,
+                                  const sofie_b200_epilogue *ep) {
+  if (n_peers == 0) return sofie_b200_gemm_enqueue(plan, A, B, Y, ep);
+  if (!plan) return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue_peers: plan is NULL");
+  const sofie_b200_gemm_desc &d = plan->desc;
+  if (n_peers < 0 || n_peers > sb200::UMMA_MAX_PEERS || !peer_Y) return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue_peers: 0 to %d peer outputs", sb200::UMMA_MAX_PEERS);
+  if (d.M == 0 || d.N == 0) return 0;
+  if (!A || !B || !Y) return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue_peers: NULL tensor pointer");
+  // every element must leave through a bulk store of a complete row segment (the only store that is repeated per peer):
+  // the tensor-core kernel on whole 64-column groups, with the epilogue's fast path
+  if (!plan->use_umma || plan->inner || plan->b_kmajor || plan->split_out || d.N % 64 != 0 || d.K <= 0)
+    return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue_peers: needs a plan on the tensor-core kernel with B as stored and N a multiple of 64");
+  if (d.ab_dtype == SOFIE_B200_I8 || d.ab_dtype == SOFIE_B200_U8)
+    return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue_peers: floating-point operands only (bf16, f16, FP8, fp32)");
+  EpiParams e;
+  int rc = make_epi(plan->desc, Y, ep, &e);
+  if (rc) return rc;
+  if (!e.fast) return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue_peers: epilogue vectors must be 16-byte aligned and the bias not a full matrix");
+  SB_CUDA(cudaSetDevice(plan->ctx->device));
+  return umma_enqueue(plan, A, B, e, peer_Y, n_peers);
 }
 
 int sofie_b200_gemm_run_host(sofie_b200_gemm_plan *plan, const void *hostA, const void *hostB, void *hostY,

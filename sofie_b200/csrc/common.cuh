@@ -62,6 +62,9 @@ struct sofie_b200_ctx {
   size_t stage2_bytes[3] = {0, 0, 0};
   cudaStream_t copy_in = nullptr, copy_out = nullptr;
   cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_done[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
+  // sofie_b200_peer_open: the other processes' allocations mapped here (IPC handle bytes -> base pointer, users)
+  struct PeerMapping { unsigned char ipc[64]; void *base; int users; };
+  std::vector<PeerMapping> peer_mappings;
 };
 
 namespace sb200 {

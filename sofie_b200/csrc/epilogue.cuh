@@ -23,6 +23,7 @@ struct EpiParams {
   int bias_mode, act, out_zp, y_dtype, residual_dtype;
   int acc_is_int;
   int params_aligned;  // col_scale and a per-column bias are 16-byte aligned (vector loads allowed)
+  int y_peers;           // further outputs (peers' copies of Y) that every bulk-stored row segment also goes to (tcgen05 kernel)
   int residual_aligned;  // residual base, pitch and batch stride are multiples of 16 bytes (1) or of 32 bytes (2); 0: neither
   int fast;            // store_chunk_fast() applies: aligned per-column vectors, no full-matrix bias
   int seg_chunks;      // tcgen05 epilogue: 32-column chunks per flushed row segment (0: a whole 128-byte segment)

@@ -36,6 +36,12 @@ constexpr int UMMA_THREADS = 32 * (UMMA_FIRST_EPI_WARP + UMMA_EPI_WARPS);
 constexpr int UMMA_MAX_ACCS = 4;      // accumulators in tensor memory (UmmaParams::accs: 2 or 4)
 constexpr int UMMA_EPI_STAGE_BYTES = 2048;   // staging buffer of one epilogue warp: 32 rows x 64 bytes
 
+// Tensor maps of further outputs (sofie_b200_gemm_enqueue_peers): peers' copies of Y, written by the epilogue's bulk stores.
+constexpr int UMMA_MAX_PEERS = 7;
+struct UmmaPeerMaps {
+  CUtensorMap tm[UMMA_MAX_PEERS];
+};
+
 // Everything the tcgen05 kernel needs besides the two tensor maps.
 struct UmmaParams {
   int M, N, K, batch;
@@ -60,6 +66,8 @@ struct UmmaParams {
   int a_bcast, b_bcast;            // operand shared by the whole batch
   int vec_ok;                      // 16-byte vector stores of 32-column chunks are aligned
   int raster_n;                    // tile order inside a batch: 0 = M index fastest, 1 = N index fastest
+  int y_peers;                     // further outputs of the same shape and pitch (other GPUs' copies of Y): every finished row segment
+                                   // is stored to each of them as well (UmmaPeerMaps)
   int rgroup;                      // > 0: tiles go in bands of this many N tiles, N index fastest inside a band (neither operand fits L2)
   int y_tma;                       // the epilogue may store complete row segments through the tensor map of Y
   int seg_kb;                      // chunk-promotion kernel: K blocks per split segment (ks / 32)
@@ -136,6 +144,7 @@ struct sofie_b200_gemm_plan {
   // tensor maps are rebuilt only when an operand pointer changes
   const void *cached_a = nullptr, *cached_b = nullptr;
   CUtensorMap tm_a{}, tm_b{}, tm_y{};
+  sb200::UmmaPeerMaps peer_maps{};        // maps of the peers' outputs of the enqueue in progress
   const void *cached_y = nullptr;
   int cached_seg_div = 0;          // row-segment divisor the cached map of Y was built for
   // fp32-accurate tensor path (3xTF32): split operands [rows, 3*ks] and the TF32 plan that multiplies them
@@ -158,7 +167,7 @@ struct sofie_b200_gemm_plan {
 namespace sb200 {
 // gemm_umma.cu
 int umma_plan_init(sofie_b200_gemm_plan *plan);          // 0 if the tcgen05 path applies, 1 if not, <0 error
-int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep);
+int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep, void *const *peer_y = nullptr, int n_peers = 0);
 // gemm_umma3x.cu (TF32 kernel that sums short K chunks in registers)
 int umma_promote_set_smem(size_t smem_bytes);
 int umma_promote_launch(sofie_b200_gemm_plan *plan, const UmmaParams &u);

@@ -82,7 +82,7 @@ __device__ __forceinline__ void tile_coords(const UmmaParams &p, uint32_t t, uin
 template <int KIND, int MH>   // MH: M halves per tile (UmmaParams::mh), a template argument so that the one-half kernel pays nothing for the other
 __global__ void __launch_bounds__(UMMA_THREADS, 1)   // 20 warps: 96 registers per thread
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                 const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ UmmaParams p) {
+                 const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ UmmaParams p, const __grid_constant__ UmmaPeerMaps peers) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;  // swizzle atoms are 1024-byte aligned
@@ -347,7 +347,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const int c_end = min(n_len, p.N - n0);          // columns of this item that exist (warp-uniform)
       ROLE_SECTION_BEGIN();
 #ifndef SB200_SKIP_EPI
-      if (m0 < p.M) drain16_any<KIND == KIND_I8>(p.ep, ew, taddr, c_end, seg_first, groups_per_team, b, row, n0, p.vec_ok != 0, p.M, y_map);
+      if (m0 < p.M) drain16_any<KIND == KIND_I8>(p.ep, ew, taddr, c_end, seg_first, groups_per_team, b, row, n0, p.vec_ok != 0, p.M, y_map, peers.tm);
 #endif
       ROLE_SECTION_END(c_st);
       if (++h == MH) {
@@ -725,10 +725,11 @@ static int build_maps(sofie_b200_gemm_plan *plan, const void *A, const void *B) 
   return 0;
 }
 
-int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep) {
+int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const EpiParams &ep, void *const *peer_y, int n_peers) {
   int rc = build_maps(plan, A, B);
   if (rc) return rc;
   UmmaParams u = plan->up;
+  u.y_peers = 0;
   u.ep = ep;
   u.ep.split_out = plan->split_out;
   if (((uintptr_t)ep.Y % 16) != 0) u.vec_ok = 0;
@@ -757,13 +758,28 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
       plan->cached_seg_div = seg_div;
     }
     u.y_tma = 1;
+    if (n_peers > 0) {
+      const sofie_b200_gemm_desc &d = plan->desc;
+      const int ys = dtype_size(d.y_dtype);
+      const uint64_t s2 = d.batch > 1 ? (uint64_t)d.stride_y * ys : (uint64_t)d.M * d.ldy * ys;
+      for (int q = 0; q < n_peers; ++q) {
+        if (!peer_y[q] || (uintptr_t)peer_y[q] % 16) return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue_peers: output %d is NULL or not 16-byte aligned", q);
+        rc = encode_map(&plan->peer_maps.tm[q], d.y_dtype, peer_y[q], (uint64_t)d.N, (uint64_t)d.M, (uint64_t)d.batch, (uint64_t)d.ldy * ys, s2,
+                        (uint32_t)(seg_bytes / ys / seg_div), 32, seg_bytes / seg_div);
+        if (rc) return rc;
+      }
+      u.y_peers = n_peers;
+      u.ep.y_peers = n_peers;
+    }
   }
+  if (n_peers > 0 && (u.y_peers != n_peers || plan->promote))
+    return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue_peers: needs the tensor-core kernel with 16-byte aligned outputs and pitches");
   if (plan->promote) return umma_promote_launch(plan, u);
   cudaStream_t st = plan->ctx->stream;
   dim3 grid(plan->grid), block(UMMA_THREADS);
 #define SB200_UMMA_LAUNCH(K)                                                                             \
-  if (u.mh == 2) umma_gemm_kernel<K, 2><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u); \
-  else umma_gemm_kernel<K, 1><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u)
+  if (u.mh == 2) umma_gemm_kernel<K, 2><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u, plan->peer_maps); \
+  else umma_gemm_kernel<K, 1><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u, plan->peer_maps)
   switch (plan->kind) {
     case KIND_I8: SB200_UMMA_LAUNCH(KIND_I8); break;
     case KIND_F8: SB200_UMMA_LAUNCH(KIND_F8); break;

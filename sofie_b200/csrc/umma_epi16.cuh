@@ -279,7 +279,7 @@ __device__ __forceinline__ void epi16_step(const EpiParams &ep, const Epi16Warp 
 // the function returns).
 template <bool ACC_INT, int OUT, uint32_t FL>
 __device__ __forceinline__ void drain16(const EpiParams &ep, const Epi16Warp &w, uint32_t taddr, int c_end, int first_group, int group_stride,
-                                        long long b, long long row, int n0, bool vec, long long rows_total, const CUtensorMap *tm_y) {
+                                        long long b, long long row, int n0, bool vec, long long rows_total, const CUtensorMap *tm_y, const CUtensorMap *tm_peers) {
   const int G = w.steps_per_seg;
   const int nst = (c_end + 15) >> 4;
   int st = first_group * G, j = 0;   // current step and its position in its segment
@@ -322,6 +322,9 @@ __device__ __forceinline__ void drain16(const EpiParams &ep, const Epi16Warp &w,
         __syncwarp();
         if ((threadIdx.x & 31) == 0) {
           ptx::tma_store_3d(tm_y, w.stage & ~3u, n0 + seg_col, (int)row0, (int)b);
+          if constexpr (!ACC_INT)   // the int8 kernels sit at the register limit: the peer stores exist for the floating kinds only
+            for (int q = 0; q < ep.y_peers; ++q)   // the same segment into every peer's copy of Y (over NVLink when it is another GPU's)
+            ptx::tma_store_3d(tm_peers + q, w.stage & ~3u, n0 + seg_col, (int)row0, (int)b);
           ptx::bulk_commit_group();
         }
         store_pending = true;
@@ -341,9 +344,9 @@ __device__ __forceinline__ void drain16(const EpiParams &ep, const Epi16Warp &w,
 // drain16 with the plan's mask as a constant where it is one of the common ones, else with the mask in a register.
 template <bool ACC_INT, int OUT>
 __device__ __forceinline__ void drain16_masks(const EpiParams &ep, const Epi16Warp &w, uint32_t taddr, int c_end, int first_group, int group_stride,
-                                              long long b, long long row, int n0, bool vec, long long rows_total, const CUtensorMap *tm_y) {
+                                              long long b, long long row, int n0, bool vec, long long rows_total, const CUtensorMap *tm_y, const CUtensorMap *tm_peers) {
 #define SB200_DRAIN16(MASK)                                                                                                  \
-  if (w.fl == (MASK)) return drain16<ACC_INT, OUT, (MASK)>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y)
+  if (w.fl == (MASK)) return drain16<ACC_INT, OUT, (MASK)>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y, tm_peers)
   if (ACC_INT && (OUT == OUT16_I8 || OUT == OUT16_BF16)) {
     SB200_DRAIN16(EPI16_ALPHA);                                   // QLinearMatMul with per-tensor scales
     SB200_DRAIN16(EPI16_CS | EPI16_BI);                           // QLinearConv
@@ -358,19 +361,19 @@ __device__ __forceinline__ void drain16_masks(const EpiParams &ep, const Epi16Wa
     SB200_DRAIN16(EPI16_RS | EPI16_CS | EPI16_BF | EPI16_ACT);    // FP8 with row and column scales
   }
 #undef SB200_DRAIN16
-  drain16<ACC_INT, OUT, EPI16_DYNAMIC>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y);
+  drain16<ACC_INT, OUT, EPI16_DYNAMIC>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y, tm_peers);
 }
 
 template <bool ACC_INT>
 __device__ __forceinline__ void drain16_any(const EpiParams &ep, const Epi16Warp &w, uint32_t taddr, int c_end, int first_group, int group_stride,
-                                            long long b, long long row, int n0, bool vec, long long rows_total, const CUtensorMap *tm_y) {
+                                            long long b, long long row, int n0, bool vec, long long rows_total, const CUtensorMap *tm_y, const CUtensorMap *tm_peers) {
   switch (w.out_class) {
-    case OUT16_F32: drain16_masks<ACC_INT, OUT16_F32>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y); break;
-    case OUT16_BF16: drain16_masks<ACC_INT, OUT16_BF16>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y); break;
-    case OUT16_I8: drain16_masks<ACC_INT, OUT16_I8>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y); break;
-    case OUT16_U8: drain16_masks<ACC_INT, OUT16_U8>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y); break;
+    case OUT16_F32: drain16_masks<ACC_INT, OUT16_F32>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y, tm_peers); break;
+    case OUT16_BF16: drain16_masks<ACC_INT, OUT16_BF16>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y, tm_peers); break;
+    case OUT16_I8: drain16_masks<ACC_INT, OUT16_I8>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y, tm_peers); break;
+    case OUT16_U8: drain16_masks<ACC_INT, OUT16_U8>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y, tm_peers); break;
     default:
-      if (ACC_INT) drain16_masks<true, OUT16_I32>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y);
+      if (ACC_INT) drain16_masks<true, OUT16_I32>(ep, w, taddr, c_end, first_group, group_stride, b, row, n0, vec, rows_total, tm_y, tm_peers);
       break;
   }
 }

@@ -41,6 +41,10 @@ class Epilogue(C.Structure):
     ]
 
 
+class PeerHandle(C.Structure):
+    _fields_ = [("ipc", C.c_ubyte * 64), ("offset", C.c_uint64)]
+
+
 class GemmDesc(C.Structure):
     _fields_ = [
         ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64),
@@ -95,10 +99,15 @@ PROTOTYPES = {
     "sofie_b200_ctx_sync": (C.c_int, [_P]),
     "sofie_b200_ctx_launch_count": (_I64, [_P]),
     "sofie_b200_selftest_wait_timeout": (C.c_int, [_P, _I64]),
+    "sofie_b200_ctx_enable_peer": (C.c_int, [_P, _I32]),
+    "sofie_b200_peer_export": (C.c_int, [_P, _P, C.POINTER(PeerHandle)]),
+    "sofie_b200_peer_open": (C.c_int, [_P, C.POINTER(PeerHandle), C.POINTER(_P)]),
+    "sofie_b200_peer_close": (C.c_int, [_P, _P]),
     "sofie_b200_gemm_plan_create": (C.c_int, [_P, C.POINTER(GemmDesc), C.POINTER(_P)]),
     "sofie_b200_gemm_plan_destroy": (C.c_int, [_P]),
     "sofie_b200_gemm_plan_kernel": (C.c_char_p, [_P]),
     "sofie_b200_gemm_enqueue": (C.c_int, [_P, _P, _P, _P, C.POINTER(Epilogue)]),
+    "sofie_b200_gemm_enqueue_peers": (C.c_int, [_P, _P, _P, _P, C.POINTER(C.c_void_p), _I32, C.POINTER(Epilogue)]),
     "sofie_b200_gemm_run_host": (C.c_int, [_P, _P, _P, _P, C.POINTER(Epilogue)]),
     "sofie_b200_gemm_run_host_many": (C.c_int, [_P, _I64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(Epilogue)]),
     "sofie_b200_conv_plan_create": (C.c_int, [_P, C.POINTER(ConvDesc), _P, C.POINTER(_P)]),

@@ -59,6 +59,27 @@ class Context:
     def launches(self) -> int:
         return int(self._lib.sofie_b200_ctx_launch_count(self._h))
 
+    # another GPU's memory, for GemmPlan.enqueue_peers
+    def enable_peer(self, peer_device: int) -> None:
+        """One process driving several GPUs: this ctx's kernels may then store to `peer_device`'s memory."""
+        L.check(self._lib.sofie_b200_ctx_enable_peer(self._h, int(peer_device)), "ctx_enable_peer")
+
+    def peer_export(self, t: torch.Tensor) -> bytes:
+        """The 72 bytes another process needs to open `t`'s first element (send them by any means)."""
+        h = L.PeerHandle()
+        L.check(self._lib.sofie_b200_peer_export(self._h, _ptr(t), C.byref(h)), "peer_export")
+        return bytes(h)
+
+    def peer_open(self, handle: bytes) -> int:
+        """Device pointer, valid in this process, to the byte another process exported."""
+        h = L.PeerHandle.from_buffer_copy(handle)
+        p = C.c_void_p()
+        L.check(self._lib.sofie_b200_peer_open(self._h, C.byref(h), C.byref(p)), "peer_open")
+        return int(p.value)
+
+    def peer_close(self, ptr: int) -> None:
+        L.check(self._lib.sofie_b200_peer_close(self._h, C.c_void_p(ptr)), "peer_close")
+
     def close(self) -> None:
         if self._h:
             self._lib.sofie_b200_ctx_destroy(self._h)
@@ -236,6 +257,14 @@ class GemmPlan:
     def enqueue(self, A, B, Y, epilogue: Optional[L.Epilogue] = None) -> None:
         ep = C.byref(epilogue) if epilogue is not None else None
         L.check(self._lib.sofie_b200_gemm_enqueue(self._h, _ptr(A), _ptr(B), _ptr(Y), ep), "gemm_enqueue")
+
+    def enqueue_peers(self, A, B, y_ptr: int, peer_ptrs, epilogue: Optional[L.Epilogue] = None) -> None:
+        """The contraction with every finished row segment stored to `y_ptr` and to each of `peer_ptrs` (raw device
+        pointers: this rank's columns inside its own and inside the other ranks' full-width results)."""
+        ep = C.byref(epilogue) if epilogue is not None else None
+        n = len(peer_ptrs)
+        arr = (C.c_void_p * max(n, 1))(*peer_ptrs)
+        L.check(self._lib.sofie_b200_gemm_enqueue_peers(self._h, _ptr(A), _ptr(B), C.c_void_p(y_ptr), arr, n, ep), "gemm_enqueue_peers")
 
     def run_host(self, hostA, hostB, hostY, epilogue: Optional[L.Epilogue] = None) -> None:
         """Host operands (pinned or pageable CPU tensors): H2D, contraction, D2H, wait."""
