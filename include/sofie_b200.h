@@ -151,7 +151,11 @@ typedef struct sofie_b200_gemm_desc {
  *               the first enqueue and again whenever B's address changes.  The tensor-core kernel then stages every
  *               B slice with one TMA box per K block instead of one per 128 bytes of columns.  Results are identical. */
 typedef enum sofie_b200_gemm_flags {
-  SOFIE_B200_GEMM_B_CONSTANT = 1
+  SOFIE_B200_GEMM_B_CONSTANT = 1,
+  /* The plan is meant for sofie_b200_gemm_enqueue_peers: its epilogue stages and stores 128-byte row segments instead of
+   * 64-byte ones (twice the staging memory, one pipeline stage less for some shapes).  NVLink carried 128-byte rows at
+   * 700 GB/s and scattered 64-byte rows at about 410 GB/s here.  Results are identical. */
+  SOFIE_B200_GEMM_WIDE_STORES = 2
 } sofie_b200_gemm_flags;
 
 /*

@@ -77,6 +77,7 @@ struct UmmaParams {
                                    // products (4 loads per 12 MMAs instead of 6); stage byte counts are the doubled ones
   int b_rows;                      // N extent of the B slice one CTA stages (= bn)
   int kb_mmas;                     // MMAs (32 bytes of K each) per K block: 4, or 2 when a K block is 64 bytes
+  int wide;                        // 128-byte row segments in the epilogue (4 KB of staging per warp) instead of 64-byte ones
   int prod_lanes;                  // TMA producer lanes per producer warp (1 to 4)
   int b_resident;                  // all K blocks of operand B stay in shared memory (tiles_n == 1); the ring holds A only
   int accs;                        // accumulators in tensor memory: 1 (tall tiles), 2 or 4

@@ -79,7 +79,9 @@ __device__ __forceinline__ void tile_coords(const UmmaParams &p, uint32_t t, uin
   else { const uint32_t q = r / (uint32_t)p.tiles_m; tn = (int)q; tm = (int)(r - q * (uint32_t)p.tiles_m); }
 }
 
-template <int KIND, int MH>   // MH: M halves per tile (UmmaParams::mh), a template argument so that the one-half kernel pays nothing for the other
+// MH: M halves per tile (UmmaParams::mh), a template argument so that the one-half kernel pays nothing for the other.
+// WIDE: 128-byte row segments in the epilogue (UmmaParams::wide), a template argument for the same reason.
+template <int KIND, int MH, bool WIDE = false>
 __global__ void __launch_bounds__(UMMA_THREADS, 1)   // 20 warps: 96 registers per thread
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                  const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ UmmaParams p, const __grid_constant__ UmmaPeerMaps peers) {
@@ -312,7 +314,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t team = (uint32_t)(group / groups_per_team);
     const int seg_first = group % groups_per_team;
     const uint32_t acc_mask = (uint32_t)p.accs - 1u, acc_shift = (uint32_t)p.accs >> 1;   // accs is 1, 2 or 4
-    const Epi16Warp ew = epi16_warp_init(p.ep, epi_stage + (uint32_t)epi_warp * UMMA_EPI_STAGE_BYTES);
+    const Epi16Warp ew = epi16_warp_init<WIDE>(p.ep, epi_stage + (uint32_t)epi_warp * (WIDE ? 2 * UMMA_EPI_STAGE_BYTES : UMMA_EPI_STAGE_BYTES));
     const CUtensorMap *y_map = p.y_tma ? &tm_y : nullptr;
     const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16);
     ROLE_TIMER(w_tfull);
@@ -507,7 +509,8 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   // per tile the slower of the MMAs (128 cycles per 128 x 256 x 32-byte step) and the operand bytes at the 48 bytes per
   // cycle an SM measured pulling from L2, times the waves of tiles; a tall tile adds its exposed epilogue (8 outputs a cycle).
   u.mh = 1;
-  if (!plan->promote && !ic.on && !d.trans_a && u.bn == 256 && es <= 2 && d.M > UMMA_BM) {
+  const bool want_wide = !plan->promote && (d.flags & SOFIE_B200_GEMM_WIDE_STORES) != 0 && d.ab_dtype != SOFIE_B200_I8 && d.ab_dtype != SOFIE_B200_U8;
+  if (!plan->promote && !ic.on && !d.trans_a && u.bn == 256 && es <= 2 && d.M > UMMA_BM && !want_wide) {
     const double nkb = (double)((d.K * es + kb_bytes - 1) / kb_bytes), tn = (double)((d.N + 255) / 256);
     double t[3] = {0, 0, 0};
     for (int mh = 1; mh <= 2; ++mh) {
@@ -592,7 +595,10 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   u.tmem_cols = 32;
   while (u.tmem_cols < (uint32_t)(u.accs * u.bn * u.mh)) u.tmem_cols <<= 1;
 
-  const size_t epi_bytes = 32 * 1024;   // staging buffers of the epilogue warps (16 x 2 KB; the promotion kernel's 8 x 4 KB)
+  // Wide stores: only where every group of a team still gets a whole 128-byte segment of the tile (else the plan stays narrow).
+  u.wide = want_wide && (u.bn / 16) / (8 / dtype_size(d.y_dtype)) >= (UMMA_EPI_WARPS / 4) / u.teams ? 1 : 0;
+  // staging buffers of the epilogue warps: 16 x 2 KB (the promotion kernel's 8 x 4 KB), 16 x 4 KB with wide stores
+  const size_t epi_bytes = u.wide ? 64 * 1024 : 32 * 1024;
   const size_t budget = 227 * 1024 - 1024 /*alignment*/ - UMMA_TAIL_BYTES /*barriers*/ - epi_bytes;
   // Resident operand B: where one tile spans all of N and every batch uses the same B (the filters of a convolution with
   // few output channels, a narrow weight matrix), all K blocks of B stay in shared memory for the whole kernel and the
@@ -671,6 +677,7 @@ int umma_plan_init(sofie_b200_gemm_plan *plan) {
   cudaError_t e = cudaSuccess;
 #define SB200_UMMA_ATTR(K) \
   e = u.mh == 2 ? cudaFuncSetAttribute(umma_gemm_kernel<K, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM) \
+      : u.wide  ? cudaFuncSetAttribute(umma_gemm_kernel<K, 1, (K) != KIND_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM) \
                 : cudaFuncSetAttribute(umma_gemm_kernel<K, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, UMMA_MAX_DYN_SMEM)
   switch (kind) {
     case KIND_I8: SB200_UMMA_ATTR(KIND_I8); break;
@@ -737,9 +744,9 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
   // 64 bytes (128 in the promotion kernel): 4 steps of 16 columns of 1-byte outputs, 2 of 2-byte, 1 of 4-byte outputs.  A
   // narrow tile then has fewer segments than the lane quarter has warps, so the segment is halved until every warp has one.
   u.y_tma = 0;
-  const int seg_bytes = plan->promote ? 128 : 64;
+  const int seg_bytes = plan->promote || u.wide ? 128 : 64;
   int seg_div = 1;
-  if (!plan->promote) {
+  if (!plan->promote && !u.wide) {
     const int full = 4 / dtype_size(plan->desc.y_dtype);   // steps per segment
     int g = full;
     while (g > 1 && (u.bn / 16) / g < (UMMA_EPI_WARPS / 4) / u.teams) g >>= 1;   // at least one segment per group of a team
@@ -761,6 +768,10 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
     if (n_peers > 0) {
       const sofie_b200_gemm_desc &d = plan->desc;
       const int ys = dtype_size(d.y_dtype);
+      const int seg_cols = seg_bytes / seg_div / ys;   // only whole segments leave through the bulk stores that are repeated per peer
+      const bool halves = u.split_from < u.num_tiles;   // tiles of a short last wave are drained as two N halves
+      if (u.bn % seg_cols != 0 || d.N % seg_cols != 0 || (halves && (u.bn / 2) % seg_cols != 0))
+        return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue_peers: N (%lld) and the tile width (%d) must be whole row segments of %d columns", (long long)d.N, u.bn, seg_cols);
       const uint64_t s2 = d.batch > 1 ? (uint64_t)d.stride_y * ys : (uint64_t)d.M * d.ldy * ys;
       for (int q = 0; q < n_peers; ++q) {
         if (!peer_y[q] || (uintptr_t)peer_y[q] % 16) return fail(SOFIE_B200_ERR_INVALID, "gemm_enqueue_peers: output %d is NULL or not 16-byte aligned", q);
@@ -779,6 +790,7 @@ int umma_enqueue(sofie_b200_gemm_plan *plan, const void *A, const void *B, const
   dim3 grid(plan->grid), block(UMMA_THREADS);
 #define SB200_UMMA_LAUNCH(K)                                                                             \
   if (u.mh == 2) umma_gemm_kernel<K, 2><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u, plan->peer_maps); \
+  else if (u.wide) umma_gemm_kernel<K, 1, (K) != KIND_I8><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u, plan->peer_maps); \
   else umma_gemm_kernel<K, 1><<<grid, block, plan->smem_bytes, st>>>(plan->tm_a, plan->tm_b, plan->tm_y, u, plan->peer_maps)
   switch (plan->kind) {
     case KIND_I8: SB200_UMMA_LAUNCH(KIND_I8); break;

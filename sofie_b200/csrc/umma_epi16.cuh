@@ -53,13 +53,15 @@ struct Epi16Warp {
   int seg_units;      // 16-byte units of a complete segment
   int out_class;      // OUT16_*
 };
+// WIDE: 128-byte segments in a 4 KB buffer (twice the steps of a 64-byte segment; pitch code 0).
+template <bool WIDE = false>
 __device__ __forceinline__ Epi16Warp epi16_warp_init(const EpiParams &ep, uint32_t stage_base) {
   Epi16Warp w;
   w.fl = epi16_flags(ep);
   w.out_class = out16_class(ep.y_dtype);
   const int G_full = chunks_per_flush(ep.y_dtype);   // steps per 64-byte segment: 1 (4-byte), 2 (2-byte), 4 (1-byte outputs)
-  const int G = ep.seg_chunks > 0 && ep.seg_chunks < G_full ? ep.seg_chunks : G_full;
-  const uint32_t code = (G == G_full) ? 1u : (2 * G == G_full ? 2u : 3u);   // row pitch 64, 32 or 16 bytes
+  const int G = WIDE ? 2 * G_full : (ep.seg_chunks > 0 && ep.seg_chunks < G_full ? ep.seg_chunks : G_full);
+  const uint32_t code = WIDE ? 0u : (G == G_full) ? 1u : (2 * G == G_full ? 2u : 3u);   // row pitch 128, 64, 32 or 16 bytes
   w.stage = stage_base | code;
   w.steps_per_seg = G;
   w.seg_units = 4 * G / G_full;

@@ -19,6 +19,7 @@ BIAS_NONE, BIAS_COL_F32, BIAS_ROW_F32, BIAS_SCALAR_F32, BIAS_COL_I32, BIAS_FULL_
 OK, ERR_INVALID, ERR_CUDA, ERR_DEVICE_WAIT, ERR_NO_DEVICE, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5
 ABI_VERSION = 2
 GEMM_B_CONSTANT = 1
+GEMM_WIDE_STORES = 2
 CONV_UNFOLD = 1
 
 

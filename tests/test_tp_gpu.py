@@ -22,7 +22,8 @@ def _free_port():
 
 
 @two_gpus
-def test_one_process_two_gpus_each_writes_its_columns_into_both_results():
+@pytest.mark.parametrize("flags", [0, 2], ids=["rows64", "rows128"])
+def test_one_process_two_gpus_each_writes_its_columns_into_both_results(flags):
     from sofie_b200 import lib as L
     from sofie_b200.ops import Context, GemmPlan, make_epilogue
     M, N, K = 1000, 512, 256          # 1000 rows: the last 32-row segment is clipped by the tensor map
@@ -44,7 +45,7 @@ def test_one_process_two_gpus_each_writes_its_columns_into_both_results():
     for d in range(2):
         torch.cuda.set_device(d)
         n0 = d * n
-        plan = GemmPlan(ctxs[d], M, n, K, bf, bf, trans_b=True, ldy=N)
+        plan = GemmPlan(ctxs[d], M, n, K, bf, bf, trans_b=True, ldy=N, flags=flags)
         ep, k = make_epilogue(bias=bias[n0:n0 + n].contiguous().to(f"cuda:{d}"), act=L.ACT_GELU_ERF)
         ad, wd = a.to(f"cuda:{d}"), w[n0:n0 + n].contiguous().to(f"cuda:{d}")
         keep += [plan, k, ad, wd]

@@ -57,6 +57,10 @@ def main():
             y_local = torch.empty(M, N, dtype=bf, device=dev)
             case["us_with_peer_stores"] = timed(lambda: split.enqueue(a, w_shard, ep))
             case["us_local_only"] = timed(lambda: local.enqueue(a, w_shard, y_local[:, n0:], ep))
+            narrow = tp.ColumnParallelGemm(ctx, M, N, K, bf, bf, wide_stores=False)
+            case["us_with_peer_stores_64_byte_rows"] = timed(lambda: narrow.enqueue(a, w_shard, ep))
+            case["same_narrow"] = bool(torch.equal(narrow(a, w_shard, ep), ys[0]))
+            narrow.close()
             case["peer_bytes"] = M * n * 2 * (rep.world - 1)
             local.close()
         out["cases"].append(case)
