@@ -34,6 +34,14 @@ struct MemoryResult {
 constexpr int64_t kArenaAlignment = 256;
 
 inline int64_t AlignUp(int64_t n, int64_t a = kArenaAlignment) { return (n + a - 1) / a * a; }
+// AlignUp of "a * n + b" with n unknown until the Session is constructed: both parts are rounded, so the sum is aligned
+// for every n (symbolicBase: the number that stands for n, a multiple of the alignment; 0 = no symbolic sizes)
+inline int64_t AlignUpSymbolic(int64_t v, int64_t symbolicBase)
+{
+   if (symbolicBase <= 0 || v < symbolicBase / 2) return AlignUp(v);
+   const int64_t a = (v + symbolicBase / 2) / symbolicBase, b = v - a * symbolicBase;
+   return AlignUp(a) * symbolicBase + AlignUp(b < 0 ? 0 : b);
+}
 
 namespace memory_detail {
 

@@ -6,8 +6,10 @@
 // this driver has GenerateGPU_B200(): it emits a header with the same Session / infer() /
 // infer_nosync() surface whose body is a sequence of calls into libsofie_b200 (include/sofie_b200.h),
 // with all weights, intermediates and scratch placed in one lifetime-planned device arena.
-// Shapes are static: a symbolic dimension named input_size, batch_size or bs takes the batch size
-// given to GenerateGPU_B200 (core/src/RModel.cxx:676-685); any other parameter is rejected.
+// A symbolic dimension named input_size, batch_size or bs takes the batch size given to GenerateGPU_B200
+// (core/src/RModel.cxx:676-685).  One other symbolic leading dimension per model stays open until the Session is constructed
+// (Session(file, N), infer(N, inputs...), tests/alpaka/TestAlpakaLinear.cxx:121-203): it travels through shape inference as
+// kSymbolicBase and every emitted size is rewritten as a * N + b (operators declare SupportsSymbolicDim).
 #pragma once
 #include <cstring>
 #include <map>
@@ -98,7 +100,9 @@ public:
       std::string kind;    // weight | input | intermediate | scratch | output
    };
    const std::vector<ArenaRegion> &GetArenaRegions() const { return fRegions; }
-   int64_t GetArenaBytes() const { return fArenaBytes; }
+   int64_t GetArenaBytes() const { return fArenaBytes; }   // with a symbolic dimension: a * kSymbolicBase + b (DecodeSymbolic)
+   // name of the model's symbolic dimension after Initialize / GenerateGPU_B200; empty when every shape is static
+   const std::string &GetSymbolicDimension() const { return fSymbol; }
    int64_t GetIntermediateMemoryPoolSize() const { return fPoolBytes; }
    int64_t GetUnplannedIntermediateBytes() const { return fUnplannedBytes; }  // sum of pooled tensors without reuse
    const std::vector<std::string> &GetFusionLog() const { return fFusionLog; }
@@ -130,6 +134,7 @@ private:
    std::underlying_type_t<Options> fOptions = 0;
    bool fIsInitialized = false;
    int fBatchSize = -1;
+   std::string fSymbol;   // name of the model's symbolic dimension (empty: all shapes are static); see kSymbolicBase
    std::string fGC;  // generated code
    std::vector<ArenaRegion> fRegions;
    int64_t fArenaBytes = 0, fPoolBytes = 0, fUnplannedBytes = 0, fWeightBytes = 0;

@@ -78,6 +78,9 @@ public:
    virtual bool FuseResidual(RModel &, const std::string & /*residualTensor*/, const std::string & /*newOutput*/) { return false; }
    // a zero-copy alias (Reshape / Flatten): output shares the input's storage
    virtual bool IsAlias() const { return false; }
+   // true if every number the operator emits is linear in a symbolic leading dimension and none of its generation-time
+   // decisions looks at it (see kSymbolicBase)
+   virtual bool SupportsSymbolicDim() const { return false; }
 };
 
 // emitted-code spelling of a sofie_b200_act

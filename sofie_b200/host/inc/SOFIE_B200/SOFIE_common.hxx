@@ -58,6 +58,28 @@ struct Dim {
    std::string GetVal() const { return isParam ? param : std::to_string(dim); }
 };
 
+// One symbolic dimension (the reference's dynamic models take it as a Session constructor argument,
+// tests/alpaka/TestAlpakaLinear.cxx:121-203) travels through shape inference as the number kSymbolicBase.  The base
+// is far above any static size and a multiple of every alignment, so each size, stride or offset the generator derives
+// from it is a * kSymbolicBase + b with small a and b, and reads back as "a * n + b" when the Session is emitted.
+constexpr size_t kSymbolicBase = size_t(1) << 36;
+struct SymbolicValue {
+   long long a = 0, b = 0;   // a * n + b
+};
+// false when v is static (below half the base); throws when v is not linear in the symbol (a product of two symbolic
+// sizes, a division that does not go through)
+inline bool DecodeSymbolic(unsigned long long v, SymbolicValue &out)
+{
+   if (v < kSymbolicBase / 2) return false;
+   const unsigned long long a = (v + kSymbolicBase / 2) / kSymbolicBase;
+   const long long b = (long long)(v - a * kSymbolicBase);
+   if (a >= (1ull << 26) || b >= (1ll << 32) || b <= -(1ll << 32))
+      throw std::runtime_error("SOFIE_B200: a size is not linear in the symbolic dimension (value " + std::to_string(v) + ")");
+   out.a = (long long)a;
+   out.b = b;
+   return true;
+}
+
 inline size_t GetTypeSize(ETensorType t)
 {
    switch (t) {

@@ -34,6 +34,7 @@ public:
    }
    EActivationType Activation() const { return fAct; }
    float GetAlpha() const { return fAlpha; }
+   bool SupportsSymbolicDim() const override { return true; }   // one element count
    void Initialize(RModel &model) override
    {
       if (!model.CheckIfTensorAlreadyExist(fNX))
@@ -103,6 +104,7 @@ public:
       fOutputTensorNames = {fNY};
    }
    static constexpr EBasicBinaryOperator Kind() { return Op; }
+   bool SupportsSymbolicDim() const override { return true; }   // two element counts; the broadcast rule compares trailing dimensions only
    const std::string &NameA() const { return fNA; }
    const std::string &NameB() const { return fNB; }
    void Initialize(RModel &model) override
@@ -164,6 +166,7 @@ public:
    const std::string &NameY() const { return fNY; }
    EActivationType GetActivationType() const override { return fActivation; }
 
+   bool SupportsSymbolicDim() const override { return true; }   // the leading dimension is the batch count of the call
    void Initialize(RModel &model) override
    {
       for (auto &n : {fNX, fNScale, fNB, fNMean, fNVar})
@@ -245,6 +248,8 @@ public:
       if (!fNMean.empty()) fOutputTensorNames.push_back(fNMean);
       if (!fNInvStdDev.empty()) fOutputTensorNames.push_back(fNInvStdDev);
    }
+   bool fAxisIsInner = false;
+   bool SupportsSymbolicDim() const override { return fAxisIsInner; }   // the leading dimension only counts rows
    void Initialize(RModel &model) override
    {
       if (!model.CheckIfTensorAlreadyExist(fNX)) throw std::runtime_error("SOFIE LayerNormalization Op Input Tensor " + fNX + " is not found in model");
@@ -256,6 +261,7 @@ public:
       const int axis = fAttrAxis < 0 ? fAttrAxis + rank : fAttrAxis;
       if (axis < 0 || axis >= rank) throw std::runtime_error("SOFIE LayerNormalization Op: axis out of range");
       fRows = 1; fCols = 1;
+      fAxisIsInner = axis > 0;
       for (int i = 0; i < axis; ++i) fRows *= fShapeX[i];
       for (int i = axis; i < rank; ++i) fCols *= fShapeX[i];
       for (auto &n : {fNScale, fNB})
@@ -299,6 +305,7 @@ public:
       fInputTensorNames = {fNX};
       fOutputTensorNames = {fNY};
    }
+   bool SupportsSymbolicDim() const override { return fAxis > 0; }   // the leading dimension only counts rows (or outer slices)
    void Initialize(RModel &model) override
    {
       if (!model.CheckIfTensorAlreadyExist(fNX)) throw std::runtime_error("SOFIE Softmax Op Input Tensor is not found in model");

@@ -351,6 +351,8 @@ public:
       return out.str();
    }
 
+   // the leading dimension only reaches M (rows of a shared weight) or the batch count, both plain descriptor fields
+   bool SupportsSymbolicDim() const override { return !fIsOutputConstant; }
    std::string Generate_GPU_B200(std::string opName) override
    {
       if (fIsOutputConstant) return "";

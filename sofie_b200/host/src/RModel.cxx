@@ -169,9 +169,18 @@ void RModel::Initialize(int batchSize, bool verbose)
          // input_size, batch_size, bs take the batch size (core/src/RModel.cxx:676-685)
          if ((d.param == "input_size" || d.param == "batch_size" || d.param == "bs") && batchSize > 0) s.push_back(size_t(batchSize));
          else if (d.dim > 0) s.push_back(d.dim);
-         else
-            throw std::runtime_error("SOFIE_B200: input " + name + " has the symbolic dimension " + d.param +
-                                     "; the B200 target needs static shapes (pass a batch size for input_size / batch_size / bs)");
+         else {
+            // a dynamic dimension: the Session constructor takes its value (tests/alpaka/TestAlpakaLinear.cxx:121-203).
+            // One symbol per model, and only as the leading dimension of an input.
+            if (!fSymbol.empty() && fSymbol != d.param)
+               throw std::runtime_error("SOFIE_B200: input " + name + " has the symbolic dimension " + d.param + " beside " + fSymbol +
+                                        "; the B200 target carries one symbolic dimension per model");
+            if (&d != &dims.front())
+               throw std::runtime_error("SOFIE_B200: input " + name + " has the symbolic dimension " + d.param +
+                                        " in an inner position; only a leading (batch) dimension may be symbolic");
+            fSymbol = d.param;
+            s.push_back(kSymbolicBase);
+         }
       }
       fInputTensorInfos[name].shape = s;
    }
@@ -434,6 +443,11 @@ void RModel::PlanArena()
    for (auto &r : outputRoots)
       if (IsInitializedTensor(r)) usedWeights.insert(r);
 
+   // With a symbolic dimension every size is a * n + b (kSymbolicBase stands for n): both parts are aligned, and the pooled
+   // tensors all count as alive for the whole inference -- a block freed by a tensor of a * n bytes cannot be promised to
+   // one of b bytes for every n -- so every offset is a sum of aligned sizes, linear in n.
+   const int64_t symBase = fSymbol.empty() ? 0 : int64_t(kSymbolicBase);
+   auto AlignUp = [symBase](int64_t v) { return AlignUpSymbolic(v, symBase); };
    int64_t off = 0;
    auto place = [&](const std::string &name, int64_t bytes, const char *kind) {
       fRegions.push_back({name, off, bytes, 0, nOps + 1, kind});
@@ -462,7 +476,8 @@ void RModel::PlanArena()
       auto &t = fIntermediateTensorInfos.at(n);
       const size_t factor = fStorageFactor.count(n) ? fStorageFactor.at(n) : 1;   // a tensor of TF32 pairs holds two values per element
       const int64_t bytes = int64_t(ConvertShapeToLength(t.shape) * GetTypeSize(t.type) * factor);
-      lives.push_back({be.first, be.second, bytes});
+      if (symBase) lives.push_back({0, nOps + 1, AlignUp(bytes)});
+      else lives.push_back({be.first, be.second, bytes});
       pooled.push_back({n, 0, bytes, be.first, be.second, "intermediate"});
       fUnplannedBytes += AlignUp(bytes);
    }
@@ -470,7 +485,8 @@ void RModel::PlanArena()
       if (fSkippedOperators.count(size_t(k))) continue;
       if (auto *b = AsB200(fOperators[k].get()))
          for (auto &s : b->GetDeviceScratch_GPU_B200()) {
-            lives.push_back({k, k + 1, int64_t(s.bytes)});
+            if (symBase) lives.push_back({0, nOps + 1, AlignUp(int64_t(s.bytes))});
+            else lives.push_back({k, k + 1, int64_t(s.bytes)});
             pooled.push_back({s.name, 0, int64_t(s.bytes), k, k + 1, "scratch"});
             fUnplannedBytes += AlignUp(int64_t(s.bytes));
          }
@@ -507,6 +523,12 @@ void RModel::GenerateGPU_B200(std::underlying_type_t<Options> options, int batch
    for (size_t i = 0; i < fOperators.size(); ++i)
       if (!AsB200(fOperators[i].get()))
          throw std::runtime_error("SOFIE_B200: operator " + std::to_string(i) + " has no B200 implementation");
+   if (!fSymbol.empty())
+      for (size_t i = 0; i < fOperators.size(); ++i)
+         if (!AsB200(fOperators[i].get())->SupportsSymbolicDim())
+            throw std::runtime_error("SOFIE_B200: operator " + std::to_string(i) + " (output " + (fOperators[i]->GetOpOutputTensors().empty() ? std::string("-") : fOperators[i]->GetOpOutputTensors()[0]) +
+                                     ") needs static shapes; the model has the symbolic dimension " +
+                                     fSymbol + " (pass a batch size for input_size / batch_size / bs, or fix the dimension in the model)");
    FuseOperators();
    FuseAttentionInputs();
    FuseDequantizePool();
@@ -558,8 +580,59 @@ void WriteTensorText(std::ostream &o, const InitializedTensor &t)
 
 }  // namespace
 
+namespace {
+
+// Rewrites every integer literal that carries the symbolic dimension (see kSymbolicBase) as "a * <member> + b".  A literal is
+// a run of digits that is not part of an identifier, a floating-point or a suffixed number.  A line that defined a
+// compile-time constant from such a literal becomes a const member initialised from the dimension.
+std::string SymbolizeCode(const std::string &code, const std::string &member)
+{
+   auto isWord = [](char c) { return std::isalnum(static_cast<unsigned char>(c)) || c == '_' || c == '.'; };
+   std::string out;
+   out.reserve(code.size() + code.size() / 8);
+   size_t lineStart = 0;
+   bool lineSymbolic = false;
+   auto endLine = [&]() {
+      if (lineSymbolic) {
+         const size_t p = out.find("static constexpr", lineStart);
+         if (p != std::string::npos) out.replace(p, 16, "const");
+      }
+      lineStart = out.size();
+      lineSymbolic = false;
+   };
+   for (size_t i = 0; i < code.size();) {
+      const char c = code[i];
+      if (std::isdigit(static_cast<unsigned char>(c)) && (i == 0 || !isWord(code[i - 1]))) {
+         size_t j = i;
+         while (j < code.size() && std::isdigit(static_cast<unsigned char>(code[j]))) ++j;
+         const std::string tok = code.substr(i, j - i);
+         SymbolicValue sv;
+         if ((j == code.size() || !isWord(code[j])) && tok.size() >= 11 && tok.size() <= 19 && DecodeSymbolic(std::stoull(tok), sv)) {
+            out += "(size_t(" + std::to_string(sv.a) + ") * " + member;
+            if (sv.b > 0) out += " + " + std::to_string(sv.b);
+            if (sv.b < 0) out += " - " + std::to_string(-sv.b);
+            out += ")";
+            lineSymbolic = true;
+         } else {
+            out += tok;
+         }
+         i = j;
+         continue;
+      }
+      out += c;
+      ++i;
+      if (c == '\n') endLine();
+   }
+   endLine();
+   return out;
+}
+
+}  // namespace
+
 std::string RModel::GenerateSessionCode_GPU_B200()
 {
+   const bool dynamic = !fSymbol.empty();
+   const std::string symMember = "fDim_" + fSymbol;
    const bool extStream = fOptions & static_cast<std::underlying_type_t<Options>>(Options::kExternalStream);
    const bool customMem = fOptions & static_cast<std::underlying_type_t<Options>>(Options::kCustomMemory);
    const bool profile = fOptions & static_cast<std::underlying_type_t<Options>>(Options::kProfile);
@@ -598,6 +671,8 @@ std::string RModel::GenerateSessionCode_GPU_B200()
       o << "\n";
    }
    o << "struct Session {\n";
+   if (dynamic)
+      o << "   // the model's symbolic dimension " << fSymbol << ": fixed by the constructor, every size below follows from it\n   const size_t " << symMember << ";\n";
    o << "   static constexpr size_t kArenaBytes = " << fArenaBytes << ";\n";
    o << "   static constexpr size_t kWeightBytes = " << fWeightBytes << ";\n";
    o << "   static constexpr size_t kPoolBytes = " << fPoolBytes << ";        // pooled intermediates + scratch, planned by lifetime\n";
@@ -755,11 +830,14 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    const std::string defFile = noWeightFile ? "\"\"" : "\"" + fName + (safetensors ? ".safetensors\"" : ".dat\"");
    const std::string prov = customMem ? "MemoryProvider provider, " : "";
    const std::string provInit = customMem ? "fProvider = provider; " : "";
-   o << "   Session(" << prov << "std::string filename = " << defFile << ")\n   {\n      " << provInit
+   // with a symbolic dimension the constructor takes its value after the file name (Session(filename, N) in the reference's tests)
+   const std::string fileParam = dynamic ? std::string("std::string filename, size_t ") + fSymbol + "_value" : "std::string filename = " + defFile;
+   const std::string memInit = dynamic ? ") : " + symMember + "(" + fSymbol + "_value" : "";
+   o << "   Session(" << prov << fileParam << memInit << ")\n   {\n      " << provInit
      << "CheckCuda(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), \"stream\");\n      fOwnStream = true;\n      InitSession(filename);\n   }\n";
    if (extStream) {
       o << "   // the stream is borrowed: it must outlive the Session and is never destroyed here\n";
-      o << "   Session(" << prov << "cudaStream_t externalStream, std::string filename = " << defFile << ")\n   {\n      " << provInit
+      o << "   Session(" << prov << "cudaStream_t externalStream, " << fileParam << memInit << ")\n   {\n      " << provInit
         << "stream = externalStream;\n      InitSession(filename);\n   }\n";
    }
    o << "   Session(const Session &) = delete;\n   Session &operator=(const Session &) = delete;\n";
@@ -848,6 +926,14 @@ std::string RModel::GenerateSessionCode_GPU_B200()
       o << "      for (size_t i = 0; i + 1 < fProfEvents.size(); ++i) { float ms = 0; if (cudaEventElapsedTime(&ms, fProfEvents[i], fProfEvents[i + 1]) == cudaSuccess) fProfTotalMs[i] += ms; }\n      ++fProfCalls;\n";
    }
    o << "      return r;\n   }\n";
+   if (dynamic) {
+      // the reference's dynamic form repeats the dimension in front of the inputs (session.infer(N, input))
+      o << "   // the dimension again, as the reference's dynamic Sessions take it: it must be the one the Session was built for\n";
+      o << "   " << outT << " *infer(size_t " << fSymbol << "_value, " << params << ")\n   {\n";
+      o << "      if (" << fSymbol << "_value != " << symMember << ") throw std::runtime_error(\"SOFIE_B200 Session::infer: the Session was built for another value of " << fSymbol << "\");\n";
+      o << "      return infer(" << args << ");\n   }\n";
+      o << "   size_t GetSymbolicDimension() const { return " << symMember << "; }\n";
+   }
    // the reference's span form (RModel_ALPAKA.cxx:814-838): views of the inputs in, results copied into the caller's output views
    o << "   // runs the model on device pointers to the inputs, copies every output into the caller's device buffers and waits\n";
    o << "   void infer(std::span<const void *const> inputs, std::span<void *const> outputs)\n   {\n";
@@ -886,8 +972,9 @@ std::string RModel::GenerateSessionCode_GPU_B200()
       // a queue of inferences from host memory
       size_t inBytes = 0;
       std::vector<size_t> inOff;
-      for (auto &n : fInputTensorNames) { inOff.push_back(inBytes); inBytes += (region.at(n)->bytes + 255) / 256 * 256; }
-      const size_t outBytes = outLen * GetTypeSize(typeOf(out0)), outPad = (outBytes + 255) / 256 * 256;
+      const int64_t symBase = dynamic ? int64_t(kSymbolicBase) : 0;   // (sizes linear in the symbolic dimension: both parts aligned)
+      for (auto &n : fInputTensorNames) { inOff.push_back(inBytes); inBytes += size_t(AlignUpSymbolic(int64_t(region.at(n)->bytes), symBase)); }
+      const size_t outBytes = outLen * GetTypeSize(typeOf(out0)), outPad = size_t(AlignUpSymbolic(int64_t(outBytes), symBase));
       std::string manyParams, stage0, stage1;
       for (size_t i = 0; i < fInputTensorNames.size(); ++i) {
          const auto &n = fInputTensorNames[i];
@@ -946,7 +1033,7 @@ std::string RModel::GenerateSessionCode_GPU_B200()
    }
    if (debug) {
       o << "   // alignment and overlap-while-alive check of the arena regions (the reference's ValidateMemory)\n";
-      o << "   void ValidateMemory() const\n   {\n      struct R { const char *name; size_t off, bytes; long b, e; };\n      static const R regions[] = {\n";
+      o << "   void ValidateMemory() const\n   {\n      struct R { const char *name; size_t off, bytes; long b, e; };\n      " << (dynamic ? "" : "static ") << "const R regions[] = {\n";
       for (auto &r : fRegions) o << "         {\"" << r.name << "\", " << r.offset << ", " << r.bytes << ", " << r.begin << ", " << r.end << "},\n";
       o << "      };\n      const size_t n = sizeof(regions) / sizeof(regions[0]);\n"
            "      for (size_t i = 0; i < n; ++i) {\n"
@@ -961,7 +1048,7 @@ std::string RModel::GenerateSessionCode_GPU_B200()
            "      std::printf(\"[SOFIE debug] arena %zu bytes, %zu regions validated\\n\", size_t(kArenaBytes), n);\n   }\n";
    }
    o << "};\n\n}  // namespace SOFIE_" << fName << "\n\n#endif  // SOFIE_B200_" << guard << "\n";
-   return o.str();
+   return dynamic ? SymbolizeCode(o.str(), symMember) : o.str();
 }
 
 // safetensors type names: the reference's F32 / F64 / I64 (core/src/RModel.cxx:51-59) plus the low-precision types of this target

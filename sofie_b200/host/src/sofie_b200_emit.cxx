@@ -41,8 +41,19 @@ int main(int argc, char **argv)
       model.OutputGenerated(argv[2]);
       std::cout << "{\"model\": \"" << model.GetName() << "\", \"operators\": " << model.GetNumberOfOperators() << ", \"fusions\": [";
       for (size_t i = 0; i < model.GetFusionLog().size(); ++i) std::cout << (i ? ", " : "") << "\"" << model.GetFusionLog()[i] << "\"";
-      std::cout << "], \"arena_bytes\": " << model.GetArenaBytes() << ", \"pool_bytes\": " << model.GetIntermediateMemoryPoolSize()
-                << ", \"unplanned_pool_bytes\": " << model.GetUnplannedIntermediateBytes() << ", \"regions\": " << model.GetArenaRegions().size() << "}\n";
+      std::cout << "]";
+      // a size of a model with a symbolic dimension N is a * N + b: reported as "<key>_per_unit": a, "<key>": b
+      const bool symbolic = !model.GetSymbolicDimension().empty();
+      if (symbolic) std::cout << ", \"symbolic_dimension\": \"" << model.GetSymbolicDimension() << "\"";
+      auto size = [&](const char *key, unsigned long long v) {
+         SymbolicValue sv;
+         if (symbolic && DecodeSymbolic(v, sv)) std::cout << ", \"" << key << "_per_unit\": " << sv.a << ", \"" << key << "\": " << sv.b;
+         else std::cout << ", \"" << key << "\": " << v;
+      };
+      size("arena_bytes", (unsigned long long)model.GetArenaBytes());
+      size("pool_bytes", (unsigned long long)model.GetIntermediateMemoryPoolSize());
+      size("unplanned_pool_bytes", (unsigned long long)model.GetUnplannedIntermediateBytes());
+      std::cout << ", \"regions\": " << model.GetArenaRegions().size() << "}\n";
    } catch (const std::exception &e) {
       std::cerr << e.what() << "\n";
       return 1;

@@ -22,9 +22,17 @@ _WRAPPER = """
 using S = SOFIE_{name}::Session;
 static thread_local std::string g_err;
 extern "C" const char *sess_error() {{ return g_err.c_str(); }}
-extern "C" void *sess_create(const char *file)
+// `dim`: the value of the model's symbolic dimension (a model without one ignores it)
+extern "C" void *sess_create(const char *file, unsigned long long dim)
 {{
-   try {{ return new S(file); }} catch (const std::exception &e) {{ g_err = e.what(); return nullptr; }}
+   (void)dim;
+   try {{ return new S(file{dim_arg}); }} catch (const std::exception &e) {{ g_err = e.what(); return nullptr; }}
+}}
+// the reference's dynamic form of infer: the dimension again, then the inputs; waits for the result
+extern "C" const void *sess_infer_dim(void *s, unsigned long long dim, const void *const *in)
+{{
+   (void)dim;
+   try {{ return static_cast<S *>(s)->infer({dim_lead}{dev_args}); }} catch (const std::exception &e) {{ g_err = e.what(); return nullptr; }}
 }}
 extern "C" void sess_destroy(void *s) {{ delete static_cast<S *>(s); }}
 extern "C" void *sess_stream(void *s) {{ return static_cast<S *>(s)->stream; }}
@@ -71,7 +79,10 @@ extern "C" int sess_infer_host_many(void *s, unsigned long long count, const voi
 class EmittedSession:
     """One emitted, compiled and constructed Session."""
 
-    def __init__(self, name: str, nodes, weights, inputs, outputs, workdir, flags=("--safetensors",), input_types=None, initializer_types=None):
+    def __init__(self, name: str, nodes, weights, inputs, outputs, workdir, flags=("--safetensors",), input_types=None, initializer_types=None,
+                 symbolic_dim=None):
+        """symbolic_dim: the value for the model's symbolic dimension (an input shape with a string in it), given to the
+        Session constructor as the reference's dynamic Sessions take it."""
         workdir = Path(workdir)
         workdir.mkdir(parents=True, exist_ok=True)
         self.name, self.workdir = name, workdir
@@ -88,12 +99,16 @@ class EmittedSession:
         types = [C_TYPE[(input_types or {}).get(n, 1)] for n, _ in inputs]
         dev_args = ", ".join(f"static_cast<const {t} *>(in[{i}])" for i, t in enumerate(types))
         many_args = "".join(f"reinterpret_cast<const {t} *const *>(ins[{i}]), " for i, t in enumerate(types))
-        src = _WRAPPER.format(header=workdir / f"{name}.hxx", name=name, dev_args=dev_args, many_args=many_args, tout=self.out_ctype)
+        dynamic = symbolic_dim is not None
+        src = _WRAPPER.format(header=workdir / f"{name}.hxx", name=name, dev_args=dev_args, many_args=many_args, tout=self.out_ctype,
+                              dim_arg=", size_t(dim)" if dynamic else "", dim_lead="size_t(dim), " if dynamic else "")
         so = B.compile_session(workdir / f"{name}.hxx", workdir / f"libsession_{name}.so", src)
         lib = C.CDLL(str(so))
         lib.sess_error.restype = C.c_char_p
         lib.sess_create.restype = C.c_void_p
-        lib.sess_create.argtypes = [C.c_char_p]
+        lib.sess_create.argtypes = [C.c_char_p, C.c_ulonglong]
+        lib.sess_infer_dim.restype = C.c_void_p
+        lib.sess_infer_dim.argtypes = [C.c_void_p, C.c_ulonglong, C.POINTER(C.c_void_p)]
         lib.sess_destroy.argtypes = [C.c_void_p]
         lib.sess_stream.restype = C.c_void_p
         lib.sess_stream.argtypes = [C.c_void_p]
@@ -112,7 +127,7 @@ class EmittedSession:
         lib.sess_infer_host_many.argtypes = [C.c_void_p, C.c_ulonglong, C.POINTER(C.POINTER(C.c_void_p)), C.POINTER(C.c_void_p)]
         self.lib = lib
         ext = ".safetensors" if "--safetensors" in flags else ".dat"
-        self.h = lib.sess_create(str(workdir / f"{name}{ext}").encode())
+        self.h = lib.sess_create(str(workdir / f"{name}{ext}").encode(), int(symbolic_dim or 0))
         if not self.h:
             raise RuntimeError(f"Session {name}: {lib.sess_error().decode()}")
 
@@ -123,6 +138,14 @@ class EmittedSession:
         if not r:
             raise RuntimeError(f"Session {self.name}: {self.lib.sess_error().decode()}")
         return r
+
+    def infer_dim(self, dim: int, *device_ptrs: int) -> int:
+        """infer(dim, inputs...) of a Session with a symbolic dimension; returns the output's device pointer after the wait."""
+        arr = (C.c_void_p * self.n_in)(*device_ptrs)
+        p = self.lib.sess_infer_dim(self.h, int(dim), arr)
+        if not p:
+            raise RuntimeError(f"Session {self.name}: {self.lib.sess_error().decode()}")
+        return p
 
     def infer_span(self, device_in_ptrs, device_out_ptrs) -> None:
         """The Session's span form of infer: device pointers of the inputs and of caller-owned output buffers; returns when

@@ -8,6 +8,7 @@ on cuda:0, and must reproduce what the reference's own emitted CPU code computed
 """
 import ctypes as C
 import json
+import re
 import subprocess
 from pathlib import Path
 
@@ -196,12 +197,43 @@ def test_unsupported_operators_fail_loudly(emit, tmp_path):
     onnx_min.save(str(tmp_path / "g.onnx"), [{"op": "Gemm", "in": ["X", "W", "b"], "out": ["Y"], "attrs": {}}], w, [("X", [3, 8])], ["Y"])
     rc, out, err = run_emit(emit, tmp_path / "g.onnx", tmp_path / "g.hxx")
     assert rc != 0 and "cannot be uni-directional broadcasted" in err
-    # a symbolic dimension needs a batch size
+    # a batch size fixes the dimensions named bs / batch_size / input_size at generation
     onnx_min.save(str(tmp_path / "d.onnx"), [{"op": "Relu", "in": ["X"], "out": ["Y"], "attrs": {}}], {}, [("X", ["bs", 3])], ["Y"])
-    rc, out, err = run_emit(emit, tmp_path / "d.onnx", tmp_path / "d.hxx")
-    assert rc != 0 and "static shapes" in err
     rc, out, err = run_emit(emit, tmp_path / "d.onnx", tmp_path / "d.hxx", "--batch", "7")
     assert rc == 0 and "unary_enqueue(ctx, tensor_X, tensor_Y, SOFIE_B200_F32, 21," in (tmp_path / "d.hxx").read_text()
+
+
+def test_a_symbolic_leading_dimension_reaches_the_session_constructor(emit, tmp_path):
+    """The reference's dynamic models (tests/alpaka/TestAlpakaLinear.cxx:121-203): Session(file, N) and infer(N, inputs)."""
+    w = {"W": np.ones((4, 3), dtype=np.float32), "B": np.zeros(3, dtype=np.float32), "g": np.ones(3, dtype=np.float32)}
+    nodes = [{"op": "Gemm", "in": ["X", "W", "B"], "out": ["H"], "attrs": {}}, {"op": "Relu", "in": ["H"], "out": ["R"], "attrs": {}},
+             {"op": "Softmax", "in": ["R"], "out": ["S"], "attrs": {"axis": -1}}, {"op": "Add", "in": ["S", "g"], "out": ["Y"], "attrs": {}}]
+    onnx_min.save(str(tmp_path / "dyn.onnx"), nodes, w, [("X", ["N", 4])], ["Y"])
+    for flags in ((), ("--debug", "--profile"), ("--external-stream", "--custom-memory"), ("--safetensors",), ("--no-weight-file",)):
+        rc, out, err = run_emit(emit, tmp_path / "dyn.onnx", tmp_path / "dyn.hxx", *flags)
+        assert rc == 0, err
+        text = (tmp_path / "dyn.hxx").read_text()
+        assert "std::string filename, size_t N_value) : fDim_N(N_value)" in text
+        assert "d.M = (size_t(1) * fDim_N);" in text and "*infer(size_t N_value, const float *tensor_X)" in text
+        assert "softmax_enqueue(ctx, tensor_R, tensor_S, SOFIE_B200_F32, SOFIE_B200_F32, (size_t(1) * fDim_N), 3, 0)" in text
+        assert "static constexpr size_t kArenaBytes" not in text and "const size_t kArenaBytes = (size_t(" in text
+        assert re.search(r"(?<![\w.])\d{11,}(?![\w.])", text) is None          # no number still carries the stand-in for N
+        chk = syntax_check(tmp_path / "dyn.hxx")
+        assert chk.returncode == 0, chk.stderr[-2000:]
+    # every offset of the arena is a sum of aligned sizes: a multiple of 256 for every N
+    for m in re.finditer(r"fArena \+ \(size_t\((\d+)\) \* fDim_N(?: \+ (\d+))?\)", text):
+        assert int(m.group(1)) % 256 == 0 and int(m.group(2) or 0) % 256 == 0
+    # what the target cannot carry is refused with the reason
+    onnx_min.save(str(tmp_path / "two.onnx"), [{"op": "Add", "in": ["A", "B"], "out": ["Y"], "attrs": {}}], {}, [("A", ["N", 4]), ("B", ["M", 4])], ["Y"])
+    rc, out, err = run_emit(emit, tmp_path / "two.onnx", tmp_path / "two.hxx")
+    assert rc != 0 and "one symbolic dimension per model" in err
+    onnx_min.save(str(tmp_path / "inner.onnx"), [{"op": "Relu", "in": ["X"], "out": ["Y"], "attrs": {}}], {}, [("X", [2, "L"])], ["Y"])
+    rc, out, err = run_emit(emit, tmp_path / "inner.onnx", tmp_path / "inner.hxx")
+    assert rc != 0 and "only a leading (batch) dimension may be symbolic" in err
+    cw = {"F": np.zeros((4, 3, 3, 3), dtype=np.float32)}
+    onnx_min.save(str(tmp_path / "conv.onnx"), [{"op": "Conv", "in": ["X", "F"], "out": ["Y"], "attrs": {"kernel_shape": [3, 3]}}], cw, [("X", ["N", 3, 8, 8])], ["Y"])
+    rc, out, err = run_emit(emit, tmp_path / "conv.onnx", tmp_path / "conv.hxx")
+    assert rc != 0 and "needs static shapes" in err and "symbolic dimension N" in err
 
 
 # ---- on the GPU: the emitted Session against the reference's own results ----------------------------------

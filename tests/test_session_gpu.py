@@ -313,3 +313,47 @@ def test_span_infer_and_pool_statistics(tmp_path, b200_lib):
     st = sess.pool_stats()
     assert st["pool"] > 0 and st["largest_free"] <= st["free"] <= st["pool"] and 0.0 <= st["fragmentation"] < 1.0
     sess.close()
+
+
+@pytest.mark.parametrize("n", [1, 8])
+def test_dynamic_linear_takes_the_batch_in_the_constructor(n, tmp_path, b200_lib):
+    """The reference's DynamicLinear test (tests/alpaka/TestAlpakaLinear.cxx:121-160): Gemm + Relu on an input [N, 4] whose
+    leading dimension is symbolic; Session(file, N), infer(N, input); its weights, inputs and 1e-5 bar.  One emitted header
+    serves both values of N."""
+    import torch
+    from sofie_b200.session import EmittedSession
+    w = np.array([[0.5, -1.0, 0.25], [0.75, 0.5, -0.5], [-0.25, 1.0, 0.75], [1.5, -0.75, 0.5]], dtype=np.float32)
+    b = np.array([0.5, -0.5, 0.25], dtype=np.float32)
+    nodes = [{"op": "Gemm", "in": ["X", "W", "B"], "out": ["H"], "attrs": {}}, {"op": "Relu", "in": ["H"], "out": ["Y"], "attrs": {}}]
+    sess = EmittedSession("DynamicLinear", nodes, {"W": w, "B": b}, [("X", ["N", 4])], ["Y"], tmp_path, symbolic_dim=n)
+    x = ((np.arange(n * 4) % 7) - 3.0).astype(np.float32).reshape(n, 4)
+    want = np.maximum(x @ w + b, 0)
+    dx = torch.from_numpy(x).cuda()
+    out = sess.infer_dim(n, dx.data_ptr())
+    got = np.zeros((n, 3), dtype=np.float32)
+    assert sess.infer_host([x], got) == 3 * n
+    assert np.abs(got - want).max() <= 1e-5
+    y = torch.empty((n, 3), dtype=torch.float32, device="cuda:0")
+    sess.infer_span([dx.data_ptr()], [y.data_ptr()])
+    assert np.abs(y.cpu().numpy() - want).max() <= 1e-5 and out
+    with pytest.raises(RuntimeError, match="another value of N"):
+        sess.infer_dim(n + 1, dx.data_ptr())
+    sess.close()
+
+
+@pytest.mark.parametrize("n", [1, 5])
+def test_dynamic_batched_matmul(n, tmp_path, b200_lib):
+    """The reference's DynamicMatMulBatched test (tests/alpaka/TestAlpakaLinear.cxx:162-203): A[N,4,8] x B[N,8,6], both inputs
+    with the symbolic leading dimension, which becomes the batch count of one strided-batched contraction."""
+    from sofie_b200.session import EmittedSession
+    nodes = [{"op": "MatMul", "in": ["A", "B"], "out": ["Y"], "attrs": {}}]
+    sess = EmittedSession("DynamicMatMulBatched", nodes, {}, [("A", ["N", 4, 8]), ("B", ["N", 8, 6])], ["Y"], tmp_path, symbolic_dim=n)
+    a = (((np.arange(n * 32) % 11) - 5.0) * 0.3).astype(np.float32).reshape(n, 4, 8)
+    b = (((np.arange(n * 48) % 7) - 3.0) * 0.5).astype(np.float32).reshape(n, 8, 6)
+    got = np.zeros((n, 4, 6), dtype=np.float32)
+    assert sess.infer_host([a, b], got) == 24 * n
+    assert np.abs(got - np.einsum("nik,nkj->nij", a, b)).max() <= 1e-5
+    outs = [np.zeros((n, 4, 6), dtype=np.float32) for _ in range(3)]      # the pipelined queue sizes its buffers from N too
+    sess.infer_host_many([[a.ctypes.data] * 3, [b.ctypes.data] * 3], [o.ctypes.data for o in outs])
+    assert all(np.array_equal(o, got) for o in outs)
+    sess.close()
