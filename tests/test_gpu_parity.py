@@ -180,6 +180,24 @@ def test_tall_tiles_with_ragged_last_tile(ctx, oracle, M, tb):
     assert np.array_equal(got[rows], want), f"{(got[rows] != want).sum()} of {want.size} differ"
 
 
+@pytest.mark.parametrize("N,tb", [(4096, True), (4032, True), (4000, False)])
+def test_tall_tiles_over_a_wide_result(ctx, oracle, N, tb):
+    """4096 x N x 4096: 16 bands of tall tiles (256 rows) and 16 tiles across N -- more tiles than SMs, so the CTAs take a
+    second tile; N = 4032 and 4000 leave a narrower last tile (4000 with B stored [K, N]: the plan's K-major copy).  Rows
+    from every band, all columns, bit for bit."""
+    M, K = 4096, 4096
+    rng = np.random.default_rng(N)
+    a = rng.integers(-127, 128, size=(M, K), dtype=np.int8)
+    b = rng.integers(-127, 128, size=(N, K) if tb else (K, N), dtype=np.int8)
+    cs = (rng.random(N, dtype=np.float32) * 2e-5 + 1e-5).astype(np.float32)
+    bias = rng.integers(-50000, 50000, size=N, dtype=np.int32)
+    got = run_gemm(ctx, a, b, M, N, K, torch.int8, torch.int8, False, tb, col_scale=cs, bias=bias, expect="umma",
+                   flags=0 if tb else L.GEMM_B_CONSTANT).cpu().numpy()
+    rows = np.sort(np.concatenate([np.arange(16) * 256 + rng.integers(0, 256, size=16), rng.choice(M, size=48, replace=False), [0, 127, 128, 255, M - 1]]))
+    want = oracle.gemm(np.ascontiguousarray(a[rows]), b, len(rows), N, K, L.I8, L.I8, False, tb, ep=oracle.epilogue(col_scale=cs, bias=bias))
+    assert np.array_equal(got[rows], want), f"{(got[rows] != want).sum()} of {want.size} differ"
+
+
 # ---- FP8 / bf16 / fp32 contractions -------------------------------------------------------------
 def fp8_operands(rng, M, N, K, tb):
     a = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32))
