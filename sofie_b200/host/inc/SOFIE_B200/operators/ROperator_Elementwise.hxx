@@ -407,6 +407,7 @@ public:
       fOutputTensorNames = {fNOutput};
    }
    bool IsAlias() const override { return true; }
+   bool SupportsSymbolicDim() const override { return true; }   // emits nothing; RModel checks where the dimension ends up
    void Initialize(RModel &model) override
    {
       if (!model.CheckIfTensorAlreadyExist(fNData)) throw std::runtime_error("SOFIE Reshape Op Input Tensor " + fNData + " is not found in model");

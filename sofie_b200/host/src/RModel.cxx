@@ -524,6 +524,12 @@ void RModel::GenerateGPU_B200(std::underlying_type_t<Options> options, int batch
       if (!AsB200(fOperators[i].get()))
          throw std::runtime_error("SOFIE_B200: operator " + std::to_string(i) + " has no B200 implementation");
    if (!fSymbol.empty())
+      for (auto &[name, info] : fIntermediateTensorInfos)   // the dimension may only lead: a Reshape or a transposing operator that moves it inward is refused
+         for (size_t i = 1; i < info.shape.size(); ++i)
+            if (info.shape[i] >= kSymbolicBase / 2)
+               throw std::runtime_error("SOFIE_B200: tensor " + name + " carries the symbolic dimension " + fSymbol + " in an inner position " +
+                                        ConvertShapeToString(info.shape) + "; only a leading dimension may be symbolic");
+   if (!fSymbol.empty())
       for (size_t i = 0; i < fOperators.size(); ++i)
          if (!AsB200(fOperators[i].get())->SupportsSymbolicDim())
             throw std::runtime_error("SOFIE_B200: operator " + std::to_string(i) + " (output " + (fOperators[i]->GetOpOutputTensors().empty() ? std::string("-") : fOperators[i]->GetOpOutputTensors()[0]) +
@@ -600,7 +606,14 @@ std::string SymbolizeCode(const std::string &code, const std::string &member)
       lineStart = out.size();
       lineSymbolic = false;
    };
+   static const std::string kWeights = "static const ";   // (Options::kNoWeightFile: the embedded weight values are data, not sizes)
    for (size_t i = 0; i < code.size();) {
+      if (out.size() == lineStart && code.compare(i, kWeights.size(), kWeights) == 0 && code.find(" fWeights_", i) < code.find('\n', i)) {
+         const size_t e = code.find('\n', i);
+         out.append(code, i, e == std::string::npos ? std::string::npos : e - i);
+         i = e == std::string::npos ? code.size() : e;
+         continue;
+      }
       const char c = code[i];
       if (std::isdigit(static_cast<unsigned char>(c)) && (i == 0 || !isWord(code[i - 1]))) {
          size_t j = i;

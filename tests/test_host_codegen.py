@@ -223,6 +223,19 @@ def test_a_symbolic_leading_dimension_reaches_the_session_constructor(emit, tmp_
     # every offset of the arena is a sum of aligned sizes: a multiple of 256 for every N
     for m in re.finditer(r"fArena \+ \(size_t\((\d+)\) \* fDim_N(?: \+ (\d+))?\)", text):
         assert int(m.group(1)) % 256 == 0 and int(m.group(2) or 0) % 256 == 0
+    # a Reshape that keeps the dimension in front is free (an alias); one that moves it inward is refused
+    rw = {"W": np.ones((48, 5), dtype=np.float32), "keep": np.array([0, -1], dtype=np.int64), "move": np.array([4, -1], dtype=np.int64)}
+    rn = [{"op": "Relu", "in": ["X"], "out": ["R"], "attrs": {}}, {"op": "Reshape", "in": ["R", "keep"], "out": ["F"], "attrs": {}},
+          {"op": "MatMul", "in": ["F", "W"], "out": ["Y"], "attrs": {}}]
+    onnx_min.save(str(tmp_path / "resh.onnx"), rn, rw, [("X", ["N", 3, 4, 4])], ["Y"])
+    rc, out, err = run_emit(emit, tmp_path / "resh.onnx", tmp_path / "resh.hxx", "--no-weight-file")
+    text = (tmp_path / "resh.hxx").read_text()
+    assert rc == 0 and "d.M = (size_t(1) * fDim_N); d.N = 5; d.K = 48;" in text and "fWeights_W[] = {1,1,1," in text
+    assert json.loads(out)["arena_bytes_per_unit"] == 768 and syntax_check(tmp_path / "resh.hxx").returncode == 0
+    rn[1]["in"] = ["R", "move"]
+    onnx_min.save(str(tmp_path / "resh2.onnx"), rn[:2], rw, [("X", ["N", 3, 4, 4])], ["F"])
+    rc, out, err = run_emit(emit, tmp_path / "resh2.onnx", tmp_path / "resh2.hxx")
+    assert rc != 0 and "in an inner position" in err
     # what the target cannot carry is refused with the reason
     onnx_min.save(str(tmp_path / "two.onnx"), [{"op": "Add", "in": ["A", "B"], "out": ["Y"], "attrs": {}}], {}, [("A", ["N", 4]), ("B", ["M", 4])], ["Y"])
     rc, out, err = run_emit(emit, tmp_path / "two.onnx", tmp_path / "two.hxx")
