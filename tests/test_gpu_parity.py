@@ -198,6 +198,38 @@ def test_tall_tiles_over_a_wide_result(ctx, oracle, N, tb):
     assert np.array_equal(got[rows], want), f"{(got[rows] != want).sum()} of {want.size} differ"
 
 
+@pytest.mark.parametrize("M,N,K", [(20000, 768, 1024), (56832, 1536, 512)])
+def test_short_k_many_bands_int8(ctx, oracle, M, N, K):
+    """Short K, several tiles across N, more 128-row bands than SMs (the shape class of the encoder's projections), int8:
+    rows of the first, a middle and the last bands (20000 rows: the last band has 32) and a random sample, all columns, bit
+    for bit, per-channel epilogue."""
+    rng = np.random.default_rng(M + K)
+    a = rng.integers(-127, 128, size=(M, K), dtype=np.int8)
+    b = rng.integers(-127, 128, size=(N, K), dtype=np.int8)
+    cs = (rng.random(N, dtype=np.float32) * 4e-5 + 1e-5).astype(np.float32)
+    bias = rng.integers(-50000, 50000, size=N, dtype=np.int32)
+    got = run_gemm(ctx, a, b, M, N, K, torch.int8, torch.int8, False, True, col_scale=cs, bias=bias, act=L.ACT_RELU, expect="umma").cpu().numpy()
+    rows = np.unique(np.concatenate([np.arange(0, 130), np.arange(148 * 128 - 3, 148 * 128 + 131), np.arange(M - 200, M), rng.choice(M, size=100, replace=False)]))
+    rows = rows[rows < M]
+    want = oracle.gemm(np.ascontiguousarray(a[rows]), b, len(rows), N, K, L.I8, L.I8, False, True, ep=oracle.epilogue(col_scale=cs, bias=bias, act=L.ACT_RELU))
+    assert np.array_equal(got[rows], want), f"{(got[rows] != want).sum()} of {want.size} differ"
+
+
+def test_short_k_many_bands_bf16_with_residual(ctx, oracle):
+    """The encoder's output projection shape class (bf16, K = 512, bias, residual add) against an fp32 product of the same
+    bf16 operands."""
+    M, N, K = 24000, 512, 512
+    rng = np.random.default_rng(5)
+    a = torch.from_numpy((rng.standard_normal((M, K)) * 0.5).astype(np.float32)).to(torch.bfloat16)
+    b = torch.from_numpy((rng.standard_normal((N, K)) * 0.05).astype(np.float32)).to(torch.bfloat16)
+    res = torch.from_numpy((rng.standard_normal((M, N)) * 0.5).astype(np.float32)).to(torch.bfloat16)
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    an, bn = a.view(torch.int16).numpy(), b.view(torch.int16).numpy()
+    got = run_gemm(ctx, an, bn, M, N, K, torch.bfloat16, torch.bfloat16, False, True, bias=bias, residual=res.to(DEV), ldr=N, expect="umma").float().cpu().numpy()
+    want = a.float().numpy() @ b.float().numpy().T + bias + res.float().numpy()
+    assert close_lowp(got, want), np.abs(got - want).max()
+
+
 # ---- FP8 / bf16 / fp32 contractions -------------------------------------------------------------
 def fp8_operands(rng, M, N, K, tb):
     a = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32))
