@@ -682,6 +682,31 @@ def test_layernorm_softmax_fp32(ctx, oracle, rows, cols):
         assert np.abs(ty.cpu().numpy() - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
 
 
+@pytest.mark.parametrize("rows,cols,bf", [(5000, 512, True), (4099, 384, True), (70001, 200, True), (4100, 128, False), (4097, 256, False), (9000, 200, False)])
+def test_layernorm_many_rows(ctx, oracle, rows, cols, bf):
+    """Rows of 17 to 64 sixteen-byte chunks, thousands of them: the one-warp-per-row kernel that keeps the next rows' loads in
+    flight (row counts that leave warps with different numbers of rows; 384 and 200 columns: lanes without a chunk).  With
+    scale and bias, mean and 1/std not requested."""
+    rng = np.random.default_rng(rows + cols)
+    x = (rng.standard_normal((rows, cols)) * 2 + 0.5).astype(np.float32)
+    g, b = rng.standard_normal(cols).astype(np.float32), rng.standard_normal(cols).astype(np.float32)
+    if bf:
+        tx = torch.from_numpy(x).to(torch.bfloat16)
+        dx = tx.to(DEV)
+        dy = torch.empty_like(dx)
+        ctx.layernorm(dx, dy, torch.from_numpy(g).to(DEV), torch.from_numpy(b).to(DEV), 1e-5)
+        ctx.sync()
+        want = bf16_bits_to_f32(oracle.layernorm(tx.view(torch.int16).numpy().view(np.uint16), g, b, 1e-5, L.BF16))
+        assert close_lowp(dy.float().cpu().numpy(), want)
+    else:
+        dx = torch.from_numpy(x).to(DEV)
+        dy = torch.empty_like(dx)
+        ctx.layernorm(dx, dy, torch.from_numpy(g).to(DEV), torch.from_numpy(b).to(DEV), 1e-5)
+        ctx.sync()
+        want = oracle.layernorm(x, g, b, 1e-5)
+        assert np.abs(dy.cpu().numpy() - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+
+
 @pytest.mark.parametrize("rows,cols", [(2048, 512), (4096, 128), (9, 72)])
 def test_layernorm_softmax_bf16(ctx, oracle, rows, cols):
     rng = np.random.default_rng(cols)
