@@ -357,3 +357,32 @@ def test_dynamic_batched_matmul(n, tmp_path, b200_lib):
     sess.infer_host_many([[a.ctypes.data] * 3, [b.ctypes.data] * 3], [o.ctypes.data for o in outs])
     assert all(np.array_equal(o, got) for o in outs)
     sess.close()
+
+
+@pytest.mark.parametrize("n", [1, 6])
+def test_dynamic_batchnorm_layernorm_softmax_chain(n, tmp_path, b200_lib):
+    """The operators that opt in to a symbolic leading dimension besides the contractions, in one model: BatchNormalization on
+    [N, 5, 4, 4] (the reference's DynamicBatchNorm4D shape class), Flatten, LayerNormalization and Softmax over the rows, an
+    Add with a per-column tensor.  Against numpy in fp32 at 1e-5."""
+    from sofie_b200.session import EmittedSession
+    rng = np.random.default_rng(17)
+    c = 5
+    w = {"s": rng.random(c).astype(np.float32) + 0.5, "b": rng.standard_normal(c).astype(np.float32), "m": rng.standard_normal(c).astype(np.float32),
+         "v": rng.random(c).astype(np.float32) + 0.5, "g": rng.standard_normal(80).astype(np.float32), "h": rng.standard_normal(80).astype(np.float32),
+         "t": rng.standard_normal(80).astype(np.float32)}
+    nodes = [{"op": "BatchNormalization", "in": ["X", "s", "b", "m", "v"], "out": ["B"], "attrs": {"epsilon": 1e-5}},
+             {"op": "Flatten", "in": ["B"], "out": ["F"], "attrs": {"axis": 1}},
+             {"op": "LayerNormalization", "in": ["F", "g", "h"], "out": ["L"], "attrs": {"axis": -1, "epsilon": 1e-5}},
+             {"op": "Softmax", "in": ["L"], "out": ["S"], "attrs": {"axis": -1}},
+             {"op": "Add", "in": ["S", "t"], "out": ["Y"], "attrs": {}}]
+    sess = EmittedSession("DynamicChain", nodes, w, [("X", ["N", c, 4, 4])], ["Y"], tmp_path, symbolic_dim=n)
+    x = rng.standard_normal((n, c, 4, 4)).astype(np.float32)
+    bn = (x - w["m"][None, :, None, None]) / np.sqrt(w["v"][None, :, None, None] + 1e-5) * w["s"][None, :, None, None] + w["b"][None, :, None, None]
+    f = bn.reshape(n, 80).astype(np.float64)
+    ln = (f - f.mean(axis=1, keepdims=True)) / np.sqrt(f.var(axis=1, keepdims=True) + 1e-5) * w["g"] + w["h"]
+    e = np.exp(ln - ln.max(axis=1, keepdims=True))
+    want = (e / e.sum(axis=1, keepdims=True) + w["t"]).astype(np.float32)
+    got = np.zeros((n, 80), dtype=np.float32)
+    assert sess.infer_host([x], got) == 80 * n
+    assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+    sess.close()
