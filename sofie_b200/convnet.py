@@ -92,7 +92,7 @@ class ConvNetB200:
         3-channel first layer unfolds straight from NCHW); then the pool and the classifier."""
         n = 2
         for i, (kern, xl) in enumerate(zip(self.kernels, self.x_layouts)):
-            n += 1 if kern in ("direct", "umma_im2col", "umma3x_im2col") else (2 if xl or i == 0 else 3)
+            n += 1 if kern in ("direct", "umma_im2col", "umma3x_im2col") else (2 if xl or i == 0 or kern == "umma_im2col_x2" else 3)
         if self.kernels[0] == "umma" and self.int8 and self.channels_last and self.first_pixels % 2 == 0:
             n += 1   # the int8 first layer on the tensor cores packs 2 or 4 pixels per row: one kernel repeats its per-channel vectors
         return n

@@ -31,6 +31,9 @@ struct sofie_b200_conv_plan {
   int implicit = 0;            // channels-last in and out on the tensor cores with no unfolded copy: the contraction's TMA producer reads
                                // the input tensor itself in im2col mode (gemm_umma.cu); no workspace
   sofie_b200_gemm_plan *gemm = nullptr;
+  // unit-stride convolution over pixel pairs: the odd output columns are a contraction of their own (gemm: the even ones)
+  sofie_b200_gemm_plan *gemm_odd = nullptr;
+  void *w_odd = nullptr;
 };
 
 namespace sb200 {
@@ -302,14 +305,20 @@ __global__ void __launch_bounds__(256) repeat_words_kernel(const uint32_t *__res
 // two-tap, unit-stride convolution over pairs with zero weights for the lower half of the first tap.  Six 128-byte rows per
 // output pixel instead of nine 64-byte ones; a third more MMA work, which this layer has to spare.
 // Filters [K, C, R, 3] -> [K][R][2][2C].
+//
+// With a horizontal stride of 1 (padding 1 on both sides, even W) the same view serves two contractions that each produce
+// every other output column, written into the output read as [N, Ho, W/2, 2K]: the even columns 2j need inputs 2j-1, 2j,
+// 2j+1 -- the stride-2 pattern, pairs j-1 and j, into channels [0, K) of output pair j -- and the odd columns 2j+1 need
+// 2j, 2j+1, 2j+2: pairs j and j+1 with zero weights for the upper half of the second tap (`odd`), into channels [K, 2K).
 template <typename T>
-__global__ void __launch_bounds__(256) pair_weights_kernel(const T *__restrict__ w, T *__restrict__ out, long long filters, int C, int R) {
+__global__ void __launch_bounds__(256) pair_weights_kernel(const T *__restrict__ w, T *__restrict__ out, long long filters, int C, int R, int odd) {
   const long long per = (long long)R * 2 * 2 * C, total = filters * per;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long k = i / per;
     const int rem = (int)(i - k * per), r = rem / (4 * C), sp = (rem / (2 * C)) & 1, cc = rem % (2 * C);
     const int c = cc % C, upper = cc / C;
-    const int s = sp == 0 ? (upper ? 0 : -1) : (upper ? 2 : 1);   // original tap, -1: no such tap (zero weight)
+    // original tap, -1: no such tap (zero weight)
+    const int s = odd ? (sp == 0 ? (upper ? 1 : 0) : (upper ? -1 : 2)) : (sp == 0 ? (upper ? 0 : -1) : (upper ? 2 : 1));
     out[i] = s < 0 ? (T)0 : w[((k * C + c) * R + r) * 3 + s];
   }
 }
@@ -724,34 +733,60 @@ int sofie_b200_conv_plan_create(sofie_b200_ctx *ctx, const sofie_b200_conv_desc 
       // pixels of 64 bytes under a horizontal stride of 2: read pixel pairs (see pair_weights_kernel)
       const bool pairs = d.C * es == 64 && d.stride_w == 2 && d.S == 3 && d.dil_w == 1 && d.pad_left == 1 && d.pad_right <= 1 && d.W % 2 == 0 &&
                          Wo == d.W / 2;
+      // ... and under a horizontal stride of 1: two contractions over the pairs, for the even and the odd output columns
+      const bool pairs1 = d.C * es == 64 && d.stride_w == 1 && d.S == 3 && d.dil_w == 1 && d.pad_left == 1 && d.pad_right == 1 && d.W % 2 == 0 &&
+                          Wo == d.W && (d.K * dtype_size(d.y_dtype)) % 16 == 0 && rows >= 16384;
       int64_t kimp = p->kdim;
-      if (pairs) {
+      if (pairs || pairs1) {
         ic.W = d.W / 2; ic.C = 2 * d.C; ic.S = 2; ic.sw = 1; ic.pl = 1; ic.pr = 0;
         kimp = d.R * 2 * 2 * d.C;
       }
+      if (pairs1) ic.Wo = Wo / 2;
       sofie_b200_gemm_desc g{};
       g.trans_a = 0; g.trans_b = 1; g.ab_dtype = d.x_dtype; g.y_dtype = d.y_dtype;
-      g.M = rows; g.N = d.K; g.K = kimp; g.batch = 1; g.lda = kimp; g.ldb = kimp; g.ldy = d.K; g.precise = 0;
+      g.M = pairs1 ? rows / 2 : rows; g.N = d.K; g.K = kimp; g.batch = 1; g.lda = kimp; g.ldb = kimp; g.ldy = pairs1 ? 2 * d.K : d.K; g.precise = 0;
       const bool y_ok = d.y_dtype == SOFIE_B200_F32 || d.y_dtype == SOFIE_B200_BF16 || d.y_dtype == SOFIE_B200_I8 || d.y_dtype == SOFIE_B200_U8 ||
                         (d.y_dtype == SOFIE_B200_I32 && d.x_dtype == SOFIE_B200_I8);
       rc = y_ok ? gemm_plan_create_im2col(ctx, g, ic, &p->gemm) : 1;
       if (rc < 0) { delete p; return rc; }
+      if (rc == 0 && pairs1) {
+        Im2colDesc io = ic;
+        io.pl = 0; io.pr = 1;   // odd columns: pairs j and j + 1
+        rc = gemm_plan_create_im2col(ctx, g, io, &p->gemm_odd);
+        if (rc) { sofie_b200_gemm_plan_destroy(p->gemm); p->gemm = nullptr; delete p; return rc < 0 ? rc : fail(SOFIE_B200_ERR_INVALID, "conv_plan_create: no plan for the odd columns"); }
+      }
       if (rc == 0) {
         p->implicit = 1; p->nhwc = 1; p->kpad = p->kdim;
-        if (cudaMalloc(&p->w_padded, (size_t)(d.K * kimp * es)) != cudaSuccess) {
+        if (cudaMalloc(&p->w_padded, (size_t)(d.K * kimp * es)) != cudaSuccess || (pairs1 && cudaMalloc(&p->w_odd, (size_t)(d.K * kimp * es)) != cudaSuccess)) {
           sofie_b200_gemm_plan_destroy(p->gemm);
+          if (p->gemm_odd) sofie_b200_gemm_plan_destroy(p->gemm_odd);
+          if (p->w_padded) cudaFree(p->w_padded);
           delete p;
           return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: allocating the filter buffer failed: %s", cudaGetErrorString(cudaGetLastError()));
         }
         const long long wt = d.K * kimp;
         const unsigned wg = (unsigned)std::min<long long>((wt + 255) / 256, (long long)ctx->sm_count * 16);
-        if (pairs && es == 4) pair_weights_kernel<float><<<wg, 256, 0, ctx->stream>>>((const float *)W, (float *)p->w_padded, d.K, (int)d.C, (int)d.R);
-        else if (pairs) pair_weights_kernel<int8_t><<<wg, 256, 0, ctx->stream>>>((const int8_t *)W, (int8_t *)p->w_padded, d.K, (int)d.C, (int)d.R);
+        if (pairs1 && es == 4) {
+          pair_weights_kernel<float><<<wg, 256, 0, ctx->stream>>>((const float *)W, (float *)p->w_padded, d.K, (int)d.C, (int)d.R, 0);
+          pair_weights_kernel<float><<<wg, 256, 0, ctx->stream>>>((const float *)W, (float *)p->w_odd, d.K, (int)d.C, (int)d.R, 1);
+        } else if (pairs1) {
+          pair_weights_kernel<int8_t><<<wg, 256, 0, ctx->stream>>>((const int8_t *)W, (int8_t *)p->w_padded, d.K, (int)d.C, (int)d.R, 0);
+          pair_weights_kernel<int8_t><<<wg, 256, 0, ctx->stream>>>((const int8_t *)W, (int8_t *)p->w_odd, d.K, (int)d.C, (int)d.R, 1);
+        }
+        else if (pairs && es == 4) pair_weights_kernel<float><<<wg, 256, 0, ctx->stream>>>((const float *)W, (float *)p->w_padded, d.K, (int)d.C, (int)d.R, 0);
+        else if (pairs) pair_weights_kernel<int8_t><<<wg, 256, 0, ctx->stream>>>((const int8_t *)W, (int8_t *)p->w_padded, d.K, (int)d.C, (int)d.R, 0);
         else if (es == 4) reorder_weights_kernel<float><<<wg, 256, 0, ctx->stream>>>((const float *)W, (float *)p->w_padded, d.K, (int)p->cg, (int)(d.R * d.S));
         else reorder_weights_kernel<int8_t><<<wg, 256, 0, ctx->stream>>>((const int8_t *)W, (int8_t *)p->w_padded, d.K, (int)p->cg, (int)(d.R * d.S));
         cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) { sofie_b200_gemm_plan_destroy(p->gemm); cudaFree(p->w_padded); delete p; return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: %s", cudaGetErrorString(e)); }
-        ctx->launches++;
+        if (e != cudaSuccess) {
+          sofie_b200_gemm_plan_destroy(p->gemm);
+          if (p->gemm_odd) sofie_b200_gemm_plan_destroy(p->gemm_odd);
+          cudaFree(p->w_padded);
+          if (p->w_odd) cudaFree(p->w_odd);
+          delete p;
+          return fail(SOFIE_B200_ERR_CUDA, "conv_plan_create: %s", cudaGetErrorString(e));
+        }
+        ctx->launches += pairs1 ? 2 : 1;
         *out = p;
         return 0;
       }
@@ -857,7 +892,9 @@ int sofie_b200_conv_plan_destroy(sofie_b200_conv_plan *plan) {
   if (!plan) return 0;
   cudaSetDevice(plan->ctx->device);
   if (plan->gemm) sofie_b200_gemm_plan_destroy(plan->gemm);
+  if (plan->gemm_odd) sofie_b200_gemm_plan_destroy(plan->gemm_odd);
   if (plan->w_padded) cudaFree(plan->w_padded);
+  if (plan->w_odd) cudaFree(plan->w_odd);
   if (plan->stem_vec) cudaFree(plan->stem_vec);
   delete plan;
   return 0;
@@ -865,6 +902,7 @@ int sofie_b200_conv_plan_destroy(sofie_b200_conv_plan *plan) {
 
 const char *sofie_b200_conv_plan_kernel(const sofie_b200_conv_plan *plan) {
   if (!plan) return "";
+  if (plan->gemm_odd) return "umma_im2col_x2";   // implicit convolution over pixel pairs, even and odd output columns: two launches
   return plan->direct ? "direct" : sofie_b200_gemm_plan_kernel(plan->gemm);   // "umma_im2col": implicit convolution
 }
 
@@ -943,6 +981,14 @@ int sofie_b200_conv_enqueue(sofie_b200_conv_plan *plan, const void *X, void *Y, 
         return fail(SOFIE_B200_ERR_INVALID, "conv_enqueue: bias_mode %d not supported for a convolution", ep->bias_mode);
       e = *ep;
       e.ldr = d.K;
+    }
+    if (plan->gemm_odd) {
+      // even output columns, then the odd ones: the output (and a residual) read as [N, Ho, W/2, 2K], channels [0, K) and [K, 2K)
+      e.ldr = 2 * d.K;
+      int rc = sofie_b200_gemm_enqueue(plan->gemm, X, plan->w_padded, Y, &e);
+      if (rc) return rc;
+      if (e.residual) e.residual = (const char *)e.residual + d.K * dtype_size(e.residual_dtype);
+      return sofie_b200_gemm_enqueue(plan->gemm_odd, X, plan->w_odd, (char *)Y + d.K * dtype_size(d.y_dtype), &e);
     }
     return sofie_b200_gemm_enqueue(plan->gemm, X, plan->w_padded, Y, &e);
   }

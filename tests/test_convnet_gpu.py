@@ -170,7 +170,7 @@ def test_full_size_layer_two_data_paths_agree(ctx, int8, monkeypatch):
         return y
 
     if int8:
-        a = run(1, x, "umma_im2col")
+        a = run(1, x, "umma_im2col_x2")   # 64-byte pixels, unit stride: read as pixel pairs, even and odd output columns apart
         b = run(1, x, "umma", flags=L.CONV_UNFOLD)
         assert torch.equal(a, b)
         assert int((a != 0).sum()) > a.numel() // 10   # not a dead layer

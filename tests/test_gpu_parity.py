@@ -484,6 +484,10 @@ IMPLICIT_CASES = {
     "pairs_w_stride_only": (2, 64, 11, 14, 80, 3, 3, [1, 1, 1, 0], [1, 2], [1, 1], 0),
     "pairs_two_rows": (2, 64, 9, 16, 32, 2, 3, [0, 1, 1, 1], [2, 2], [1, 1], 0),
     "pairs_row_dilation": (3, 64, 20, 18, 64, 3, 3, [2, 1, 2, 1], [2, 2], [2, 1], 0),
+    # ... and under a horizontal stride of 1 (16384 pixels or more) as two contractions over the pairs: even and odd output columns
+    "pairs1_many_tiles": (6, 64, 56, 56, 128, 3, 3, [1, 1, 1, 1], [1, 1], [1, 1], 0),
+    "pairs1_row_dilation": (4, 64, 70, 72, 48, 3, 3, [2, 1, 2, 1], [1, 1], [2, 1], 0),
+    "pairs1_row_stride": (8, 64, 64, 80, 64, 3, 3, [1, 1, 1, 1], [2, 1], [1, 1], 0),
 }
 
 
@@ -509,7 +513,7 @@ def test_conv_implicit_int8(ctx, oracle, case):
     tw = torch.from_numpy(w).to(DEV)
     h = C.c_void_p()
     L.check(lib.sofie_b200_conv_plan_create(ctx._h, C.byref(d), tw.data_ptr(), C.byref(h)), "conv_plan_create")
-    assert lib.sofie_b200_conv_plan_kernel(h).decode() == "umma_im2col"
+    assert lib.sofie_b200_conv_plan_kernel(h).decode() == ("umma_im2col_x2" if case.startswith("pairs1") else "umma_im2col")
     assert lib.sofie_b200_conv_workspace_bytes(h) == 0
     y = torch.zeros((N, ho.value, wo.value, Co), dtype=torch.int8, device=DEV)
     ep, keep = make_epilogue(col_scale=torch.from_numpy(cs).to(DEV), bias=torch.from_numpy(bias).to(DEV), act=L.ACT_RELU)
