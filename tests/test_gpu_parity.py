@@ -488,6 +488,11 @@ IMPLICIT_CASES = {
     "pairs1_many_tiles": (6, 64, 56, 56, 128, 3, 3, [1, 1, 1, 1], [1, 1], [1, 1], 0),
     "pairs1_row_dilation": (4, 64, 70, 72, 48, 3, 3, [2, 1, 2, 1], [1, 1], [2, 1], 0),
     "pairs1_row_stride": (8, 64, 64, 80, 64, 3, 3, [1, 1, 1, 1], [2, 1], [1, 1], 0),
+    # 128-byte K blocks, output rows of 40 to 112 pixels: windows that wrap rows inside a tile, with every W / H parameter in turn
+    "rows_c128_two_per_tile": (3, 128, 24, 56, 96, 3, 3, [1, 1, 1, 1], [1, 1], [1, 1], 0),
+    "rows_c128_w112_dilated": (2, 128, 10, 112, 64, 3, 3, [2, 2, 2, 2], [1, 1], [2, 2], 0),
+    "rows_c256_row_stride": (2, 256, 35, 40, 64, 3, 3, [1, 1, 1, 1], [2, 1], [1, 1], 0),
+    "rows_c128_5x3_asymmetric": (2, 128, 20, 48, 272, 5, 3, [3, 0, 1, 2], [1, 1], [1, 1], 0),
 }
 
 
